@@ -1,0 +1,6 @@
+"""Simulator + planners (CPU only)."""
+from .schema import (Event, EventLog, MemoryTracePoint, Object, OutputAlloc, Task, TaskChain,
+                     TaskInterval, TransferTrigger)
+from .errors import SimulationCapacityError, SimulationError
+from .simulator import Simulator, compute_lower_bound, run
+from .validate import ValidationError, validate_chain, validate_planning_input
