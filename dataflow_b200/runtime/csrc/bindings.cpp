@@ -1,0 +1,234 @@
+// Python bindings of the native runtime (pybind11): backends, session, executor,
+// slab allocator.  The module never imports torch.
+#include <pybind11/functional.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <atomic>
+
+#include "backends_host.hpp"
+#include "engine.hpp"
+#ifdef DFB_WITH_CUDA
+#include <nvtx3/nvToolsExt.h>
+
+#include "backend_cuda.hpp"
+#include "vmm.hpp"
+#endif
+
+namespace py = pybind11;
+using namespace dfb;
+
+static std::atomic<bool> g_nvtx{false};
+
+static py::dict result_to_py(const RunResult& r) {
+  py::dict d;
+  d["outcome"] = r.outcome;
+  d["message"] = r.message;
+  d["failed_task"] = r.failed_task;
+  d["error_kind"] = r.error_kind;
+  py::list iv;
+  for (auto& i : r.intervals) iv.append(py::make_tuple(i.name, i.track, i.start, i.end));
+  d["intervals"] = iv;
+  py::list ev;
+  for (auto& e : r.events) ev.append(py::make_tuple(e.kind, e.what, e.fast_bytes));
+  d["events"] = ev;
+  py::dict s;
+  s["makespan_us"] = r.stats.makespan_us;
+  s["peak_fast_bytes"] = r.stats.peak_fast;
+  s["peak_backing_bytes"] = r.stats.peak_backing;
+  s["slab_overflows"] = r.stats.slab_overflows;
+  s["vendor_allocs"] = r.stats.vendor_allocs;
+  s["pressure_evictions"] = r.stats.pressure_evictions;
+  s["placement_escapes"] = r.stats.placement_escapes;
+  s["h2d_bytes"] = r.stats.h2d_bytes;
+  s["d2h_bytes"] = r.stats.d2h_bytes;
+  s["h2d_count"] = r.stats.h2d_count;
+  s["d2h_count"] = r.stats.d2h_count;
+  s["dispatch_us_total"] = r.stats.dispatch_us_total;
+  s["wait_us_total"] = r.stats.wait_us_total;
+  d["stats"] = s;
+  py::dict f;
+  for (auto& b : r.finals) f[py::str(b.id)] = py::make_tuple(b.loc, b.ptr, b.size, b.external);
+  d["finals"] = f;
+  return d;
+}
+
+PYBIND11_MODULE(_runtime, m) {
+  m.doc() = "dataflow_b200 native runtime: backends, session, task executor";
+  m.attr("PRIO_H2D_DONE") = PRIO_H2D_DONE;
+  m.attr("PRIO_D2H_DONE") = PRIO_D2H_DONE;
+  m.attr("PRIO_TASK") = PRIO_TASK;
+#ifdef DFB_WITH_CUDA
+  m.attr("with_cuda") = true;
+#else
+  m.attr("with_cuda") = false;
+#endif
+
+  py::class_<Backend, std::shared_ptr<Backend>>(m, "Backend")
+      .def("name", &Backend::name)
+      .def("is_virtual", &Backend::is_virtual)
+      .def("synchronize", &Backend::synchronize)
+      .def("pending", &Backend::pending)
+      .def("create_stream", &Backend::create_stream)
+      .def("stream_handle", &Backend::stream_handle)
+      .def("record_event", &Backend::record_event)
+      .def("release_event", &Backend::release_event)
+      .def("event_time_us", &Backend::event_time_us)
+      .def("mark_epoch", &Backend::mark_epoch)
+      .def("busy", &Backend::busy)
+      .def("alloc", [](Backend& b, int loc, size_t n) { return reinterpret_cast<uint64_t>(b.alloc(static_cast<Location>(loc), n)); })
+      .def("free", [](Backend& b, int loc, uint64_t p, size_t n) { b.free(static_cast<Location>(loc), reinterpret_cast<void*>(p), n); })
+      .def("memcpy_async", [](Backend& b, uint64_t dst, uint64_t src, size_t n, int stream) {
+        b.memcpy_async(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), n, stream, 0.0);
+      })
+      .def("memset_async", [](Backend& b, uint64_t dst, int v, size_t n, int stream) {
+        b.memset_async(reinterpret_cast<void*>(dst), v, n, stream);
+      });
+
+  py::class_<FakeBackend, Backend, std::shared_ptr<FakeBackend>>(m, "FakeBackend")
+      .def(py::init<>())
+      .def_readwrite("transfer_time_scale", &FakeBackend::transfer_time_scale)
+      .def_readwrite("compute_time_scale", &FakeBackend::compute_time_scale)
+      .def("now", &FakeBackend::now);
+
+  py::class_<CpuBackend, Backend, std::shared_ptr<CpuBackend>>(m, "CpuBackend")
+      .def(py::init<>())
+      .def_readwrite("spin_busy", &CpuBackend::spin_busy);
+
+#ifdef DFB_WITH_CUDA
+  py::class_<CudaBackend, Backend, std::shared_ptr<CudaBackend>>(m, "CudaBackend")
+      .def(py::init<int, const char*>(), py::arg("device") = 0, py::arg("completion") = "poll")
+      .def("device", &CudaBackend::device)
+      .def_readonly("device_allocs", &CudaBackend::device_allocs)
+      .def_readonly("host_allocs", &CudaBackend::host_allocs)
+      .def("pin_region", [](CudaBackend& b, size_t n, bool populate) {
+        py::gil_scoped_release rel;
+        return reinterpret_cast<uint64_t>(b.pin_region(n, populate));
+      }, py::arg("bytes"), py::arg("populate") = true)
+      .def("unpin_region", [](CudaBackend& b, uint64_t p, size_t n) { b.unpin_region(reinterpret_cast<void*>(p), n); })
+      .def("measure_pcie", [](CudaBackend& b, size_t bytes, int repeats) {
+        double out[4];
+        {
+          py::gil_scoped_release rel;
+          b.measure_pcie(bytes, repeats, out);
+        }
+        py::dict d;
+        d["h2d_gbs"] = out[0]; d["d2h_gbs"] = out[1]; d["h2d_bidi_gbs"] = out[2]; d["d2h_bidi_gbs"] = out[3];
+        return d;
+      }, py::arg("bytes") = (256u << 20), py::arg("repeats") = 4);
+
+  py::class_<VmmArena, std::shared_ptr<VmmArena>>(m, "VmmArena")
+      .def(py::init<int, size_t>(), py::arg("device"), py::arg("va_bytes"))
+      .def("available", &VmmArena::available)
+      .def("granule", &VmmArena::granule)
+      .def("base", &VmmArena::base)
+      .def("map", &VmmArena::map)
+      .def("unmap", &VmmArena::unmap)
+      .def("mapped_bytes", &VmmArena::mapped_bytes)
+      .def("parked_bytes", &VmmArena::parked_bytes)
+      .def("trim", &VmmArena::trim)
+      .def("driver_calls", &VmmArena::driver_calls);
+  m.def("set_nvtx", [](bool on) { g_nvtx.store(on); });
+  m.def("nvtx_mark", [](const std::string& s) { if (g_nvtx.load()) nvtxMarkA(s.c_str()); });
+#else
+  m.def("set_nvtx", [](bool) {});
+  m.def("nvtx_mark", [](const std::string&) {});
+#endif
+
+  py::class_<SlabAllocator>(m, "SlabAllocator")
+      .def(py::init<size_t, size_t>(), py::arg("capacity"), py::arg("align") = 512)
+      .def("allocate", [](SlabAllocator& s, size_t n) -> py::object {
+        size_t off = s.allocate(n);
+        if (off == SlabAllocator::kNone) return py::none();
+        return py::int_(off);
+      })
+      .def("allocate_at", &SlabAllocator::allocate_at)
+      .def("release", &SlabAllocator::release)
+      .def("capacity", &SlabAllocator::capacity)
+      .def("used", &SlabAllocator::used)
+      .def("peak", &SlabAllocator::peak)
+      .def("largest_free", &SlabAllocator::largest_free)
+      .def("live_blocks", &SlabAllocator::live_blocks)
+      .def("block_size", &SlabAllocator::block_size);
+
+  py::class_<ObjIR>(m, "ObjIR").def(py::init<>())
+      .def_readwrite("id", &ObjIR::id).def_readwrite("size", &ObjIR::size)
+      .def_readwrite("init_fast", &ObjIR::init_fast).def_readwrite("init_backing", &ObjIR::init_backing)
+      .def_readwrite("final_loc", &ObjIR::final_loc).def_readwrite("last_ref", &ObjIR::last_ref);
+  py::class_<TaskIR>(m, "TaskIR").def(py::init<>())
+      .def_readwrite("id", &TaskIR::id).def_readwrite("inputs", &TaskIR::inputs)
+      .def_readwrite("mutates", &TaskIR::mutates).def_readwrite("releases", &TaskIR::releases)
+      .def_readwrite("runtime_us", &TaskIR::runtime_us).def_readwrite("workspace", &TaskIR::workspace)
+      .def("add_output", [](TaskIR& t, int obj, int loc) { t.outputs.push_back({obj, loc}); })
+      .def("add_offload", [](TaskIR& t, int obj, double us) { t.offloads.push_back({obj, us}); })
+      .def("add_prefetch", [](TaskIR& t, int obj, double us) { t.prefetches.push_back({obj, us}); });
+  py::class_<ProgramIR, std::shared_ptr<ProgramIR>>(m, "ProgramIR").def(py::init<>())
+      .def_readwrite("name", &ProgramIR::name)
+      .def_readwrite("fast_cap", &ProgramIR::fast_cap).def_readwrite("backing_cap", &ProgramIR::backing_cap)
+      .def_readwrite("bw_from", &ProgramIR::bw_from).def_readwrite("bw_to", &ProgramIR::bw_to)
+      .def("add_obj", [](ProgramIR& p, const ObjIR& o) { p.objs.push_back(o); return p.objs.size() - 1; })
+      .def("add_task", [](ProgramIR& p, const TaskIR& t) { p.tasks.push_back(t); return p.tasks.size() - 1; })
+      .def("num_tasks", [](ProgramIR& p) { return p.tasks.size(); })
+      .def("num_objs", [](ProgramIR& p) { return p.objs.size(); });
+
+  py::class_<Session, std::shared_ptr<Session>>(m, "Session")
+      .def(py::init<std::shared_ptr<Backend>>())
+      .def_readonly("compute_stream", &Session::compute_stream)
+      .def_readonly("h2d_stream", &Session::h2d_stream)
+      .def_readonly("d2h_stream", &Session::d2h_stream)
+      .def("ensure_pools", &Session::ensure_pools, py::arg("fast_cap"), py::arg("backing_cap"), py::arg("headroom") = 0.0)
+      .def("fast_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.fast_pool.slab_base()), s.fast_pool.slab_capacity()); })
+      .def("backing_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.backing_pool.slab_base()), s.backing_pool.slab_capacity()); })
+      .def("vendor_allocs", [](Session& s) { return s.fast_pool.vendor_allocs + s.backing_pool.vendor_allocs; })
+      .def("trim", [](Session& s) { s.fast_pool.trim(); s.backing_pool.trim(); });
+
+  py::class_<std::atomic<bool>, std::shared_ptr<std::atomic<bool>>>(m, "CancelFlag")
+      .def(py::init([]() { return std::make_shared<std::atomic<bool>>(false); }))
+      .def("set", [](std::atomic<bool>& f) { f.store(true); })
+      .def("clear", [](std::atomic<bool>& f) { f.store(false); })
+      .def("is_set", [](std::atomic<bool>& f) { return f.load(); });
+
+  py::class_<Engine>(m, "Engine")
+      .def(py::init<std::shared_ptr<Session>>())
+      .def("execute",
+           [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
+              bool strict_final, bool poison, bool record_events, double headroom,
+              std::shared_ptr<std::atomic<bool>> cancel) {
+             std::unordered_map<std::string, InitialBuffer> init;
+             for (auto kv : initial) {
+               auto t = kv.second.cast<py::tuple>();
+               init[kv.first.cast<std::string>()] = {t[0].cast<uint64_t>(), t[1].cast<size_t>(), t[2].cast<int>()};
+             }
+             ExecOptions opt;
+             opt.strict_final_locations = strict_final;
+             opt.poison_on_free = poison;
+             opt.record_events = record_events;
+             opt.slab_headroom = headroom;
+             opt.cancel = cancel ? cancel.get() : nullptr;
+             LaunchFn fn;
+             if (!launch.is_none()) {
+               fn = [launch](const LaunchArgs& a) {
+                 py::gil_scoped_acquire gil;
+                 launch(a.task_index, a.input_ptrs, a.output_ptrs, a.stream_handle);
+               };
+             }
+             RangeFn range;
+#ifdef DFB_WITH_CUDA
+             if (g_nvtx.load()) {
+               range = [](const std::string& name, bool push) {
+                 if (push) nvtxRangePushA(name.c_str()); else nvtxRangePop();
+               };
+             }
+#endif
+             RunResult r;
+             {
+               py::gil_scoped_release rel;
+               r = e.execute(*p, fn, init, opt, range);
+             }
+             return result_to_py(r);
+           },
+           py::arg("program"), py::arg("launch") = py::none(), py::arg("initial") = py::dict(),
+           py::arg("strict_final_locations") = true, py::arg("poison_on_free") = false,
+           py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
+           py::arg("cancel") = std::shared_ptr<std::atomic<bool>>());
+}

@@ -1,0 +1,207 @@
+// Task executor: runs one annotated program over a Backend.
+//
+// One control thread.  Every state change happens in a completion handler, in
+// the order the planner's simulator models:
+//   task done  : outputs live -> mutations bump versions -> releases (dead-everywhere
+//                frees the backing copy too) -> offload enqueue -> prefetch enqueue
+//                (deferred while the same object's offload is pending) -> poke lanes
+//   h2d done   : fast copy live -> poke lanes
+//   d2h done   : fast copy freed, backing copy live, deferred prefetches join the
+//                h2d queue -> poke lanes
+// Dispatch is strictly paced: task i+1 is launched only after task i's token was
+// observed, all its inputs are live in fast memory and the ledger admits its fast
+// outputs.  Two FIFO transfer lanes, one transfer in flight each, destination bytes
+// charged when the transfer starts.  Behavioural parity: reference
+// src/dataflow/runtime/engine.py:508-1329 and transfers.py:46-244.
+#pragma once
+#include <atomic>
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "backend.hpp"
+#include "slab.hpp"
+
+namespace dfb {
+
+struct ObjIR {
+  std::string id;
+  int64_t size = 0;
+  bool init_fast = false, init_backing = false;
+  int final_loc = -1;      // -1 none, else Location
+  int last_ref = -1;       // last task index that reads it or names it in a directive
+};
+struct OutIR { int obj; int loc; };
+struct DirIR { int obj; double runtime_us; };   // runtime_us < 0: derive from bandwidth
+struct TaskIR {
+  std::string id;
+  std::vector<int> inputs, mutates, releases;
+  std::vector<OutIR> outputs;
+  std::vector<DirIR> offloads, prefetches;
+  double runtime_us = 1.0;
+  int64_t workspace = 0;
+};
+struct ProgramIR {
+  std::string name;
+  std::vector<ObjIR> objs;
+  std::vector<TaskIR> tasks;
+  int64_t fast_cap = -1, backing_cap = -1;    // -1: unbounded
+  int64_t bw_from = 0, bw_to = 0;             // bytes per microsecond
+};
+
+struct BufferRef {
+  void* ptr = nullptr;
+  size_t size = 0;
+  size_t slab_off = SlabAllocator::kNone;     // kNone: not from a slab
+  bool external = false;                      // caller-owned (store extent); never freed here
+  bool overflow = false;                      // vendor allocation outside the slab
+};
+
+// Per-location buffer source.  Bounded locations carve from one slab allocation;
+// unbounded ones recycle exact-size vendor allocations.
+class BufferPool {
+ public:
+  BufferPool(Backend* be, Location loc) : be_(be), loc_(loc) {}
+  ~BufferPool();
+  void ensure_slab(size_t capacity);
+  BufferRef get(size_t bytes);
+  void put(BufferRef& b);
+  void trim();
+  size_t slab_capacity() const { return slab_ ? slab_->capacity() : 0; }
+  void* slab_base() const { return base_; }
+  int64_t slab_overflows = 0;
+  int64_t vendor_allocs = 0;
+ private:
+  Backend* be_;
+  Location loc_;
+  void* base_ = nullptr;
+  std::unique_ptr<SlabAllocator> slab_;
+  std::multimap<size_t, void*> free_exact_;
+};
+
+// Streams and pools that outlive one execute() so steady-state steps allocate nothing.
+class Session {
+ public:
+  explicit Session(std::shared_ptr<Backend> be);
+  ~Session();
+  std::shared_ptr<Backend> backend;
+  int compute_stream, h2d_stream, d2h_stream;
+  BufferPool fast_pool, backing_pool;
+  void ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom);
+};
+
+enum class SlotState : int { ABSENT = 0, RESERVED, LIVE, PENDING_OUTBOUND, OUTBOUND, INBOUND };
+
+struct Slot {
+  SlotState state = SlotState::ABSENT;
+  BufferRef buf;
+  int64_t version = -1;
+  int ready_event = -1;       // event after which the bytes are valid for other streams
+};
+
+struct ObjState {
+  Slot fast, backing;
+  int64_t version = 0;
+};
+
+struct Interval { std::string name; std::string track; double start, end; };
+struct TraceEvent { double t; std::string kind; std::string what; int64_t fast_bytes; };
+
+struct RunStats {
+  double makespan_us = 0;
+  int64_t peak_fast = 0, peak_backing = 0;
+  int64_t slab_overflows = 0, pressure_evictions = 0, placement_escapes = 0, vendor_allocs = 0;
+  int64_t h2d_bytes = 0, d2h_bytes = 0, h2d_count = 0, d2h_count = 0;
+  double dispatch_us_total = 0;      // host time spent inside launch callbacks
+  double wait_us_total = 0;          // host time spent blocked on completions
+};
+
+struct FinalBuffer { std::string id; int loc; uint64_t ptr; size_t size; bool external; };
+
+struct RunResult {
+  std::string outcome = "SUCCESS";   // SUCCESS | FAILED | CANCELLED
+  std::string message, failed_task, error_kind;
+  std::vector<Interval> intervals;
+  std::vector<TraceEvent> events;
+  RunStats stats;
+  std::vector<FinalBuffer> finals;
+};
+
+struct LaunchArgs {
+  int task_index;
+  std::vector<uint64_t> input_ptrs, output_ptrs;
+  std::vector<size_t> input_sizes, output_sizes;
+  uint64_t stream_handle;
+};
+
+using LaunchFn = std::function<void(const LaunchArgs&)>;
+using RangeFn = std::function<void(const std::string&, bool)>;   // (name, push?) for NVTX
+
+struct InitialBuffer { uint64_t ptr; size_t size; int loc; };
+
+struct ExecOptions {
+  bool strict_final_locations = true;
+  bool poison_on_free = false;
+  bool record_events = false;
+  bool keep_finals = true;          // hand final backing buffers to the caller instead of freeing
+  double slab_headroom = 0.0;
+  std::atomic<bool>* cancel = nullptr;
+};
+
+class Engine {
+ public:
+  Engine(std::shared_ptr<Session> s) : sess_(std::move(s)), be_(sess_->backend.get()) {}
+  RunResult execute(const ProgramIR& p, const LaunchFn& launch,
+                    const std::unordered_map<std::string, InitialBuffer>& initial,
+                    const ExecOptions& opt, const RangeFn& range);
+
+ private:
+  struct Xfer { int obj; int dir; int64_t size; double runtime_us; };   // dir 0 = from_slow, 1 = to_slow
+  struct Flight { Xfer x; int start_ev, end_ev; std::string name; };
+
+  void run_dispatch(const ProgramIR& p, const LaunchFn& launch,
+                    const std::unordered_map<std::string, InitialBuffer>& initial,
+                    const ExecOptions& opt, const RangeFn& range, RunResult& out);
+  void load_initial(const std::unordered_map<std::string, InitialBuffer>& initial);
+  bool try_start(int dir);
+  void poke() { try_start(0); try_start(1); }
+  void handle(const Completion& c);
+  void on_task_done(int idx);
+  void on_transfer_done(int dir);
+  bool pump_one(bool block);
+  void charge(Location loc, int64_t bytes);
+  void uncharge(Location loc, int64_t bytes);
+  int64_t free_bytes(Location loc) const;
+  void free_slot(Slot& s, Location loc);
+  double xfer_us(const Xfer& x) const;
+  void note(const std::string& kind, const std::string& what);
+  [[noreturn]] void deadlock(const std::string& why);
+  void cleanup(bool failed);
+
+  std::shared_ptr<Session> sess_;
+  Backend* be_;
+  const ProgramIR* p_ = nullptr;
+  const ExecOptions* opt_ = nullptr;
+  RunResult* out_ = nullptr;
+  std::vector<ObjState> objs_;
+  int64_t used_[2] = {0, 0};
+  int64_t workspace_ = 0;
+  std::deque<Xfer> queue_[2];
+  std::unique_ptr<Flight> flight_[2];
+  std::unordered_map<int, std::vector<Xfer>> deferred_;
+  std::map<std::pair<int, int>, int> xfer_seq_;
+  int task_done_upto_ = -1;
+  int running_task_ = -1;
+  int task_start_ev_ = -1, task_end_ev_ = -1;
+  std::vector<int> events_to_release_;
+  struct PendingInterval { std::string name, track; int ev0, ev1; };
+  std::vector<PendingInterval> pending_intervals_;
+};
+
+ProgramIR make_program_ir();   // helper for bindings
+
+}  // namespace dfb
