@@ -120,7 +120,7 @@ def build_ops(force: bool = False, verbose: bool = False) -> Path:
     inc = tinc + [f"-I{sysconfig.get_paths()['include']}", f"-I{src}"] + _cutlass_include()
     common = ["-O3", "-std=c++17", "-DTORCH_EXTENSION_NAME=_ops", "-DTORCH_API_INCLUDE_EXTENSION_H",
               "-D_GLIBCXX_USE_CXX11_ABI=1"]
-    nv = [NVCC] + common + ["-Xcompiler", "-fPIC", "-lineinfo", "--use_fast_math", "--expt-relaxed-constexpr",
+    nv = [NVCC] + common + ["-Xcompiler", "-fPIC", "-lineinfo", "--expt-relaxed-constexpr",
                             "--expt-extended-lambda", "-Xptxas", "-v" if verbose else "-O3",
                             "-D__CUDA_NO_HALF_OPERATORS__", "-D__CUDA_NO_HALF_CONVERSIONS__",
                             "-D__CUDA_NO_BFLOAT16_CONVERSIONS__", "-D__CUDA_NO_HALF2_OPERATORS__"] + ARCH_FLAGS

@@ -1,0 +1,215 @@
+// Torch-facing bindings of the kernel launch API: tensors in, raw pointers out,
+// on the current CUDA stream.  Shape / dtype / contiguity checks live here so
+// the kernels can assume their contracts.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "ops.h"
+
+using at::Tensor;
+
+#define CHECK_CUDA(x) TORCH_CHECK((x).is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_BF16(x) TORCH_CHECK((x).scalar_type() == at::kBFloat16, #x " must be bf16")
+#define CHECK_F32(x) TORCH_CHECK((x).scalar_type() == at::kFloat, #x " must be fp32")
+#define CHECK_I32(x) TORCH_CHECK((x).scalar_type() == at::kInt, #x " must be int32")
+#define CHECK_CONTIG(x) TORCH_CHECK((x).is_contiguous(), #x " must be contiguous")
+
+static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+static const void* optp(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+static int num_sms() {
+  static int n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// ---------------------------------------------------------------- norms
+static void rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& w, Tensor& y, c10::optional<Tensor> rstd, double eps) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_CONTIG(x); CHECK_BF16(y); CHECK_CONTIG(y);
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  dfb::rmsnorm_fwd(x.data_ptr(), optp(w), y.data_ptr(), rstd.has_value() ? rstd->data_ptr<float>() : nullptr, rows, cols,
+                   (float)eps, cur_stream());
+}
+static void rmsnorm_apply(const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& y) {
+  CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(rstd); CHECK_CONTIG(y);
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  dfb::rmsnorm_apply(x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), y.data_ptr(), rows, cols, cur_stream());
+}
+static void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& dx,
+                        const c10::optional<Tensor>& dx_add, c10::optional<Tensor> dw, bool accumulate, Tensor& partial) {
+  CHECK_BF16(dy); CHECK_CONTIG(dy); CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(rstd); CHECK_F32(partial);
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "rmsnorm_bwd needs cols % 8 == 0");
+  TORCH_CHECK(partial.numel() >= (int64_t)dfb::norm_bwd_parts(rows) * 2 * cols, "rmsnorm_bwd scratch too small");
+  dfb::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), optp(dx_add),
+                   dw.has_value() ? dw->data_ptr() : nullptr, dw.has_value() && dw->scalar_type() == at::kFloat,
+                   accumulate, partial.data_ptr<float>(), rows, cols, cur_stream());
+}
+static void layernorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, Tensor& y, Tensor& mean,
+                          Tensor& rstd, double eps) {
+  CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(mean); CHECK_F32(rstd);
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  dfb::layernorm_fwd(x.data_ptr(), w.data_ptr(), optp(b), y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                     rows, cols, (float)eps, cur_stream());
+}
+static void layernorm_apply(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, const Tensor& mean,
+                            const Tensor& rstd, Tensor& y) {
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  dfb::layernorm_apply(x.data_ptr(), w.data_ptr(), optp(b), mean.data_ptr<float>(), rstd.data_ptr<float>(), y.data_ptr(),
+                       rows, cols, cur_stream());
+}
+static void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean, const Tensor& rstd,
+                          Tensor& dx, const c10::optional<Tensor>& dx_add, c10::optional<Tensor> dw,
+                          c10::optional<Tensor> db, bool accumulate, Tensor& partial) {
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "layernorm_bwd needs cols % 8 == 0");
+  TORCH_CHECK(partial.numel() >= (int64_t)dfb::norm_bwd_parts(rows) * 2 * cols, "layernorm_bwd scratch too small");
+  dfb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                     dx.data_ptr(), optp(dx_add), dw.has_value() ? dw->data_ptr() : nullptr,
+                     db.has_value() ? db->data_ptr() : nullptr, dw.has_value() && dw->scalar_type() == at::kFloat,
+                     accumulate, partial.data_ptr<float>(), rows, cols, cur_stream());
+}
+static int64_t norm_bwd_scratch_elems(int64_t rows, int64_t cols) { return (int64_t)dfb::norm_bwd_parts((int)rows) * 2 * cols; }
+
+// ---------------------------------------------------------------- pointwise
+static void rope_inplace(Tensor& x, const Tensor& positions, int64_t heads, int64_t rot_dim, int64_t row_stride,
+                         int64_t head_stride, int64_t col_base, double theta, bool backward) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_I32(positions);
+  int tokens = positions.numel();
+  dfb::rope_inplace(x.data_ptr(), positions.data_ptr<int>(), tokens, (int)heads, (int)rot_dim, row_stride, (int)head_stride,
+                    (int)col_base, (float)theta, backward, cur_stream());
+}
+static void swiglu_fwd(const Tensor& x1, const Tensor& x3, Tensor& out, int64_t rows, int64_t F, int64_t ld1, int64_t ld3) {
+  CHECK_BF16(x1); CHECK_BF16(out); TORCH_CHECK(F % 8 == 0 && ld1 % 8 == 0 && ld3 % 8 == 0, "swiglu: dims must be multiples of 8");
+  dfb::swiglu_fwd(x1.data_ptr(), x3.data_ptr(), out.data_ptr(), rows, (int)F, ld1, ld3, cur_stream());
+}
+static void swiglu_bwd(const Tensor& ds, const Tensor& x1, const Tensor& x3, Tensor& dx1, Tensor& dx3, int64_t rows,
+                       int64_t F, int64_t ld1, int64_t ld3, int64_t ldd1, int64_t ldd3) {
+  TORCH_CHECK(F % 8 == 0, "swiglu: F must be a multiple of 8");
+  dfb::swiglu_bwd(ds.data_ptr(), x1.data_ptr(), x3.data_ptr(), dx1.data_ptr(), dx3.data_ptr(), rows, (int)F, ld1, ld3, ldd1,
+                  ldd3, cur_stream());
+}
+static void gelu_fwd(const Tensor& x, Tensor& y) { TORCH_CHECK(x.numel() % 8 == 0); dfb::gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), cur_stream()); }
+static void gelu_bwd(const Tensor& dy, const Tensor& x, Tensor& dx) { TORCH_CHECK(x.numel() % 8 == 0); dfb::gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), cur_stream()); }
+static void add_bf16(const Tensor& a, const Tensor& b, Tensor& out) { TORCH_CHECK(a.numel() % 8 == 0); dfb::add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream()); }
+static void colsum_bf16(const Tensor& x, Tensor& partial, Tensor& out, bool accumulate) {
+  CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(partial);
+  int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(partial.numel() >= (int64_t)dfb::colsum_parts(rows) * cols, "colsum scratch too small");
+  dfb::colsum_bf16(x.data_ptr(), partial.data_ptr<float>(), out.data_ptr(), accumulate, rows, cols, cur_stream());
+}
+static void adamw_bf16(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
+                       double wd, int64_t step, double gscale) {
+  CHECK_BF16(w); CHECK_BF16(m); CHECK_BF16(v);
+  dfb::adamw_bf16(w.data_ptr(), g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(), v.data_ptr(), w.numel(), lr, b1,
+                  b2, eps, wd, (int)step, gscale, cur_stream());
+}
+static void adamw_master(Tensor& master, Tensor& w_out, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1,
+                         double b2, double eps, double wd, int64_t step, double gscale) {
+  CHECK_F32(master); CHECK_BF16(w_out); CHECK_F32(m); CHECK_F32(v);
+  dfb::adamw_master(master.data_ptr<float>(), w_out.data_ptr(), g.data_ptr(), g.scalar_type() == at::kFloat,
+                    m.data_ptr<float>(), v.data_ptr<float>(), master.numel(), lr, b1, b2, eps, wd, (int)step, gscale,
+                    cur_stream());
+}
+static void adamw_f32(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
+                      double wd, int64_t step, double gscale) {
+  CHECK_F32(w); CHECK_F32(g); CHECK_F32(m); CHECK_F32(v);
+  dfb::adamw_f32(w.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), w.numel(), lr, b1, b2,
+                 eps, wd, (int)step, gscale, cur_stream());
+}
+static void sgd_bf16(Tensor& w, const Tensor& g, c10::optional<Tensor> m, double lr, double mu, double wd) {
+  dfb::sgd_bf16(w.data_ptr(), g.data_ptr(), m.has_value() ? m->data_ptr() : nullptr, w.numel(), lr, mu, wd, cur_stream());
+}
+
+// ---------------------------------------------------------------- loss / embedding
+static void ce_loss_fwd_bwd(Tensor& logits, const Tensor& targets, Tensor& nll_rows, c10::optional<Tensor> loss,
+                            bool accumulate, double scale) {
+  CHECK_CUDA(logits); CHECK_BF16(logits); CHECK_I32(targets); CHECK_F32(nll_rows);
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "logits must be (rows, vocab), row stride % 8 == 0");
+  dfb::ce_loss_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), nll_rows.data_ptr<float>(),
+                       loss.has_value() ? loss->data_ptr<float>() : nullptr, accumulate, logits.size(0), logits.size(1),
+                       logits.stride(0), (float)scale, cur_stream());
+}
+static void embed_fwd(const Tensor& tok, const Tensor& table, Tensor& out, const c10::optional<Tensor>& positions,
+                      const c10::optional<Tensor>& pos_table) {
+  CHECK_I32(tok); CHECK_BF16(table); CHECK_CONTIG(table);
+  int d = table.size(1);
+  TORCH_CHECK(d % 8 == 0, "embedding width must be a multiple of 8");
+  dfb::embed_fwd(tok.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tok.numel(), d,
+                 positions.has_value() ? positions->data_ptr<int>() : nullptr, optp(pos_table), cur_stream());
+}
+static void embed_bwd_sorted(const Tensor& sorted_key, const Tensor& order, const Tensor& dy, Tensor& dtable, bool accumulate) {
+  CHECK_I32(sorted_key); CHECK_I32(order); CHECK_BF16(dy); CHECK_CONTIG(dy);
+  int d = dy.size(-1);
+  dfb::embed_bwd_sorted(sorted_key.data_ptr<int>(), order.data_ptr<int>(), dy.data_ptr(), dtable.data_ptr(),
+                        dtable.scalar_type() == at::kFloat, sorted_key.numel(), d, accumulate, cur_stream());
+}
+
+// ---------------------------------------------------------------- GEMM
+// D(M,N) = op(A) * op(B) (+ addend) (+ bias).  A is (M,K) row-major, or (K,M) row-major when a_mn.
+// B is (N,K) row-major, or (K,N) row-major when b_mn.
+static void gemm_bf16(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& D,
+                      const c10::optional<Tensor>& addend, const c10::optional<Tensor>& bias) {
+  CHECK_CUDA(A); CHECK_BF16(A); CHECK_BF16(B);
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && D.dim() == 2, "gemm operands must be 2-D");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && D.stride(1) == 1, "gemm operands must have unit inner stride");
+  int M = a_mn ? A.size(1) : A.size(0), K = a_mn ? A.size(0) : A.size(1);
+  int N = b_mn ? B.size(1) : B.size(0), Kb = b_mn ? B.size(0) : B.size(1);
+  TORCH_CHECK(K == Kb, "gemm reduction dims differ: ", K, " vs ", Kb);
+  TORCH_CHECK(D.size(0) == M && D.size(1) == N, "gemm output shape mismatch");
+  bool d32 = D.scalar_type() == at::kFloat;
+  TORCH_CHECK(d32 || D.scalar_type() == at::kBFloat16, "gemm output must be bf16 or fp32");
+  bool a32 = false;
+  long long ld_add = 0;
+  if (addend.has_value()) {
+    a32 = addend->scalar_type() == at::kFloat;
+    TORCH_CHECK(addend->stride(1) == 1 && addend->size(0) == M && addend->size(1) == N, "addend shape mismatch");
+    ld_add = addend->stride(0);
+  }
+  if (bias.has_value()) { CHECK_BF16(*bias); TORCH_CHECK(bias->numel() == N, "bias length mismatch"); }
+  int rc = dfb::gemm_bf16(A.data_ptr(), A.stride(0), a_mn, B.data_ptr(), B.stride(0), b_mn, D.data_ptr(), D.stride(0), d32,
+                          optp(addend), ld_add, a32, optp(bias), M, N, K, num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc);
+}
+static int64_t gemm_last_error() { return dfb::gemm_bf16_last_error(); }
+
+// ---------------------------------------------------------------- interop
+// Zero-copy tensor over engine-owned memory (device or pinned host).
+static Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
+  static const std::map<std::string, at::ScalarType> types = {
+      {"bf16", at::kBFloat16}, {"fp32", at::kFloat}, {"fp16", at::kHalf}, {"int32", at::kInt}, {"int64", at::kLong},
+      {"uint8", at::kByte}, {"int8", at::kChar}, {"fp64", at::kDouble}, {"bool", at::kBool},
+      {"fp8_e4m3", at::kFloat8_e4m3fn}, {"fp8_e5m2", at::kFloat8_e5m2}};
+  auto it = types.find(dtype);
+  TORCH_CHECK(it != types.end(), "unknown dtype ", dtype);
+  auto opts = at::TensorOptions().dtype(it->second);
+  if (device >= 0) opts = opts.device(at::kCUDA, device);
+  return at::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_apply", &rmsnorm_apply);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_apply", &layernorm_apply);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("norm_bwd_scratch_elems", &norm_bwd_scratch_elems);
+  m.def("rope_inplace", &rope_inplace);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("gelu_fwd", &gelu_fwd);
+  m.def("gelu_bwd", &gelu_bwd);
+  m.def("add_bf16", &add_bf16);
+  m.def("colsum_bf16", &colsum_bf16);
+  m.def("colsum_parts", [](int64_t rows) { return (int64_t)dfb::colsum_parts((int)rows); });
+  m.def("adamw_bf16", &adamw_bf16);
+  m.def("adamw_master", &adamw_master);
+  m.def("adamw_f32", &adamw_f32);
+  m.def("sgd_bf16", &sgd_bf16);
+  m.def("ce_loss_fwd_bwd", &ce_loss_fwd_bwd);
+  m.def("embed_fwd", &embed_fwd);
+  m.def("embed_bwd_sorted", &embed_bwd_sorted);
+  m.def("gemm_bf16", &gemm_bf16);
+  m.def("gemm_last_error", &gemm_last_error);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+}

@@ -1,0 +1,60 @@
+// Plain C++ launch API of the sm_100a kernels: raw pointers, sizes and a stream.
+// No allocation happens behind these calls; scratch is passed in by the caller.
+// bf16 tensors are passed as void*.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace dfb {
+
+// ---- norms (norm.cu)
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
+void rmsnorm_apply(const void* x, const void* w, const float* rstd, void* y, int rows, int cols, cudaStream_t s);
+void layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int cols,
+                   float eps, cudaStream_t s);
+void layernorm_apply(const void* x, const void* w, const void* b, const float* mean, const float* rstd, void* y,
+                     int rows, int cols, cudaStream_t s);
+int norm_bwd_parts(int rows);   // rows of the (parts, 2, cols) fp32 scratch the backward needs
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, const void* dx_add,
+                 void* dw, int dw_is_f32, int accumulate, float* partial, int rows, int cols, cudaStream_t s);
+void layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                   const void* dx_add, void* dw, void* db, int dw_is_f32, int accumulate, float* partial, int rows,
+                   int cols, cudaStream_t s);
+
+// ---- pointwise (pointwise.cu)
+void rope_inplace(void* x, const int* positions, int tokens, int heads, int rot_dim, long long row_stride,
+                  int head_stride, int col_base, float theta, int backward, cudaStream_t s);
+void swiglu_fwd(const void* x1, const void* x3, void* out, long long rows, int F, long long ld1, long long ld3, cudaStream_t s);
+void swiglu_bwd(const void* ds, const void* x1, const void* x3, void* dx1, void* dx3, long long rows, int F,
+                long long ld1, long long ld3, long long ldd1, long long ldd3, cudaStream_t s);
+void gelu_fwd(const void* x, void* y, long long n, cudaStream_t s);
+void gelu_bwd(const void* dy, const void* x, void* dx, long long n, cudaStream_t s);
+void add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t s);
+void cast_f32_to_bf16(const float* x, void* y, long long n, cudaStream_t s);
+void cast_bf16_to_f32(const void* x, float* y, long long n, cudaStream_t s);
+int colsum_parts(int rows);
+void colsum_bf16(const void* x, float* partial, void* out, int accumulate, int rows, int cols, cudaStream_t s);
+void adamw_bf16(void* w, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2,
+                float eps, float wd, int step, float gscale, cudaStream_t s);
+void adamw_master(float* master, void* w_out, const void* g, int g_is_f32, float* m, float* v, long long n, float lr,
+                  float b1, float b2, float eps, float wd, int step, float gscale, cudaStream_t s);
+void adamw_f32(float* w, const float* g, float* m, float* v, long long n, float lr, float b1, float b2, float eps,
+               float wd, int step, float gscale, cudaStream_t s);
+void sgd_bf16(void* w, const void* g, void* m, long long n, float lr, float mu, float wd, cudaStream_t s);
+
+// ---- loss (loss.cu)
+void ce_loss_fwd_bwd(void* logits, const int* targets, float* nll_rows, float* loss, int accumulate, int rows, int vocab,
+                     long long ld, float scale, cudaStream_t s);
+
+// ---- embedding (embed.cu)
+void embed_fwd(const int* tok, const void* table, void* out, int tokens, int d, const int* positions,
+               const void* pos_table, cudaStream_t s);
+void embed_bwd_sorted(const int* sorted_key, const int* order, const void* dy, void* dtable, int dtable_is_f32, int n,
+                      int d, int accumulate, cudaStream_t s);
+
+// ---- GEMM (gemm_tcgen05.cu)
+int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,
+              int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
+              int num_sms, cudaStream_t stream);
+int gemm_bf16_last_error();
+
+}  // namespace dfb
