@@ -1,0 +1,237 @@
+"""Native lane: the hand-written sm_100a kernels (``ops/csrc``).  Registered with the
+highest priority and required to exist on a Blackwell device: if the extension
+is missing there, resolution raises instead of silently falling back.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native, native_available
+from .registry import Workspace, register
+
+P = 10
+
+
+def _native(caps):
+    if caps.get("sm100") and not native_available():
+        native()        # raises with the build hint: no silent fallback on a B200
+    return bool(caps.get("native_ops"))
+
+
+def _scratch(n, device):
+    return torch.empty(int(n), dtype=torch.float32, device=device)
+
+
+# ------------------------------------------------------------------ norms
+@register("rmsnorm_fwd", "sm100", priority=P, requires=_native, native=True)
+def rmsnorm_fwd(x, w, eps=1e-5, out=None):
+    x = x.contiguous()
+    rows = x.numel() // x.shape[-1]
+    y = out if out is not None else torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    native().rmsnorm_fwd(x, w, y, rstd, float(eps))
+    return y, rstd
+
+
+@register("rmsnorm_apply", "sm100", priority=P, requires=_native, native=True)
+def rmsnorm_apply(x, w, rstd, out=None):
+    y = out if out is not None else torch.empty_like(x)
+    native().rmsnorm_apply(x, w, rstd, y)
+    return y
+
+
+@register("rmsnorm_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+def rmsnorm_bwd(dy, x, w, rstd, dx_add=None, dw=None, accumulate=False, out=None):
+    rows, cols = x.numel() // x.shape[-1], x.shape[-1]
+    dx = out if out is not None else torch.empty_like(x)
+    part = _scratch(native().norm_bwd_scratch_elems(rows, cols), x.device)
+    native().rmsnorm_bwd(dy, x, w, rstd, dx, dx_add, dw, bool(accumulate), part)
+    return dx
+
+
+@register("layernorm_fwd", "sm100", priority=P, requires=_native, native=True)
+def layernorm_fwd(x, w, b, eps=1e-5, out=None):
+    rows = x.numel() // x.shape[-1]
+    y = out if out is not None else torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    native().layernorm_fwd(x, w, b, y, mean, rstd, float(eps))
+    return y, mean, rstd
+
+
+@register("layernorm_apply", "sm100", priority=P, requires=_native, native=True)
+def layernorm_apply(x, w, b, mean, rstd, out=None):
+    y = out if out is not None else torch.empty_like(x)
+    native().layernorm_apply(x, w, b, mean, rstd, y)
+    return y
+
+
+@register("layernorm_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+def layernorm_bwd(dy, x, w, mean, rstd, dx_add=None, dw=None, db=None, accumulate=False, out=None):
+    rows, cols = x.numel() // x.shape[-1], x.shape[-1]
+    dx = out if out is not None else torch.empty_like(x)
+    part = _scratch(native().norm_bwd_scratch_elems(rows, cols), x.device)
+    native().layernorm_bwd(dy, x, w, mean, rstd, dx, dx_add, dw, db, bool(accumulate), part)
+    return dx
+
+
+# ------------------------------------------------------------------ rope (x: (tokens, heads, head_dim) view, inner stride 1)
+def _rope(x, positions, theta, rot_dim, col_base, backward):
+    assert x.dim() == 3 and x.stride(2) == 1
+    native().rope_inplace(x, positions, x.shape[1], rot_dim or x.shape[2], x.stride(0), x.stride(1), col_base,
+                          float(theta), backward)
+    return x
+
+
+@register("rope_fwd", "sm100", priority=P, requires=_native, native=True)
+def rope_fwd(x, positions, theta, rot_dim=None, col_base=0):
+    return _rope(x, positions, theta, rot_dim, col_base, False)
+
+
+@register("rope_bwd", "sm100", priority=P, requires=_native, native=True)
+def rope_bwd(x, positions, theta, rot_dim=None, col_base=0):
+    return _rope(x, positions, theta, rot_dim, col_base, True)
+
+
+# ------------------------------------------------------------------ activations
+def _rows_ld(t):
+    assert t.stride(-1) == 1
+    F = t.shape[-1]
+    rows = t.numel() // F
+    ld = t.stride(-2) if t.dim() >= 2 else F
+    return rows, F, ld
+
+
+@register("swiglu_fwd_out", "sm100", priority=P, requires=_native, native=True)
+def swiglu_fwd_out(x1, x3, out=None):
+    rows, F, ld1 = _rows_ld(x1)
+    _, _, ld3 = _rows_ld(x3)
+    if out is None:
+        out = torch.empty(*x1.shape, dtype=x1.dtype, device=x1.device)
+    native().swiglu_fwd(x1, x3, out, rows, F, ld1, ld3)
+    return out
+
+
+@register("swiglu_bwd", "sm100", priority=P, requires=_native, native=True)
+def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None):
+    rows, F, ld1 = _rows_ld(x1)
+    _, _, ld3 = _rows_ld(x3)
+    if dx1 is None:
+        dx1 = torch.empty(*x1.shape, dtype=x1.dtype, device=x1.device)
+    if dx3 is None:
+        dx3 = torch.empty(*x3.shape, dtype=x3.dtype, device=x3.device)
+    native().swiglu_bwd(ds, x1, x3, dx1, dx3, rows, F, ld1, ld3, _rows_ld(dx1)[2], _rows_ld(dx3)[2])
+    return dx1, dx3
+
+
+@register("swiglu_packed_fwd", "sm100", priority=P, requires=_native, native=True)
+def swiglu_packed_fwd(h13, out=None):
+    F = h13.shape[-1] // 2
+    return swiglu_fwd_out(h13[..., :F], h13[..., F:], out)
+
+
+@register("swiglu_packed_bwd", "sm100", priority=P, requires=_native, native=True)
+def swiglu_packed_bwd(ds, h13, dh13=None):
+    F = h13.shape[-1] // 2
+    if dh13 is None:
+        dh13 = torch.empty_like(h13)
+    swiglu_bwd(ds, h13[..., :F], h13[..., F:], dh13[..., :F], dh13[..., F:])
+    return dh13
+
+
+@register("gelu_fwd_out", "sm100", priority=P, requires=_native, native=True)
+def gelu_fwd_out(x, out=None):
+    out = out if out is not None else torch.empty_like(x)
+    native().gelu_fwd(x, out)
+    return out
+
+
+@register("gelu_bwd", "sm100", priority=P, requires=_native, native=True)
+def gelu_bwd(dy, x, out=None):
+    out = out if out is not None else torch.empty_like(x)
+    native().gelu_bwd(dy, x, out)
+    return out
+
+
+@register("add", "sm100", priority=P, requires=_native, native=True)
+def add(a, b, out=None):
+    out = out if out is not None else torch.empty_like(a)
+    native().add_bf16(a, b, out)
+    return out
+
+
+# ------------------------------------------------------------------ loss / embedding
+@register("ce_loss_fwd_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+def ce_loss_fwd_bwd(logits, targets, total_rows, loss_out=None, accumulate=False):
+    nll = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+    if loss_out is None:
+        loss_out = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        accumulate = False
+    native().ce_loss_fwd_bwd(logits, targets, nll, loss_out, bool(accumulate), 1.0 / float(total_rows))
+    return loss_out
+
+
+@register("embed_fwd", "sm100", priority=P, requires=_native, native=True)
+def embed_fwd(tok, table, out=None, positions=None, pos_table=None):
+    if out is None:
+        out = torch.empty(tok.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    native().embed_fwd(tok, table, out, positions, pos_table)
+    return out
+
+
+@register("embed_bwd_accum", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+def embed_bwd_accum(tok, dy, dtable, accumulate=False):
+    if not accumulate:
+        dtable.zero_()
+    sorted_tok, order = torch.sort(tok, stable=True)
+    native().embed_bwd_sorted(sorted_tok.int(), order.int(), dy, dtable, True)
+    return dtable
+
+
+# ------------------------------------------------------------------ optimizers
+@register("adamw_step", "sm100", priority=P, requires=_native, native=True)
+def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, master=None, gscale=1.0):
+    if master is not None:
+        native().adamw_master(master, w, g, m, v, lr, beta1, beta2, eps, wd, int(step), gscale)
+    elif w.dtype == torch.float32:
+        native().adamw_f32(w, g, m, v, lr, beta1, beta2, eps, wd, int(step), gscale)
+    else:
+        native().adamw_bf16(w, g, m, v, lr, beta1, beta2, eps, wd, int(step), gscale)
+    return w
+
+
+@register("sgd_step", "sm100", priority=P, requires=_native, native=True)
+def sgd_step(w, g, m=None, lr=1e-2, momentum=0.0, wd=0.0):
+    native().sgd_bf16(w, g, m, lr, momentum, wd)
+    return w
+
+
+# ------------------------------------------------------------------ linear triple on the tcgen05 GEMM (W stored (in, out))
+@register("linear_fwd_bf16", "sm100", priority=P, requires=_native, native=True)
+def linear_fwd(x, w, out=None, add=None, bias=None):
+    if out is None:
+        out = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+    native().gemm_bf16(x, False, w, True, out, add, bias)          # A (M,K) K-major; B stored (K,N): N-major
+    return out
+
+
+@register("linear_dgrad_bf16", "sm100", priority=P, requires=_native, native=True)
+def linear_dgrad(dy, w, out=None, add=None):
+    if out is None:
+        out = torch.empty(dy.shape[0], w.shape[0], dtype=dy.dtype, device=dy.device)
+    native().gemm_bf16(dy, False, w, False, out, add, None)        # B = W as (N_out=in, K_red=out): K-major
+    return out
+
+
+@register("linear_wgrad_bf16", "sm100", priority=P, requires=_native, native=True)
+def linear_wgrad(x, dy, dw, accumulate=False):
+    native().gemm_bf16(x, True, dy, True, dw, dw if accumulate else None, None)   # both operands token-major
+    return dw
+
+
+@register("bias_grad", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+def bias_grad(dy, db, accumulate=False):
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    part = _scratch(native().colsum_parts(dy2.shape[0]) * dy2.shape[1], dy.device)
+    native().colsum_bf16(dy2, part, db, bool(accumulate))
+    return db

@@ -1,0 +1,415 @@
+"""Pure-PyTorch reference lane ("eager"): the oracle of every numerics test and the
+math path on machines without a GPU.  Runs on CPU or CUDA tensors of any float
+dtype; all reductions and elementwise math are done in fp32 and rounded once to
+the storage dtype.  Numerics follow the reference's eager ops
+(``src/dataflow_training/blocks/ops.py:30-500``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .registry import register
+
+RMS_EPS = 1e-5
+
+
+def _st(x, ref):
+    return x.to(ref.dtype)
+
+
+# ------------------------------------------------------------------ norms
+@register("rmsnorm_fwd", "eager")
+def rmsnorm_fwd(x, w, eps=RMS_EPS, out=None):
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1) + eps)
+    y = xf * rstd.unsqueeze(-1)
+    if w is not None:
+        y = y * w.float()
+    y = _st(y, x)
+    if out is not None:
+        out.copy_(y)
+        y = out
+    return y, rstd.reshape(-1)
+
+
+@register("rmsnorm_apply", "eager")
+def rmsnorm_apply(x, w, rstd, out=None):
+    y = _st(x.float() * rstd.reshape(*x.shape[:-1], 1) * w.float(), x)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("rmsnorm_bwd", "eager")
+def rmsnorm_bwd(dy, x, w, rstd, dx_add=None, dw=None, accumulate=False, out=None):
+    xf, g = x.float(), dy.float() * w.float()
+    r = rstd.reshape(*x.shape[:-1], 1)
+    xh = xf * r
+    dx = (g - xh * (g * xh).mean(-1, keepdim=True)) * r
+    if dx_add is not None:
+        dx = dx + dx_add.float()
+    if dw is not None:
+        gw = (dy.float() * xh).reshape(-1, x.shape[-1]).sum(0)
+        dw.copy_(_st(gw + (dw.float() if accumulate else 0), dw))
+    dx = _st(dx, x)
+    if out is not None:
+        out.copy_(dx)
+        return out
+    return dx
+
+
+@register("layernorm_fwd", "eager")
+def layernorm_fwd(x, w, b, eps=RMS_EPS, out=None):
+    xf = x.float()
+    mean = xf.mean(-1)
+    var = (xf - mean.unsqueeze(-1)).pow(2).mean(-1)
+    rstd = torch.rsqrt(var + eps)
+    y = (xf - mean.unsqueeze(-1)) * rstd.unsqueeze(-1) * w.float()
+    if b is not None:
+        y = y + b.float()
+    y = _st(y, x)
+    if out is not None:
+        out.copy_(y)
+        y = out
+    return y, mean.reshape(-1), rstd.reshape(-1)
+
+
+@register("layernorm_apply", "eager")
+def layernorm_apply(x, w, b, mean, rstd, out=None):
+    sh = (*x.shape[:-1], 1)
+    y = (x.float() - mean.reshape(sh)) * rstd.reshape(sh) * w.float()
+    if b is not None:
+        y = y + b.float()
+    y = _st(y, x)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("layernorm_bwd", "eager")
+def layernorm_bwd(dy, x, w, mean, rstd, dx_add=None, dw=None, db=None, accumulate=False, out=None):
+    sh = (*x.shape[:-1], 1)
+    xh = (x.float() - mean.reshape(sh)) * rstd.reshape(sh)
+    g = dy.float() * w.float()
+    dx = (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True)) * rstd.reshape(sh)
+    if dx_add is not None:
+        dx = dx + dx_add.float()
+    if dw is not None:
+        gw = (dy.float() * xh).reshape(-1, x.shape[-1]).sum(0)
+        dw.copy_(_st(gw + (dw.float() if accumulate else 0), dw))
+    if db is not None:
+        gb = dy.float().reshape(-1, x.shape[-1]).sum(0)
+        db.copy_(_st(gb + (db.float() if accumulate else 0), db))
+    dx = _st(dx, x)
+    if out is not None:
+        out.copy_(dx)
+        return out
+    return dx
+
+
+# ------------------------------------------------------------------ rope
+def _rope(x, positions, theta, rot_dim, col_base, sign):
+    """x: (tokens, heads, head_dim) view (any strides); rotate-half on [col_base, col_base+rot_dim)."""
+    half = rot_dim // 2
+    inv = torch.exp2(-math.log2(theta) * (2.0 * torch.arange(half, device=x.device, dtype=torch.float32) / rot_dim))
+    ang = positions.float().unsqueeze(-1) * inv
+    cs, sn = torch.cos(ang).unsqueeze(1), (torch.sin(ang) * sign).unsqueeze(1)
+    a = x[..., col_base:col_base + half].float()
+    b = x[..., col_base + half:col_base + rot_dim].float()
+    x[..., col_base:col_base + half] = _st(a * cs - b * sn, x)
+    x[..., col_base + half:col_base + rot_dim] = _st(b * cs + a * sn, x)
+    return x
+
+
+@register("rope_fwd", "eager")
+def rope_fwd(x, positions, theta, rot_dim=None, col_base=0):
+    return _rope(x, positions, theta, rot_dim or x.shape[-1], col_base, 1.0)
+
+
+@register("rope_bwd", "eager")
+def rope_bwd(x, positions, theta, rot_dim=None, col_base=0):
+    return _rope(x, positions, theta, rot_dim or x.shape[-1], col_base, -1.0)
+
+
+# ------------------------------------------------------------------ attention
+def attention_reference(q, k, v, cu_seqlens, scale=None, causal=True):
+    """Varlen causal GQA attention in fp32.  q (t, hq, d), k (t, hkv, d), v (t, hkv, dv).
+    Returns out (t, hq, dv) in q's dtype and lse (hq, t) fp32."""
+    t, hq, d = q.shape
+    hkv, dv = k.shape[1], v.shape[-1]
+    rep = hq // hkv
+    scale = scale if scale is not None else d ** -0.5
+    out = torch.empty(t, hq, dv, dtype=torch.float32, device=q.device)
+    lse = torch.empty(hq, t, dtype=torch.float32, device=q.device)
+    cu = [int(c) for c in cu_seqlens.tolist()] if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+    for s, e in zip(cu[:-1], cu[1:]):
+        if e <= s:
+            continue
+        qs = q[s:e].float().transpose(0, 1)                                 # (hq, L, d)
+        ks = k[s:e].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vs = v[s:e].float().transpose(0, 1).repeat_interleave(rep, 0)
+        sc = torch.matmul(qs, ks.transpose(1, 2)) * scale
+        if causal:
+            L = e - s
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            sc = sc.masked_fill(~mask, float("-inf"))
+        l = torch.logsumexp(sc, -1)
+        p = torch.exp(sc - l.unsqueeze(-1))
+        out[s:e] = torch.matmul(p, vs).transpose(0, 1)
+        lse[:, s:e] = l
+    return out.to(q.dtype), lse
+
+
+@register("flash_fwd", "eager")
+def flash_fwd(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
+    o, lse = attention_reference(q, k, v, cu_seqlens, scale)
+    if out is not None:
+        out.copy_(o)
+        o = out
+    return o, lse
+
+
+@register("flash_bwd", "eager")
+def flash_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale=None, dq=None, dk=None, dv=None):
+    t, hq, d = q.shape
+    hkv = k.shape[1]
+    rep = hq // hkv
+    scale = scale if scale is not None else d ** -0.5
+    dq_ = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dk_ = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+    dv_ = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    cu = [int(c) for c in cu_seqlens.tolist()] if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+    for s, e in zip(cu[:-1], cu[1:]):
+        if e <= s:
+            continue
+        L = e - s
+        qs = q[s:e].float().transpose(0, 1)
+        ks = k[s:e].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vs = v[s:e].float().transpose(0, 1).repeat_interleave(rep, 0)
+        do = dout[s:e].float().transpose(0, 1)
+        o = out[s:e].float().transpose(0, 1)
+        sc = torch.matmul(qs, ks.transpose(1, 2)) * scale
+        mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+        p = torch.exp(sc - lse[:, s:e].unsqueeze(-1))
+        dvs = torch.matmul(p.transpose(1, 2), do)
+        dp = torch.matmul(do, vs.transpose(1, 2))
+        delta = (do * o).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dq_[s:e] = torch.matmul(ds, ks).transpose(0, 1)
+        dks = torch.matmul(ds.transpose(1, 2), qs)
+        dk_[s:e] = dks.reshape(hkv, rep, L, d).sum(1).transpose(0, 1)
+        dv_[s:e] = dvs.reshape(hkv, rep, L, v.shape[-1]).sum(1).transpose(0, 1)
+    res = []
+    for buf, val, ref in ((dq, dq_, q), (dk, dk_, k), (dv, dv_, v)):
+        val = val.to(ref.dtype)
+        if buf is not None:
+            buf.copy_(val)
+            val = buf
+        res.append(val)
+    return tuple(res)
+
+
+# ------------------------------------------------------------------ activations
+def _silu_st(x1):
+    return (x1.float() * torch.sigmoid(x1.float())).to(x1.dtype).float()
+
+
+@register("swiglu_fwd_out", "eager")
+def swiglu_fwd_out(x1, x3, out=None):
+    y = _st(_silu_st(x1) * x3.float(), x1)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("swiglu_bwd", "eager")
+def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None):
+    f1, f3, g = x1.float(), x3.float(), ds.float()
+    sg = torch.sigmoid(f1)
+    sl = f1 * sg
+    d1 = _st(g * f3 * (sg + sl * (1 - sg)), x1)
+    d3 = _st(g * sl, x1)
+    if dx1 is not None:
+        dx1.copy_(d1)
+        d1 = dx1
+    if dx3 is not None:
+        dx3.copy_(d3)
+        d3 = dx3
+    return d1, d3
+
+
+@register("swiglu_packed_fwd", "eager")
+def swiglu_packed_fwd(h13, out=None):
+    F = h13.shape[-1] // 2
+    return swiglu_fwd_out(h13[..., :F], h13[..., F:], out)
+
+
+@register("swiglu_packed_bwd", "eager")
+def swiglu_packed_bwd(ds, h13, dh13=None):
+    F = h13.shape[-1] // 2
+    if dh13 is None:
+        dh13 = torch.empty_like(h13)
+    swiglu_bwd(ds, h13[..., :F], h13[..., F:], dh13[..., :F], dh13[..., F:])
+    return dh13
+
+
+@register("gelu_fwd_out", "eager")
+def gelu_fwd_out(x, out=None):
+    y = _st(torch.nn.functional.gelu(x.float(), approximate="tanh"), x)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("gelu_bwd", "eager")
+def gelu_bwd(dy, x, out=None):
+    xf = x.float()
+    k0, k1 = 0.7978845608028654, 0.044715
+    t = torch.tanh(k0 * (xf + k1 * xf ** 3))
+    g = 0.5 * (1 + t) + 0.5 * xf * (1 - t * t) * k0 * (1 + 3 * k1 * xf * xf)
+    d = _st(dy.float() * g, x)
+    if out is not None:
+        out.copy_(d)
+        return out
+    return d
+
+
+# ------------------------------------------------------------------ loss / embedding
+@register("ce_loss_fwd_bwd", "eager")
+def ce_loss_fwd_bwd(logits, targets, total_rows, loss_out=None, accumulate=False):
+    """Overwrites ``logits`` with dlogits; returns the summed loss contribution (fp32 scalar tensor)."""
+    lf = logits.float()
+    keep = (targets >= 0)
+    lse = torch.logsumexp(lf, -1)
+    tl = lf.gather(1, targets.clamp(min=0).long().unsqueeze(1)).squeeze(1)
+    scale = 1.0 / float(total_rows)
+    nll = (lse - tl) * keep.float() * scale
+    p = torch.exp(lf - lse.unsqueeze(-1))
+    p.scatter_add_(1, targets.clamp(min=0).long().unsqueeze(1), -torch.ones_like(p[:, :1]))
+    logits.copy_((p * (keep.float() * scale).unsqueeze(-1)).to(logits.dtype))
+    s = nll.sum()
+    if loss_out is not None:
+        loss_out.copy_((loss_out.float() + s if accumulate else s).reshape(loss_out.shape))
+        return loss_out
+    return s
+
+
+@register("embed_fwd", "eager")
+def embed_fwd(tok, table, out=None, positions=None, pos_table=None):
+    y = table[tok.long()]
+    if pos_table is not None:
+        y = _st(y.float() + pos_table[positions.long()].float(), table)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("embed_bwd_accum", "eager")
+def embed_bwd_accum(tok, dy, dtable, accumulate=False):
+    acc = torch.zeros(dtable.shape, dtype=torch.float32, device=dtable.device)
+    valid = tok >= 0
+    acc.index_add_(0, tok[valid].long(), dy[valid].float())
+    if accumulate:
+        acc += dtable.float()
+        dtable.copy_(acc.to(dtable.dtype))
+    else:
+        # rows not hit stay zero on a create
+        dtable.copy_(acc.to(dtable.dtype))
+    return dtable
+
+
+# ------------------------------------------------------------------ optimizers
+@register("adamw_step", "eager")
+def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, master=None, gscale=1.0):
+    gf = g.float() * gscale
+    mf = beta1 * m.float() + (1 - beta1) * gf
+    vf = beta2 * v.float() + (1 - beta2) * gf * gf
+    m.copy_(mf.to(m.dtype))
+    v.copy_(vf.to(v.dtype))
+    mh = m.float() / (1 - beta1 ** step)
+    vh = v.float() / (1 - beta2 ** step)
+    src = master if master is not None else w
+    wf = src.float()
+    wf = wf - lr * (mh / (vh.sqrt() + eps) + wd * wf)
+    if master is not None:
+        master.copy_(wf)
+    w.copy_(wf.to(w.dtype))
+    return w
+
+
+@register("sgd_step", "eager")
+def sgd_step(w, g, m=None, lr=1e-2, momentum=0.0, wd=0.0):
+    gf = g.float()
+    if m is not None:
+        m.copy_((momentum * m.float() + gf).to(m.dtype))
+        gf = m.float()
+    w.copy_((w.float() * (1 - lr * wd) - lr * gf).to(w.dtype))
+    return w
+
+
+# ------------------------------------------------------------------ linear triple (W stored (in, out))
+def _mm(a, b):
+    if a.dtype == torch.float32 or a.device.type == "cpu":
+        return a.float() @ b.float()
+    return (a @ b).float()
+
+
+@register("linear_fwd_bf16", "eager")
+def linear_fwd(x, w, out=None, add=None, bias=None):
+    y = _mm(x, w)
+    if bias is not None:
+        y = y + bias.float()
+    if add is not None:
+        y = y + add.float()
+    y = y.to(out.dtype if out is not None else x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("linear_dgrad_bf16", "eager")
+def linear_dgrad(dy, w, out=None, add=None):
+    dx = _mm(dy, w.t())
+    if add is not None:
+        dx = dx + add.float()
+    dx = dx.to(out.dtype if out is not None else dy.dtype)
+    if out is not None:
+        out.copy_(dx)
+        return out
+    return dx
+
+
+@register("linear_wgrad_bf16", "eager")
+def linear_wgrad(x, dy, dw, accumulate=False):
+    g = _mm(x.t(), dy)
+    if accumulate:
+        g = g + dw.float()
+    dw.copy_(g.to(dw.dtype))
+    return dw
+
+
+@register("bias_grad", "eager")
+def bias_grad(dy, db, accumulate=False):
+    g = dy.float().reshape(-1, dy.shape[-1]).sum(0)
+    if accumulate:
+        g = g + db.float()
+    db.copy_(g.to(db.dtype))
+    return db
+
+
+@register("add", "eager")
+def add(a, b, out=None):
+    y = _st(a.float() + b.float(), a)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
