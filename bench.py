@@ -1,0 +1,208 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of Llama-3-8B (seq 4096, bf16 + fp32 master
+weights, AdamW) under a fixed per-GPU fast-memory budget, through the framework's
+public ``Trainer`` API, on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference, same metric and config
+
+Weak scaling: every GPU processes ``--tokens-per-gpu`` tokens per step (131072 by
+default, i.e. 1M tokens per step on 8 GPUs).  Data is synthetic (uniform random
+token ids, seed 0) and weights are random-init.  Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOK_S = 12618.0     # reference's best published llama3_8b number (1x H100 80GB, seq 1024)
+
+PRESET_BUDGET_GIB = {"llama3_8b": 60.0}
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--preset", default="llama3_8b")
+    ap.add_argument("--family", default="llama3")
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=4, help="sequences per grad-accumulation round")
+    ap.add_argument("--tokens-per-gpu", type=int, default=131072)
+    ap.add_argument("--budget-gib", type=float, default=None)
+    ap.add_argument("--dtype-policy", default="bf16_master")
+    ap.add_argument("--layers", type=int, default=None, help="debug only: cut the model (the result is not a valid bench)")
+    ap.add_argument("--kernels", default=None, help="kernel lane override (e.g. baseline)")
+    ap.add_argument("--no-profile", action="store_true", help="plan from roofline seeds instead of measured task costs")
+    ap.add_argument("--parallel", default=None, help="zero3 | zero1 | co (default: zero3 when --gpus > 1)")
+    return ap.parse_args(argv)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def bench_ours(a) -> dict:
+    import dataclasses
+    import torch
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if a.gpus > 1 and world != a.gpus:
+        raise SystemExit(f"--gpus {a.gpus} needs WORLD_SIZE={a.gpus} (launch with torch.distributed.run)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.ops import cuda as cuda_lane
+    from dataflow_b200.run.driver import Trainer, synthetic_rounds
+    fam = resolve_family(a.family)
+    cfg = fam.presets[a.preset]()
+    rounds = max(a.tokens_per_gpu // (a.seq_len * a.batch), 1)
+    cfg = dataclasses.replace(cfg, seq_len=a.seq_len, batch=a.batch, grad_accum_rounds=rounds, dtype_policy=a.dtype_policy)
+    if a.layers:
+        cfg = dataclasses.replace(cfg, n_layers=a.layers)
+    budget = a.budget_gib if a.budget_gib is not None else PRESET_BUDGET_GIB.get(a.preset, 60.0)
+    parallel = a.parallel or ("zero3" if world > 1 else "solo")
+    groups, lower_kwargs = {}, None
+    if world > 1:
+        from dataflow_b200.parallel.zero import make_dp_group, zero_lower_kwargs
+        groups = {"dp": make_dp_group(rank, world, local)}
+        lower_kwargs = zero_lower_kwargs(parallel, rank, world)
+    hyper = {"lr": 3e-4, "weight_decay": 0.1, "beta1": 0.9, "beta2": 0.95}
+    tr = Trainer(a.family, cfg, budget_gib=budget, device=local, hyper=hyper, seed=0, kernel_set=a.kernels,
+                 profile=not a.no_profile, groups=groups, lower_kwargs=lower_kwargs)
+    tokens_step = tr.T * tr.rounds
+    vocab = cfg.vocab_size
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    h2d = d2h = 0
+    for s in range(a.warmup):
+        tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, vocab, rank, s, pin=True), valid_rows=tokens_step * world)
+    barrier()
+    cuda_lane.LAUNCHES.reset()
+    sampler = ClockSampler(local)
+    sampler.start()
+    data = [synthetic_rounds(cfg, tr.rounds, tr.T, vocab, rank, a.warmup + s, pin=True) for s in range(a.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    dev_us = 0.0
+    losses = []
+    for s in range(a.steps):
+        for r, (tk, tg) in enumerate(data[s]):
+            h2d += tr.put_round(r, tk, tg)          # pinned host -> engine store; the engine DMA-copies it to the device
+        losses.append(tr.step(None, valid_rows=tokens_step * world))     # reads the loss words back from pinned memory
+        d2h += 4 * len(tr.loss_ids)
+        dev_us += tr.last_result.makespan_us
+    e1.record()
+    barrier()
+    wall_s = time.perf_counter() - t0
+    ev_s = e0.elapsed_time(e1) / 1e3
+    clocks = sampler.stop()
+    launches = cuda_lane.LAUNCHES.total
+    t = torch.tensor([dev_us / 1e6, max(ev_s, wall_s)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    dev_s, e2e_s = float(t[0]), float(t[1])
+    total_tokens = tokens_step * world * a.steps
+    value = total_tokens / dev_s
+    res = tr.last_result
+    out = {
+        "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": dev_s / a.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": a.preset + (f"-cut{a.layers}L" if a.layers else ""), "global_batch": tokens_step * world // a.seq_len,
+                   "seq_len": a.seq_len, "tokens_per_step": tokens_step * world,
+                   "parallelism": parallel if world > 1 else "solo", "fast_budget_gib": budget,
+                   "dtype_policy": a.dtype_policy, "optimizer": "adamw", "l2": "inputs_larger_than_L2",
+                   "costs": "measured" if tr.measured else "roofline"},
+        "clocks": clocks,
+        "e2e": {"value": total_tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d // a.steps,
+                "d2h_bytes_per_step": d2h // a.steps},
+        "gpu_launches": launches,
+        "loss": losses[-1] if losses else None,
+        "plan": {"predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
+                 "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
+                 "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows,
+                 "plan_s": tr.plan_s},
+        "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},
+    }
+    tr.close()
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def main(argv=None) -> int:
+    a = parse_args(argv)
+    if a.impl == "reference":
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from baseline.reference_arm import run_reference_arm
+        out = run_reference_arm(a)
+    else:
+        out = bench_ours(a)
+    if out:
+        print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

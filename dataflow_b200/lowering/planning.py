@@ -1,0 +1,102 @@
+"""Plan a bare Program against a fast-memory budget.
+
+``budget = planned object pool + largest task workspace + leeway``: the planner is
+given ``budget - leeway - max(workspace)`` for declared objects, so the executor's
+slab (objects) plus the framework allocator's scratch (workspace) stay under the
+budget on the device.  PressureFit (optionally wrapped by the recompute planner)
+produces the directives; the result is re-simulated and returned with its
+predicted makespan, peaks and transfer statistics.  Role parity: reference
+``src/dataflow_training/lowering/planning.py:22-356``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, replace
+from typing import Any, Callable, Mapping
+
+from ..core import Program, apply_chain_annotations, to_sim_chain
+from ..sim import run as simulate
+from ..sim.policies.pressurefit import PlanningError, pressurefit
+
+DEFAULT_PROGRAM_LEEWAY_BYTES = int(1.5 * (1 << 30))
+
+
+@dataclass
+class PlannedProgram:
+    program: Program
+    makespan_us: float
+    lower_bound_us: float
+    peak_fast_bytes: int
+    peak_backing_bytes: int
+    object_capacity: int
+    max_workspace: int
+    budget: int | None
+    policy: str
+    recompute_levels: dict[int, int] = field(default_factory=dict)
+    transfer: dict[str, Any] = field(default_factory=dict)
+    candidates: int = 0
+
+    @property
+    def idle_fraction(self) -> float:
+        return 0.0 if not self.makespan_us else 1.0 - self.lower_bound_us / self.makespan_us
+
+
+def transfer_summary(log) -> dict[str, Any]:
+    out: dict[str, Any] = {}
+    for d in ("from_slow", "to_slow"):
+        ivs = log.transfer_intervals(d)
+        out[d] = {"count": len(ivs), "busy_us": sum(i.end - i.start for i in ivs)}
+    out["makespan_us"] = log.makespan
+    for d in ("from_slow", "to_slow"):
+        out[d]["busy_fraction"] = out[d]["busy_us"] / log.makespan if log.makespan else 0.0
+    return out
+
+
+def strip_plan_annotations(program: Program) -> Program:
+    return replace(program, tasks=tuple(t.with_directives(releases_after=(), offload_after=(), prefetch_after=())
+                                        for t in program.tasks),
+                   initial_objects=_dedup_initial(program), fast_memory_capacity=None)
+
+
+def _dedup_initial(program: Program):
+    seen, out = set(), []
+    for o in program.initial_objects:
+        if o.id in seen:
+            continue
+        seen.add(o.id)
+        out.append(replace(o, location="backing") if o.persistent or o.role == "input" else o)
+    return tuple(out)
+
+
+def plan_program(program: Program, fast_memory_capacity: int | None, *, recompute: bool = False,
+                 build_variant: Callable[[Mapping[int, int]], Program] | None = None,
+                 backing_memory_capacity: int | None = None,
+                 leeway_bytes: int = DEFAULT_PROGRAM_LEEWAY_BYTES, policy: str = "pressurefit",
+                 specs=None, rules=None) -> PlannedProgram:
+    """``fast_memory_capacity`` is the whole device budget in bytes (``None`` = unbounded)."""
+    levels: dict[int, int] = {}
+    if recompute and build_variant is not None and program.recompute_rewrites:
+        from ..sim.planning.recompute import plan_with_recompute
+        return plan_with_recompute(program, fast_memory_capacity, build_variant,
+                                   backing_memory_capacity=backing_memory_capacity, leeway_bytes=leeway_bytes)
+    max_ws = max((t.workspace_bytes for t in program.tasks), default=0)
+    cap = None
+    if fast_memory_capacity is not None:
+        cap = int(fast_memory_capacity) - int(leeway_bytes) - max_ws
+        if cap <= 0:
+            raise PlanningError(f"budget {fast_memory_capacity} leaves no room after workspace {max_ws} and leeway {leeway_bytes}")
+    chain = to_sim_chain(program, with_directives=False)
+    chain = replace(chain, tasks=[replace(t, workspace_bytes=0) for t in chain.tasks],
+                    backing_memory_capacity=backing_memory_capacity)
+    if policy == "pressurefit":
+        res = pressurefit(chain, cap, specs=specs, rules=rules)
+        planned_chain, ncand = res.chain, len(res.candidates)
+    else:
+        from ..sim.policies import get_all_policies
+        planned_chain, ncand = get_all_policies()[policy](chain, cap), 1
+    log = simulate(planned_chain, validate=False)
+    annotated = apply_chain_annotations(program, planned_chain)
+    annotated = replace(annotated, metadata={**dict(annotated.metadata), "workspace_accounting": "external",
+                                             "max_workspace_bytes": max_ws, "budget_bytes": fast_memory_capacity})
+    return PlannedProgram(annotated, log.makespan, float(sum(t.runtime_us for t in program.tasks)),
+                          log.peak_fast_memory_bytes, log.peak_backing_memory_bytes, cap if cap is not None else 0,
+                          max_ws, fast_memory_capacity, policy, levels, transfer_summary(log), ncand)

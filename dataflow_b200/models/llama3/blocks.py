@@ -1,0 +1,223 @@
+"""llama3 block executables: staged forward, derived recompute, backward, resolver.
+
+The forward is an ordered list of stages ``(name, fn, emitted_context_fields)``;
+saved context is written *through* into the ``A`` object as it is produced, and the
+recompute task is derived — it runs the same stages up to the last one that emits
+context.  Backward re-applies both norms from saved statistics and recomputes the
+SwiGLU product instead of saving them.  Structure parity: reference
+``src/dataflow_training/model_families/llama3/blocks.py:132-619``.
+"""
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+from ...blocks.base_blocks import _Base, common_executables
+
+
+# --------------------------------------------------------------------------- stages
+def stage_attn_norm(K, d, st):
+    st["h"], rstd = K.rmsnorm_fwd(st["x"], st["w"]["attn_norm"], d.eps)
+    st["a"]["rstd_attn"].copy_(rstd)
+
+
+def _qkv_views(d, qkv, n):
+    q = qkv[:, :d.q_dim].unflatten(1, (d.hq, d.hd))
+    k = qkv[:, d.q_dim:d.q_dim + d.kv_dim].unflatten(1, (d.hkv, d.hd))
+    v = qkv[:, d.q_dim + d.kv_dim:].unflatten(1, (d.hkv, d.hd))
+    return q, k, v
+
+
+def stage_qkv_rope(K, d, st):
+    qkv = st["a"]["qkv"]
+    K.linear_fwd_bf16(st["h"], st["w"]["w_qkv"], out=qkv)
+    q, k, v = _qkv_views(d, qkv, st["n"])
+    if d.qk_norm:
+        a = st["a"]
+        a["qk_pre"].copy_(qkv[:, :d.q_dim + d.kv_dim])
+        qn, qr = K.rmsnorm_fwd(q.contiguous(), st["w"]["q_norm"], d.eps)
+        kn, kr = K.rmsnorm_fwd(k.contiguous(), st["w"]["k_norm"], d.eps)
+        q.copy_(qn)
+        k.copy_(kn)
+        a["q_rstd"].copy_(qr.view(-1, d.hq))
+        a["k_rstd"].copy_(kr.view(-1, d.hkv))
+    pos = st["seg"].positions
+    K.rope_fwd(q, pos, d.theta)
+    K.rope_fwd(k, pos, d.theta)
+    st["q"], st["k"], st["v"] = q, k, v
+
+
+def stage_attn(K, d, st):
+    seg = st["seg"]
+    out = st["a"]["attn_out"].unflatten(1, (d.hq, d.hd))
+    _, lse = K.flash_fwd(st["q"], st["k"], st["v"], seg.cu_seqlens, seg.max_len, out=out)
+    st["a"]["lse"].copy_(lse)
+
+
+def stage_resid1_norm2(K, d, st):
+    h_mid = st["a"]["h_mid"]
+    K.linear_fwd_bf16(st["a"]["attn_out"], st["w"]["wo"], out=h_mid, add=st["x"])
+    st["h2"], rstd = K.rmsnorm_fwd(h_mid, st["w"]["ffn_norm"], d.eps)
+    st["a"]["rstd_ffn"].copy_(rstd)
+
+
+def stage_up_proj(K, d, st):
+    K.linear_fwd_bf16(st["h2"], st["w"]["w13"], out=st["a"]["h13"])
+
+
+def stage_swiglu(K, d, st):
+    st["s"] = K.swiglu_packed_fwd(st["a"]["h13"])
+
+
+def stage_down_resid(K, d, st):
+    K.linear_fwd_bf16(st["s"], st["w"]["w2"], out=st["y"], add=st["a"]["h_mid"])
+
+
+STAGES = (
+    ("attn_norm", stage_attn_norm, ("rstd_attn",)),
+    ("qkv_rope", stage_qkv_rope, ("qkv",)),
+    ("attn", stage_attn, ("lse", "attn_out")),
+    ("resid1_norm2", stage_resid1_norm2, ("h_mid", "rstd_ffn")),
+    ("up_proj", stage_up_proj, ("h13",)),
+    ("swiglu", stage_swiglu, ()),
+    ("down_resid", stage_down_resid, ()),
+)
+
+
+def recompute_stages(stages=STAGES):
+    """Stages up to and including the last one that emits saved context."""
+    last = max(i for i, s in enumerate(stages) if s[2])
+    return stages[:last + 1]
+
+
+def context_rows(d, n):
+    """Content-row trims of the context fields for an under-full round (token-axis aware)."""
+    rows = {name: n for name in ("rstd_attn", "qkv", "attn_out", "h_mid", "rstd_ffn", "h13", "q_rstd", "k_rstd", "qk_pre")}
+    return rows
+
+
+class _Block(_Base):
+    stages = STAGES
+
+    def ctx_views(self, buf, n):
+        a = self.views(buf, self.lay.ctx, context_rows(self.dims, n))
+        if n != self.dims.T:
+            a = dict(a)
+            a["lse"] = a["lse"][:, :n]
+        return a
+
+    def common(self, ctx, x_buf, w_buf):
+        d = self.dims
+        seg = self.segments(ctx)
+        n = seg.n_tokens
+        return {"seg": seg, "n": n, "x": self.tview(x_buf, (d.T, d.d))[:n], "w": self.views(w_buf, self.lay.block_w)}
+
+
+class BlockFwd(_Block):
+    """(x, W) -> (y, A)"""
+
+    def run(self, ctx):
+        d = self.dims
+        st = self.common(ctx, ctx.inputs[0], ctx.inputs[1])
+        st["y"] = self.tview(ctx.outputs[0], (d.T, d.d))[:st["n"]]
+        lvl = int(ctx.task.block_params.get("recompute_level", 0))
+        if lvl == 0:
+            st["a"] = self.ctx_views(ctx.outputs[1], st["n"])
+        else:
+            st["a"] = self.scratch_ctx(st["n"], st["x"].device)      # context is dropped: recomputed before backward
+        for _, fn, _ in self.stages:
+            fn(self.K, d, st)
+
+    def scratch_ctx(self, n, device):
+        import torch
+        from ...runtime.interop import _dtypes
+        out = {}
+        for f in self.lay.ctx.fields:
+            shape = (f.shape[0], n) if f.name == "lse" else (n,) + tuple(f.shape[1:])
+            out[f.name] = torch.empty(shape, dtype=_dtypes()[f.dtype], device=device)
+        return out
+
+
+class BlockRecompute(_Block):
+    """(x, W) -> (A): the forward stages up to the last context-emitting one."""
+
+    def run(self, ctx):
+        st = self.common(ctx, ctx.inputs[0], ctx.inputs[1])
+        st["a"] = self.ctx_views(ctx.outputs[0], st["n"])
+        for _, fn, _ in recompute_stages(self.stages):
+            fn(self.K, self.dims, st)
+
+
+class BlockBwd(_Block):
+    """(dy, A, x, W[, dW]) -> (dx[, dW]); dW is created when it is an output, accumulated when mutated."""
+
+    def run(self, ctx):
+        import torch
+        d, K = self.dims, self.K
+        st = self.common(ctx, ctx.inputs[2], ctx.inputs[3])
+        n, x, w, seg = st["n"], st["x"], st["w"], st["seg"]
+        dy = self.tview(ctx.inputs[0], (d.T, d.d))[:n]
+        a = self.ctx_views(ctx.inputs[1], n)
+        dx = self.tview(ctx.outputs[0], (d.T, d.d))[:n]
+        acc = not self.creating(ctx, "dW_")
+        g = self.views(self.by_id(ctx, "dW_"), self.lay.block_dw)
+
+        def wgrad(name, xin, dout):
+            if name in g:                       # frozen fields have no gradient storage
+                K.linear_wgrad_bf16(xin, dout, g[name], accumulate=acc)
+
+        # ---- MLP tail
+        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+        s = K.swiglu_packed_fwd(a["h13"])
+        wgrad("w2", s, dy)
+        ds = K.linear_dgrad_bf16(dy, w["w2"])
+        del s
+        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
+        del ds
+        wgrad("w13", h2, dh13)
+        dh2 = K.linear_dgrad_bf16(dh13, w["w13"])
+        del dh13, h2
+        dh_mid = K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
+        del dh2
+        # ---- attention
+        wgrad("wo", a["attn_out"], dh_mid)
+        dattn = K.linear_dgrad_bf16(dh_mid, w["wo"])
+        q, k, v = _qkv_views(d, a["qkv"], n)
+        dqkv = torch.empty(n, d.qkv_dim, dtype=x.dtype, device=x.device)
+        dq, dk, dv = _qkv_views(d, dqkv, n)
+        K.flash_bwd(dattn.unflatten(1, (d.hq, d.hd)), q, k, v, a["attn_out"].unflatten(1, (d.hq, d.hd)), a["lse"],
+                    seg.cu_seqlens, seg.max_len, dq=dq, dk=dk, dv=dv)
+        del dattn
+        K.rope_bwd(dq, seg.positions, d.theta)
+        K.rope_bwd(dk, seg.positions, d.theta)
+        if d.qk_norm:
+            pre = a["qk_pre"]
+            qp = pre[:, :d.q_dim].unflatten(1, (d.hq, d.hd)).contiguous()
+            kp = pre[:, d.q_dim:].unflatten(1, (d.hkv, d.hd)).contiguous()
+            dq.copy_(K.rmsnorm_bwd(dq.contiguous(), qp, w["q_norm"], a["q_rstd"].reshape(-1), dw=g.get("q_norm"), accumulate=acc))
+            dk.copy_(K.rmsnorm_bwd(dk.contiguous(), kp, w["k_norm"], a["k_rstd"].reshape(-1), dw=g.get("k_norm"), accumulate=acc))
+        h = K.rmsnorm_apply(x, w["attn_norm"], a["rstd_attn"])
+        wgrad("w_qkv", h, dqkv)
+        dh = K.linear_dgrad_bf16(dqkv, w["w_qkv"])
+        K.rmsnorm_bwd(dh, x, w["attn_norm"], a["rstd_attn"], dx_add=dh_mid, dw=g.get("attn_norm"), accumulate=acc, out=dx)
+
+
+def build_llama3_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device, layouts=None, policy=None):
+    from .model import family_layouts
+    from ...blocks.layouts import DTypePolicy
+    hyper = dict(hyper or {})
+    lay = layouts or family_layouts(dims, policy or DTypePolicy.from_dict(hyper.get("dtype_policy", "bf16")),
+                                    hyper.get("optimizer", "adamw"))
+    table = common_executables(dims, lay, kernels, device, hyper)
+    table.update({
+        "block_fwd": BlockFwd(dims, lay, kernels, device, hyper),
+        "block_recompute": BlockRecompute(dims, lay, kernels, device, hyper),
+        "block_bwd": BlockBwd(dims, lay, kernels, device, hyper),
+    })
+
+    def resolver(task):
+        try:
+            return table[task.compute_block_key]
+        except KeyError:
+            raise KeyError(f"llama3: no executable for compute key {task.compute_block_key!r} (task {task.id})") from None
+    resolver.table = table
+    return resolver

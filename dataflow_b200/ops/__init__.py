@@ -4,21 +4,21 @@ from __future__ import annotations
 
 import os
 
-_ops = None
+_mod = None
 _load_error: Exception | None = None
 
 
 def _load():
-    global _ops, _load_error
-    if _ops is not None or _load_error is not None:
-        return _ops
+    global _mod, _load_error
+    if _mod is not None or _load_error is not None:
+        return _mod
     try:
+        import importlib
         import torch  # noqa: F401  (libtorch must be loaded before the extension)
-        from . import _ops as mod  # type: ignore[attr-defined]
-        _ops = mod
+        _mod = importlib.import_module(__name__ + "._ops")
     except Exception as e:  # missing build or missing CUDA libs
         _load_error = e
-    return _ops
+    return _mod
 
 
 def native_available() -> bool:

@@ -12,6 +12,30 @@ from .registry import Workspace, register
 P = 10
 
 
+class _LaunchCounter:
+    """Counts launches of this package's own kernels (benchmarks report it)."""
+    total = 0
+
+    def reset(self):
+        self.total = 0
+
+
+LAUNCHES = _LaunchCounter()
+
+
+def reg(op, launches=1, **kw):
+    """Register a native implementation; the registered callable counts its kernel launches."""
+    def deco(f):
+        def counted(*a, **k):
+            LAUNCHES.total += launches
+            return f(*a, **k)
+        counted.__name__ = f.__name__
+        counted.__doc__ = f.__doc__
+        register(op, "sm100", counted, priority=P, requires=_native, native=True, **kw)
+        return f
+    return deco
+
+
 def _native(caps):
     if caps.get("sm100") and not native_available():
         native()        # raises with the build hint: no silent fallback on a B200
@@ -23,7 +47,7 @@ def _scratch(n, device):
 
 
 # ------------------------------------------------------------------ norms
-@register("rmsnorm_fwd", "sm100", priority=P, requires=_native, native=True)
+@reg("rmsnorm_fwd")
 def rmsnorm_fwd(x, w, eps=1e-5, out=None):
     x = x.contiguous()
     rows = x.numel() // x.shape[-1]
@@ -33,14 +57,14 @@ def rmsnorm_fwd(x, w, eps=1e-5, out=None):
     return y, rstd
 
 
-@register("rmsnorm_apply", "sm100", priority=P, requires=_native, native=True)
+@reg("rmsnorm_apply")
 def rmsnorm_apply(x, w, rstd, out=None):
     y = out if out is not None else torch.empty_like(x)
     native().rmsnorm_apply(x, w, rstd, y)
     return y
 
 
-@register("rmsnorm_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+@reg("rmsnorm_bwd", 2, workspace=Workspace.internal())
 def rmsnorm_bwd(dy, x, w, rstd, dx_add=None, dw=None, accumulate=False, out=None):
     rows, cols = x.numel() // x.shape[-1], x.shape[-1]
     dx = out if out is not None else torch.empty_like(x)
@@ -49,7 +73,7 @@ def rmsnorm_bwd(dy, x, w, rstd, dx_add=None, dw=None, accumulate=False, out=None
     return dx
 
 
-@register("layernorm_fwd", "sm100", priority=P, requires=_native, native=True)
+@reg("layernorm_fwd")
 def layernorm_fwd(x, w, b, eps=1e-5, out=None):
     rows = x.numel() // x.shape[-1]
     y = out if out is not None else torch.empty_like(x)
@@ -59,14 +83,14 @@ def layernorm_fwd(x, w, b, eps=1e-5, out=None):
     return y, mean, rstd
 
 
-@register("layernorm_apply", "sm100", priority=P, requires=_native, native=True)
+@reg("layernorm_apply")
 def layernorm_apply(x, w, b, mean, rstd, out=None):
     y = out if out is not None else torch.empty_like(x)
     native().layernorm_apply(x, w, b, mean, rstd, y)
     return y
 
 
-@register("layernorm_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+@reg("layernorm_bwd", 2, workspace=Workspace.internal())
 def layernorm_bwd(dy, x, w, mean, rstd, dx_add=None, dw=None, db=None, accumulate=False, out=None):
     rows, cols = x.numel() // x.shape[-1], x.shape[-1]
     dx = out if out is not None else torch.empty_like(x)
@@ -83,12 +107,12 @@ def _rope(x, positions, theta, rot_dim, col_base, backward):
     return x
 
 
-@register("rope_fwd", "sm100", priority=P, requires=_native, native=True)
+@reg("rope_fwd")
 def rope_fwd(x, positions, theta, rot_dim=None, col_base=0):
     return _rope(x, positions, theta, rot_dim, col_base, False)
 
 
-@register("rope_bwd", "sm100", priority=P, requires=_native, native=True)
+@reg("rope_bwd")
 def rope_bwd(x, positions, theta, rot_dim=None, col_base=0):
     return _rope(x, positions, theta, rot_dim, col_base, True)
 
@@ -102,7 +126,7 @@ def _rows_ld(t):
     return rows, F, ld
 
 
-@register("swiglu_fwd_out", "sm100", priority=P, requires=_native, native=True)
+@reg("swiglu_fwd_out")
 def swiglu_fwd_out(x1, x3, out=None):
     rows, F, ld1 = _rows_ld(x1)
     _, _, ld3 = _rows_ld(x3)
@@ -112,7 +136,7 @@ def swiglu_fwd_out(x1, x3, out=None):
     return out
 
 
-@register("swiglu_bwd", "sm100", priority=P, requires=_native, native=True)
+@reg("swiglu_bwd")
 def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None):
     rows, F, ld1 = _rows_ld(x1)
     _, _, ld3 = _rows_ld(x3)
@@ -124,13 +148,13 @@ def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None):
     return dx1, dx3
 
 
-@register("swiglu_packed_fwd", "sm100", priority=P, requires=_native, native=True)
+@reg("swiglu_packed_fwd")
 def swiglu_packed_fwd(h13, out=None):
     F = h13.shape[-1] // 2
     return swiglu_fwd_out(h13[..., :F], h13[..., F:], out)
 
 
-@register("swiglu_packed_bwd", "sm100", priority=P, requires=_native, native=True)
+@reg("swiglu_packed_bwd")
 def swiglu_packed_bwd(ds, h13, dh13=None):
     F = h13.shape[-1] // 2
     if dh13 is None:
@@ -139,21 +163,21 @@ def swiglu_packed_bwd(ds, h13, dh13=None):
     return dh13
 
 
-@register("gelu_fwd_out", "sm100", priority=P, requires=_native, native=True)
+@reg("gelu_fwd_out")
 def gelu_fwd_out(x, out=None):
     out = out if out is not None else torch.empty_like(x)
     native().gelu_fwd(x, out)
     return out
 
 
-@register("gelu_bwd", "sm100", priority=P, requires=_native, native=True)
+@reg("gelu_bwd")
 def gelu_bwd(dy, x, out=None):
     out = out if out is not None else torch.empty_like(x)
     native().gelu_bwd(dy, x, out)
     return out
 
 
-@register("add", "sm100", priority=P, requires=_native, native=True)
+@reg("add")
 def add(a, b, out=None):
     out = out if out is not None else torch.empty_like(a)
     native().add_bf16(a, b, out)
@@ -161,7 +185,7 @@ def add(a, b, out=None):
 
 
 # ------------------------------------------------------------------ loss / embedding
-@register("ce_loss_fwd_bwd", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+@reg("ce_loss_fwd_bwd", 2, workspace=Workspace.internal())
 def ce_loss_fwd_bwd(logits, targets, total_rows, loss_out=None, accumulate=False):
     nll = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
     if loss_out is None:
@@ -171,7 +195,7 @@ def ce_loss_fwd_bwd(logits, targets, total_rows, loss_out=None, accumulate=False
     return loss_out
 
 
-@register("embed_fwd", "sm100", priority=P, requires=_native, native=True)
+@reg("embed_fwd")
 def embed_fwd(tok, table, out=None, positions=None, pos_table=None):
     if out is None:
         out = torch.empty(tok.numel(), table.shape[1], dtype=table.dtype, device=table.device)
@@ -179,7 +203,7 @@ def embed_fwd(tok, table, out=None, positions=None, pos_table=None):
     return out
 
 
-@register("embed_bwd_accum", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+@reg("embed_bwd_accum", workspace=Workspace.internal())
 def embed_bwd_accum(tok, dy, dtable, accumulate=False):
     if not accumulate:
         dtable.zero_()
@@ -189,7 +213,7 @@ def embed_bwd_accum(tok, dy, dtable, accumulate=False):
 
 
 # ------------------------------------------------------------------ optimizers
-@register("adamw_step", "sm100", priority=P, requires=_native, native=True)
+@reg("adamw_step")
 def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, master=None, gscale=1.0):
     if master is not None:
         native().adamw_master(master, w, g, m, v, lr, beta1, beta2, eps, wd, int(step), gscale)
@@ -200,14 +224,14 @@ def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, 
     return w
 
 
-@register("sgd_step", "sm100", priority=P, requires=_native, native=True)
+@reg("sgd_step")
 def sgd_step(w, g, m=None, lr=1e-2, momentum=0.0, wd=0.0):
     native().sgd_bf16(w, g, m, lr, momentum, wd)
     return w
 
 
 # ------------------------------------------------------------------ linear triple on the tcgen05 GEMM (W stored (in, out))
-@register("linear_fwd_bf16", "sm100", priority=P, requires=_native, native=True)
+@reg("linear_fwd_bf16")
 def linear_fwd(x, w, out=None, add=None, bias=None):
     if out is None:
         out = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
@@ -215,7 +239,7 @@ def linear_fwd(x, w, out=None, add=None, bias=None):
     return out
 
 
-@register("linear_dgrad_bf16", "sm100", priority=P, requires=_native, native=True)
+@reg("linear_dgrad_bf16")
 def linear_dgrad(dy, w, out=None, add=None):
     if out is None:
         out = torch.empty(dy.shape[0], w.shape[0], dtype=dy.dtype, device=dy.device)
@@ -223,13 +247,13 @@ def linear_dgrad(dy, w, out=None, add=None):
     return out
 
 
-@register("linear_wgrad_bf16", "sm100", priority=P, requires=_native, native=True)
+@reg("linear_wgrad_bf16")
 def linear_wgrad(x, dy, dw, accumulate=False):
     native().gemm_bf16(x, True, dy, True, dw, dw if accumulate else None, None)   # both operands token-major
     return dw
 
 
-@register("bias_grad", "sm100", priority=P, requires=_native, native=True, workspace=Workspace.internal())
+@reg("bias_grad", 2, workspace=Workspace.internal())
 def bias_grad(dy, db, accumulate=False):
     dy2 = dy.reshape(-1, dy.shape[-1])
     part = _scratch(native().colsum_parts(dy2.shape[0]) * dy2.shape[1], dy.device)

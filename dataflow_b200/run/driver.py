@@ -1,0 +1,259 @@
+"""In-process training driver: lower → (profile) → plan → init → per-step ``execute``.
+
+``Trainer`` is the public single-process API: it owns the backend, the session
+(streams + fast slab), a pinned host *store* holding every persistent object and
+the per-round token buffers, the planned Program and the resolver.  ``step()``
+writes one step's tokens into the store, runs the annotated chain once and returns
+the step loss read back from the ``loss_*`` objects.  Role parity: reference
+``src/dataflow_training/run/driver.py:410-942`` (``init_model``, ``plan_at_budget``,
+``run_engine``) — without the daemon hop, which ``dataflow_b200.service`` adds.
+"""
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Mapping
+
+from ..core import Program
+from ..lowering.planning import PlannedProgram, plan_program
+from ..lowering.shaped_program import ShapedHardware, resolve_hardware
+from ..models.families import resolve_family
+from ..runtime import Buffer, CpuBackend, Engine, Session
+
+GiB = 1 << 30
+
+
+@dataclass
+class RunResult:
+    """Loss curve and timing of a run (``.save`` writes the run-curve JSON)."""
+    losses: list[float] = field(default_factory=list)
+    step_wall_s: list[float] = field(default_factory=list)
+    tokens_per_step: int = 0
+    meta: dict[str, Any] = field(default_factory=dict)
+
+    @property
+    def tokens_per_s(self) -> float:
+        t = sum(self.step_wall_s)
+        return self.tokens_per_step * len(self.step_wall_s) / t if t else 0.0
+
+    def save(self, path) -> None:
+        Path(path).write_text(json.dumps({"losses": self.losses, "step_wall_s": self.step_wall_s,
+                                          "tokens_per_step": self.tokens_per_step, "meta": self.meta}, indent=1))
+
+
+class HostStore:
+    """Named extents inside one host region (pinned when the backend is CUDA)."""
+
+    ALIGN = 4096
+
+    def __init__(self, backend, sizes: Mapping[str, int], pinned: bool):
+        self.backend = backend
+        self.pinned = pinned
+        self.offsets: dict[str, int] = {}
+        off = 0
+        for k, n in sizes.items():
+            self.offsets[k] = off
+            off += (int(n) + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.total = max(off, self.ALIGN)
+        self.sizes = {k: int(v) for k, v in sizes.items()}
+        if pinned:
+            self.base = backend.pin_region(self.total, True)
+        else:
+            self.base = backend.alloc(1, self.total)
+
+    def buffer(self, oid: str) -> Buffer:
+        return Buffer(self.base + self.offsets[oid], self.sizes[oid], "backing", oid)
+
+    def buffers(self) -> dict[str, Buffer]:
+        return {k: self.buffer(k) for k in self.offsets}
+
+    def close(self):
+        if self.base:
+            if self.pinned:
+                self.backend.unpin_region(self.base, self.total)
+            else:
+                self.backend.free(1, self.base, self.total)
+            self.base = 0
+
+
+def plan_at_budget(family, cfg, budget_bytes: int | None, hw: ShapedHardware | None = None, *,
+                   recompute: bool = True, measured: Mapping[str, float] | None = None,
+                   leeway_bytes: int | None = None, lower_kwargs: Mapping[str, Any] | None = None) -> PlannedProgram:
+    """Lower ``cfg`` and plan it under ``budget_bytes`` of device memory."""
+    from ..lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
+    from .profiling import apply_measured_costs
+    fam = resolve_family(family) if isinstance(family, str) else family
+    hw = hw or resolve_hardware(None)
+    kw = dict(lower_kwargs or {})
+
+    def variant(levels):
+        p = fam.lower(cfg, recompute_levels=levels, hw=hw, **kw)
+        return apply_measured_costs(p, measured) if measured else p
+
+    program = variant(None)
+    return plan_program(program, budget_bytes, recompute=recompute, build_variant=variant,
+                        leeway_bytes=DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else leeway_bytes)
+
+
+class Trainer:
+    """Single-process engine training loop over one device (or the CPU backend)."""
+
+    def __init__(self, family: str, cfg, *, budget_gib: float | None = None, device: int | None = 0,
+                 hyper: Mapping[str, Any] | None = None, seed: int = 0, hw: ShapedHardware | None = None,
+                 kernels=None, kernel_set: str | None = None, recompute: bool = True, profile: bool = False,
+                 leeway_bytes: int | None = None, planned: PlannedProgram | None = None,
+                 lower_kwargs: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
+                 init: bool = True, verbose: bool = False):
+        import torch
+        from ..ops import resolve_kernels
+        self.fam = resolve_family(family)
+        self.cfg = cfg
+        self.device = device
+        self.verbose = verbose
+        self.hyper = {"optimizer": getattr(cfg, "optimizer", "adamw"),
+                      "dtype_policy": cfg.policy().to_dict() if hasattr(cfg, "policy") else "bf16", **dict(hyper or {})}
+        self.groups = dict(groups or {})
+        if device is None:
+            self.backend = CpuBackend()
+            self.hw = hw or resolve_hardware("cpu")
+            self.K = kernels or resolve_kernels(kernel_set="eager" if kernel_set is None else kernel_set)
+        else:
+            from ..runtime import CudaBackend
+            torch.cuda.set_device(device)
+            self.backend = CudaBackend(device, "poll")
+            self.hw = hw or resolve_hardware(None)
+            self.K = kernels or resolve_kernels(kernel_set=kernel_set)
+        self.dims = self.fam.derive_dims(cfg)
+        self.layouts = self.fam.family_layouts(self.dims, cfg.policy() if hasattr(cfg, "policy") else None,
+                                               self.hyper["optimizer"])
+        self.session = Session(self.backend)
+        self.engine = Engine(self.backend, session=self.session)
+        self.resolver = self.fam.build_resolver(self.dims, self.hyper, self.K, device, layouts=self.layouts)
+        budget = None if budget_gib is None else int(budget_gib * GiB)
+        measured = None
+        t0 = time.time()
+        if planned is None:
+            if profile and device is not None:
+                from .profiling import profile_program
+                bare = self.fam.lower(cfg, hw=self.hw, **dict(lower_kwargs or {}))
+                measured = profile_program(self, bare)
+            planned = plan_at_budget(self.fam, cfg, budget, self.hw, recompute=recompute, measured=measured,
+                                     leeway_bytes=leeway_bytes, lower_kwargs=lower_kwargs)
+        self.planned = planned
+        self.program: Program = planned.program
+        self.plan_s = time.time() - t0
+        self.measured = measured
+        # host store: persistent objects, tokens/targets, loss landing words
+        sizes: dict[str, int] = {}
+        for o in self.program.initial_objects:
+            if o.id not in sizes:
+                sizes[o.id] = o.size_bytes
+        for t in self.program.tasks:
+            for out in t.outputs:
+                if out.location == "backing" and out.id.startswith("loss_"):
+                    sizes[out.id] = out.size_bytes
+        self.store = HostStore(self.backend, sizes, pinned=device is not None)
+        self.loss_ids = sorted(k for k in sizes if k.startswith("loss_"))
+        self.rounds = int(self.program.metadata.get("grad_accum_rounds", 1))
+        self.T = int(self.program.metadata.get("tokens_per_round", self.dims.T))
+        # size the session pools once: objects only (scratch lives in the framework allocator)
+        if device is not None:
+            store_bytes = sum(sizes.values())
+            transient_backing = max(planned.peak_backing_bytes - store_bytes, 0) + (64 << 20)
+            fast = planned.object_capacity or (planned.peak_fast_bytes + (256 << 20))
+            self.session.native.ensure_pools(int(min(fast, planned.peak_fast_bytes + (512 << 20))), int(transient_backing), 0.0)
+        self.step_index = 0
+        self.last_result = None
+        if init:
+            self.init_model(seed)
+
+    # -- store views
+    def views_of(self, oid: str, layout):
+        return layout.views(self.store.buffer(oid), None)
+
+    def host_tensor(self, oid: str, shape, dtype: str):
+        from ..runtime.interop import torch_view
+        return torch_view(self.store.buffer(oid), shape, dtype, 0, None)
+
+    def init_model(self, seed: int = 0) -> None:
+        self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts)
+
+    # -- data
+    def put_round(self, r: int, tokens, targets) -> int:
+        """Copy one round's int32 ids into the store; returns the bytes written."""
+        import torch
+        n = int(tokens.numel())
+        tk = self.host_tensor(f"tokens_0_{r}", (self.T,), "int32")
+        tg = self.host_tensor(f"targets_0_{r}", (self.T,), "int32")
+        tk[:n].copy_(tokens.reshape(-1).to(torch.int32))
+        tg[:n].copy_(targets.reshape(-1).to(torch.int32))
+        if n < self.T:
+            tk[n:].zero_()
+            tg[n:].fill_(-1)
+        return 2 * 4 * n
+
+    def step(self, rounds_data=None, *, seq_lens: Mapping[int, list[int]] | None = None,
+             valid_rows: int | None = None, extra_args: Mapping[str, Any] | None = None) -> float:
+        """One optimizer step.  ``rounds_data``: list of (tokens, targets) per round (already in the
+        store if ``None``).  Returns the step loss."""
+        if rounds_data is not None:
+            for r, (tk, tg) in enumerate(rounds_data):
+                self.put_round(r, tk, tg)
+        self.step_index += 1
+        if valid_rows is None:
+            valid_rows = self.T * self.rounds
+        args = {"step": self.step_index, "valid_rows": int(valid_rows), **dict(extra_args or {})}
+        if seq_lens:
+            args["seq_lens"] = dict(seq_lens)
+        res = self.engine.execute(self.program, self.resolver, self.store.buffers(), run_args=args,
+                                  groups=self.groups, manage_pools=self.device is None)
+        self.last_result = res
+        res.raise_if_failed()
+        loss = 0.0
+        for k in self.loss_ids:
+            loss += float(self.host_tensor(k, (1,), "fp32")[0])
+        return loss
+
+    def close(self):
+        self.backend.synchronize()
+        from ..runtime.interop import invalidate_views
+        invalidate_views()
+        self.store.close()
+
+
+def synthetic_rounds(cfg, rounds: int, tokens_per_round: int, vocab: int, seed: int = 0, step: int = 0, pin: bool = False):
+    """Uniform random token ids with next-token targets (the data of every benchmark config)."""
+    import torch
+    g = torch.Generator().manual_seed(seed * 1000003 + step)
+    out = []
+    for _ in range(rounds):
+        ids = torch.randint(0, vocab, (tokens_per_round + 1,), generator=g, dtype=torch.int64).to(torch.int32)
+        tk, tg = ids[:-1].clone(), ids[1:].clone()
+        if pin and torch.cuda.is_available():
+            tk, tg = tk.pin_memory(), tg.pin_memory()
+        out.append((tk, tg))
+    return out
+
+
+def run_engine(family: str, cfg, steps: int, *, budget_gib=None, device=0, hyper=None, seed=0, data_seed=0,
+               verbose=True, **kw) -> RunResult:
+    tr = Trainer(family, cfg, budget_gib=budget_gib, device=device, hyper=hyper, seed=seed, **kw)
+    res = RunResult(tokens_per_step=tr.T * tr.rounds, meta={"family": family, "preset": getattr(cfg, "name", ""),
+                                                            "plan_makespan_us": tr.planned.makespan_us,
+                                                            "peak_fast_bytes": tr.planned.peak_fast_bytes})
+    vocab = getattr(cfg, "vocab_size")
+    try:
+        for s in range(steps):
+            data = synthetic_rounds(cfg, tr.rounds, tr.T, vocab, data_seed, s)
+            t0 = time.time()
+            loss = tr.step(data)
+            dt = time.time() - t0
+            res.losses.append(loss)
+            res.step_wall_s.append(dt)
+            if verbose:
+                print(f"step {s + 1:4d} loss {loss:.4f} {res.tokens_per_step / dt:,.0f} tok/s", flush=True)
+    finally:
+        tr.close()
+    return res

@@ -1,0 +1,83 @@
+"""Measured task costs.  Every distinct task *signature* of a program is timed on the
+real device by running a one-layer, two-round cut of the same model through the
+engine (so inputs are real activations, not zeros: zero inputs under-price dense
+kernels because the chip clocks higher on them) and reading the per-task intervals
+of a warm step; the result is cached on disk keyed by geometry, kernel set, device
+and library versions.  Role parity: reference ``src/dataflow_training/run/profiling.py:78-964``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import hashlib
+import json
+import os
+from pathlib import Path
+from typing import Any, Mapping
+
+from ..core import Program, TaskSpec
+
+PROFILE_CACHE_REV = 3
+
+
+def task_signature(t: TaskSpec) -> str:
+    acc = "acc" if any(m.startswith("dW") for m in t.mutates) else "new"
+    lvl = int(t.block_params.get("recompute_level", 0)) if t.block_params else 0
+    return f"{t.compute_block_key}|{acc}|l{lvl}"
+
+
+def apply_measured_costs(program: Program, measured: Mapping[str, float] | None) -> Program:
+    if not measured:
+        return program
+    tasks = []
+    for t in program.tasks:
+        us = measured.get(task_signature(t))
+        tasks.append(dataclasses.replace(t, runtime_us=float(us)) if us else t)
+    md = dict(program.metadata)
+    md["costs"] = "measured"
+    return dataclasses.replace(program, tasks=tuple(tasks), metadata=md)
+
+
+def _cache_path(key: str) -> Path:
+    root = Path(os.environ.get("DATAFLOW_PROFILE_CACHE", Path.home() / ".cache" / "dataflow_b200" / "profiles"))
+    root.mkdir(parents=True, exist_ok=True)
+    return root / f"{key}.json"
+
+
+def profile_key(trainer, cfg) -> str:
+    import torch
+    desc = {"rev": PROFILE_CACHE_REV, "cfg": {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v))
+                                              for k, v in dataclasses.asdict(cfg).items() if k not in ("n_layers", "grad_accum_rounds", "name")},
+            "kernels": trainer.K.describe(), "torch": torch.__version__,
+            "device": torch.cuda.get_device_name(trainer.device) if trainer.device is not None else "cpu"}
+    return hashlib.sha256(json.dumps(desc, sort_keys=True).encode()).hexdigest()[:20]
+
+
+def profile_program(trainer, program: Program | None = None, *, steps: int = 3, use_cache: bool = True) -> dict[str, float]:
+    """signature → median measured µs, from a 1-layer 2-round cut of ``trainer.cfg`` on ``trainer.device``."""
+    from .driver import Trainer, synthetic_rounds
+    cfg = trainer.cfg
+    key = profile_key(trainer, cfg)
+    path = _cache_path(key)
+    if use_cache and path.exists():
+        return json.loads(path.read_text())
+    out: dict[str, list[float]] = {}
+    for levels in (None, {0: 1}):
+        small = dataclasses.replace(cfg, n_layers=1, grad_accum_rounds=2)
+        tr = Trainer(trainer.fam.name, small, budget_gib=None, device=trainer.device, hyper=trainer.hyper,
+                     kernels=trainer.K, recompute=False, profile=False,
+                     lower_kwargs={"recompute_levels": levels} if levels else None)
+        try:
+            for s in range(steps):
+                data = synthetic_rounds(small, tr.rounds, tr.T, getattr(small, "vocab_size"), 7, s)
+                tr.step(data)
+            by_id = {t.id: t for t in tr.program.tasks}
+            for iv in tr.last_result.trace.by_track("compute"):
+                t = by_id.get(iv.name)
+                if t is not None:
+                    out.setdefault(task_signature(t), []).append(iv.end_us - iv.start_us)
+        finally:
+            tr.close()
+    med = {k: sorted(v)[len(v) // 2] for k, v in out.items()}
+    if use_cache:
+        path.write_text(json.dumps(med, indent=1))
+    return med

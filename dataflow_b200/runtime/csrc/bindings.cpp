@@ -193,7 +193,7 @@ PYBIND11_MODULE(_runtime, m) {
       .def("execute",
            [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
               bool strict_final, bool poison, bool record_events, double headroom,
-              std::shared_ptr<std::atomic<bool>> cancel) {
+              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools) {
              std::unordered_map<std::string, InitialBuffer> init;
              for (auto kv : initial) {
                auto t = kv.second.cast<py::tuple>();
@@ -205,6 +205,7 @@ PYBIND11_MODULE(_runtime, m) {
              opt.record_events = record_events;
              opt.slab_headroom = headroom;
              opt.cancel = cancel ? cancel.get() : nullptr;
+             opt.manage_pools = manage_pools;
              LaunchFn fn;
              if (!launch.is_none()) {
                fn = [launch](const LaunchArgs& a) {
@@ -230,5 +231,5 @@ PYBIND11_MODULE(_runtime, m) {
            py::arg("program"), py::arg("launch") = py::none(), py::arg("initial") = py::dict(),
            py::arg("strict_final_locations") = true, py::arg("poison_on_free") = false,
            py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
-           py::arg("cancel") = std::shared_ptr<std::atomic<bool>>());
+           py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true);
 }

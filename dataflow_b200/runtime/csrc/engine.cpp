@@ -319,7 +319,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
   queue_[0].clear(); queue_[1].clear(); flight_[0].reset(); flight_[1].reset();
   deferred_.clear(); xfer_seq_.clear(); pending_intervals_.clear(); events_to_release_.clear();
   task_done_upto_ = -1; running_task_ = -1;
-  sess_->ensure_pools(p.fast_cap, p.backing_cap, opt.slab_headroom);
+  if (opt.manage_pools) sess_->ensure_pools(p.fast_cap, p.backing_cap, opt.slab_headroom);
   int64_t of0 = sess_->fast_pool.slab_overflows + sess_->backing_pool.slab_overflows;
   int64_t va0 = sess_->fast_pool.vendor_allocs + sess_->backing_pool.vendor_allocs;
   be_->mark_epoch();
@@ -440,7 +440,7 @@ void Engine::cleanup(bool failed) {
     if (!failed && opt_->keep_finals && oi.final_loc >= 0) {
       Slot& s = oi.final_loc == FAST ? o.fast : o.backing;
       if (s.state == SlotState::LIVE && !s.buf.external) {
-        // ownership moves to the caller, who returns the buffer with Session::give_back (or adopts it)
+        // engine-owned bytes: valid until the next execute() on this session; the caller copies them out
         out_->finals.push_back({oi.id, oi.final_loc, reinterpret_cast<uint64_t>(s.buf.ptr), s.buf.size, false});
       } else if (s.state == SlotState::LIVE) {
         out_->finals.push_back({oi.id, oi.final_loc, reinterpret_cast<uint64_t>(s.buf.ptr), s.buf.size, true});

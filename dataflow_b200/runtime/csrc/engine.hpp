@@ -149,6 +149,7 @@ struct ExecOptions {
   bool record_events = false;
   bool keep_finals = true;          // hand final backing buffers to the caller instead of freeing
   double slab_headroom = 0.0;
+  bool manage_pools = true;         // size the session's slabs from the program's capacities
   std::atomic<bool>* cancel = nullptr;
 };
 

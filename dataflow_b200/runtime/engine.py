@@ -104,6 +104,8 @@ class ChainIndex:
         ir.bw_to = int(program.bandwidth_to_slow or 0)
         index: dict[str, int] = {}
         objs: list[Any] = []
+        # planned programs budget task scratch outside the object pool (see lowering.planning)
+        ext_ws = (program.metadata or {}).get("workspace_accounting") == "external"
 
         def obj(oid: str, size: int):
             if oid not in index:
@@ -140,7 +142,7 @@ class ChainIndex:
             tr.mutates = [index[i] for i in t.mutates]
             tr.releases = [index[i] for i in t.releases_after]
             tr.runtime_us = float(t.runtime_us)
-            tr.workspace = int(t.workspace_bytes)
+            tr.workspace = 0 if ext_ws else int(t.workspace_bytes)
             for out in t.outputs:
                 tr.add_output(index[out.id], _LOC[out.location])
             for d in t.offload_after:
@@ -179,7 +181,7 @@ class Engine:
                 initial_buffers: Mapping[str, Buffer] | None = None, *,
                 run_args: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
                 cancel_event: threading.Event | None = None, record_events: bool = False,
-                slab_headroom: float = 0.0) -> RunResult:
+                slab_headroom: float = 0.0, manage_pools: bool = True) -> RunResult:
         ci = self.chain_index(program)
         tasks = program.tasks
         run_values: dict[str, Any] = {}
@@ -224,7 +226,7 @@ class Engine:
             watcher.start()
         try:
             raw = self._native.execute(ci.ir, launch, initial, self.strict_final_locations,
-                                       self.poison_on_free, record_events, slab_headroom, cancel)
+                                       self.poison_on_free, record_events, slab_headroom, cancel, manage_pools)
         finally:
             if watcher is not None:
                 stop.set()
