@@ -185,6 +185,11 @@ def bench_ours(a) -> dict:
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},
     }
+    if os.environ.get("DFB_BENCH_TRACE") and rank == 0:
+        from dataflow_b200.run.trace_report import summarize_trace
+        with open(os.environ["DFB_BENCH_TRACE"], "w") as f:
+            json.dump({"summary": summarize_trace(tr.program, res), "measured": tr.measured,
+                       "plan_transfer": tr.planned.transfer}, f, indent=1)
     tr.close()
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -198,8 +198,8 @@ def block_kind_spec(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware, optim
     fwd_us = hw.matmul_us(gemm) + hw.attn_us(attn) + hw.mem_us(ew_bytes)
     bwd_us = hw.matmul_us(2 * gemm) + hw.attn_us(2.5 * attn, True) + hw.mem_us(2.5 * ew_bytes)
     w, dw, o = lay.block_w.size_bytes, lay.block_dw.size_bytes, lay.block_o.size_bytes
-    ws_f = T * max(d.qkv_dim, 2 * d.F) * 2 + (64 << 20)
-    ws_b = T * (2 * d.F * 2 + d.F + d.qkv_dim + 2 * d.d) * 2 + (64 << 20)
+    ws_f = T * max(d.qkv_dim, 2 * d.F) * 2 + (1 << 20)
+    ws_b = T * (2 * d.F * 2 + d.F + d.qkv_dim + 2 * d.d) * 2 + (1 << 20)
     return LayerKindSpec(
         "block", w, dw, o, lay.ctx.size_bytes, fwd_us, bwd_us, fwd_us, optimizer_cost_seed(hw, w, dw, o, optimizer),
         fwd_sub, bwd_sub, fwd_sub, (_subop("optimizer", nbytes=2 * w + dw + 2 * o, eff="memory"),),
@@ -210,7 +210,7 @@ def loose_costs(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware) -> LooseC
     T = d.T
     head_gemm = 2.0 * T * d.d * d.vocab
     head_us = hw.matmul_us(3 * head_gemm) + hw.mem_us(3.0 * T * d.vocab * 2)
-    ws = d.head_chunk * d.vocab * 2 + d.head_chunk * d.d * 4 + (32 << 20)
+    ws = d.head_chunk * d.vocab * 2 + d.head_chunk * d.d * 4 + (1 << 20)
     return LooseCosts(hw.mem_us(2.0 * T * d.d * 2) + 5, hw.mem_us(4.0 * T * d.d * 2) + 30, head_us, 2.0,
                       (_subop("head_gemms", 3 * head_gemm), _subop("ce", nbytes=3.0 * T * d.vocab * 2, eff="memory")), ws)
 

@@ -88,8 +88,10 @@ def plan_at_budget(family, cfg, budget_bytes: int | None, hw: ShapedHardware | N
     hw = hw or resolve_hardware(None)
     kw = dict(lower_kwargs or {})
 
+    fixed_levels = kw.pop("recompute_levels", None)
+
     def variant(levels):
-        p = fam.lower(cfg, recompute_levels=levels, hw=hw, **kw)
+        p = fam.lower(cfg, recompute_levels=levels if levels is not None else fixed_levels, hw=hw, **kw)
         return apply_measured_costs(p, measured) if measured else p
 
     program = variant(None)

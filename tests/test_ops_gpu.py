@@ -1,0 +1,179 @@
+"""Numerics of every hand-written sm_100a kernel against the plain PyTorch fp32 reference of the
+same op (the ``eager`` lane), plus the write-coverage check: running an op twice with different
+poison in its outputs must give identical bytes."""
+import pytest
+import torch
+
+from dataflow_b200.ops import eager, resolve_kernels
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def K():
+    k = resolve_kernels()
+    assert k.caps["sm100"], "these tests expect a Blackwell GPU"
+    assert len(k.native_ops()) >= 20, f"native kernels not selected: {k.describe()}"
+    return k
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 64), (300, 4096), (1000, 768), (33, 200)])
+def test_rmsnorm_fwd_bwd(K, rows, cols):
+    torch.manual_seed(0)
+    x, w, dy, add = bf(rows, cols), bf(cols) + 1, bf(rows, cols), bf(rows, cols)
+    y, rstd = K.rmsnorm_fwd(x, w, 1e-5)
+    yr, rr = eager.rmsnorm_fwd(x.float(), w.float(), 1e-5)
+    assert rel(y, yr) < 5e-3 and rel(rstd, rr) < 1e-5
+    assert rel(K.rmsnorm_apply(x, w, rstd), yr) < 5e-3
+    if cols % 8:
+        return
+    for acc in (False, True):
+        dw = bf(cols)
+        dw_ref = dw.float().clone()
+        dx = K.rmsnorm_bwd(dy, x, w, rstd, dx_add=add, dw=dw, accumulate=acc)
+        dxr = eager.rmsnorm_bwd(dy.float(), x.float(), w.float(), rr, dx_add=add.float(), dw=dw_ref, accumulate=acc)
+        assert rel(dx, dxr) < 5e-3 and rel(dw, dw_ref) < 1e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 768), (257, 1024)])
+def test_layernorm_fwd_bwd(K, rows, cols):
+    torch.manual_seed(1)
+    x, w, b, dy = bf(rows, cols) + 0.5, bf(cols) + 1, bf(cols), bf(rows, cols)
+    y, mean, rstd = K.layernorm_fwd(x, w, b, 1e-5)
+    yr, mr, rr = eager.layernorm_fwd(x.float(), w.float(), b.float(), 1e-5)
+    assert rel(y, yr) < 5e-3 and rel(mean, mr) < 1e-4 and rel(rstd, rr) < 1e-4
+    dw, db = torch.zeros(cols, device=DEV, dtype=torch.bfloat16), torch.zeros(cols, device=DEV, dtype=torch.bfloat16)
+    dwr, dbr = torch.zeros(cols, device=DEV), torch.zeros(cols, device=DEV)
+    dx = K.layernorm_bwd(dy, x, w, mean, rstd, dw=dw, db=db)
+    dxr = eager.layernorm_bwd(dy.float(), x.float(), w.float(), mr, rr, dw=dwr, db=dbr)
+    assert rel(dx, dxr) < 5e-3 and rel(dw, dwr) < 1e-2 and rel(db, dbr) < 1e-2
+
+
+def test_rope_strided_and_inverse(K):
+    torch.manual_seed(2)
+    t, hq, hkv, hd = 300, 8, 2, 128
+    qkv = bf(t, (hq + 2 * hkv) * hd)
+    pos = torch.arange(t, device=DEV, dtype=torch.int32) % 97
+    ref = qkv.float().clone()
+    q = qkv[:, :hq * hd].unflatten(1, (hq, hd))
+    K.rope_fwd(q, pos, 500000.0)
+    eager.rope_fwd(ref[:, :hq * hd].unflatten(1, (hq, hd)), pos, 500000.0)
+    assert rel(qkv, ref) < 5e-3
+    assert torch.equal(qkv[:, hq * hd:].float(), ref[:, hq * hd:])        # untouched columns
+    orig = bf(t, hq, hd)
+    x = orig.clone()
+    K.rope_fwd(x, pos, 10000.0)
+    K.rope_bwd(x, pos, 10000.0)
+    assert rel(x, orig) < 1e-2
+    # partial rotation at a column base (MLA-style decoupled rope)
+    y = bf(t, 4, 192)
+    yr = y.float().clone()
+    K.rope_fwd(y, pos, 10000.0, rot_dim=64, col_base=128)
+    eager.rope_fwd(yr, pos, 10000.0, rot_dim=64, col_base=128)
+    assert rel(y, yr) < 5e-3
+
+
+def test_swiglu_gelu_add(K):
+    torch.manual_seed(3)
+    rows, F = 513, 1024
+    h13, ds = bf(rows, 2 * F), bf(rows, F)
+    s = K.swiglu_packed_fwd(h13)
+    assert rel(s, eager.swiglu_packed_fwd(h13)) < 2e-3
+    d = K.swiglu_packed_bwd(ds, h13)
+    assert rel(d, eager.swiglu_packed_bwd(ds.float(), h13.float())) < 5e-3
+    x, dy = bf(rows, F), bf(rows, F)
+    assert rel(K.gelu_fwd_out(x), eager.gelu_fwd_out(x.float())) < 5e-3
+    assert rel(K.gelu_bwd(dy, x), eager.gelu_bwd(dy.float(), x.float())) < 5e-3
+    assert rel(K.add(x, dy), x.float() + dy.float()) < 5e-3
+
+
+@pytest.mark.parametrize("rows,vocab", [(64, 1000), (300, 50304), (17, 128256)])
+def test_ce_loss(K, rows, vocab):
+    torch.manual_seed(4)
+    logits = bf(rows, vocab, scale=2.0)
+    tgt = torch.randint(0, vocab, (rows,), device=DEV, dtype=torch.int32)
+    tgt[::5] = -1
+    ref_logits = logits.float().clone()
+    loss = K.ce_loss_fwd_bwd(logits, tgt, 1000.0)
+    loss_ref = eager.ce_loss_fwd_bwd(ref_logits, tgt, 1000.0)
+    assert abs(loss.item() - loss_ref.item()) < 1e-3 * abs(loss_ref.item()) + 1e-6
+    assert rel(logits, ref_logits) < 1e-2
+    assert torch.all(logits[::5] == 0)
+
+
+def test_embed_fwd_bwd_deterministic(K):
+    torch.manual_seed(5)
+    vocab, d, t = 1000, 256, 4096
+    table, dy = bf(vocab, d), bf(t, d)
+    tok = torch.randint(0, 50, (t,), device=DEV, dtype=torch.int32)       # heavy collisions
+    assert torch.equal(K.embed_fwd(tok, table), table[tok.long()])
+    g1, g2 = torch.full((vocab, d), 7.0, device=DEV, dtype=torch.bfloat16), torch.full((vocab, d), -3.0, device=DEV, dtype=torch.bfloat16)
+    K.embed_bwd_accum(tok, dy, g1, accumulate=False)
+    K.embed_bwd_accum(tok, dy, g2, accumulate=False)
+    assert torch.equal(g1, g2)                                           # create ignores previous bytes; order is fixed
+    ref = torch.zeros(vocab, d, device=DEV)
+    eager.embed_bwd_accum(tok, dy.float(), ref)
+    assert rel(g1, ref) < 5e-3
+    K.embed_bwd_accum(tok, dy, g1, accumulate=True)
+    assert rel(g1, 2 * ref) < 1e-2
+
+
+def test_adamw_variants(K):
+    torch.manual_seed(6)
+    n = 100_003
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
+    w, g = bf(n), bf(n)
+    m, v = torch.zeros(n, device=DEV, dtype=torch.bfloat16), torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    wr, mr, vr = w.clone(), m.clone(), v.clone()
+    for step in (1, 2, 3):
+        K.adamw_step(w, g, m, v, step=step, **hp)
+        eager.adamw_step(wr, g, mr, vr, step=step, **hp)
+    assert rel(w, wr) < 2e-3 and rel(m, mr) < 5e-3
+    master = torch.randn(n, device=DEV)
+    w2 = master.to(torch.bfloat16)
+    m32, v32 = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    mref, wref2, m2, v2 = master.clone(), w2.clone(), m32.clone(), v32.clone()
+    for step in (1, 2):
+        K.adamw_step(w2, g, m32, v32, step=step, master=master, **hp)
+        eager.adamw_step(wref2, g, m2, v2, step=step, master=mref, **hp)
+    assert rel(master, mref) < 1e-5 and torch.equal(w2, master.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (200, 264, 136), (1024, 768, 512), (4096, 1024, 2048)])
+def test_linear_triple_matches_fp32(K, M, N, K_):
+    torch.manual_seed(7)
+    x, w, dy, add = bf(M, K_), bf(K_, N, scale=0.05), bf(M, N), bf(M, N)
+    y = K.linear_fwd_bf16(x, w, add=add)
+    assert rel(y, x.float() @ w.float() + add.float()) < 5e-3
+    dx = K.linear_dgrad_bf16(dy, w)
+    assert rel(dx, dy.float() @ w.float().t()) < 5e-3
+    dw = torch.full((K_, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.linear_wgrad_bf16(x, dy, dw, accumulate=False)
+    ref = x.float().t() @ dy.float()
+    assert rel(dw, ref) < 5e-3
+    K.linear_wgrad_bf16(x, dy, dw, accumulate=True)
+    assert rel(dw, 2 * ref) < 1e-2
+    dw32 = torch.zeros(K_, N, device=DEV)
+    K.linear_wgrad_bf16(x, dy, dw32, accumulate=False)
+    assert rel(dw32, ref) < 1e-5
+    from dataflow_b200.ops import native
+    assert native().gemm_last_error() == 0
+
+
+def test_bias_grad_and_write_coverage(K):
+    torch.manual_seed(8)
+    dy = bf(1000, 768)
+    for poison in (5.0, -9.0):
+        db = torch.full((768,), poison, device=DEV, dtype=torch.bfloat16)
+        K.bias_grad(dy, db)
+        assert rel(db, dy.float().sum(0)) < 5e-3

@@ -1,0 +1,59 @@
+import pytest
+
+from chains import train_chain
+from dataflow_b200.core import from_sim_chain
+from dataflow_b200.runtime import DeadlockError, Engine, FakeBackend, compare_to_sim_eventlog
+from dataflow_b200.sim import run
+from dataflow_b200.sim.policies.pressurefit import PlanningError, pressurefit
+
+
+@pytest.mark.parametrize("cap", [20000, 6000, 3000, 2200, 1800])
+def test_pressurefit_fits_and_engine_matches_simulator_exactly(cap):
+    r = pressurefit(train_chain(), cap)
+    log = run(r.chain)
+    assert log.peak_fast_memory_bytes <= cap
+    assert r.makespan >= r.lower_bound
+    res = Engine(FakeBackend()).execute(from_sim_chain(r.chain)).raise_if_failed()
+    assert compare_to_sim_eventlog(res.trace, log) == []
+    assert res.slab_overflows == 0 and res.makespan_us == log.makespan
+
+
+def test_ample_budget_is_compute_bound_after_preload():
+    r = pressurefit(train_chain(L=4, rounds=1), 10 ** 9)
+    assert r.makespan <= r.lower_bound * 1.35      # first load and last write-back cannot overlap compute
+
+
+def test_infeasible_budget_raises():
+    with pytest.raises(PlanningError):
+        pressurefit(train_chain(), 1000)       # optimizer task alone needs 1600 bytes
+
+
+def test_engine_session_reuse_allocates_nothing_in_steady_state():
+    r = pressurefit(train_chain(L=4, rounds=2), 3000)
+    prog = from_sim_chain(r.chain)
+    eng = Engine(FakeBackend())
+    eng.execute(prog).raise_if_failed()
+    before = eng.session.vendor_allocs()
+    for _ in range(3):
+        res = eng.execute(prog).raise_if_failed()
+        assert res.vendor_allocs == 0
+    assert eng.session.vendor_allocs() == before
+
+
+def test_engine_deadlock_is_reported_not_hung():
+    from dataflow_b200.core import ObjectSpec, OutputSpec, Program, TaskSpec
+    p = Program("d", (ObjectSpec("x", 90, "fast"),), (TaskSpec("a", inputs=("x",), outputs=(OutputSpec("y", 20),)),),
+                fast_memory_capacity=100)
+    res = Engine(FakeBackend()).execute(p)
+    assert res.outcome.kind.value == "FAILED" and res.outcome.error_kind == "DeadlockError"
+    with pytest.raises(DeadlockError):
+        res.raise_if_failed()
+
+
+def test_transfer_time_distortion_changes_timing_not_results():
+    r = pressurefit(train_chain(L=4, rounds=2), 2500)
+    prog = from_sim_chain(r.chain)
+    be = FakeBackend()
+    be.transfer_time_scale = 3.0
+    res = Engine(be).execute(prog)
+    assert res.outcome.ok and res.makespan_us >= r.makespan
