@@ -173,14 +173,13 @@ class OptimizerStep(_Base):
 
     def run(self, ctx):
         wl, gl, ol = self.layouts_for(ctx)
+        if ctx.task.block_params.get("shard"):
+            from ..parallel.zero import sharded_optimizer_step
+            if sharded_optimizer_step(self, ctx, wl, gl, ol, None, None, None):
+                return
         w = self.views(ctx.inputs[0], wl)
         g = self.views(ctx.inputs[1], gl)
         o = self.views(ctx.inputs[2], ol) if len(ctx.inputs) > 2 else {}
-        shard = ctx.task.block_params.get("shard")
-        if shard or ctx.task.comm_groups:
-            from ..parallel.zero import sharded_optimizer_step
-            if sharded_optimizer_step(self, ctx, wl, gl, ol, w, g, o):
-                return
         self.update_fields(ctx, wl, w, g, o)
 
     def update_fields(self, ctx, wl, w, g, o, rows: Mapping[str, slice] | None = None):
@@ -212,7 +211,9 @@ class OptimizerStep(_Base):
 
 
 def common_executables(dims, layouts, kernels, device, hyper) -> dict[str, Any]:
+    from ..parallel.zero import ParamGather
     return {
+        "param_gather": ParamGather(dims, layouts, kernels, device, hyper),
         "prologue_round": RoundPrologue(dims, layouts, kernels, device, hyper),
         "embed_fwd": EmbedFwd(dims, layouts, kernels, device, hyper),
         "embed_bwd": EmbedBwd(dims, layouts, kernels, device, hyper),

@@ -151,9 +151,11 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                          block_params: Mapping[str, Any] | None = None,
                          comm_groups: Mapping[str, str] | None = None,
                          metadata: Mapping[str, Any] | None = None,
-                         opt_embed_us: float | None = None, opt_head_us: float | None = None) -> Program:
-    """Emit the bare program.  ``recompute_levels[i] > 0`` makes layer ``i`` save a reduced
-    context and inserts a ``{kind}_recompute`` task in front of its backward."""
+                         opt_embed_us: float | None = None, opt_head_us: float | None = None,
+                         zero: Mapping[str, Any] | None = None) -> Program:
+    """Emit the bare program.  ``recompute_levels[i] > 0`` (all rounds) or
+    ``recompute_levels[(round, i)] > 0`` (one round) makes layer ``i`` save a reduced context and
+    inserts a ``{kind}_recompute`` task in front of its backward."""
     L = cfg.n_layers
     assert len(layer_kinds) == L
     levels = dict(recompute_levels or {})
@@ -163,26 +165,47 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     tok_bytes = T * 4
     bp = dict(block_params or {})
     cg = dict(comm_groups or {})
+    # ZeRO data parallelism: stage 3 keeps only this rank's flat slice of every weight object
+    # (``Ws_*``) and of its optimizer state persistent; the full ``W_*`` is a per-step temp made by a
+    # ``param_gather`` task in front of its first use.  Stage 1 keeps ``W_*`` whole and persistent and
+    # shards the optimizer state only.
+    zstage = int(zero.get("stage", 0)) if zero else 0
+    zworld = int(zero.get("world", 1)) if zero else 1
+    zfactor = float(zero.get("opt_bytes_per_param_byte", 6.0)) if zero else 0.0
 
-    init: list[ObjectSpec] = [ObjectSpec("W_embed", embed_w_bytes, "backing", "parameter", persistent=True)]
-    if embed_o_bytes:
-        init.append(ObjectSpec("O_embed", embed_o_bytes, "backing", "optimizer_state", persistent=True))
+    def zslice(nbytes: int) -> int:
+        per = (nbytes + zworld - 1) // zworld
+        return (per + 255) // 256 * 256
+
+    def zo(nbytes: int, solo_o: int) -> int:
+        return int(zslice(nbytes) * zfactor) if zstage else solo_o
+
+    if zstage:
+        bp["shard"] = {"stage": zstage, "rank": int(zero.get("rank", 0)), "world": zworld}
+        cg.setdefault("dp", zero.get("group", "dp"))
+    gathered: dict[str, int] = {}        # W object id -> full byte size (stage 3)
+
+    def param_objects(name: str, w_bytes: int, o_bytes: int) -> None:
+        wid, oid = f"W_{name}", f"O_{name}"
+        if zstage == 3:
+            init.append(ObjectSpec(f"Ws_{name}", zslice(w_bytes), "backing", "parameter", persistent=True))
+            gathered[wid] = w_bytes
+        else:
+            init.append(ObjectSpec(wid, w_bytes, "backing", "parameter", persistent=True))
+        ob = zo(w_bytes, o_bytes)
+        if ob:
+            init.append(ObjectSpec(oid, ob, "backing", "optimizer_state", persistent=True))
+
+    init: list[ObjectSpec] = []
+    param_objects("embed", embed_w_bytes, embed_o_bytes)
     for i in range(L):
         k = kinds[layer_kinds[i]]
-        init.append(ObjectSpec(f"W_{i}", k.w_bytes, "backing", "parameter", persistent=True))
-        if k.o_bytes:
-            init.append(ObjectSpec(f"O_{i}", k.o_bytes, "backing", "optimizer_state", persistent=True))
+        param_objects(str(i), k.w_bytes, k.o_bytes)
         if k.aux_bytes:
             init.append(ObjectSpec(f"Aux_{i}", k.aux_bytes, "backing", "other", persistent=True))
-    if not cfg.tied_embeddings:
-        init.append(ObjectSpec("W_head", head_w_bytes, "backing", "parameter", persistent=True))
-        if head_o_bytes:
-            init.append(ObjectSpec("O_head", head_o_bytes, "backing", "optimizer_state", persistent=True))
-    elif head_w_bytes:
+    if head_w_bytes:
         # tied: the head object only carries what is not shared with the embedding (final norm)
-        init.append(ObjectSpec("W_head", head_w_bytes, "backing", "parameter", persistent=True))
-        if head_o_bytes:
-            init.append(ObjectSpec("O_head", head_o_bytes, "backing", "optimizer_state", persistent=True))
+        param_objects("head", head_w_bytes, head_o_bytes)
     for r in range(cfg.grad_accum_rounds):
         init.append(ObjectSpec(f"tokens_{s}_{r}", tok_bytes, "backing", "input"))
         init.append(ObjectSpec(f"targets_{s}_{r}", tok_bytes, "backing", "input"))
@@ -194,7 +217,25 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     last = R - 1
     opt_tasks_tail: list[TaskSpec] = []
 
+    def gather_task(wid: str, params) -> None:
+        """Stage 3: materialise the full weight object from the ranks' slices before its first use."""
+        if wid not in gathered:
+            return
+        nbytes = gathered[wid]
+        tasks.append(TaskSpec(f"param_gather_{s}_{wid[2:]}", inputs=("Ws_" + wid[2:],),
+                              outputs=(OutputSpec(wid, nbytes, "fast", "parameter"),),
+                              runtime_us=hw.comm_us(nbytes * (zworld - 1) / zworld) + hw.mem_us(2 * nbytes) + 10.0,
+                              group="comm", compute_block_key="param_gather", block_params={**bp, **params},
+                              comm_groups=cg, metadata=_meta(({"name": "all_gather", "memory_bytes": float(nbytes),
+                                                               "efficiency": "scale_up"},))))
+
     def opt_task(tid: str, key: str, w: str, dw: str, o: str | None, us: float, subops, ws: int, params) -> TaskSpec:
+        if zstage == 3:
+            w = "Ws_" + w[2:]
+        if zstage and o is None:
+            o = "O_" + w.split("_", 1)[1]
+        if zstage:
+            us = us / zworld + hw.comm_us(float(sizes_of[dw]) * (zworld - 1) / zworld) + 20.0
         ins = (w, dw) + ((o,) if o else ())
         return TaskSpec(tid, inputs=ins, mutates=(w,) + ((o,) if o else ()), runtime_us=us, workspace_bytes=ws,
                         group="optimizer", compute_block_key=key, block_params={**bp, **params},
@@ -203,8 +244,13 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     def place_opt(t: TaskSpec):
         (tasks if cfg.optimizer_placement == "interleaved" else opt_tasks_tail).append(t)
 
+    sizes_of: dict[str, int] = {f"dW_embed_{s}": embed_dw_bytes, f"dW_head_{s}": head_dw_bytes}
+    for i in range(L):
+        sizes_of[f"dW_{s}_{i}"] = kinds[layer_kinds[i]].dw_bytes
     for r in range(R):
         create = r == 0
+        if create:
+            gather_task("W_embed", {"target": "embed"})
         tasks.append(TaskSpec(f"prologue_round_{s}_{r}", outputs=(OutputSpec(f"current_round_{s}_{r}", 4, "fast", "other"),),
                               runtime_us=loose.prologue_us, group="prologue", compute_block_key="prologue_round",
                               block_params={**bp, "round": r}))
@@ -215,7 +261,7 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
         prev = f"y_embed_{s}_{r}"
         for i in range(L):
             k = kinds[layer_kinds[i]]
-            lvl = levels.get(i, 0)
+            lvl = levels.get((r, i), levels.get(i, 0))
             ctx_bytes = k.ctx_bytes
             if lvl:
                 ctx_bytes = next(sb for (lv, sb, _) in k.recompute_levels if lv == lvl)
@@ -225,6 +271,8 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
             if k.aux_temp_bytes:
                 outs.append(OutputSpec(f"AuxTemp_{s}_{r}_{i}", k.aux_temp_bytes, "fast", "other"))
             ins = (prev, f"W_{i}") + ((f"Aux_{i}",) if k.aux_bytes else ())
+            if create:
+                gather_task(f"W_{i}", {"target": "block", "layer": i})
             tasks.append(TaskSpec(f"block_fwd_{s}_{r}_{i}", inputs=ins, outputs=tuple(outs),
                                   mutates=(f"Aux_{i}",) if k.aux_bytes else (),
                                   runtime_us=k.fwd_us, workspace_bytes=k.workspace_fwd, group="fwd",
@@ -239,6 +287,8 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                     f"{k.kind}_fwd", f"{k.kind}_recompute", f"layer{i}"))
             prev = f"y_{s}_{r}_{i}"
         # head + loss
+        if create:
+            gather_task("W_head", {"target": "head"})
         head_in = [prev, f"targets_{s}_{r}", "W_head"] + (["W_embed"] if cfg.tied_embeddings else [])
         head_out = [OutputSpec(f"dy_{s}_{r}_{L - 1}" if L else f"dy_embed_{s}_{r}", x_bytes, "fast", "activation"),
                     OutputSpec(f"loss_{s}_{r}", 4, "backing", "output")]
@@ -262,13 +312,13 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
         finals[f"loss_{s}_{r}"] = "backing"
         if r == last and head_dw_bytes:
             place_opt(opt_task(f"optimizer_head_{s}", "optimizer_head", "W_head", head_dw,
-                               "O_head" if head_o_bytes else None,
+                               "O_head" if (head_o_bytes or zstage) else None,
                                opt_head_us if opt_head_us is not None else optimizer_cost_seed(hw, head_w_bytes, head_dw_bytes, head_o_bytes),
                                (), 0, {"step": s, "target": "head"}))
         # backward
         for i in reversed(range(L)):
             k = kinds[layer_kinds[i]]
-            lvl = levels.get(i, 0)
+            lvl = levels.get((r, i), levels.get(i, 0))
             x_in = f"y_{s}_{r}_{i - 1}" if i > 0 else f"y_embed_{s}_{r}"
             dy = f"dy_{s}_{r}_{i}"
             dx = f"dy_{s}_{r}_{i - 1}" if i > 0 else f"dy_embed_{s}_{r}"
@@ -299,7 +349,7 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                                   compute_block_key=f"{k.kind}_bwd", block_params={**bp, "layer": i, "round": r},
                                   comm_groups=cg, metadata=_meta(k.bwd_subops)))
             if r == last and k.dw_bytes:
-                place_opt(opt_task(f"optimizer_{s}_{i}", "optimizer_block", f"W_{i}", dw, f"O_{i}" if k.o_bytes else None,
+                place_opt(opt_task(f"optimizer_{s}_{i}", "optimizer_block", f"W_{i}", dw, f"O_{i}" if (k.o_bytes or zstage) else None,
                                    k.opt_us, k.opt_subops, k.workspace_opt, {"step": s, "layer": i, "kind": k.kind}))
         # embedding backward
         ein = [f"dy_embed_{s}_{r}", f"tokens_{s}_{r}"]
@@ -315,10 +365,12 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                               block_params={**bp, "round": r}))
         if r == last:
             place_opt(opt_task(f"optimizer_embed_{s}", "optimizer_embed", "W_embed", tied_dw,
-                               "O_embed" if embed_o_bytes else None,
+                               "O_embed" if (embed_o_bytes or zstage) else None,
                                opt_embed_us if opt_embed_us is not None else optimizer_cost_seed(hw, embed_w_bytes, embed_dw_bytes, embed_o_bytes),
                                (), 0, {"step": s, "target": "embed"}))
     tasks.extend(opt_tasks_tail)
+    if zstage:
+        metadata = {**dict(metadata or {}), "zero": {"stage": zstage, "world": zworld, "rank": int(zero.get("rank", 0))}}
     md = {"tokens_per_step": T * R, "tokens_per_round": T, "grad_accum_rounds": R, "n_layers": L,
           "hardware": hw.name, **dict(metadata or {})}
     return Program(cfg.name, tuple(init), tuple(tasks), finals, None, None,

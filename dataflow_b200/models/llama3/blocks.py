@@ -105,6 +105,14 @@ class _Block(_Base):
             a["lse"] = a["lse"][:, :n]
         return a
 
+    def partial_views(self, buf, n):
+        lay = self.lay.extra["Ap"]
+        a = self.views(buf, lay, context_rows(self.dims, n))
+        if n != self.dims.T:
+            a = dict(a)
+            a["lse"] = a["lse"][:, :n]
+        return a
+
     def common(self, ctx, x_buf, w_buf):
         d = self.dims
         seg = self.segments(ctx)
@@ -122,16 +130,22 @@ class BlockFwd(_Block):
         lvl = int(ctx.task.block_params.get("recompute_level", 0))
         if lvl == 0:
             st["a"] = self.ctx_views(ctx.outputs[1], st["n"])
+        elif lvl == 1:
+            # everything but h13 is saved (object Ap); h13 lives in scratch and is rebuilt before backward
+            st["a"] = dict(self.partial_views(ctx.outputs[1], st["n"]))
+            st["a"].update(self.scratch_ctx(st["n"], st["x"].device, only=("h13",)))
         else:
             st["a"] = self.scratch_ctx(st["n"], st["x"].device)      # context is dropped: recomputed before backward
         for _, fn, _ in self.stages:
             fn(self.K, d, st)
 
-    def scratch_ctx(self, n, device):
+    def scratch_ctx(self, n, device, only=None):
         import torch
         from ...runtime.interop import _dtypes
         out = {}
         for f in self.lay.ctx.fields:
+            if only is not None and f.name not in only:
+                continue
             shape = (f.shape[0], n) if f.name == "lse" else (n,) + tuple(f.shape[1:])
             out[f.name] = torch.empty(shape, dtype=_dtypes()[f.dtype], device=device)
         return out
@@ -143,6 +157,15 @@ class BlockRecompute(_Block):
     def run(self, ctx):
         st = self.common(ctx, ctx.inputs[0], ctx.inputs[1])
         st["a"] = self.ctx_views(ctx.outputs[0], st["n"])
+        lvl = int(ctx.task.block_params.get("recompute_level", 2))
+        if lvl == 1:
+            # (x, W, Ap) -> A: copy the saved fields, rebuild h13 = rmsnorm(h_mid) @ w13
+            saved = self.partial_views(ctx.inputs[2], st["n"])
+            for name, t in saved.items():
+                st["a"][name].copy_(t)
+            st["h2"] = self.K.rmsnorm_apply(st["a"]["h_mid"], st["w"]["ffn_norm"], st["a"]["rstd_ffn"])
+            stage_up_proj(self.K, self.dims, st)
+            return
         for _, fn, _ in recompute_stages(self.stages):
             fn(self.K, self.dims, st)
 

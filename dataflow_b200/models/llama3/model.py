@@ -110,7 +110,18 @@ def head_fields(d: Llama3Dims) -> tuple[Field, ...]:
             Field("w_head", (d.d, d.vocab), "bf16", "matrix", "normal"))
 
 
-def context_layout(d: Llama3Dims) -> PackedLayout:
+def context_layout(d: Llama3Dims, level: int = 0) -> PackedLayout:
+    """Saved context of one block.  Level 1 drops ``h13`` (two thirds of the bytes; rebuilt by one
+    norm re-apply + one GEMM), level 2 saves nothing."""
+    if level >= 2:
+        return PackedLayout(())
+    full = _context_layout_full(d)
+    if level == 1:
+        return PackedLayout(tuple(f for f in full.fields if f.name != "h13"))
+    return full
+
+
+def _context_layout_full(d: Llama3Dims) -> PackedLayout:
     f = [Field("rstd_attn", (d.T,), "fp32"), Field("qkv", (d.T, d.qkv_dim), "bf16")]
     if d.qk_norm:
         f += [Field("q_rstd", (d.T, d.hq), "fp32"), Field("k_rstd", (d.T, d.hkv), "fp32"),
@@ -167,6 +178,8 @@ class FamilyLayouts:
             return self.block_dw
         if oid.startswith("A_"):
             return self.ctx
+        if oid.startswith("Ap_"):
+            return self.extra.get("Ap")
         return self.extra.get(oid.split("_")[0])
 
 
@@ -179,7 +192,7 @@ def family_layouts(d: Llama3Dims, policy: DTypePolicy | None = None, optimizer: 
         weight_layout(bf, policy), grad_layout(bf, policy), opt_state_layout(bf, policy, rule_of=rule),
         weight_layout(ef, policy), grad_layout(ef, policy), opt_state_layout(ef, policy, rule_of=rule),
         weight_layout(hf, policy), grad_layout(hf, policy), opt_state_layout(hf, policy, rule_of=rule),
-        context_layout(d))
+        context_layout(d), {"Ap": context_layout(d, 1)})
 
 
 # --------------------------------------------------------------------------- cost seeds
@@ -203,7 +216,9 @@ def block_kind_spec(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware, optim
     return LayerKindSpec(
         "block", w, dw, o, lay.ctx.size_bytes, fwd_us, bwd_us, fwd_us, optimizer_cost_seed(hw, w, dw, o, optimizer),
         fwd_sub, bwd_sub, fwd_sub, (_subop("optimizer", nbytes=2 * w + dw + 2 * o, eff="memory"),),
-        ws_f, ws_b, 0, recompute_levels=((1, 0, fwd_us),))
+        ws_f, ws_b, 0,
+        recompute_levels=((1, lay.extra["Ap"].size_bytes, hw.matmul_us(2.0 * T * d.d * 2 * d.F) + hw.mem_us(ew_bytes / 3)),
+                          (2, 0, fwd_us)))
 
 
 def loose_costs(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware) -> LooseCosts:
@@ -226,7 +241,7 @@ def flops_per_token(cfg: ShapedLlama3Config) -> float:
 # --------------------------------------------------------------------------- lowering
 def lower_llama3(cfg: ShapedLlama3Config, recompute_levels: Mapping[int, int] | None = None,
                  hw: ShapedHardware | None = None, block_params: Mapping[str, Any] | None = None,
-                 comm_groups: Mapping[str, str] | None = None) -> Program:
+                 comm_groups: Mapping[str, str] | None = None, zero: Mapping[str, Any] | None = None) -> Program:
     hw = hw or resolve_hardware("b200")
     d = derive_dims(cfg)
     lay = family_layouts(d, cfg.policy(), cfg.optimizer)
@@ -237,7 +252,7 @@ def lower_llama3(cfg: ShapedLlama3Config, recompute_levels: Mapping[int, int] | 
         embed_w_bytes=lay.embed_w.size_bytes, embed_dw_bytes=lay.embed_dw.size_bytes, embed_o_bytes=lay.embed_o.size_bytes,
         head_w_bytes=lay.head_w.size_bytes, head_dw_bytes=lay.head_dw.size_bytes, head_o_bytes=lay.head_o.size_bytes,
         loose=loose_costs(d, lay, hw), hw=hw, recompute_levels=recompute_levels, block_params=block_params,
-        comm_groups=comm_groups,
+        comm_groups=comm_groups, zero=zero,
         metadata={"family": cfg.family, "preset": cfg.name, "flops_per_token": flops_per_token(cfg),
                   "seq_len": cfg.seq_len, "batch": cfg.batch})
 

@@ -172,6 +172,38 @@ static void gemm_bf16(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Te
 }
 static int64_t gemm_last_error() { return dfb::gemm_bf16_last_error(); }
 
+// ---------------------------------------------------------------- fused DP communication
+static void zero_rs_adamw(std::vector<int64_t> slabs, std::vector<int64_t> ctrls, int64_t rank, int64_t slots, int64_t slot,
+                          int64_t seq, int64_t ack_expect, int64_t grad_ptr, int64_t slice_begin, int64_t slice_len,
+                          c10::optional<Tensor> master, Tensor& m, Tensor& v, int64_t shard_ptr,
+                          std::vector<int64_t> fbegin, std::vector<int64_t> fend, std::vector<double> fwd, double lr,
+                          double b1, double b2, double eps, int64_t step, double gscale, double timeout_s, Tensor& err,
+                          Tensor& done_ctr) {
+  int world = slabs.size();
+  std::vector<unsigned long long> sl(slabs.begin(), slabs.end()), ct(ctrls.begin(), ctrls.end());
+  std::vector<long long> fb(fbegin.begin(), fbegin.end()), fe(fend.begin(), fend.end());
+  std::vector<float> fw(fwd.begin(), fwd.end());
+  CHECK_F32(m); CHECK_F32(v); CHECK_I32(err); CHECK_I32(done_ctr);
+  int rc = dfb::zero_rs_adamw(sl.data(), ct.data(), rank, world, slots, slot, (unsigned)seq, (unsigned)ack_expect,
+                              reinterpret_cast<const void*>(grad_ptr), slice_begin, slice_len,
+                              master.has_value() ? master->data_ptr<float>() : nullptr, m.data_ptr<float>(),
+                              v.data_ptr<float>(), reinterpret_cast<void*>(shard_ptr), fb.data(), fe.data(), fw.data(),
+                              fb.size(), lr, b1, b2, eps, step, gscale, timeout_s, err.data_ptr<int>(),
+                              reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "zero_rs_adamw launch failed with code ", rc);
+}
+static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls, int64_t rank, int64_t slots, int64_t slot,
+                         int64_t seq, int64_t ack_expect, int64_t shard_ptr, int64_t full_ptr, int64_t per_bytes,
+                         int64_t total_bytes, double timeout_s, Tensor& err, Tensor& done_ctr) {
+  int world = slabs.size();
+  std::vector<unsigned long long> sl(slabs.begin(), slabs.end()), ct(ctrls.begin(), ctrls.end());
+  int rc = dfb::param_gather(sl.data(), ct.data(), rank, world, slots, slot, (unsigned)seq, (unsigned)ack_expect,
+                             reinterpret_cast<const void*>(shard_ptr), reinterpret_cast<void*>(full_ptr), per_bytes,
+                             total_bytes, timeout_s, err.data_ptr<int>(),
+                             reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "param_gather launch failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- interop
 // Zero-copy tensor over engine-owned memory (device or pinned host).
 static Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
@@ -212,4 +244,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16);
   m.def("gemm_last_error", &gemm_last_error);
   m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("zero_rs_adamw", &zero_rs_adamw);
+  m.def("param_gather", &param_gather);
 }

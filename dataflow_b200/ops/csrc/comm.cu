@@ -1,0 +1,293 @@
+// Fused data-parallel communication kernels over NVLink peer memory (one process per GPU).
+//
+//   zero_rs_adamw : gradient reduce-scatter fused with the fp32 accumulate / cast and the
+//                   partitioned AdamW update.  Every rank owns one flat slice of a layer's
+//                   packed weight object.  The owner *pulls* its slice of every rank's local
+//                   gradient straight out of that rank's memory (plain peer loads over NVSwitch),
+//                   sums the contributions in rank order (deterministic), applies AdamW to its fp32
+//                   master / moment slice and writes the bf16 parameter slice — one kernel, no
+//                   staging buffers, no library collective.
+//   param_gather  : parameter all-gather by peer loads into the full per-layer weight object.
+//
+// Rendezvous is a small control block per rank in peer-mapped memory: a *mailbox*
+// (slot -> byte offset of the published buffer inside the rank's slab, plus a sequence number)
+// and an *ack* counter per slot.  A rank publishes a buffer, readers wait for the sequence number,
+// read, then bump the owner's ack counter; the owner leaves its kernel only after every reader has
+// acked, so the buffer stays valid while peers read it.  Every wait is bounded by %globaltimer;
+// on expiry the kernel records {phase, peer} in the error word, skips the rest and returns.
+//
+// The reference has no such kernels: its ZeRO lane is NCCL reduce-scatter -> Triton AdamW -> NCCL
+// all-gather (src/dataflow_training/blocks/adamw/rs.py:34-105).
+#include "common.cuh"
+#include "ops.h"
+
+namespace dfb {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxFields = 16;
+
+struct PeerTable {
+  unsigned char* slab[kMaxWorld];     // peer-mapped base of each rank's fast slab
+  unsigned char* ctrl[kMaxWorld];     // peer-mapped control block of each rank
+  int rank, world;
+};
+
+// control block layout (bytes): [0, 8*S) mailbox offsets (u64) | [8*S, 12*S) mailbox seq (u32) | [12*S, 16*S) ack (u32)
+DFB_DEVICE unsigned long long* mail_off(unsigned char* ctrl, int slots, int slot) {
+  return reinterpret_cast<unsigned long long*>(ctrl) + slot;
+}
+DFB_DEVICE unsigned int* mail_seq(unsigned char* ctrl, int slots, int slot) {
+  return reinterpret_cast<unsigned int*>(ctrl + 8ull * slots) + slot;
+}
+DFB_DEVICE unsigned int* ack_ctr(unsigned char* ctrl, int slots, int slot) {
+  return reinterpret_cast<unsigned int*>(ctrl + 12ull * slots) + slot;
+}
+
+DFB_DEVICE unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+DFB_DEVICE void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+DFB_DEVICE unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait until *p >= want (sequence numbers only grow).  false on timeout.
+DFB_DEVICE bool wait_ge(const unsigned int* p, unsigned int want, unsigned long long timeout_ns) {
+  unsigned long long t0 = gtimer();
+  for (;;) {
+    if (static_cast<int>(ld_acquire_sys(p) - want) >= 0) return true;
+    if (gtimer() - t0 > timeout_ns) return false;
+    __nanosleep(200);
+  }
+}
+
+struct FieldRange { long long begin, end; float wd; };   // element ranges of the flat object that take weight decay
+
+struct RsAdamwParams {
+  PeerTable peers;
+  int slots, slot;
+  unsigned int seq, ack_expect;
+  const bf16* grad;             // this rank's full local gradient (flat, n_total elements)
+  long long slice_begin;        // first element of this rank's slice in the flat object
+  long long slice_len;          // elements in this rank's slice (multiple of 8)
+  float* master;                // slice-sized fp32 master weights (may be null: update bf16 in place)
+  float* m;
+  float* v;
+  bf16* shard_out;              // slice-sized bf16 parameter shard
+  FieldRange fields[kMaxFields];
+  int n_fields;
+  float lr, b1, b2, eps, bc1, bc2, gscale;
+  unsigned long long timeout_ns;
+  int* err;                     // error word: 0 ok, else (phase << 8 | peer)
+  unsigned int* done_ctr;       // local counter for "last CTA" detection (zeroed by the kernel's last CTA)
+};
+
+__global__ void __launch_bounds__(512) zero_rs_adamw_kernel(RsAdamwParams p) {
+  __shared__ const bf16* src[kMaxWorld];
+  __shared__ int failed;
+  const int me = p.peers.rank, W = p.peers.world;
+  if (threadIdx.x == 0) failed = 0;
+  // publish my gradient buffer (one thread of the grid)
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *mail_off(p.peers.ctrl[me], p.slots, p.slot) =
+        static_cast<unsigned long long>(reinterpret_cast<const unsigned char*>(p.grad) - p.peers.slab[me]);
+    __threadfence_system();
+    st_release_sys(mail_seq(p.peers.ctrl[me], p.slots, p.slot), p.seq);
+  }
+  __syncthreads();
+  // every CTA resolves the peers' published buffers itself (no intra-grid dependency)
+  if (threadIdx.x < W) {
+    int r = threadIdx.x;
+    if (r == me) {
+      src[r] = p.grad;
+    } else if (wait_ge(mail_seq(p.peers.ctrl[r], p.slots, p.slot), p.seq, p.timeout_ns)) {
+      unsigned long long off = *reinterpret_cast<volatile unsigned long long*>(mail_off(p.peers.ctrl[r], p.slots, p.slot));
+      src[r] = reinterpret_cast<const bf16*>(p.peers.slab[r] + off);
+    } else {
+      atomicExch(p.err, (1 << 8) | r);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  if (!failed) {
+    const long long nvec = p.slice_len >> 3;
+    for (long long vi = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vi < nvec;
+         vi += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long e0 = vi << 3;                         // element inside the slice
+      const long long g0 = p.slice_begin + e0;              // element inside the flat object
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int r = 0; r < W; ++r) {                         // fixed rank order: deterministic sum
+        float f[8];
+        unpack8(ld8(src[r] + g0), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      float wd = 0.f;
+      for (int k = 0; k < p.n_fields; ++k)
+        if (g0 >= p.fields[k].begin && g0 < p.fields[k].end) wd = p.fields[k].wd;
+      float wv[8];
+      if (p.master) {
+        float4 a = *reinterpret_cast<const float4*>(p.master + e0), b = *reinterpret_cast<const float4*>(p.master + e0 + 4);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+      } else {
+        unpack8(ld8(p.shard_out + e0), wv);
+      }
+      float mv[8], vv[8];
+      {
+        float4 a = *reinterpret_cast<const float4*>(p.m + e0), b = *reinterpret_cast<const float4*>(p.m + e0 + 4);
+        mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
+        float4 c = *reinterpret_cast<const float4*>(p.v + e0), d = *reinterpret_cast<const float4*>(p.v + e0 + 4);
+        vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float g = acc[i] * p.gscale;
+        mv[i] = p.b1 * mv[i] + (1.f - p.b1) * g;
+        vv[i] = p.b2 * vv[i] + (1.f - p.b2) * g * g;
+        wv[i] -= p.lr * ((mv[i] / p.bc1) / (sqrtf(vv[i] / p.bc2) + p.eps) + wd * wv[i]);
+      }
+      *reinterpret_cast<float4*>(p.m + e0) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      *reinterpret_cast<float4*>(p.m + e0 + 4) = make_float4(mv[4], mv[5], mv[6], mv[7]);
+      *reinterpret_cast<float4*>(p.v + e0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      *reinterpret_cast<float4*>(p.v + e0 + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+      if (p.master) {
+        *reinterpret_cast<float4*>(p.master + e0) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+        *reinterpret_cast<float4*>(p.master + e0 + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+      }
+      st8(p.shard_out + e0, pack8(wv));
+    }
+  }
+  // last CTA of the grid: ack every peer (we are done reading them), then hold until every peer acked us
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) is_last = (atomicAdd(p.done_ctr, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    *p.done_ctr = 0;
+    for (int r = 0; r < W; ++r)
+      if (r != me) atomicAdd_system(ack_ctr(p.peers.ctrl[r], p.slots, p.slot), 1u);
+    if (!wait_ge(ack_ctr(p.peers.ctrl[me], p.slots, p.slot), p.ack_expect, p.timeout_ns)) atomicExch(p.err, (2 << 8) | me);
+  }
+}
+
+struct GatherParams {
+  PeerTable peers;
+  int slots, slot;
+  unsigned int seq, ack_expect;
+  const uint4* shard;        // my slice (published to the peers)
+  uint4* full;               // destination: the whole object
+  long long per_vec;         // 16-byte vectors per slice (slice stride)
+  long long total_vec;       // 16-byte vectors in the whole object
+  unsigned long long timeout_ns;
+  int* err;
+  unsigned int* done_ctr;
+};
+
+__global__ void __launch_bounds__(512) param_gather_kernel(GatherParams p) {
+  __shared__ const uint4* src[kMaxWorld];
+  __shared__ int failed, is_last;
+  const int me = p.peers.rank, W = p.peers.world;
+  if (threadIdx.x == 0) failed = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *mail_off(p.peers.ctrl[me], p.slots, p.slot) =
+        static_cast<unsigned long long>(reinterpret_cast<const unsigned char*>(p.shard) - p.peers.slab[me]);
+    __threadfence_system();
+    st_release_sys(mail_seq(p.peers.ctrl[me], p.slots, p.slot), p.seq);
+  }
+  __syncthreads();
+  if (threadIdx.x < W) {
+    int r = threadIdx.x;
+    if (r == me) {
+      src[r] = p.shard;
+    } else if (wait_ge(mail_seq(p.peers.ctrl[r], p.slots, p.slot), p.seq, p.timeout_ns)) {
+      unsigned long long off = *reinterpret_cast<volatile unsigned long long*>(mail_off(p.peers.ctrl[r], p.slots, p.slot));
+      src[r] = reinterpret_cast<const uint4*>(p.peers.slab[r] + off);
+    } else {
+      atomicExch(p.err, (3 << 8) | r);
+      failed = 1;
+    }
+  }
+  __syncthreads();
+  if (!failed) {
+    for (long long vi = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vi < p.total_vec;
+         vi += static_cast<long long>(gridDim.x) * blockDim.x) {
+      // start with the slice after mine so that the ranks do not all hit the same peer at once
+      long long rot = (vi + (static_cast<long long>(me) + 1) * p.per_vec) % p.total_vec;
+      int r = static_cast<int>(rot / p.per_vec);
+      if (r >= W) r = W - 1;
+      p.full[rot] = src[r][rot - static_cast<long long>(r) * p.per_vec];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(p.done_ctr, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (is_last && threadIdx.x == 0) {
+    *p.done_ctr = 0;
+    for (int r = 0; r < W; ++r)
+      if (r != me) atomicAdd_system(ack_ctr(p.peers.ctrl[r], p.slots, p.slot), 1u);
+    if (!wait_ge(ack_ctr(p.peers.ctrl[me], p.slots, p.slot), p.ack_expect, p.timeout_ns)) atomicExch(p.err, (4 << 8) | me);
+  }
+}
+
+// ---------------------------------------------------------------------------- host entry points
+static PeerTable make_table(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world) {
+  PeerTable t{};
+  for (int i = 0; i < world && i < kMaxWorld; ++i) {
+    t.slab[i] = reinterpret_cast<unsigned char*>(slabs[i]);
+    t.ctrl[i] = reinterpret_cast<unsigned char*>(ctrls[i]);
+  }
+  t.rank = rank;
+  t.world = world;
+  return t;
+}
+
+int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                  unsigned int seq, unsigned int ack_expect, const void* grad, long long slice_begin, long long slice_len,
+                  float* master, float* m, float* v, void* shard_out, const long long* field_begin,
+                  const long long* field_end, const float* field_wd, int n_fields, float lr, float b1, float b2, float eps,
+                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s) {
+  if (world > kMaxWorld || n_fields > kMaxFields || (slice_len & 7) || (slice_begin & 7)) return -2;
+  RsAdamwParams p{};
+  p.peers = make_table(slabs, ctrls, rank, world);
+  p.slots = slots; p.slot = slot; p.seq = seq; p.ack_expect = ack_expect;
+  p.grad = reinterpret_cast<const bf16*>(grad);
+  p.slice_begin = slice_begin; p.slice_len = slice_len;
+  p.master = master; p.m = m; p.v = v; p.shard_out = reinterpret_cast<bf16*>(shard_out);
+  for (int i = 0; i < n_fields; ++i) p.fields[i] = {field_begin[i], field_end[i], field_wd[i]};
+  p.n_fields = n_fields;
+  p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps;
+  p.bc1 = 1.f - powf(b1, (float)step); p.bc2 = 1.f - powf(b2, (float)step);
+  p.gscale = gscale;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.err = err; p.done_ctr = done_ctr;
+  zero_rs_adamw_kernel<<<num_sms, 512, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int param_gather(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                 unsigned int seq, unsigned int ack_expect, const void* shard, void* full, long long per_bytes,
+                 long long total_bytes, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s) {
+  if (world > kMaxWorld || (per_bytes & 15) || (total_bytes & 15)) return -2;
+  GatherParams p{};
+  p.peers = make_table(slabs, ctrls, rank, world);
+  p.slots = slots; p.slot = slot; p.seq = seq; p.ack_expect = ack_expect;
+  p.shard = reinterpret_cast<const uint4*>(shard);
+  p.full = reinterpret_cast<uint4*>(full);
+  p.per_vec = per_bytes >> 4; p.total_vec = total_bytes >> 4;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.err = err; p.done_ctr = done_ctr;
+  param_gather_kernel<<<num_sms, 512, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace dfb

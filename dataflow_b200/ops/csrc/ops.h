@@ -57,4 +57,14 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
               int num_sms, cudaStream_t stream);
 int gemm_bf16_last_error();
 
+// ---- fused data-parallel communication (comm.cu)
+int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                  unsigned int seq, unsigned int ack_expect, const void* grad, long long slice_begin, long long slice_len,
+                  float* master, float* m, float* v, void* shard_out, const long long* field_begin,
+                  const long long* field_end, const float* field_wd, int n_fields, float lr, float b1, float b2, float eps,
+                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);
+int param_gather(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                 unsigned int seq, unsigned int ack_expect, const void* shard, void* full, long long per_bytes,
+                 long long total_bytes, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);
+
 }  // namespace dfb

@@ -120,8 +120,9 @@ def _rope(x, positions, theta, rot_dim, col_base, sign):
     cs, sn = torch.cos(ang).unsqueeze(1), (torch.sin(ang) * sign).unsqueeze(1)
     a = x[..., col_base:col_base + half].float()
     b = x[..., col_base + half:col_base + rot_dim].float()
-    x[..., col_base:col_base + half] = _st(a * cs - b * sn, x)
-    x[..., col_base + half:col_base + rot_dim] = _st(b * cs + a * sn, x)
+    lo, hi = _st(a * cs - b * sn, x), _st(b * cs + a * sn, x)     # both halves before either is overwritten
+    x[..., col_base:col_base + half] = lo
+    x[..., col_base + half:col_base + rot_dim] = hi
     return x
 
 

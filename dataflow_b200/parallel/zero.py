@@ -1,0 +1,337 @@
+"""ZeRO data parallelism over one NVSwitch box.
+
+Each rank owns one flat, 256-byte aligned slice of every packed weight object.
+Stage 3 keeps only that slice (``Ws_*``) and its optimizer state persistent; the
+full ``W_*`` is gathered once per step in front of its first use.  Stage 1 keeps
+``W_*`` whole and shards the optimizer state.  Two lanes serve a group:
+
+* ``p2p``  — the hand-written fused kernels of ``ops/csrc/comm.cu``: gradient
+  reduce-scatter ⊕ fp32 accumulate ⊕ partitioned AdamW in ONE kernel that pulls the
+  peers' gradients over NVLink by plain peer loads, and an all-gather by peer loads.
+  Every rank's engine slab and a small control block are mapped into the peers
+  through CUDA IPC handles exchanged over ``torch.distributed``.
+* ``collective`` — ``torch.distributed`` reduce-scatter / all-gather + the local AdamW
+  kernel: the baseline lane (NCCL on GPUs, gloo on CPU ranks) and the oracle of the
+  bitwise tests.
+
+Reference: its ZeRO-1 lanes ``blocks/adamw/rs.py:34-105`` (flat equal slices) and
+``distributed/sharding.py:588-652``; ZeRO-3 is absent there.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, Mapping
+
+from ..blocks.base_blocks import _Base
+from ..blocks.layouts import Field, PackedLayout
+from ..blocks.optim import lr_at
+
+
+class CommTimeout(RuntimeError):
+    """A fused communication kernel gave up waiting for a peer (the error word names phase and peer)."""
+
+
+def slice_bytes(total: int, world: int) -> int:
+    per = (total + world - 1) // world
+    return (per + 255) // 256 * 256
+
+
+def slice_range(total: int, world: int, rank: int) -> tuple[int, int]:
+    """(byte offset, byte length) of ``rank``'s slice; trailing ranks may be short or empty."""
+    per = slice_bytes(total, world)
+    lo = min(per * rank, total)
+    hi = min(per * (rank + 1), total)
+    return lo, hi - lo
+
+
+def zero_opt_layout(slice_nbytes: int, master: bool = True) -> PackedLayout:
+    """Optimizer state of one slice: fp32 master (optional) + fp32 first / second moments."""
+    n = slice_nbytes // 2
+    f = ([Field("master", (n,), "fp32")] if master else []) + [Field("m", (n,), "fp32"), Field("v", (n,), "fp32")]
+    return PackedLayout(tuple(f))
+
+
+def zero_lower_kwargs(mode: str, rank: int, world: int, group: str = "dp") -> dict[str, Any]:
+    stage = {"zero3": 3, "zero1": 1, "zero1rs": 1}.get(mode)
+    if stage is None:
+        raise KeyError(f"unknown ZeRO mode {mode!r} (zero3 | zero1)")
+    # fp32 master + two fp32 moments per bf16 parameter: 12 bytes per 2 parameter bytes, 256-byte aligned planes
+    return {"zero": {"stage": stage, "rank": rank, "world": world, "group": group, "opt_bytes_per_param_byte": 6.0}}
+
+
+@dataclass
+class _Slot:
+    calls: int = 0
+
+
+class DpGroup:
+    """One data-parallel group as seen by this rank."""
+
+    SLOTS = 512
+
+    def __init__(self, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 60.0):
+        self.rank, self.world, self.device = rank, world, device
+        self.lane = lane or ("p2p" if device is not None else "collective")
+        self.timeout_s = timeout_s
+        self.calls: dict[int, int] = {}
+        self.slabs: list[int] = []
+        self.ctrls: list[int] = []
+        self.backend = None
+        self.err = None
+        self.done = None
+        self.name = "dp"
+
+    # -- set-up (p2p lane): map every rank's slab and control block
+    def attach(self, trainer) -> None:
+        if self.lane != "p2p":
+            return
+        import torch
+        import torch.distributed as dist
+        be = trainer.backend
+        self.backend = be
+        base, cap = trainer.session.native.fast_slab()
+        if not base:
+            raise RuntimeError("the p2p lane needs the engine's fast slab to exist before attach()")
+        self.slab_base, self.slab_cap = base, cap
+        self.ctrl = be.device_alloc_zeroed(16 * self.SLOTS)
+        mine = (be.ipc_handle(base), be.ipc_handle(self.ctrl))
+        handles: list[Any] = [None] * self.world
+        dist.all_gather_object(handles, mine)
+        self.slabs, self.ctrls = [], []
+        for r, (hs, hc) in enumerate(handles):
+            if r == self.rank:
+                self.slabs.append(base)
+                self.ctrls.append(self.ctrl)
+            else:
+                self.slabs.append(be.ipc_open(hs))
+                self.ctrls.append(be.ipc_open(hc))
+        dev = torch.device("cuda", self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        dist.barrier()
+
+    def _in_slab(self, ptr: int, nbytes: int) -> None:
+        if not (self.slab_base <= ptr and ptr + nbytes <= self.slab_base + self.slab_cap):
+            raise RuntimeError("a buffer published to peers lies outside the peer-mapped engine slab "
+                               "(slab overflow): raise the budget headroom")
+
+    def _next(self, slot: int) -> tuple[int, int]:
+        c = self.calls.get(slot, 0) + 1
+        self.calls[slot] = c
+        return c, c * (self.world - 1)
+
+    def check(self) -> None:
+        """Raise if a kernel of this group timed out (reads the error word: a host sync)."""
+        if self.err is not None:
+            code = int(self.err.item())
+            if code:
+                self.err.zero_()
+                raise CommTimeout(f"fused communication kernel gave up: phase {code >> 8}, peer/rank {code & 255}")
+
+    # -- collectives
+    def rs_adamw(self, slot: int, grad, begin_elem: int, len_elem: int, master, m, v, shard_out, fields, hyper, step, K):
+        """grad: flat bf16 tensor of the whole object.  Updates (master, m, v, shard_out) of this rank's slice."""
+        lr = lr_at(hyper, step)
+        b1, b2, eps = hyper.get("beta1", 0.9), hyper.get("beta2", 0.95), hyper.get("eps", 1e-8)
+        if self.lane == "p2p":
+            from ..ops import native
+            from ..ops.cuda import LAUNCHES
+            seq, ack = self._next(slot)
+            self._in_slab(grad.data_ptr(), grad.numel() * 2)
+            native().zero_rs_adamw(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, grad.data_ptr(),
+                                   begin_elem, len_elem, master, m, v, shard_out.data_ptr(),
+                                   [f[0] for f in fields], [f[1] for f in fields], [f[2] for f in fields],
+                                   lr, b1, b2, eps, int(step), 1.0, self.timeout_s, self.err, self.done)
+            LAUNCHES.total += 1
+            return
+        import torch
+        import torch.distributed as dist
+        per = slice_bytes(grad.numel() * 2, self.world) // 2
+        g32 = torch.zeros(per * self.world, dtype=torch.float32, device=grad.device)
+        g32[:grad.numel()] = grad.float()
+        if dist.get_backend() == "gloo":
+            dist.all_reduce(g32)
+            acc = g32[self.rank * per:self.rank * per + len_elem].clone()
+        else:
+            out = torch.empty(per, dtype=torch.float32, device=grad.device)
+            dist.reduce_scatter_tensor(out, g32)
+            acc = out[:len_elem]
+        wd_vec = torch.zeros(len_elem, dtype=torch.float32, device=grad.device)
+        for b, e, wd in fields:
+            lo, hi = max(b, begin_elem) - begin_elem, min(e, begin_elem + len_elem) - begin_elem
+            if hi > lo:
+                wd_vec[lo:hi] = wd
+        m.mul_(b1).add_(acc, alpha=1 - b1)
+        v.mul_(b2).addcmul_(acc, acc, value=1 - b2)
+        w = master if master is not None else shard_out.float()
+        upd = (m / (1 - b1 ** step)) / ((v / (1 - b2 ** step)).sqrt() + eps) + wd_vec * w
+        w = w - lr * upd
+        if master is not None:
+            master.copy_(w)
+        shard_out.copy_(w.to(shard_out.dtype))
+
+    def gather(self, slot: int, shard, full, per_bytes: int) -> None:
+        """shard, full: uint8 tensors; ``full`` receives every rank's slice at ``rank * per_bytes``."""
+        total = full.numel()
+        if self.lane == "p2p":
+            from ..ops import native
+            from ..ops.cuda import LAUNCHES
+            seq, ack = self._next(slot)
+            self._in_slab(shard.data_ptr(), min(per_bytes, shard.numel()))
+            native().param_gather(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, shard.data_ptr(),
+                                  full.data_ptr(), per_bytes, total, self.timeout_s, self.err, self.done)
+            LAUNCHES.total += 1
+            return
+        import torch
+        import torch.distributed as dist
+        mine = torch.zeros(per_bytes, dtype=torch.uint8, device=full.device)
+        n = min(per_bytes, shard.numel())
+        mine[:n] = shard[:n]
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine)
+        for r, p in enumerate(parts):
+            lo, ln = slice_range(total, self.world, r)
+            if ln:
+                full[lo:lo + ln] = p[:ln]
+
+    def close(self) -> None:
+        if self.lane == "p2p" and self.backend is not None:
+            for r, (s, c) in enumerate(zip(self.slabs, self.ctrls)):
+                if r != self.rank:
+                    self.backend.ipc_close(s)
+                    self.backend.ipc_close(c)
+            self.backend.device_free(self.ctrl)
+            self.slabs, self.ctrls = [], []
+
+
+def make_dp_group(rank: int, world: int, device: int | None, lane: str | None = None) -> DpGroup:
+    lane = lane or os.environ.get("DATAFLOW_DP_LANE")
+    return DpGroup(rank, world, device, lane)
+
+
+def slot_of(target: str, layer: int | None, kind: int) -> int:
+    """kind 0: gradient reduce-scatter, kind 1: parameter gather."""
+    idx = 0 if target == "embed" else 1 if target == "head" else 2 + int(layer)
+    return 2 * idx + kind
+
+
+def wd_fields(layout: PackedLayout, wd: float, wd_all: bool = False) -> list[tuple[int, int, float]]:
+    """Element ranges (bf16 elements of the flat packed object) that take weight decay."""
+    offs = layout.offsets()
+    out = []
+    for f in layout.fields:
+        if wd and (wd_all or f.kind in ("matrix", "embedding")):
+            out.append((offs[f.name] // 2, (offs[f.name] + f.nbytes) // 2, float(wd)))
+    return out
+
+
+def _flat(buf, nbytes: int, dtype: str, device):
+    from ..runtime.interop import torch_view
+    item = {"bf16": 2, "uint8": 1, "fp32": 4}[dtype]
+    return torch_view(buf, (nbytes // item,), dtype, 0, device if buf.location == "fast" else None)
+
+
+def _group(ctx) -> DpGroup:
+    name = ctx.task.comm_groups.get("dp", "dp")
+    g = ctx.groups.get(name)
+    if g is None:
+        raise KeyError(f"task {ctx.task.id} needs peer group {name!r} but the run was started without it")
+    return g
+
+
+class ParamGather(_Base):
+    """(Ws_X) -> (W_X): all-gather of the ranks' flat slices into the full packed weight object."""
+
+    def run(self, ctx):
+        g = _group(ctx)
+        bp = ctx.task.block_params
+        full_b = ctx.outputs[0]
+        shard = _flat(ctx.inputs[0], ctx.inputs[0].size, "uint8", self.device)
+        full = _flat(full_b, full_b.size, "uint8", self.device)
+        g.gather(slot_of(bp.get("target", "block"), bp.get("layer"), 1), shard, full, slice_bytes(full_b.size, g.world))
+
+
+def sharded_optimizer_step(exe, ctx, wl, gl, ol, w, g, o) -> bool:
+    """ZeRO optimizer task: ``(Ws|W, dW, O) -> update of this rank's slice`` (+ in-place gather at stage 1)."""
+    shard = ctx.task.block_params.get("shard")
+    if not shard:
+        return False
+    grp = _group(ctx)
+    stage, rank, world = int(shard["stage"]), grp.rank, grp.world
+    bp = ctx.task.block_params
+    total = wl.size_bytes
+    lo, ln = slice_range(total, world, rank)
+    per = slice_bytes(total, world)
+    dev = exe.device
+    grad = _flat(ctx.inputs[1], total, "bf16", dev)
+    ost = zero_opt_layout(per).views(ctx.inputs[2], dev if ctx.inputs[2].location == "fast" else None)
+    n = ln // 2
+    if stage == 3:
+        shard_out = _flat(ctx.inputs[0], per, "bf16", dev)[:n]
+    else:
+        shard_out = _flat(ctx.inputs[0], total, "bf16", dev)[lo // 2:lo // 2 + n]
+    hy = exe.hyper
+    fields = wd_fields(wl, hy.get("weight_decay", 0.0), bool(hy.get("wd_all")))
+    step = int(ctx.run_args.get("step", 1))
+    tgt = bp.get("target", "block")
+    if n:
+        grp.rs_adamw(slot_of(tgt, bp.get("layer"), 0), grad, lo // 2, n, ost["master"][:n], ost["m"][:n], ost["v"][:n],
+                     shard_out, fields, hy, step, exe.K)
+    else:
+        grp.rs_adamw(slot_of(tgt, bp.get("layer"), 0), grad, 0, 0, ost["master"][:0], ost["m"][:0], ost["v"][:0],
+                     shard_out, fields, hy, step, exe.K)
+    if stage == 1:
+        full = _flat(ctx.inputs[0], total, "uint8", dev)
+        grp.gather(slot_of(tgt, bp.get("layer"), 1), full[lo:lo + ln], full, per)
+    return True
+
+
+def zero_initial_values(fam, cfg, program, store, seed: int, layouts, rank: int, world: int, stage: int) -> None:
+    """Seeded init under ZeRO: every rank generates the same full objects one at a time (same seed,
+    same order as the solo program) and keeps its slice; master = fp32 copy of the slice, moments zero."""
+    import torch
+    from ..runtime.executable import Buffer
+    solo = fam.lower(cfg)
+    keep = tuple(o for o in solo.initial_objects if o.id.startswith("W_"))
+    import dataclasses
+    solo = dataclasses.replace(solo, initial_objects=keep)
+    pending: dict[str, Any] = {}
+
+    def flush():
+        for oid, (t, lay) in list(pending.items()):
+            name = oid[2:]
+            total = lay.size_bytes
+            lo, ln = slice_range(total, world, rank)
+            per = slice_bytes(total, world)
+            raw = t
+            if stage == 3:
+                dst = views_of_raw(f"Ws_{name}", per)
+                dst.zero_()
+                dst[:ln] = raw[lo:lo + ln]
+            else:
+                views_of_raw(oid, total).copy_(raw)
+            ost = zero_opt_layout(per).views(store_buffer(f"O_{name}"), None)
+            ost["m"].zero_()
+            ost["v"].zero_()
+            ost["master"].zero_()
+            if ln:
+                ost["master"][:ln // 2] = raw[lo:lo + ln].view(torch.bfloat16).float()
+            del pending[oid]
+
+    store_buffer = store.buffer
+
+    def views_of_raw(oid, nbytes):
+        from ..runtime.interop import torch_view
+        return torch_view(store_buffer(oid), (nbytes,), "uint8", 0, None)
+
+    def temp_views(oid, layout):
+        from ..runtime.interop import invalidate_views
+        flush()
+        invalidate_views()       # temp tensors may reuse an address: never serve a stale cached view
+        t = torch.zeros(layout.size_bytes, dtype=torch.uint8)
+        pending[oid] = (t, layout)
+        return layout.views(Buffer(t.data_ptr(), t.numel(), "backing", oid), None)
+
+    fam.initial_values(solo, cfg, temp_views, seed, layouts=layouts)
+    flush()

@@ -168,6 +168,10 @@ class Trainer:
             self.session.native.ensure_pools(int(min(fast, planned.peak_fast_bytes + (512 << 20))), int(transient_backing), 0.0)
         self.step_index = 0
         self.last_result = None
+        self.zero = (self.program.metadata or {}).get("zero")
+        for g in self.groups.values():
+            if hasattr(g, "attach"):
+                g.attach(self)
         if init:
             self.init_model(seed)
 
@@ -180,7 +184,12 @@ class Trainer:
         return torch_view(self.store.buffer(oid), shape, dtype, 0, None)
 
     def init_model(self, seed: int = 0) -> None:
-        self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts)
+        if self.zero:
+            from ..parallel.zero import zero_initial_values
+            zero_initial_values(self.fam, self.cfg, self.program, self.store, seed, self.layouts,
+                                int(self.zero["rank"]), int(self.zero["world"]), int(self.zero["stage"]))
+        else:
+            self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts)
 
     # -- data
     def put_round(self, r: int, tokens, targets) -> int:
@@ -213,6 +222,9 @@ class Trainer:
                                   groups=self.groups, manage_pools=self.device is None)
         self.last_result = res
         res.raise_if_failed()
+        for g in self.groups.values():
+            if hasattr(g, "check"):
+                g.check()
         loss = 0.0
         for k in self.loss_ids:
             loss += float(self.host_tensor(k, (1,), "fp32")[0])
@@ -220,6 +232,9 @@ class Trainer:
 
     def close(self):
         self.backend.synchronize()
+        for g in self.groups.values():
+            if hasattr(g, "close"):
+                g.close()
         from ..runtime.interop import invalidate_views
         invalidate_views()
         self.store.close()

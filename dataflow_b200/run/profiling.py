@@ -16,7 +16,7 @@ from typing import Any, Mapping
 
 from ..core import Program, TaskSpec
 
-PROFILE_CACHE_REV = 3
+PROFILE_CACHE_REV = 4
 
 
 def task_signature(t: TaskSpec) -> str:
@@ -61,7 +61,7 @@ def profile_program(trainer, program: Program | None = None, *, steps: int = 3, 
     if use_cache and path.exists():
         return json.loads(path.read_text())
     out: dict[str, list[float]] = {}
-    for levels in (None, {0: 1}):
+    for levels in (None, {0: 1}, {0: 2}):
         small = dataclasses.replace(cfg, n_layers=1, grad_accum_rounds=2)
         tr = Trainer(trainer.fam.name, small, budget_gib=None, device=trainer.device, hyper=trainer.hyper,
                      kernels=trainer.K, recompute=False, profile=False,

@@ -5,6 +5,7 @@
 #include <pybind11/stl.h>
 
 #include <atomic>
+#include <cstring>
 
 #include "backends_host.hpp"
 #include "engine.hpp"
@@ -106,6 +107,31 @@ PYBIND11_MODULE(_runtime, m) {
         return reinterpret_cast<uint64_t>(b.pin_region(n, populate));
       }, py::arg("bytes"), py::arg("populate") = true)
       .def("unpin_region", [](CudaBackend& b, uint64_t p, size_t n) { b.unpin_region(reinterpret_cast<void*>(p), n); })
+      .def("ipc_handle", [](CudaBackend&, uint64_t ptr) {
+        cudaIpcMemHandle_t h;
+        cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(ptr));
+        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+        return py::bytes(reinterpret_cast<const char*>(&h), sizeof(h));
+      })
+      .def("ipc_open", [](CudaBackend&, py::bytes handle) {
+        std::string s = handle;
+        if (s.size() != sizeof(cudaIpcMemHandle_t)) throw std::runtime_error("bad IPC handle size");
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, s.data(), sizeof(h));
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+        return reinterpret_cast<uint64_t>(p);
+      })
+      .def("ipc_close", [](CudaBackend&, uint64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); })
+      .def("device_alloc_zeroed", [](CudaBackend&, size_t n) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, n) != cudaSuccess) throw std::runtime_error("cudaMalloc failed");
+        cudaMemset(p, 0, n);
+        cudaDeviceSynchronize();
+        return reinterpret_cast<uint64_t>(p);
+      })
+      .def("device_free", [](CudaBackend&, uint64_t p) { cudaFree(reinterpret_cast<void*>(p)); })
       .def("measure_pcie", [](CudaBackend& b, size_t bytes, int repeats) {
         double out[4];
         {

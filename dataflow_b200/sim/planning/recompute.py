@@ -3,83 +3,123 @@
 Each saved-context object may carry recompute options (``RecomputeRewrite``): level 0
 keeps the full context, higher levels keep less and add a recompute task in front of
 the backward.  The selector prices whole assignments by re-lowering
-(``build_variant(levels)``), planning and simulating them: seeds *none*, *all* and
-*every other layer*, then an evidence-directed greedy pass that flips the layers
-whose context the best plan so far had to stream through backing memory.  Role
-parity: reference ``src/dataflow_sim/planning/recompute.py:48-224``.
+(``build_variant(levels)``), planning and simulating them:
+
+* seeds: nothing recomputed, every layer at each offered level;
+* a sweep over *how many* layers run at each level (evenly spread over depth);
+* a local refinement that moves the count up or down while the makespan improves.
+
+The search uses a reduced PressureFit portfolio; the winner is re-planned with the
+full one.  Role parity: reference ``src/dataflow_sim/planning/recompute.py:48-224``.
 """
 from __future__ import annotations
 
 import re
 from typing import Callable, Mapping
 
-from ..policies.pressurefit import PlanningError
+from ..policies.pressurefit import PREFETCH_RULES, RESIDENCY_SPECS, PlanningError
 
 
-def _layers_with_rewrites(program) -> list[int]:
-    out = set()
+def _layers_and_levels(program) -> tuple[list[int], list[int]]:
+    layers, levels = set(), set()
     for rw in program.recompute_rewrites:
         m = re.match(r"layer(\d+)", rw.group_key or "")
         if m:
-            out.add(int(m.group(1)))
-    return sorted(out)
+            layers.add(int(m.group(1)))
+        for o in rw.options:
+            if o.level:
+                levels.add(o.level)
+    return sorted(layers), sorted(levels)
 
 
-def _streamed_context_layers(planned) -> list[int]:
-    hit: dict[int, int] = {}
-    for t in planned.program.tasks:
-        for d in t.offload_after:
-            m = re.match(r"A_\d+_\d+_(\d+)$", d.object_id)
-            if m:
-                hit[int(m.group(1))] = hit.get(int(m.group(1)), 0) + 1
-    return [k for k, _ in sorted(hit.items(), key=lambda kv: -kv[1])]
+def spread(layers: list[int], k: int) -> list[int]:
+    """``k`` layers evenly spread over ``layers``."""
+    if k <= 0:
+        return []
+    if k >= len(layers):
+        return list(layers)
+    step = len(layers) / k
+    return sorted({layers[min(int(i * step + step / 2), len(layers) - 1)] for i in range(k)})
 
 
 def plan_with_recompute(program, fast_memory_capacity, build_variant: Callable[[Mapping[int, int]], object], *,
-                        backing_memory_capacity=None, leeway_bytes=None, max_evals: int = 8, level: int = 1):
+                        backing_memory_capacity=None, leeway_bytes=None, max_evals: int = 14):
     from ...lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES, plan_program
     leeway = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else leeway_bytes
-    layers = _layers_with_rewrites(program)
+    layers, levels = _layers_and_levels(program)
+    quick_specs = [s for s in RESIDENCY_SPECS if s.name in ("belady", "bytes_x_distance")]
+    quick_rules = [r for r in PREFETCH_RULES if r.name in ("jit_1.0", "jit_1.6", "window_2")]
     tried: dict[tuple, object] = {}
+    evals = 0
 
-    def price(levels: Mapping[int, int]):
-        key = tuple(sorted((k, v) for k, v in levels.items() if v))
-        if key in tried:
+    def price(assign: Mapping[int, int], full: bool = False):
+        nonlocal evals
+        key = tuple(sorted(((k, v) for k, v in assign.items() if v), key=lambda kv: (str(type(kv[0])), kv)))
+        if not full and key in tried:
             return tried[key]
         prog = program if not key else build_variant(dict(key))
         try:
             p = plan_program(prog, fast_memory_capacity, recompute=False,
-                             backing_memory_capacity=backing_memory_capacity, leeway_bytes=leeway)
+                             backing_memory_capacity=backing_memory_capacity, leeway_bytes=leeway,
+                             specs=None if full else quick_specs, rules=None if full else quick_rules)
             p.recompute_levels = dict(key)
         except PlanningError:
             p = None
-        tried[key] = p
+        if not full:
+            tried[key] = p
+            evals += 1
         return p
+
+    def better(a, b):
+        return a is not None and (b is None or a.makespan_us < b.makespan_us * (1 - 1e-5))
 
     best = price({})
     if best is not None and best.makespan_us <= best.lower_bound_us * (1 + 1e-6):
-        return best                                        # nothing to gain: the plan is compute-bound already
-    seeds = [{l: level for l in layers}, {l: level for l in layers[::2]}]
-    for s in seeds:
-        c = price(s)
-        if c is not None and (best is None or c.makespan_us < best.makespan_us):
+        return price({}, full=True) or best
+    L = len(layers)
+    for lv in levels:
+        c = price({l: lv for l in layers})
+        if better(c, best):
             best = c
+    # how many layers at each level
+    for lv in levels:
+        for k in (L // 4, L // 2, (3 * L) // 4):
+            if evals >= max_evals or k <= 0 or k >= L:
+                continue
+            c = price({l: lv for l in spread(layers, k)})
+            if better(c, best):
+                best = c
+    # recompute only in the last round: its backward is where optimizer state streams in, so
+    # freeing that round's activations buys room to prefetch the state ahead of the optimizer tasks
+    R = int((program.metadata or {}).get("grad_accum_rounds", 1))
+    if R > 1:
+        base = dict(best.recompute_levels) if best is not None else {}
+        for lv in levels:
+            for nlast in (L, L // 2):
+                if evals >= max_evals + 4:
+                    break
+                trial = dict(base)
+                trial.update({(R - 1, l): lv for l in spread(layers, nlast)})
+                c = price(trial)
+                if better(c, best):
+                    best = c
     if best is None:
         raise PlanningError("no recompute assignment fits the budget")
-    evals = len(tried)
-    improved = True
-    while improved and evals < max_evals:
-        improved = False
-        cur = dict(best.recompute_levels)
-        streamed = [l for l in _streamed_context_layers(best) if not cur.get(l)]
-        for l in streamed[:2]:
-            trial = dict(cur)
-            trial[l] = level
-            c = price(trial)
-            evals += 1
-            if c is not None and c.makespan_us < best.makespan_us * (1 - 1e-4):
-                best, improved = c, True
-                break
-            if evals >= max_evals:
-                break
-    return best
+    # local refinement of the winning count
+    cur = dict(best.recompute_levels)
+    if cur and len(set(cur.values())) == 1 and all(isinstance(k, int) for k in cur):
+        lv = next(iter(cur.values()))
+        k = len(cur)
+        step = max(L // 8, 1)
+        while evals < max_evals and step >= 1:
+            moved = False
+            for nk in (k - step, k + step):
+                if 0 < nk <= L and evals < max_evals:
+                    c = price({l: lv for l in spread(layers, nk)})
+                    if better(c, best):
+                        best, k, moved = c, nk, True
+                        break
+            if not moved:
+                step //= 2
+    final = price(dict(best.recompute_levels), full=True)
+    return final if better(final, best) or final is not None and final.makespan_us <= best.makespan_us else best
