@@ -1,15 +1,86 @@
-"""Reference arm of the benchmark: runs the unmodified reference (installed under
-``baseline/_ref``) through its own public API on the same metric and config.
-Prints ``{"impl": "reference", "unavailable": ...}`` when it cannot run here."""
+"""Reference arm of the benchmark: runs the UNMODIFIED reference (installed under
+``baseline/_ref``) through its own public API and stock code path — its preset
+(``resolve_preset``), its planner (``plan_at_budget``), its in-process daemon
+(``engine_client``), its kernels and its step loop (``run_engine``) — on the same
+metric and configuration as our arm, and prints the same JSON line with
+``"impl": "reference"``.
+
+What the reference can run of the configuration: its ``llama3_8b`` preset at seq 4096,
+131072 tokens per step, AdamW with its all-bf16 state policy (it has no fp32-master
+lane), one GPU per daemon.  It has no B200 hardware preset, so the plan is priced from
+its own measured task profiles (``measured=True``: its documented route for a new box).
+Multi-GPU (its ZeRO-1 ``zero1rs`` lane through the conductor / fleet loop) is not driven
+from here; for N > 1 the arm reports ``unavailable``.
+"""
 from __future__ import annotations
 
+import json
 import os
 import sys
+import time
+from dataclasses import replace
+
+
+def _unavailable(why: str) -> dict:
+    return {"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}
 
 
 def run_reference_arm(a) -> dict:
     rank = int(os.environ.get("RANK", 0))
-    ref = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref = os.path.join(here, "_ref")
     if not os.path.isdir(os.path.join(ref, "dataflow_training")):
-        return {"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"} if rank == 0 else {}
-    return {"impl": "reference", "unavailable": "reference arm not wired yet"} if rank == 0 else {}
+        return _unavailable("baseline/_ref is not installed on this machine") if rank == 0 else {}
+    if world > 1 or a.gpus > 1:
+        return _unavailable("the reference's multi-GPU lane (conductor + one daemon per GPU, ZeRO-1 over NCCL) is not "
+                            "driven by this harness; single-GPU only") if rank == 0 else {}
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from dataflow_training.run import presets as P
+        from dataflow_training.run.driver import engine_client, plan_at_budget, run_engine
+        from dataflow_training.run.recipe import Recipe
+        from dataflow_training.data.pipeline import pipeline_from_args
+    except Exception as e:       # noqa: BLE001
+        return _unavailable(f"reference import failed: {type(e).__name__}: {e}")
+    try:
+        base = P.resolve_preset(a.preset)
+        rounds = max(a.tokens_per_gpu // (a.seq_len * a.batch), 1)
+        cfg = replace(base, seq_len=a.seq_len, batch=a.batch, grad_accum_rounds=rounds)
+        budget = a.budget_gib if a.budget_gib is not None else 60.0
+        steps = a.warmup + a.steps
+        recipe = Recipe(peak_lr=3e-4, min_lr=3e-5, warmup_steps=max(1, steps // 3), total_steps=steps)
+        tokens_step = cfg.max_tokens * cfg.grad_accum_rounds
+        # synthetic uniform ids, full windows of seq_len (mean_len large and trimmed to the window)
+        spec = f"synthetic:mean_len={8 * a.seq_len},seed=0,long_policy=trim"
+        logs: list[str] = []
+
+        def factory(cursor=None):
+            return pipeline_from_args(cfg, spec)
+
+        t_plan = time.perf_counter()
+        planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=True, backing_gib=150.0)
+        plan_s = time.perf_counter() - t_plan
+        with engine_client(backing_gib=150.0, log=lambda *x, **k: None) as client:
+            res = run_engine(client, cfg, recipe, factory, steps, budget_gib=budget, seed=11, planned=planned,
+                             log=lambda *x, **k: logs.append(" ".join(map(str, x))))
+        tail = res.step_wall_s[a.warmup:] or res.step_wall_s
+        s_per_step = sum(tail) / len(tail)
+        value = tokens_step / s_per_step
+        return {
+            "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": len(tail),
+            "warmup": a.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / 12618.0, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"model": a.preset, "global_batch": tokens_step // a.seq_len, "seq_len": a.seq_len,
+                       "tokens_per_step": tokens_step, "parallelism": "solo", "fast_budget_gib": budget,
+                       "dtype_policy": "all-bf16 (the reference has no fp32-master lane)", "optimizer": "adamw",
+                       "timing": "reference's own per-step wall clock (its step loop blocks on the loss fetch)"},
+            "plan": {"predicted_ms_per_step": planned.makespan_us / 1e3, "plan_s": plan_s},
+            "loss": res.losses[-1] if res.losses else None,
+            "gpu_launches": None, "torch": torch.__version__,
+        }
+    except Exception as e:       # noqa: BLE001
+        import traceback
+        tb = traceback.format_exc().strip().splitlines()
+        return _unavailable(f"reference run failed: {type(e).__name__}: {e} | {tb[-3] if len(tb) > 2 else ''}")
