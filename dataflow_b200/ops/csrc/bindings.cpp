@@ -243,6 +243,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embed_bwd_sorted", &embed_bwd_sorted);
   m.def("gemm_bf16", &gemm_bf16);
   m.def("gemm_last_error", &gemm_last_error);
+  m.def("gemm_set_mt", [](int64_t mt) { dfb::gemm_bf16_set_mt((int)mt); });
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("zero_rs_adamw", &zero_rs_adamw);
   m.def("param_gather", &param_gather);

@@ -28,15 +28,25 @@ namespace dfb {
 
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;           // 16 KiB
+// MT = number of 128-row MMA sub-tiles a CTA stacks along M.  MT = 1: 128 x 256 tile, two TMEM
+// accumulators (the epilogue of one tile overlaps the main loop of the next).  MT = 2: 256 x 256
+// tile, both sub-tiles share every B stage (1.5x fewer shared-memory fill bytes per FLOP, which is
+// what bounds the kernel when operands stream from L2), one accumulator set.
+constexpr int SUB_M = 128, BN = 256, BK = 64, UK = 16;
+constexpr int MAX_STAGES = 4;
+constexpr int SUB_A_BYTES = SUB_M * BK * 2;    // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;           // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;       // one 64-wide MN-major chunk: 8 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+template <int MT> struct Cfg {
+  static constexpr int BM = SUB_M * MT;
+  static constexpr int A_BYTES = SUB_A_BYTES * MT;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = MT == 1 ? 4 : 3;
+  static constexpr int ACCS = MT == 1 ? 2 : 1;           // accumulator sets in tensor memory
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
 
 struct Params {
   int M, N, K;
@@ -50,8 +60,8 @@ struct Params {
 };
 
 struct SharedBarriers {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -68,9 +78,11 @@ DFB_DEVICE void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, i
   nb = r / gm;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+  constexpr int BM = Cfg<MT>::BM, A_BYTES = Cfg<MT>::A_BYTES, STAGE_BYTES = Cfg<MT>::STAGE_BYTES;
+  constexpr int STAGES = Cfg<MT>::STAGES, ACCS = Cfg<MT>::ACCS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SharedBarriers* sb = reinterpret_cast<SharedBarriers*>(smem + STAGES * STAGE_BYTES);
@@ -82,7 +94,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&sb->full[s], 1); ptx::mbar_init(&sb->empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(&sb->tmem_full[a], 1); ptx::mbar_init(&sb->tmem_empty[a], 4); }
+    for (int a = 0; a < ACCS; ++a) { ptx::mbar_init(&sb->tmem_full[a], 1); ptx::mbar_init(&sb->tmem_empty[a], 4); }
     sb->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmap_a);
@@ -116,7 +128,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int c = 0; c < BM / 64; ++c)
               ptx::tma_load_2d(sa + c * CHUNK_BYTES, &tmap_a, &sb->full[s], mb * BM + c * 64, kb * BK);
           } else {
-            ptx::tma_load_2d(sa, &tmap_a, &sb->full[s], kb * BK, mb * BM);
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+              ptx::tma_load_2d(sa + t * SUB_A_BYTES, &tmap_a, &sb->full[s], kb * BK, mb * BM + t * SUB_M);
           }
           if (B_MN) {
 #pragma unroll
@@ -131,11 +145,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(SUB_M, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-        int acc = tcount & 1;
-        uint32_t aph = (tcount >> 1) & 1;
+        int acc = ACCS == 2 ? (tcount & 1) : 0;
+        uint32_t aph = ACCS == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
         if (!ptx::mbar_wait(&sb->tmem_empty[acc], aph ^ 1, abort_flag)) { sb->abort = 1; atomicExch(p.err, 2); break; }
         ptx::tc_fence_after();
         uint32_t tmem_d = tmem_base + acc * BN;
@@ -151,9 +165,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint64_t bdesc = B_MN ? ptx::desc_mnmajor_sw128(b_addr, CHUNK_BYTES) : ptx::desc_kmajor_sw128(b_addr);
           constexpr uint64_t a_step = (A_MN ? UK * 128 : UK * 2) >> 4;   // bytes per K=16 step, in 16-byte units
           constexpr uint64_t b_step = (B_MN ? UK * 128 : UK * 2) >> 4;
+          // an MN-major A sub-tile is two 64-wide chunks further on; a K-major one is SUB_A_BYTES further on
+          constexpr uint64_t a_sub = (A_MN ? 2 * CHUNK_BYTES : SUB_A_BYTES) >> 4;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k)
-            ptx::umma_bf16(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+              ptx::umma_bf16(tmem_d + t * BN, adesc + t * a_sub + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
           ptx::umma_commit(&sb->empty[s]);          // stage reusable once these MMAs have read it
         }
         if (failed) break;
@@ -167,13 +185,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
-      int acc = tcount & 1;
-      uint32_t aph = (tcount >> 1) & 1;
+      int acc = ACCS == 2 ? (tcount & 1) : 0;
+      uint32_t aph = ACCS == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
       if (!ptx::mbar_wait(&sb->tmem_full[acc], aph, abort_flag)) { sb->abort = 1; atomicExch(p.err, 4); break; }
       ptx::tc_fence_after();
-      const int row = mb * BM + q * 32 + lane;
+#pragma unroll 1
+      for (int t = 0; t < MT; ++t) {
+      const int row = mb * BM + t * SUB_M + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t taddr = tmem_base + (acc + t) * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -236,6 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+      }
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -307,6 +328,9 @@ int gemm_bf16_last_error() {
 
 // a_mn / b_mn: operand is MN-major in memory (A stored as (K, M) row-major; B stored as (K, N) row-major).
 // Otherwise K-major (A stored (M, K), B stored (N, K)).  Returns 0 on success.
+static int g_gemm_mt_override = 0;      // 0: heuristic; 1 / 2: force the M stacking (benchmarks)
+void gemm_bf16_set_mt(int mt) { g_gemm_mt_override = mt; }
+
 int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,
               int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
               int num_sms, cudaStream_t stream) {
@@ -317,30 +341,48 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
   if ((ldd % (d_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
   if (addend && ((ld_add % (add_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(addend) & 15))) return -3;
   CUtensorMap ta, tb;
-  bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, BM);
+  bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, SUB_M);
   ok = ok && (b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN));
   if (!ok) return -4;
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.D = D; p.addend = addend; p.bias = bias;
   p.ldd = ldd; p.ld_add = ld_add; p.d_is_f32 = d_is_f32; p.add_is_f32 = add_is_f32;
-  p.group_m = 16;
   p.err = gemm_error_word();
-  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int grid = tiles < num_sms ? tiles : num_sms;
-  auto launch = [&](auto kernel) {
-    static thread_local bool configured[4] = {false, false, false, false};
-    int idx = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+  const long long n_blocks = (N + BN - 1) / BN;
+  const long long tiles2 = ((M + 255) / 256) * n_blocks;
+  // stack two M sub-tiles when that still leaves every SM at least two tiles of work
+  int mt = g_gemm_mt_override ? g_gemm_mt_override : ((tiles2 >= 2LL * num_sms && M >= 512) ? 2 : 1);
+  const int bm = SUB_M * mt;
+  p.group_m = mt == 2 ? 8 : 16;
+  long long tiles = ((M + bm - 1) / bm) * n_blocks;
+  int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
+  auto launch = [&](auto kernel, int smem, int idx) {
+    static bool configured[8] = {false, false, false, false, false, false, false, false};
     if (!configured[idx]) {
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       configured[idx] = true;
     }
-    kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    kernel<<<grid, THREADS, smem, stream>>>(ta, tb, p);
   };
-  if (a_mn && b_mn) launch(gemm_bf16_kernel<true, true>);
-  else if (a_mn) launch(gemm_bf16_kernel<true, false>);
-  else if (b_mn) launch(gemm_bf16_kernel<false, true>);
-  else launch(gemm_bf16_kernel<false, false>);
+  const int lay = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+  if (mt == 2) {
+    constexpr int smem = Cfg<2>::SMEM_BYTES;
+    switch (lay) {
+      case 3: launch(gemm_bf16_kernel<true, true, 2>, smem, 7); break;
+      case 2: launch(gemm_bf16_kernel<true, false, 2>, smem, 6); break;
+      case 1: launch(gemm_bf16_kernel<false, true, 2>, smem, 5); break;
+      default: launch(gemm_bf16_kernel<false, false, 2>, smem, 4); break;
+    }
+  } else {
+    constexpr int smem = Cfg<1>::SMEM_BYTES;
+    switch (lay) {
+      case 3: launch(gemm_bf16_kernel<true, true, 1>, smem, 3); break;
+      case 2: launch(gemm_bf16_kernel<true, false, 1>, smem, 2); break;
+      case 1: launch(gemm_bf16_kernel<false, true, 1>, smem, 1); break;
+      default: launch(gemm_bf16_kernel<false, false, 1>, smem, 0); break;
+    }
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

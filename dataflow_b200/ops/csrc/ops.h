@@ -56,6 +56,7 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
               int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
               int num_sms, cudaStream_t stream);
 int gemm_bf16_last_error();
+void gemm_bf16_set_mt(int mt);
 
 // ---- fused data-parallel communication (comm.cu)
 int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
