@@ -8,7 +8,8 @@ metric and configuration as our arm, and prints the same JSON line with
 What the reference can run of the configuration: its ``llama3_8b`` preset at seq 4096,
 131072 tokens per step, AdamW with its all-bf16 state policy (it has no fp32-master
 lane), one GPU per daemon.  It has no B200 hardware preset, so the plan is priced from
-its own measured task profiles (``measured=True``: its documented route for a new box).
+its H100 roofline preset passed explicitly (``hw=hardware_preset("h100")``, the route its own
+error message names); its measured-cost path raises on an unknown device.
 Multi-GPU (its ZeRO-1 ``zero1rs`` lane through the conductor / fleet loop) is not driven
 from here; for N > 1 the arm reports ``unavailable``.
 """
@@ -60,7 +61,12 @@ def run_reference_arm(a) -> dict:
             return pipeline_from_args(cfg, spec)
 
         t_plan = time.perf_counter()
-        planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=True, backing_gib=150.0)
+        # no B200 row in its HW_PRESETS: both its measured-cost path and its default roofline path call
+        # resolve_hardware(), which raises on this device; the route its own error message names is an
+        # explicit preset, so the plan is priced with its H100 roofline and executed on the B200
+        from dataflow_training.lowering.shaped_program import hardware_preset
+        planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=False, hw=hardware_preset("h100"),
+                                 backing_gib=150.0)
         plan_s = time.perf_counter() - t_plan
         with engine_client(backing_gib=150.0, log=lambda *x, **k: None) as client:
             res = run_engine(client, cfg, recipe, factory, steps, budget_gib=budget, seed=11, planned=planned,

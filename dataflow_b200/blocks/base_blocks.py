@@ -44,8 +44,9 @@ class _Base:
         dev = self.device if buf.location == "fast" else None
         return layout.views(buf, dev, rows)
 
-    def tview(self, buf, shape, dtype="bf16"):
+    def tview(self, buf, shape, dtype=None):
         from ..runtime.interop import torch_view
+        dtype = dtype or getattr(self.dims, "act", "bf16")       # activations follow the family's activation dtype
         return torch_view(buf, shape, dtype, 0, self.device if buf.location == "fast" else None)
 
     def by_id(self, ctx, prefix: str):
@@ -120,8 +121,14 @@ class HeadLoss(_Base):
         tied = "w_head" not in w
         if tied:
             w_head_t = self.views(self.by_id(ctx, "W_embed"), self.lay.embed_w)["wte"]      # (vocab, d)
-            dwe = self.views(self.by_id(ctx, "dW_embed"), self.lay.embed_dw)["wte"]
+            dwe_all = self.views(self.by_id(ctx, "dW_embed"), self.lay.embed_dw)
+            dwe = dwe_all["wte"]
             create_e = self.creating(ctx, "dW_embed")
+            if create_e:
+                # this task creates the shared gradient object: fields it does not write start at zero
+                for name, t in dwe_all.items():
+                    if name != "wte":
+                        t.zero_()
         total_rows = float(ctx.run_args.get("valid_rows", n))
         dev = y.device
         loss_dev = torch.zeros(1, dtype=torch.float32, device=dev)
