@@ -320,6 +320,12 @@ static int* gemm_error_word() {
   return word;
 }
 
+int* gemm_error_word_shared() { return gemm_error_word(); }
+
+int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,
+                  int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
+                  int num_sms, cudaStream_t stream);
+
 int gemm_bf16_last_error() {
   int v = 0;
   cudaMemcpy(&v, gemm_error_word(), sizeof(int), cudaMemcpyDeviceToHost);
@@ -328,8 +334,11 @@ int gemm_bf16_last_error() {
 
 // a_mn / b_mn: operand is MN-major in memory (A stored as (K, M) row-major; B stored as (K, N) row-major).
 // Otherwise K-major (A stored (M, K), B stored (N, K)).  Returns 0 on success.
-static int g_gemm_mt_override = 0;      // 0: heuristic; 1 / 2: force the M stacking (benchmarks)
+// 0: default path; 1 / 2: single-CTA kernel with that M stacking; 3: CTA-pair kernel (falls back when too few tiles)
+static int g_gemm_mt_override = 0;
+static int g_gemm_default_path = 1;
 void gemm_bf16_set_mt(int mt) { g_gemm_mt_override = mt; }
+void gemm_bf16_set_default_path(int path) { g_gemm_default_path = path; }
 
 int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,
               int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
@@ -340,6 +349,11 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -2;
   if ((ldd % (d_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
   if (addend && ((ld_add % (add_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(addend) & 15))) return -3;
+  const int path = g_gemm_mt_override ? g_gemm_mt_override : g_gemm_default_path;
+  if (path == 3) {
+    int rc = gemm_bf16_2sm(A, lda, a_mn, B, ldb, b_mn, D, ldd, d_is_f32, addend, ld_add, add_is_f32, bias, M, N, K, num_sms, stream);
+    if (rc != -6) return rc;            // -6: too few pair tiles, use the single-CTA kernel below
+  }
   CUtensorMap ta, tb;
   bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, SUB_M);
   ok = ok && (b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, BN));
@@ -352,7 +366,9 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
   const long long n_blocks = (N + BN - 1) / BN;
   const long long tiles2 = ((M + 255) / 256) * n_blocks;
   // stack two M sub-tiles when that still leaves every SM at least two tiles of work
-  int mt = g_gemm_mt_override ? g_gemm_mt_override : ((tiles2 >= 2LL * num_sms && M >= 512) ? 2 : 1);
+  // measured on B200: the stacked variant loses more to its un-overlapped epilogue than it gains, so it is opt-in
+  (void)tiles2;
+  int mt = path == 2 ? 2 : 1;
   const int bm = SUB_M * mt;
   p.group_m = mt == 2 ? 8 : 16;
   long long tiles = ((M + bm - 1) / bm) * n_blocks;

@@ -1,0 +1,336 @@
+// bf16 GEMM on CTA pairs: D = A * B (+ addend) (+ bias), 256 x 256 output tile per pair of SMs.
+//
+// With one CTA per tile the 128 x 256 x 16 MMA reads 12 KiB of shared memory every 128 cycles while
+// TMA fills the same shared memory at the same rate: the shared-memory port saturates near two
+// thirds of tensor peak (measured: tensor pipe 61 % active, l1tex 78 %).  Pairing two SMs on one
+// 256-row MMA (tcgen05 cta_group::2) halves both streams per SM: each CTA stages only its own 128
+// rows of A and HALF of the tile's B rows, and the pair shares B through the MMA itself.
+//
+// Cluster of two CTAs along M, persistent over tiles.  Per CTA:
+//   warp 0      TMA producer: own A rows + own half of B into a 6-stage ring; transaction bytes of
+//               BOTH CTAs are counted on the leader's "full" barrier
+//   warp 1      leader only: issues tcgen05.mma.cta_group::2; tcgen05.commit arrives on the
+//               "empty" barrier of both CTAs and publishes finished accumulators to both
+//   warps 2-5   epilogue for the CTA's own 128 accumulator lanes (two 256-column accumulators in
+//               tensor memory, so the epilogue overlaps the next tile's main loop)
+// No TMA load carries a cluster-broadcast qualifier.  Every wait is bounded.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ops.h"
+#include "ptx.cuh"
+
+namespace dfb {
+namespace gemm2 {
+
+constexpr int BM = 256, HALF_M = 128, BN = 256, HALF_N = 128, BK = 64, UK = 16;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = HALF_M * BK * 2;       // 16 KiB: this CTA's rows of A
+constexpr int B_BYTES = HALF_N * BK * 2;       // 16 KiB: this CTA's half of B
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;
+constexpr int TMEM_COLS = 512;
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Params {
+  int M, N, K;
+  void* D;
+  const void* addend;
+  const void* bias;
+  long long ldd, ld_add;
+  int d_is_f32, add_is_f32;
+  int group_m;
+  int* err;
+};
+
+struct SharedBarriers {
+  uint64_t full[STAGES];        // used in the leader: both CTAs' TMA bytes land here
+  uint64_t empty[STAGES];       // per CTA: stage reusable
+  uint64_t tmem_full[2];        // per CTA: accumulator ready
+  uint64_t tmem_empty[2];       // used in the leader: both CTAs' epilogues drained the accumulator
+  uint32_t tmem_base;
+  int abort;
+};
+
+DFB_DEVICE void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, int& mb, int& nb) {
+  int per_group = group_m * n_blocks;
+  int g = tile / per_group;
+  int first = g * group_m;
+  int gm = min(m_blocks - first, group_m);
+  int r = tile - g * per_group;
+  mb = first + r % gm;
+  nb = r / gm;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedBarriers* sb = reinterpret_cast<SharedBarriers*>(smem + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = ptx::cluster_ctarank();            // 0 = leader
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  volatile int* abort_flag = &sb->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&sb->full[s], 1); ptx::mbar_init(&sb->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(&sb->tmem_full[a], 1); ptx::mbar_init(&sb->tmem_empty[a], 8); }
+    sb->abort = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(&sb->tmem_base, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();                 // both CTAs' barriers exist before anything remote touches them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = sb->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (ptx::elect_one()) {
+      uint32_t it = 0;
+      for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
+        const int m0 = mb * BM + static_cast<int>(cta) * HALF_M;
+        const int n0 = nb * BN + static_cast<int>(cta) * HALF_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait(&sb->empty[s], ph ^ 1, abort_flag)) { sb->abort = 1; atomicExch(p.err, 11); break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sbm = sa + A_BYTES;
+          if (cta == 0) ptx::mbar_expect_tx(&sb->full[s], 2 * STAGE_BYTES);     // bytes of both CTAs
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < HALF_M / 64; ++c)
+              ptx::tma_load_2d_pair(sa + c * CHUNK_BYTES, &tmap_a, &sb->full[s], m0 + c * 64, kb * BK);
+          } else {
+            ptx::tma_load_2d_pair(sa, &tmap_a, &sb->full[s], kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < HALF_N / 64; ++c)
+              ptx::tma_load_2d_pair(sbm + c * CHUNK_BYTES, &tmap_b, &sb->full[s], n0 + c * 64, kb * BK);
+          } else {
+            ptx::tma_load_2d_pair(sbm, &tmap_b, &sb->full[s], kb * BK, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (cta == 0 && ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tcount = 0;
+      for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters, ++tcount) {
+        int acc = tcount & 1;
+        uint32_t aph = (tcount >> 1) & 1;
+        if (!ptx::mbar_wait(&sb->tmem_empty[acc], aph ^ 1, abort_flag)) { sb->abort = 1; atomicExch(p.err, 12); break; }
+        ptx::tc_fence_after();
+        uint32_t tmem_d = tmem_base + acc * BN;
+        bool failed = false;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait(&sb->full[s], ph, abort_flag)) { sb->abort = 1; atomicExch(p.err, 13); failed = true; break; }
+          ptx::tc_fence_after();
+          uint32_t a_addr = ptx::smem_u32(smem + s * STAGE_BYTES);
+          uint32_t b_addr = a_addr + A_BYTES;
+          uint64_t adesc = A_MN ? ptx::desc_mnmajor_sw128(a_addr, CHUNK_BYTES) : ptx::desc_kmajor_sw128(a_addr);
+          uint64_t bdesc = B_MN ? ptx::desc_mnmajor_sw128(b_addr, CHUNK_BYTES) : ptx::desc_kmajor_sw128(b_addr);
+          constexpr uint64_t a_step = (A_MN ? UK * 128 : UK * 2) >> 4;
+          constexpr uint64_t b_step = (B_MN ? UK * 128 : UK * 2) >> 4;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k)
+            ptx::umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
+          ptx::umma_commit_pair(&sb->empty[s], 0x3);        // both CTAs may refill this stage
+        }
+        if (failed) break;
+        ptx::umma_commit_pair(&sb->tmem_full[acc], 0x3);    // both CTAs' epilogues may drain
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs, own lanes)
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters, ++tcount) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
+      int acc = tcount & 1;
+      uint32_t aph = (tcount >> 1) & 1;
+      if (!ptx::mbar_wait(&sb->tmem_full[acc], aph, abort_flag)) { sb->abort = 1; atomicExch(p.err, 14); break; }
+      ptx::tc_fence_after();
+      const int row = mb * BM + static_cast<int>(cta) * HALF_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col0 = nb * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+          const int ncol = min(32, p.N - col0);
+          if (p.bias) {
+            const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + col0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < ncol) f[i] += bf2f(bp[i]);
+          }
+          if (p.addend) {
+            if (p.add_is_f32) {
+              const float* ap = reinterpret_cast<const float*>(p.addend) + static_cast<long long>(row) * p.ld_add + col0;
+              if (ncol == 32) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                  float4 t = *reinterpret_cast<const float4*>(ap + v * 4);
+                  f[v * 4] += t.x; f[v * 4 + 1] += t.y; f[v * 4 + 2] += t.z; f[v * 4 + 3] += t.w;
+                }
+              } else {
+                for (int i = 0; i < ncol; ++i) f[i] += ap[i];
+              }
+            } else {
+              const bf16* ap = reinterpret_cast<const bf16*>(p.addend) + static_cast<long long>(row) * p.ld_add + col0;
+              if (ncol == 32) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  float t[8];
+                  unpack8(ld8(ap + v * 8), t);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) f[v * 8 + i] += t[i];
+                }
+              } else {
+                for (int i = 0; i < ncol; ++i) f[i] += bf2f(ap[i]);
+              }
+            }
+          }
+          if (p.d_is_f32) {
+            float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            if (ncol == 32) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<float4*>(dp + v * 4) = make_float4(f[v * 4], f[v * 4 + 1], f[v * 4 + 2], f[v * 4 + 3]);
+            } else {
+              for (int i = 0; i < ncol; ++i) dp[i] = f[i];
+            }
+          } else {
+            bf16* dp = reinterpret_cast<bf16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+            if (ncol == 32) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) st8(dp + v * 8, pack8(f + v * 8));
+            } else {
+              for (int i = 0; i < ncol; ++i) dp[i] = f2bf(f[i]);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(&sb->tmem_empty[acc], 0);     // the leader owns the accumulator handshake
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);      // let copies still in flight land
+  }
+  ptx::cluster_sync();                 // neither CTA leaves while its partner may still touch its memory
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+static bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                     uint32_t box_outer) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace gemm2
+
+int* gemm_error_word_shared();
+
+// Same contract as gemm_bf16 (gemm_tcgen05.cu); returns -6 when the shape is better served by the
+// single-CTA kernel (too few 256 x 256 tiles), so the caller can fall back.
+int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,
+                  int d_is_f32, const void* addend, long long ld_add, int add_is_f32, const void* bias, int M, int N, int K,
+                  int num_sms, cudaStream_t stream) {
+  using namespace gemm2;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -5;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -2;
+  if ((ldd % (d_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
+  if (addend && ((ld_add % (add_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(addend) & 15))) return -3;
+  long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int clusters = num_sms / 2;
+  if (tiles < clusters) return -6;
+  CUtensorMap ta, tb;
+  bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, HALF_M);
+  ok = ok && (b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, HALF_N));
+  if (!ok) return -4;
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.D = D; p.addend = addend; p.bias = bias;
+  p.ldd = ldd; p.ld_add = ld_add; p.d_is_f32 = d_is_f32; p.add_is_f32 = add_is_f32;
+  p.group_m = 8;
+  p.err = gemm_error_word_shared();
+  int grid = 2 * static_cast<int>(tiles < clusters ? tiles : clusters);
+  auto launch = [&](auto kernel, int idx) {
+    static bool configured[4] = {false, false, false, false};
+    if (!configured[idx]) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      configured[idx] = true;
+    }
+    kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  };
+  const int lay = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+  switch (lay) {
+    case 3: launch(gemm2_bf16_kernel<true, true>, 3); break;
+    case 2: launch(gemm2_bf16_kernel<true, false>, 2); break;
+    case 1: launch(gemm2_bf16_kernel<false, true>, 1); break;
+    default: launch(gemm2_bf16_kernel<false, false>, 0); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace dfb

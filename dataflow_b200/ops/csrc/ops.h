@@ -57,6 +57,7 @@ int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long l
               int num_sms, cudaStream_t stream);
 int gemm_bf16_last_error();
 void gemm_bf16_set_mt(int mt);
+void gemm_bf16_set_default_path(int path);
 
 // ---- fused data-parallel communication (comm.cu)
 int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,

@@ -156,3 +156,59 @@ DFB_PTX void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: 
 
 }  // namespace ptx
 }  // namespace dfb
+
+// ---------------------------------------------------------------------------- CTA-pair (cta_group::2) forms
+// Two CTAs of one cluster drive ONE 256-row MMA: each CTA holds its own 128 rows of A and half of
+// B's N rows in shared memory and its own 128 lanes of the accumulator in tensor memory; the leader
+// CTA (cluster rank 0) issues the instruction for both.
+namespace dfb {
+namespace ptx {
+
+DFB_PTX uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+DFB_PTX void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+DFB_PTX void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+}
+DFB_PTX void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+DFB_PTX void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// TMA tile load issued by either CTA of the pair; the transaction bytes are counted on the
+// barrier at the same shared-memory offset in the LEADER CTA (peer bit of the address cleared).
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+DFB_PTX void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      : : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+DFB_PTX void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      : : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in every CTA named by ``cta_mask`` once the
+// MMAs issued so far have completed.
+DFB_PTX void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+// Arrive on the barrier at this offset in CTA ``rank`` of the cluster.
+DFB_PTX void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      : : "r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+
+}  // namespace ptx
+}  // namespace dfb
