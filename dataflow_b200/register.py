@@ -1,0 +1,58 @@
+"""Registers the workload with the service: resolver kind ``"model_family"`` (spec =
+``{"kind", "family", "cfg", "hyper"}``) and the HOST init task (``family_init``) that fills a
+training program's persistent objects with the family's seeded initial values directly in the
+store's extents (init-as-program).  Role parity: reference ``src/dataflow_training/register.py:40-122``."""
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+
+def canonical_spec(family: str, cfg, hyper: Mapping[str, Any] | None = None, seed: int | None = None) -> dict:
+    from .run.presets import cfg_dict
+    spec = {"kind": "model_family", "family": family, "cfg": cfg_dict(cfg), "hyper": dict(hyper or {})}
+    if seed is not None:
+        spec["seed"] = int(seed)
+    return spec
+
+
+class FamilyInitExecutable:
+    def __init__(self, fam, cfg, seed: int):
+        self.fam, self.cfg, self.seed = fam, cfg, seed
+
+    def launch(self, ctx) -> None:
+        bufs = {b.object_id: b for b in ctx.inputs}
+        program = self.fam.lower(self.cfg)
+
+        def views_of(oid, layout):
+            return layout.views(bufs[oid], None)
+        import dataclasses
+        keep = tuple(o for o in program.initial_objects if o.id in bufs)
+        self.fam.initial_values(dataclasses.replace(program, initial_objects=keep), self.cfg, views_of, self.seed)
+
+
+def build_model_family_resolver(spec: Mapping[str, Any], env):
+    from .models.families import resolve_family
+    from .ops import resolve_kernels
+    from .run.presets import cfg_from_dict
+    fam = resolve_family(spec["family"])
+    cfg = cfg_from_dict(fam, spec["cfg"])
+    device = getattr(env, "device", None)
+    kernel_set = getattr(env, "kernel_set", None)
+    K = resolve_kernels(kernel_set=("eager" if device is None and kernel_set is None else kernel_set))
+    hyper = dict(spec.get("hyper") or {})
+    hyper.setdefault("optimizer", getattr(cfg, "optimizer", "adamw"))
+    if hasattr(cfg, "policy"):
+        hyper.setdefault("dtype_policy", cfg.policy().to_dict())
+    inner = fam.build_resolver(fam.derive_dims(cfg), hyper, K, device)
+    init = FamilyInitExecutable(fam, cfg, int(spec.get("seed", 0)))
+
+    def resolver(task):
+        if task.compute_block_key == "family_init":
+            return init
+        return inner(task)
+    return resolver
+
+
+def register_all() -> None:
+    from .service.registry import register_program_resolver
+    register_program_resolver("model_family", build_model_family_resolver)
