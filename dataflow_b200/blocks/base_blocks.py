@@ -201,7 +201,10 @@ class OptimizerStep(_Base):
                 continue            # frozen field: no gradient storage, no update
             wf, gf = w[f.name], g[f.name]
             f_wd = wd if (f.kind in ("matrix", "embedding") or hy.get("wd_all")) else 0.0
-            if rule == "adamw":
+            if rule == "adamw" and f"{f.name}.mlo" in o:
+                self.K.adamw_split_step(wf.reshape(-1), o[f"{f.name}.mlo"].reshape(-1), gf.reshape(-1),
+                                        o[f"{f.name}.s0"].reshape(-1), o[f"{f.name}.s1"].reshape(-1), lr, b1, b2, eps, f_wd, step)
+            elif rule == "adamw":
                 self.K.adamw_step(wf.reshape(-1), gf.reshape(-1), o[f"{f.name}.s0"].reshape(-1),
                                   o[f"{f.name}.s1"].reshape(-1), lr, b1, b2, eps, f_wd, step,
                                   master=o[f"{f.name}.master"].reshape(-1) if f"{f.name}.master" in o else None)

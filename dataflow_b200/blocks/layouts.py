@@ -131,6 +131,9 @@ class DTypePolicy:
             return DTypePolicy(ParamDTypes("bf16", "bf16", "fp32", "fp32"))
         if name in ("bf16_master_bf16opt",):
             return DTypePolicy(ParamDTypes("bf16", "bf16", "bf16", "fp32"))
+        if name in ("bf16_split_master", "split_master"):
+            # exact fp32 master whose high half IS the bf16 weight; only the low 16 bits are optimizer state
+            return DTypePolicy(ParamDTypes("bf16", "bf16", "bf16", "lo16"))
         if name == "fp32":
             return DTypePolicy(ParamDTypes("fp32", "fp32", "fp32", None))
         if name in ("fp8", "fp8_block"):
@@ -168,14 +171,17 @@ def grad_layout(fields: Sequence[Field], policy: DTypePolicy, layer=None, frozen
 
 def opt_state_layout(fields: Sequence[Field], policy: DTypePolicy, layer=None,
                      rule_of=lambda f: "adamw") -> PackedLayout:
-    """Per field: [``<f>.master`` fp32] then ``<f>.s0`` … one per optimizer slot."""
+    """Per field: [``<f>.master`` fp32 | ``<f>.mlo`` int16 low half of a split master] then ``<f>.s0`` … one per
+    optimizer slot."""
     out: list[Field] = []
     for f in fields:
         dt = policy.for_field(f.name, layer)
         rule = rule_of(f)
         if rule == "frozen":
             continue
-        if dt.master:
+        if dt.master == "lo16":
+            out.append(Field(f"{f.name}.mlo", f.shape, "int16", f.kind, "zeros"))
+        elif dt.master:
             out.append(Field(f"{f.name}.master", f.shape, dt.master, f.kind, "copy"))
         for s in range(OPT_SLOTS[rule]):
             out.append(Field(f"{f.name}.s{s}", f.shape, dt.opt, f.kind, "zeros"))

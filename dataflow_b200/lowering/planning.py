@@ -3,8 +3,9 @@
 ``budget = planned object pool + largest task workspace + leeway``: the planner is
 given ``budget - leeway - max(workspace)`` for declared objects, so the executor's
 slab (objects) plus the framework allocator's scratch (workspace) stay under the
-budget on the device.  PressureFit (optionally wrapped by the recompute planner)
-produces the directives; the result is re-simulated and returned with its
+budget on the device.  The directives come from the best of two planners, both verified
+by the simulator: Lookahead (decides inside a simulation run) and PressureFit (offline
+residency sweep), optionally wrapped by the recompute planner; the result is returned with its
 predicted makespan, peaks and transfer statistics.  Role parity: reference
 ``src/dataflow_training/lowering/planning.py:22-356``.
 """
@@ -70,9 +71,13 @@ def _dedup_initial(program: Program):
 def plan_program(program: Program, fast_memory_capacity: int | None, *, recompute: bool = False,
                  build_variant: Callable[[Mapping[int, int]], Program] | None = None,
                  backing_memory_capacity: int | None = None,
-                 leeway_bytes: int = DEFAULT_PROGRAM_LEEWAY_BYTES, policy: str = "pressurefit",
-                 specs=None, rules=None) -> PlannedProgram:
-    """``fast_memory_capacity`` is the whole device budget in bytes (``None`` = unbounded)."""
+                 leeway_bytes: int = DEFAULT_PROGRAM_LEEWAY_BYTES, policy: str = "auto",
+                 specs=None, rules=None, lookahead_specs=None, quick: bool = False) -> PlannedProgram:
+    """``fast_memory_capacity`` is the whole device budget in bytes (``None`` = unbounded).
+
+    ``policy``: ``"auto"`` (best of Lookahead and PressureFit), ``"lookahead"``, ``"pressurefit"`` or any name
+    of ``sim.policies.get_all_policies()``.  ``quick`` keeps ``auto`` to a few Lookahead candidates (used by
+    searches that price many program variants)."""
     levels: dict[int, int] = {}
     if recompute and build_variant is not None and program.recompute_rewrites:
         from ..sim.planning.recompute import plan_with_recompute
@@ -87,9 +92,33 @@ def plan_program(program: Program, fast_memory_capacity: int | None, *, recomput
     chain = to_sim_chain(program, with_directives=False)
     chain = replace(chain, tasks=[replace(t, workspace_bytes=0) for t in chain.tasks],
                     backing_memory_capacity=backing_memory_capacity)
-    if policy == "pressurefit":
-        res = pressurefit(chain, cap, specs=specs, rules=rules)
-        planned_chain, ncand = res.chain, len(res.candidates)
+    if policy in ("auto", "lookahead", "pressurefit"):
+        from ..sim.policies.lookahead import LOOKAHEAD_SPECS, lookahead
+        best_chain, best_ms, ncand, errors = None, float("inf"), 0, []
+        if policy != "pressurefit":
+            la = lookahead_specs
+            if la is None and quick:
+                la = [x for x in LOOKAHEAD_SPECS if x.name in ("cost_aware", "cost_aware_wide", "bytes")]
+            try:
+                r = lookahead(chain, cap, specs=la, headrooms=(0.02,) if quick else (0.02, 0.05))
+                best_chain, best_ms, ncand = r.chain, r.makespan, len(r.candidates)
+                policy_used = f"lookahead:{r.chosen.spec}"
+            except PlanningError as e:
+                errors.append(str(e))
+        lower = float(sum(t.runtime for t in chain.tasks))
+        if policy == "pressurefit" or (policy == "auto" and not quick and best_ms > lower * (1 + 1e-9)) \
+                or best_chain is None and policy == "auto":
+            try:
+                res = pressurefit(chain, cap, specs=specs, rules=rules)
+                ncand += len(res.candidates)
+                if res.makespan < best_ms:
+                    best_chain, best_ms = res.chain, res.makespan
+                    policy_used = f"pressurefit:{res.chosen.spec}/{res.chosen.rule}"
+            except PlanningError as e:
+                errors.append(str(e))
+        if best_chain is None:
+            raise PlanningError("; ".join(errors))
+        planned_chain, policy = best_chain, policy_used
     else:
         from ..sim.policies import get_all_policies
         planned_chain, ncand = get_all_policies()[policy](chain, cap), 1

@@ -152,10 +152,13 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                          comm_groups: Mapping[str, str] | None = None,
                          metadata: Mapping[str, Any] | None = None,
                          opt_embed_us: float | None = None, opt_head_us: float | None = None,
-                         zero: Mapping[str, Any] | None = None) -> Program:
+                         zero: Mapping[str, Any] | None = None,
+                         resident_params: bool = False) -> Program:
     """Emit the bare program.  ``recompute_levels[i] > 0`` (all rounds) or
     ``recompute_levels[(round, i)] > 0`` (one round) makes layer ``i`` save a reduced context and
-    inserts a ``{kind}_recompute`` task in front of its backward."""
+    inserts a ``{kind}_recompute`` task in front of its backward.  ``resident_params`` starts and ends every
+    whole weight object on the fast tier: a session that keeps final-fast objects between runs then carries
+    the parameters from step to step with no transfer (the planner may still evict them inside a step)."""
     L = cfg.n_layers
     assert len(layer_kinds) == L
     levels = dict(recompute_levels or {})
@@ -191,12 +194,15 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
             init.append(ObjectSpec(f"Ws_{name}", zslice(w_bytes), "backing", "parameter", persistent=True))
             gathered[wid] = w_bytes
         else:
-            init.append(ObjectSpec(wid, w_bytes, "backing", "parameter", persistent=True))
+            init.append(ObjectSpec(wid, w_bytes, "fast" if resident_params else "backing", "parameter", persistent=True))
+            if resident_params:
+                resident_ids.add(wid)
         ob = zo(w_bytes, o_bytes)
         if ob:
             init.append(ObjectSpec(oid, ob, "backing", "optimizer_state", persistent=True))
 
     init: list[ObjectSpec] = []
+    resident_ids: set[str] = set()
     param_objects("embed", embed_w_bytes, embed_o_bytes)
     for i in range(L):
         k = kinds[layer_kinds[i]]
@@ -212,7 +218,7 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
 
     tasks: list[TaskSpec] = []
     rewrites: list[RecomputeRewrite] = []
-    finals: dict[str, str] = {o.id: "backing" for o in init if o.persistent}
+    finals: dict[str, str] = {o.id: ("fast" if o.id in resident_ids else "backing") for o in init if o.persistent}
     R = cfg.grad_accum_rounds
     last = R - 1
     opt_tasks_tail: list[TaskSpec] = []

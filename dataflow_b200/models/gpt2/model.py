@@ -144,7 +144,8 @@ def flops_per_token(cfg: ShapedGpt2Config) -> float:
 
 def lower_gpt2(cfg: ShapedGpt2Config, recompute_levels: Mapping | None = None, hw: ShapedHardware | None = None,
                block_params: Mapping[str, Any] | None = None, comm_groups: Mapping[str, str] | None = None,
-               zero: Mapping[str, Any] | None = None) -> Program:
+               zero: Mapping[str, Any] | None = None,
+                 resident_params: bool = False) -> Program:
     hw = hw or resolve_hardware("b200")
     d = derive_dims(cfg)
     lay = family_layouts(d, cfg.policy(), cfg.optimizer)
@@ -173,7 +174,7 @@ def lower_gpt2(cfg: ShapedGpt2Config, recompute_levels: Mapping | None = None, h
         sc, {"block": kind}, ["block"] * d.n_layers,
         embed_w_bytes=lay.embed_w.size_bytes, embed_dw_bytes=lay.embed_dw.size_bytes, embed_o_bytes=lay.embed_o.size_bytes,
         head_w_bytes=lay.head_w.size_bytes, head_dw_bytes=lay.head_dw.size_bytes, head_o_bytes=lay.head_o.size_bytes,
-        loose=loose, hw=hw, recompute_levels=recompute_levels, block_params=block_params, comm_groups=comm_groups, zero=zero,
+        loose=loose, hw=hw, recompute_levels=recompute_levels, block_params=block_params, comm_groups=comm_groups, zero=zero, resident_params=resident_params,
         metadata={"family": "gpt2", "preset": cfg.name, "flops_per_token": flops_per_token(cfg), "seq_len": cfg.seq_len,
                   "batch": cfg.batch})
 

@@ -110,6 +110,16 @@ static void adamw_master(Tensor& master, Tensor& w_out, const Tensor& g, Tensor&
                     m.data_ptr<float>(), v.data_ptr<float>(), master.numel(), lr, b1, b2, eps, wd, (int)step, gscale,
                     cur_stream());
 }
+static void adamw_split(Tensor& w, Tensor& lo, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2,
+                        double eps, double wd, int64_t step, double gscale) {
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16 && m.scalar_type() == at::kBFloat16 &&
+              v.scalar_type() == at::kBFloat16 && lo.element_size() == 2, "adamw_split: bf16 w/g/m/v and a 16-bit lo plane");
+  TORCH_CHECK(lo.numel() == w.numel() && g.numel() == w.numel() && m.numel() == w.numel() && v.numel() == w.numel(),
+              "adamw_split: size mismatch");
+  int rc = dfb::adamw_split(w.data_ptr(), lo.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), w.numel(), lr, b1, b2, eps,
+                            wd, (int)step, gscale, cur_stream());
+  TORCH_CHECK(rc == 0, "adamw_split: arrays must be 16-byte aligned (code ", rc, ")");
+}
 static void adamw_f32(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
                       double wd, int64_t step, double gscale) {
   CHECK_F32(w); CHECK_F32(g); CHECK_F32(m); CHECK_F32(v);
@@ -237,6 +247,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_bf16", &adamw_bf16);
   m.def("adamw_master", &adamw_master);
   m.def("adamw_f32", &adamw_f32);
+  m.def("adamw_split", &adamw_split);
   m.def("sgd_bf16", &sgd_bf16);
   m.def("ce_loss_fwd_bwd", &ce_loss_fwd_bwd);
   m.def("embed_fwd", &embed_fwd);

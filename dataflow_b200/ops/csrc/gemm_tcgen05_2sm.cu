@@ -16,6 +16,7 @@
 // No TMA load carries a cluster-broadcast qualifier.  Every wait is bounded.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -43,6 +44,7 @@ struct Params {
   long long ldd, ld_add;
   int d_is_f32, add_is_f32;
   int group_m;
+  int dbg;
   int* err;
 };
 
@@ -179,10 +181,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, r);
-        ptx::tmem_ld_wait();
+        if (!(p.dbg & 2)) {
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+        }
         const int col0 = nb * BN + c * 32;
-        if (row_ok && col0 < p.N) {
+        if (p.dbg & 2) continue;
+        if (row_ok && col0 < p.N && !(p.dbg & 1)) {
           float f[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
@@ -312,7 +317,10 @@ int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long lo
   p.M = M; p.N = N; p.K = K;
   p.D = D; p.addend = addend; p.bias = bias;
   p.ldd = ldd; p.ld_add = ld_add; p.d_is_f32 = d_is_f32; p.add_is_f32 = add_is_f32;
-  p.group_m = 8;
+  static int env_gm = getenv("DFB_GEMM2_GROUPM") ? atoi(getenv("DFB_GEMM2_GROUPM")) : 8;
+  static int env_dbg = getenv("DFB_GEMM2_DBG") ? atoi(getenv("DFB_GEMM2_DBG")) : 0;
+  p.group_m = env_gm;
+  p.dbg = env_dbg;
   p.err = gemm_error_word_shared();
   int grid = 2 * static_cast<int>(tiles < clusters ? tiles : clusters);
   auto launch = [&](auto kernel, int idx) {

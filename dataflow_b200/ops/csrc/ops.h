@@ -35,6 +35,8 @@ int colsum_parts(int rows);
 void colsum_bf16(const void* x, float* partial, void* out, int accumulate, int rows, int cols, cudaStream_t s);
 void adamw_bf16(void* w, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2,
                 float eps, float wd, int step, float gscale, cudaStream_t s);
+int adamw_split(void* w, void* lo, const void* g, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
+                float wd, int step, float gscale, cudaStream_t s);
 void adamw_master(float* master, void* w_out, const void* g, int g_is_f32, float* m, float* v, long long n, float lr,
                   float b1, float b2, float eps, float wd, int step, float gscale, cudaStream_t s);
 void adamw_f32(float* w, const float* g, float* m, float* v, long long n, float lr, float b1, float b2, float eps,

@@ -266,6 +266,67 @@ __global__ void adamw_f32_kernel(float* __restrict__ w, const float* __restrict_
   }
 }
 
+// AdamW on an fp32 master that is stored SPLIT: its high 16 bits are the bf16 working weight itself (kept
+// where forward and backward read it) and only its low 16 bits travel with the optimizer state, so the
+// state is 6 bytes per parameter (low half + bf16 moments) with an exact fp32 master.  The working
+// weight is the master rounded half away from zero, which makes the split exact:
+//   master_bits = (w_bits << 16) + (int16) lo,   lo = master_bits & 0xffff.
+DFB_DEVICE float split_join(bf16 w, uint16_t lo) {
+  uint32_t hi = static_cast<uint32_t>(__bfloat16_as_ushort(w)) << 16;
+  return __uint_as_float(hi + static_cast<uint32_t>(static_cast<int32_t>(static_cast<int16_t>(lo))));
+}
+DFB_DEVICE void split_cut(float x, bf16& w, uint16_t& lo) {
+  uint32_t b = __float_as_uint(x);
+  w = __ushort_as_bfloat16(static_cast<uint16_t>((b + 0x8000u) >> 16));
+  lo = static_cast<uint16_t>(b & 0xffffu);
+}
+DFB_DEVICE float adamw_split_one(bf16& w, uint16_t& lo, float gi, bf16& m, bf16& v, float lr, float b1, float b2, float eps,
+                                 float wd, float bc1, float bc2) {
+  float mi = b1 * bf2f(m) + (1.f - b1) * gi;
+  float vi = b2 * bf2f(v) + (1.f - b2) * gi * gi;
+  m = f2bf(mi); v = f2bf(vi);
+  float mh = bf2f(m) / bc1, vh = bf2f(v) / bc2;
+  float wi = split_join(w, lo);
+  wi -= lr * (mh / (sqrtf(vh) + eps) + wd * wi);
+  split_cut(wi, w, lo);
+  return wi;
+}
+// 8 elements per thread through 16-byte accesses; the tail (n % 8) runs scalar in the last block.
+__global__ void adamw_split_kernel(bf16* __restrict__ w, uint16_t* __restrict__ lo, const bf16* __restrict__ g,
+                                   bf16* __restrict__ m, bf16* __restrict__ v, long long n, float lr, float b1, float b2,
+                                   float eps, float wd, float bc1, float bc2, float gscale) {
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 wq = reinterpret_cast<uint4*>(w)[i], lq = reinterpret_cast<uint4*>(lo)[i];
+    uint4 gq = reinterpret_cast<const uint4*>(g)[i], mq = reinterpret_cast<uint4*>(m)[i], vq = reinterpret_cast<uint4*>(v)[i];
+    bf16* wp = reinterpret_cast<bf16*>(&wq); uint16_t* lp = reinterpret_cast<uint16_t*>(&lq);
+    const bf16* gp = reinterpret_cast<const bf16*>(&gq);
+    bf16* mp = reinterpret_cast<bf16*>(&mq); bf16* vp = reinterpret_cast<bf16*>(&vq);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) adamw_split_one(wp[k], lp[k], bf2f(gp[k]) * gscale, mp[k], vp[k], lr, b1, b2, eps, wd, bc1, bc2);
+    reinterpret_cast<uint4*>(w)[i] = wq; reinterpret_cast<uint4*>(lo)[i] = lq;
+    reinterpret_cast<uint4*>(m)[i] = mq; reinterpret_cast<uint4*>(v)[i] = vq;
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    for (long long i = (n8 << 3) + threadIdx.x; i < n; i += blockDim.x)
+      adamw_split_one(w[i], lo[i], bf2f(g[i]) * gscale, m[i], v[i], lr, b1, b2, eps, wd, bc1, bc2);
+  }
+}
+// A weight that was never stepped has lo == 0 (master == weight).  All five arrays must be 16-byte aligned
+// (fields of packed layouts are 256-byte aligned); returns -2 otherwise.
+int adamw_split(void* w, void* lo, const void* g, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
+                float wd, int step, float gscale, cudaStream_t s) {
+  if (n == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(lo) | reinterpret_cast<uintptr_t>(g) |
+       reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15)
+    return -2;
+  float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  adamw_split_kernel<<<ew_blocks((n + 7) / 8), 256, 0, s>>>((bf16*)w, (uint16_t*)lo, (const bf16*)g, (bf16*)m, (bf16*)v, n, lr,
+                                                            b1, b2, eps, wd, bc1, bc2, gscale);
+  return 0;
+}
+
 void adamw_bf16(void* w, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2,
                 float eps, float wd, int step, float gscale, cudaStream_t s) {
   if (n == 0) return;

@@ -224,6 +224,12 @@ def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, 
     return w
 
 
+@reg("adamw_split_step")
+def adamw_split_step(w, lo, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, gscale=1.0):
+    native().adamw_split(w, lo, g, m, v, lr, beta1, beta2, eps, wd, int(step), gscale)
+    return w
+
+
 @reg("sgd_step")
 def sgd_step(w, g, m=None, lr=1e-2, momentum=0.0, wd=0.0):
     native().sgd_bf16(w, g, m, lr, momentum, wd)

@@ -346,6 +346,35 @@ def adamw_step(w, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, 
     return w
 
 
+def split_master_join(w, lo):
+    """fp32 master from a bf16 weight (high half) and its int16 low-half plane."""
+    hi = w.view(torch.int16).to(torch.int32) << 16
+    return (hi + lo.view(torch.int16).to(torch.int32)).view(torch.float32)
+
+
+def split_master_cut(x):
+    """fp32 -> (bf16 weight rounded half away from zero, int16 low half); exact inverse of the join."""
+    b = x.contiguous().view(torch.int32)
+    hi = ((b + 0x8000) >> 16).to(torch.int16).view(torch.bfloat16)
+    lo = (b & 0xFFFF).to(torch.int16)
+    return hi, lo
+
+
+@register("adamw_split_step", "eager")
+def adamw_split_step(w, lo, g, m, v, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.0, step=1, gscale=1.0):
+    gf = g.float() * gscale
+    m.copy_((beta1 * m.float() + (1 - beta1) * gf).to(m.dtype))
+    v.copy_((beta2 * v.float() + (1 - beta2) * gf * gf).to(v.dtype))
+    mh = m.float() / (1 - beta1 ** step)
+    vh = v.float() / (1 - beta2 ** step)
+    wf = split_master_join(w, lo)
+    wf = wf - lr * (mh / (vh.sqrt() + eps) + wd * wf)
+    hi, low = split_master_cut(wf)
+    w.copy_(hi)
+    lo.view(torch.int16).copy_(low)
+    return w
+
+
 @register("sgd_step", "eager")
 def sgd_step(w, g, m=None, lr=1e-2, momentum=0.0, wd=0.0):
     gf = g.float()

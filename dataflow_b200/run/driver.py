@@ -169,6 +169,8 @@ class Trainer:
         self.step_index = 0
         self.last_result = None
         self.zero = (self.program.metadata or {}).get("zero")
+        # weights that end a step on the device stay there for the next one (Session.resident)
+        self.keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
         for g in self.groups.values():
             if hasattr(g, "attach"):
                 g.attach(self)
@@ -219,7 +221,8 @@ class Trainer:
         if seq_lens:
             args["seq_lens"] = dict(seq_lens)
         res = self.engine.execute(self.program, self.resolver, self.store.buffers(), run_args=args,
-                                  groups=self.groups, manage_pools=self.device is None)
+                                  groups=self.groups, manage_pools=self.device is None,
+                                  keep_resident=self.keep_resident)
         self.last_result = res
         res.raise_if_failed()
         for g in self.groups.values():
@@ -230,8 +233,34 @@ class Trainer:
             loss += float(self.host_tensor(k, (1,), "fp32")[0])
         return loss
 
+    def sync_to_host(self) -> int:
+        """Copy every device-resident persistent object back into the host store (its host bytes go stale
+        while it lives on the device between steps).  Call before reading weights from the store, e.g. to
+        checkpoint.  Returns the bytes copied."""
+        held = self.session.resident()
+        if not held:
+            return 0
+        n = 0
+        if self.device is None:
+            import ctypes
+            for oid, (ptr, size) in held.items():
+                ctypes.memmove(self.store.buffer(oid).ptr, ptr, size)
+                n += size
+            return n
+        import torch
+        from ..runtime.interop import torch_view
+        from ..runtime.executable import Buffer
+        self.backend.synchronize()
+        for oid, (ptr, size) in held.items():
+            src = torch_view(Buffer(ptr, size, "fast", oid), (size,), "uint8", 0, self.device)
+            torch_view(self.store.buffer(oid), (size,), "uint8", 0, None).copy_(src)
+            n += size
+        torch.cuda.synchronize(self.device)
+        return n
+
     def close(self):
         self.backend.synchronize()
+        self.session.drop_resident()
         for g in self.groups.values():
             if hasattr(g, "close"):
                 g.close()

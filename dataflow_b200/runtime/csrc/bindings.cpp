@@ -206,7 +206,13 @@ PYBIND11_MODULE(_runtime, m) {
       .def("fast_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.fast_pool.slab_base()), s.fast_pool.slab_capacity()); })
       .def("backing_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.backing_pool.slab_base()), s.backing_pool.slab_capacity()); })
       .def("vendor_allocs", [](Session& s) { return s.fast_pool.vendor_allocs + s.backing_pool.vendor_allocs; })
-      .def("trim", [](Session& s) { s.fast_pool.trim(); s.backing_pool.trim(); });
+      .def("trim", [](Session& s) { s.fast_pool.trim(); s.backing_pool.trim(); })
+      .def("resident", [](Session& s) {
+        py::dict d;
+        for (auto& kv : s.resident) d[py::str(kv.first)] = py::make_tuple(reinterpret_cast<uint64_t>(kv.second.ptr), kv.second.size);
+        return d;
+      })
+      .def("drop_resident", [](Session& s) { s.drop_resident(); });
 
   py::class_<std::atomic<bool>, std::shared_ptr<std::atomic<bool>>>(m, "CancelFlag")
       .def(py::init([]() { return std::make_shared<std::atomic<bool>>(false); }))
@@ -219,7 +225,7 @@ PYBIND11_MODULE(_runtime, m) {
       .def("execute",
            [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
               bool strict_final, bool poison, bool record_events, double headroom,
-              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools) {
+              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident) {
              std::unordered_map<std::string, InitialBuffer> init;
              for (auto kv : initial) {
                auto t = kv.second.cast<py::tuple>();
@@ -232,6 +238,7 @@ PYBIND11_MODULE(_runtime, m) {
              opt.slab_headroom = headroom;
              opt.cancel = cancel ? cancel.get() : nullptr;
              opt.manage_pools = manage_pools;
+             opt.keep_resident = keep_resident;
              LaunchFn fn;
              if (!launch.is_none()) {
                fn = [launch](const LaunchArgs& a) {
@@ -257,5 +264,6 @@ PYBIND11_MODULE(_runtime, m) {
            py::arg("program"), py::arg("launch") = py::none(), py::arg("initial") = py::dict(),
            py::arg("strict_final_locations") = true, py::arg("poison_on_free") = false,
            py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
-           py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true);
+           py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true,
+           py::arg("keep_resident") = false);
 }

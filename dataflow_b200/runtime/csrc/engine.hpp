@@ -92,6 +92,12 @@ class Session {
   int compute_stream, h2d_stream, d2h_stream;
   BufferPool fast_pool, backing_pool;
   void ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom);
+  // Fast copies of objects whose final location is "fast", kept out of the pool between execute() calls
+  // (ExecOptions::keep_resident).  The next program that starts such an object in fast adopts the bytes
+  // in place: parameters stay on the device across steps with no transfer.
+  std::unordered_map<std::string, BufferRef> resident;
+  void drop_resident();
+  void drop_resident(const std::string& id);
 };
 
 enum class SlotState : int { ABSENT = 0, RESERVED, LIVE, PENDING_OUTBOUND, OUTBOUND, INBOUND };
@@ -150,6 +156,7 @@ struct ExecOptions {
   bool keep_finals = true;          // hand final backing buffers to the caller instead of freeing
   double slab_headroom = 0.0;
   bool manage_pools = true;         // size the session's slabs from the program's capacities
+  bool keep_resident = false;       // final-fast objects stay in Session::resident for the next execute()
   std::atomic<bool>* cancel = nullptr;
 };
 

@@ -91,6 +91,13 @@ class Session:
     def compute_stream_handle(self) -> int:
         return self.backend.stream_handle(self.native.compute_stream)
 
+    def resident(self) -> dict[str, tuple[int, int]]:
+        """``{object id: (device address, bytes)}`` of the final-fast objects held since the last run."""
+        return dict(self.native.resident())
+
+    def drop_resident(self) -> None:
+        self.native.drop_resident()
+
 
 class ChainIndex:
     """Program → executor index form, cached per program object."""
@@ -181,7 +188,7 @@ class Engine:
                 initial_buffers: Mapping[str, Buffer] | None = None, *,
                 run_args: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
                 cancel_event: threading.Event | None = None, record_events: bool = False,
-                slab_headroom: float = 0.0, manage_pools: bool = True) -> RunResult:
+                slab_headroom: float = 0.0, manage_pools: bool = True, keep_resident: bool = False) -> RunResult:
         ci = self.chain_index(program)
         tasks = program.tasks
         run_values: dict[str, Any] = {}
@@ -226,7 +233,8 @@ class Engine:
             watcher.start()
         try:
             raw = self._native.execute(ci.ir, launch, initial, self.strict_final_locations,
-                                       self.poison_on_free, record_events, slab_headroom, cancel, manage_pools)
+                                       self.poison_on_free, record_events, slab_headroom, cancel, manage_pools,
+                                       keep_resident)
         finally:
             if watcher is not None:
                 stop.set()

@@ -10,7 +10,7 @@ import ctypes
 from typing import Sequence
 
 TORCH_DTYPE_BY_NAME: dict[str, object] = {}
-_ITEMSIZE = {"fp32": 4, "bf16": 2, "fp16": 2, "int32": 4, "int64": 8, "uint8": 1, "int8": 1, "fp64": 8, "bool": 1,
+_ITEMSIZE = {"fp32": 4, "bf16": 2, "fp16": 2, "int32": 4, "int64": 8, "int16": 2, "uint8": 1, "int8": 1, "fp64": 8, "bool": 1,
              "fp8_e4m3": 1, "fp8_e5m2": 1}
 
 
@@ -19,7 +19,7 @@ def _dtypes():
         import torch
         TORCH_DTYPE_BY_NAME.update({
             "fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16, "int32": torch.int32,
-            "int64": torch.int64, "uint8": torch.uint8, "int8": torch.int8, "fp64": torch.float64,
+            "int64": torch.int64, "int16": torch.int16, "uint8": torch.uint8, "int8": torch.int8, "fp64": torch.float64,
             "bool": torch.bool, "fp8_e4m3": torch.float8_e4m3fn, "fp8_e5m2": torch.float8_e5m2})
     return TORCH_DTYPE_BY_NAME
 

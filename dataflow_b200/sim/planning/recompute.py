@@ -43,7 +43,7 @@ def spread(layers: list[int], k: int) -> list[int]:
 
 
 def plan_with_recompute(program, fast_memory_capacity, build_variant: Callable[[Mapping[int, int]], object], *,
-                        backing_memory_capacity=None, leeway_bytes=None, max_evals: int = 14):
+                        backing_memory_capacity=None, leeway_bytes=None, max_evals: int = 24):
     from ...lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES, plan_program
     leeway = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else leeway_bytes
     layers, levels = _layers_and_levels(program)
@@ -61,7 +61,8 @@ def plan_with_recompute(program, fast_memory_capacity, build_variant: Callable[[
         try:
             p = plan_program(prog, fast_memory_capacity, recompute=False,
                              backing_memory_capacity=backing_memory_capacity, leeway_bytes=leeway,
-                             specs=None if full else quick_specs, rules=None if full else quick_rules)
+                             specs=None if full else quick_specs, rules=None if full else quick_rules,
+                             quick=not full)
             p.recompute_levels = dict(key)
         except PlanningError:
             p = None
@@ -95,8 +96,8 @@ def plan_with_recompute(program, fast_memory_capacity, build_variant: Callable[[
     if R > 1:
         base = dict(best.recompute_levels) if best is not None else {}
         for lv in levels:
-            for nlast in (L, L // 2):
-                if evals >= max_evals + 4:
+            for nlast in (L, (3 * L) // 4, L // 2):
+                if evals >= max_evals + 8 or nlast <= 0:
                     break
                 trial = dict(base)
                 trial.update({(R - 1, l): lv for l in spread(layers, nlast)})

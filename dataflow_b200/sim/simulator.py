@@ -200,6 +200,13 @@ class Simulator:
             self._complete(d)
 
     # -- tasks ----------------------------------------------------------------
+    def _before_directives(self, idx: int, task: Task, t: float) -> None:
+        """Hook for planners that decide a task's directives while the run unfolds (``policies.lookahead``)."""
+
+    def _on_deadlock(self, idx: int, task: Task, now: float, need: int, missing: list[str]) -> bool:
+        """Hook: return True after making progress possible (planners add an emergency eviction)."""
+        return False
+
     def _blocked_reason(self, task: Task, need: int):
         missing = [i for i in task.inputs
                    if (e := self.pool.get((i, FAST))) is None or e.state != "live"]
@@ -233,6 +240,7 @@ class Simulator:
         for m in task.mutates_inputs:
             pool[(m, FAST)].dirty = True
         self._note("task_end", t, task_id=task.id)
+        self._before_directives(idx, task, t)
         if task.releases_after:
             for obj in task.releases_after:
                 e = pool.get((obj, FAST))
@@ -320,6 +328,8 @@ class Simulator:
                     break
                 t, d = self._next_completion()
                 if d is None:
+                    if self._on_deadlock(idx, task, now, need, missing):
+                        continue
                     self._deadlock(task, now, need, missing)
                 now = self._complete(d)
             b_need = sum(o.size for o in task.outputs if o.location == BACKING)

@@ -1,0 +1,46 @@
+"""Final-fast objects stay on the fast tier across execute() calls (Session.resident)."""
+import numpy as np
+import torch
+
+from dataflow_b200.core import ObjectSpec, OutputSpec, Program, TaskSpec
+from dataflow_b200.runtime import CpuBackend, Engine
+from dataflow_b200.runtime.executable import Buffer
+from dataflow_b200.runtime.interop import torch_view
+
+
+class _AddOne:
+    def launch(self, ctx):
+        w = torch_view(ctx.inputs[0], (4,), "fp32")
+        w += 1.0
+        out = torch_view(ctx.outputs[0], (4,), "fp32")
+        out.copy_(w)
+
+
+def _program():
+    return Program(
+        name="resident",
+        initial_objects=(ObjectSpec("W", 16, "fast", "parameter", persistent=True),),
+        tasks=(TaskSpec("bump", inputs=("W",), mutates=("W",),
+                        outputs=(OutputSpec("snap", 16, "backing", "output"),), runtime_us=1.0),),
+        final_locations={"W": "fast", "snap": "backing"})
+
+
+def test_resident_object_is_adopted_in_place_and_host_copy_is_not_reread():
+    be = CpuBackend()
+    eng = Engine(be)
+    host = np.zeros(4, dtype=np.float32)
+    snap = np.zeros(4, dtype=np.float32)
+    bufs = {"W": Buffer(host.ctypes.data, 16, "backing", "W"), "snap": Buffer(snap.ctypes.data, 16, "backing", "snap")}
+    prog = _program()
+    for step in range(1, 4):
+        res = eng.execute(prog, lambda t: _AddOne(), bufs, keep_resident=True).raise_if_failed()
+        assert "W" in eng.session.resident()
+        ptr, size = eng.session.resident()["W"]
+        got = torch_view(Buffer(ptr, size, "fast", "W"), (4,), "fp32")
+        assert torch.equal(got, torch.full((4,), float(step)))
+        assert (host == 0).all()                       # the stale host copy was read once, never written
+    eng.session.drop_resident()
+    assert eng.session.resident() == {}
+    # without the held copy the object is loaded from the host bytes again
+    res = eng.execute(prog, lambda t: _AddOne(), bufs, keep_resident=False).raise_if_failed()
+    assert eng.session.resident() == {}

@@ -30,11 +30,12 @@ def twin_curve(cfg, tr, data_steps, hyper, steps):
     return losses
 
 
-def run_pair(device, policy, steps=4, budget=None):
+def run_pair(device, policy, steps=4, budget=None, lower_kwargs=None):
     fam = resolve_family("llama3")
     cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy=policy)
     hyper = {"lr": 2e-3, "weight_decay": 0.1}
-    tr = Trainer("llama3", cfg, budget_gib=budget, device=device, hyper=hyper, seed=3, leeway_bytes=0)
+    tr = Trainer("llama3", cfg, budget_gib=budget, device=device, hyper=hyper, seed=3, leeway_bytes=0,
+                 lower_kwargs=lower_kwargs)
     try:
         data = [synthetic_rounds(cfg, tr.rounds, tr.T, 64, 11, s) for s in range(steps)]   # small id range: learnable
         ref = twin_curve(cfg, tr, data, hyper, steps)
@@ -67,6 +68,31 @@ def test_plan_invariance_on_cpu():
     a, _ = run_pair(None, "fp32", steps=3, budget=None)
     b, _ = run_pair(None, "fp32", steps=3, budget=0.02)
     assert a == pytest.approx(b, rel=1e-6)
+
+
+def test_split_master_policy_tracks_fp32_master_policy():
+    """Same fp32 master either way; only the moments differ (bf16 vs fp32 storage)."""
+    a, ref = run_pair(None, "bf16_split_master")
+    b, _ = run_pair(None, "bf16_master")
+    for x, y in zip(a, b):
+        assert x == pytest.approx(y, rel=5e-3)
+    assert a[-1] < a[0]
+
+
+@pytest.mark.parametrize("budget", [None, 0.02])
+def test_resident_params_give_the_same_losses(budget):
+    """Weights that stay on the fast tier between steps (never re-read from the host store) train identically."""
+    a, _ = run_pair(None, "fp32", steps=4, budget=budget)
+    b, _ = run_pair(None, "fp32", steps=4, budget=budget, lower_kwargs={"resident_params": True})
+    assert a == pytest.approx(b, rel=1e-6)
+
+
+@pytest.mark.gpu
+def test_gpu_split_master_resident_in_band():
+    eng, ref = run_pair(0, "bf16_split_master", lower_kwargs={"resident_params": True})
+    for a, b in zip(eng, ref):
+        assert a == pytest.approx(b, rel=3e-2)
+    assert eng[-1] < eng[0]
 
 
 @pytest.mark.gpu

@@ -57,3 +57,38 @@ def test_transfer_time_distortion_changes_timing_not_results():
     be.transfer_time_scale = 3.0
     res = Engine(be).execute(prog)
     assert res.outcome.ok and res.makespan_us >= r.makespan
+
+
+# ---------------------------------------------------------------- lookahead (oracle-in-the-loop) planner
+@pytest.mark.parametrize("cap", [20000, 6000, 3000, 2200, 1800])
+def test_lookahead_fits_and_engine_matches_simulator_exactly(cap):
+    from dataflow_b200.sim.policies.lookahead import lookahead
+    r = lookahead(train_chain(), cap)
+    log = run(r.chain)
+    assert log.peak_fast_memory_bytes <= cap
+    assert log.makespan == r.makespan >= r.lower_bound
+    res = Engine(FakeBackend()).execute(from_sim_chain(r.chain)).raise_if_failed()
+    assert compare_to_sim_eventlog(res.trace, log) == []
+    assert res.makespan_us == log.makespan
+
+
+def test_lookahead_unbounded_moves_only_what_must_move():
+    from dataflow_b200.sim.policies.lookahead import lookahead
+    ch = train_chain(L=4, rounds=2)
+    r = lookahead(ch, None)
+    log = run(r.chain)
+    loads = [iv for iv in log.task_intervals if iv.track == "from_slow"]
+    stores = [iv for iv in log.task_intervals if iv.track == "to_slow"]
+    preplaced = [o for o in r.chain.initial_memory if o.location == "fast"]
+    # tok + W, O come in once each (up front or by prefetch); W, O are written back once
+    assert len(loads) + len(preplaced) == 9 and len(stores) == 8
+
+
+def test_plan_program_auto_takes_the_better_planner():
+    from dataflow_b200.lowering.planning import plan_program
+    prog = from_sim_chain(train_chain())
+    a = plan_program(prog, 3000, leeway_bytes=0, policy="auto")
+    b = plan_program(prog, 3000, leeway_bytes=0, policy="pressurefit")
+    c = plan_program(prog, 3000, leeway_bytes=0, policy="lookahead")
+    assert a.makespan_us <= min(b.makespan_us, c.makespan_us) + 1e-9
+    assert c.policy.startswith("lookahead:")
