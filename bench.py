@@ -39,7 +39,8 @@ def parse_args(argv=None):
     ap.add_argument("--batch", type=int, default=4, help="sequences per grad-accumulation round")
     ap.add_argument("--tokens-per-gpu", type=int, default=131072)
     ap.add_argument("--budget-gib", type=float, default=None)
-    ap.add_argument("--dtype-policy", default="bf16_master")
+    ap.add_argument("--dtype-policy", default="bf16_split_master",
+                    help="bf16 weights with an exact fp32 master stored split (low halves + bf16 moments as optimizer state)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: cut the model (the result is not a valid bench)")
     ap.add_argument("--kernels", default=None, help="kernel lane override (e.g. baseline)")
     ap.add_argument("--no-profile", action="store_true", help="plan from roofline seeds instead of measured task costs")
@@ -116,7 +117,7 @@ def bench_ours(a) -> dict:
         cfg = dataclasses.replace(cfg, n_layers=a.layers)
     budget = a.budget_gib if a.budget_gib is not None else PRESET_BUDGET_GIB.get(a.preset, 60.0)
     parallel = a.parallel or ("zero3" if world > 1 else "solo")
-    groups, lower_kwargs = {}, None
+    groups, lower_kwargs = {}, {"resident_params": True}      # weights stay on the device from step to step
     if world > 1:
         from dataflow_b200.parallel.zero import make_dp_group, zero_lower_kwargs
         groups = {"dp": make_dp_group(rank, world, local)}

@@ -18,6 +18,8 @@
 // Replaces the reference's cuBLAS calls behind its linear seam (src/dataflow_training/blocks/linear.py:58-90).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -336,7 +338,8 @@ int gemm_bf16_last_error() {
 // Otherwise K-major (A stored (M, K), B stored (N, K)).  Returns 0 on success.
 // 0: default path; 1 / 2: single-CTA kernel with that M stacking; 3: CTA-pair kernel (falls back when too few tiles)
 static int g_gemm_mt_override = 0;
-static int g_gemm_default_path = 1;
+// DFB_GEMM_PATH in the environment picks the default path of the process (read once)
+static int g_gemm_default_path = getenv("DFB_GEMM_PATH") ? atoi(getenv("DFB_GEMM_PATH")) : 1;
 void gemm_bf16_set_mt(int mt) { g_gemm_mt_override = mt; }
 void gemm_bf16_set_default_path(int path) { g_gemm_default_path = path; }
 

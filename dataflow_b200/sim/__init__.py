@@ -4,3 +4,5 @@ from .schema import (Event, EventLog, MemoryTracePoint, Object, OutputAlloc, Tas
 from .errors import SimulationCapacityError, SimulationError
 from .simulator import Simulator, compute_lower_bound, run
 from .validate import ValidationError, validate_chain, validate_planning_input
+from .stall_report import StallReport, build_stall_report
+from .reference_stream import Reference, compute_reference_stream, next_ref_time

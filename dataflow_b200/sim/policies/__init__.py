@@ -5,8 +5,10 @@ from .pressurefit import (PREFETCH_RULES, RESIDENCY_SPECS, PlanningError, Pressu
 
 def get_all_policies():
     from . import baselines
+    from .lookahead import apply_lookahead_policy
     return {
         "pressurefit": apply_pressurefit_policy,
+        "lookahead": apply_lookahead_policy,
         "sliding_window": baselines.sliding_window,
         "belady_reactive": baselines.belady_reactive,
         "roundtrip": baselines.roundtrip_planner,

@@ -145,6 +145,8 @@ class EventLog:
     peak_backing_memory_bytes: int = 0
     memory_trace: list[MemoryTracePoint] = field(default_factory=list)
     stalls: dict[str, float] = field(default_factory=dict)     # task id -> µs waited after compute was free
+    # task id -> (input objects that were not live when the task first blocked, short of fast memory?)
+    stall_causes: dict[str, tuple[tuple[str, ...], bool]] = field(default_factory=dict)
 
     @property
     def makespan(self) -> Time:

@@ -102,6 +102,7 @@ class Simulator:
         self.peak_fast = 0
         self.peak_backing = 0
         self.stalls: dict[str, float] = {}
+        self.stall_causes: dict[str, tuple[tuple[str, ...], bool]] = {}
         self.last_ref = last_references(chain.tasks)
 
     # -- bookkeeping ---------------------------------------------------------
@@ -326,6 +327,8 @@ class Simulator:
                 missing, short = self._blocked_reason(task, need)
                 if not missing and not short:
                     break
+                if task.id not in self.stall_causes:
+                    self.stall_causes[task.id] = (tuple(missing), bool(short))
                 t, d = self._next_completion()
                 if d is None:
                     if self._on_deadlock(idx, task, now, need, missing):
@@ -348,6 +351,8 @@ class Simulator:
             self.workspace = task.workspace_bytes
             if now > free_at:
                 self.stalls[task.id] = now - free_at
+            else:
+                self.stall_causes.pop(task.id, None)
             end = now + task.runtime
             self.intervals.append(TaskInterval(task.id, now, end, "compute"))
             self._note("task_start", now, task_id=task.id)
@@ -374,7 +379,7 @@ class Simulator:
                 if f is not None and f.dirty:
                     raise SimulationError(f"final location violated: backing copy of {obj!r} is stale")
         return EventLog(self.intervals, self.events, self.peak_fast, max(self.peak_backing, used[BACKING]),
-                        self.trace, self.stalls)
+                        self.trace, self.stalls, self.stall_causes)
 
 
 def run(chain: TaskChain, validate: bool = True, snapshots: bool = False,

@@ -92,3 +92,20 @@ def test_plan_program_auto_takes_the_better_planner():
     c = plan_program(prog, 3000, leeway_bytes=0, policy="lookahead")
     assert a.makespan_us <= min(b.makespan_us, c.makespan_us) + 1e-9
     assert c.policy.startswith("lookahead:")
+
+
+@pytest.mark.parametrize("cap", [None, 20000, 3000])
+def test_every_registered_policy_produces_a_plan_the_simulator_accepts(cap):
+    from dataflow_b200.sim.policies import get_all_policies
+    ch = train_chain(L=4, rounds=2)
+    lower = sum(t.runtime for t in ch.tasks)
+    for name, fn in get_all_policies().items():
+        if name == "all_resident" and cap == 3000:
+            with pytest.raises(PlanningError):
+                fn(ch, cap)
+            continue
+        planned = fn(ch, cap)
+        log = run(planned)
+        assert log.makespan >= lower, name
+        if cap is not None:
+            assert log.peak_fast_memory_bytes <= cap, name

@@ -82,3 +82,30 @@ def test_final_location_checked():
     ch = TaskChain([Object("x", 10, "fast")], [Task("a", ["x"], [], 5, mutates_inputs=["x"])], {"x": "backing"}, 100, None, 10, 10)
     with pytest.raises(SimulationError):
         run(ch)
+
+
+def test_stall_report_names_the_blocking_transfer():
+    from dataflow_b200.sim import build_stall_report
+    # W arrives late: the task stalls on it; the report names W and the lane shows the busy time
+    ch = TaskChain([Object("W", 400, "backing", "weight"), Object("x", 10, "fast")],
+                   [Task("a", ["x"], [OutputAlloc("y", 10)], 50, prefetch_after=[TransferTrigger("W")]),
+                    Task("b", ["y", "W"], [OutputAlloc("z", 10)], 50)],
+                   {}, 1000, None, 4, 4)
+    log = run(ch)
+    rep = build_stall_report(ch, log)
+    assert rep.stall_us == pytest.approx(100.0)
+    (s,) = rep.stalls
+    assert s.task_id == "b" and s.waited_inputs == ("W",) and s.blocking_object == "W" and not s.waited_capacity
+    assert rep.by_object_type == {"weight": pytest.approx(100.0)}
+    assert rep.lanes["from_slow"].transfers == 1 and rep.lanes["from_slow"].busy_us == pytest.approx(100.0)
+    assert "waiting for inputs ['W']" in rep.format()
+
+
+def test_reference_stream_orders_first_touches():
+    from dataflow_b200.sim import compute_reference_stream, next_ref_time
+    from dataflow_b200.sim.reference_stream import stall_free_starts
+    tasks = [Task("a", ["x"], [OutputAlloc("y", 1)], 10), Task("b", ["y", "w"], [], 5), Task("c", ["x"], [], 1)]
+    st = stall_free_starts(tasks)
+    refs = compute_reference_stream(tasks, st)
+    assert [(r.obj_id, r.ref_t) for r in refs] == [("x", 0.0), ("y", 0.0), ("w", 10.0)]
+    assert next_ref_time("x", tasks[1:], st) == 15.0 and next_ref_time("q", tasks, st) is None
