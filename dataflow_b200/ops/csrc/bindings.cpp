@@ -219,7 +219,7 @@ static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls,
 static Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
   static const std::map<std::string, at::ScalarType> types = {
       {"bf16", at::kBFloat16}, {"fp32", at::kFloat}, {"fp16", at::kHalf}, {"int32", at::kInt}, {"int64", at::kLong},
-      {"uint8", at::kByte}, {"int8", at::kChar}, {"fp64", at::kDouble}, {"bool", at::kBool},
+      {"int16", at::kShort}, {"uint8", at::kByte}, {"int8", at::kChar}, {"fp64", at::kDouble}, {"bool", at::kBool},
       {"fp8_e4m3", at::kFloat8_e4m3fn}, {"fp8_e5m2", at::kFloat8_e5m2}};
   auto it = types.find(dtype);
   TORCH_CHECK(it != types.end(), "unknown dtype ", dtype);

@@ -12,11 +12,14 @@
 //   warp 1      leader only: issues tcgen05.mma.cta_group::2; tcgen05.commit arrives on the
 //               "empty" barrier of both CTAs and publishes finished accumulators to both
 //   warps 2-5   epilogue for the CTA's own 128 accumulator lanes (two 256-column accumulators in
-//               tensor memory, so the epilogue overlaps the next tile's main loop)
+//               tensor memory, so the epilogue overlaps the next tile's main loop).  Each warp turns
+//               its 32 rows into 128-byte-swizzled 32 x 128 B boxes in shared memory and hands them
+//               to TMA stores (row-per-thread stores straight to global cost a quarter of the
+//               throughput on short-K shapes); an addend (residual / gradient accumulation) is
+//               fetched by TMA into the same box one chunk ahead
 // No TMA load carries a cluster-broadcast qualifier.  Every wait is bounded.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -34,7 +37,9 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int EPI_BOX_BYTES = 32 * 128;       // 32 rows x 128 bytes: one TMA store of one epilogue warp
+constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;   // four warps, double buffered
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
 
 struct Params {
   int M, N, K;
@@ -44,7 +49,7 @@ struct Params {
   long long ldd, ld_add;
   int d_is_f32, add_is_f32;
   int group_m;
-  int dbg;
+  int tma_epi;                  // epilogue through shared memory + TMA (needs addend dtype == D dtype)
   int* err;
 };
 
@@ -53,6 +58,7 @@ struct SharedBarriers {
   uint64_t empty[STAGES];       // per CTA: stage reusable
   uint64_t tmem_full[2];        // per CTA: accumulator ready
   uint64_t tmem_empty[2];       // used in the leader: both CTAs' epilogues drained the accumulator
+  uint64_t add_full[4][2];      // per epilogue warp and box: addend bytes landed
   uint32_t tmem_base;
   int abort;
 };
@@ -69,10 +75,12 @@ DFB_DEVICE void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, i
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Params p) {
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_add, Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedBarriers* sb = reinterpret_cast<SharedBarriers*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;          // 1024-byte aligned (swizzle atom)
+  SharedBarriers* sb = reinterpret_cast<SharedBarriers*>(epi_smem + EPI_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = ptx::cluster_ctarank();            // 0 = leader
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
@@ -84,10 +92,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&sb->full[s], 1); ptx::mbar_init(&sb->empty[s], 1); }
     for (int a = 0; a < 2; ++a) { ptx::mbar_init(&sb->tmem_full[a], 1); ptx::mbar_init(&sb->tmem_empty[a], 8); }
+    for (int w = 0; w < 4; ++w) { ptx::mbar_init(&sb->add_full[w][0], 1); ptx::mbar_init(&sb->add_full[w][1], 1); }
     sb->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
+    if (p.tma_epi) {
+      ptx::prefetch_tmap(&tmap_d);
+      if (p.addend) ptx::prefetch_tmap(&tmap_add);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(&sb->tmem_base, TMEM_COLS);
@@ -168,6 +181,116 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // ------------------------------------------------------------------ epilogue (both CTAs, own lanes)
     const int q = warp & 3;
     uint32_t tcount = 0;
+    if (p.tma_epi) {
+      // One box = this warp's 32 rows x 128 bytes of D (64 bf16 or 32 fp32 columns), 128-byte swizzled.
+      const int box_cols = p.d_is_f32 ? 32 : 64;
+      const int chunks = BN / box_cols;
+      uint8_t* my_smem = epi_smem + q * 2 * EPI_BOX_BYTES;
+      uint64_t* my_bar = sb->add_full[q];
+      const bool has_add = p.addend != nullptr;
+      const int row_in_cta = static_cast<int>(cta) * HALF_M + q * 32;
+      uint32_t cc = 0;                       // boxes handled by this warp so far (buffer = cc & 1)
+      if (has_add && lane == 0 && cluster_id < num_tiles) {
+        int mb, nb;
+        tile_coords(cluster_id, m_blocks, n_blocks, p.group_m, mb, nb);
+        ptx::mbar_expect_tx(&my_bar[0], EPI_BOX_BYTES);
+        ptx::tma_load_2d(my_smem, &tmap_add, &my_bar[0], nb * BN, mb * BM + row_in_cta);
+      }
+      for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters, ++tcount) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
+        const int acc = tcount & 1;
+        const uint32_t aph = (tcount >> 1) & 1;
+        if (!ptx::mbar_wait(&sb->tmem_full[acc], aph, abort_flag)) { sb->abort = 1; atomicExch(p.err, 14); break; }
+        ptx::tc_fence_after();
+        const int row0 = mb * BM + row_in_cta;
+        const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+        bool failed = false;
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c, ++cc) {
+          const int b = cc & 1;
+          uint8_t* buf = my_smem + b * EPI_BOX_BYTES;
+          uint8_t* my_row = buf + lane * 128;
+          const int col0 = nb * BN + c * box_cols;
+          float f[64];
+          {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr + c * box_cols, r);
+            if (!p.d_is_f32) {
+              uint32_t r2[32];
+              ptx::tmem_ld_32x32(taddr + c * box_cols + 32, r2);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[32 + i] = __uint_as_float(r2[i]);
+            } else {
+              ptx::tmem_ld_wait();
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+          }
+          if (p.bias) {
+            const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + col0;
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (i < box_cols && col0 + i < p.N) f[i] += bf2f(bp[i]);
+          }
+          if (has_add) {
+            if (!ptx::mbar_wait(&my_bar[b], (cc >> 1) & 1, abort_flag)) { sb->abort = 1; atomicExch(p.err, 15); failed = true; break; }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 v = *reinterpret_cast<const uint4*>(my_row + ((j ^ (lane & 7)) << 4));
+              if (p.d_is_f32) {
+                f[j * 4] += __uint_as_float(v.x); f[j * 4 + 1] += __uint_as_float(v.y);
+                f[j * 4 + 2] += __uint_as_float(v.z); f[j * 4 + 3] += __uint_as_float(v.w);
+              } else {
+                float t[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(&v), t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[j * 8 + i] += t[i];
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            if (p.d_is_f32) {
+              v = make_uint4(__float_as_uint(f[j * 4]), __float_as_uint(f[j * 4 + 1]), __float_as_uint(f[j * 4 + 2]),
+                             __float_as_uint(f[j * 4 + 3]));
+            } else {
+              const bf16x8 pk = pack8(f + j * 8);
+              v = *reinterpret_cast<const uint4*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          ptx::fence_proxy_async();          // generic-proxy writes -> visible to the TMA engine
+          __syncwarp();
+          if (lane == 0) {
+            if (col0 < p.N && row0 < p.M) ptx::tma_store_2d(&tmap_d, buf, col0, row0);
+            ptx::tma_store_commit();
+            ptx::tma_store_wait_read<1>();   // the other box's previous store has left shared memory
+            if (has_add) {
+              // addend of the next box (same tile, or the first box of this cluster's next tile)
+              int nt = tile, nc = c + 1;
+              if (nc == chunks) { nt = tile + num_clusters; nc = 0; }
+              if (nt < num_tiles) {
+                int nmb, nnb;
+                tile_coords(nt, m_blocks, n_blocks, p.group_m, nmb, nnb);
+                ptx::mbar_expect_tx(&my_bar[b ^ 1], EPI_BOX_BYTES);
+                ptx::tma_load_2d(my_smem + (b ^ 1) * EPI_BOX_BYTES, &tmap_add, &my_bar[b ^ 1], nnb * BN + nc * box_cols,
+                                 nmb * BM + row_in_cta);
+              }
+            }
+          }
+          __syncwarp();
+        }
+        if (failed) break;
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(&sb->tmem_empty[acc], 0);
+      }
+      if (lane == 0) ptx::tma_store_wait<0>();     // every store of this warp has completed before the CTA exits
+      __syncwarp();
+    } else
     for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters, ++tcount) {
       int mb, nb;
       tile_coords(tile, m_blocks, n_blocks, p.group_m, mb, nb);
@@ -181,13 +304,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
-        if (!(p.dbg & 2)) {
-          ptx::tmem_ld_32x32(taddr + c * 32, r);
-          ptx::tmem_ld_wait();
-        }
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
         const int col0 = nb * BN + c * 32;
-        if (p.dbg & 2) continue;
-        if (row_ok && col0 < p.N && !(p.dbg & 1)) {
+        if (row_ok && col0 < p.N) {
           float f[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
@@ -279,14 +399,14 @@ static EncodeFn encode_fn() {
 }
 
 static bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
-                     uint32_t box_outer) {
+                     uint32_t box_outer, bool f32 = false) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
+  cuuint64_t strides[1] = {ld * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -312,15 +432,23 @@ int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long lo
   CUtensorMap ta, tb;
   bool ok = a_mn ? make_map(&ta, A, M, K, lda, 64, BK) : make_map(&ta, A, K, M, lda, BK, HALF_M);
   ok = ok && (b_mn ? make_map(&tb, B, N, K, ldb, 64, BK) : make_map(&tb, B, K, N, ldb, BK, HALF_N));
+  // epilogue through TMA when the addend (if any) has D's element type; otherwise direct stores
+  const bool tma_epi = !addend || (add_is_f32 != 0) == (d_is_f32 != 0);
+  CUtensorMap td, tadd;
+  if (tma_epi) {
+    const uint32_t bc = d_is_f32 ? 32 : 64;
+    ok = ok && make_map(&td, D, N, M, ldd, bc, 32, d_is_f32 != 0);
+    ok = ok && make_map(&tadd, addend ? addend : D, N, M, addend ? ld_add : ldd, bc, 32, d_is_f32 != 0);
+  } else {
+    td = ta; tadd = ta;
+  }
   if (!ok) return -4;
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.D = D; p.addend = addend; p.bias = bias;
   p.ldd = ldd; p.ld_add = ld_add; p.d_is_f32 = d_is_f32; p.add_is_f32 = add_is_f32;
-  static int env_gm = getenv("DFB_GEMM2_GROUPM") ? atoi(getenv("DFB_GEMM2_GROUPM")) : 8;
-  static int env_dbg = getenv("DFB_GEMM2_DBG") ? atoi(getenv("DFB_GEMM2_DBG")) : 0;
-  p.group_m = env_gm;
-  p.dbg = env_dbg;
+  p.group_m = 16;
+  p.tma_epi = tma_epi ? 1 : 0;
   p.err = gemm_error_word_shared();
   int grid = 2 * static_cast<int>(tiles < clusters ? tiles : clusters);
   auto launch = [&](auto kernel, int idx) {
@@ -329,7 +457,7 @@ int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long lo
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
       configured[idx] = true;
     }
-    kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, td, tadd, p);
   };
   const int lay = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
   switch (lay) {
