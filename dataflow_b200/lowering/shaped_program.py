@@ -376,7 +376,8 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                                (), 0, {"step": s, "target": "embed"}))
     tasks.extend(opt_tasks_tail)
     if zstage:
-        metadata = {**dict(metadata or {}), "zero": {"stage": zstage, "world": zworld, "rank": int(zero.get("rank", 0))}}
+        metadata = {**dict(metadata or {}), "zero": {"stage": zstage, "world": zworld, "rank": int(zero.get("rank", 0))},
+                    "zero_full_bytes": dict(gathered)}
     md = {"tokens_per_step": T * R, "tokens_per_round": T, "grad_accum_rounds": R, "n_layers": L,
           "hardware": hw.name, **dict(metadata or {})}
     return Program(cfg.name, tuple(init), tuple(tasks), finals, None, None,

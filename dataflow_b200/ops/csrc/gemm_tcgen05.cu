@@ -339,7 +339,7 @@ int gemm_bf16_last_error() {
 // 0: default path; 1 / 2: single-CTA kernel with that M stacking; 3: CTA-pair kernel (falls back when too few tiles)
 static int g_gemm_mt_override = 0;
 // DFB_GEMM_PATH in the environment picks the default path of the process (read once)
-static int g_gemm_default_path = getenv("DFB_GEMM_PATH") ? atoi(getenv("DFB_GEMM_PATH")) : 1;
+static int g_gemm_default_path = getenv("DFB_GEMM_PATH") ? atoi(getenv("DFB_GEMM_PATH")) : 3;
 void gemm_bf16_set_mt(int mt) { g_gemm_mt_override = mt; }
 void gemm_bf16_set_default_path(int path) { g_gemm_default_path = path; }
 

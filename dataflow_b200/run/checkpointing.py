@@ -1,0 +1,233 @@
+"""Training checkpoints: ``<dir>/step_{n:06d}/`` holds one engine snapshot per rank (``rank{i}/``), the exact
+lowered programs (``programs/rank{i}.json``) and the checkpoint record, which is written last.
+
+``save_checkpoint(trainer, ...)`` works for a solo trainer and, when ``torch.distributed`` is initialised, for
+every rank of a job calling it at the same step: each rank snapshots its own persistent objects, rank 0 gathers
+the slice hashes and writes the record.  Sharded weights (``Ws_*``) are recorded as byte ranges of the logical
+``W_*`` object, so a checkpoint taken at one world size restores its weights at another; sharded optimizer state
+is recorded per source (``O_*@rank``) and restores at the same world size.  ``load_checkpoint`` reads the record,
+verifies every slice hash, fills the host store and drops device-resident copies; the returned payload carries
+the losses and the data cursor, so a resumed curve continues exactly.
+Role parity: reference ``src/dataflow_training/run/checkpointing.py:25-420``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import shutil
+from typing import Any, Mapping
+
+from ..checkpoint import read_record, resolve_targets, save_checkpoint as compose_checkpoint
+from ..checkpoint.compose import SourceSlice
+from ..checkpoint.record import has_record
+from ..core.jsonio import save_program
+from ..service.snapshots import read_manifest, read_snapshot_slice, resolve_slices, write_snapshot  # noqa: F401
+
+STEP_DIR = re.compile(r"^step_(\d{6,})$")
+
+
+def step_dir(root: str, step: int) -> str:
+    return os.path.join(root, f"step_{int(step):06d}")
+
+
+def list_checkpoints(root: str) -> list[tuple[int, str]]:
+    out = []
+    if os.path.isdir(root):
+        for name in os.listdir(root):
+            m = STEP_DIR.match(name)
+            if m and has_record(os.path.join(root, name)):
+                out.append((int(m.group(1)), os.path.join(root, name)))
+    return sorted(out)
+
+
+def resolve_resume(spec: str | None, root: str | None = None) -> str | None:
+    """``None`` / ``"none"`` -> no resume; ``"latest"`` -> newest complete step under ``root``; else a step
+    directory (or a root, meaning its latest).  Directories without a record are never resumable."""
+    if not spec or spec == "none":
+        return None
+    if spec == "latest":
+        found = list_checkpoints(root or "")
+        return found[-1][1] if found else None
+    if has_record(spec):
+        return spec
+    found = list_checkpoints(spec)
+    if found:
+        return found[-1][1]
+    raise FileNotFoundError(f"{spec}: no complete checkpoint (no checkpoint_record.json)")
+
+
+def _world(trainer) -> tuple[int, int]:
+    z = trainer.zero or {}
+    return int(z.get("rank", 0)), int(z.get("world", 1))
+
+
+class TrainerSource:
+    """The persistent objects of one in-process trainer as a checkpoint source."""
+
+    def __init__(self, trainer):
+        self.t = trainer
+        self.rank, self.world = _world(trainer)
+        self.name = str(self.rank)
+        self._pending: dict[int, dict] = {}
+
+    def persistent(self) -> dict[str, int]:
+        return {o.id: int(o.size_bytes) for o in self.t.program.initial_objects if o.persistent}
+
+    def logical_objects(self) -> dict[str, int]:
+        out: dict[str, int] = {}
+        for s in self.slices():
+            out[s.logical_id] = max(out.get(s.logical_id, 0), s.logical_offset + s.size)
+        meta = (self.t.program.metadata or {}).get("zero_full_bytes") or {}
+        for k, v in meta.items():
+            if k in out:
+                out[k] = int(v)
+        return out
+
+    def slices(self) -> list[SourceSlice]:
+        out = []
+        full = (self.t.program.metadata or {}).get("zero_full_bytes") or {}
+        for oid, size in self.persistent().items():
+            if oid.startswith("Ws_") and self.world > 1:
+                logical = "W_" + oid[3:]
+                total = int(full.get(logical, size * self.world))
+                lo = min(size * self.rank, total)
+                n = max(min(size, total - lo), 0)
+                if n:
+                    out.append(SourceSlice(oid, 0, n, logical, lo))
+            elif self.world > 1 and oid.startswith("O_") and (self.t.zero or {}).get("stage"):
+                out.append(SourceSlice(oid, 0, size, f"{oid}@{self.rank}", 0))
+            else:
+                out.append(SourceSlice(oid, 0, size, oid, 0))
+        return out
+
+    def resident_objects(self) -> dict[str, int]:
+        return self.persistent()
+
+    def start_snapshot(self, dest: str, slices: list[dict], client_meta: Mapping[str, Any]):
+        self.t.sync_to_host()
+        store = self.t.store
+        concrete = [{"id": s["id"], "offset": int(s["offset"]), "size": int(s["size"]), "as": s["id"],
+                     "object_size": store.sizes[s["id"]]} for s in slices]
+
+        def view_of(oid):
+            import ctypes
+            b = store.buffer(oid)
+            return memoryview((ctypes.c_char * b.size).from_address(b.ptr)).cast("B")
+        manifest = write_snapshot(dest, concrete, view_of, client_meta)
+        return manifest
+
+    def wait_snapshot(self, handle, timeout):
+        return handle
+
+    def engine_spec(self) -> dict:
+        return {"backing_bytes": int(self.t.store.total), "device": self.t.device,
+                "kernel_set": sorted(set(self.t.K.describe().values())), "fake": False}
+
+
+def save_checkpoint(trainer, root: str, step: int, *, seed: int = 0, client_payload: Any = None, summary: Any = None,
+                    launch: Any = None, keep_last: int | None = None, scheme: Mapping[str, Any] | None = None) -> str:
+    """Every rank of the job calls this at the same step.  Returns the step directory."""
+    src = TrainerSource(trainer)
+    sdir = step_dir(root, step)
+    rank, world = src.rank, src.world
+    os.makedirs(os.path.join(sdir, "programs"), exist_ok=True)
+    save_program(trainer.program, os.path.join(sdir, "programs", f"rank{rank}.json"))
+    if world == 1:
+        compose_checkpoint([src], sdir, step=step, seed=seed, logical_objects=src.logical_objects(),
+                           scheme={"world": 1, **dict(scheme or {})}, client_payload=client_payload, summary=summary,
+                           launch=launch)
+    else:
+        import torch.distributed as dist
+        manifest = src.start_snapshot(os.path.join(sdir, f"rank{rank}"),
+                                      [{"id": s.object_id, "offset": s.offset, "size": s.size} for s in src.slices()],
+                                      {"step": step, "source": src.name})
+        mine = {"name": src.name, "slices": [vars(s) for s in src.slices()], "resident": src.resident_objects(),
+                "hashes": {f"{e['as']}@{e['offset']}": e["hash"] for e in manifest["slices"]}, "spec": src.engine_spec(),
+                "logical": src.logical_objects()}
+        gathered: list[Any] = [None] * world
+        dist.all_gather_object(gathered, mine)
+        if rank == 0:
+            sources = [_Recorded(g) for g in gathered]
+            logical: dict[str, int] = {}
+            for g in gathered:
+                for k, v in g["logical"].items():
+                    logical[k] = max(logical.get(k, 0), int(v))
+            compose_checkpoint(sources, sdir, step=step, seed=seed, logical_objects=logical,
+                               scheme={"world": world, "zero": trainer.zero, **dict(scheme or {})},
+                               client_payload=client_payload, summary=summary, launch=launch)
+        dist.barrier()
+    if keep_last and rank == 0:
+        for _, old in list_checkpoints(root)[:-int(keep_last)]:
+            shutil.rmtree(old, ignore_errors=True)
+    return sdir
+
+
+class _Recorded:
+    """A rank whose snapshot is already on disk (its facts were gathered to the composing rank)."""
+
+    def __init__(self, g: Mapping[str, Any]):
+        self.g = g
+        self.name = g["name"]
+
+    def slices(self):
+        return [SourceSlice(**s) for s in self.g["slices"]]
+
+    def resident_objects(self):
+        return dict(self.g["resident"])
+
+    def start_snapshot(self, dest, slices, client_meta):
+        return None
+
+    def wait_snapshot(self, handle, timeout):
+        return {"slices": [{"as": k.rsplit("@", 1)[0], "offset": int(k.rsplit("@", 1)[1]), "hash": h}
+                           for k, h in self.g["hashes"].items()]}
+
+    def engine_spec(self):
+        return dict(self.g["spec"])
+
+
+def load_checkpoint(trainer, sdir: str) -> dict:
+    """Fill the trainer's host store from a step directory; returns the record (``client_payload`` has the
+    caller's resume state).  Device-resident copies are dropped so the next step reloads from the store."""
+    import ctypes
+    rec = read_record(sdir)
+    src = TrainerSource(trainer)
+    want: dict[str, SourceSlice] = {s.object_id: s for s in src.slices()}
+    store = trainer.store
+    for oid, s in want.items():
+        logical = s.logical_id
+        if logical not in rec["logical_objects"]:
+            raise KeyError(f"checkpoint {sdir} has no object {logical!r} (needed for {oid!r} of rank {src.rank})")
+        lo, hi = s.logical_offset, s.logical_offset + s.size
+        filled = 0
+        spans: dict[tuple[int, int], dict] = {}
+        for e in rec["slices"][logical]:
+            key = (int(e["object_range"][0]), int(e["object_range"][1]))
+            if key not in spans or int(e["snapshot"]) < int(spans[key]["snapshot"]):
+                spans[key] = e
+        for (a, b), e in sorted(spans.items()):
+            if b <= lo or a >= hi:
+                continue
+            snap = rec["snapshots"][int(e["snapshot"])]
+            manifest = read_manifest(os.path.join(sdir, snap["path"]))
+            local = e.get("snapshot_object", logical)
+            ent = next(m for m in manifest["slices"] if m["as"] == local and int(m["offset"]) == int(e["snapshot_range"][0]))
+            data = read_snapshot_slice(os.path.join(sdir, snap["path"]), ent)
+            ca, cb = max(a, lo), min(b, hi)
+            dst = store.buffer(oid).ptr + s.offset + (ca - lo)
+            ctypes.memmove(dst, data[ca - a:cb - a], cb - ca)
+            filled += cb - ca
+        if filled != s.size:
+            raise ValueError(f"{oid}: checkpoint covers {filled} of the {s.size} bytes this rank needs")
+    trainer.session.drop_resident()
+    trainer.step_index = int(rec["step"])
+    return rec
+
+
+def peek(sdir: str) -> dict:
+    """Display facts of a checkpoint without touching its payload."""
+    rec = read_record(sdir)
+    return {"step": rec["step"], "seed": rec["seed"], "scheme": rec["scheme"], "summary": rec.get("summary"),
+            "objects": len(rec["logical_objects"]), "bytes": sum(int(v["bytes"]) for v in rec["logical_objects"].values()),
+            "snapshots": [s["path"] for s in rec["snapshots"]], "launch": (rec.get("launch") or {}).get("argv")}

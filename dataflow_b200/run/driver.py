@@ -165,7 +165,8 @@ class Trainer:
             store_bytes = sum(sizes.values())
             transient_backing = max(planned.peak_backing_bytes - store_bytes, 0) + (64 << 20)
             fast = planned.object_capacity or (planned.peak_fast_bytes + (256 << 20))
-            self.session.native.ensure_pools(int(min(fast, planned.peak_fast_bytes + (512 << 20))), int(transient_backing), 0.0)
+            # the whole object share of the budget: the room above the planned peak absorbs slab fragmentation
+            self.session.native.ensure_pools(int(fast), int(transient_backing), 0.0)
         self.step_index = 0
         self.last_result = None
         self.zero = (self.program.metadata or {}).get("zero")

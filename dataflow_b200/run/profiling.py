@@ -43,11 +43,21 @@ def _cache_path(key: str) -> Path:
     return root / f"{key}.json"
 
 
+def _ops_build_id() -> str:
+    """Digest of the compiled kernel library (and the GEMM path override): new kernels, new measurements."""
+    import glob
+    h = hashlib.sha256(os.environ.get("DFB_GEMM_PATH", "").encode())
+    for f in sorted(glob.glob(str(Path(__file__).resolve().parent.parent / "ops" / "_ops*.so"))):
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
 def profile_key(trainer, cfg) -> str:
     import torch
     desc = {"rev": PROFILE_CACHE_REV, "cfg": {k: (v if isinstance(v, (int, float, str, bool, type(None))) else str(v))
                                               for k, v in dataclasses.asdict(cfg).items() if k not in ("n_layers", "grad_accum_rounds", "name")},
-            "kernels": trainer.K.describe(), "torch": torch.__version__,
+            "kernels": trainer.K.describe(), "kernel_build": _ops_build_id(), "torch": torch.__version__,
             "device": torch.cuda.get_device_name(trainer.device) if trainer.device is not None else "cpu"}
     return hashlib.sha256(json.dumps(desc, sort_keys=True).encode()).hexdigest()[:20]
 

@@ -41,29 +41,52 @@ def resolve_slices(store, spec) -> list[dict]:
     return out
 
 
+def write_snapshot(dest, slices: list[dict], view_of, client_meta=None, progress=None) -> dict:
+    """Write ``slices`` (concrete: id / offset / size / as) of the objects ``view_of(id) -> memoryview`` into
+    ``dest`` as chunk files plus the manifest (written last).  Usable without a daemon."""
+    dest = Path(dest)
+    dest.mkdir(parents=True, exist_ok=True)
+    entries = []
+    for i, s in enumerate(slices):
+        view = view_of(s["id"])[s["offset"]:s["offset"] + s["size"]]
+        files = []
+        for c, off in enumerate(range(0, max(s["size"], 1), CHUNK_BYTES)):
+            name = f"slice{i:05d}_{c:04d}.bin"
+            with open(dest / name, "wb") as f:
+                f.write(view[off:off + CHUNK_BYTES])
+            files.append(name)
+            if progress is not None:
+                progress(len(view[off:off + CHUNK_BYTES]))
+        entries.append({**s, "files": files, "hash": slice_hash(view)})
+    manifest = {"schema": SNAPSHOT_SCHEMA, "created": time.time(), "slices": entries,
+                "client_meta": dict(client_meta or {}), "total_bytes": sum(s["size"] for s in slices)}
+    tmp = dest / (MANIFEST + ".tmp")
+    tmp.write_text(json.dumps(manifest, indent=1))
+    os.replace(tmp, dest / MANIFEST)                 # the manifest lands last: it is the completeness marker
+    return manifest
+
+
+def read_snapshot_slice(path, entry: dict) -> bytes:
+    """Bytes of one manifest entry, hash-verified."""
+    buf = bytearray()
+    for name in entry["files"]:
+        with open(Path(path) / name, "rb") as f:
+            buf += f.read()
+    buf = bytes(buf[:entry["size"]])
+    if slice_hash(memoryview(buf)) != entry["hash"]:
+        raise ServiceError("VERIFY_FAILED", f"slice of {entry['as']!r} in {path} does not match its recorded hash")
+    return buf
+
+
 def snapshot_job(server, job: dict) -> None:
     st = server.store
-    dest = Path(job["dest"])
     ids = sorted({s["id"] for s in job["slices"]})
     try:
-        dest.mkdir(parents=True, exist_ok=True)
-        entries = []
-        for i, s in enumerate(job["slices"]):
-            view = st.view(s["id"])[s["offset"]:s["offset"] + s["size"]]
-            files = []
-            for c, off in enumerate(range(0, max(s["size"], 1), CHUNK_BYTES)):
-                name = f"slice{i:05d}_{c:04d}.bin"
-                with open(dest / name, "wb") as f:
-                    f.write(view[off:off + CHUNK_BYTES])
-                files.append(name)
-                job["bytes_done"] += len(view[off:off + CHUNK_BYTES])
-            entries.append({**s, "files": files, "hash": slice_hash(view)})
-        manifest = {"schema": SNAPSHOT_SCHEMA, "created": time.time(), "slices": entries,
-                    "client_meta": job.get("client_meta", {}), "total_bytes": sum(s["size"] for s in job["slices"])}
-        tmp = dest / (MANIFEST + ".tmp")
-        tmp.write_text(json.dumps(manifest, indent=1))
-        os.replace(tmp, dest / MANIFEST)             # the manifest lands last: it is the completeness marker
-        job.update(state="done", hashes={e["as"] + f"@{e['offset']}": e["hash"] for e in entries}, manifest=manifest)
+        def progress(n):
+            job["bytes_done"] += n
+        manifest = write_snapshot(job["dest"], job["slices"], st.view, job.get("client_meta", {}), progress)
+        job.update(state="done", hashes={e["as"] + f"@{e['offset']}": e["hash"] for e in manifest["slices"]},
+                   manifest=manifest)
     except Exception as e:          # noqa: BLE001
         job.update(state="failed", message=f"{type(e).__name__}: {e}")
     finally:
