@@ -1,0 +1,106 @@
+"""``run(...)``: from a run specification to a finished ``RunResult``.
+
+World size 1 runs in this process.  Larger worlds launch one process per GPU on this node through
+``torch.distributed.run`` (rendezvous on 127.0.0.1) with ``dataflow_b200.run.rank_main`` as the entry; rank 0
+writes the result file this function returns.  A run that checkpoints takes an exclusive ``flock`` on its
+checkpoint directory for its whole lifetime, so two runs can never interleave step directories.
+Role parity: reference ``src/dataflow_training/run/conductor.py:146-452`` (there: daemons + a conductor; here the
+ranks are the processes themselves).
+"""
+from __future__ import annotations
+
+import dataclasses
+import fcntl
+import json
+import os
+import socket
+import subprocess
+import sys
+import tempfile
+from typing import Any, Mapping
+
+from .driver import RunResult
+
+
+@dataclasses.dataclass
+class RunSpec:
+    preset: str
+    steps: int
+    overrides: dict[str, Any] = dataclasses.field(default_factory=dict)        # config fields (seq_len, batch, ...)
+    recipe: dict[str, Any] = dataclasses.field(default_factory=dict)
+    data: str | None = None
+    packing_policy: str = "ffd"
+    allow_round_split: bool = False
+    capture: str | None = None
+    budget_gib: float | None = None
+    device: int | None = 0                  # None = CPU backend
+    world: int = 1
+    parallel: str = "zero3"                 # zero3 | zero1 (world > 1)
+    seed: int = 0
+    profile: bool = False
+    recompute: bool = True
+    kernels: str | None = None
+    resident_params: bool = True
+    checkpoint_every: int = 0
+    checkpoint_dir: str | None = None
+    checkpoint_keep_last: int | None = None
+    resume: str | None = None
+    out: str | None = None
+    argv: list[str] = dataclasses.field(default_factory=list)
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self))
+
+    @staticmethod
+    def from_json(s: str) -> "RunSpec":
+        return RunSpec(**json.loads(s))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class RunLock:
+    def __init__(self, directory: str | None):
+        self.path = os.path.join(directory, ".run.lock") if directory else None
+        self.f = None
+
+    def __enter__(self):
+        if self.path:
+            os.makedirs(os.path.dirname(self.path), exist_ok=True)
+            self.f = open(self.path, "w")
+            try:
+                fcntl.flock(self.f, fcntl.LOCK_EX | fcntl.LOCK_NB)
+            except BlockingIOError:
+                self.f.close()
+                raise RuntimeError(f"another run holds {self.path}: two runs must not share a checkpoint directory") from None
+            self.f.write(str(os.getpid()))
+            self.f.flush()
+        return self
+
+    def __exit__(self, *exc):
+        if self.f:
+            fcntl.flock(self.f, fcntl.LOCK_UN)
+            self.f.close()
+
+
+def run(spec: RunSpec, log=print) -> RunResult:
+    with RunLock(spec.checkpoint_dir if spec.checkpoint_every else None):
+        if spec.world <= 1:
+            from .rank_main import run_rank
+            return run_rank(spec, log=log)
+        out = spec.out or os.path.join(tempfile.mkdtemp(prefix="dataflow_run_"), "result.json")
+        spec = dataclasses.replace(spec, out=out)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={spec.world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               "-m", "dataflow_b200.run.rank_main", "--spec", spec.to_json()]
+        env = dict(os.environ)
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+        proc = subprocess.run(cmd, env=env)
+        if proc.returncode != 0:
+            raise RuntimeError(f"the {spec.world}-rank job exited with code {proc.returncode}")
+        d = json.loads(open(out).read())
+        return RunResult(d["losses"], d["step_wall_s"], d["tokens_per_step"], d["meta"])

@@ -1,0 +1,101 @@
+"""What one rank of a training job does: resolve the config, build the trainer (plan, init or resume), run the
+loop, save the result (rank 0).  Entry of ``torch.distributed.run`` for multi-GPU jobs and called in-process for
+solo runs."""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import os
+import sys
+from typing import Any
+
+from .conductor import RunSpec
+from .driver import RunResult, Trainer
+
+
+def build_cfg(spec: RunSpec):
+    from .presets import resolve_preset
+    family, cfg = resolve_preset(spec.preset)
+    known = {f.name for f in dataclasses.fields(cfg)}
+    bad = set(spec.overrides) - known
+    if bad:
+        raise KeyError(f"preset {spec.preset!r} has no config fields {sorted(bad)}")
+    return family, dataclasses.replace(cfg, **spec.overrides)
+
+
+def run_rank(spec: RunSpec, log=print) -> RunResult:
+    from ..data.pipeline import pipeline_from_args
+    from .checkpointing import load_checkpoint, resolve_resume
+    from .loop import train_loop
+    from .recipe import Recipe
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1)) if spec.world > 1 else 1
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = None if spec.device is None else (local if world > 1 else spec.device)
+    groups: dict[str, Any] = {}
+    lower_kwargs: dict[str, Any] = {}
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        if device is None:
+            dist.init_process_group("gloo")
+        else:
+            torch.cuda.set_device(device)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", device))
+        from ..parallel.zero import make_dp_group, zero_lower_kwargs
+        groups = {"dp": make_dp_group(rank, world, device)}
+        lower_kwargs = zero_lower_kwargs(spec.parallel, rank, world)
+    elif spec.resident_params:
+        lower_kwargs = {"resident_params": True}
+    family, cfg = build_cfg(spec)
+    recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
+    say = log if rank == 0 else (lambda *a, **k: None)
+    tr = Trainer(family, cfg, budget_gib=spec.budget_gib, device=device, hyper=recipe.hyper(), seed=spec.seed,
+                 kernel_set=spec.kernels, recompute=spec.recompute, profile=spec.profile and device is not None,
+                 groups=groups, lower_kwargs=lower_kwargs or None)
+    say(f"plan: {tr.planned.policy}, predicted {tr.planned.makespan_us / 1e3:.1f} ms/step, peak fast "
+        f"{tr.planned.peak_fast_bytes / 2 ** 30:.2f} GiB, planned in {tr.plan_s:.1f} s")
+    # the job-wide pipeline: every rank packs all rounds of the step and keeps its own
+    wide = dataclasses.replace(cfg, grad_accum_rounds=cfg.grad_accum_rounds * world)
+    factory = pipeline_from_args(wide, spec.data, policy=spec.packing_policy, allow_round_split=spec.allow_round_split,
+                                 capture=spec.capture if rank == 0 else None)
+    start, cursor, losses = 0, None, []
+    sdir = resolve_resume(spec.resume, spec.checkpoint_dir)
+    if sdir:
+        rec = load_checkpoint(tr, sdir)
+        payload = rec.get("client_payload") or {}
+        start, cursor, losses = int(rec["step"]), payload.get("cursor"), list(payload.get("losses") or [])
+        say(f"resumed from {sdir} at step {start}")
+    launch = {"argv": spec.argv, "resolved": {"preset": spec.preset, "seed": spec.seed, "world": world,
+                                              "parallel": spec.parallel if world > 1 else "solo", **spec.overrides},
+              "data": factory.describe(), "env": _env_facts()}
+    try:
+        res = train_loop(tr, factory, spec.steps, cursor=cursor, start_step=start, losses=losses,
+                         checkpoint_every=spec.checkpoint_every, checkpoint_dir=spec.checkpoint_dir,
+                         keep_last=spec.checkpoint_keep_last, seed=spec.seed, launch=launch, log=say)
+    finally:
+        tr.close()
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+    res.meta["launch"] = launch
+    if spec.out and rank == 0:
+        res.save(spec.out)
+    return res
+
+
+def _env_facts() -> dict:
+    import torch
+    return {"torch": torch.__version__, "cuda": torch.version.cuda, "python": sys.version.split()[0]}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--spec", required=True)
+    a = ap.parse_args(argv)
+    run_rank(RunSpec.from_json(a.spec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

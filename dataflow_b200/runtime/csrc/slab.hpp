@@ -1,5 +1,5 @@
-// Offset allocator over one contiguous region: best-fit carve, immediate
-// coalescing of neighbours on free.  Used for the fast (device) slab, the pinned
+// Offset allocator over one contiguous region: exact-fit reuse, then size-segregated
+// first fit from both ends, immediate coalescing of neighbours on free.  Used for the fast (device) slab, the pinned
 // backing slab and the service store.  Role parity: reference
 // src/dataflow/runtime/slab.py:24-113 (best fit, 512-byte alignment, coalescing).
 #pragma once
@@ -22,18 +22,42 @@ class SlabAllocator {
 
   static size_t round_up(size_t n, size_t a) { return (n + a - 1) / a * a; }
 
-  // returns an offset or kNone
+  // returns an offset or kNone.  Exact-size holes are reused first (training chains allocate a handful of
+  // sizes over and over).  Otherwise large requests (>= capacity / 48) take the lowest-address hole that fits
+  // and small ones are carved from the END of the highest-address hole that fits, so the two size classes
+  // grow towards each other and a small object never splits a hole that a large one will need again.
   size_t allocate(size_t bytes) {
     size_t need = round_up(bytes ? bytes : 1, align_);
-    auto it = by_size_.lower_bound({need, 0});
-    if (it == by_size_.end()) return kNone;
-    size_t off = it->second, len = it->first;
+    auto exact = by_size_.lower_bound({need, 0});
+    if (exact == by_size_.end()) return kNone;
+    size_t off, len;
+    bool from_end = false;
+    if (exact->first == need) {
+      off = exact->second; len = exact->first;
+    } else if (need >= cap_ / 48) {
+      off = kNone; len = 0;
+      for (auto& kv : by_off_) {
+        if (kv.second >= need) { off = kv.first; len = kv.second; break; }
+      }
+      if (off == kNone) return kNone;
+    } else {
+      off = kNone; len = 0;
+      for (auto it = by_off_.rbegin(); it != by_off_.rend(); ++it) {
+        if (it->second >= need) { off = it->first; len = it->second; break; }
+      }
+      if (off == kNone) return kNone;
+      from_end = true;
+    }
     erase_free(off, len);
-    if (len > need) insert_free(off + need, len - need);
-    live_[off] = need;
+    size_t at = off;
+    if (len > need) {
+      if (from_end) { insert_free(off, len - need); at = off + len - need; }
+      else insert_free(off + need, len - need);
+    }
+    live_[at] = need;
     used_ += need;
     if (used_ > peak_) peak_ = used_;
-    return off;
+    return at;
   }
 
   // place at a fixed offset (static placement); false if any byte is taken

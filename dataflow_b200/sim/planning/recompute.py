@@ -78,32 +78,49 @@ def plan_with_recompute(program, fast_memory_capacity, build_variant: Callable[[
     if best is not None and best.makespan_us <= best.lower_bound_us * (1 + 1e-6):
         return price({}, full=True) or best
     L = len(layers)
-    for lv in levels:
-        c = price({l: lv for l in layers})
-        if better(c, best):
-            best = c
-    # how many layers at each level
-    for lv in levels:
-        for k in (L // 4, L // 2, (3 * L) // 4):
-            if evals >= max_evals or k <= 0 or k >= L:
-                continue
-            c = price({l: lv for l in spread(layers, k)})
-            if better(c, best):
-                best = c
-    # recompute only in the last round: its backward is where optimizer state streams in, so
-    # freeing that round's activations buys room to prefetch the state ahead of the optimizer tasks
     R = int((program.metadata or {}).get("grad_accum_rounds", 1))
+    # (a) recompute only in the last round(s): their backward is where optimizer state streams in, so freeing
+    #     those rounds' activations buys room to prefetch the state ahead of the optimizer tasks, while the
+    #     other rounds keep streaming activations over lanes that are otherwise idle
+    best_tail: dict = {}
     if R > 1:
-        base = dict(best.recompute_levels) if best is not None else {}
-        for lv in levels:
+        tail_best = None
+        for lv in reversed(levels):
             for nlast in (L, (3 * L) // 4, L // 2):
-                if evals >= max_evals + 8 or nlast <= 0:
-                    break
-                trial = dict(base)
-                trial.update({(R - 1, l): lv for l in spread(layers, nlast)})
+                if nlast <= 0:
+                    continue
+                trial = {(R - 1, l): lv for l in spread(layers, nlast)}
                 c = price(trial)
+                if better(c, tail_best):
+                    tail_best, best_tail = c, trial
                 if better(c, best):
                     best = c
+        if R > 2 and best_tail:
+            lv = next(iter(best_tail.values()))
+            trial = dict(best_tail)
+            trial.update({(R - 2, l): lv for l in spread(layers, L // 2)})
+            c = price(trial)
+            if better(c, best):
+                best = c
+    # (b) the same level in every round, for all layers and for spread subsets
+    uniform_best, best_uniform = None, {}
+    for lv in levels:
+        for k in (L, (3 * L) // 4, L // 2, L // 4):
+            if evals >= max_evals + 8 or k <= 0:
+                continue
+            trial = {l: lv for l in spread(layers, k)}
+            c = price(trial)
+            if better(c, uniform_best):
+                uniform_best, best_uniform = c, trial
+            if better(c, best):
+                best = c
+    # (c) both together
+    if best_tail and best_uniform and evals < max_evals + 12:
+        trial = dict(best_uniform)
+        trial.update(best_tail)
+        c = price(trial)
+        if better(c, best):
+            best = c
     if best is None:
         raise PlanningError("no recompute assignment fits the budget")
     # local refinement of the winning count

@@ -1,0 +1,204 @@
+#!/usr/bin/env python
+"""The training tool.
+
+    train.py train     --preset llama3_8b --steps 100 --fast-budget 60 [--gpus 8] [--data SPEC] [--checkpoint-every N ...]
+    train.py reference --preset tiny --steps 20          # the pure-torch twin on the same data (CPU, fp32)
+    train.py smoke     [--preset tiny] [--device cpu]    # a few steps end to end, asserts a healthy curve
+    train.py parity    --preset tiny --steps 8           # engine vs twin from identical init and data
+    train.py scaling   --preset l3_125m --gpus 1,2,4     # tokens/s per world size + fit
+    train.py peek      CHECKPOINT_DIR                    # what a checkpoint holds
+    train.py compare   A.json B.json [--band bf16]       # two saved curves
+
+Role parity: reference ``tools/train/train.py:112-457`` (same subcommands and flag vocabulary; ``--gpus`` replaces
+the topology / group flags because ranks here are processes of one node, one per GPU).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def add_run_flags(ap: argparse.ArgumentParser) -> None:
+    ap.add_argument("--preset", default="llama3:tiny", help="preset name or family:preset")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--peak-lr", type=float, default=3e-4)
+    ap.add_argument("--min-lr", type=float, default=None)
+    ap.add_argument("--warmup-steps", type=int, default=0)
+    ap.add_argument("--muon-lr", type=float, default=None)
+    ap.add_argument("--opt", default=None, help="adamw | muon | sgd | sgdm")
+    ap.add_argument("--ga-rounds", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--max-seq-len", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--dtype-policy", default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--fast-budget", type=float, default=None, help="device memory budget in GiB")
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--device", default="0", help="CUDA ordinal, or 'cpu'")
+    ap.add_argument("--opt-shard", default="zero3", choices=["zero3", "zero1", "zero1rs"])
+    ap.add_argument("--kernels", default=None, help="kernel lane: sm100 | baseline | eager")
+    ap.add_argument("--profile", action="store_true", help="plan from measured task costs")
+    ap.add_argument("--no-recompute", action="store_true")
+    ap.add_argument("--no-resident-params", action="store_true")
+    ap.add_argument("--checkpoint-every", type=int, default=0)
+    ap.add_argument("--checkpoint-dir", default=None)
+    ap.add_argument("--checkpoint-keep-last", type=int, default=None)
+    ap.add_argument("--resume", default=None, help="step directory, checkpoint root, or 'latest'")
+    ap.add_argument("--data", default=None, help="scheme:main[,k=v...] (synthetic | shards | jsonl | txt | parquet | capture)")
+    ap.add_argument("--packing-policy", default="ffd", choices=["ffd", "greedy"])
+    ap.add_argument("--allow-round-split", action="store_true")
+    ap.add_argument("--capture", default=None)
+    ap.add_argument("--out", default=None, help="write the run curve JSON here")
+
+
+def spec_from_args(a, argv):
+    from dataflow_b200.run.conductor import RunSpec
+    ov = {}
+    for flag, fieldname in (("ga_rounds", "grad_accum_rounds"), ("batch", "batch"), ("max_seq_len", "seq_len"),
+                            ("layers", "n_layers"), ("dtype_policy", "dtype_policy"), ("opt", "optimizer")):
+        v = getattr(a, flag)
+        if v is not None:
+            ov[fieldname] = v
+    recipe = {"peak_lr": a.peak_lr, "min_lr": a.min_lr if a.min_lr is not None else a.peak_lr * 0.1,
+              "warmup_steps": a.warmup_steps}
+    if a.muon_lr is not None:
+        recipe["muon_lr"] = a.muon_lr
+    if a.opt:
+        recipe["optimizer"] = a.opt
+    return RunSpec(preset=a.preset, steps=a.steps, overrides=ov, recipe=recipe, data=a.data, packing_policy=a.packing_policy,
+                   allow_round_split=a.allow_round_split, capture=a.capture, budget_gib=a.fast_budget,
+                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel=a.opt_shard, seed=a.seed,
+                   profile=a.profile, recompute=not a.no_recompute, kernels=a.kernels,
+                   resident_params=not a.no_resident_params, checkpoint_every=a.checkpoint_every,
+                   checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, resume=a.resume, out=a.out,
+                   argv=list(argv))
+
+
+def cmd_train(a, argv) -> int:
+    from dataflow_b200.run.conductor import run
+    res = run(spec_from_args(a, argv))
+    print(f"done: {len(res.losses)} steps, last loss {res.losses[-1]:.4f}, {res.tokens_per_s:,.0f} tok/s" if res.losses else "no steps ran")
+    return 0
+
+
+def _twin_setup(a, argv):
+    import dataclasses
+    from dataflow_b200.data.pipeline import pipeline_from_args
+    from dataflow_b200.run.rank_main import build_cfg
+    from dataflow_b200.run.recipe import Recipe
+    spec = spec_from_args(a, argv)
+    family, cfg = build_cfg(spec)
+    recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
+    factory = pipeline_from_args(cfg, spec.data, policy=spec.packing_policy, allow_round_split=spec.allow_round_split)
+    return spec, family, cfg, recipe, factory
+
+
+def cmd_reference(a, argv) -> int:
+    from dataflow_b200.run.driver import Trainer
+    from dataflow_b200.run.loop import reference_loop
+    spec, family, cfg, recipe, factory = _twin_setup(a, argv)
+    # identical init: build the engine's initial values on the CPU store and bridge them into the twin
+    tr = Trainer(family, cfg, budget_gib=None, device=None, hyper=recipe.hyper(), seed=spec.seed, recompute=False)
+    try:
+        res = reference_loop(family, cfg, factory, spec.steps, recipe.hyper(), seed=spec.seed, views_of=tr.views_of)
+    finally:
+        tr.close()
+    if a.out:
+        res.save(a.out)
+    return 0
+
+
+def cmd_parity(a, argv) -> int:
+    from dataflow_b200.run.driver import Trainer
+    from dataflow_b200.run.loop import reference_loop, train_loop
+    from dataflow_b200.run.parity import Band, compare
+    spec, family, cfg, recipe, factory = _twin_setup(a, argv)
+    tr = Trainer(family, cfg, budget_gib=spec.budget_gib, device=spec.device, hyper=recipe.hyper(), seed=spec.seed,
+                 kernel_set=spec.kernels, lower_kwargs={"resident_params": True} if spec.resident_params else None)
+    try:
+        ref = reference_loop(family, cfg, factory, spec.steps, recipe.hyper(), seed=spec.seed, views_of=tr.views_of, log=None)
+        eng = train_loop(tr, factory, spec.steps, log=None)
+    finally:
+        tr.close()
+    band = Band.named(a.band or ("fp32" if str(getattr(cfg, "dtype_policy", "")) == "fp32" else "bf16"))
+    cmp_ = compare(eng.losses, ref.losses, band)
+    for i, (x, y) in enumerate(zip(eng.losses, ref.losses), 1):
+        print(f"step {i:4d}  engine {x:.5f}  twin {y:.5f}  rel {abs(x - y) / max(abs(y), 1e-30):.2e}")
+    print("PARITY OK" if cmp_ else f"PARITY FAILED at steps {[m[0] for m in cmp_.mismatches]}", f"(worst rel {cmp_.worst_rel:.2e})")
+    return 0 if cmp_ else 1
+
+
+def cmd_smoke(a, argv) -> int:
+    from dataflow_b200.run.conductor import run
+    from dataflow_b200.run.parity import curves_healthy
+    a.steps = a.steps or 6
+    a.peak_lr = max(a.peak_lr, 2e-3)
+    if a.data is None:
+        a.data = "synthetic:vocab=64,mean_len=48,seed=0"          # small id range: learnable in a few steps
+    res = run(spec_from_args(a, argv))
+    ok = curves_healthy(res.losses)
+    print("SMOKE OK" if ok else f"SMOKE FAILED: {res.losses}")
+    return 0 if ok else 1
+
+
+def cmd_scaling(a, argv) -> int:
+    import dataclasses
+    from dataflow_b200.run.conductor import run
+    from dataflow_b200.run.scaling import fit_scaling
+    pts, per_gpu = [], 0
+    for n in [int(x) for x in str(a.gpu_list).split(",")]:
+        spec = dataclasses.replace(spec_from_args(a, argv), world=n)
+        res = run(spec)
+        skip = min(2, max(len(res.step_wall_s) - 1, 0))
+        t = sum(res.step_wall_s[skip:]) / max(len(res.step_wall_s) - skip, 1)
+        pts.append((n, res.tokens_per_step / t))
+        per_gpu = res.tokens_per_step / n
+        print(f"{n} GPU: {pts[-1][1]:,.0f} tok/s")
+    fit = fit_scaling(pts, per_gpu)
+    print(json.dumps({"points": fit.points, "efficiency": fit.efficiency, "t_compute_ms": fit.t_compute_ms,
+                      "t_comm_ms": fit.t_comm_ms}, indent=1))
+    return 0
+
+
+def cmd_peek(a, argv) -> int:
+    from dataflow_b200.run.checkpointing import peek, resolve_resume
+    print(json.dumps(peek(resolve_resume(a.path)), indent=1, default=str))
+    return 0
+
+
+def cmd_compare(a, argv) -> int:
+    from dataflow_b200.run.parity import Band, compare
+    x, y = (json.load(open(p))["losses"] for p in (a.a, a.b))
+    c = compare(x, y, Band.named(a.band))
+    print(f"{'MATCH' if c else 'DIFFER'}: worst rel {c.worst_rel:.3e} at step {c.worst_step}; {len(c.mismatches)} outside band {a.band}")
+    return 0 if c else 1
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("train", "reference", "smoke", "parity", "scaling"):
+        p = sub.add_parser(name)
+        add_run_flags(p)
+        if name == "parity":
+            p.add_argument("--band", default=None, help="bitwise | fp32 | bf16 | loose")
+        if name == "scaling":
+            p.add_argument("--gpu-list", default="1,2", help="world sizes to run, comma separated")
+    p = sub.add_parser("peek")
+    p.add_argument("path")
+    p = sub.add_parser("compare")
+    p.add_argument("a")
+    p.add_argument("b")
+    p.add_argument("--band", default="bf16")
+    a = ap.parse_args(argv)
+    return {"train": cmd_train, "reference": cmd_reference, "smoke": cmd_smoke, "parity": cmd_parity,
+            "scaling": cmd_scaling, "peek": cmd_peek, "compare": cmd_compare}[a.cmd](a, argv)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
