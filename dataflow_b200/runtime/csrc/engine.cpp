@@ -18,6 +18,7 @@ BufferPool::~BufferPool() {
 }
 
 void BufferPool::ensure_slab(size_t capacity) {
+  capacity = SlabAllocator::round_up(capacity, SlabAllocator::kAlign);   // the slab's usable extent is aligned
   if (slab_ && slab_->capacity() >= capacity) return;
   if (slab_) {
     if (slab_->live_blocks()) return;   // cannot grow under live buffers; overflow handles the rest

@@ -16,8 +16,10 @@ class SlabAllocator {
   static constexpr size_t kAlign = 512;
   static constexpr size_t kNone = static_cast<size_t>(-1);
 
-  explicit SlabAllocator(size_t capacity = 0, size_t align = kAlign) : cap_(capacity), align_(align) {
-    if (capacity) insert_free(0, capacity);
+  // The usable extent is the capacity rounded down to the alignment, so every block edge (carved from
+  // either end of a hole) is aligned.
+  explicit SlabAllocator(size_t capacity = 0, size_t align = kAlign) : cap_(capacity / align * align), align_(align) {
+    if (cap_) insert_free(0, cap_);
   }
 
   static size_t round_up(size_t n, size_t a) { return (n + a - 1) / a * a; }

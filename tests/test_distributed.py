@@ -1,0 +1,121 @@
+"""Schemes, shard plans, responsibilities / source policy, topology, group annotation, and the daemon tools."""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+
+from dataflow_b200.distributed import (ParallelismScheme, SchemeError, annotate_groups, compile_source_policy, expert_shards,
+                                       load_topology, local_topology, responsibility_map, rs_eligible, scheme_from_flags,
+                                       tp_attn_shards, tp_mlp_shards, zero_slices)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_scheme_grid_and_validation():
+    s = scheme_from_flags(8, tp=4)                       # dp2 x tp4
+    assert [a.kind for a in s.axes] == ["dp", "tp"] and s.world == 8
+    assert s.coords(5) == {"dp": 1, "tp": 1}
+    assert s.group_members("tp", 5) == [4, 5, 6, 7] and s.group_members("dp", 5) == [1, 5]
+    assert ParallelismScheme.from_dict(s.to_dict()) == s
+    w = ParallelismScheme.data_parallel(rank_rounds=[6, 2], responsibility="zero1rs").validate(2)
+    assert w.rounds_of(0, 4) == 6 and w.rounds_of(1, 4) == 2
+    with pytest.raises(SchemeError, match="responsibility"):
+        ParallelismScheme.data_parallel(2, responsibility="zero9").validate()
+    with pytest.raises(SchemeError, match="covers 4 ranks"):
+        scheme_from_flags(4).validate(8)
+    with pytest.raises(SchemeError, match="does not divide"):
+        scheme_from_flags(6, tp=4)
+    with pytest.raises(SchemeError, match="tp and ep"):
+        scheme_from_flags(8, tp=2, ep=2)
+
+
+def test_tp_and_ep_shard_plans_cover_everything_once():
+    mlp = tp_mlp_shards(64, 256, 4)
+    assert mlp.equal_shards and mlp.local_shape(1, "w13") == (64, 128) and mlp.local_shape(1, "w2") == (64, 64)
+    assert mlp.replicated("norm2")
+    attn = tp_attn_shards(4096, 32, 8, 128, 8)            # llama-3 geometry over 8 ranks: one KV head each
+    assert attn.local_shape(3, "w_qkv") == (4096, (4 + 2) * 128) and attn.local_shape(3, "wo") == (512, 4096)
+    with pytest.raises(ValueError, match="GQA groups"):
+        tp_attn_shards(4096, 32, 8, 128, 16)
+    ep = expert_shards(64, 8, {"w13": (2048, 2048), "w2": (1024, 2048)})
+    assert ep.equal_shards and ep.owned_ranges(2, "w2")[0].row_lo == 16 * 1024
+
+
+def test_zero_slices_and_eligibility():
+    sl = zero_slices(1000, 4)
+    assert sl == [(0, 256), (256, 256), (512, 256), (768, 232)] and sum(n for _, n in sl) == 1000
+    assert zero_slices(300, 4)[2:] == [(300, 0), (300, 0)]
+    assert rs_eligible(["bf16"], ["bf16"], ["adamw"]) and not rs_eligible(["bf16"], ["fp32"], ["adamw"])
+    assert not rs_eligible(["bf16"], ["bf16"], ["adamw", "muon"])
+
+
+def test_responsibilities_and_source_policy():
+    objs = {"W_0": 1000, "O_0": 3000, "Aux_0": 64}
+    z3 = responsibility_map(objs, scheme_from_flags(4, opt_shard="zero3"))
+    assert [(s.lo, s.hi) for s in z3["W_0"]] == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    z1 = responsibility_map(objs, scheme_from_flags(4, opt_shard="zero1rs"))
+    assert all(s.lo == 0 and s.hi == 1000 for s in z1["W_0"]) and len(z1["O_0"]) == 4 and z1["O_0"][1].lo == 768
+    logical, writes = compile_source_policy("dedup", z1, private=["Aux_0"])
+    assert logical == {"W_0": 1000, "O_0": 3000, "Aux_0@0": 64, "Aux_0@1": 64, "Aux_0@2": 64, "Aux_0@3": 64}
+    assert [w.source for w in writes if w.logical_id == "W_0"] == [0]
+    _, simple = compile_source_policy("simple", z1)
+    assert len([w for w in simple if w.logical_id == "W_0"]) == 4
+    # dp2 x tp2: the dp slice is replicated across the tp pair; dedup keeps one writer per slice
+    mesh = responsibility_map({"O_0": 1024}, scheme_from_flags(4, tp=2, opt_shard="zero1rs"))
+    _, w = compile_source_policy("dedup", mesh)
+    assert sorted((x.source, x.lo) for x in w) == [(0, 0), (2, 512)]
+
+
+def test_topology_toml_and_local(tmp_path):
+    p = tmp_path / "topo.toml"
+    p.write_text('[hosts.box]\ndevices = [0, 1]\nbacking_gib = 32\n[hosts.far]\naddress = "me@far"\ndevices = [0]\n'
+                 '[groups.train]\nmembers = ["box:0", "box:1", "far:0"]\n')
+    t = load_topology(str(p))
+    g = t.group()
+    assert g.world == 3 and g.coordinator.key == "box:0" and t.host_of(g.members[2]).address == "me@far"
+    assert t.hosts["box"].local and not t.hosts["far"].local
+    p.write_text('[hosts.box]\ndevices = [0]\n[groups.g]\nmembers = ["box:1"]\n')
+    with pytest.raises(ValueError, match="no device 1"):
+        load_topology(str(p))
+    assert local_topology(4).group().world == 4
+
+
+def test_group_annotation_stamps_communicating_tasks():
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    fam = resolve_family("llama3")
+    prog = fam.lower(fam.presets["tiny"]())
+    s = scheme_from_flags(4, tp=2)
+    out = annotate_groups(prog, s, rank=3, group_names={"tp": "tp_group_1"})
+    opt = next(t for t in out.tasks if (t.compute_block_key or "").startswith("optimizer_block"))
+    assert opt.comm_groups == {"dp": "dp", "tp": "tp_group_1"} and opt.block_params["axes"]["tp"]["rank"] == 1
+    blk = next(t for t in out.tasks if "fwd" in t.id and "block" in t.id)
+    assert blk.compute_block_key.startswith("tp_")
+    assert out.metadata["scheme"]["world"] == 4
+    assert annotate_groups(prog, ParallelismScheme.solo(), 0) is prog
+
+
+def test_daemon_start_status_stop(tmp_path):
+    sock = str(tmp_path / "d.sock")
+    tool = os.path.join(ROOT, "tools/train/dataflowd.py")
+    env = {**os.environ, "PYTHONPATH": ROOT}
+    assert subprocess.call([sys.executable, tool, "start", "--socket", sock, "--fake", "--backing-gib", "0.05"], env=env) == 0
+    try:
+        for _ in range(150):
+            if subprocess.call([sys.executable, tool, "status", "--socket", sock], env=env, stdout=subprocess.DEVNULL,
+                               stderr=subprocess.DEVNULL) == 0:
+                break
+            time.sleep(0.2)
+        else:
+            pytest.fail("daemon did not come up: " + open(sock[:-5] + ".log").read()[-2000:])
+        assert subprocess.call([sys.executable, tool, "stop", "--socket", sock], env=env) == 0
+        for _ in range(100):
+            if not os.path.exists(sock):
+                break
+            time.sleep(0.1)
+        assert not os.path.exists(sock)
+    finally:
+        subprocess.call([sys.executable, os.path.join(ROOT, "tools/train/daemonize.py"), "--pidfile", sock[:-5] + ".pid", "--kill"],
+                        stderr=subprocess.DEVNULL)
