@@ -44,7 +44,7 @@ def parse_args(argv=None):
     ap.add_argument("--layers", type=int, default=None, help="debug only: cut the model (the result is not a valid bench)")
     ap.add_argument("--kernels", default=None, help="kernel lane override (e.g. baseline)")
     ap.add_argument("--no-profile", action="store_true", help="plan from roofline seeds instead of measured task costs")
-    ap.add_argument("--parallel", default=None, help="zero3 | zero1 | co (default: zero3 when --gpus > 1)")
+    ap.add_argument("--parallel", default=None, help="fsdp | zero3 | zero1 (default: fsdp when --gpus > 1)")
     return ap.parse_args(argv)
 
 
@@ -116,14 +116,16 @@ def bench_ours(a) -> dict:
     if a.layers:
         cfg = dataclasses.replace(cfg, n_layers=a.layers)
     budget = a.budget_gib if a.budget_gib is not None else PRESET_BUDGET_GIB.get(a.preset, 60.0)
-    parallel = a.parallel or ("zero3" if world > 1 else "solo")
+    parallel = a.parallel or ("fsdp" if world > 1 else "solo")
     groups, lower_kwargs = {}, {"resident_params": True}      # weights stay on the device from step to step
     if world > 1:
         from dataflow_b200.parallel.zero import make_dp_group, zero_lower_kwargs
         groups = {"dp": make_dp_group(rank, world, local)}
         lower_kwargs = zero_lower_kwargs(parallel, rank, world)
     hyper = {"lr": 3e-4, "weight_decay": 0.1, "beta1": 0.9, "beta2": 0.95}
-    tr = Trainer(a.family, cfg, budget_gib=budget, device=local, hyper=hyper, seed=0, kernel_set=a.kernels,
+    from dataflow_b200.lowering import resolve_hardware
+    hw = resolve_hardware(None).shared(world)        # all ranks of the node stream through one host memory
+    tr = Trainer(a.family, cfg, budget_gib=budget, device=local, hyper=hyper, seed=0, kernel_set=a.kernels, hw=hw,
                  profile=not a.no_profile, groups=groups, lower_kwargs=lower_kwargs)
     tokens_step = tr.T * tr.rounds
     vocab = cfg.vocab_size

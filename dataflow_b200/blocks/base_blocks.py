@@ -34,6 +34,14 @@ class _Base:
         import torch
         from ..runtime.interop import external_stream
         with torch.cuda.stream(external_stream(ctx.stream, self.device)):
+            pending = ctx.run_values.get("_ready")
+            if pending:
+                # inputs produced on another stream (asynchronous gathers / reduce-scatters): wait on-stream
+                cur = torch.cuda.current_stream()
+                for b in ctx.inputs:
+                    ev = pending.pop(b.object_id, None)
+                    if ev is not None:
+                        cur.wait_event(ev)
             self.run(ctx)
 
     def run(self, ctx) -> None:      # pragma: no cover - abstract
@@ -221,9 +229,11 @@ class OptimizerStep(_Base):
 
 
 def common_executables(dims, layouts, kernels, device, hyper) -> dict[str, Any]:
-    from ..parallel.zero import ParamGather
+    from ..parallel.zero import CommJoin, GradReduceScatter, ParamGather
     return {
         "param_gather": ParamGather(dims, layouts, kernels, device, hyper),
+        "grad_rs": GradReduceScatter(dims, layouts, kernels, device, hyper),
+        "grad_rs_join": CommJoin(dims, layouts, kernels, device, hyper),
         "prologue_round": RoundPrologue(dims, layouts, kernels, device, hyper),
         "embed_fwd": EmbedFwd(dims, layouts, kernels, device, hyper),
         "embed_bwd": EmbedBwd(dims, layouts, kernels, device, hyper),

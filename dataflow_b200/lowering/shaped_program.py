@@ -36,6 +36,15 @@ class ShapedHardware:
     scale_up_gbs: float = 0.0          # per-direction NVLink bandwidth per GPU
     fast_gib: float = 80.0
     peak_tflops_fp8: float = 0.0
+    host_gbs: float = 0.0              # host-memory bandwidth per direction shared by all GPUs of a node (0 = unknown)
+
+    def shared(self, ranks_per_node: int) -> "ShapedHardware":
+        """The preset as one of ``ranks_per_node`` GPUs sees it: the copy lanes of all GPUs of a node end in the
+        same host memory, so each gets at most its share of the host bandwidth."""
+        if ranks_per_node <= 1 or not self.host_gbs:
+            return self
+        share = self.host_gbs / ranks_per_node
+        return replace(self, h2d_gbs=min(self.h2d_gbs, share), d2h_gbs=min(self.d2h_gbs, share))
 
     def matmul_us(self, flops: float, dtype: str = "bf16") -> float:
         peak = self.peak_tflops_fp8 if dtype.startswith("fp8") and self.peak_tflops_fp8 else self.peak_tflops
@@ -53,7 +62,7 @@ class ShapedHardware:
 
 
 HW_PRESETS: dict[str, ShapedHardware] = {
-    "b200": ShapedHardware("b200", 1669.0, 0.80, 0.45, 0.35, 6524.0, 0.90, 52.0, 52.0, 770.0, 180.0, 3300.0),
+    "b200": ShapedHardware("b200", 1669.0, 0.80, 0.45, 0.35, 6524.0, 0.90, 52.0, 52.0, 770.0, 180.0, 3300.0, 160.0),
     "h100": ShapedHardware("h100", 989.0, 0.72, 0.55, 0.45, 3350.0, 0.85, 52.0, 50.0, 450.0, 80.0, 1979.0),
     "rtx 5090": ShapedHardware("rtx 5090", 209.0, 0.90, 0.6, 0.5, 1792.0, 0.85, 25.0, 25.0, 0.0, 32.0),
     "rtx 3090": ShapedHardware("rtx 3090", 71.0, 0.85, 0.6, 0.5, 936.0, 0.85, 16.5, 18.7, 0.0, 24.0),
@@ -175,34 +184,49 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     zstage = int(zero.get("stage", 0)) if zero else 0
     zworld = int(zero.get("world", 1)) if zero else 1
     zfactor = float(zero.get("opt_bytes_per_param_byte", 6.0)) if zero else 0.0
+    # Re-gathering (FSDP) mode of stage 3: a block's full weights are gathered in front of EVERY use and freed after
+    # it, and every backward's gradient is reduce-scattered straight into this rank's fp32 slice, so neither full
+    # weights nor full gradients stay resident; the optimizer then runs locally on the slice.  NVLink carries
+    # 2 x rounds gathers + rounds reduce-scatters per layer instead of PCIe carrying evicted weights.
+    regather = bool(zero.get("regather")) if zero else False
+    # With ``comm_async`` the re-gathers and reduce-scatters run on the group's communication stream: a gather is
+    # issued one layer ahead of its consumer (which waits for it on-stream), a reduce-scatter is joined one layer
+    # later (``grad_rs_join``), so NVLink traffic overlaps the neighbouring layer's compute.
+    comm_async = bool(zero.get("comm_async", True)) if zero else False
+    zfactor_blocks = float(zero.get("block_opt_bytes_per_param_byte", zfactor)) if zero else 0.0
 
     def zslice(nbytes: int) -> int:
         per = (nbytes + zworld - 1) // zworld
         return (per + 255) // 256 * 256
 
-    def zo(nbytes: int, solo_o: int) -> int:
-        return int(zslice(nbytes) * zfactor) if zstage else solo_o
+    def zo(nbytes: int, solo_o: int, block: bool = False) -> int:
+        return int(zslice(nbytes) * (zfactor_blocks if block and regather else zfactor)) if zstage else solo_o
 
     if zstage:
         bp["shard"] = {"stage": zstage, "rank": int(zero.get("rank", 0)), "world": zworld}
         cg.setdefault("dp", zero.get("group", "dp"))
     gathered: dict[str, int] = {}        # W object id -> full byte size (stage 3)
+    init: list[ObjectSpec] = []
+    resident_ids: set[str] = set()
 
     def param_objects(name: str, w_bytes: int, o_bytes: int) -> None:
         wid, oid = f"W_{name}", f"O_{name}"
+        is_block = name.isdigit()
         if zstage == 3:
-            init.append(ObjectSpec(f"Ws_{name}", zslice(w_bytes), "backing", "parameter", persistent=True))
+            # a re-gathered block keeps its slice on the device from step to step (it is small)
+            init.append(ObjectSpec(f"Ws_{name}", zslice(w_bytes), "fast" if regather and is_block and resident_params else "backing",
+                                   "parameter", persistent=True))
+            if regather and is_block and resident_params:
+                resident_ids.add(f"Ws_{name}")
             gathered[wid] = w_bytes
         else:
             init.append(ObjectSpec(wid, w_bytes, "fast" if resident_params else "backing", "parameter", persistent=True))
             if resident_params:
                 resident_ids.add(wid)
-        ob = zo(w_bytes, o_bytes)
+        ob = zo(w_bytes, o_bytes, is_block)
         if ob:
             init.append(ObjectSpec(oid, ob, "backing", "optimizer_state", persistent=True))
 
-    init: list[ObjectSpec] = []
-    resident_ids: set[str] = set()
     param_objects("embed", embed_w_bytes, embed_o_bytes)
     for i in range(L):
         k = kinds[layer_kinds[i]]
@@ -223,14 +247,18 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     last = R - 1
     opt_tasks_tail: list[TaskSpec] = []
 
-    def gather_task(wid: str, params) -> None:
-        """Stage 3: materialise the full weight object from the ranks' slices before its first use."""
+    def gather_task(wid: str, params, out_id: str | None = None, tag: str = "") -> None:
+        """Stage 3: materialise the full weight object from the ranks' slices before its first use (or, when
+        re-gathering, before this use: ``out_id`` names the temporary)."""
         if wid not in gathered:
             return
         nbytes = gathered[wid]
-        tasks.append(TaskSpec(f"param_gather_{s}_{wid[2:]}", inputs=("Ws_" + wid[2:],),
-                              outputs=(OutputSpec(wid, nbytes, "fast", "parameter"),),
-                              runtime_us=hw.comm_us(nbytes * (zworld - 1) / zworld) + hw.mem_us(2 * nbytes) + 10.0,
+        us = hw.comm_us(nbytes * (zworld - 1) / zworld) + hw.mem_us(2 * nbytes) + 10.0
+        if tag and comm_async:
+            us = 15.0           # issued on the communication stream one layer ahead: only the launch is on the chain
+        tasks.append(TaskSpec(f"param_gather_{s}_{wid[2:]}{tag}", inputs=("Ws_" + wid[2:],),
+                              outputs=(OutputSpec(out_id or wid, nbytes, "fast", "parameter"),),
+                              runtime_us=us,
                               group="comm", compute_block_key="param_gather", block_params={**bp, **params},
                               comm_groups=cg, metadata=_meta(({"name": "all_gather", "memory_bytes": float(nbytes),
                                                                "efficiency": "scale_up"},))))
@@ -250,11 +278,27 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
     def place_opt(t: TaskSpec):
         (tasks if cfg.optimizer_placement == "interleaved" else opt_tasks_tail).append(t)
 
+    pending_join = None
+
+    def emit_join(i: int, dw: str, gacc: str, k) -> None:
+        """One layer after its reduce-scatter was issued: wait for it (the full gradient is freed here) and, in
+        the last round, step the optimizer on the slice."""
+        if comm_async:
+            tasks.append(TaskSpec(f"grad_rs_join_{s}_{cur_round[0]}_{i}", inputs=(dw, gacc), runtime_us=5.0, group="comm",
+                                  compute_block_key="grad_rs_join", block_params={**bp, "layer": i, "round": cur_round[0]},
+                                  comm_groups=cg))
+        if cur_round[0] == last:
+            t = opt_task(f"optimizer_{s}_{i}", "optimizer_block", f"W_{i}", gacc, f"O_{i}",
+                         k.opt_us, k.opt_subops, k.workspace_opt, {"step": s, "layer": i, "kind": k.kind, "local": True})
+            place_opt(replace(t, runtime_us=k.opt_us / zworld + 10.0))
+
+    cur_round = [0]
     sizes_of: dict[str, int] = {f"dW_embed_{s}": embed_dw_bytes, f"dW_head_{s}": head_dw_bytes}
     for i in range(L):
         sizes_of[f"dW_{s}_{i}"] = kinds[layer_kinds[i]].dw_bytes
     for r in range(R):
         create = r == 0
+        cur_round[0] = r
         if create:
             gather_task("W_embed", {"target": "embed"})
         tasks.append(TaskSpec(f"prologue_round_{s}_{r}", outputs=(OutputSpec(f"current_round_{s}_{r}", 4, "fast", "other"),),
@@ -276,9 +320,16 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                 outs.append(OutputSpec(f"A_{s}_{r}_{i}" if not lvl else f"Ap_{s}_{r}_{i}", ctx_bytes, "fast", "activation"))
             if k.aux_temp_bytes:
                 outs.append(OutputSpec(f"AuxTemp_{s}_{r}_{i}", k.aux_temp_bytes, "fast", "other"))
-            ins = (prev, f"W_{i}") + ((f"Aux_{i}",) if k.aux_bytes else ())
-            if create:
+            w_f = f"W_{i}"
+            if regather and zstage == 3:
+                w_f = f"Wg_{s}_{r}_{i}f"
+                ahead = [0, 1] if i == 0 else [i + 1]
+                for j in ahead:
+                    if j < L:
+                        gather_task(f"W_{j}", {"target": "block", "layer": j}, f"Wg_{s}_{r}_{j}f", f"_{r}f")
+            elif create:
                 gather_task(f"W_{i}", {"target": "block", "layer": i})
+            ins = (prev, w_f) + ((f"Aux_{i}",) if k.aux_bytes else ())
             tasks.append(TaskSpec(f"block_fwd_{s}_{r}_{i}", inputs=ins, outputs=tuple(outs),
                                   mutates=(f"Aux_{i}",) if k.aux_bytes else (),
                                   runtime_us=k.fwd_us, workspace_bytes=k.workspace_fwd, group="fwd",
@@ -293,6 +344,8 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                     f"{k.kind}_fwd", f"{k.kind}_recompute", f"layer{i}"))
             prev = f"y_{s}_{r}_{i}"
         # head + loss
+        if regather and zstage == 3 and L:
+            gather_task(f"W_{L - 1}", {"target": "block", "layer": L - 1}, f"Wg_{s}_{r}_{L - 1}b", f"_{r}b")
         if create:
             gather_task("W_head", {"target": "head"})
         head_in = [prev, f"targets_{s}_{r}", "W_head"] + (["W_embed"] if cfg.tied_embeddings else [])
@@ -330,22 +383,28 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
             dx = f"dy_{s}_{r}_{i - 1}" if i > 0 else f"dy_embed_{s}_{r}"
             a_obj = f"A_{s}_{r}_{i}"
             aux_t = (f"AuxTemp_{s}_{r}_{i}",) if k.aux_temp_bytes else ()
+            w_b = f"W_{i}"
+            fsdp_block = regather and zstage == 3 and k.dw_bytes
+            if regather and zstage == 3:
+                w_b = f"Wg_{s}_{r}_{i}b"
+                if i - 1 >= 0:
+                    gather_task(f"W_{i - 1}", {"target": "block", "layer": i - 1}, f"Wg_{s}_{r}_{i - 1}b", f"_{r}b")
             if lvl:
                 rus = next(us for (lv, _, us) in k.recompute_levels if lv == lvl)
                 saved = next(sb for (lv, sb, _) in k.recompute_levels if lv == lvl)
-                rin = (x_in, f"W_{i}") + ((f"Ap_{s}_{r}_{i}",) if saved else ()) + aux_t
+                rin = (x_in, w_b) + ((f"Ap_{s}_{r}_{i}",) if saved else ()) + aux_t
                 tasks.append(TaskSpec(f"block_recompute_{s}_{r}_{i}", inputs=rin,
                                       outputs=(OutputSpec(a_obj, k.ctx_bytes, "fast", "activation"),),
                                       runtime_us=rus, workspace_bytes=k.workspace_fwd, group="recompute",
                                       compute_block_key=f"{k.kind}_recompute",
                                       block_params={**bp, "layer": i, "round": r, "recompute_level": lvl},
                                       comm_groups=cg, metadata=_meta(k.recompute_subops)))
-            ins = [dy, a_obj, x_in, f"W_{i}"] + list(aux_t)
+            ins = [dy, a_obj, x_in, w_b] + list(aux_t)
             outs = [OutputSpec(dx, x_bytes, "fast", "activation")]
             mut: tuple[str, ...] = ()
-            dw = f"dW_{s}_{i}"
+            dw = f"dW_{s}_{r}_{i}" if fsdp_block else f"dW_{s}_{i}"
             if k.dw_bytes:
-                if create:
+                if create or fsdp_block:
                     outs.append(OutputSpec(dw, k.dw_bytes, "fast", "gradient"))
                 else:
                     ins.append(dw)
@@ -354,7 +413,24 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                                   runtime_us=k.bwd_us, workspace_bytes=k.workspace_bwd, group="bwd",
                                   compute_block_key=f"{k.kind}_bwd", block_params={**bp, "layer": i, "round": r},
                                   comm_groups=cg, metadata=_meta(k.bwd_subops)))
-            if r == last and k.dw_bytes:
+            if fsdp_block:
+                # reduce-scatter this round's gradient into the rank's fp32 slice; the full gradient dies at the join
+                gacc = f"G_{s}_{i}"
+                gbytes = 2 * zslice(k.dw_bytes)
+                rs_us = hw.comm_us(k.dw_bytes * (zworld - 1) / zworld) + hw.mem_us(k.dw_bytes + gbytes) + 10.0
+                tasks.append(TaskSpec(f"grad_rs_{s}_{r}_{i}", inputs=(dw,) + (() if create else (gacc,)),
+                                      outputs=(OutputSpec(gacc, gbytes, "fast", "gradient"),) if create else (),
+                                      mutates=() if create else (gacc,),
+                                      runtime_us=15.0 if comm_async else rs_us,
+                                      group="comm", compute_block_key="grad_rs",
+                                      block_params={**bp, "layer": i, "round": r, "target": "block", "first": create},
+                                      comm_groups=cg, metadata=_meta(({"name": "reduce_scatter", "memory_bytes": float(k.dw_bytes),
+                                                                       "efficiency": "scale_up"},))))
+                sizes_of[gacc] = gbytes
+                if pending_join is not None:
+                    emit_join(*pending_join)
+                pending_join = (i, dw, gacc, k)
+            elif r == last and k.dw_bytes:
                 place_opt(opt_task(f"optimizer_{s}_{i}", "optimizer_block", f"W_{i}", dw, f"O_{i}" if (k.o_bytes or zstage) else None,
                                    k.opt_us, k.opt_subops, k.workspace_opt, {"step": s, "layer": i, "kind": k.kind}))
         # embedding backward
@@ -369,6 +445,9 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
         tasks.append(TaskSpec(f"embed_bwd_{s}_{r}", inputs=tuple(ein), outputs=eout, mutates=emut,
                               runtime_us=loose.embed_bwd_us, group="bwd", compute_block_key="embed_bwd",
                               block_params={**bp, "round": r}))
+        if pending_join is not None:
+            emit_join(*pending_join)
+            pending_join = None
         if r == last:
             place_opt(opt_task(f"optimizer_embed_{s}", "optimizer_embed", "W_embed", tied_dw,
                                "O_embed" if (embed_o_bytes or zstage) else None,
@@ -376,7 +455,8 @@ def build_shaped_program(cfg: ShapedConfig, kinds: Mapping[str, LayerKindSpec], 
                                (), 0, {"step": s, "target": "embed"}))
     tasks.extend(opt_tasks_tail)
     if zstage:
-        metadata = {**dict(metadata or {}), "zero": {"stage": zstage, "world": zworld, "rank": int(zero.get("rank", 0))},
+        metadata = {**dict(metadata or {}), "zero": {"stage": zstage, "world": zworld, "rank": int(zero.get("rank", 0)),
+                                                     "regather": regather},
                     "zero_full_bytes": dict(gathered)}
     md = {"tokens_per_step": T * R, "tokens_per_round": T, "grad_accum_rounds": R, "n_layers": L,
           "hardware": hw.name, **dict(metadata or {})}

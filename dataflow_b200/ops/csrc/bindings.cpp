@@ -112,12 +112,13 @@ static void adamw_master(Tensor& master, Tensor& w_out, const Tensor& g, Tensor&
 }
 static void adamw_split(Tensor& w, Tensor& lo, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2,
                         double eps, double wd, int64_t step, double gscale) {
-  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16 && m.scalar_type() == at::kBFloat16 &&
-              v.scalar_type() == at::kBFloat16 && lo.element_size() == 2, "adamw_split: bf16 w/g/m/v and a 16-bit lo plane");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && (g.scalar_type() == at::kBFloat16 || g.scalar_type() == at::kFloat) &&
+              m.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 && lo.element_size() == 2,
+              "adamw_split: bf16 w/m/v, bf16 or fp32 g, and a 16-bit lo plane");
   TORCH_CHECK(lo.numel() == w.numel() && g.numel() == w.numel() && m.numel() == w.numel() && v.numel() == w.numel(),
               "adamw_split: size mismatch");
-  int rc = dfb::adamw_split(w.data_ptr(), lo.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), w.numel(), lr, b1, b2, eps,
-                            wd, (int)step, gscale, cur_stream());
+  int rc = dfb::adamw_split(w.data_ptr(), lo.data_ptr(), g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(), v.data_ptr(),
+                            w.numel(), lr, b1, b2, eps, wd, (int)step, gscale, cur_stream());
   TORCH_CHECK(rc == 0, "adamw_split: arrays must be 16-byte aligned (code ", rc, ")");
 }
 static void adamw_f32(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
@@ -202,6 +203,21 @@ static void zero_rs_adamw(std::vector<int64_t> slabs, std::vector<int64_t> ctrls
                               reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
   TORCH_CHECK(rc == 0, "zero_rs_adamw launch failed with code ", rc);
 }
+// Reduce-scatter + fp32 accumulate of one packed gradient object into this rank's slice (no optimizer step).
+static void zero_rs_accum(std::vector<int64_t> slabs, std::vector<int64_t> ctrls, int64_t rank, int64_t slots, int64_t slot,
+                          int64_t seq, int64_t ack_expect, int64_t grad_ptr, int64_t slice_begin, int64_t slice_len,
+                          Tensor& gacc, bool first, double timeout_s, Tensor& err, Tensor& done_ctr) {
+  int world = slabs.size();
+  std::vector<unsigned long long> sl(slabs.begin(), slabs.end()), ct(ctrls.begin(), ctrls.end());
+  CHECK_F32(gacc); CHECK_I32(err); CHECK_I32(done_ctr);
+  TORCH_CHECK(gacc.numel() >= slice_len, "zero_rs_accum: accumulator holds ", gacc.numel(), " elements, the slice has ", slice_len);
+  int rc = dfb::zero_rs_adamw(sl.data(), ct.data(), rank, world, slots, slot, (unsigned)seq, (unsigned)ack_expect,
+                              reinterpret_cast<const void*>(grad_ptr), slice_begin, slice_len, nullptr, nullptr, nullptr,
+                              nullptr, nullptr, nullptr, nullptr, 0, 0.f, 0.9f, 0.95f, 1e-8f, 1, 1.f, timeout_s,
+                              err.data_ptr<int>(), reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(),
+                              cur_stream(), gacc.data_ptr<float>(), first ? 1 : 0);
+  TORCH_CHECK(rc == 0, "zero_rs_accum launch failed with code ", rc);
+}
 static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls, int64_t rank, int64_t slots, int64_t slot,
                          int64_t seq, int64_t ack_expect, int64_t shard_ptr, int64_t full_ptr, int64_t per_bytes,
                          int64_t total_bytes, double timeout_s, Tensor& err, Tensor& done_ctr) {
@@ -257,5 +273,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_set_mt", [](int64_t mt) { dfb::gemm_bf16_set_mt((int)mt); });
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("zero_rs_adamw", &zero_rs_adamw);
+  m.def("zero_rs_accum", &zero_rs_accum);
   m.def("param_gather", &param_gather);
 }

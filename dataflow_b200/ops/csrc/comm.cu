@@ -7,6 +7,9 @@
 //                   sums the contributions in rank order (deterministic), applies AdamW to its fp32
 //                   master / moment slice and writes the bf16 parameter slice — one kernel, no
 //                   staging buffers, no library collective.
+//                   With an accumulator given instead, the same kernel is the per-round gradient
+//                   reduce-scatter of the re-gathering (FSDP) mode: pull, sum in rank order, add into
+//                   this rank's fp32 gradient slice; the optimizer then runs locally on the slice.
 //   param_gather  : parameter all-gather by peer loads into the full per-layer weight object.
 //
 // Rendezvous is a small control block per rank in peer-mapped memory: a *mailbox*
@@ -80,6 +83,8 @@ struct RsAdamwParams {
   float* m;
   float* v;
   bf16* shard_out;              // slice-sized bf16 parameter shard
+  float* gacc;                  // when set: reduce-scatter + fp32 accumulate only (no optimizer step) into this slice
+  int gacc_first;               // 1: overwrite the accumulator (first round of a step), 0: add to it
   FieldRange fields[kMaxFields];
   int n_fields;
   float lr, b1, b2, eps, bc1, bc2, gscale;
@@ -129,6 +134,16 @@ __global__ void __launch_bounds__(512) zero_rs_adamw_kernel(RsAdamwParams p) {
         unpack8(ld8(src[r] + g0), f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      if (p.gacc) {
+        float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (!p.gacc_first) {
+          const float4 c = *reinterpret_cast<const float4*>(p.gacc + e0), d = *reinterpret_cast<const float4*>(p.gacc + e0 + 4);
+          a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+        }
+        *reinterpret_cast<float4*>(p.gacc + e0) = a;
+        *reinterpret_cast<float4*>(p.gacc + e0 + 4) = b;
+        continue;
       }
       float wd = 0.f;
       for (int k = 0; k < p.n_fields; ++k)
@@ -255,7 +270,8 @@ int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctr
                   unsigned int seq, unsigned int ack_expect, const void* grad, long long slice_begin, long long slice_len,
                   float* master, float* m, float* v, void* shard_out, const long long* field_begin,
                   const long long* field_end, const float* field_wd, int n_fields, float lr, float b1, float b2, float eps,
-                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s) {
+                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s,
+                  float* gacc, int gacc_first) {
   if (world > kMaxWorld || n_fields > kMaxFields || (slice_len & 7) || (slice_begin & 7)) return -2;
   RsAdamwParams p{};
   p.peers = make_table(slabs, ctrls, rank, world);
@@ -270,6 +286,7 @@ int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctr
   p.gscale = gscale;
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.err = err; p.done_ctr = done_ctr;
+  p.gacc = gacc; p.gacc_first = gacc_first;
   zero_rs_adamw_kernel<<<num_sms, 512, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -35,7 +35,7 @@ int colsum_parts(int rows);
 void colsum_bf16(const void* x, float* partial, void* out, int accumulate, int rows, int cols, cudaStream_t s);
 void adamw_bf16(void* w, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2,
                 float eps, float wd, int step, float gscale, cudaStream_t s);
-int adamw_split(void* w, void* lo, const void* g, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
+int adamw_split(void* w, void* lo, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
                 float wd, int step, float gscale, cudaStream_t s);
 void adamw_master(float* master, void* w_out, const void* g, int g_is_f32, float* m, float* v, long long n, float lr,
                   float b1, float b2, float eps, float wd, int step, float gscale, cudaStream_t s);
@@ -66,7 +66,8 @@ int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctr
                   unsigned int seq, unsigned int ack_expect, const void* grad, long long slice_begin, long long slice_len,
                   float* master, float* m, float* v, void* shard_out, const long long* field_begin,
                   const long long* field_end, const float* field_wd, int n_fields, float lr, float b1, float b2, float eps,
-                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);
+                  int step, float gscale, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s,
+                  float* gacc = nullptr, int gacc_first = 0);
 int param_gather(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
                  unsigned int seq, unsigned int ack_expect, const void* shard, void* full, long long per_bytes,
                  long long total_bytes, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);

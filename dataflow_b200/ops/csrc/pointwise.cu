@@ -291,39 +291,52 @@ DFB_DEVICE float adamw_split_one(bf16& w, uint16_t& lo, float gi, bf16& m, bf16&
   split_cut(wi, w, lo);
   return wi;
 }
-// 8 elements per thread through 16-byte accesses; the tail (n % 8) runs scalar in the last block.
-__global__ void adamw_split_kernel(bf16* __restrict__ w, uint16_t* __restrict__ lo, const bf16* __restrict__ g,
+// 8 elements per thread through 16-byte accesses (two for fp32 gradients); the tail (n % 8) runs scalar in the
+// last block.
+template <typename G>
+__global__ void adamw_split_kernel(bf16* __restrict__ w, uint16_t* __restrict__ lo, const G* __restrict__ g,
                                    bf16* __restrict__ m, bf16* __restrict__ v, long long n, float lr, float b1, float b2,
                                    float eps, float wd, float bc1, float bc2, float gscale) {
   const long long n8 = n >> 3;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     uint4 wq = reinterpret_cast<uint4*>(w)[i], lq = reinterpret_cast<uint4*>(lo)[i];
-    uint4 gq = reinterpret_cast<const uint4*>(g)[i], mq = reinterpret_cast<uint4*>(m)[i], vq = reinterpret_cast<uint4*>(v)[i];
+    uint4 mq = reinterpret_cast<uint4*>(m)[i], vq = reinterpret_cast<uint4*>(v)[i];
+    float gf[8];
+    if constexpr (sizeof(G) == 4) {
+      const float4 a = reinterpret_cast<const float4*>(g)[2 * i], b = reinterpret_cast<const float4*>(g)[2 * i + 1];
+      gf[0] = a.x; gf[1] = a.y; gf[2] = a.z; gf[3] = a.w; gf[4] = b.x; gf[5] = b.y; gf[6] = b.z; gf[7] = b.w;
+    } else {
+      const uint4 gq = reinterpret_cast<const uint4*>(g)[i];
+      unpack8(*reinterpret_cast<const bf16x8*>(&gq), gf);
+    }
     bf16* wp = reinterpret_cast<bf16*>(&wq); uint16_t* lp = reinterpret_cast<uint16_t*>(&lq);
-    const bf16* gp = reinterpret_cast<const bf16*>(&gq);
     bf16* mp = reinterpret_cast<bf16*>(&mq); bf16* vp = reinterpret_cast<bf16*>(&vq);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) adamw_split_one(wp[k], lp[k], bf2f(gp[k]) * gscale, mp[k], vp[k], lr, b1, b2, eps, wd, bc1, bc2);
+    for (int k = 0; k < 8; ++k) adamw_split_one(wp[k], lp[k], gf[k] * gscale, mp[k], vp[k], lr, b1, b2, eps, wd, bc1, bc2);
     reinterpret_cast<uint4*>(w)[i] = wq; reinterpret_cast<uint4*>(lo)[i] = lq;
     reinterpret_cast<uint4*>(m)[i] = mq; reinterpret_cast<uint4*>(v)[i] = vq;
   }
   if (blockIdx.x == gridDim.x - 1) {
     for (long long i = (n8 << 3) + threadIdx.x; i < n; i += blockDim.x)
-      adamw_split_one(w[i], lo[i], bf2f(g[i]) * gscale, m[i], v[i], lr, b1, b2, eps, wd, bc1, bc2);
+      adamw_split_one(w[i], lo[i], to_f(g[i]) * gscale, m[i], v[i], lr, b1, b2, eps, wd, bc1, bc2);
   }
 }
 // A weight that was never stepped has lo == 0 (master == weight).  All five arrays must be 16-byte aligned
 // (fields of packed layouts are 256-byte aligned); returns -2 otherwise.
-int adamw_split(void* w, void* lo, const void* g, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
-                float wd, int step, float gscale, cudaStream_t s) {
+int adamw_split(void* w, void* lo, const void* g, int g_is_f32, void* m, void* v, long long n, float lr, float b1, float b2,
+                float eps, float wd, int step, float gscale, cudaStream_t s) {
   if (n == 0) return 0;
   if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(lo) | reinterpret_cast<uintptr_t>(g) |
        reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15)
     return -2;
   float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  adamw_split_kernel<<<ew_blocks((n + 7) / 8), 256, 0, s>>>((bf16*)w, (uint16_t*)lo, (const bf16*)g, (bf16*)m, (bf16*)v, n, lr,
-                                                            b1, b2, eps, wd, bc1, bc2, gscale);
+  if (g_is_f32)
+    adamw_split_kernel<float><<<ew_blocks((n + 7) / 8), 256, 0, s>>>((bf16*)w, (uint16_t*)lo, (const float*)g, (bf16*)m, (bf16*)v,
+                                                                   n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  else
+    adamw_split_kernel<bf16><<<ew_blocks((n + 7) / 8), 256, 0, s>>>((bf16*)w, (uint16_t*)lo, (const bf16*)g, (bf16*)m, (bf16*)v,
+                                                                  n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
   return 0;
 }
 

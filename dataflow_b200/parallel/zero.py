@@ -52,12 +52,26 @@ def zero_opt_layout(slice_nbytes: int, master: bool = True) -> PackedLayout:
     return PackedLayout(tuple(f))
 
 
+def split_opt_layout(slice_nbytes: int) -> PackedLayout:
+    """Optimizer state of one re-gathered (FSDP) slice: low halves of the split fp32 master + bf16 moments."""
+    n = slice_nbytes // 2
+    return PackedLayout((Field("mlo", (n,), "int16"), Field("m", (n,), "bf16"), Field("v", (n,), "bf16")))
+
+
 def zero_lower_kwargs(mode: str, rank: int, world: int, group: str = "dp") -> dict[str, Any]:
-    stage = {"zero3": 3, "zero1": 1, "zero1rs": 1}.get(mode)
+    """``zero3``: gather each layer once per step, fused reduce-scatter + AdamW at the end of the step.
+    ``fsdp``: stage 3 with re-gathering — gather in front of every use, reduce-scatter every backward into an
+    fp32 slice, local split-master AdamW (6 bytes of state per parameter, divided by the world size).
+    ``zero1`` / ``zero1rs``: whole weights everywhere, sharded optimizer state."""
+    stage = {"zero3": 3, "fsdp": 3, "zero1": 1, "zero1rs": 1}.get(mode)
     if stage is None:
-        raise KeyError(f"unknown ZeRO mode {mode!r} (zero3 | zero1)")
+        raise KeyError(f"unknown ZeRO mode {mode!r} (fsdp | zero3 | zero1)")
     # fp32 master + two fp32 moments per bf16 parameter: 12 bytes per 2 parameter bytes, 256-byte aligned planes
-    return {"zero": {"stage": stage, "rank": rank, "world": world, "group": group, "opt_bytes_per_param_byte": 6.0}}
+    z = {"stage": stage, "rank": rank, "world": world, "group": group, "opt_bytes_per_param_byte": 6.0}
+    if mode == "fsdp":
+        z.update(regather=True, block_opt_bytes_per_param_byte=3.0)
+        return {"zero": z, "resident_params": True}
+    return {"zero": z}
 
 
 @dataclass
@@ -80,6 +94,9 @@ class DpGroup:
         self.backend = None
         self.err = None
         self.done = None
+        self.comm_stream = None
+        self.done_async = None
+        self.async_comm = False
         self.name = "dp"
 
     # -- set-up (p2p lane): map every rank's slab and control block
@@ -109,12 +126,39 @@ class DpGroup:
         dev = torch.device("cuda", self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        # asynchronous gathers / reduce-scatters run here, off the engine's compute stream; the "last CTA"
+        # counter is per stream because kernels of the two streams may overlap
+        self.comm_stream = torch.cuda.Stream(device=dev)
+        self.done_async = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.async_comm = os.environ.get("DATAFLOW_ASYNC_COMM", "1") != "0"
         dist.barrier()
 
     def _in_slab(self, ptr: int, nbytes: int) -> None:
         if not (self.slab_base <= ptr and ptr + nbytes <= self.slab_base + self.slab_cap):
             raise RuntimeError("a buffer published to peers lies outside the peer-mapped engine slab "
                                "(slab overflow): raise the budget headroom")
+
+    def side(self, ctx, ready_ids):
+        """Context for an asynchronous launch: the communication stream, ordered after everything the compute
+        stream has queued so far; on exit an event is registered for the objects ``ready_ids`` so that their next
+        consumer waits for the transfer on its own stream."""
+        import contextlib
+        import torch
+
+        @contextlib.contextmanager
+        def scope():
+            cur = torch.cuda.current_stream()
+            e0 = torch.cuda.Event()
+            e0.record(cur)
+            self.comm_stream.wait_event(e0)
+            with torch.cuda.stream(self.comm_stream):
+                yield
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+            ready = ctx.run_values.setdefault("_ready", {})
+            for oid in ready_ids:
+                ready[oid] = ev
+        return scope()
 
     def _next(self, slot: int) -> tuple[int, int]:
         c = self.calls.get(slot, 0) + 1
@@ -171,7 +215,30 @@ class DpGroup:
             master.copy_(w)
         shard_out.copy_(w.to(shard_out.dtype))
 
-    def gather(self, slot: int, shard, full, per_bytes: int) -> None:
+    def rs_accum(self, slot: int, grad, begin_elem: int, len_elem: int, gacc, first: bool, asynchronous: bool = False) -> None:
+        """Reduce-scatter ``grad`` (flat bf16, whole object) over the group and add this rank's slice of the sum
+        into ``gacc`` (fp32, slice-sized); ``first`` overwrites instead."""
+        if self.lane == "p2p":
+            from ..ops import native
+            from ..ops.cuda import LAUNCHES
+            seq, ack = self._next(slot)
+            self._in_slab(grad.data_ptr(), grad.numel() * 2)
+            native().zero_rs_accum(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, grad.data_ptr(),
+                                   begin_elem, len_elem, gacc, bool(first), self.timeout_s, self.err,
+                                   self.done_async if asynchronous else self.done)
+            LAUNCHES.total += 1
+            return
+        import torch
+        import torch.distributed as dist
+        g32 = grad.float()
+        dist.all_reduce(g32)
+        part = g32[begin_elem:begin_elem + len_elem]
+        if first:
+            gacc[:len_elem].copy_(part)
+        else:
+            gacc[:len_elem].add_(part)
+
+    def gather(self, slot: int, shard, full, per_bytes: int, asynchronous: bool = False) -> None:
         """shard, full: uint8 tensors; ``full`` receives every rank's slice at ``rank * per_bytes``."""
         total = full.numel()
         if self.lane == "p2p":
@@ -180,7 +247,8 @@ class DpGroup:
             seq, ack = self._next(slot)
             self._in_slab(shard.data_ptr(), min(per_bytes, shard.numel()))
             native().param_gather(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, shard.data_ptr(),
-                                  full.data_ptr(), per_bytes, total, self.timeout_s, self.err, self.done)
+                                  full.data_ptr(), per_bytes, total, self.timeout_s, self.err,
+                                  self.done_async if asynchronous else self.done)
             LAUNCHES.total += 1
             return
         import torch
@@ -249,7 +317,77 @@ class ParamGather(_Base):
         full_b = ctx.outputs[0]
         shard = _flat(ctx.inputs[0], ctx.inputs[0].size, "uint8", self.device)
         full = _flat(full_b, full_b.size, "uint8", self.device)
-        g.gather(slot_of(bp.get("target", "block"), bp.get("layer"), 1), shard, full, slice_bytes(full_b.size, g.world))
+        slot = slot_of(bp.get("target", "block"), bp.get("layer"), 1)
+        if g.async_comm and g.lane == "p2p" and ctx.task.id.endswith(("f", "b")) and full_b.object_id.startswith("Wg_"):
+            with g.side(ctx, [full_b.object_id]):         # re-gather issued ahead of its consumer
+                g.gather(slot, shard, full, slice_bytes(full_b.size, g.world), asynchronous=True)
+            return
+        g.gather(slot, shard, full, slice_bytes(full_b.size, g.world))
+
+
+class GradReduceScatter(_Base):
+    """(dW[, G]) -> ([G]): this round's full gradient, reduce-scattered and added into the rank's fp32 slice."""
+
+    def run(self, ctx):
+        g = _group(ctx)
+        bp = ctx.task.block_params
+        total = ctx.inputs[0].size
+        lo, ln = slice_range(total, g.world, g.rank)
+        first = bool(bp.get("first"))
+        acc_buf = ctx.outputs[0] if first else ctx.inputs[1]
+        gacc = _flat(acc_buf, acc_buf.size, "fp32", self.device)
+        grad = _flat(ctx.inputs[0], total, "bf16", self.device)
+        slot = slot_of(bp.get("target", "block"), bp.get("layer"), 0)
+        if g.async_comm and g.lane == "p2p":
+            with g.side(ctx, [ctx.inputs[0].object_id, acc_buf.object_id]):      # joined by grad_rs_join / the optimizer
+                g.rs_accum(slot, grad, lo // 2, ln // 2, gacc, first, asynchronous=True)
+            return
+        g.rs_accum(slot, grad, lo // 2, ln // 2, gacc, first)
+
+
+class CommJoin(_Base):
+    """(dW, G) -> (): the point where an asynchronous reduce-scatter must be complete.  The wait itself is the
+    generic input wait of ``launch``; the full gradient's last use is here, so the engine frees it after."""
+
+    def run(self, ctx):
+        return None
+
+
+def local_split_step(exe, ctx, wl, grp) -> None:
+    """FSDP optimizer task ``(Ws, G, O)``: split-master AdamW on this rank's slice, field by field (weight decay
+    differs between matrices and vectors); no communication."""
+    total = wl.size_bytes
+    lo, ln = slice_range(total, grp.world, grp.rank)
+    per = slice_bytes(total, grp.world)
+    dev = exe.device
+    n = ln // 2
+    if not n:
+        return
+    w = _flat(ctx.inputs[0], per, "bf16", dev)
+    gacc = _flat(ctx.inputs[1], ctx.inputs[1].size, "fp32", dev)
+    ost = split_opt_layout(per).views(ctx.inputs[2], dev if ctx.inputs[2].location == "fast" else None)
+    hy = exe.hyper
+    step = int(ctx.run_args.get("step", 1))
+    lr = lr_at(hy, step)
+    b1, b2, eps = hy.get("beta1", 0.9), hy.get("beta2", 0.95), hy.get("eps", 1e-8)
+    wd, wd_all = hy.get("weight_decay", 0.0), bool(hy.get("wd_all"))
+    offs = wl.offsets()
+    e0 = lo // 2
+    pos = 0                                  # elements of the slice handled so far
+    cuts: list[tuple[int, int, float]] = []
+    for f in wl.fields:                      # fields in layout order; gaps (alignment padding) take no decay
+        a, b = offs[f.name] // 2 - e0, (offs[f.name] + f.nbytes) // 2 - e0
+        a, b = max(a, 0), min(b, n)
+        if b <= a:
+            continue
+        if a > pos:
+            cuts.append((pos, a, 0.0))
+        cuts.append((a, b, float(wd) if (wd and (wd_all or f.kind in ("matrix", "embedding"))) else 0.0))
+        pos = b
+    if pos < n:
+        cuts.append((pos, n, 0.0))
+    for a, b, fwd in cuts:
+        exe.K.adamw_split_step(w[a:b], ost["mlo"][a:b], gacc[a:b], ost["m"][a:b], ost["v"][a:b], lr, b1, b2, eps, fwd, step)
 
 
 def sharded_optimizer_step(exe, ctx, wl, gl, ol, w, g, o) -> bool:
@@ -260,6 +398,9 @@ def sharded_optimizer_step(exe, ctx, wl, gl, ol, w, g, o) -> bool:
     grp = _group(ctx)
     stage, rank, world = int(shard["stage"]), grp.rank, grp.world
     bp = ctx.task.block_params
+    if bp.get("local"):
+        local_split_step(exe, ctx, wl, grp)
+        return True
     total = wl.size_bytes
     lo, ln = slice_range(total, world, rank)
     per = slice_bytes(total, world)
@@ -297,6 +438,7 @@ def zero_initial_values(fam, cfg, program, store, seed: int, layouts, rank: int,
     import dataclasses
     solo = dataclasses.replace(solo, initial_objects=keep)
     pending: dict[str, Any] = {}
+    regather = bool(((program.metadata or {}).get("zero") or {}).get("regather"))
 
     def flush():
         for oid, (t, lay) in list(pending.items()):
@@ -311,12 +453,17 @@ def zero_initial_values(fam, cfg, program, store, seed: int, layouts, rank: int,
                 dst[:ln] = raw[lo:lo + ln]
             else:
                 views_of_raw(oid, total).copy_(raw)
-            ost = zero_opt_layout(per).views(store_buffer(f"O_{name}"), None)
-            ost["m"].zero_()
-            ost["v"].zero_()
-            ost["master"].zero_()
-            if ln:
-                ost["master"][:ln // 2] = raw[lo:lo + ln].view(torch.bfloat16).float()
+            if regather and name.isdigit():
+                ost = split_opt_layout(per).views(store_buffer(f"O_{name}"), None)
+                for plane in ("mlo", "m", "v"):         # master == weight: low halves are zero
+                    ost[plane].zero_()
+            else:
+                ost = zero_opt_layout(per).views(store_buffer(f"O_{name}"), None)
+                ost["m"].zero_()
+                ost["v"].zero_()
+                ost["master"].zero_()
+                if ln:
+                    ost["master"][:ln // 2] = raw[lo:lo + ln].view(torch.bfloat16).float()
             del pending[oid]
 
     store_buffer = store.buffer

@@ -29,6 +29,8 @@ def main():
     grp = make_dp_group(rank, world, rank if gpu else None, lane)
     tr = Trainer("llama3", cfg, budget_gib=None, device=rank if gpu else None, hyper=hyper, seed=5,
                  groups={"dp": grp}, lower_kwargs=zero_lower_kwargs(mode, rank, world), recompute=False)
+    if mode == "fsdp":
+        assert any(t.id.startswith("grad_rs_") for t in tr.program.tasks)
     losses = []
     for s in range(4):
         data = synthetic_rounds(cfg, tr.rounds, tr.T, 64, 100 + rank, s)        # each rank its own data
@@ -39,7 +41,8 @@ def main():
     dist.all_reduce(t)
     # the slice this rank owns of layer 0's weights, for cross-lane comparison
     from dataflow_b200.runtime.interop import torch_view
-    oid = "Ws_0" if mode == "zero3" else "W_0"
+    tr.sync_to_host()
+    oid = "Ws_0" if mode in ("zero3", "fsdp") else "W_0"
     w0 = torch_view(tr.store.buffer(oid), (tr.store.sizes[oid] // 2,), "bf16", 0, None).float()
     if rank == 0:
         json.dump({"losses": t.tolist(), "w0_sum": float(w0.double().sum()), "w0_abs": float(w0.double().abs().sum())},

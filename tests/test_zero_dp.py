@@ -45,9 +45,9 @@ def solo_reference_losses():
     return losses
 
 
-@pytest.mark.parametrize("mode", ["zero3", "zero1"])
+@pytest.mark.parametrize("mode", ["zero3", "zero1", "fsdp"])
 def test_zero_on_cpu_ranks_matches_single_process(mode, tmp_path):
-    got = launch(mode, 2, "cpu", tmp_path, port=29611 if mode == "zero3" else 29613)
+    got = launch(mode, 2, "cpu", tmp_path, port={"zero3": 29611, "zero1": 29613, "fsdp": 29615}[mode])
     ref = solo_reference_losses()
     for a, b in zip(got["losses"], ref):
         assert a == pytest.approx(b, rel=2e-3)
@@ -56,7 +56,7 @@ def test_zero_on_cpu_ranks_matches_single_process(mode, tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
-@pytest.mark.parametrize("mode", ["zero3", "zero1"])
+@pytest.mark.parametrize("mode", ["zero3", "zero1", "fsdp"])
 def test_fused_p2p_kernels_match_collective_lane(mode, tmp_path):
     p2p = launch(mode, 2, "cuda", tmp_path, lane="p2p", port=29621)
     col = launch(mode, 2, "cuda", tmp_path, lane="collective", port=29623)
