@@ -230,6 +230,37 @@ static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls,
   TORCH_CHECK(rc == 0, "param_gather launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- tensor-parallel fused GEMMs
+static void tp_ag_gemm(std::vector<int64_t> x_src, int64_t x_ld, int64_t gathered_ptr, const Tensor& w, bool b_mn, Tensor& y,
+                       int64_t panel_rows, int64_t rank, Tensor& flags, std::vector<int64_t> ready, std::vector<int64_t> acks,
+                       int64_t launch_seq, int64_t chunk_rows, double timeout_s, Tensor& err, Tensor& done_ctr) {
+  CHECK_BF16(w); CHECK_BF16(y); CHECK_I32(flags); CHECK_I32(err); CHECK_I32(done_ctr);
+  int world = x_src.size();
+  const int64_t K = b_mn ? w.size(0) : w.size(1), N = b_mn ? w.size(1) : w.size(0);
+  TORCH_CHECK(y.size(0) == panel_rows * world && y.size(1) == N, "tp_ag_gemm: y must be (world * panel_rows, N)");
+  std::vector<unsigned long long> xs(x_src.begin(), x_src.end()), rd(ready.begin(), ready.end()), ak(acks.begin(), acks.end());
+  int rc = dfb::tp_ag_gemm(xs.data(), x_ld, reinterpret_cast<void*>(gathered_ptr), w.data_ptr(), w.stride(0), b_mn, y.data_ptr(),
+                           y.stride(0), panel_rows, N, K, rank, world, reinterpret_cast<unsigned int*>(flags.data_ptr<int>()),
+                           rd.data(), ak.data(), (unsigned)launch_seq, chunk_rows, timeout_s, err.data_ptr<int>(),
+                           reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "tp_ag_gemm launch failed with code ", rc);
+}
+static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c10::optional<Tensor> addend, int64_t panel_rows,
+                       int64_t rank, std::vector<int64_t> stage, std::vector<int64_t> tile_flags, int64_t launch_seq,
+                       double timeout_s, Tensor& err, Tensor& done_ctr) {
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(d); CHECK_I32(err); CHECK_I32(done_ctr);
+  int world = stage.size();
+  const int64_t K = b_mn ? w.size(0) : w.size(1), N = b_mn ? w.size(1) : w.size(0);
+  TORCH_CHECK(x.size(0) == panel_rows * world && x.size(1) == K, "tp_gemm_rs: x must be (world * panel_rows, K)");
+  TORCH_CHECK(d.size(0) == panel_rows && d.size(1) == N, "tp_gemm_rs: d must be (panel_rows, N)");
+  std::vector<unsigned long long> st(stage.begin(), stage.end()), tf(tile_flags.begin(), tile_flags.end());
+  int rc = dfb::tp_gemm_rs(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), b_mn, d.data_ptr(), d.stride(0),
+                           addend.has_value() ? addend->data_ptr() : nullptr, addend.has_value() ? addend->stride(0) : 0,
+                           panel_rows, N, K, rank, world, st.data(), tf.data(), (unsigned)launch_seq, timeout_s,
+                           err.data_ptr<int>(), reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "tp_gemm_rs launch failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- interop
 // Zero-copy tensor over engine-owned memory (device or pinned host).
 static Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
@@ -274,5 +305,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("zero_rs_adamw", &zero_rs_adamw);
   m.def("zero_rs_accum", &zero_rs_accum);
+  m.def("tp_ag_gemm", &tp_ag_gemm);
+  m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("param_gather", &param_gather);
 }

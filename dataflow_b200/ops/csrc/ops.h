@@ -72,4 +72,14 @@ int param_gather(const unsigned long long* slabs, const unsigned long long* ctrl
                  unsigned int seq, unsigned int ack_expect, const void* shard, void* full, long long per_bytes,
                  long long total_bytes, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);
 
+
+// Tensor-parallel GEMMs fused with their collective (gemm_tp.cu)
+int tp_ag_gemm(const unsigned long long* x_src, long long x_ld, void* gathered, const void* W, long long ldw, int b_mn, void* Y,
+               long long ldy, int panel_rows, int N, int K, int rank, int world, unsigned int* flags,
+               const unsigned long long* ready, const unsigned long long* acks, unsigned int launch_seq, int chunk_rows,
+               double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t stream);
+int tp_gemm_rs(const void* X, long long ldx, const void* W, long long ldw, int b_mn, void* D, long long ldd, const void* addend,
+               long long ld_add, int panel_rows, int N, int K, int rank, int world, const unsigned long long* stage,
+               const unsigned long long* tile_flags, unsigned int launch_seq, double timeout_s, int* err,
+               unsigned int* done_ctr, int num_sms, cudaStream_t stream);
 }  // namespace dfb
