@@ -1,9 +1,9 @@
 // Tensor-parallel GEMMs fused with their collective, on the CTA-pair tcgen05 pipeline.
 //
 //   mode 1, all-gather -> GEMM (column-parallel linear under sequence parallelism):
-//       Y[M, N] = concat_r(X_r)[M, K] * W[K, N]; rank r holds the rows X_r.  Four extra "copy" warps in every
-//       CTA pull the peers' row panels over NVLink (plain peer loads) into a local gathered buffer, panel by
-//       panel in ring order starting with this rank's own rows, and bump a per-panel arrival counter; the TMA
+//       Y[M, N] = concat_r(X_r)[M, K] * W[K, N]; rank r holds the rows X_r, stored in slot r of its own gathered
+//       buffer.  Four extra "copy" warps in every CTA pull the peers' row panels over NVLink (plain peer loads)
+//       into the other slots, panel by panel in ring order, and bump a per-panel arrival counter; the TMA
 //       producer of a tile waits for the counter of the panel its rows come from.  The main loop of the first
 //       panels overlaps the transfer of the later ones and every remote row crosses NVLink exactly once.
 //   mode 2, GEMM -> reduce-scatter (row-parallel linear under sequence parallelism):
@@ -183,7 +183,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters) {
         int mb, nb, panel;
         tile_coords(p, tile, n_blocks, mb, nb, panel);
-        if (p.mode == 1 && panel != have_panel) {
+        if (p.mode == 1 && panel != have_panel && panel != p.rank) {
           // the rows of this tile come from ``panel``: wait until every chunk of it has landed locally
           if (!wait_ge<false>(&p.ag_flags[panel], p.ag_target, p.timeout_ns, abort_flag)) {
             sb->abort = 1; atomicExch(p.err, (21 << 8) | panel); break;
@@ -315,37 +315,50 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // ------------------------------------------------------------------ copy warps: all-gather by peer loads
     const int t = threadIdx.x - GEMM_THREADS;                   // 0 .. 127
     const int chunks_per_panel = p.panel_rows / p.ag_chunk_rows;
-    const int total_chunks = p.world * chunks_per_panel;
     const long long row_vecs = static_cast<long long>(p.K) / 8;  // 16-byte vectors per row
     __shared__ int copy_failed;
     if (t == 0) copy_failed = 0;
     asm volatile("bar.sync 2, 128;" ::: "memory");
-    for (int c = blockIdx.x; c < total_chunks && !copy_failed; c += gridDim.x) {
-      const int k = c / chunks_per_panel;
+    // this rank's own rows already sit in their slot of the gathered buffer (that slot IS the buffer peers read),
+    // so only the world - 1 remote panels are fetched, in ring order, spread over the CTAs in small chunks
+    const int remote_chunks = (p.world - 1) * chunks_per_panel;
+    for (int c = blockIdx.x; c < remote_chunks && !copy_failed; c += gridDim.x) {
+      const int k = c / chunks_per_panel + 1;
       const int panel = (p.rank + k) % p.world;
-      const int r0 = (c - k * chunks_per_panel) * p.ag_chunk_rows;
-      if (panel != p.rank) {
-        if (t == 0 && !wait_ge<true>(p.ready[panel], p.seq, p.timeout_ns, abort_flag)) {
-          atomicExch(p.err, (22 << 8) | panel);
-          copy_failed = 1;
-        }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (copy_failed) break;
+      const int r0 = (c - (k - 1) * chunks_per_panel) * p.ag_chunk_rows;
+      if (t == 0 && !wait_ge<true>(p.ready[panel], p.seq, p.timeout_ns, abort_flag)) {
+        atomicExch(p.err, (22 << 8) | panel);
+        copy_failed = 1;
       }
-      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[panel]);
-      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst);
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (copy_failed) break;
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src[panel]) + static_cast<long long>(r0) * (p.ag_src_ld / 8);
+      uint4* dst = reinterpret_cast<uint4*>(p.ag_dst) + (static_cast<long long>(panel) * p.panel_rows + r0) * row_vecs;
       const long long n_vec = static_cast<long long>(p.ag_chunk_rows) * row_vecs;
-      for (long long v = t; v < n_vec; v += COPY_THREADS) {
-        const long long row = v / row_vecs, cv = v - row * row_vecs;
-        const uint4 x = __ldcg(src + (r0 + row) * (p.ag_src_ld / 8) + cv);
-        dst[(static_cast<long long>(panel) * p.panel_rows + r0 + row) * row_vecs + cv] = x;
+      const bool dense = p.ag_src_ld == p.K;
+      long long v = t;
+      // four independent 16-byte peer loads in flight per thread: NVLink latency, not issue rate, is the limit
+      for (; v + 3 * COPY_THREADS < n_vec; v += 4 * COPY_THREADS) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long vv = v + u * COPY_THREADS;
+          const long long row = dense ? 0 : vv / row_vecs;
+          x[u] = __ldcg(dense ? src + vv : src + row * (p.ag_src_ld / 8) + (vv - row * row_vecs));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dst[v + u * COPY_THREADS] = x[u];
+      }
+      for (; v < n_vec; v += COPY_THREADS) {
+        const long long row = v / row_vecs;
+        dst[v] = __ldcg(src + row * (p.ag_src_ld / 8) + (v - row * row_vecs));
       }
       __threadfence();
       asm volatile("bar.sync 2, 128;" ::: "memory");
       if (t == 0) {
         const unsigned int prev = atomicAdd(&p.ag_flags[panel], 1u);
         // the chunk that completes a remote panel tells its owner that this rank is done reading it
-        if (panel != p.rank && prev + 1u == p.ag_target) {
+        if (prev + 1u == p.ag_target) {
           __threadfence_system();
           red_release_sys_add(p.acks[panel], 1u);
         }

@@ -32,8 +32,7 @@ class TpGroup:
         self.x_bytes = self.max_rows * self.max_k * 2
         self.gathered_bytes = self.world * self.x_bytes
         self.stage_bytes = self.world * self.max_rows * self.max_n * 2
-        self.off_x = CTRL_BYTES
-        self.off_gathered = self.off_x + _up(self.x_bytes)
+        self.off_gathered = CTRL_BYTES
         self.off_stage = self.off_gathered + _up(self.gathered_bytes)
         self.ws_bytes = self.off_stage + _up(self.stage_bytes)
         self.ws: list[int] = []
@@ -94,11 +93,12 @@ class TpGroup:
 
     # -- buffers
     def x_buffer(self, rows: int, k: int):
-        """The peer-readable buffer for this rank's rows: producers write their output here (zero copy)."""
+        """The peer-readable buffer for this rank's rows — its own slot of the gathered operand: a producer that
+        writes its output here hands it to the fused all-gather with no copy at all."""
         from ..ops import native
         if rows > self.max_rows or k > self.max_k:
             raise ValueError(f"rows x k = {rows} x {k} exceeds the workspace ({self.max_rows} x {self.max_k})")
-        return native().tensor_from_ptr(self.base + self.off_x, [rows, k], "bf16", self.device)
+        return native().tensor_from_ptr(self.base + self.off_gathered + self.rank * rows * k * 2, [rows, k], "bf16", self.device)
 
     # -- fused ops
     def ag_gemm(self, x, w, out=None, w_is_kn: bool = True):
@@ -122,8 +122,10 @@ class TpGroup:
         if x.data_ptr() != xb.data_ptr():
             xb.copy_(x)
         st = self._words(("ag", rows, k), 32)
-        chunk = 64 if rows % 64 == 0 else rows
-        native().tp_ag_gemm([p + self.off_x for p in self.ws], k, self.base + self.off_gathered, w, w_is_kn, out, rows, self.rank,
+        chunk = 16 if rows % 16 == 0 else rows
+        slot = rows * k * 2
+        native().tp_ag_gemm([p + self.off_gathered + r * slot for r, p in enumerate(self.ws)], k, self.base + self.off_gathered,
+                            w, w_is_kn, out, rows, self.rank,
                             st["flags"], [p + st["off"] for p in self.ws], [p + st["off"] + 64 for p in self.ws], st["seq"],
                             chunk, self.timeout_s, self.err, self.done)
         LAUNCHES.total += 1

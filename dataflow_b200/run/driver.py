@@ -172,6 +172,8 @@ class Trainer:
         self.zero = (self.program.metadata or {}).get("zero")
         # weights that end a step on the device stay there for the next one (Session.resident)
         self.keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
+        # on a device, launch up to two tasks behind an unfinished one: host dispatch hides behind device work
+        self.dispatch_ahead = 2 if device is not None else 0
         for g in self.groups.values():
             if hasattr(g, "attach"):
                 g.attach(self)
@@ -223,7 +225,8 @@ class Trainer:
             args["seq_lens"] = dict(seq_lens)
         res = self.engine.execute(self.program, self.resolver, self.store.buffers(), run_args=args,
                                   groups=self.groups, manage_pools=self.device is None,
-                                  keep_resident=self.keep_resident)
+                                  keep_resident=self.keep_resident,
+                                  dispatch_ahead=self.dispatch_ahead)
         self.last_result = res
         res.raise_if_failed()
         for g in self.groups.values():

@@ -225,7 +225,7 @@ PYBIND11_MODULE(_runtime, m) {
       .def("execute",
            [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
               bool strict_final, bool poison, bool record_events, double headroom,
-              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident) {
+              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident, int dispatch_ahead) {
              std::unordered_map<std::string, InitialBuffer> init;
              for (auto kv : initial) {
                auto t = kv.second.cast<py::tuple>();
@@ -239,6 +239,7 @@ PYBIND11_MODULE(_runtime, m) {
              opt.cancel = cancel ? cancel.get() : nullptr;
              opt.manage_pools = manage_pools;
              opt.keep_resident = keep_resident;
+             opt.dispatch_ahead = dispatch_ahead;
              LaunchFn fn;
              if (!launch.is_none()) {
                fn = [launch](const LaunchArgs& a) {
@@ -265,5 +266,5 @@ PYBIND11_MODULE(_runtime, m) {
            py::arg("strict_final_locations") = true, py::arg("poison_on_free") = false,
            py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
            py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true,
-           py::arg("keep_resident") = false);
+           py::arg("keep_resident") = false, py::arg("dispatch_ahead") = 0);
 }

@@ -212,7 +212,7 @@ void Engine::on_transfer_done(int dir) {
 // ----------------------------------------------------------------------------- task completion
 void Engine::on_task_done(int idx) {
   const TaskIR& t = p_->tasks[idx];
-  workspace_ = 0;
+  workspace_ -= t.workspace;
   for (auto& out : t.outputs) {
     ObjState& o = objs_[out.obj];
     Slot& s = out.loc == FAST ? o.fast : o.backing;
@@ -352,9 +352,14 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
   for (int i = 0; i < static_cast<int>(p.tasks.size()); ++i) {
     const TaskIR& t = p.tasks[i];
     if (opt.cancel && opt.cancel->load()) { out.outcome = "CANCELLED"; out.failed_task = t.id; break; }
-    // (0) strict pacing: the previous task must have retired
-    while (task_done_upto_ < i - 1) {
+    // (0) pacing: at most ``dispatch_ahead`` earlier tasks may still be in flight (0 = the previous task must have
+    // retired).  Tasks share one stream, so a task launched behind an unfinished predecessor still runs after it;
+    // launching ahead only hides the host's dispatch latency behind device work.
+    while (task_done_upto_ < i - 1 - opt.dispatch_ahead) {
       if (!pump_one(true)) deadlock("waiting for task " + p.tasks[i - 1].id + " to retire with nothing in flight");
+    }
+    if (opt.dispatch_ahead > 0) {
+      while (pump_one(false)) {}        // retire whatever has completed meanwhile before looking at the ledger
     }
     // (1)+(2) inputs live and the ledger admits outputs + workspace
     int64_t need = t.workspace;
@@ -363,9 +368,17 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
       bool ready = true;
       std::string missing;
       for (int in : t.inputs) {
-        if (objs_[in].fast.state != SlotState::LIVE) { ready = false; missing = p.objs[in].id; break; }
+        SlotState st = objs_[in].fast.state;
+        // RESERVED: the output of a task that is still in flight ahead of this one on the same stream
+        if (st != SlotState::LIVE && !(opt.dispatch_ahead > 0 && st == SlotState::RESERVED)) {
+          ready = false; missing = p.objs[in].id; break;
+        }
       }
       bool short_mem = p.fast_cap >= 0 && used_[FAST] + need > p.fast_cap;
+      // launched ahead of an unfinished predecessor, a task must not take the room the next queued prefetch is
+      // waiting for: reserving early would stall the copy lane, which strict pacing would not have done
+      if (!short_mem && p.fast_cap >= 0 && task_done_upto_ < i - 1 && !queue_[0].empty() && !flight_[0])
+        short_mem = used_[FAST] + need + queue_[0].front().size > p.fast_cap;
       if (ready && !short_mem) break;
       if (!pump_one(true)) {
         deadlock("task " + t.id + (missing.empty() ? std::string(" needs ") + std::to_string(need) + " fast bytes"
@@ -403,7 +416,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
       args.output_ptrs.push_back(reinterpret_cast<uint64_t>(s.buf.ptr));
       args.output_sizes.push_back(static_cast<size_t>(p.objs[o.obj].size));
     }
-    workspace_ = t.workspace;
+    workspace_ += t.workspace;
     note("task_start", t.id);
     // (5) launch
     args.stream_handle = be_->stream_handle(sess_->compute_stream);

@@ -157,6 +157,7 @@ struct ExecOptions {
   double slab_headroom = 0.0;
   bool manage_pools = true;         // size the session's slabs from the program's capacities
   bool keep_resident = false;       // final-fast objects stay in Session::resident for the next execute()
+  int dispatch_ahead = 0;           // tasks that may be launched behind an unfinished predecessor (0 = strict pacing)
   std::atomic<bool>* cancel = nullptr;
 };
 

@@ -188,7 +188,8 @@ class Engine:
                 initial_buffers: Mapping[str, Buffer] | None = None, *,
                 run_args: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
                 cancel_event: threading.Event | None = None, record_events: bool = False,
-                slab_headroom: float = 0.0, manage_pools: bool = True, keep_resident: bool = False) -> RunResult:
+                slab_headroom: float = 0.0, manage_pools: bool = True, keep_resident: bool = False,
+                dispatch_ahead: int = 0) -> RunResult:
         ci = self.chain_index(program)
         tasks = program.tasks
         run_values: dict[str, Any] = {}
@@ -234,7 +235,7 @@ class Engine:
         try:
             raw = self._native.execute(ci.ir, launch, initial, self.strict_final_locations,
                                        self.poison_on_free, record_events, slab_headroom, cancel, manage_pools,
-                                       keep_resident)
+                                       keep_resident, int(dispatch_ahead))
         finally:
             if watcher is not None:
                 stop.set()

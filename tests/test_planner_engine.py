@@ -109,3 +109,14 @@ def test_every_registered_policy_produces_a_plan_the_simulator_accepts(cap):
         assert log.makespan >= lower, name
         if cap is not None:
             assert log.peak_fast_memory_bytes <= cap, name
+
+
+@pytest.mark.parametrize("cap", [6000, 2200])
+def test_dispatch_ahead_keeps_results_and_capacity(cap):
+    """Launching up to two tasks behind an unfinished one changes when the host dispatches, not what runs."""
+    r = pressurefit(train_chain(), cap)
+    prog = from_sim_chain(r.chain)
+    strict = Engine(FakeBackend()).execute(prog).raise_if_failed()
+    ahead = Engine(FakeBackend()).execute(prog, dispatch_ahead=2).raise_if_failed()
+    assert ahead.peak_fast_bytes <= cap          # (virtual time is only meaningful under strict pacing: no makespan claim)
+    assert [iv.name for iv in ahead.trace.by_track("compute")] == [iv.name for iv in strict.trace.by_track("compute")]
