@@ -230,6 +230,72 @@ static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls,
   TORCH_CHECK(rc == 0, "param_gather launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- mixture of experts
+static int mode_id(const std::string& mode) {
+  if (mode == "topk_then_softmax") return 0;
+  if (mode == "softmax_then_topk") return 1;
+  TORCH_CHECK(false, "unknown routing mode ", mode);
+}
+static void moe_topk_softmax(const Tensor& logits, Tensor& route_w, Tensor& route_ids, const std::string& mode) {
+  CHECK_F32(route_w); CHECK_I32(route_ids);
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "logits must be a contiguous (t, E) matrix");
+  int rc = dfb::moe_topk_softmax(logits.data_ptr(), logits.scalar_type() == at::kFloat, route_w.data_ptr<float>(),
+                                 route_ids.data_ptr<int>(), logits.size(0), logits.size(1), route_w.size(1), mode_id(mode), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_topk_softmax: unsupported shape (E <= 1024, K <= 16), code ", rc);
+}
+static void moe_router_bwd(const Tensor& dprob, const Tensor& route_w, const Tensor& route_ids, const Tensor& logits,
+                           Tensor& dlogits, const std::string& mode) {
+  CHECK_F32(dprob); CHECK_F32(route_w); CHECK_I32(route_ids); CHECK_F32(dlogits);
+  int rc = dfb::moe_router_bwd(dprob.data_ptr<float>(), route_w.data_ptr<float>(), route_ids.data_ptr<int>(), logits.data_ptr(),
+                               logits.scalar_type() == at::kFloat, dlogits.data_ptr<float>(), logits.size(0), logits.size(1),
+                               route_w.size(1), mode_id(mode), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_router_bwd failed with code ", rc);
+}
+static void moe_dispatch(const Tensor& x, const Tensor& row_src, Tensor& xp) {
+  CHECK_BF16(x); CHECK_BF16(xp); CHECK_I32(row_src);
+  int rc = dfb::moe_dispatch(x.data_ptr(), x.stride(0), row_src.data_ptr<int>(), xp.data_ptr(), xp.size(0), xp.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_dispatch: the row width must be a multiple of 8 (code ", rc, ")");
+}
+static void moe_combine(c10::optional<Tensor> base, const Tensor& yp, const Tensor& route_w, const Tensor& row_of, Tensor& out) {
+  CHECK_BF16(yp); CHECK_BF16(out); CHECK_F32(route_w); CHECK_I32(row_of);
+  int rc = dfb::moe_combine(base.has_value() ? base->data_ptr() : nullptr, yp.data_ptr(), route_w.data_ptr<float>(),
+                            row_of.data_ptr<int>(), out.data_ptr(), out.size(0), out.size(1), row_of.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_combine failed with code ", rc);
+}
+static void moe_dispatch_bwd(const Tensor& dxp, const Tensor& row_of, Tensor& out, bool accumulate) {
+  CHECK_BF16(dxp); CHECK_BF16(out); CHECK_I32(row_of);
+  int rc = dfb::moe_dispatch_bwd(dxp.data_ptr(), row_of.data_ptr<int>(), out.data_ptr(), out.size(0), out.size(1), row_of.size(1),
+                                 accumulate, cur_stream());
+  TORCH_CHECK(rc == 0, "moe_dispatch_bwd failed with code ", rc);
+}
+static void moe_scale_rows(Tensor& xp, const Tensor& route_w, const Tensor& row_of) {
+  CHECK_BF16(xp); CHECK_F32(route_w); CHECK_I32(row_of);
+  int rc = dfb::moe_scale_rows(xp.data_ptr(), route_w.data_ptr<float>(), row_of.data_ptr<int>(), row_of.numel(), xp.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_scale_rows failed with code ", rc);
+}
+static void moe_rowdot(const Tensor& a, const Tensor& b, const Tensor& row_of, Tensor& out) {
+  CHECK_BF16(a); CHECK_BF16(b); CHECK_I32(row_of); CHECK_F32(out);
+  int rc = dfb::moe_rowdot(a.data_ptr(), b.data_ptr(), row_of.data_ptr<int>(), out.data_ptr<float>(), row_of.numel(), a.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_rowdot failed with code ", rc);
+}
+static void moe_grouped_mm(const Tensor& x, const Tensor& w, Tensor& y, const Tensor& tile_expert, bool w_kn) {
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(y); CHECK_I32(tile_expert);
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous() && y.is_contiguous(), "moe_grouped_mm: contiguous operands");
+  const int64_t K = x.size(1), N = y.size(1);
+  TORCH_CHECK(w.dim() == 3 && (w_kn ? (w.size(1) == K && w.size(2) == N) : (w.size(1) == N && w.size(2) == K)), "moe_grouped_mm: weight shape");
+  TORCH_CHECK(tile_expert.numel() * 256 >= x.size(0), "moe_grouped_mm: tile_expert too short");
+  int rc = dfb::moe_grouped_mm(x.data_ptr(), w.data_ptr(), y.data_ptr(), tile_expert.data_ptr<int>(), x.size(0), N, K, w.size(0), w_kn,
+                               num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_grouped_mm launch failed with code ", rc);
+}
+static void moe_grouped_wgrad(const Tensor& x, const Tensor& dy, Tensor& dw, const Tensor& offsets_pad, bool accumulate) {
+  CHECK_BF16(x); CHECK_BF16(dy); CHECK_BF16(dw); CHECK_I32(offsets_pad);
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dw.is_contiguous(), "moe_grouped_wgrad: contiguous operands");
+  int rc = dfb::moe_grouped_wgrad(x.data_ptr(), dy.data_ptr(), dw.data_ptr(), offsets_pad.data_ptr<int>(), x.size(0), x.size(1),
+                                  dy.size(1), dw.size(0), accumulate, num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_grouped_wgrad launch failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- tensor-parallel fused GEMMs
 static void tp_ag_gemm(std::vector<int64_t> x_src, int64_t x_ld, int64_t gathered_ptr, const Tensor& w, bool b_mn, Tensor& y,
                        int64_t panel_rows, int64_t rank, Tensor& flags, std::vector<int64_t> ready, std::vector<int64_t> acks,
@@ -305,6 +371,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("zero_rs_adamw", &zero_rs_adamw);
   m.def("zero_rs_accum", &zero_rs_accum);
+  m.def("moe_topk_softmax", &moe_topk_softmax);
+  m.def("moe_router_bwd", &moe_router_bwd);
+  m.def("moe_dispatch", &moe_dispatch);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_dispatch_bwd", &moe_dispatch_bwd);
+  m.def("moe_scale_rows", &moe_scale_rows);
+  m.def("moe_rowdot", &moe_rowdot);
+  m.def("moe_grouped_mm", &moe_grouped_mm);
+  m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
   m.def("tp_ag_gemm", &tp_ag_gemm);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("param_gather", &param_gather);

@@ -82,4 +82,20 @@ int tp_gemm_rs(const void* X, long long ldx, const void* W, long long ldw, int b
                long long ld_add, int panel_rows, int N, int K, int rank, int world, const unsigned long long* stage,
                const unsigned long long* tile_flags, unsigned int launch_seq, double timeout_s, int* err,
                unsigned int* done_ctr, int num_sms, cudaStream_t stream);
+
+// Mixture of experts (moe.cu, gemm_grouped.cu)
+int moe_topk_softmax(const void* logits, int logits_f32, float* route_w, int* route_ids, int t, int E, int K, int mode,
+                     cudaStream_t s);
+int moe_router_bwd(const float* dprob, const float* route_w, const int* route_ids, const void* logits, int logits_f32,
+                   float* dlogits, int t, int E, int K, int mode, cudaStream_t s);
+int moe_dispatch(const void* x, long long ldx, const int* row_src, void* xp, int rows, int d, cudaStream_t s);
+int moe_combine(const void* base, const void* yp, const float* w, const int* row_of, void* out, int t, int d, int K,
+                cudaStream_t s);
+int moe_dispatch_bwd(const void* dxp, const int* row_of, void* out, int t, int d, int K, int accumulate, cudaStream_t s);
+int moe_scale_rows(void* xp, const float* w, const int* row_of, int slots, int d, cudaStream_t s);
+int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int slots, int d, cudaStream_t s);
+int moe_grouped_mm(const void* X, const void* W, void* Y, const int* tile_expert, int Mp, int N, int K, int E, int w_kn,
+                   int num_sms, cudaStream_t stream);
+int moe_grouped_wgrad(const void* X, const void* dY, void* dW, const int* offsets_pad, int Mp, int Kw, int N, int E,
+                      int accumulate, int num_sms, cudaStream_t stream);
 }  // namespace dfb

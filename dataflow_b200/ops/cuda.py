@@ -265,3 +265,72 @@ def bias_grad(dy, db, accumulate=False):
     part = _scratch(native().colsum_parts(dy2.shape[0]) * dy2.shape[1], dy.device)
     native().colsum_bf16(dy2, part, db, bool(accumulate))
     return db
+
+
+# ------------------------------------------------------------------ mixture of experts
+@reg("moe_topk_softmax")
+def moe_topk_softmax(logits, top_k: int, mode: str = "topk_then_softmax"):
+    t = logits.shape[0]
+    w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    native().moe_topk_softmax(logits.contiguous(), w, ids, mode)
+    return w, ids
+
+
+@reg("moe_router_bwd")
+def moe_router_bwd(dprob, route_w, route_ids, logits, mode: str = "topk_then_softmax"):
+    out = torch.empty(logits.shape, dtype=torch.float32, device=logits.device)
+    native().moe_router_bwd(dprob.float().contiguous(), route_w.float().contiguous(), route_ids.contiguous(), logits.contiguous(),
+                            out, mode)
+    return out
+
+
+@reg("moe_dispatch")
+def moe_dispatch(x, row_src, out=None):
+    xp = out if out is not None else torch.empty(row_src.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
+    native().moe_dispatch(x, row_src, xp)
+    return xp
+
+
+@reg("moe_combine")
+def moe_combine(base, yp, route_w, row_of, out=None):
+    y = out if out is not None else torch.empty(row_of.shape[0], yp.shape[1], dtype=yp.dtype, device=yp.device)
+    native().moe_combine(base, yp, route_w.float().contiguous(), row_of, y)
+    return y
+
+
+@reg("moe_dispatch_bwd")
+def moe_dispatch_bwd(dxp, row_of, out=None, accumulate: bool = False):
+    if out is None:
+        out = torch.empty(row_of.shape[0], dxp.shape[1], dtype=dxp.dtype, device=dxp.device)
+        accumulate = False
+    native().moe_dispatch_bwd(dxp, row_of, out, bool(accumulate))
+    return out
+
+
+@reg("moe_scale_rows")
+def moe_scale_rows(xp, route_w, row_of):
+    native().moe_scale_rows(xp, route_w.float().contiguous(), row_of)
+    return xp
+
+
+@reg("moe_rowdot")
+def moe_rowdot(a, b, row_of):
+    out = torch.empty(row_of.shape, dtype=torch.float32, device=a.device)
+    native().moe_rowdot(a, b, row_of, out)
+    return out
+
+
+@reg("moe_grouped_mm")
+def moe_grouped_mm(xp, w, tile_expert, out=None, transpose_w: bool = False):
+    """``tile_expert``: the per-row-tile expert table of ``moe_sort`` (device int32)."""
+    n = w.shape[1] if transpose_w else w.shape[2]
+    y = out if out is not None else torch.empty(xp.shape[0], n, dtype=xp.dtype, device=xp.device)
+    native().moe_grouped_mm(xp, w, y, tile_expert, not transpose_w)
+    return y
+
+
+@reg("moe_grouped_wgrad", launches=2)
+def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
+    native().moe_grouped_wgrad(xp, dyp, dw, offsets_pad, bool(accumulate))
+    return dw

@@ -443,3 +443,199 @@ def add(a, b, out=None):
         out.copy_(y)
         return out
     return y
+
+
+# ------------------------------------------------------------------ mixture of experts (oracle lane)
+# Routing math is fp32 from the given logits; ties go to the SMALLEST expert index in every mode.
+# Semantics follow the reference's router / dispatch ops (src/dataflow_training/kernels/moe_router.py:42-111,
+# kernels/moe_dispatch.py:49-235); the padded expert-major layout below is this repository's own.
+MOE_TILE_ROWS = 256          # expert segments are padded to whole GEMM row tiles
+
+
+def _topk_smallest_index(scores, k):
+    """Top-k by value, ties broken towards the smaller index (a stable descending sort)."""
+    order = torch.sort(scores, dim=-1, descending=True, stable=True).indices
+    ids = order[..., :k]
+    return scores.gather(-1, ids), ids
+
+
+@register("moe_topk_softmax", "eager")
+def moe_topk_softmax(logits, top_k: int, mode: str = "topk_then_softmax"):
+    z = logits.float()
+    if mode == "topk_then_softmax":
+        vals, ids = _topk_smallest_index(z, top_k)
+        w = torch.softmax(vals, dim=-1)
+    elif mode == "softmax_then_topk":
+        p = torch.softmax(z, dim=-1)
+        w, ids = _topk_smallest_index(p, top_k)
+    else:
+        raise KeyError(f"routing mode {mode!r}")
+    return w, ids.to(torch.int32)
+
+
+@register("moe_topk_sigmoid_noaux", "eager")
+def moe_topk_sigmoid_noaux(logits, bias, top_k: int, n_group: int = 1, topk_group: int = 1, routed_scaling: float = 1.0,
+                           norm_topk: bool = True):
+    """DeepSeek-V3 routing: sigmoid scores; selection on score + bias restricted to the best ``topk_group`` of
+    ``n_group`` expert groups (a group's rank = sum of its two best biased scores); weights from the unbiased
+    scores, normalised over the selection and scaled."""
+    s = torch.sigmoid(logits.float())
+    sel = s + bias.float().unsqueeze(0)
+    t, e = s.shape
+    if n_group > 1:
+        g = sel.view(t, n_group, e // n_group)
+        top2 = torch.sort(g, dim=-1, descending=True, stable=True).values[..., :2].sum(-1)
+        _, gid = _topk_smallest_index(top2, topk_group)
+        mask = torch.zeros(t, n_group, dtype=torch.bool, device=s.device).scatter_(1, gid, True)
+        sel = torch.where(mask.unsqueeze(-1).expand_as(g).reshape(t, e), sel, torch.full_like(sel, float("-inf")))
+    _, ids = _topk_smallest_index(sel, top_k)
+    w = s.gather(1, ids)
+    if norm_topk:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * routed_scaling, ids.to(torch.int32)
+
+
+@register("moe_router_bwd", "eager")
+def moe_router_bwd(dprob, route_w, route_ids, logits, mode: str = "topk_then_softmax"):
+    """d(logits) (t, E) fp32 from d(route weights) (t, K)."""
+    ids = route_ids.long()
+    dp = dprob.float()
+    out = torch.zeros(logits.shape, dtype=torch.float32, device=logits.device)
+    if mode == "topk_then_softmax":
+        p = route_w.float()
+        out.scatter_(1, ids, p * (dp - (p * dp).sum(-1, keepdim=True)))
+    else:
+        pf = torch.softmax(logits.float(), dim=-1)
+        tp = pf.gather(1, ids)
+        out.copy_(-pf * (dp * tp).sum(-1, keepdim=True))
+        out.scatter_add_(1, ids, dp * tp)
+    return out
+
+
+@register("moe_aux_lb_grad", "eager")
+def moe_aux_lb_grad(logits, counts, dlogits, alpha: float, top_k: int):
+    """Adds the load-balance gradient (alpha E / T) p (f - <f, p>) in place; f = counts / (T K) is detached."""
+    t, e = logits.shape
+    p = torch.softmax(logits.float(), dim=-1)
+    f = counts.float() / (t * top_k)
+    dlogits.add_((alpha * e / t) * p * (f.unsqueeze(0) - (p @ f).unsqueeze(1)))
+    return dlogits
+
+
+@register("moe_sort", "eager")
+def moe_sort(route_ids, n_experts: int, tile_rows: int = MOE_TILE_ROWS):
+    """Padded expert-major layout of the t*K routed slots, computed without a host sync.
+
+    Returns ``(row_of (t, K) int32, row_src (Mp,) int32, offsets_pad (E + 1,) int32, tile_expert (Mp / tile,) int32,
+    counts (E,) int32)``: slot (t, k) lives in row ``row_of[t, k]`` of the dispatched matrix; ``row_src[r]`` is the
+    token a row holds (-1 for padding); expert e owns rows ``[offsets_pad[e], offsets_pad[e + 1])``, a whole number
+    of ``tile_rows`` tiles; ``tile_expert`` names the expert of every row tile (-1 past the end).  ``Mp`` is the
+    static worst case ``roundup(t K) + E * tile_rows``.  Within an expert rows keep token order (stable)."""
+    t, k = route_ids.shape
+    n = t * k
+    flat = route_ids.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices                         # expert-major, stable
+    counts = torch.zeros(n_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
+    padded = (counts + tile_rows - 1) // tile_rows * tile_rows
+    off = torch.zeros(n_experts + 1, dtype=torch.int64, device=flat.device)
+    off[1:] = torch.cumsum(counts, 0)
+    off_pad = torch.zeros(n_experts + 1, dtype=torch.int64, device=flat.device)
+    off_pad[1:] = torch.cumsum(padded, 0)
+    e_sorted = flat[order]
+    rank = torch.arange(n, device=flat.device) - off[e_sorted]
+    rows = off_pad[e_sorted] + rank                                       # padded row of each sorted slot
+    mp = (n + tile_rows - 1) // tile_rows * tile_rows + n_experts * tile_rows
+    row_of = torch.empty(n, dtype=torch.int64, device=flat.device)
+    row_of[order] = rows
+    row_src = torch.full((mp,), -1, dtype=torch.int64, device=flat.device)
+    row_src[rows] = order // k
+    tiles = torch.arange(mp // tile_rows, device=flat.device) * tile_rows
+    tile_expert = torch.searchsorted(off_pad[1:], tiles, right=True)
+    tile_expert = torch.where(tiles < off_pad[-1], tile_expert, torch.full_like(tile_expert, -1))
+    return (row_of.view(t, k).to(torch.int32), row_src.to(torch.int32), off_pad.to(torch.int32),
+            tile_expert.to(torch.int32), counts.to(torch.int32))
+
+
+@register("moe_dispatch", "eager")
+def moe_dispatch(x, row_src, out=None):
+    """xp[r] = x[row_src[r]] (zeros where row_src < 0)."""
+    src = row_src.long()
+    xp = x[src.clamp(min=0)] * (src >= 0).unsqueeze(-1).to(x.dtype)
+    if out is not None:
+        out.copy_(xp)
+        return out
+    return xp
+
+
+@register("moe_combine", "eager")
+def moe_combine(base, yp, route_w, row_of, out=None):
+    """y[t] = base[t] + sum_k route_w[t, k] * yp[row_of[t, k]]  (fp32 accumulate, one rounding)."""
+    t, k = row_of.shape
+    g = yp[row_of.reshape(-1).long()].float().view(t, k, -1)
+    y = (g * route_w.float().unsqueeze(-1)).sum(1)
+    if base is not None:
+        y = y + base.float()
+    y = y.to(yp.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+@register("moe_dispatch_bwd", "eager")
+def moe_dispatch_bwd(dxp, row_of, out=None, accumulate: bool = False):
+    """dx[t] (+)= sum_k dxp[row_of[t, k]]."""
+    t, k = row_of.shape
+    g = dxp[row_of.reshape(-1).long()].float().view(t, k, -1).sum(1)
+    if out is None:
+        return g.to(dxp.dtype)
+    out.copy_((out.float() + g if accumulate else g).to(out.dtype))
+    return out
+
+
+@register("moe_scale_rows", "eager")
+def moe_scale_rows(xp, route_w, row_of):
+    """In place: row row_of[t, k] of xp is multiplied by route_w[t, k] (padding rows untouched)."""
+    idx = row_of.reshape(-1).long()
+    xp[idx] = (xp[idx].float() * route_w.reshape(-1, 1).float()).to(xp.dtype)
+    return xp
+
+
+@register("moe_rowdot", "eager")
+def moe_rowdot(a, b, row_of):
+    """(t, K) fp32: <a[row], b[row]> for row = row_of[t, k]."""
+    idx = row_of.reshape(-1).long()
+    return (a[idx].float() * b[idx].float()).sum(-1).view(row_of.shape)
+
+
+@register("moe_grouped_mm", "eager")
+def moe_grouped_mm(xp, w, tile_expert, out=None, transpose_w: bool = False):
+    """Rows of expert e times ``w[e]`` ((K, N), or its transpose): (Mp, K) -> (Mp, N).  ``tile_expert`` names the expert
+    of every ``MOE_TILE_ROWS`` row tile (-1: no expert, rows stay zero).  Padding rows are zero in, zero out."""
+    n = w.shape[1] if transpose_w else w.shape[2]
+    y = out if out is not None else torch.zeros(xp.shape[0], n, dtype=xp.dtype, device=xp.device)
+    if out is not None:
+        y.zero_()
+    te = tile_expert.tolist()
+    tile = xp.shape[0] // max(len(te), 1) if len(te) * MOE_TILE_ROWS != xp.shape[0] else MOE_TILE_ROWS
+    i = 0
+    while i < len(te):
+        j = i
+        while j < len(te) and te[j] == te[i]:
+            j += 1
+        if te[i] >= 0:
+            wi = w[te[i]].t() if transpose_w else w[te[i]]
+            y[i * tile:j * tile] = _mm(xp[i * tile:j * tile], wi).to(y.dtype)
+        i = j
+    return y
+
+
+@register("moe_grouped_wgrad", "eager")
+def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
+    """dw[e] (+)= xp_e^T dyp_e."""
+    off = offsets_pad.tolist() if offsets_pad.device.type == "cpu" else offsets_pad.cpu().tolist()
+    for i in range(dw.shape[0]):
+        a, b = off[i], off[i + 1]
+        g = _mm(xp[a:b].t(), dyp[a:b]) if b > a else torch.zeros_like(dw[i], dtype=torch.float32)
+        dw[i].copy_((dw[i].float() + g.float() if accumulate else g).to(dw.dtype))
+    return dw

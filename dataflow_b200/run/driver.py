@@ -166,7 +166,12 @@ class Trainer:
             transient_backing = max(planned.peak_backing_bytes - store_bytes, 0) + (64 << 20)
             fast = planned.object_capacity or (planned.peak_fast_bytes + (256 << 20))
             # the whole object share of the budget: the room above the planned peak absorbs slab fragmentation
-            self.session.native.ensure_pools(int(fast), int(transient_backing), 0.0)
+            # plus most of the budget's leeway share: the planner never counts on it, it only absorbs fragmentation
+            # (a buffer that overflows the slab cannot be read by peers, and costs a vendor allocation)
+            from ..lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
+            lee = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else int(leeway_bytes)
+            spare = min(lee * 3 // 4, 1 << 30) if budget is not None else 0
+            self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0)
         self.step_index = 0
         self.last_result = None
         self.zero = (self.program.metadata or {}).get("zero")
