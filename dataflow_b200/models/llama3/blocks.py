@@ -72,6 +72,54 @@ def stage_down_resid(K, d, st):
     K.linear_fwd_bf16(st["s"], st["w"]["w2"], out=st["y"], add=st["a"]["h_mid"])
 
 
+# ---- mixture-of-experts MLP (olmoe / qwen3moe variants): route -> dispatch + grouped up-projection -> SwiGLU ->
+# grouped down-projection + weighted combine.  The routing decision and the row tables are saved context.
+def stage_moe_route(K, d, st):
+    a = st["a"]
+    K.linear_fwd_bf16(st["h2"], st["w"]["w_router"], out=a["router_logits"])
+    w, ids = K.moe_topk_softmax(a["router_logits"], d.topk, d.routing_mode)
+    a["route_w"].copy_(w)
+    a["route_ids"].copy_(ids)
+    row_of, row_src, offp, tile_e, counts = K.moe_sort(ids, d.E)
+    mp = row_src.shape[0]
+    a["row_of"].copy_(row_of)
+    a["row_src"][:mp].copy_(row_src)
+    a["row_src"][mp:].fill_(-1)                 # rows past this round's content hold nothing
+    a["offsets_pad"].copy_(offp)
+    a["tile_expert"][:mp // 256].copy_(tile_e)
+    a["tile_expert"][mp // 256:].fill_(-1)
+    a["counts"].copy_(counts)
+
+
+def stage_moe_up(K, d, st):
+    a = st["a"]
+    st["xp"] = K.moe_dispatch(st["h2"], a["row_src"])
+    K.moe_grouped_mm(st["xp"], st["w"]["w13_experts"], a["tile_expert"], out=a["h13p"])
+
+
+def stage_moe_act(K, d, st):
+    st["sp"] = K.swiglu_packed_fwd(st["a"]["h13p"])
+
+
+def stage_moe_down_combine(K, d, st):
+    a = st["a"]
+    yp = K.moe_grouped_mm(st["sp"], st["w"]["w2_experts"], a["tile_expert"])
+    K.moe_combine(a["h_mid"], yp, a["route_w"], a["row_of"], out=st["y"])
+
+
+MOE_ROUTE_FIELDS = ("router_logits", "route_w", "route_ids", "row_of", "row_src", "offsets_pad", "tile_expert", "counts")
+
+STAGES_MOE = (
+    ("attn_norm", stage_attn_norm, ("rstd_attn",)),
+    ("qkv_rope", stage_qkv_rope, ("qkv",)),
+    ("attn", stage_attn, ("lse", "attn_out")),
+    ("resid1_norm2", stage_resid1_norm2, ("h_mid", "rstd_ffn")),
+    ("moe_route", stage_moe_route, MOE_ROUTE_FIELDS),
+    ("moe_up", stage_moe_up, ("h13p",)),
+    ("moe_act", stage_moe_act, ()),
+    ("moe_down_combine", stage_moe_down_combine, ()),
+)
+
 STAGES = (
     ("attn_norm", stage_attn_norm, ("rstd_attn",)),
     ("qkv_rope", stage_qkv_rope, ("qkv",)),
@@ -91,12 +139,15 @@ def recompute_stages(stages=STAGES):
 
 def context_rows(d, n):
     """Content-row trims of the context fields for an under-full round (token-axis aware)."""
-    rows = {name: n for name in ("rstd_attn", "qkv", "attn_out", "h_mid", "rstd_ffn", "h13", "q_rstd", "k_rstd", "qk_pre")}
+    rows = {name: n for name in ("rstd_attn", "qkv", "attn_out", "h_mid", "rstd_ffn", "h13", "q_rstd", "k_rstd", "qk_pre",
+                                 "router_logits", "route_w", "route_ids", "row_of")}
     return rows
 
 
 class _Block(_Base):
-    stages = STAGES
+    @property
+    def stages(self):
+        return STAGES_MOE if getattr(self.dims, "moe", False) else STAGES
 
     def ctx_views(self, buf, n):
         a = self.views(buf, self.lay.ctx, context_rows(self.dims, n))
@@ -133,7 +184,7 @@ class BlockFwd(_Block):
         elif lvl == 1:
             # everything but h13 is saved (object Ap); h13 lives in scratch and is rebuilt before backward
             st["a"] = dict(self.partial_views(ctx.outputs[1], st["n"]))
-            st["a"].update(self.scratch_ctx(st["n"], st["x"].device, only=("h13",)))
+            st["a"].update(self.scratch_ctx(st["n"], st["x"].device, only=("h13", "h13p")))
         else:
             st["a"] = self.scratch_ctx(st["n"], st["x"].device)      # context is dropped: recomputed before backward
         for _, fn, _ in self.stages:
@@ -146,7 +197,8 @@ class BlockFwd(_Block):
         for f in self.lay.ctx.fields:
             if only is not None and f.name not in only:
                 continue
-            shape = (f.shape[0], n) if f.name == "lse" else (n,) + tuple(f.shape[1:])
+            token_axis = f.name not in ("row_src", "offsets_pad", "tile_expert", "counts", "h13p")
+            shape = (f.shape[0], n) if f.name == "lse" else ((n,) + tuple(f.shape[1:]) if token_axis else tuple(f.shape))
             out[f.name] = torch.empty(shape, dtype=_dtypes()[f.dtype], device=device)
         return out
 
@@ -164,7 +216,7 @@ class BlockRecompute(_Block):
             for name, t in saved.items():
                 st["a"][name].copy_(t)
             st["h2"] = self.K.rmsnorm_apply(st["a"]["h_mid"], st["w"]["ffn_norm"], st["a"]["rstd_ffn"])
-            stage_up_proj(self.K, self.dims, st)
+            (stage_moe_up if self.dims.moe else stage_up_proj)(self.K, self.dims, st)      # routing is saved context
             return
         for _, fn, _ in recompute_stages(self.stages):
             fn(self.K, self.dims, st)
@@ -188,19 +240,7 @@ class BlockBwd(_Block):
             if name in g:                       # frozen fields have no gradient storage
                 K.linear_wgrad_bf16(xin, dout, g[name], accumulate=acc)
 
-        # ---- MLP tail
-        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
-        s = K.swiglu_packed_fwd(a["h13"])
-        wgrad("w2", s, dy)
-        ds = K.linear_dgrad_bf16(dy, w["w2"])
-        del s
-        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
-        del ds
-        wgrad("w13", h2, dh13)
-        dh2 = K.linear_dgrad_bf16(dh13, w["w13"])
-        del dh13, h2
-        dh_mid = K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
-        del dh2
+        dh_mid = (self.bwd_moe if d.moe else self.bwd_mlp)(a, w, g, dy, acc, wgrad)
         # ---- attention
         wgrad("wo", a["attn_out"], dh_mid)
         dattn = K.linear_dgrad_bf16(dh_mid, w["wo"])
@@ -222,6 +262,53 @@ class BlockBwd(_Block):
         wgrad("w_qkv", h, dqkv)
         dh = K.linear_dgrad_bf16(dqkv, w["w_qkv"])
         K.rmsnorm_bwd(dh, x, w["attn_norm"], a["rstd_attn"], dx_add=dh_mid, dw=g.get("attn_norm"), accumulate=acc, out=dx)
+
+
+    def bwd_mlp(self, a, w, g, dy, acc, wgrad):
+        K = self.K
+        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+        s = K.swiglu_packed_fwd(a["h13"])
+        wgrad("w2", s, dy)
+        ds = K.linear_dgrad_bf16(dy, w["w2"])
+        del s
+        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
+        del ds
+        wgrad("w13", h2, dh13)
+        dh2 = K.linear_dgrad_bf16(dh13, w["w13"])
+        del dh13, h2
+        return K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
+
+    def bwd_moe(self, a, w, g, dy, acc, wgrad):
+        """Backward of route -> dispatch -> experts -> combine.  d(route_w)[t, k] = <dy[t], yp[row]> is taken as
+        <dy W2^T, s> from the raw (unscaled) down-projection dgrad, then both are scaled by the route weight."""
+        K, d = self.K, self.dims
+        rw, row_of, tile_e, offp = a["route_w"], a["row_of"], a["tile_expert"], a["offsets_pad"]
+        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+        xp = K.moe_dispatch(h2, a["row_src"])
+        dyp = K.moe_dispatch(dy, a["row_src"])
+        sp = K.swiglu_packed_fwd(a["h13p"])
+        dsp = K.moe_grouped_mm(dyp, w["w2_experts"], tile_e, transpose_w=True)
+        d_rw = K.moe_rowdot(dsp, sp, row_of)
+        K.moe_scale_rows(dyp, rw, row_of)
+        K.moe_scale_rows(dsp, rw, row_of)
+        if "w2_experts" in g:
+            K.moe_grouped_wgrad(sp, dyp, offp, g["w2_experts"], accumulate=acc)
+        del sp, dyp
+        dh13p = K.swiglu_packed_bwd(dsp, a["h13p"])
+        del dsp
+        if "w13_experts" in g:
+            K.moe_grouped_wgrad(xp, dh13p, offp, g["w13_experts"], accumulate=acc)
+        dxp = K.moe_grouped_mm(dh13p, w["w13_experts"], tile_e, transpose_w=True)
+        del dh13p, xp
+        dh2 = K.moe_dispatch_bwd(dxp, row_of)
+        del dxp
+        dlogits = K.moe_router_bwd(d_rw, rw, a["route_ids"], a["router_logits"], d.routing_mode)
+        if d.aux_coef:
+            K.moe_aux_lb_grad(a["router_logits"], a["counts"], dlogits, d.aux_coef, d.topk)
+        dlog = dlogits.to(h2.dtype)
+        wgrad("w_router", h2, dlog)
+        dh2 = dh2 + K.linear_dgrad_bf16(dlog, w["w_router"])
+        return K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
 
 
 def build_llama3_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device, layouts=None, policy=None):

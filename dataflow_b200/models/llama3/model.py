@@ -39,6 +39,12 @@ class ShapedLlama3Config:
     head_chunk_tokens: int = 2048
     qk_norm: bool = False                # qwen3 variant: per-head RMSNorm on q and k
     family: str = "llama3"
+    # mixture-of-experts MLP (olmoe / qwen3moe variants): n_experts > 0 replaces the dense SwiGLU MLP
+    n_experts: int = 0
+    top_k: int = 0
+    d_ff_expert: int = 0
+    routing_mode: str = "topk_then_softmax"
+    aux_coef: float = 0.0                # load-balance loss coefficient (gradient injected analytically)
 
     @property
     def tokens_per_round(self) -> int:
@@ -67,6 +73,21 @@ class Llama3Dims:
     seq_len: int
     head_chunk: int
     qk_norm: bool = False
+    E: int = 0                           # experts (0: dense MLP)
+    topk: int = 0
+    Fe: int = 0                          # expert FFN width
+    routing_mode: str = "topk_then_softmax"
+    aux_coef: float = 0.0
+
+    @property
+    def moe(self) -> bool:
+        return self.E > 0
+
+    @property
+    def Mp(self) -> int:
+        """Rows of the dispatched (expert-major, tile-padded) activation matrix: the static worst case."""
+        n = self.T * self.topk
+        return (n + 255) // 256 * 256 + self.E * 256
 
     @property
     def qkv_dim(self) -> int:
@@ -85,7 +106,8 @@ def derive_dims(cfg: ShapedLlama3Config) -> Llama3Dims:
     assert cfg.n_heads % cfg.n_kv_heads == 0
     return Llama3Dims(cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.d_ff, cfg.vocab_size,
                       cfg.rope_theta, cfg.rms_eps, cfg.tokens_per_round, cfg.seq_len,
-                      min(cfg.head_chunk_tokens, cfg.tokens_per_round), cfg.qk_norm)
+                      min(cfg.head_chunk_tokens, cfg.tokens_per_round), cfg.qk_norm, cfg.n_experts, cfg.top_k,
+                      cfg.d_ff_expert, cfg.routing_mode, cfg.aux_coef)
 
 
 # --------------------------------------------------------------------------- layouts
@@ -95,9 +117,14 @@ def block_fields(d: Llama3Dims) -> tuple[Field, ...]:
     if d.qk_norm:
         f += [Field("q_norm", (d.hd,), "bf16", "vector", "ones"), Field("k_norm", (d.hd,), "bf16", "vector", "ones")]
     f += [Field("wo", (d.q_dim, d.d), "bf16", "matrix", "normal"),
-          Field("ffn_norm", (d.d,), "bf16", "vector", "ones"),
-          Field("w13", (d.d, 2 * d.F), "bf16", "matrix", "normal"),
-          Field("w2", (d.F, d.d), "bf16", "matrix", "normal")]
+          Field("ffn_norm", (d.d,), "bf16", "vector", "ones")]
+    if d.moe:
+        f += [Field("w_router", (d.d, d.E), "bf16", "matrix", "normal"),
+              Field("w13_experts", (d.E, d.d, 2 * d.Fe), "bf16", "matrix", "normal"),
+              Field("w2_experts", (d.E, d.Fe, d.d), "bf16", "matrix", "normal")]
+    else:
+        f += [Field("w13", (d.d, 2 * d.F), "bf16", "matrix", "normal"),
+              Field("w2", (d.F, d.d), "bf16", "matrix", "normal")]
     return tuple(f)
 
 
@@ -117,7 +144,7 @@ def context_layout(d: Llama3Dims, level: int = 0) -> PackedLayout:
         return PackedLayout(())
     full = _context_layout_full(d)
     if level == 1:
-        return PackedLayout(tuple(f for f in full.fields if f.name != "h13"))
+        return PackedLayout(tuple(f for f in full.fields if f.name not in ("h13", "h13p")))
     return full
 
 
@@ -127,8 +154,17 @@ def _context_layout_full(d: Llama3Dims) -> PackedLayout:
         f += [Field("q_rstd", (d.T, d.hq), "fp32"), Field("k_rstd", (d.T, d.hkv), "fp32"),
               Field("qk_pre", (d.T, d.q_dim + d.kv_dim), "bf16")]
     f += [Field("lse", (d.hq, d.T), "fp32"), Field("attn_out", (d.T, d.q_dim), "bf16"),
-          Field("h_mid", (d.T, d.d), "bf16"), Field("rstd_ffn", (d.T,), "fp32"),
-          Field("h13", (d.T, 2 * d.F), "bf16")]
+          Field("h_mid", (d.T, d.d), "bf16"), Field("rstd_ffn", (d.T,), "fp32")]
+    if d.moe:
+        # the routing decision and the padded expert-major row tables are context: recompute and backward never
+        # re-route; h13p is the up-projection of the dispatched rows (expert-major)
+        f += [Field("router_logits", (d.T, d.E), "bf16"), Field("route_w", (d.T, d.topk), "fp32"),
+              Field("route_ids", (d.T, d.topk), "int32"), Field("row_of", (d.T, d.topk), "int32"),
+              Field("row_src", (d.Mp,), "int32"), Field("offsets_pad", (d.E + 1,), "int32"),
+              Field("tile_expert", (d.Mp // 256,), "int32"), Field("counts", (d.E,), "int32"),
+              Field("h13p", (d.Mp, 2 * d.Fe), "bf16")]
+    else:
+        f.append(Field("h13", (d.T, 2 * d.F), "bf16"))
     return PackedLayout(tuple(f))
 
 
@@ -202,22 +238,29 @@ def _subop(name, flops=0.0, nbytes=0.0, eff="matmul", dtype="bf16"):
 
 def block_kind_spec(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware, optimizer: str = "adamw") -> LayerKindSpec:
     T, S = d.T, d.seq_len
-    gemm = 2.0 * T * (d.d * d.qkv_dim + d.q_dim * d.d + d.d * 2 * d.F + d.F * d.d)
+    mlp = (d.d * d.E + d.topk * (d.d * 2 * d.Fe + d.Fe * d.d)) if d.moe else (d.d * 2 * d.F + d.F * d.d)
+    gemm = 2.0 * T * (d.d * d.qkv_dim + d.q_dim * d.d + mlp)
     attn = 2.0 * S * T * d.hd * d.hq            # causal: half of 4*S*T*hd*hq
-    ew_bytes = 2.0 * T * (6 * d.d + 2 * d.qkv_dim + 3 * 2 * d.F)
+    ffw = d.topk * (2 * d.Fe + 2 * d.d) if d.moe else 2 * d.F
+    ew_bytes = 2.0 * T * (6 * d.d + 2 * d.qkv_dim + 3 * ffw)
     fwd_sub = (_subop("gemms", gemm), _subop("attention", attn, eff="attention"), _subop("elementwise", nbytes=ew_bytes, eff="memory"))
     bwd_sub = (_subop("gemms", 2 * gemm), _subop("attention", 2.5 * attn, eff="attention_bwd"),
                _subop("elementwise", nbytes=2.5 * ew_bytes, eff="memory"))
     fwd_us = hw.matmul_us(gemm) + hw.attn_us(attn) + hw.mem_us(ew_bytes)
     bwd_us = hw.matmul_us(2 * gemm) + hw.attn_us(2.5 * attn, True) + hw.mem_us(2.5 * ew_bytes)
     w, dw, o = lay.block_w.size_bytes, lay.block_dw.size_bytes, lay.block_o.size_bytes
-    ws_f = T * max(d.qkv_dim, 2 * d.F) * 2 + (1 << 20)
-    ws_b = T * (2 * d.F * 2 + d.F + d.qkv_dim + 2 * d.d) * 2 + (1 << 20)
+    if d.moe:
+        ws_f = d.Mp * (2 * d.d + d.Fe) * 2 + T * d.qkv_dim * 2 + (1 << 20)
+        ws_b = d.Mp * (3 * d.d + 2 * d.Fe * 2 + d.Fe) * 2 + T * (d.qkv_dim + 3 * d.d) * 2 + (1 << 20)
+    else:
+        ws_f = T * max(d.qkv_dim, 2 * d.F) * 2 + (1 << 20)
+        ws_b = T * (2 * d.F * 2 + d.F + d.qkv_dim + 2 * d.d) * 2 + (1 << 20)
     return LayerKindSpec(
         "block", w, dw, o, lay.ctx.size_bytes, fwd_us, bwd_us, fwd_us, optimizer_cost_seed(hw, w, dw, o, optimizer),
         fwd_sub, bwd_sub, fwd_sub, (_subop("optimizer", nbytes=2 * w + dw + 2 * o, eff="memory"),),
         ws_f, ws_b, 0,
-        recompute_levels=((1, lay.extra["Ap"].size_bytes, hw.matmul_us(2.0 * T * d.d * 2 * d.F) + hw.mem_us(ew_bytes / 3)),
+        recompute_levels=((1, lay.extra["Ap"].size_bytes,
+                           hw.matmul_us(2.0 * T * d.d * (2 * d.Fe * d.topk if d.moe else 2 * d.F)) + hw.mem_us(ew_bytes / 3)),
                           (2, 0, fwd_us)))
 
 
@@ -233,7 +276,8 @@ def loose_costs(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware) -> LooseC
 def flops_per_token(cfg: ShapedLlama3Config) -> float:
     """Effective training FLOPs per token (fwd + bwd, causal attention counted at half)."""
     d = derive_dims(cfg)
-    gemm = 2.0 * (d.d * d.qkv_dim + d.q_dim * d.d + d.d * 2 * d.F + d.F * d.d)
+    mlp = (d.d * d.E + d.topk * (d.d * 2 * d.Fe + d.Fe * d.d)) if d.moe else (d.d * 2 * d.F + d.F * d.d)
+    gemm = 2.0 * (d.d * d.qkv_dim + d.q_dim * d.d + mlp)
     attn = 2.0 * d.seq_len * d.hd * d.hq
     return 3.0 * (d.n_layers * (gemm + attn) + 2.0 * d.d * d.vocab) + 0.5 * d.n_layers * attn
 

@@ -39,7 +39,11 @@ class Llama3Twin(nn.Module):
         for _ in range(d.n_layers):
             l = nn.Module()
             l.attn_norm, l.w_qkv, l.wo = P(d.d), P(d.d, d.qkv_dim), P(d.q_dim, d.d)
-            l.ffn_norm, l.w13, l.w2 = P(d.d), P(d.d, 2 * d.F), P(d.F, d.d)
+            l.ffn_norm = P(d.d)
+            if d.moe:
+                l.w_router, l.w13_experts, l.w2_experts = P(d.d, d.E), P(d.E, d.d, 2 * d.Fe), P(d.E, d.Fe, d.d)
+            else:
+                l.w13, l.w2 = P(d.d, 2 * d.F), P(d.F, d.d)
             if d.qk_norm:
                 l.q_norm, l.k_norm = P(d.hd), P(d.hd)
             self.layers.append(l)
@@ -71,10 +75,35 @@ class Llama3Twin(nn.Module):
             attn = torch.cat(outs, 0)
             h_mid = x + attn @ l.wo
             h2 = _rms(h_mid, l.ffn_norm, d.eps)
-            h13 = h2 @ l.w13
-            s = torch.nn.functional.silu(h13[:, :d.F]) * h13[:, d.F:]
-            x = h_mid + s @ l.w2
+            if d.moe:
+                x = h_mid + self._moe(l, h2)
+            else:
+                h13 = h2 @ l.w13
+                s = torch.nn.functional.silu(h13[:, :d.F]) * h13[:, d.F:]
+                x = h_mid + s @ l.w2
         return _rms(x, self.final_norm, d.eps) @ self.w_head
+
+    def _moe(self, l, h2):
+        """Dense-loop mixture of experts: the same selection rule as the engine (ties to the smallest index),
+        differentiable route weights."""
+        from ...ops.eager import moe_topk_softmax
+        d = self.d
+        logits = h2 @ l.w_router
+        _, ids = moe_topk_softmax(logits.detach(), d.topk, d.routing_mode)
+        ids = ids.long()
+        if d.routing_mode == "topk_then_softmax":
+            w = torch.softmax(logits.float().gather(1, ids), -1)
+        else:
+            w = torch.softmax(logits.float(), -1).gather(1, ids)
+        out = torch.zeros_like(h2)
+        for e in range(d.E):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h13 = h2[tok] @ l.w13_experts[e]
+            s = torch.nn.functional.silu(h13[:, :d.Fe]) * h13[:, d.Fe:]
+            out = out.index_add(0, tok, (s @ l.w2_experts[e]) * w[tok, slot].unsqueeze(-1).to(h2.dtype))
+        return out
 
     def loss(self, tokens, targets, bounds, total_rows=None):
         logits = self.forward(tokens, bounds).float()
