@@ -9,3 +9,9 @@ from .trace import Interval, RunTrace, compare_to_sim_eventlog, trace_from_dict,
 
 CudaBackend = getattr(_runtime, "CudaBackend", None)
 VmmArena = getattr(_runtime, "VmmArena", None)
+
+
+def set_nvtx(on: bool) -> None:
+    """Turn NVTX ranges around tasks and transfers on or off (profiler control)."""
+    from . import _runtime
+    _runtime.set_nvtx(bool(on))

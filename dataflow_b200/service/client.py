@@ -133,5 +133,5 @@ class EngineClient:
     def destroy_peer_group(self, name: str): return self.call("destroy_peer_group", name=name)
     def list_peer_groups(self): return self.call("list_peer_groups")["groups"]
     def p2p_bench(self, peer: str, nbytes: int = 1 << 24): return self.call("p2p_bench", peer=peer, nbytes=nbytes)
-    def coll_bench(self, group: str, op: str = "allreduce", nbytes: int = 1 << 20): return self.call("coll_bench", group=group, op=op, nbytes=nbytes)
+    def coll_bench(self, group: str, op: str = "allreduce", nbytes: int = 1 << 20): return self.call("coll_bench", group=group, coll_op=op, nbytes=nbytes)
     def profiler_control(self, action: str): return self.call("profiler_control", action=action)

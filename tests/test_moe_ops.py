@@ -105,11 +105,13 @@ def test_gpu_grouped_gemms_match_eager():
     torch.cuda.synchronize()
     assert native().gemm_last_error() == 0
     ref = E.moe_grouped_mm(xp, W, tile_e)
-    assert ((h.float() - ref.float()).norm() / ref.float().norm()) < 5e-3
+    used = int(offp[-1])                    # row tiles past the last expert are skipped by the kernel: never read
+    assert ((h[:used].float() - ref[:used].float()).norm() / ref.float().norm()) < 5e-3
+    h[used:].zero_()
     # dgrad through the transpose: (Mp, 2F) x W^T -> (Mp, d)
     dx = C.moe_grouped_mm(h, W, tile_e, transpose_w=True)
     refd = E.moe_grouped_mm(h, W, tile_e, transpose_w=True)
-    assert ((dx.float() - refd.float()).norm() / refd.float().norm()) < 5e-3
+    assert ((dx[:used].float() - refd[:used].float()).norm() / refd.float().norm()) < 5e-3
     # wgrad, create then accumulate
     dW = torch.full_like(W, float("nan"))
     C.moe_grouped_wgrad(xp, h, offp, dW, accumulate=False)
