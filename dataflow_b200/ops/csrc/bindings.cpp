@@ -327,6 +327,51 @@ static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c
   TORCH_CHECK(rc == 0, "tp_gemm_rs launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- expert-parallel fused kernels
+static void ep_dispatch_mm(std::vector<int64_t> x_src, Tensor& xp, const Tensor& row_src, const Tensor& w, bool transpose_w, Tensor& y,
+                           const Tensor& tile_expert, int64_t tokens_per_rank, int64_t rank, Tensor& tile_flags,
+                           std::vector<int64_t> ready, std::vector<int64_t> acks, int64_t launch_seq, double timeout_s,
+                           Tensor& err, Tensor& done_ctr) {
+  CHECK_I32(err);
+  CHECK_BF16(xp); CHECK_BF16(w); CHECK_BF16(y); CHECK_I32(row_src); CHECK_I32(tile_expert); CHECK_I32(tile_flags); CHECK_I32(done_ctr);
+  const int64_t Mp = xp.size(0), K = xp.size(1), E = w.size(0);
+  const int64_t N = transpose_w ? w.size(1) : w.size(2);
+  TORCH_CHECK((transpose_w ? w.size(2) : w.size(1)) == K, "ep_dispatch_mm: weight inner extent must match the activations");
+  TORCH_CHECK(y.size(0) == Mp && y.size(1) == N && row_src.numel() >= Mp && tile_expert.numel() * 256 >= Mp &&
+              tile_flags.numel() * 256 >= Mp, "ep_dispatch_mm: table extents");
+  std::vector<unsigned long long> xs(x_src.begin(), x_src.end()), rd(ready.begin(), ready.end()), ak(acks.begin(), acks.end());
+  int rc = dfb::moe_grouped_mm_gather(xs.data(), xp.data_ptr(), row_src.data_ptr<int>(), w.data_ptr(), y.data_ptr(),
+                                      tile_expert.data_ptr<int>(), Mp, N, K, E, transpose_w ? 0 : 1, tokens_per_rank, rank,
+                                      xs.size(), reinterpret_cast<unsigned int*>(tile_flags.data_ptr<int>()), rd.data(), ak.data(),
+                                      (unsigned)launch_seq, timeout_s, err.data_ptr<int>(),
+                                      reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "ep_dispatch_mm launch failed with code ", rc);
+}
+static void ep_pull_rows(const Tensor& tables_dev, const Tensor& ids, Tensor& rows_local, int64_t e_local, int64_t my_first_slot) {
+  CHECK_I32(ids); CHECK_I32(rows_local);
+  TORCH_CHECK(tables_dev.scalar_type() == at::kLong && tables_dev.is_cuda(), "ep_pull_rows: the pointer table is a device int64 tensor");
+  int rc = dfb::ep_pull_rows(reinterpret_cast<const unsigned long long*>(tables_dev.data_ptr<int64_t>()), ids.data_ptr<int>(),
+                             rows_local.data_ptr<int>(), ids.numel(), e_local, my_first_slot, cur_stream());
+  TORCH_CHECK(rc == 0, "ep_pull_rows launch failed with code ", rc);
+}
+static void ep_combine(std::vector<int64_t> rows, std::vector<int64_t> scal, c10::optional<Tensor> base, c10::optional<Tensor> route_w,
+                       const Tensor& ids, const Tensor& rows_local, Tensor& out, c10::optional<Tensor> out_s, int64_t e_local,
+                       int64_t rank, std::vector<int64_t> ready, std::vector<int64_t> acks, int64_t seq, double timeout_s,
+                       Tensor& err, Tensor& done_ctr) {
+  CHECK_BF16(out); CHECK_I32(ids); CHECK_I32(rows_local); CHECK_I32(err); CHECK_I32(done_ctr);
+  const int64_t T = ids.size(0), K = ids.size(1), d = out.size(1);
+  std::vector<unsigned long long> rw(rows.begin(), rows.end()), sc(scal.begin(), scal.end()), rd(ready.begin(), ready.end()),
+      ak(acks.begin(), acks.end());
+  if (route_w.has_value()) CHECK_F32((*route_w));
+  if (out_s.has_value()) CHECK_F32((*out_s));
+  int rc = dfb::ep_combine(rw.data(), sc.empty() ? nullptr : sc.data(), base.has_value() ? base->data_ptr() : nullptr,
+                           route_w.has_value() ? route_w->data_ptr<float>() : nullptr, ids.data_ptr<int>(),
+                           rows_local.data_ptr<int>(), out.data_ptr(), out_s.has_value() ? out_s->data_ptr<float>() : nullptr, T, K, d,
+                           e_local, rank, rw.size(), rd.data(), ak.data(), (unsigned)seq, timeout_s, err.data_ptr<int>(),
+                           reinterpret_cast<unsigned int*>(done_ctr.data_ptr<int>()), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "ep_combine launch failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- interop
 // Zero-copy tensor over engine-owned memory (device or pinned host).
 static Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
@@ -380,6 +425,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rowdot", &moe_rowdot);
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
+  m.def("ep_dispatch_mm", &ep_dispatch_mm);
+  m.def("ep_pull_rows", &ep_pull_rows);
+  m.def("ep_combine", &ep_combine);
   m.def("tp_ag_gemm", &tp_ag_gemm);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("param_gather", &param_gather);

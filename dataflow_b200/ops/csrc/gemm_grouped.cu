@@ -10,6 +10,11 @@
 //           one tile per (expert, 256 x 256 block of dW); the contraction runs over the expert's padded row range
 //           ``offsets_pad[e] .. offsets_pad[e + 1]`` read on the device (padding rows are zero: they add nothing);
 //           experts with no rows are skipped (the host zero-fills dW when it is not accumulating).
+//   mode 0 + GATHER (expert parallelism: the dispatch all-to-all fused into the up-projection): the rows of X do
+//           not exist locally yet.  Four extra copy warps per CTA pull them from the ranks that own the tokens
+//           (``row_src[r]`` = source rank * tokens_per_rank + token; plain peer loads over NVLink) into the local X,
+//           each CTA of a pair filling its own 128 rows of a tile, and bump the tile's arrival counter; the TMA
+//           producer of a tile waits for that counter.  Transfer and multiplication overlap tile by tile.
 // Pipeline, barriers and the TMA-store epilogue are those of gemm_tcgen05_2sm.cu.  Every wait is bounded.
 // Reference role: src/dataflow_training/kernels/moe_grouped_gemm.py:190-339 (Triton, device prefix search).
 #include <cuda.h>
@@ -31,6 +36,8 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
+constexpr int COPY_THREADS = 128;
+constexpr int kMaxWorld = 8;
 constexpr int EPI_BOX_BYTES = 32 * 128;
 constexpr int EPI_BYTES = 4 * 2 * EPI_BOX_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 256;
@@ -43,7 +50,46 @@ struct Params {
   int accumulate;                // mode 1: dW += (fetched through the same 3-D map)
   int group_m;
   int* err;
+  // GATHER (mode 0): rows pulled from the token owners
+  const unsigned char* x_src[kMaxWorld];    // every rank's (tokens_per_rank, K) activations (peer pointers)
+  unsigned char* x_dst;                     // local X, (Mp, K)
+  const int* row_src;                       // Mp entries: rank * tokens_per_rank + token, or -1 (padding: zero row)
+  int tokens_per_rank;
+  int rank, world;
+  unsigned int* tile_flags;                 // local, one per row tile, zeroed in front of the launch
+  unsigned int flag_target;                 // 2: each CTA of a pair fills half a tile
+  unsigned int* ready[kMaxWorld];           // rank r's "my activations may be read, launch seq" word
+  unsigned int* acks[kMaxWorld];            // rank r's "readers are done with my activations" counter
+  unsigned int seq, ack_expect;
+  unsigned long long timeout_ns;
+  unsigned int* done_ctr;
 };
+
+DFB_DEVICE unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+DFB_DEVICE unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+DFB_DEVICE unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+template <bool SYS>
+DFB_DEVICE bool wait_ge(const unsigned int* p, unsigned int want, unsigned long long timeout_ns, volatile int* abort_flag) {
+  unsigned long long t0 = gtimer();
+  for (;;) {
+    unsigned int v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if (static_cast<int>(v - want) >= 0) return true;
+    if (*abort_flag || gtimer() - t0 > timeout_ns) return false;
+    __nanosleep(200);
+  }
+}
 
 struct SharedBarriers {
   uint64_t full[STAGES];
@@ -84,8 +130,8 @@ DFB_DEVICE bool get_tile(const Params& p, int tile, int m_blocks, int n_blocks, 
   return t.kblocks > 0;
 }
 
-template <int MODE, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+template <int MODE, bool B_MN, bool GATHER = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS + (GATHER ? COPY_THREADS : 0), 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_d, Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -115,6 +161,10 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     ptx::tmem_alloc_pair(&sb->tmem_base, TMEM_COLS);
     ptx::tmem_relinquish_pair();
   }
+  if (GATHER && blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ready[p.rank]), "r"(p.seq) : "memory");
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_sync();
@@ -125,9 +175,18 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (ptx::elect_one()) {
       uint32_t it = 0;
+      int have_tile = -1;
       for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters) {
         Tile t;
         if (!get_tile<MODE>(p, tile, m_blocks, n_blocks, t)) continue;
+        if (GATHER && t.mb != have_tile) {
+          // both halves of this row tile must have landed in the local X
+          if (!wait_ge<false>(&p.tile_flags[t.mb], p.flag_target, p.timeout_ns, abort_flag)) {
+            sb->abort = 1; atomicExch(p.err, (41 << 8)); break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+          have_tile = t.mb;
+        }
         const int m0 = t.mb * BM + static_cast<int>(cta) * HALF_M;
         const int n0 = t.nb * BN + static_cast<int>(cta) * HALF_N;
         for (int kb = 0; kb < t.kblocks; ++kb, ++it) {
@@ -192,7 +251,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         ptx::umma_commit_pair(&sb->tmem_full[acc], 0x3);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue: boxes through shared memory + TMA
     const int q = warp & 3;
     uint8_t* my_smem = epi_smem + q * 2 * EPI_BOX_BYTES;
@@ -268,10 +327,72 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     if (lane == 0) ptx::tma_store_wait<0>();
     __syncwarp();
+  } else if (GATHER) {
+    // ------------------------------------------------------------------ copy warps: the dispatch all-to-all
+    const int t = threadIdx.x - THREADS;                         // 0 .. 127
+    const long long row_vecs = static_cast<long long>(p.K) / 8;   // 16-byte vectors per row
+    __shared__ int copy_failed;
+    __shared__ int srcs[HALF_M];
+    if (t == 0) copy_failed = 0;
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    // every peer's activations must be final before the first remote row is read
+    if (t < p.world && t != p.rank) {
+      if (!wait_ge<true>(p.ready[t], p.seq, p.timeout_ns, abort_flag)) { atomicExch(p.err, (42 << 8) | t); copy_failed = 1; }
+    }
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    // row tiles in the order the GEMM consumes them; this CTA fills its own 128 rows of each
+    for (int mb = cluster_id; mb < m_blocks && !copy_failed; mb += num_clusters) {
+      if (p.tile_expert[mb] < 0) continue;
+      const long long r0 = static_cast<long long>(mb) * BM + static_cast<long long>(cta) * HALF_M;
+      srcs[t] = p.row_src[r0 + t];
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      uint4* dst = reinterpret_cast<uint4*>(p.x_dst) + r0 * row_vecs;
+      const long long n_vec = static_cast<long long>(HALF_M) * row_vecs;
+      for (long long v = t; v < n_vec; v += 4 * COPY_THREADS) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long vv = v + u * COPY_THREADS;
+          x[u] = make_uint4(0, 0, 0, 0);
+          if (vv < n_vec) {
+            const int row = static_cast<int>(vv / row_vecs);
+            const int s = srcs[row];
+            if (s >= 0) {
+              const int rk = s / p.tokens_per_rank, tok = s - rk * p.tokens_per_rank;
+              x[u] = __ldcg(reinterpret_cast<const uint4*>(p.x_src[rk]) + static_cast<long long>(tok) * row_vecs + (vv - row * row_vecs));
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long vv = v + u * COPY_THREADS;
+          if (vv < n_vec) dst[vv] = x[u];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (t == 0) atomicAdd(&p.tile_flags[mb], 1u);
+    }
+    if (copy_failed && t == 0) sb->abort = 1;
   }
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (GATHER) {
+    // the last CTA tells every peer that this rank is done reading, then holds the kernel until every peer is done
+    // reading this rank's activations
+    __shared__ int is_last;
+    __threadfence();
+    if (threadIdx.x == 0) is_last = (atomicAdd(p.done_ctr, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (is_last && threadIdx.x == 0) {
+      *p.done_ctr = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        if (r != p.rank) asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.acks[r]), "r"(1u) : "memory");
+      if (!wait_ge<true>(p.acks[p.rank], p.ack_expect, p.timeout_ns, abort_flag)) atomicExch(p.err, (43 << 8) | p.rank);
+    }
+  }
   if (*abort_flag && threadIdx.x == 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -352,6 +473,48 @@ int moe_grouped_mm(const void* X, const void* W, void* Y, const int* tile_expert
     kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, td, p);
   };
   if (w_kn) launch(gemm_grouped_kernel<0, true>, 1); else launch(gemm_grouped_kernel<0, false>, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Expert-parallel dispatch fused with the grouped up-projection: like moe_grouped_mm, but the rows of X are pulled
+// from the ranks that own the tokens while the GEMM runs.  ``x_src[r]``: rank r's (tokens_per_rank, K) activations
+// (peer pointers); ``X``: the local (Mp, K) matrix the kernel fills; ``row_src``: Mp device ints (global token or -1).
+int moe_grouped_mm_gather(const unsigned long long* x_src, void* X, const int* row_src, const void* W, void* Y,
+                          const int* tile_expert, int Mp, int N, int K, int E, int w_kn, int tokens_per_rank, int rank,
+                          int world, unsigned int* tile_flags, const unsigned long long* ready, const unsigned long long* acks,
+                          unsigned int launch_seq, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t stream) {
+  using namespace gemmg;
+  if (Mp <= 0) return 0;
+  if (Mp % BM || N % 8 || K % 8 || world > kMaxWorld) return -2;
+  CUtensorMap ta, tb, td;
+  bool ok = map2(&ta, X, K, Mp, K, BK, HALF_M);
+  ok = ok && (w_kn ? map3(&tb, W, N, K, E, 64, BK) : map3(&tb, W, K, N, E, BK, HALF_N));
+  ok = ok && map2(&td, Y, N, Mp, N, 64, 32);
+  if (!ok) return -4;
+  Params p{};
+  p.M = Mp; p.N = N; p.K = K; p.E = E; p.tile_expert = tile_expert; p.group_m = 4; p.err = err;
+  for (int r = 0; r < world; ++r) {
+    p.x_src[r] = reinterpret_cast<const unsigned char*>(x_src[r]);
+    p.ready[r] = reinterpret_cast<unsigned int*>(ready[r]);
+    p.acks[r] = reinterpret_cast<unsigned int*>(acks[r]);
+  }
+  p.x_dst = reinterpret_cast<unsigned char*>(X); p.row_src = row_src; p.tokens_per_rank = tokens_per_rank;
+  // arrival counters start from zero every launch (tiles past the last expert are never filled)
+  cudaMemsetAsync(tile_flags, 0, sizeof(unsigned int) * (Mp / BM), stream);
+  p.rank = rank; p.world = world; p.tile_flags = tile_flags; p.flag_target = 2u;
+  p.seq = launch_seq; p.ack_expect = static_cast<unsigned int>(world - 1) * launch_seq;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9); p.done_ctr = done_ctr;
+  int clusters = num_sms / 2;
+  int grid = 2 * clusters;          // every pair takes part in the copy, whatever the tile count
+  auto launch = [&](auto kernel, int idx) {
+    static bool configured[2] = {false, false};
+    if (!configured[idx]) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      configured[idx] = true;
+    }
+    kernel<<<grid, THREADS + COPY_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, p);
+  };
+  if (w_kn) launch(gemm_grouped_kernel<0, true, true>, 1); else launch(gemm_grouped_kernel<0, false, true>, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -94,6 +94,18 @@ int moe_combine(const void* base, const void* yp, const float* w, const int* row
 int moe_dispatch_bwd(const void* dxp, const int* row_of, void* out, int t, int d, int K, int accumulate, cudaStream_t s);
 int moe_scale_rows(void* xp, const float* w, const int* row_of, int slots, int d, cudaStream_t s);
 int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int slots, int d, cudaStream_t s);
+// expert parallelism: dispatch fused into the grouped up-projection; pull-and-reduce combine (gemm_grouped.cu, moe_ep.cu)
+int moe_grouped_mm_gather(const unsigned long long* x_src, void* X, const int* row_src, const void* W, void* Y,
+                          const int* tile_expert, int Mp, int N, int K, int E, int w_kn, int tokens_per_rank, int rank,
+                          int world, unsigned int* tile_flags, const unsigned long long* ready, const unsigned long long* acks,
+                          unsigned int launch_seq, double timeout_s, int* err, unsigned int* done_ctr, int num_sms,
+                          cudaStream_t stream);
+int ep_pull_rows(const unsigned long long* tables_dev_array, const int* ids, int* rows_local, int n, int e_local,
+                 long long my_first_slot, cudaStream_t stream);
+int ep_combine(const unsigned long long* rows, const unsigned long long* scal, const void* base, const float* route_w,
+               const int* ids, const int* rows_local, void* out, float* out_s, int T, int K, int d, int e_local, int rank,
+               int world, const unsigned long long* ready, const unsigned long long* acks, unsigned int seq,
+               double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t stream);
 int moe_grouped_mm(const void* X, const void* W, void* Y, const int* tile_expert, int Mp, int N, int K, int E, int w_kn,
                    int num_sms, cudaStream_t stream);
 int moe_grouped_wgrad(const void* X, const void* dY, void* dW, const int* offsets_pad, int Mp, int Kw, int N, int E,

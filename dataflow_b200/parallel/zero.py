@@ -97,6 +97,7 @@ class DpGroup:
         self.comm_stream = None
         self.done_async = None
         self.async_comm = False
+        self.force_stage = False       # tests: treat every published buffer as if it had overflowed the slab
         self.name = "dp"
 
     # -- set-up (p2p lane): map every rank's slab and control block
@@ -111,6 +112,10 @@ class DpGroup:
         if not base:
             raise RuntimeError("the p2p lane needs the engine's fast slab to exist before attach()")
         self.slab_base, self.slab_cap = base, cap
+        # staging behind the managed extent (same allocation, so the peers' mapping covers it): two halves, one for
+        # launches on the compute stream, one for the communication stream
+        self.tail_bytes = int(trainer.session.native.fast_tail())
+        self.staged = 0
         self.ctrl = be.device_alloc_zeroed(16 * self.SLOTS)
         mine = (be.ipc_handle(base), be.ipc_handle(self.ctrl))
         handles: list[Any] = [None] * self.world
@@ -133,10 +138,25 @@ class DpGroup:
         self.async_comm = os.environ.get("DATAFLOW_ASYNC_COMM", "1") != "0"
         dist.barrier()
 
-    def _in_slab(self, ptr: int, nbytes: int) -> None:
-        if not (self.slab_base <= ptr and ptr + nbytes <= self.slab_base + self.slab_cap):
-            raise RuntimeError("a buffer published to peers lies outside the peer-mapped engine slab "
-                               "(slab overflow): raise the budget headroom")
+    def _in_slab(self, t, nbytes: int, asynchronous: bool = False) -> int:
+        """Address of ``t``'s first ``nbytes`` that the peers can read.  A buffer inside the slab is its own address;
+        one that overflowed the slab (a vendor allocation the peers never mapped) is copied into the staging half of
+        the calling stream first — the kernel that reads it holds the stream until every peer is done reading, so
+        the next copy into the same half cannot overtake a reader."""
+        ptr = t.data_ptr()
+        if self.slab_base <= ptr and ptr + nbytes <= self.slab_base + self.slab_cap and not self.force_stage:
+            return ptr
+        half = self.tail_bytes // 2
+        if nbytes > half:
+            raise RuntimeError("a buffer published to peers lies outside the peer-mapped engine slab and is larger "
+                               f"than the staging behind it ({nbytes} > {half} bytes)")
+        from ..ops import native
+        import torch
+        dst_ptr = self.slab_base + self.slab_cap + (half if asynchronous else 0)
+        dst = native().tensor_from_ptr(dst_ptr, [nbytes], "uint8", self.device)
+        dst.copy_(t.reshape(-1).view(torch.uint8)[:nbytes])
+        self.staged += 1
+        return dst_ptr
 
     def side(self, ctx, ready_ids):
         """Context for an asynchronous launch: the communication stream, ordered after everything the compute
@@ -182,8 +202,8 @@ class DpGroup:
             from ..ops import native
             from ..ops.cuda import LAUNCHES
             seq, ack = self._next(slot)
-            self._in_slab(grad.data_ptr(), grad.numel() * 2)
-            native().zero_rs_adamw(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, grad.data_ptr(),
+            gptr = self._in_slab(grad, grad.numel() * 2)
+            native().zero_rs_adamw(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, gptr,
                                    begin_elem, len_elem, master, m, v, shard_out.data_ptr(),
                                    [f[0] for f in fields], [f[1] for f in fields], [f[2] for f in fields],
                                    lr, b1, b2, eps, int(step), 1.0, self.timeout_s, self.err, self.done)
@@ -222,8 +242,8 @@ class DpGroup:
             from ..ops import native
             from ..ops.cuda import LAUNCHES
             seq, ack = self._next(slot)
-            self._in_slab(grad.data_ptr(), grad.numel() * 2)
-            native().zero_rs_accum(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, grad.data_ptr(),
+            gptr = self._in_slab(grad, grad.numel() * 2, asynchronous)
+            native().zero_rs_accum(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, gptr,
                                    begin_elem, len_elem, gacc, bool(first), self.timeout_s, self.err,
                                    self.done_async if asynchronous else self.done)
             LAUNCHES.total += 1
@@ -245,8 +265,8 @@ class DpGroup:
             from ..ops import native
             from ..ops.cuda import LAUNCHES
             seq, ack = self._next(slot)
-            self._in_slab(shard.data_ptr(), min(per_bytes, shard.numel()))
-            native().param_gather(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, shard.data_ptr(),
+            sptr = self._in_slab(shard, min(per_bytes, shard.numel()), asynchronous)
+            native().param_gather(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, sptr,
                                   full.data_ptr(), per_bytes, total, self.timeout_s, self.err,
                                   self.done_async if asynchronous else self.done)
             LAUNCHES.total += 1

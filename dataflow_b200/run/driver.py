@@ -171,6 +171,13 @@ class Trainer:
             from ..lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
             lee = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else int(leeway_bytes)
             spare = min(lee * 3 // 4, 1 << 30) if budget is not None else 0
+            zero_md = (self.program.metadata or {}).get("zero")
+            if zero_md and int(zero_md.get("world", 1)) > 1:
+                # staging behind the slab, mapped by the peers with it: a published buffer (gradient, parameter slice)
+                # that overflowed the slab is copied there first; one region per stream that publishes
+                sizes_all = self.program.object_sizes()
+                pub = max((b for oid, b in sizes_all.items() if oid.startswith(("dW", "W", "dEmbed", "dHead", "Embed", "Head"))), default=0)
+                self.session.native.set_fast_tail(2 * (int(pub) + 4096))
             self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0)
         self.step_index = 0
         self.last_result = None

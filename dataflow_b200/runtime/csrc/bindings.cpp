@@ -204,6 +204,8 @@ PYBIND11_MODULE(_runtime, m) {
       .def_readonly("d2h_stream", &Session::d2h_stream)
       .def("ensure_pools", &Session::ensure_pools, py::arg("fast_cap"), py::arg("backing_cap"), py::arg("headroom") = 0.0)
       .def("fast_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.fast_pool.slab_base()), s.fast_pool.slab_capacity()); })
+      .def("set_fast_tail", [](Session& s, size_t bytes) { s.fast_pool.set_tail(bytes); })
+      .def("fast_tail", [](Session& s) { return s.fast_pool.slab_tail(); })
       .def("backing_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.backing_pool.slab_base()), s.backing_pool.slab_capacity()); })
       .def("vendor_allocs", [](Session& s) { return s.fast_pool.vendor_allocs + s.backing_pool.vendor_allocs; })
       .def("trim", [](Session& s) { s.fast_pool.trim(); s.backing_pool.trim(); })

@@ -14,7 +14,7 @@ static inline double host_now_us() {
 // ----------------------------------------------------------------------------- BufferPool
 BufferPool::~BufferPool() {
   trim();
-  if (base_) be_->free(loc_, base_, slab_->capacity());
+  if (base_) be_->free(loc_, base_, alloc_bytes_);
 }
 
 void BufferPool::ensure_slab(size_t capacity) {
@@ -22,11 +22,14 @@ void BufferPool::ensure_slab(size_t capacity) {
   if (slab_ && slab_->capacity() >= capacity) return;
   if (slab_) {
     if (slab_->live_blocks()) return;   // cannot grow under live buffers; overflow handles the rest
-    be_->free(loc_, base_, slab_->capacity());
+    be_->free(loc_, base_, alloc_bytes_);
     slab_.reset();
     base_ = nullptr;
   }
-  base_ = be_->alloc(loc_, capacity);
+  // the tail (set_tail) lies behind the managed extent, in the same allocation: whoever maps the slab for peers
+  // gets it too, and the allocator never hands it out
+  alloc_bytes_ = capacity + tail_bytes_;
+  base_ = be_->alloc(loc_, alloc_bytes_);
   vendor_allocs++;
   slab_ = std::make_unique<SlabAllocator>(capacity);
 }

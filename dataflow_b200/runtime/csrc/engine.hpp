@@ -73,12 +73,16 @@ class BufferPool {
   void trim();
   size_t slab_capacity() const { return slab_ ? slab_->capacity() : 0; }
   void* slab_base() const { return base_; }
+  // bytes kept behind the managed extent of the NEXT slab allocation (staging that peers must be able to address)
+  void set_tail(size_t bytes) { tail_bytes_ = SlabAllocator::round_up(bytes, SlabAllocator::kAlign); }
+  size_t slab_tail() const { return base_ ? alloc_bytes_ - slab_->capacity() : 0; }
   int64_t slab_overflows = 0;
   int64_t vendor_allocs = 0;
  private:
   Backend* be_;
   Location loc_;
   void* base_ = nullptr;
+  size_t alloc_bytes_ = 0, tail_bytes_ = 0;
   std::unique_ptr<SlabAllocator> slab_;
   std::multimap<size_t, void*> free_exact_;
 };

@@ -29,6 +29,7 @@ def main():
     grp = make_dp_group(rank, world, rank if gpu else None, lane)
     tr = Trainer("llama3", cfg, budget_gib=None, device=rank if gpu else None, hyper=hyper, seed=5,
                  groups={"dp": grp}, lower_kwargs=zero_lower_kwargs(mode, rank, world), recompute=False)
+    grp.force_stage = os.environ.get("ZERO_TEST_FORCE_STAGE") == "1"
     if mode == "fsdp":
         assert any(t.id.startswith("grad_rs_") for t in tr.program.tasks)
     losses = []
@@ -47,6 +48,8 @@ def main():
     if rank == 0:
         json.dump({"losses": t.tolist(), "w0_sum": float(w0.double().sum()), "w0_abs": float(w0.double().abs().sum())},
                   open(out_path, "w"))
+    if grp.force_stage and gpu and lane == "p2p":
+        assert grp.staged > 0
     tr.close()
     dist.barrier()
     dist.destroy_process_group()
