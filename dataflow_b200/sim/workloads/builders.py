@@ -1,0 +1,381 @@
+"""Analytic training workloads: a model described by dimensions becomes a hardware-free ``WorkloadProgram``.
+
+No tensors are touched: every layer contributes closed-form FLOPs, bytes and saved-activation sizes, and
+``TrainingBuilder`` schedules them into forward / head / backward / recompute / optimizer tasks for a number of
+gradient-accumulation rounds.  The result is priced on any ``HardwareSpec`` (``schema.realize_workload``) and planned
+by any policy — the "what would this model do on that box" path that needs no GPU.
+Reference role: ``src/dataflow_sim/workloads/dataflow_builder/__init__.py:65-463`` (dtype policies, training and
+parallelism configs, symbolic tracing), ``workloads/training_builder.py:61-286`` (task scheduling, interleaved or tail
+optimizer), ``workloads/modules/*.py`` and ``workloads/ops/**`` (per-module FLOP / byte formulas, expert parallelism
+priced on the scale-up fabric).
+"""
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field, replace
+
+from .schema import SubOp, WorkloadCost, WorkloadObject, WorkloadOutput, WorkloadProgram, WorkloadTask
+
+DTYPE_BYTES = {"fp32": 4, "tf32": 4, "bf16": 2, "fp16": 2, "fp8": 1, "fp8_e4m3": 1, "fp8_e5m2": 1, "fp4": 0.5}
+
+
+@dataclass(frozen=True)
+class DTypePolicy:
+    param: str = "bf16"
+    grad: str = "bf16"
+    activation: str = "bf16"
+    compute: str = "bf16"
+    master: str | None = "fp32"
+    moments: str = "fp32"
+
+    def state_bytes_per_param(self, optimizer: str) -> float:
+        n_moments = {"adamw": 2, "muon": 1, "sgdm": 1, "sgd": 0, "frozen": 0}[optimizer]
+        return (DTYPE_BYTES[self.master] if self.master else 0) + n_moments * DTYPE_BYTES[self.moments]
+
+
+@dataclass(frozen=True)
+class ParallelismConfig:
+    dp: int = 1
+    tp: int = 1
+    ep_group_size: int = 1
+    zero_stage: int = 0
+
+
+@dataclass(frozen=True)
+class TrainingConfig:
+    seq_len: int = 4096
+    tokens_per_round: int = 16384
+    rounds: int = 1
+    optimizer: str = "adamw"
+    optimizer_placement: str = "interleaved"        # interleaved | tail
+    recompute: str = "none"                         # none | selective | full
+    dtypes: DTypePolicy = field(default_factory=DTypePolicy)
+    parallel: ParallelismConfig = field(default_factory=ParallelismConfig)
+
+
+@dataclass(frozen=True)
+class AttnSpec:
+    kind: str = "dense"             # dense | mla | dsa | linear | mamba | none
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    window: int = 0                 # sliding window (0: full causal)
+    q_lora: int = 0                 # MLA
+    kv_lora: int = 0
+    rope_dim: int = 0
+    v_head_dim: int = 0
+    index_heads: int = 0            # DSA indexer
+    index_dim: int = 0
+    index_topk: int = 0
+    state_dim: int = 0              # linear attention / mamba state per head
+
+
+@dataclass(frozen=True)
+class MlpSpec:
+    kind: str = "swiglu"            # swiglu | relu2 | gelu | moe | none
+    d_ff: int = 0
+    n_experts: int = 0
+    top_k: int = 0
+    d_expert: int = 0
+    n_shared: int = 0
+    expert_act: str = "swiglu"      # swiglu | relu2
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    attn: AttnSpec
+    mlp: MlpSpec
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    name: str
+    d_model: int
+    vocab: int
+    layers: tuple
+    tied_embeddings: bool = False
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+
+# ------------------------------------------------------------------------------------------- per-module formulas
+def attn_params(a: AttnSpec, d: int) -> int:
+    if a.kind == "none":
+        return 0
+    if a.kind in ("mla", "dsa"):
+        dq = a.head_dim + a.rope_dim
+        q = (d * a.q_lora + a.q_lora * a.n_heads * dq) if a.q_lora else d * a.n_heads * dq
+        kv = d * (a.kv_lora + a.rope_dim) + a.kv_lora * a.n_heads * (a.head_dim + a.v_head_dim)
+        o = a.n_heads * a.v_head_dim * d
+        idx = d * a.index_heads * a.index_dim + d * a.index_dim + d * a.index_heads if a.kind == "dsa" else 0
+        return q + kv + o + idx
+    if a.kind in ("linear", "mamba"):
+        inner = a.n_heads * a.head_dim
+        return d * (2 * a.n_kv_heads * a.state_dim + 2 * inner) + inner * d + 2 * d * a.n_heads
+    return d * (a.n_heads + 2 * a.n_kv_heads) * a.head_dim + a.n_heads * a.head_dim * d
+
+
+def attn_core_flops(a: AttnSpec, tokens: int, seq: int) -> float:
+    """Forward FLOPs of the score / value part (projections are counted with the parameters)."""
+    if a.kind == "none":
+        return 0.0
+    if a.kind == "dense":
+        span = min(a.window, seq) if a.window else seq
+        causal = 0.5 if not a.window or a.window >= seq else 1.0
+        return 4.0 * tokens * span * a.n_heads * a.head_dim * causal
+    if a.kind == "mla":
+        return 2.0 * tokens * seq * a.n_heads * (a.head_dim + a.rope_dim + a.v_head_dim) * 0.5
+    if a.kind == "dsa":
+        keys = min(a.index_topk or seq, seq)
+        sparse = 2.0 * tokens * keys * a.n_heads * (a.kv_lora + a.rope_dim + a.kv_lora)        # absorbed form
+        index = 2.0 * tokens * seq * a.index_heads * a.index_dim * 0.5
+        return sparse + index
+    # chunked linear recurrences: state update + read per token
+    return 6.0 * tokens * a.n_heads * a.head_dim * max(a.state_dim, 1)
+
+
+def attn_saved_elems(a: AttnSpec, d: int) -> float:
+    """Activation elements saved per token for the backward (no recompute)."""
+    if a.kind == "none":
+        return 0.0
+    if a.kind in ("mla", "dsa"):
+        extra = a.index_topk / 8 + a.index_heads if a.kind == "dsa" else 0          # packed selection bits + index weights
+        return d + a.q_lora + a.kv_lora + a.rope_dim + a.n_heads * (a.head_dim + a.rope_dim) + a.n_heads * a.v_head_dim + extra
+    if a.kind in ("linear", "mamba"):
+        return d + 3 * a.n_heads * a.head_dim + 2 * a.n_kv_heads * a.state_dim
+    return d + (a.n_heads + 2 * a.n_kv_heads) * a.head_dim + a.n_heads * a.head_dim
+
+
+def mlp_params(m: MlpSpec, d: int) -> tuple[int, int]:
+    """(total, active per token)."""
+    gate = 3 if m.kind == "swiglu" else 2
+    if m.kind == "none":
+        return 0, 0
+    if m.kind != "moe":
+        p = gate * d * m.d_ff
+        return p, p
+    eg = 3 if m.expert_act == "swiglu" else 2
+    per = eg * d * m.d_expert
+    shared = m.n_shared * per
+    return m.n_experts * per + shared + d * m.n_experts, m.top_k * per + shared + d * m.n_experts
+
+
+def mlp_saved_elems(m: MlpSpec, d: int) -> float:
+    if m.kind == "none":
+        return 0.0
+    if m.kind != "moe":
+        return d + (2 if m.kind == "swiglu" else 1) * m.d_ff
+    width = (2 if m.expert_act == "swiglu" else 1) * m.d_expert
+    return d + (m.top_k + m.n_shared) * (d + width) + 2 * m.top_k
+
+
+# ------------------------------------------------------------------------------------------- the scheduler
+class TrainingBuilder:
+    """Schedules one optimizer step of ``model`` under ``cfg`` into a ``WorkloadProgram``."""
+
+    def __init__(self, model: ModelSpec, cfg: TrainingConfig):
+        self.m, self.cfg = model, cfg
+        self.act_b = DTYPE_BYTES[cfg.dtypes.activation]
+        self.par_b = DTYPE_BYTES[cfg.dtypes.param]
+        self.grad_b = DTYPE_BYTES[cfg.dtypes.grad]
+
+    # -- costs
+    def _mm(self, name: str, flops: float, bytes_: float = 0.0) -> SubOp:
+        return SubOp(name=name, kind="matmul", flops=flops, dtype=self.cfg.dtypes.compute, bytes=bytes_)
+
+    def _layer_cost(self, layer: LayerSpec, backward: bool) -> tuple[WorkloadCost, dict]:
+        cfg, d, T, S = self.cfg, self.m.d_model, self.cfg.tokens_per_round, self.cfg.seq_len
+        tp, ep = cfg.parallel.tp, cfg.parallel.ep_group_size
+        a, m = layer.attn, layer.mlp
+        mult = 2.0 if backward else 1.0                       # dgrad + wgrad
+        ops = []
+        ap = attn_params(a, d)
+        if ap:
+            ops.append(self._mm("attn_proj", mult * 2.0 * T * ap / tp, ap * self.par_b / tp))
+            core = attn_core_flops(a, T, S) / tp
+            ops.append(SubOp(name="attn_core", kind="attention", flops=(2.5 if backward else 1.0) * core, dtype=cfg.dtypes.compute))
+        total, active = mlp_params(m, d)
+        if total:
+            if m.kind == "moe":
+                routed = (active - m.n_shared * (3 if m.expert_act == "swiglu" else 2) * d * m.d_expert - d * m.n_experts)
+                ops.append(self._mm("experts", mult * 2.0 * T * routed, total * self.par_b / ep))
+                if m.n_shared:
+                    ops.append(self._mm("shared_experts", mult * 2.0 * T * (active - routed - d * m.n_experts) / tp))
+                ops.append(self._mm("router", mult * 2.0 * T * d * m.n_experts))
+                ops.append(SubOp(name="dispatch_combine_local", kind="memory", bytes=mult * 4.0 * T * m.top_k * d * self.act_b))
+                if ep > 1:
+                    # dispatch + combine cross the scale-up fabric once each way (and again in the backward)
+                    ops.append(SubOp(name="ep_all_to_all", kind="scale_up", bytes=2.0 * T * m.top_k * d * self.act_b * (ep - 1) / ep))
+            else:
+                ops.append(self._mm("mlp", mult * 2.0 * T * active / tp, total * self.par_b / tp))
+        if tp > 1:
+            # sequence-parallel all-gather + reduce-scatter around attention and around the MLP
+            ops.append(SubOp(name="tp_collectives", kind="scale_up", bytes=mult * 4.0 * T * d * self.act_b * (tp - 1) / tp))
+        elem = (attn_saved_elems(a, d) + mlp_saved_elems(m, d)) / max(tp, 1)
+        ops.append(SubOp(name="elementwise", kind="memory", bytes=(3.0 if backward else 2.0) * T * elem * self.act_b))
+        info = {"params": (ap + total), "local_params": ap / tp + (total / ep if m.kind == "moe" else total / tp),
+                "saved_bytes": int(T * elem * self.act_b)}
+        return WorkloadCost(ops=ops), info
+
+    # -- program
+    def build(self) -> WorkloadProgram:
+        cfg, mdl = self.cfg, self.m
+        d, T = mdl.d_model, cfg.tokens_per_round
+        dp = cfg.parallel.dp
+        objects, tasks, final = [], [], {}
+        opt_b = cfg.dtypes.state_bytes_per_param(cfg.optimizer)
+        shard = dp if cfg.parallel.zero_stage >= 1 else 1
+        infos = []
+        for i, layer in enumerate(mdl.layers):
+            _, info = self._layer_cost(layer, False)
+            infos.append(info)
+            wb = int(info["local_params"] * self.par_b / (dp if cfg.parallel.zero_stage >= 3 else 1))
+            objects.append(WorkloadObject(id=f"W_{i}", bytes=wb, type="parameter"))
+            final[f"W_{i}"] = "backing"
+            if opt_b:
+                objects.append(WorkloadObject(id=f"O_{i}", bytes=int(info["local_params"] * opt_b / shard), type="optimizer_state"))
+                final[f"O_{i}"] = "backing"
+        emb = mdl.vocab * d
+        head_params = 0 if mdl.tied_embeddings else emb
+        objects.append(WorkloadObject(id="W_embed", bytes=int(emb * self.par_b), type="parameter"))
+        final["W_embed"] = "backing"
+        if head_params:
+            objects.append(WorkloadObject(id="W_head", bytes=int(head_params * self.par_b), type="parameter"))
+            final["W_head"] = "backing"
+        if opt_b:
+            objects.append(WorkloadObject(id="O_embed", bytes=int((emb + head_params) * opt_b / shard), type="optimizer_state"))
+            final["O_embed"] = "backing"
+        head_w = "W_head" if head_params else "W_embed"
+        x_bytes = int(T * d * self.act_b)
+        L = mdl.n_layers
+        recompute = cfg.recompute
+
+        def opt_task(i: int) -> WorkloadTask:
+            p = infos[i]["local_params"] / shard
+            ops = [SubOp(name="optimizer", kind="memory", bytes=p * (opt_b * 2 + self.par_b + self.grad_b))]
+            if cfg.optimizer == "muon":
+                ops.append(self._mm("newton_schulz", 5 * 3 * 2.0 * p * d))
+            if dp > 1:
+                ops.append(SubOp(name="grad_reduce", kind="scale_up", bytes=infos[i]["local_params"] * self.grad_b * (dp - 1) / dp *
+                                 (1 if cfg.parallel.zero_stage else 2)))
+            ins = [f"W_{i}", f"dW_{i}"] + ([f"O_{i}"] if opt_b else [])
+            return WorkloadTask(id=f"opt_{i}", inputs=ins, mutates=[f"W_{i}"] + ([f"O_{i}"] if opt_b else []),
+                                cost=WorkloadCost(ops=ops), phase="optimizer")
+
+        for r in range(cfg.rounds):
+            tasks.append(WorkloadTask(id=f"embed_{r}", inputs=["W_embed"], outputs=[WorkloadOutput(id=f"X_{r}_0", bytes=x_bytes, type="activation")],
+                                      cost=WorkloadCost(ops=[SubOp(name="embed", kind="memory", bytes=2.0 * x_bytes)]), phase="fwd", tokens=T))
+            for i, layer in enumerate(mdl.layers):
+                cost, info = self._layer_cost(layer, False)
+                saved = x_bytes if recompute == "full" else int(info["saved_bytes"] * (0.4 if recompute == "selective" else 1.0))
+                tasks.append(WorkloadTask(id=f"fwd_{r}_{i}", inputs=[f"X_{r}_{i}", f"W_{i}"],
+                                          outputs=[WorkloadOutput(id=f"A_{r}_{i}", bytes=saved, type="activation"),
+                                                   WorkloadOutput(id=f"X_{r}_{i + 1}", bytes=x_bytes, type="activation")],
+                                          cost=cost, workspace_bytes=int(info["saved_bytes"]), phase="fwd", tokens=T))
+            head_flops = 2.0 * T * d * mdl.vocab
+            tasks.append(WorkloadTask(id=f"head_{r}", inputs=[f"X_{r}_{L}", head_w] + (["dW_head"] if r else []),
+                                      outputs=[WorkloadOutput(id=f"dX_{r}_{L}", bytes=x_bytes, type="activation")] +
+                                      ([] if r else [WorkloadOutput(id="dW_head", bytes=int((head_params or emb) * self.grad_b), type="gradient")]),
+                                      mutates=["dW_head"] if r else [],
+                                      cost=WorkloadCost(ops=[self._mm("head_fwd_bwd", 3.0 * head_flops),
+                                                             SubOp(name="loss", kind="memory", bytes=4.0 * T * min(mdl.vocab, 8192) * 4)]),
+                                      workspace_bytes=int(T * min(mdl.vocab, 8192) * 4), phase="head", tokens=T))
+            for i in reversed(range(L)):
+                layer = mdl.layers[i]
+                bcost, info = self._layer_cost(layer, True)
+                act_in = f"A_{r}_{i}"
+                if recompute != "none":
+                    fcost, _ = self._layer_cost(layer, False)
+                    frac = 1.0 if recompute == "full" else 0.35
+                    rc = WorkloadCost(ops=[replace_flops(op, frac) for op in fcost.ops])
+                    tasks.append(WorkloadTask(id=f"recompute_{r}_{i}", inputs=[f"A_{r}_{i}", f"W_{i}"],
+                                              outputs=[WorkloadOutput(id=f"R_{r}_{i}", bytes=int(info["saved_bytes"]), type="activation")],
+                                              cost=rc, phase="recompute", tokens=T))
+                    act_in = f"R_{r}_{i}"
+                first = r == 0
+                ins = [f"dX_{r}_{i + 1}", act_in, f"W_{i}"] + ([] if first else [f"dW_{i}"])
+                outs = [WorkloadOutput(id=f"dX_{r}_{i}", bytes=x_bytes, type="activation")]
+                if first:
+                    outs.append(WorkloadOutput(id=f"dW_{i}", bytes=int(info["local_params"] * self.grad_b), type="gradient"))
+                tasks.append(WorkloadTask(id=f"bwd_{r}_{i}", inputs=ins, outputs=outs, mutates=[] if first else [f"dW_{i}"],
+                                          cost=bcost, workspace_bytes=int(info["saved_bytes"]), phase="bwd", tokens=T))
+                if r == cfg.rounds - 1 and cfg.optimizer_placement == "interleaved" and cfg.optimizer != "frozen":
+                    tasks.append(opt_task(i))
+            tasks.append(WorkloadTask(id=f"embed_bwd_{r}", inputs=[f"dX_{r}_0"] + (["dW_embed"] if r else []),
+                                      outputs=[] if r else [WorkloadOutput(id="dW_embed", bytes=int(emb * self.grad_b), type="gradient")],
+                                      mutates=["dW_embed"] if r else [],
+                                      cost=WorkloadCost(ops=[SubOp(name="embed_bwd", kind="memory", bytes=3.0 * x_bytes)]), phase="bwd"))
+        if cfg.optimizer != "frozen":
+            if cfg.optimizer_placement == "tail":
+                tasks.extend(opt_task(i) for i in reversed(range(L)))
+            ins = ["W_embed", "dW_embed", "dW_head"] + (["W_head"] if head_params else []) + (["O_embed"] if opt_b else [])
+            tasks.append(WorkloadTask(id="opt_embed", inputs=ins, mutates=["W_embed"] + (["W_head"] if head_params else []) + (["O_embed"] if opt_b else []),
+                                      cost=WorkloadCost(ops=[SubOp(name="optimizer", kind="memory",
+                                                                   bytes=(emb + head_params) / shard * (opt_b * 2 + self.par_b + self.grad_b))]),
+                                      phase="optimizer"))
+        total_params = sum(i["params"] for i in infos) + emb + head_params
+        active = sum(attn_params(l.attn, d) + mlp_params(l.mlp, d)[1] for l in mdl.layers) + emb + head_params
+        md = {"model": mdl.name, "tokens_per_step": T * cfg.rounds, "seq_len": cfg.seq_len, "rounds": cfg.rounds,
+              "total_params": int(total_params), "active_params": int(active), "optimizer": cfg.optimizer,
+              "recompute": recompute, "parallel": asdict(cfg.parallel)}
+        return WorkloadProgram(name=f"{mdl.name}-train", objects=objects, tasks=tasks, final_locations=final, metadata=md)
+
+
+def replace_flops(op: SubOp, frac: float) -> SubOp:
+    return op.model_copy(update={"flops": op.flops * frac, "bytes": op.bytes * frac})
+
+
+def trace_training_model(model: ModelSpec, cfg: TrainingConfig) -> WorkloadProgram:
+    return TrainingBuilder(model, cfg).build()
+
+
+# ------------------------------------------------------------------------------------------- model library
+def _uniform(n: int, attn: AttnSpec, mlp: MlpSpec) -> tuple:
+    return tuple(LayerSpec(attn, mlp) for _ in range(n))
+
+
+def _hybrid(n: int, full: AttnSpec, lin: AttnSpec, mlp: MlpSpec, every: int = 4) -> tuple:
+    return tuple(LayerSpec(full if (i + 1) % every == 0 else lin, mlp) for i in range(n))
+
+
+def _dense_then(n: int, n_dense: int, attn: AttnSpec, dense: MlpSpec, moe: MlpSpec) -> tuple:
+    return tuple(LayerSpec(attn, dense if i < n_dense else moe) for i in range(n))
+
+
+_MLA = AttnSpec("mla", 128, 128, 128, q_lora=1536, kv_lora=512, rope_dim=64, v_head_dim=128)
+_DSA = replace(_MLA, kind="dsa", index_heads=64, index_dim=128, index_topk=2048)
+_GDN = AttnSpec("linear", 32, 16, 128, state_dim=128)
+
+MODEL_LIBRARY: dict[str, ModelSpec] = {
+    "llama3_8b": ModelSpec("llama3_8b", 4096, 128256, _uniform(32, AttnSpec("dense", 32, 8, 128), MlpSpec("swiglu", 14336))),
+    "llama3_70b": ModelSpec("llama3_70b", 8192, 128256, _uniform(80, AttnSpec("dense", 64, 8, 128), MlpSpec("swiglu", 28672))),
+    "qwen3_8b": ModelSpec("qwen3_8b", 4096, 151936, _uniform(36, AttnSpec("dense", 32, 8, 128), MlpSpec("swiglu", 12288))),
+    "qwen3_moe_30b_a3b": ModelSpec("qwen3_moe_30b_a3b", 2048, 151936,
+                                   _uniform(48, AttnSpec("dense", 32, 4, 128), MlpSpec("moe", 0, 128, 8, 768))),
+    "qwen3_hybrid_dense": ModelSpec("qwen3_hybrid_dense", 4096, 151936,
+                                    _hybrid(36, AttnSpec("dense", 32, 8, 128), _GDN, MlpSpec("swiglu", 12288))),
+    "qwen3_hybrid_moe": ModelSpec("qwen3_hybrid_moe", 2048, 151936,
+                                  _hybrid(48, AttnSpec("dense", 16, 2, 256), _GDN, MlpSpec("moe", 0, 512, 10, 512, 1))),
+    "olmoe_1b_7b": ModelSpec("olmoe_1b_7b", 2048, 50304, _uniform(16, AttnSpec("dense", 16, 16, 128), MlpSpec("moe", 0, 64, 8, 1024))),
+    "deepseek_v3": ModelSpec("deepseek_v3", 7168, 129280, _dense_then(61, 3, _MLA, MlpSpec("swiglu", 18432), MlpSpec("moe", 0, 256, 8, 2048, 1))),
+    "deepseek_v3_2": ModelSpec("deepseek_v3_2", 7168, 129280, _dense_then(61, 3, _DSA, MlpSpec("swiglu", 18432), MlpSpec("moe", 0, 256, 8, 2048, 1))),
+    "glm5": ModelSpec("glm5", 5120, 151552, _dense_then(92, 3, AttnSpec("dense", 96, 8, 128), MlpSpec("swiglu", 12288), MlpSpec("moe", 0, 160, 8, 1536, 1))),
+    "glm5_2": ModelSpec("glm5_2", 6144, 154880, _dense_then(78, 3, replace(_DSA, n_heads=64, n_kv_heads=64, q_lora=2048), MlpSpec("swiglu", 12288),
+                                                             MlpSpec("moe", 0, 256, 8, 2048, 1))),
+    "kimi_k2": ModelSpec("kimi_k2", 7168, 163840, _dense_then(61, 1, replace(_MLA, n_heads=64, n_kv_heads=64), MlpSpec("swiglu", 18432),
+                                                             MlpSpec("moe", 0, 384, 8, 2048, 1))),
+    "gpt_oss_120b": ModelSpec("gpt_oss_120b", 2880, 201088,
+                              tuple(LayerSpec(AttnSpec("dense", 64, 8, 64, window=128 if i % 2 == 0 else 0), MlpSpec("moe", 0, 128, 4, 2880))
+                                    for i in range(36))),
+    "nemotron_h_8b": ModelSpec("nemotron_h_8b", 4096, 131072,
+                               tuple(LayerSpec(AttnSpec("dense", 32, 8, 128), MlpSpec("none")) if i % 13 == 6 else
+                                     LayerSpec(AttnSpec("mamba", 128, 8, 64, state_dim=128), MlpSpec("none")) if i % 2 == 0 else
+                                     LayerSpec(AttnSpec("none"), MlpSpec("relu2", 21504)) for i in range(52))),
+}
+
+
+def get_model(name: str) -> ModelSpec:
+    if name not in MODEL_LIBRARY:
+        raise KeyError(f"unknown model {name!r}; known: {sorted(MODEL_LIBRARY)}")
+    return MODEL_LIBRARY[name]
