@@ -1,0 +1,82 @@
+"""Smoke runs of the command-line tools on the CPU (each through its ``main``)."""
+import importlib.util
+import json
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def tool(rel):
+    sys.path.insert(0, os.path.join(ROOT, "tools"))
+    spec = importlib.util.spec_from_file_location("tool_" + rel.replace("/", "_").replace(".py", ""), os.path.join(ROOT, "tools", rel))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_predict_step_grid_and_infeasible_rows(capsys, tmp_path):
+    out = tmp_path / "rows.json"
+    assert tool("bench/predict_step.py").main(["--preset", "llama3:tiny", "--budget", "0.0001,0.02,1", "--top", "2", "--json", str(out)]) == 0
+    rows = json.loads(out.read_text())
+    assert "INFEASIBLE" in rows[0]["note"] and rows[1]["tok_s"] > 0 and rows[2]["fast_gib"] <= 1
+    assert "most expensive tasks" in capsys.readouterr().out
+
+
+def test_export_then_trace_program(tmp_path, capsys):
+    assert tool("export/export_program.py").main(["--preset", "llama3:tiny", "--fast-gib", "0.02", "--recompute", "--out", str(tmp_path)]) == 0
+    for ext in ("program", "annotated", "webapp", "summary"):
+        assert (tmp_path / f"llama3-tiny.{ext}.json").exists()
+    assert tool("export/trace_program.py").main(["--program", str(tmp_path / "llama3-tiny.annotated.json"), "--kinds", "offload", "--intervals"]) == 0
+    assert "outcome SUCCESS" in capsys.readouterr().out
+
+
+def test_engine_gate_on_the_virtual_backend_matches_the_simulator(tmp_path):
+    assert tool("verify/engine_gate.py").main(["--config", "mini", "--fast-gib", "0.05", "--backend", "fake", "--out", str(tmp_path)]) == 0
+    s = json.loads((tmp_path / "engine_gate-mini.summary.json").read_text())
+    assert s["peak_equal"] and abs(s["gap_pct"]) < 1e-6
+
+
+def test_dispatch_floor_and_gap_census(capsys):
+    assert tool("bench/dispatch_floor.py").main(["--backend", "fake", "--tasks", "200", "--repeat", "2"]) == 0
+    assert "us/task" in capsys.readouterr().out
+    assert tool("bench/gap_census.py").main(["--preset", "llama3:tiny", "--device", "cpu", "--steps", "2"]) == 0
+    assert "compute intervals" in capsys.readouterr().out
+
+
+def test_planners_match_the_exact_oracle_on_tiny_chains(capsys):
+    assert tool("bench/pressurefit_exact_oracle.py").main(["--chains", "4", "--tasks", "6", "--tolerance", "0.05"]) == 0
+    assert "worst excess" in capsys.readouterr().out
+
+
+def test_verify_family_audit_and_listing(capsys):
+    vf = tool("verify/verify_family.py")
+    assert vf.main(["--list"]) == 0
+    assert "llama3" in capsys.readouterr().out
+    assert vf.main(["--family", "llama3", "--audit-only"]) == 0
+    assert vf.audit("no_such_family")
+
+
+def test_pressure_correctness_is_exact_on_the_host_backend():
+    assert tool("verify/pressure_correctness.py").main(["--budgets", "0.02", "--steps", "2"]) == 0
+
+
+def test_fetch_dataset_writes_shards_the_source_reads(tmp_path):
+    (tmp_path / "a.txt").write_text("first document\n\nsecond document, longer\n\nthird\n")
+    out = tmp_path / "ds"
+    assert tool("train/fetch_dataset.py").main(["--inputs", str(tmp_path / "*.txt"), "--out", str(out), "--split-paragraphs", "--val-fraction", "0.34"]) == 0
+    meta = json.loads((out / "corpus.meta.json").read_text())
+    assert meta["tokens"]["documents"] == 3 and meta["shards"] == {"train": 1, "val": 1}
+    from dataflow_b200.data.sources.shards import read_shard
+    ids = read_shard(str(out / "corpus_train_000000.bin"))
+    assert bytes(int(x) for x in ids if x < 256).startswith(b"first document")
+
+
+def test_doc_tools(capsys, tmp_path):
+    assert tool("gen_model_docs/list_models.py").main([]) == 0
+    assert "llama3_8b" in capsys.readouterr().out
+    assert tool("gen_model_docs/list_kernels.py").main(["--kernel-set", "eager"]) == 0
+    assert tool("gen_model_docs/gen_model_docs.py").main(["--out", str(tmp_path)]) == 0
+    assert (tmp_path / "index.md").exists() and "w_qkv" in (tmp_path / "llama3.md").read_text()
