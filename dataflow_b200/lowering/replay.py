@@ -33,7 +33,11 @@ def replay_program(program, durations_us: Mapping[str, float], *, h2d_bytes_per_
 
 
 def replay_makespan_us(program, durations_us: Mapping[str, float], **bw) -> float:
-    return float(simulate(to_sim_chain(replay_program(program, durations_us, **bw)), validate=False).makespan)
+    chain = to_sim_chain(replay_program(program, durations_us, **bw))
+    if (program.metadata or {}).get("workspace_accounting") == "external":
+        # the plan's capacity is the object pool alone; scratch lives outside it
+        chain = replace(chain, tasks=[replace(t, workspace_bytes=0) for t in chain.tasks])
+    return float(simulate(chain, validate=False).makespan)
 
 
 def replay_gap_pct(program, result, *, use_measured_links: bool = False) -> dict[str, float]:

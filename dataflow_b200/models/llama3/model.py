@@ -45,6 +45,9 @@ class ShapedLlama3Config:
     d_ff_expert: int = 0
     routing_mode: str = "topk_then_softmax"
     aux_coef: float = 0.0                # load-balance loss coefficient (gradient injected analytically)
+    # tensor + sequence parallelism (tp_mlp family): heads and FFN columns split over ``tp`` ranks, the residual
+    # stream split by rows
+    tp: int = 1
 
     @property
     def tokens_per_round(self) -> int:
@@ -78,6 +81,12 @@ class Llama3Dims:
     Fe: int = 0                          # expert FFN width
     routing_mode: str = "topk_then_softmax"
     aux_coef: float = 0.0
+    tp: int = 1                          # > 1: hq / hkv / F are this rank's share; the residual stream holds Ts rows
+
+    @property
+    def Ts(self) -> int:
+        """Rows of the residual stream this rank holds (sequence parallelism)."""
+        return self.T // self.tp
 
     @property
     def moe(self) -> bool:
@@ -149,12 +158,14 @@ def context_layout(d: Llama3Dims, level: int = 0) -> PackedLayout:
 
 
 def _context_layout_full(d: Llama3Dims) -> PackedLayout:
-    f = [Field("rstd_attn", (d.T,), "fp32"), Field("qkv", (d.T, d.qkv_dim), "bf16")]
+    # with tensor parallelism the norms and the residual stream see this rank's rows only (Ts); the attention and
+    # MLP intermediates see every row of this rank's heads / columns
+    f = [Field("rstd_attn", (d.Ts,), "fp32"), Field("qkv", (d.T, d.qkv_dim), "bf16")]
     if d.qk_norm:
         f += [Field("q_rstd", (d.T, d.hq), "fp32"), Field("k_rstd", (d.T, d.hkv), "fp32"),
               Field("qk_pre", (d.T, d.q_dim + d.kv_dim), "bf16")]
     f += [Field("lse", (d.hq, d.T), "fp32"), Field("attn_out", (d.T, d.q_dim), "bf16"),
-          Field("h_mid", (d.T, d.d), "bf16"), Field("rstd_ffn", (d.T,), "fp32")]
+          Field("h_mid", (d.Ts, d.d), "bf16"), Field("rstd_ffn", (d.Ts,), "fp32")]
     if d.moe:
         # the routing decision and the padded expert-major row tables are context: recompute and backward never
         # re-route; h13p is the up-projection of the dispatched rows (expert-major)

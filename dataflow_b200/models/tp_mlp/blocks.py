@@ -1,0 +1,217 @@
+"""Executables of the tensor + sequence parallel llama block.
+
+Shapes on one rank (``T`` rows per round, ``Ts = T / tp`` of them its own, local heads / FFN columns):
+
+    x, y, h_mid            (Ts, d)          the residual stream, row-sharded
+    qkv, attn_out, h13     (T, local)       every row of this rank's heads / columns
+
+Forward:   rmsnorm -> [all-gather -> qkv GEMM] -> rope, attention -> [wo GEMM -> reduce-scatter (+x)] -> rmsnorm
+           -> [all-gather -> w13 GEMM] -> SwiGLU -> [w2 GEMM -> reduce-scatter (+h_mid)]
+Backward:  the transposes of the four bracketed kernels in reverse; weight gradients of the column-parallel matrices
+           contract over all T rows, for which the gathered operand of the fused kernel (or one plain all-gather of
+           the re-applied norm) is used; norm-weight gradients are partial sums over this rank's rows and are summed
+           over the group by the optimizer wrapper.
+Reference role: ``src/dataflow_training/model_families/tp_mlp/`` (MLP-only sharding, NCCL all-reduce).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Mapping
+
+from ...blocks.base_blocks import _Base, common_executables
+from ...data.segments import make_segments
+from ..llama3.blocks import _qkv_views
+
+
+def _group(ctx):
+    g = ctx.groups.get(ctx.task.comm_groups.get("tp", "tp"))
+    if g is None:
+        raise RuntimeError(f"task {ctx.task.id} needs the tensor-parallel group 'tp' (pass groups={{'tp': TpGroup(...)}})")
+    return g
+
+
+class _TpBlock(_Base):
+    def rows(self, ctx):
+        seg = self.segments(ctx)
+        if seg.n_tokens != self.dims.T:
+            raise ValueError("tensor-parallel blocks need full rounds (every rank holds exactly T / tp rows)")
+        return seg
+
+    def ctx_views(self, buf):
+        return self.views(buf, self.lay.ctx)
+
+    def scratch_ctx(self, device, only=None):
+        import torch
+        from ...runtime.interop import _dtypes
+        return {f.name: torch.empty(tuple(f.shape), dtype=_dtypes()[f.dtype], device=device)
+                for f in self.lay.ctx.fields if only is None or f.name in only}
+
+    # -- forward pieces
+    def attention_half(self, g, K, d, seg, x, w, a):
+        h, rstd = K.rmsnorm_fwd(x, w["attn_norm"], d.eps)
+        a["rstd_attn"].copy_(rstd)
+        g.ag_gemm(h, w["w_qkv"], out=a["qkv"])
+        q, k, v = _qkv_views(d, a["qkv"], d.T)
+        K.rope_fwd(q, seg.positions, d.theta)
+        K.rope_fwd(k, seg.positions, d.theta)
+        _, lse = K.flash_fwd(q, k, v, seg.cu_seqlens, seg.max_len, out=a["attn_out"].unflatten(1, (d.hq, d.hd)))
+        a["lse"].copy_(lse)
+        g.gemm_rs(a["attn_out"], w["wo"], out=a["h_mid"], addend=x)
+
+    def up_projection(self, g, K, d, w, a):
+        h2, rstd = K.rmsnorm_fwd(a["h_mid"], w["ffn_norm"], d.eps)
+        a["rstd_ffn"].copy_(rstd)
+        g.ag_gemm(h2, w["w13"], out=a["h13"])
+
+
+class TpBlockFwd(_TpBlock):
+    """(x, W) -> (y, A)"""
+
+    def run(self, ctx):
+        d, K, g = self.dims, self.K, _group(ctx)
+        seg = self.rows(ctx)
+        x = self.tview(ctx.inputs[0], (d.Ts, d.d))
+        w = self.views(ctx.inputs[1], self.lay.block_w)
+        y = self.tview(ctx.outputs[0], (d.Ts, d.d))
+        lvl = int(ctx.task.block_params.get("recompute_level", 0))
+        if lvl == 0:
+            a = self.ctx_views(ctx.outputs[1])
+        elif lvl == 1:
+            a = dict(self.views(ctx.outputs[1], self.lay.extra["Ap"]))
+            a.update(self.scratch_ctx(x.device, only=("h13",)))
+        else:
+            a = self.scratch_ctx(x.device)
+        self.attention_half(g, K, d, seg, x, w, a)
+        self.up_projection(g, K, d, w, a)
+        s = K.swiglu_packed_fwd(a["h13"])
+        g.gemm_rs(s, w["w2"], out=y, addend=a["h_mid"])
+
+
+class TpBlockRecompute(_TpBlock):
+    """(x, W[, Ap]) -> (A)"""
+
+    def run(self, ctx):
+        d, K, g = self.dims, self.K, _group(ctx)
+        seg = self.rows(ctx)
+        x = self.tview(ctx.inputs[0], (d.Ts, d.d))
+        w = self.views(ctx.inputs[1], self.lay.block_w)
+        a = self.ctx_views(ctx.outputs[0])
+        if int(ctx.task.block_params.get("recompute_level", 2)) == 1:
+            for name, t in self.views(ctx.inputs[2], self.lay.extra["Ap"]).items():
+                a[name].copy_(t)
+            h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+            g.ag_gemm(h2, w["w13"], out=a["h13"])
+            return
+        self.attention_half(g, K, d, seg, x, w, a)
+        self.up_projection(g, K, d, w, a)
+
+
+class TpBlockBwd(_TpBlock):
+    """(dy, A, x, W[, dW]) -> (dx[, dW])"""
+
+    def run(self, ctx):
+        import torch
+        d, K, g = self.dims, self.K, _group(ctx)
+        seg = self.rows(ctx)
+        dy = self.tview(ctx.inputs[0], (d.Ts, d.d))
+        a = self.ctx_views(ctx.inputs[1])
+        x = self.tview(ctx.inputs[2], (d.Ts, d.d))
+        w = self.views(ctx.inputs[3], self.lay.block_w)
+        dx = self.tview(ctx.outputs[0], (d.Ts, d.d))
+        acc = not self.creating(ctx, "dW_")
+        gr = self.views(self.by_id(ctx, "dW_"), self.lay.block_dw)
+
+        def wgrad(name, xin, dout):
+            if name in gr:
+                K.linear_wgrad_bf16(xin, dout, gr[name], accumulate=acc)
+
+        # ---- MLP
+        s = K.swiglu_packed_fwd(a["h13"])
+        ds = g.ag_gemm(dy, w["w2"], w_is_kn=False)                      # dy (all rows) x W2^T, gather fused
+        wgrad("w2", s, g.last_gathered(d.Ts, d.d))
+        del s
+        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
+        del ds
+        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+        wgrad("w13", g.all_gather(h2), dh13)
+        del h2
+        dh2 = g.gemm_rs(dh13, w["w13"], w_is_kn=False)                  # dh13 x W13^T, reduce-scatter fused
+        del dh13
+        dh_mid = K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=gr.get("ffn_norm"), accumulate=acc)
+        # ---- attention
+        dattn = g.ag_gemm(dh_mid, w["wo"], w_is_kn=False)
+        wgrad("wo", a["attn_out"], g.last_gathered(d.Ts, d.d))
+        q, k, v = _qkv_views(d, a["qkv"], d.T)
+        dqkv = torch.empty(d.T, d.qkv_dim, dtype=x.dtype, device=x.device)
+        dq, dk, dv = _qkv_views(d, dqkv, d.T)
+        K.flash_bwd(dattn.unflatten(1, (d.hq, d.hd)), q, k, v, a["attn_out"].unflatten(1, (d.hq, d.hd)), a["lse"],
+                    seg.cu_seqlens, seg.max_len, dq=dq, dk=dk, dv=dv)
+        del dattn
+        K.rope_bwd(dq, seg.positions, d.theta)
+        K.rope_bwd(dk, seg.positions, d.theta)
+        h = K.rmsnorm_apply(x, w["attn_norm"], a["rstd_attn"])
+        wgrad("w_qkv", g.all_gather(h), dqkv)
+        del h
+        dh = g.gemm_rs(dqkv, w["w_qkv"], w_is_kn=False)
+        K.rmsnorm_bwd(dh, x, w["attn_norm"], a["rstd_attn"], dx_add=dh_mid, dw=gr.get("attn_norm"), accumulate=acc, out=dx)
+
+
+class _ShardRows:
+    """Row-sharded executables see one segment of ``Ts`` rows (they need the row count, not the sequence structure)."""
+
+    def segments(self, ctx):
+        seg = getattr(self, "_seg", None)
+        if seg is None:
+            seg = self._seg = make_segments([0, self.dims.T], self.device)
+        return seg
+
+
+class ReplicatedGradSum:
+    """Wraps an optimizer executable: sums the gradients of parameters every rank holds in full over the group first.
+    ``fields``: names inside the packed gradient object, or ``None`` for all of them."""
+
+    def __init__(self, inner, layout_of_grad, fields):
+        self.inner, self.layout_of_grad, self.fields = inner, layout_of_grad, fields
+
+    def launch(self, ctx):
+        inner = self.inner
+        if inner.device is None:
+            return self.run(ctx)
+        import torch
+        from ...runtime.interop import external_stream
+        with torch.cuda.stream(external_stream(ctx.stream, inner.device)):
+            self.run(ctx)
+
+    def run(self, ctx):
+        g = _group(ctx)
+        views = self.inner.views(ctx.inputs[1], self.layout_of_grad)
+        for name, t in views.items():
+            if self.fields is None or name in self.fields:
+                g.all_reduce(t)
+        self.inner.run(ctx)
+
+
+def build_tp_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device, layouts=None, policy=None):
+    from ...blocks.layouts import DTypePolicy
+    from ..llama3.model import family_layouts
+    hyper = dict(hyper or {})
+    lay = layouts or family_layouts(dims, policy or DTypePolicy.from_dict(hyper.get("dtype_policy", "bf16")), hyper.get("optimizer", "adamw"))
+    sd = dataclasses.replace(dims, T=dims.Ts, tp=1, head_chunk=min(dims.head_chunk, dims.Ts))
+    table = {}
+    for key, exe in common_executables(sd, lay, kernels, device, hyper).items():
+        cls = type(exe)
+        table[key] = type("Shard" + cls.__name__, (_ShardRows, cls), {})(sd, lay, kernels, device, hyper)
+    table["optimizer_block"] = ReplicatedGradSum(table["optimizer_block"], lay.block_dw, ("attn_norm", "ffn_norm"))
+    table["optimizer_embed"] = ReplicatedGradSum(table["optimizer_embed"], lay.embed_dw, None)
+    table["optimizer_head"] = ReplicatedGradSum(table["optimizer_head"], lay.head_dw, None)
+    table.update({"block_fwd": TpBlockFwd(dims, lay, kernels, device, hyper),
+                  "block_recompute": TpBlockRecompute(dims, lay, kernels, device, hyper),
+                  "block_bwd": TpBlockBwd(dims, lay, kernels, device, hyper)})
+
+    def resolver(task):
+        try:
+            return table[task.compute_block_key]
+        except KeyError:
+            raise KeyError(f"tp_mlp: no executable for compute key {task.compute_block_key!r} (task {task.id})") from None
+    resolver.table = table
+    return resolver

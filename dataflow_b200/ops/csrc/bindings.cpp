@@ -128,6 +128,9 @@ static void adamw_f32(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double l
                  eps, wd, (int)step, gscale, cur_stream());
 }
 static void sgd_bf16(Tensor& w, const Tensor& g, c10::optional<Tensor> m, double lr, double mu, double wd) {
+  CHECK_CUDA(w); CHECK_BF16(w); CHECK_BF16(g);
+  if (m.has_value()) CHECK_BF16((*m));
+  TORCH_CHECK(g.numel() == w.numel() && (!m.has_value() || m->numel() == w.numel()), "sgd_bf16: extents differ");
   dfb::sgd_bf16(w.data_ptr(), g.data_ptr(), m.has_value() ? m->data_ptr() : nullptr, w.numel(), lr, mu, wd, cur_stream());
 }
 

@@ -100,6 +100,31 @@ class TpGroup:
             raise ValueError(f"rows x k = {rows} x {k} exceeds the workspace ({self.max_rows} x {self.max_k})")
         return native().tensor_from_ptr(self.base + self.off_gathered + self.rank * rows * k * 2, [rows, k], "bf16", self.device)
 
+    def last_gathered(self, rows: int, k: int):
+        """The (world * rows, k) operand the last ``ag_gemm`` assembled (valid until the next one): the weight
+        gradient of a column-parallel linear needs exactly this matrix."""
+        if self.lane != "p2p":
+            return self._last_full
+        from ..ops import native
+        return native().tensor_from_ptr(self.base + self.off_gathered, [rows * self.world, k], "bf16", self.device)
+
+    def all_gather(self, x):
+        """(rows, k) -> (world * rows, k), no GEMM attached (operands of weight gradients in the backward)."""
+        import torch
+        import torch.distributed as dist
+        out = torch.empty(x.shape[0] * self.world, x.shape[1], dtype=x.dtype, device=x.device)
+        if self.world == 1:
+            out.copy_(x)
+        else:
+            dist.all_gather_into_tensor(out, x.contiguous())
+        return out
+
+    def all_reduce(self, t):
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.all_reduce(t)
+        return t
+
     # -- fused ops
     def ag_gemm(self, x, w, out=None, w_is_kn: bool = True):
         """``x``: this rank's rows (rows, K) — ideally ``x_buffer`` itself; ``w``: (K, N) when ``w_is_kn`` else (N, K).
@@ -114,7 +139,8 @@ class TpGroup:
             parts = [torch.empty_like(x) for _ in range(self.world)]
             dist.all_gather(parts, x.contiguous())
             full = torch.cat(parts, 0)
-            torch.matmul(full, w if w_is_kn else w.t(), out=out)
+            self._last_full = full
+            out.copy_(torch.matmul(full.float(), (w if w_is_kn else w.t()).float()).to(out.dtype))
             return out
         from ..ops import native
         from ..ops.cuda import LAUNCHES
@@ -142,7 +168,7 @@ class TpGroup:
             out = torch.empty(rows, n, dtype=x.dtype, device=x.device)
         if self.lane != "p2p":
             import torch.distributed as dist
-            part = torch.matmul(x, w if w_is_kn else w.t()).float()
+            part = torch.matmul(x.float(), (w if w_is_kn else w.t()).float())
             if dist.get_backend() == "gloo":
                 dist.all_reduce(part)
                 mine = part[self.rank * rows:(self.rank + 1) * rows]

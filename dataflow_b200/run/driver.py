@@ -206,7 +206,9 @@ class Trainer:
             zero_initial_values(self.fam, self.cfg, self.program, self.store, seed, self.layouts,
                                 int(self.zero["rank"]), int(self.zero["world"]), int(self.zero["stage"]))
         else:
-            self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts)
+            # a tensor-parallel family cuts the same seeded full model differently on every rank
+            kw = {"rank": self.groups["tp"].rank} if "tp" in self.groups else {}
+            self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts, **kw)
 
     # -- data
     def put_round(self, r: int, tokens, targets) -> int:

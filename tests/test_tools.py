@@ -80,3 +80,19 @@ def test_doc_tools(capsys, tmp_path):
     assert tool("gen_model_docs/list_kernels.py").main(["--kernel-set", "eager"]) == 0
     assert tool("gen_model_docs/gen_model_docs.py").main(["--out", str(tmp_path)]) == 0
     assert (tmp_path / "index.md").exists() and "w_qkv" in (tmp_path / "llama3.md").read_text()
+
+
+def test_reproducibility_drivers_run_staged_and_resume(tmp_path, capsys):
+    spec = importlib.util.spec_from_file_location("run_accuracy", os.path.join(ROOT, "reproducibility", "accuracy_fidelity", "run_accuracy.py"))
+    acc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(acc)
+    args = ["--preset", "llama3:tiny", "--device", "cpu", "--steps", "2", "--budgets", "0.02", "--out", str(tmp_path / "acc")]
+    assert acc.main(args) == 0
+    assert "budget GiB" in (tmp_path / "acc" / "report.md").read_text()
+    assert acc.main(args + ["--resume"]) == 0
+    assert "kept" in capsys.readouterr().out
+    spec = importlib.util.spec_from_file_location("run_experiment", os.path.join(ROOT, "reproducibility", "throughput_fidelity", "run_experiment.py"))
+    thr = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(thr)
+    assert thr.main(["--preset", "llama3:tiny", "--device", "cpu", "--budgets", "0.02", "--steps", "4", "--out", str(tmp_path / "thr")]) == 0
+    assert "measured / predicted" in (tmp_path / "thr" / "report.md").read_text()
