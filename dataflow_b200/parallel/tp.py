@@ -47,6 +47,9 @@ class TpGroup:
             return
         import torch
         import torch.distributed as dist
+        backend = getattr(backend, "backend", backend)          # a Trainer hands itself over
+        if self.ws:
+            return
         self.backend = backend
         self.base = backend.device_alloc_zeroed(self.ws_bytes)
         handles: list[Any] = [None] * self.world

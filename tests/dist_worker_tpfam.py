@@ -32,8 +32,6 @@ def main():
     budget = float(os.environ["TP_TEST_BUDGET"]) if os.environ.get("TP_TEST_BUDGET") else None
     tr = Trainer("tp_mlp", cfg, budget_gib=budget, device=rank if gpu else None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=3,
                  groups={"tp": grp}, leeway_bytes=0)
-    if gpu:
-        grp.attach(tr.backend)
     losses = []
     for s in range(3):
         full = synthetic_rounds(cfg, tr.rounds, d.T, 64, 11, s)                 # the same global data on every rank

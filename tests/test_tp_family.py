@@ -22,7 +22,9 @@ def launch(world, device_kind, tmp_path, lane=None, port=29811, budget=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(HERE, "dist_worker_tpfam.py"), str(out), device_kind]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    if r.returncode:
+        at = r.stderr.find("Traceback")
+        raise AssertionError(r.stderr[at:at + 3000] if at >= 0 else r.stdout[-1500:] + r.stderr[-1500:])
     return json.loads(out.read_text())
 
 
