@@ -1,0 +1,174 @@
+"""Reference forms, in differentiable torch, of the inner ops the newer families share: RMSNorm, rotate-half RoPE on a
+slice, causal segment masks, SwiGLU, a mixture-of-experts MLP with either softmax or sigmoid "no-aux" grouped routing
+and optional shared experts, multi-head latent attention, the sparse-attention indexer, and the gated delta rule.
+Reference role: ``src/dataflow_training/blocks/modules/{mla_forms,dsa_forms}.py``, ``moe/forms.py`` and the DeltaNet
+references of ``blocks/ops.py:509-623``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def rmsnorm(x, w, eps: float):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def rope(x, positions, theta: float):
+    """Rotate-half RoPE over the last dim of x (tokens, heads, dim)."""
+    d = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
+    ang = positions.to(torch.float32)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
+    x1, x2 = x[..., :d // 2], x[..., d // 2:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+def segment_causal_mask(seg, n: int, device):
+    """(n, n) bool: query i may see key j (same segment, j <= i)."""
+    pos = seg.positions.to(device)[:n].long()
+    idx = torch.arange(n, device=device)
+    start = idx - pos                                     # first token of the segment each token lives in
+    return (start[:, None] == start[None, :]) & (idx[None, :] <= idx[:, None])
+
+
+def attention(q, k, v, mask, scale: float):
+    """q (n, h, dq), k (n, hk, dq), v (n, hk, dv); grouped heads; ``mask`` (n, n) or (h, n, n) bool."""
+    h, hk = q.shape[1], k.shape[1]
+    if hk != h:
+        k, v = k.repeat_interleave(h // hk, 1), v.repeat_interleave(h // hk, 1)
+    s = torch.einsum("ihd,jhd->hij", q.float(), k.float()) * scale
+    s = s.masked_fill(~(mask if mask.dim() == 3 else mask[None]), float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("hij,jhd->ihd", p, v.float()).to(q.dtype), p
+
+
+def swiglu_mlp(x, w13, w2):
+    h = x @ w13
+    f = h.shape[-1] // 2
+    return (F.silu(h[..., :f].float()).to(x.dtype) * h[..., f:]) @ w2
+
+
+def route_softmax_topk(logits, k: int):
+    vals, ids = torch.topk(logits.float(), k, dim=-1)
+    return torch.softmax(vals, -1), ids
+
+
+def route_sigmoid_noaux(logits, bias, k: int, n_group: int, topk_group: int, scaling: float):
+    """Sigmoid scores; selection on score + bias inside the best ``topk_group`` of ``n_group`` expert groups (a group's
+    rank is the sum of its two best biased scores); weights from the unbiased scores, normalised and scaled."""
+    s = torch.sigmoid(logits.float())
+    sel = s + bias.float()[None]
+    t, e = s.shape
+    if n_group > 1:
+        g = sel.view(t, n_group, e // n_group)
+        rank = g.topk(min(2, e // n_group), dim=-1).values.sum(-1)
+        keep = torch.zeros_like(rank, dtype=torch.bool).scatter_(1, rank.topk(topk_group, dim=-1).indices, True)
+        sel = sel.masked_fill(~keep[:, :, None].expand_as(g).reshape(t, e), float("-inf"))
+    ids = sel.topk(k, dim=-1).indices
+    w = s.gather(1, ids)
+    return w / (w.sum(-1, keepdim=True) + 1e-20) * scaling, ids
+
+
+def moe_mlp(x, w13_experts, w2_experts, weights, ids):
+    """Token-choice experts, dense loop over experts (reference form)."""
+    y = torch.zeros_like(x)
+    for e in range(w13_experts.shape[0]):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel():
+            y = y.index_add(0, tok, swiglu_mlp(x[tok], w13_experts[e], w2_experts[e]) * weights[tok, slot].to(x.dtype)[:, None])
+    return y
+
+
+def load_balance_aux(logits, ids, coef: float):
+    """Switch-style balance loss coef * E * sum_e f_e * p_e (f: fraction of slots, p: mean router probability)."""
+    if not coef:
+        return None
+    t, e = logits.shape
+    p = torch.softmax(logits.float(), -1).mean(0)
+    f = torch.zeros(e, device=logits.device).scatter_add_(0, ids.reshape(-1), torch.ones(ids.numel(), device=logits.device)) / ids.numel()
+    return coef * e * (f.detach() * p).sum() * t
+
+
+def mla_qkv(x, w, cfg, positions):
+    """Multi-head latent attention projections: two low-rank stacks, decoupled RoPE with one shared rope key.
+    Returns q (n, h, nope + rope), k (n, h, nope + rope), v (n, h, dv) and the compressed latents."""
+    n, h = x.shape[0], cfg.n_heads
+    if cfg.q_lora:
+        cq = rmsnorm(x @ w["wq_a"], w["q_norm"], cfg.rms_eps)
+        q = (cq @ w["wq_b"]).view(n, h, cfg.d_nope + cfg.d_rope)
+    else:
+        q = (x @ w["wq"]).view(n, h, cfg.d_nope + cfg.d_rope)
+    kv_a = x @ w["wkv_a"]                                           # (n, kv_lora + rope)
+    ckv = rmsnorm(kv_a[:, :cfg.kv_lora], w["kv_norm"], cfg.rms_eps)
+    k_rope = rope(kv_a[:, None, cfg.kv_lora:], positions, cfg.rope_theta)              # (n, 1, rope): shared by the heads
+    kv = (ckv @ w["wkv_b"]).view(n, h, cfg.d_nope + cfg.d_v)
+    q = torch.cat([q[..., :cfg.d_nope], rope(q[..., cfg.d_nope:], positions, cfg.rope_theta)], -1)
+    k = torch.cat([kv[..., :cfg.d_nope], k_rope.expand(n, h, cfg.d_rope)], -1)
+    return q, k, kv[..., cfg.d_nope:], ckv
+
+
+def dsa_index_scores(x, w, cfg, positions):
+    """Lightning indexer: I[i, j] = sum_h wgt[i, h] * relu(<q_idx[i, h], k_idx[j]>), a few small heads, one shared key."""
+    n = x.shape[0]
+    qi = rope((x @ w["wi_q"]).view(n, cfg.index_heads, cfg.index_dim), positions, cfg.rope_theta)
+    ki = rope((x @ w["wi_k"]).view(n, 1, cfg.index_dim), positions, cfg.rope_theta)[:, 0]
+    wgt = (x @ w["wi_w"]).float() * cfg.index_heads ** -0.5
+    s = torch.relu(torch.einsum("ihd,jd->ihj", qi.float(), ki.float())) * cfg.index_dim ** -0.5
+    return (s * wgt[:, :, None]).sum(1)
+
+
+def dsa_topk_mask(scores, causal, k: int):
+    """(n, n) bool: the ``k`` best visible keys of every query (all visible keys when there are fewer)."""
+    s = scores.masked_fill(~causal, float("-inf"))
+    kk = min(k, s.shape[-1])
+    idx = s.topk(kk, dim=-1).indices
+    return torch.zeros_like(causal).scatter_(1, idx, True) & causal
+
+
+def dsa_indexer_kl(scores, probs, causal):
+    """KL(attention distribution summed over heads || softmax of the index scores), mean over queries; the attention
+    side is a constant target."""
+    target = probs.detach().sum(0)
+    target = target / (target.sum(-1, keepdim=True) + 1e-20)
+    logq = torch.log_softmax(scores.masked_fill(~causal, float("-inf")), dim=-1)
+    term = torch.where(target > 0, target * (torch.log(target.clamp_min(1e-20)) - logq), torch.zeros_like(target))
+    return term.sum(-1).mean()
+
+
+def l2norm(x, eps: float = 1e-6):
+    return x * torch.rsqrt(x.float().pow(2).sum(-1, keepdim=True) + eps).to(x.dtype)
+
+
+def causal_conv1d_silu(x, w, seg_start):
+    """Depthwise causal convolution of width ``w.shape[1]`` along tokens, never crossing a segment start, then SiLU.
+    x (n, c), w (c, width), seg_start (n,) index of the first token of each token's segment."""
+    n, width = x.shape[0], w.shape[1]
+    idx = torch.arange(n, device=x.device)
+    out = torch.zeros_like(x)
+    for j in range(width):
+        src = idx - (width - 1 - j)
+        ok = (src >= seg_start).to(x.dtype)[:, None]
+        out = out + x[src.clamp(min=0)] * ok * w[:, j][None, :]
+    return F.silu(out.float()).to(x.dtype)
+
+
+def gated_delta_rule(q, k, v, g, beta, seg_start):
+    """Sequential form: S <- exp(g_t) S (I - beta_t k_t k_t^T) + beta_t v_t k_t^T;  o_t = S q_t.
+    q, k (n, h, dk) l2-normalised; v (n, h, dv); g (n, h) log-decay <= 0; beta (n, h) in (0, 1).  State resets at
+    segment starts."""
+    n, h, dk = q.shape
+    dv = v.shape[-1]
+    S = torch.zeros(h, dv, dk, dtype=torch.float32, device=q.device)
+    outs = []
+    qf, kf, vf = q.float() * dk ** -0.5, k.float(), v.float()
+    for t in range(n):
+        if int(seg_start[t]) == t:
+            S = torch.zeros_like(S)
+        S = S * torch.exp(g[t].float())[:, None, None]
+        kt, vt, bt = kf[t], vf[t], beta[t].float()[:, None]
+        pred = torch.einsum("hvk,hk->hv", S, kt)
+        S = S + torch.einsum("hv,hk->hvk", bt * (vt - pred), kt)
+        outs.append(torch.einsum("hvk,hk->hv", S, qf[t]))
+    return torch.stack(outs, 0).to(q.dtype)

@@ -1,0 +1,34 @@
+"""dsv32 family (DeepSeek-V3.2 architecture): dsv3 plus sparse attention — a lightning indexer (a few small heads, one
+shared key, ReLU scores) ranks the visible keys of every query, attention runs over the ``index_topk`` best, and the
+indexer is trained by a KL term towards the attention distribution (gradient injected in the block backward; the
+attention side is a constant target).  Kinds ``dsadense`` / ``dsamoe``.
+Family parity: reference ``src/dataflow_training/model_families/dsv32/{blocks.py,model.py}``; the reference's dense
+warm-up mode (only the indexer trains) is the optimizer policy ``freeze(...)`` of every field but ``wi_*`` here.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+from ..dsv3 import Dsv3Config, block_fn as _block_fn, kind_fields as _kind_fields, kind_flops
+from .._torch_family import TorchFamilySpec, register_torch_family
+
+
+def layer_kinds(c: Dsv3Config):
+    return ["dsadense" if i < c.n_dense else "dsamoe" for i in range(c.n_layers)]
+
+
+BASE = dict(index_heads=2, index_dim=16, index_topk=32, index_kl_coef=0.1, family="dsv32")
+PRESETS = {
+    "tiny": dict(name="tiny", **BASE),
+    "dsv32_mini": dict(name="dsv32_mini", n_layers=6, n_dense=1, d_model=512, n_heads=8, q_lora=192, kv_lora=128, d_nope=64, d_rope=32, d_v=64,
+                       d_ff=1408, n_experts=16, top_k=4, d_ff_expert=256, n_group=4, topk_group=2, vocab_size=32000, seq_len=1024, batch=4,
+                       grad_accum_rounds=4, **{**BASE, "index_heads": 4, "index_dim": 32, "index_topk": 256}),
+    "dsv32_671b": dict(name="dsv32_671b", n_layers=61, n_dense=3, d_model=7168, n_heads=128, q_lora=1536, kv_lora=512, d_nope=128, d_rope=64,
+                       d_v=128, d_ff=18432, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5,
+                       vocab_size=129280, seq_len=4096, batch=1, grad_accum_rounds=16, dtype_policy="bf16_split_master",
+                       **{**BASE, "index_heads": 64, "index_dim": 128, "index_topk": 2048}),
+}
+
+SPEC = TorchFamilySpec("dsv32", Dsv3Config, {k: (lambda kw=v: Dsv3Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, _kind_fields,
+                       _block_fn, kind_flops)
+FAMILY = register_torch_family(SPEC)

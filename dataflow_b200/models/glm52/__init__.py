@@ -1,0 +1,98 @@
+"""glm52 family: the dsv32 architecture (multi-head latent attention, sparse attention through a lightning indexer,
+mixture of experts after the first dense layers) with CROSS-LAYER INDEX SHARING: layers come in groups of
+``index_share``; the first layer of a group (the leader) runs the indexer and stores the keys it selected in its context
+object, the others (followers) carry no indexer weights and attend over the leader's selection.  Kinds ``gdl`` / ``gdf``
+(dense leader / follower) and ``gml`` / ``gmf`` (mixture-of-experts leader / follower).  A lowering post-pass makes the
+followers' forward and backward tasks read the leader's context object.
+The indexer is trained by the KL term of its own (leader) layer; the reference additionally accumulates the followers'
+attention distributions into that target (``src/dataflow_training/model_families/glm52/{blocks.py,model.py}``), which
+this lane leaves out.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ...blocks.layouts import Field
+from .. import _forms as F
+from ..dsv3 import Dsv3Config, kind_fields as _dsv3_fields, kind_flops as _dsv3_flops
+from .._torch_family import TorchFamilySpec, register_torch_family
+
+
+@dataclasses.dataclass(frozen=True)
+class Glm52Config(Dsv3Config):
+    index_share: int = 2
+
+
+def leader_of(c: Glm52Config, layer: int):
+    lead = layer - layer % c.index_share
+    return None if lead == layer else lead
+
+
+def layer_kinds(c: Glm52Config):
+    return [("gd" if i < c.n_dense else "gm") + ("l" if leader_of(c, i) is None else "f") for i in range(c.n_layers)]
+
+
+def kind_fields(c: Glm52Config, kind: str):
+    f = _dsv3_fields(c, "x_dense" if kind.startswith("gd") else "x_moe")
+    return tuple(x for x in f if kind.endswith("l") or not x.name.startswith("wi_"))
+
+
+def ctx_fields(c: Glm52Config, tokens: int):
+    return (Field("sel", (tokens, min(c.index_topk, c.seq_len)), "int32"),)
+
+
+def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None):
+    n = x.shape[0]
+    pos = seg.positions[:n]
+    h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
+    q, k, v, _ = F.mla_qkv(h, w, c, pos)
+    causal = F.segment_causal_mask(seg, n, x.device)
+    aux, emit = None, None
+    if shared is None:                                              # leader: rank the keys, publish the selection
+        scores = F.dsa_index_scores(h.detach(), {k_: w[k_] for k_ in ("wi_q", "wi_k", "wi_w")}, c, pos)
+        kk = min(c.index_topk, c.seq_len, n)
+        sel = scores.detach().masked_fill(~causal, float("-inf")).topk(kk, dim=-1).indices
+        emit = {"sel": torch.nn.functional.pad(sel, (0, min(c.index_topk, c.seq_len) - kk)).to(torch.int32)}
+    else:
+        sel = shared["sel"].long()[:, :min(c.index_topk, c.seq_len, n)]
+    mask = torch.zeros_like(causal).scatter_(1, sel.clamp(max=n - 1), True) & causal
+    o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
+    if shared is None and c.index_kl_coef:
+        aux = c.index_kl_coef * F.dsa_indexer_kl(scores, probs, mask) * n
+    h_mid = x + o.reshape(n, -1) @ w["wo"]
+    h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
+    if kind.startswith("gd"):
+        y = F.swiglu_mlp(h2, w["w13"], w["w2"])
+    else:
+        wts, ids = F.route_sigmoid_noaux(h2 @ w["w_router"], w["router_bias"].detach(), c.top_k, c.n_group, c.topk_group, c.routed_scaling)
+        y = F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
+        if c.n_shared:
+            y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
+    return h_mid + y, aux, emit
+
+
+def kind_flops(c: Glm52Config, kind: str, tokens: int):
+    mm, at = _dsv3_flops(c, "x_dense" if kind.startswith("gd") else "x_moe", tokens)
+    if kind.endswith("f"):                                          # followers run no indexer
+        mm -= 2.0 * tokens * c.d_model * (c.index_heads * c.index_dim + c.index_dim + c.index_heads)
+        at -= 2.0 * tokens * c.seq_len / 2 * c.index_heads * c.index_dim
+    return mm, at
+
+
+BASE = dict(index_heads=2, index_dim=16, index_topk=32, index_kl_coef=0.1, index_share=2, family="glm52")
+PRESETS = {
+    "tiny": dict(name="tiny", n_layers=4, n_dense=2, **BASE),
+    "glm52_mini": dict(name="glm52_mini", n_layers=8, n_dense=2, d_model=512, n_heads=8, q_lora=192, kv_lora=128, d_nope=64, d_rope=32, d_v=64,
+                       d_ff=1408, n_experts=16, top_k=4, d_ff_expert=256, n_group=4, topk_group=2, vocab_size=32000, seq_len=1024, batch=4,
+                       grad_accum_rounds=4, **{**BASE, "index_heads": 4, "index_dim": 32, "index_topk": 256, "index_share": 4}),
+    "glm52": dict(name="glm52", n_layers=78, n_dense=3, d_model=6144, n_heads=64, q_lora=2048, kv_lora=512, d_nope=128, d_rope=64, d_v=128,
+                  d_ff=12288, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5, vocab_size=154880,
+                  seq_len=4096, batch=1, grad_accum_rounds=16, dtype_policy="bf16_split_master",
+                  **{**BASE, "index_heads": 32, "index_dim": 128, "index_topk": 2048, "index_share": 3}),
+}
+
+SPEC = TorchFamilySpec("glm52", Glm52Config, {k: (lambda kw=v: Glm52Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,
+                       block_fn, kind_flops, ctx_fields=ctx_fields, leader_of=leader_of)
+FAMILY = register_torch_family(SPEC)

@@ -1,0 +1,114 @@
+"""dsv3, dsv32, glm52, qwen35, qwen35moe: families in the reference-form (autograd) lane against their twins."""
+import pytest
+import torch
+
+from dataflow_b200.models import _forms as F
+from dataflow_b200.models.families import resolve_family, validate_family
+from dataflow_b200.testing.family_gate import run_pair
+
+FAMILIES = ["dsv3", "dsv32", "glm52", "qwen35", "qwen35moe"]
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_family_structure(family):
+    assert validate_family(family) == []
+    fam = resolve_family(family)
+    cfg = fam.presets["tiny"]()
+    prog = fam.lower(cfg)
+    kinds = fam.derive_dims(cfg).kinds
+    assert len(set(kinds)) >= 2                                    # every one of these stacks mixes kinds of layers
+    for i, kind in enumerate(kinds):
+        assert any(t.compute_block_key == f"{kind}_fwd" and t.block_params["layer"] == i for t in prog.tasks)
+    lay = fam.family_layouts(fam.derive_dims(cfg))
+    sizes = prog.object_sizes()
+    for i in range(cfg.n_layers):
+        assert sizes[f"W_{i}"] == lay.of_layer(i)[0].size_bytes
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_engine_matches_twin_fp32(family):
+    r = run_pair(family, steps=3)
+    assert r["max_loss_rel"] < 1e-3
+    assert r["engine"][-1] < r["engine"][0]
+
+
+@pytest.mark.parametrize("family", ["dsv32", "qwen35"])
+def test_ragged_rounds_match_twin(family):
+    assert run_pair(family, steps=2, shape="ragged")["max_loss_rel"] < 1e-3
+
+
+def test_glm52_followers_read_their_leaders_selection_and_budget_does_not_change_losses():
+    fam = resolve_family("glm52")
+    cfg = fam.presets["tiny"]()
+    prog = fam.lower(cfg)
+    kinds = fam.derive_dims(cfg).kinds
+    assert kinds == ("gdl", "gdf", "gml", "gmf")
+    for t in prog.tasks:
+        if t.compute_block_key in ("gdf_fwd", "gdf_bwd", "gmf_fwd", "gmf_bwd"):
+            r, i = t.block_params["round"], t.block_params["layer"]
+            assert f"A_0_{r}_{i - 1}" in t.inputs
+        if t.compute_block_key in ("gdl_fwd", "gml_bwd"):
+            assert sum(x.startswith("A_") for x in t.inputs) <= 1
+    lay = fam.family_layouts(fam.derive_dims(cfg))
+    assert "wi_q" in lay.of_layer(0)[0].names() and "wi_q" not in lay.of_layer(1)[0].names()
+    free = run_pair("glm52", steps=2)
+    tight = run_pair("glm52", steps=2, budget_gib=0.012)
+    assert tight["engine"] == pytest.approx(free["engine"], rel=1e-6)
+
+
+def test_delta_rule_with_full_write_strength_stores_and_recalls_an_association():
+    # one head, orthonormal keys, beta = 1, no decay: after writing (k_i -> v_i) the state returns v_i for q = k_i
+    dk = dv = 4
+    k = torch.eye(dk)[:3].view(3, 1, dk)
+    v = torch.randn(3, 1, dv)
+    g, beta = torch.zeros(3, 1), torch.ones(3, 1)
+    start = torch.zeros(3, dtype=torch.long)
+    o = F.gated_delta_rule(k * dk ** 0.5, k, v, g, beta, start)      # the rule scales q by dk^-0.5
+    assert torch.allclose(o, v, atol=1e-5)
+    # a second write to the same key REPLACES the value (delta rule), it does not add to it
+    k2 = torch.stack([k[0], k[0]]);  v2 = torch.randn(2, 1, dv)
+    o2 = F.gated_delta_rule(k2 * dk ** 0.5, k2, v2, torch.zeros(2, 1), torch.ones(2, 1), torch.zeros(2, dtype=torch.long))
+    assert torch.allclose(o2[1], v2[1], atol=1e-5)
+    # a segment start clears the state
+    o3 = F.gated_delta_rule(k2 * dk ** 0.5, k2, v2, torch.zeros(2, 1), torch.zeros(2, 1) + 1e-9, torch.tensor([0, 1]))
+    assert o3[1].abs().max() < 1e-6
+
+
+def test_causal_conv_never_reads_across_a_segment_start():
+    x = torch.randn(10, 3)
+    w = torch.randn(3, 4)
+    start = torch.tensor([0] * 6 + [6] * 4)
+    full = F.causal_conv1d_silu(x, w, start)
+    tail = F.causal_conv1d_silu(x[6:], w, torch.zeros(4, dtype=torch.long))
+    assert torch.allclose(full[6:], tail, atol=1e-6)
+
+
+def test_sigmoid_noaux_routing_restricts_selection_to_the_best_groups():
+    logits = torch.tensor([[5.0, 4.0, -9.0, -9.0, 3.0, 3.5, 3.6, 3.7]])
+    w, ids = F.route_sigmoid_noaux(logits, torch.zeros(8), k=2, n_group=2, topk_group=1, scaling=2.0)
+    assert set(ids[0].tolist()) == {0, 1}                             # group 0 has the larger sum of its two best scores
+    assert w.sum().item() == pytest.approx(2.0, rel=1e-5)
+    # one very good expert does not carry its group: the rank is the sum of the two best
+    lone = torch.tensor([[9.0, -9.0, -9.0, -9.0, 2.0, 2.0, 2.0, 2.0]])
+    _, ids1 = F.route_sigmoid_noaux(lone, torch.zeros(8), k=2, n_group=2, topk_group=1, scaling=1.0)
+    assert set(ids1[0].tolist()) <= {4, 5, 6, 7}
+    w2, ids2 = F.route_sigmoid_noaux(logits, torch.tensor([0, 0, 0, 0, 0, 0, 0, -10.0]), 2, 1, 1, 1.0)
+    assert 7 not in ids2[0].tolist()                                  # the bias steers selection ...
+    assert w2.sum().item() == pytest.approx(1.0, rel=1e-5)            # ... the weights come from the unbiased scores
+
+
+def test_dsa_topk_mask_keeps_k_visible_keys_per_query():
+    torch.manual_seed(0)
+    n = 12
+    causal = torch.tril(torch.ones(n, n, dtype=torch.bool))
+    m = F.dsa_topk_mask(torch.randn(n, n), causal, 4)
+    assert (m & ~causal).sum() == 0
+    assert m.sum(-1).tolist() == [min(i + 1, 4) for i in range(n)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("family", FAMILIES)
+def test_gpu_engine_in_band(family):
+    r = run_pair(family, device=0, policy="bf16_master", steps=3)
+    assert r["max_loss_rel"] < 3e-2
+    assert r["engine"][-1] < r["engine"][0]
