@@ -58,6 +58,12 @@ def route_softmax_topk(logits, k: int):
 def route_sigmoid_noaux(logits, bias, k: int, n_group: int, topk_group: int, scaling: float):
     """Sigmoid scores; selection on score + bias inside the best ``topk_group`` of ``n_group`` expert groups (a group's
     rank is the sum of its two best biased scores); weights from the unbiased scores, normalised and scaled."""
+    K = _native(logits)
+    if K is not None and logits.shape[1] <= 256 and k <= 16:
+        # selection by the native router; the weights are re-derived from the scores so that gradients reach the router
+        _, ids = K.moe_topk_sigmoid_noaux(logits.detach(), bias, k, n_group, topk_group, scaling)
+        w = torch.sigmoid(logits.float()).gather(1, ids.long())
+        return w / (w.sum(-1, keepdim=True) + 1e-20) * scaling, ids.long()
     s = torch.sigmoid(logits.float())
     sel = s + bias.float()[None]
     t, e = s.shape
@@ -137,13 +143,84 @@ def dsa_indexer_kl(scores, probs, causal):
     return term.sum(-1).mean()
 
 
+_KS = {}
+
+
+def _native(x):
+    """The hand-written kernels, when ``x`` is a bf16 tensor on a device that has them (else ``None``)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16):
+        return None
+    if "ks" not in _KS:
+        from ..ops import resolve_kernels
+        ks = resolve_kernels()
+        _KS["ks"] = ks if "l2norm_fwd" in ks.native_ops() else None
+    return _KS["ks"]
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps, K):
+        y, rstd = K.l2norm_fwd(x, eps)
+        ctx.save_for_backward(x, rstd)
+        ctx.K = K
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, rstd = ctx.saved_tensors
+        return ctx.K.l2norm_bwd(dy, x, rstd), None, None
+
+
+class _GatedRmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, g, w, eps, K):
+        y, rstd = K.gated_rmsnorm_fwd(x, g, w, eps)
+        ctx.save_for_backward(x, g, w, rstd)
+        ctx.K = K
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g, w, rstd = ctx.saved_tensors
+        dx, dg, dw = ctx.K.gated_rmsnorm_bwd(dy, x, g, w, rstd)
+        return dx, dg, dw.to(w.dtype), None, None
+
+
+class _ConvSilu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, seg_start, K):
+        ctx.save_for_backward(x, w, seg_start)
+        ctx.K = K
+        return K.conv_silu_fwd(x, w, seg_start)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, seg_start = ctx.saved_tensors
+        dx, dw = ctx.K.conv_silu_bwd(dy, x, w, seg_start)
+        return dx, dw.to(w.dtype), None, None
+
+
 def l2norm(x, eps: float = 1e-6):
+    K = _native(x)
+    if K is not None and x.shape[-1] <= 512:
+        return _L2Norm.apply(x, eps, K)
     return x * torch.rsqrt(x.float().pow(2).sum(-1, keepdim=True) + eps).to(x.dtype)
+
+
+def gated_rmsnorm(x, g, w, eps: float):
+    """rmsnorm(x) * w * silu(g)."""
+    K = _native(x)
+    if K is not None and x.shape[-1] <= 512:
+        return _GatedRmsNorm.apply(x, g.to(x.dtype), w, eps, K)
+    return rmsnorm(x, w, eps) * F.silu(g.float()).to(x.dtype)
 
 
 def causal_conv1d_silu(x, w, seg_start):
     """Depthwise causal convolution of width ``w.shape[1]`` along tokens, never crossing a segment start, then SiLU.
     x (n, c), w (c, width), seg_start (n,) index of the first token of each token's segment."""
+    K = _native(x)
+    if K is not None and w.shape[1] <= 4:
+        return _ConvSilu.apply(x, w, seg_start.to(torch.int32), K)
     n, width = x.shape[0], w.shape[1]
     idx = torch.arange(n, device=x.device)
     out = torch.zeros_like(x)

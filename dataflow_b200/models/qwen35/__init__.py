@@ -111,7 +111,7 @@ def linear_attention(c: Qwen35Config, x, w, seg):
     beta = torch.sigmoid((h @ w["w_beta"]).float())
     o = F.gated_delta_rule(q, k, v, g, beta, start)                               # (n, hv, dv)
     gate = (h @ w["w_gate"]).view(n, c.lin_v_heads, c.lin_dv)
-    o = F.rmsnorm(o, w["o_norm"], c.rms_eps) * torch.nn.functional.silu(gate.float()).to(o.dtype)      # gated RMSNorm
+    o = F.gated_rmsnorm(o, gate, w["o_norm"], c.rms_eps)
     return x + o.reshape(n, -1) @ w["wo"]
 
 

@@ -330,6 +330,61 @@ static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c
   TORCH_CHECK(rc == 0, "tp_gemm_rs launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- sequence-mixing helpers
+static void l2norm_fwd(const Tensor& x, Tensor& y, Tensor& rstd, double eps) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(y); CHECK_F32(rstd);
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous(), "l2norm_fwd: contiguous tensors");
+  int rc = dfb::l2norm_fwd(x.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.numel() / x.size(-1), x.size(-1), eps, cur_stream());
+  TORCH_CHECK(rc == 0, "l2norm_fwd failed with code ", rc);
+}
+static void l2norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& rstd, Tensor& dx) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(dy); CHECK_BF16(dx); CHECK_F32(rstd);
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous(), "l2norm_bwd: contiguous tensors");
+  int rc = dfb::l2norm_bwd(dy.data_ptr(), x.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), x.numel() / x.size(-1), x.size(-1), cur_stream());
+  TORCH_CHECK(rc == 0, "l2norm_bwd failed with code ", rc);
+}
+static void gated_rmsnorm_fwd(const Tensor& x, const Tensor& g, const Tensor& w, Tensor& y, Tensor& rstd, double eps) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(g); CHECK_BF16(w); CHECK_BF16(y); CHECK_F32(rstd);
+  TORCH_CHECK(x.is_contiguous() && g.is_contiguous() && y.is_contiguous() && w.numel() == x.size(-1), "gated_rmsnorm_fwd: shapes");
+  int rc = dfb::gated_rmsnorm_fwd(x.data_ptr(), g.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.numel() / x.size(-1),
+                                  x.size(-1), eps, cur_stream());
+  TORCH_CHECK(rc == 0, "gated_rmsnorm_fwd failed with code ", rc);
+}
+static void gated_rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& g, const Tensor& w, const Tensor& rstd, Tensor& dx, Tensor& dg,
+                              Tensor& dw_partial) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(g); CHECK_BF16(w); CHECK_BF16(dy); CHECK_BF16(dx); CHECK_BF16(dg); CHECK_F32(rstd); CHECK_F32(dw_partial);
+  TORCH_CHECK(x.is_contiguous() && g.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dg.is_contiguous() &&
+              dw_partial.dim() == 2 && dw_partial.size(1) == x.size(-1), "gated_rmsnorm_bwd: shapes");
+  int rc = dfb::gated_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), g.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dg.data_ptr(),
+                                  dw_partial.data_ptr<float>(), dw_partial.size(0), x.numel() / x.size(-1), x.size(-1), cur_stream());
+  TORCH_CHECK(rc == 0, "gated_rmsnorm_bwd failed with code ", rc);
+}
+static void conv_silu_fwd(const Tensor& x, const Tensor& w, const Tensor& seg_start, Tensor& y) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(y); CHECK_I32(seg_start);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && y.is_contiguous() && w.is_contiguous() && w.size(0) == x.size(1) && seg_start.numel() == x.size(0),
+              "conv_silu_fwd: shapes");
+  int rc = dfb::conv_silu_fwd(x.data_ptr(), w.data_ptr(), seg_start.data_ptr<int>(), y.data_ptr(), x.size(0), x.size(1), w.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "conv_silu_fwd failed with code ", rc);
+}
+static void conv_silu_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& seg_start, Tensor& dx, Tensor& dw_partial,
+                          int64_t rows_per_block) {
+  CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(dy); CHECK_BF16(dx); CHECK_I32(seg_start); CHECK_F32(dw_partial);
+  TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous() && dw_partial.dim() == 3 && dw_partial.size(1) == x.size(1) &&
+              dw_partial.size(2) == w.size(1) && dw_partial.size(0) * rows_per_block >= x.size(0), "conv_silu_bwd: shapes");
+  int rc = dfb::conv_silu_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), seg_start.data_ptr<int>(), dx.data_ptr(), dw_partial.data_ptr<float>(),
+                              dw_partial.size(0), rows_per_block, x.size(0), x.size(1), w.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "conv_silu_bwd failed with code ", rc);
+}
+static void router_sigmoid_noaux(const Tensor& logits, const Tensor& bias, Tensor& route_w, Tensor& route_ids, int64_t n_group,
+                                 int64_t topk_group, double scaling) {
+  CHECK_CUDA(logits); CHECK_BF16(logits); CHECK_F32(bias); CHECK_F32(route_w); CHECK_I32(route_ids);
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && bias.numel() == logits.size(1) && route_w.size(0) == logits.size(0) &&
+              route_ids.sizes() == route_w.sizes(), "router_sigmoid_noaux: shapes");
+  int rc = dfb::router_sigmoid_noaux(logits.data_ptr(), bias.data_ptr<float>(), route_w.data_ptr<float>(), route_ids.data_ptr<int>(),
+                                     logits.size(0), logits.size(1), route_w.size(1), n_group, topk_group, scaling, cur_stream());
+  TORCH_CHECK(rc == 0, "router_sigmoid_noaux failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- expert-parallel fused kernels
 static void ep_dispatch_mm(std::vector<int64_t> x_src, Tensor& xp, const Tensor& row_src, const Tensor& w, bool transpose_w, Tensor& y,
                            const Tensor& tile_expert, int64_t tokens_per_rank, int64_t rank, Tensor& tile_flags,
@@ -428,6 +483,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rowdot", &moe_rowdot);
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
+  m.def("l2norm_fwd", &l2norm_fwd);
+  m.def("l2norm_bwd", &l2norm_bwd);
+  m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
+  m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
+  m.def("conv_silu_fwd", &conv_silu_fwd);
+  m.def("conv_silu_bwd", &conv_silu_bwd);
+  m.def("router_sigmoid_noaux", &router_sigmoid_noaux);
   m.def("ep_dispatch_mm", &ep_dispatch_mm);
   m.def("ep_pull_rows", &ep_pull_rows);
   m.def("ep_combine", &ep_combine);

@@ -94,6 +94,17 @@ int moe_combine(const void* base, const void* yp, const float* w, const int* row
 int moe_dispatch_bwd(const void* dxp, const int* row_of, void* out, int t, int d, int K, int accumulate, cudaStream_t s);
 int moe_scale_rows(void* xp, const float* w, const int* row_of, int slots, int d, cudaStream_t s);
 int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int slots, int d, cudaStream_t s);
+// sequence-mixing helpers of the linear / latent attention families (seqmix.cu)
+int l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, float eps, cudaStream_t s);
+int l2norm_bwd(const void* dy, const void* x, const float* rstd, void* dx, long long rows, int D, cudaStream_t s);
+int gated_rmsnorm_fwd(const void* x, const void* g, const void* w, void* y, float* rstd, long long rows, int D, float eps, cudaStream_t s);
+int gated_rmsnorm_bwd(const void* dy, const void* x, const void* g, const void* w, const float* rstd, void* dx, void* dg,
+                      float* dw_partial, int blocks, long long rows, int D, cudaStream_t s);
+int conv_silu_fwd(const void* x, const void* w, const int* seg_start, void* y, long long n, int C, int W, cudaStream_t s);
+int conv_silu_bwd(const void* dy, const void* x, const void* w, const int* seg_start, void* dx, float* dw_partial, int row_blocks,
+                  int rows_per_block, long long n, int C, int W, cudaStream_t s);
+int router_sigmoid_noaux(const void* logits, const float* bias, float* route_w, int* route_ids, int t, int E, int K, int n_group,
+                         int topk_group, float scaling, cudaStream_t s);
 // expert parallelism: dispatch fused into the grouped up-projection; pull-and-reduce combine (gemm_grouped.cu, moe_ep.cu)
 int moe_grouped_mm_gather(const unsigned long long* x_src, void* X, const int* row_src, const void* W, void* Y,
                           const int* tile_expert, int Mp, int N, int K, int E, int w_kn, int tokens_per_rank, int rank,

@@ -334,3 +334,71 @@ def moe_grouped_mm(xp, w, tile_expert, out=None, transpose_w: bool = False):
 def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
     native().moe_grouped_wgrad(xp, dyp, dw, offsets_pad, bool(accumulate))
     return dw
+
+
+# ------------------------------------------------------------------ sequence-mixing helpers (seqmix.cu)
+@reg("l2norm_fwd")
+def l2norm_fwd(x, eps: float = 1e-6):
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+    native().l2norm_fwd(xc, y, rstd, float(eps))
+    return y, rstd
+
+
+@reg("l2norm_bwd")
+def l2norm_bwd(dy, x, rstd):
+    dx = torch.empty_like(x, memory_format=torch.contiguous_format)
+    native().l2norm_bwd(dy.contiguous(), x.contiguous(), rstd, dx)
+    return dx
+
+
+@reg("gated_rmsnorm_fwd")
+def gated_rmsnorm_fwd(x, g, w, eps: float = 1e-6):
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+    native().gated_rmsnorm_fwd(xc, g.contiguous(), w.contiguous(), y, rstd, float(eps))
+    return y, rstd
+
+
+@reg("gated_rmsnorm_bwd", 2)
+def gated_rmsnorm_bwd(dy, x, g, w, rstd):
+    xc = x.contiguous()
+    dx, dg = torch.empty_like(xc), torch.empty_like(xc)
+    rows = xc.numel() // xc.shape[-1]
+    blocks = max(min((rows + 7) // 8, 296), 1)
+    part = torch.empty(blocks, xc.shape[-1], dtype=torch.float32, device=x.device)
+    native().gated_rmsnorm_bwd(dy.contiguous(), xc, g.contiguous(), w.contiguous(), rstd, dx, dg, part)
+    return dx, dg, part.sum(0)
+
+
+@reg("conv_silu_fwd")
+def conv_silu_fwd(x, w, seg_start):
+    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+    native().conv_silu_fwd(x.contiguous(), w.contiguous(), seg_start.to(torch.int32), y)
+    return y
+
+
+@reg("conv_silu_bwd", 2)
+def conv_silu_bwd(dy, x, w, seg_start):
+    n, c = x.shape
+    rows_per_block = 64
+    blocks = max((n + rows_per_block - 1) // rows_per_block, 1)
+    dx = torch.empty_like(x, memory_format=torch.contiguous_format)
+    part = torch.empty(blocks, c, w.shape[1], dtype=torch.float32, device=x.device)
+    native().conv_silu_bwd(dy.contiguous(), x.contiguous(), w.contiguous(), seg_start.to(torch.int32), dx, part, rows_per_block)
+    return dx, part.sum(0)
+
+
+@reg("moe_topk_sigmoid_noaux")
+def moe_topk_sigmoid_noaux(logits, bias, top_k: int, n_group: int = 1, topk_group: int = 1, routed_scaling: float = 1.0,
+                           norm_topk: bool = True):
+    if not norm_topk:
+        raise NotImplementedError("the native router normalises the selected weights")
+    t = logits.shape[0]
+    w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    native().router_sigmoid_noaux(logits.to(torch.bfloat16).contiguous(), bias.float().contiguous(), w, ids, int(n_group), int(topk_group),
+                                  float(routed_scaling))
+    return w, ids

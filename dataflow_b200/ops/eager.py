@@ -639,3 +639,70 @@ def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
         g = _mm(xp[a:b].t(), dyp[a:b]) if b > a else torch.zeros_like(dw[i], dtype=torch.float32)
         dw[i].copy_((dw[i].float() + g.float() if accumulate else g).to(dw.dtype))
     return dw
+
+
+# ------------------------------------------------------------------ sequence-mixing helpers (linear / latent attention families)
+@register("l2norm_fwd", "eager")
+def l2norm_fwd(x, eps: float = 1e-6):
+    """y = x * rsqrt(sum x^2 + eps) over the last dim.  Returns (y, rstd (rows,) fp32)."""
+    r = torch.rsqrt(x.float().pow(2).sum(-1) + eps)
+    return (x.float() * r.unsqueeze(-1)).to(x.dtype), r.reshape(-1)
+
+
+@register("l2norm_bwd", "eager")
+def l2norm_bwd(dy, x, rstd):
+    r = rstd.reshape(*x.shape[:-1], 1)
+    xf, gf = x.float(), dy.float()
+    return (r * gf - xf * r.pow(3) * (xf * gf).sum(-1, keepdim=True)).to(x.dtype)
+
+
+@register("gated_rmsnorm_fwd", "eager")
+def gated_rmsnorm_fwd(x, g, w, eps: float = 1e-6):
+    """y = rmsnorm(x) * w * silu(g).  Returns (y, rstd (rows,) fp32)."""
+    r = torch.rsqrt(x.float().pow(2).mean(-1) + eps)
+    n = (x.float() * r.unsqueeze(-1)).to(x.dtype) * w
+    return n * torch.nn.functional.silu(g.float()).to(x.dtype), r.reshape(-1)
+
+
+@register("gated_rmsnorm_bwd", "eager")
+def gated_rmsnorm_bwd(dy, x, g, w, rstd):
+    """Returns (dx, dg, dw fp32)."""
+    r = rstd.reshape(*x.shape[:-1], 1)
+    xf, gf, gy, wf = x.float(), g.float(), dy.float(), w.float()
+    sg = torch.sigmoid(gf)
+    nrm = xf * r
+    dg = gy * nrm * wf * (sg * (1 + gf * (1 - sg)))
+    d_n = gy * gf * sg
+    dw = (d_n * nrm).reshape(-1, x.shape[-1]).sum(0)
+    dn = d_n * wf
+    dx = r * dn - xf * r.pow(3) * (dn * xf).mean(-1, keepdim=True)
+    return dx.to(x.dtype), dg.to(x.dtype), dw
+
+
+@register("conv_silu_fwd", "eager")
+def conv_silu_fwd(x, w, seg_start):
+    """Depthwise causal convolution along tokens (width w.shape[1]) that never crosses a segment start, then SiLU."""
+    n, width = x.shape[0], w.shape[1]
+    idx = torch.arange(n, device=x.device)
+    acc = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    for j in range(width):
+        src = idx - (width - 1 - j)
+        ok = (src >= seg_start.long()).float()[:, None]
+        acc = acc + x[src.clamp(min=0)].float() * ok * w[:, j].float()[None, :]
+    return torch.nn.functional.silu(acc.to(x.dtype).float()).to(x.dtype)
+
+
+@register("conv_silu_bwd", "eager")
+def conv_silu_bwd(dy, x, w, seg_start):
+    """Returns (dx, dw fp32) by differentiating the forward."""
+    with torch.enable_grad():
+        xf, wf = x.float().detach().requires_grad_(True), w.float().detach().requires_grad_(True)
+        n, width = x.shape[0], w.shape[1]
+        idx = torch.arange(n, device=x.device)
+        acc = 0
+        for j in range(width):
+            src = idx - (width - 1 - j)
+            acc = acc + xf[src.clamp(min=0)] * (src >= seg_start.long()).float()[:, None] * wf[:, j][None, :]
+        y = torch.nn.functional.silu(acc)
+        gx, gw = torch.autograd.grad(y, [xf, wf], dy.float())
+    return gx.to(x.dtype), gw

@@ -97,3 +97,66 @@ def test_sgd_step_matches_oracle(momentum):
     assert torch.allclose(w.float().cpu(), w_ref.float(), atol=2e-2, rtol=1e-2)
     if m is not None:
         assert torch.allclose(m.float().cpu(), m_ref.float(), atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.gpu
+def test_l2norm_fwd_and_l2norm_bwd_match_oracle():
+    fwd, fwd_ref = _pair("l2norm_fwd")
+    bwd, bwd_ref = _pair("l2norm_bwd")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(513, 4, 128, device="cuda", generator=g).bfloat16()
+    dy = torch.randn(513, 4, 128, device="cuda", generator=g).bfloat16()
+    y, r = fwd(x)
+    y_ref, r_ref = fwd_ref(x.cpu())
+    assert torch.allclose(y.float().cpu(), y_ref.float(), atol=1e-2, rtol=1e-2) and torch.allclose(r.cpu(), r_ref, rtol=1e-4)
+    assert torch.allclose(bwd(dy, x, r).float().cpu(), bwd_ref(dy.cpu(), x.cpu(), r_ref).float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_gated_rmsnorm_fwd_and_gated_rmsnorm_bwd_match_oracle():
+    fwd, fwd_ref = _pair("gated_rmsnorm_fwd")
+    bwd, bwd_ref = _pair("gated_rmsnorm_bwd")
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(700, 8, 128, device="cuda", generator=g).bfloat16()
+    gate = torch.randn(700, 8, 128, device="cuda", generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(128, device="cuda", generator=g)).bfloat16()
+    dy = torch.randn(700, 8, 128, device="cuda", generator=g).bfloat16()
+    y, r = fwd(x, gate, w)
+    y_ref, r_ref = fwd_ref(x.cpu(), gate.cpu(), w.cpu())
+    assert torch.allclose(y.float().cpu(), y_ref.float(), atol=3e-2, rtol=3e-2)
+    dx, dg, dw = bwd(dy, x, gate, w, r)
+    rx, rg, rw = bwd_ref(dy.cpu(), x.cpu(), gate.cpu(), w.cpu(), r_ref)
+    for a, b in ((dx, rx), (dg, rg), (dw, rw)):
+        assert float((a.float().cpu() - b.float()).norm() / b.float().norm()) < 1e-2
+
+
+@pytest.mark.gpu
+def test_conv_silu_fwd_and_conv_silu_bwd_match_oracle():
+    fwd, fwd_ref = _pair("conv_silu_fwd")
+    bwd, bwd_ref = _pair("conv_silu_bwd")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    n, c = 333, 200
+    x = torch.randn(n, c, device="cuda", generator=g).bfloat16()
+    w = (0.5 * torch.randn(c, 4, device="cuda", generator=g)).bfloat16()
+    dy = torch.randn(n, c, device="cuda", generator=g).bfloat16()
+    start = torch.tensor([0] * 100 + [100] * 133 + [233] * 100, dtype=torch.int32, device="cuda")
+    assert torch.allclose(fwd(x, w, start).float().cpu(), fwd_ref(x.cpu(), w.cpu(), start.cpu()).float(), atol=3e-2, rtol=3e-2)
+    dx, dw = bwd(dy, x, w, start)
+    rx, rw = bwd_ref(dy.cpu(), x.cpu(), w.cpu(), start.cpu())
+    assert float((dx.float().cpu() - rx.float()).norm() / rx.float().norm()) < 1e-2
+    assert float((dw.cpu() - rw).norm() / rw.norm()) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("groups", [(1, 1), (4, 2)])
+def test_moe_topk_sigmoid_noaux_matches_oracle(groups):
+    native, oracle = _pair("moe_topk_sigmoid_noaux")
+    g = torch.Generator(device="cuda").manual_seed(6)
+    logits = torch.randn(1000, 64, device="cuda", generator=g).bfloat16()
+    bias = 0.1 * torch.randn(64, device="cuda", generator=g)
+    w, ids = native(logits, bias, 6, groups[0], groups[1], 2.5)
+    w_ref, ids_ref = oracle(logits.cpu(), bias.cpu(), 6, groups[0], groups[1], 2.5)
+    same = (ids.cpu().sort(-1).values == ids_ref.sort(-1).values.to(torch.int32)).all(-1)
+    assert same.float().mean() > 0.995                    # ties between nearly equal bf16 scores may break differently
+    assert torch.allclose(w.cpu().sum(-1), torch.full((1000,), 2.5), atol=1e-4)
+    assert torch.allclose(w.cpu()[same].sort(-1).values, w_ref[same].sort(-1).values, atol=1e-4)
