@@ -107,6 +107,57 @@ def stage_moe_down_combine(K, d, st):
     K.moe_combine(a["h_mid"], yp, a["route_w"], a["row_of"], out=st["y"])
 
 
+# ---- the same MLP under expert parallelism: this rank holds E / ep experts and serves rows of every rank's tokens.
+# The routing plan (which global token each local row holds, its weight, the padded expert ranges) is saved context;
+# dispatch and combine are the fused kernels of ``parallel.ep.EpGroup``.
+def _ep_group(st):
+    g = st.get("ep")
+    if g is None:
+        raise RuntimeError("expert-parallel MoE stages need the group 'ep' (pass groups={'ep': EpGroup(...)})")
+    return g
+
+
+def ep_plan_from_context(a, d):
+    from ...parallel.ep import EpPlan
+    return EpPlan(ids=a["route_ids"], weights=a["route_w"], row_src=a["row_src"], row_slot=None, row_w=a["row_w"],
+                  tile_expert=a["tile_expert"], offsets_pad=a["offsets_pad"], counts=a["counts"], rows_local=a["row_of"])
+
+
+def stage_ep_route(K, d, st):
+    a, g = st["a"], _ep_group(st)
+    K.linear_fwd_bf16(st["h2"], st["w"]["w_router"], out=a["router_logits"])
+    w, ids = K.moe_topk_softmax(a["router_logits"], d.topk, d.routing_mode)
+    a["route_w"].copy_(w)
+    a["route_ids"].copy_(ids)
+    plan = g.plan(a["route_ids"], a["route_w"])
+    for name in ("row_src", "row_w", "tile_expert", "offsets_pad"):
+        a[name].copy_(getattr(plan, name))
+    # the balance term is per rank and round, like the single-rank layer: counts of THIS rank's slots
+    import torch
+    flat = a["route_ids"].reshape(-1).long()
+    a["counts"].copy_(torch.zeros(d.E, dtype=torch.int32, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int32)))
+    st["plan"] = plan
+
+
+def stage_ep_up(K, d, st):
+    g, plan = _ep_group(st), st["plan"]
+    st["xp"], st["h13p"] = g.dispatch_mm(st["h2"], st["w"]["w13_experts"], plan)
+    st["a"]["row_of"].copy_(plan.rows_local)
+
+
+def stage_ep_act(K, d, st):
+    st["sp"] = K.swiglu_packed_fwd(st["h13p"])
+
+
+def stage_ep_down_combine(K, d, st):
+    g, a = _ep_group(st), st["a"]
+    te = a["tile_expert"] if g.lane == "p2p" else a["tile_expert"].cpu()
+    yp = K.moe_grouped_mm(st["sp"], st["w"]["w2_experts"], te, out=g.rows_buffer() if g.lane == "p2p" else None)
+    g.combine(yp, st["plan"], base=a["h_mid"], weighted=True, out=st["y"])
+
+
+EP_ROUTE_FIELDS = ("router_logits", "route_w", "route_ids", "row_src", "row_w", "offsets_pad", "tile_expert", "counts")
+
 MOE_ROUTE_FIELDS = ("router_logits", "route_w", "route_ids", "row_of", "row_src", "offsets_pad", "tile_expert", "counts")
 
 STAGES_MOE = (
@@ -118,6 +169,13 @@ STAGES_MOE = (
     ("moe_up", stage_moe_up, ("h13p",)),
     ("moe_act", stage_moe_act, ()),
     ("moe_down_combine", stage_moe_down_combine, ()),
+)
+
+STAGES_EP = STAGES_MOE[:4] + (
+    ("ep_route", stage_ep_route, EP_ROUTE_FIELDS),
+    ("ep_up", stage_ep_up, ("row_of",)),
+    ("ep_act", stage_ep_act, ()),
+    ("ep_down_combine", stage_ep_down_combine, ()),
 )
 
 STAGES = (
@@ -147,7 +205,9 @@ def context_rows(d, n):
 class _Block(_Base):
     @property
     def stages(self):
-        return STAGES_MOE if getattr(self.dims, "moe", False) else STAGES
+        if getattr(self.dims, "moe", False):
+            return STAGES_EP if self.dims.ep > 1 else STAGES_MOE
+        return STAGES
 
     def ctx_views(self, buf, n):
         a = self.views(buf, self.lay.ctx, context_rows(self.dims, n))
@@ -168,7 +228,12 @@ class _Block(_Base):
         d = self.dims
         seg = self.segments(ctx)
         n = seg.n_tokens
-        return {"seg": seg, "n": n, "x": self.tview(x_buf, (d.T, d.d))[:n], "w": self.views(w_buf, self.lay.block_w)}
+        st = {"seg": seg, "n": n, "x": self.tview(x_buf, (d.T, d.d))[:n], "w": self.views(w_buf, self.lay.block_w)}
+        if getattr(d, "ep", 1) > 1:
+            if n != d.T:
+                raise ValueError("expert-parallel blocks need full rounds (the peers pull exactly T rows from each rank)")
+            st["ep"] = ctx.groups.get(ctx.task.comm_groups.get("ep", "ep"))
+        return st
 
 
 class BlockFwd(_Block):
@@ -240,7 +305,10 @@ class BlockBwd(_Block):
             if name in g:                       # frozen fields have no gradient storage
                 K.linear_wgrad_bf16(xin, dout, g[name], accumulate=acc)
 
-        dh_mid = (self.bwd_moe if d.moe else self.bwd_mlp)(a, w, g, dy, acc, wgrad)
+        if d.moe and d.ep > 1:
+            dh_mid = self.bwd_moe_ep(st["ep"], a, w, g, dy, acc, wgrad)
+        else:
+            dh_mid = (self.bwd_moe if d.moe else self.bwd_mlp)(a, w, g, dy, acc, wgrad)
         # ---- attention
         wgrad("wo", a["attn_out"], dh_mid)
         dattn = K.linear_dgrad_bf16(dh_mid, w["wo"])
@@ -311,6 +379,40 @@ class BlockBwd(_Block):
         return K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
 
 
+    def bwd_moe_ep(self, grp, a, w, g, dy, acc, wgrad):
+        """Expert-parallel backward: the rows of other ranks' tokens are pulled again (fused with the up-projection, which
+        rebuilds h13p), dy is pulled fused with the down-projection's dgrad, and the owners of the tokens pull
+        d(h2) and d(route_w) back in one combine."""
+        K, d = self.K, self.dims
+        plan = ep_plan_from_context(a, d)
+        te = a["tile_expert"] if grp.lane == "p2p" else a["tile_expert"].cpu()
+        h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
+        xp, h13p = grp.dispatch_mm(h2, w["w13_experts"], plan)
+        sp = K.swiglu_packed_fwd(h13p)
+        dyp, dsp = grp.dispatch_mm(dy, w["w2_experts"], plan, transpose_w=True)
+        dscal = (dsp.float() * sp.float()).sum(-1)                       # <dy W2^T, s> per row, before scaling
+        rw = plan.row_w.unsqueeze(-1)
+        dsp = (dsp.float() * rw).to(dsp.dtype)
+        dyp = (dyp.float() * rw).to(dyp.dtype)
+        if "w2_experts" in g:
+            K.moe_grouped_wgrad(sp, dyp, a["offsets_pad"], g["w2_experts"], accumulate=acc)
+        del sp, dyp
+        dh13p = K.swiglu_packed_bwd(dsp, h13p)
+        del dsp, h13p
+        if "w13_experts" in g:
+            K.moe_grouped_wgrad(xp, dh13p, a["offsets_pad"], g["w13_experts"], accumulate=acc)
+        dxp = K.moe_grouped_mm(dh13p, w["w13_experts"], te, out=grp.rows_buffer() if grp.lane == "p2p" else None, transpose_w=True)
+        del dh13p, xp
+        dh2, d_rw = grp.combine(dxp, plan, base=None, weighted=False, scal=dscal)
+        dlogits = K.moe_router_bwd(d_rw, a["route_w"], a["route_ids"], a["router_logits"], d.routing_mode)
+        if d.aux_coef:
+            K.moe_aux_lb_grad(a["router_logits"], a["counts"], dlogits, d.aux_coef, d.topk)
+        dlog = dlogits.to(h2.dtype)
+        wgrad("w_router", h2, dlog)
+        dh2 = dh2 + K.linear_dgrad_bf16(dlog, w["w_router"])
+        return K.rmsnorm_bwd(dh2, a["h_mid"], w["ffn_norm"], a["rstd_ffn"], dx_add=dy, dw=g.get("ffn_norm"), accumulate=acc)
+
+
 def build_llama3_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device, layouts=None, policy=None):
     from .model import family_layouts
     from ...blocks.layouts import DTypePolicy
@@ -318,6 +420,12 @@ def build_llama3_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device
     lay = layouts or family_layouts(dims, policy or DTypePolicy.from_dict(hyper.get("dtype_policy", "bf16")),
                                     hyper.get("optimizer", "adamw"))
     table = common_executables(dims, lay, kernels, device, hyper)
+    if getattr(dims, "ep", 1) > 1:
+        # every rank sees different tokens: gradients of everything but the (rank-local) experts are summed over the group
+        from ..tp_mlp.blocks import ReplicatedGradSum
+        table["optimizer_block"] = ReplicatedGradSum(table["optimizer_block"], lay.block_dw, None, "ep", skip=("w13_experts", "w2_experts"))
+        table["optimizer_embed"] = ReplicatedGradSum(table["optimizer_embed"], lay.embed_dw, None, "ep")
+        table["optimizer_head"] = ReplicatedGradSum(table["optimizer_head"], lay.head_dw, None, "ep")
     table.update({
         "block_fwd": BlockFwd(dims, lay, kernels, device, hyper),
         "block_recompute": BlockRecompute(dims, lay, kernels, device, hyper),

@@ -48,6 +48,10 @@ class ShapedLlama3Config:
     # tensor + sequence parallelism (tp_mlp family): heads and FFN columns split over ``tp`` ranks, the residual
     # stream split by rows
     tp: int = 1
+    # expert parallelism: experts split over ``ep`` ranks (each keeps its own tokens); dispatched matrices hold
+    # ``ep_capacity`` times the balanced share of rows
+    ep: int = 1
+    ep_capacity: float = 2.0
 
     @property
     def tokens_per_round(self) -> int:
@@ -82,6 +86,13 @@ class Llama3Dims:
     routing_mode: str = "topk_then_softmax"
     aux_coef: float = 0.0
     tp: int = 1                          # > 1: hq / hkv / F are this rank's share; the residual stream holds Ts rows
+    ep: int = 1                          # > 1: this rank holds E / ep experts and serves rows of every rank's tokens
+    ep_capacity: float = 2.0
+
+    @property
+    def El(self) -> int:
+        """Experts held by this rank."""
+        return self.E // self.ep
 
     @property
     def Ts(self) -> int:
@@ -96,6 +107,10 @@ class Llama3Dims:
     def Mp(self) -> int:
         """Rows of the dispatched (expert-major, tile-padded) activation matrix: the static worst case."""
         n = self.T * self.topk
+        if self.ep > 1:
+            # expert parallelism: room for ``ep_capacity`` times the balanced share (at most every slot of every rank)
+            want = int(min(self.ep_capacity * n, self.ep * n))
+            return (want + 255) // 256 * 256 + self.El * 256
         return (n + 255) // 256 * 256 + self.E * 256
 
     @property
@@ -116,7 +131,8 @@ def derive_dims(cfg: ShapedLlama3Config) -> Llama3Dims:
     return Llama3Dims(cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.d_ff, cfg.vocab_size,
                       cfg.rope_theta, cfg.rms_eps, cfg.tokens_per_round, cfg.seq_len,
                       min(cfg.head_chunk_tokens, cfg.tokens_per_round), cfg.qk_norm, cfg.n_experts, cfg.top_k,
-                      cfg.d_ff_expert, cfg.routing_mode, cfg.aux_coef)
+                      cfg.d_ff_expert, cfg.routing_mode, cfg.aux_coef, ep=int(getattr(cfg, "ep", 1)),
+                      ep_capacity=float(getattr(cfg, "ep_capacity", 2.0)))
 
 
 # --------------------------------------------------------------------------- layouts
@@ -129,8 +145,8 @@ def block_fields(d: Llama3Dims) -> tuple[Field, ...]:
           Field("ffn_norm", (d.d,), "bf16", "vector", "ones")]
     if d.moe:
         f += [Field("w_router", (d.d, d.E), "bf16", "matrix", "normal"),
-              Field("w13_experts", (d.E, d.d, 2 * d.Fe), "bf16", "matrix", "normal"),
-              Field("w2_experts", (d.E, d.Fe, d.d), "bf16", "matrix", "normal")]
+              Field("w13_experts", (d.El, d.d, 2 * d.Fe), "bf16", "matrix", "normal"),
+              Field("w2_experts", (d.El, d.Fe, d.d), "bf16", "matrix", "normal")]
     else:
         f += [Field("w13", (d.d, 2 * d.F), "bf16", "matrix", "normal"),
               Field("w2", (d.F, d.d), "bf16", "matrix", "normal")]
@@ -171,9 +187,14 @@ def _context_layout_full(d: Llama3Dims) -> PackedLayout:
         # re-route; h13p is the up-projection of the dispatched rows (expert-major)
         f += [Field("router_logits", (d.T, d.E), "bf16"), Field("route_w", (d.T, d.topk), "fp32"),
               Field("route_ids", (d.T, d.topk), "int32"), Field("row_of", (d.T, d.topk), "int32"),
-              Field("row_src", (d.Mp,), "int32"), Field("offsets_pad", (d.E + 1,), "int32"),
-              Field("tile_expert", (d.Mp // 256,), "int32"), Field("counts", (d.E,), "int32"),
-              Field("h13p", (d.Mp, 2 * d.Fe), "bf16")]
+              Field("row_src", (d.Mp,), "int32"), Field("offsets_pad", (d.El + 1,), "int32"),
+              Field("tile_expert", (d.Mp // 256,), "int32"), Field("counts", (d.E,), "int32")]
+        if d.ep > 1:
+            # rows of other ranks' tokens are pulled again in the backward, which rebuilds h13p with them: only the
+            # routing plan is context (row_of = the row every local slot got at its expert's owner)
+            f.append(Field("row_w", (d.Mp,), "fp32"))
+        else:
+            f.append(Field("h13p", (d.Mp, 2 * d.Fe), "bf16"))
     else:
         f.append(Field("h13", (d.T, 2 * d.F), "bf16"))
     return PackedLayout(tuple(f))
@@ -270,9 +291,9 @@ def block_kind_spec(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware, optim
         "block", w, dw, o, lay.ctx.size_bytes, fwd_us, bwd_us, fwd_us, optimizer_cost_seed(hw, w, dw, o, optimizer),
         fwd_sub, bwd_sub, fwd_sub, (_subop("optimizer", nbytes=2 * w + dw + 2 * o, eff="memory"),),
         ws_f, ws_b, 0,
-        recompute_levels=((1, lay.extra["Ap"].size_bytes,
-                           hw.matmul_us(2.0 * T * d.d * (2 * d.Fe * d.topk if d.moe else 2 * d.F)) + hw.mem_us(ew_bytes / 3)),
-                          (2, 0, fwd_us)))
+        recompute_levels=(((1, lay.extra["Ap"].size_bytes,
+                            hw.matmul_us(2.0 * T * d.d * (2 * d.Fe * d.topk if d.moe else 2 * d.F)) + hw.mem_us(ew_bytes / 3)),)
+                          if d.ep == 1 else ()) + ((2, 0, fwd_us),))
 
 
 def loose_costs(d: Llama3Dims, lay: FamilyLayouts, hw: ShapedHardware) -> LooseCosts:
@@ -308,9 +329,9 @@ def lower_llama3(cfg: ShapedLlama3Config, recompute_levels: Mapping[int, int] | 
         embed_w_bytes=lay.embed_w.size_bytes, embed_dw_bytes=lay.embed_dw.size_bytes, embed_o_bytes=lay.embed_o.size_bytes,
         head_w_bytes=lay.head_w.size_bytes, head_dw_bytes=lay.head_dw.size_bytes, head_o_bytes=lay.head_o.size_bytes,
         loose=loose_costs(d, lay, hw), hw=hw, recompute_levels=recompute_levels, block_params=block_params,
-        comm_groups=comm_groups, zero=zero, resident_params=resident_params,
+        comm_groups=({"ep": "ep", **dict(comm_groups or {})} if d.ep > 1 else comm_groups), zero=zero, resident_params=resident_params,
         metadata={"family": cfg.family, "preset": cfg.name, "flops_per_token": flops_per_token(cfg),
-                  "seq_len": cfg.seq_len, "batch": cfg.batch})
+                  "seq_len": cfg.seq_len, "batch": cfg.batch, **({"ep": d.ep} if d.ep > 1 else {})})
 
 
 # --------------------------------------------------------------------------- init
@@ -331,9 +352,11 @@ def init_field(t, f: Field, gen, n_layers: int, std: float = 0.02) -> None:
             flat[lo:lo + n].copy_(torch.empty(n, dtype=torch.float32).normal_(0.0, s, generator=gen))
 
 
-def initial_values(program: Program, cfg: ShapedLlama3Config, views_of, seed: int = 0, layouts: FamilyLayouts | None = None) -> None:
+def initial_values(program: Program, cfg: ShapedLlama3Config, views_of, seed: int = 0, layouts: FamilyLayouts | None = None,
+                   rank: int = 0) -> None:
     """Write seeded initial parameters and optimizer state.  ``views_of(object_id, layout)`` returns
-    name → tensor views over that object's backing bytes."""
+    name → tensor views over that object's backing bytes.  Under expert parallelism every rank draws the full expert
+    stacks from the seeded generator and keeps the experts it owns (``rank``)."""
     import torch
     d = derive_dims(cfg)
     lay = layouts or family_layouts(d, cfg.policy(), cfg.optimizer)
@@ -346,7 +369,12 @@ def initial_values(program: Program, cfg: ShapedLlama3Config, views_of, seed: in
         wl = lay.layout_of(oid)
         wv = views_of(oid, wl)
         for f in wl.fields:
-            init_field(wv[f.name], f, gen, d.n_layers)
+            if d.ep > 1 and f.name in ("w13_experts", "w2_experts"):
+                full = torch.empty((d.E,) + tuple(f.shape[1:]), dtype=torch.float32)
+                init_field(full, f, gen, d.n_layers)
+                wv[f.name].copy_(full[rank * d.El:(rank + 1) * d.El].to(wv[f.name].dtype))
+            else:
+                init_field(wv[f.name], f, gen, d.n_layers)
         oname = "O" + oid[1:]
         if oname in ids:
             ol = lay.layout_of(oname)

@@ -23,10 +23,10 @@ from ...data.segments import make_segments
 from ..llama3.blocks import _qkv_views
 
 
-def _group(ctx):
-    g = ctx.groups.get(ctx.task.comm_groups.get("tp", "tp"))
+def _group(ctx, key: str = "tp"):
+    g = ctx.groups.get(ctx.task.comm_groups.get(key, key))
     if g is None:
-        raise RuntimeError(f"task {ctx.task.id} needs the tensor-parallel group 'tp' (pass groups={{'tp': TpGroup(...)}})")
+        raise RuntimeError(f"task {ctx.task.id} needs the group {key!r} (pass groups={{{key!r}: ...}})")
     return g
 
 
@@ -170,8 +170,8 @@ class ReplicatedGradSum:
     """Wraps an optimizer executable: sums the gradients of parameters every rank holds in full over the group first.
     ``fields``: names inside the packed gradient object, or ``None`` for all of them."""
 
-    def __init__(self, inner, layout_of_grad, fields):
-        self.inner, self.layout_of_grad, self.fields = inner, layout_of_grad, fields
+    def __init__(self, inner, layout_of_grad, fields, group: str = "tp", skip=()):
+        self.inner, self.layout_of_grad, self.fields, self.group, self.skip = inner, layout_of_grad, fields, group, tuple(skip)
 
     def launch(self, ctx):
         inner = self.inner
@@ -183,10 +183,10 @@ class ReplicatedGradSum:
             self.run(ctx)
 
     def run(self, ctx):
-        g = _group(ctx)
+        g = _group(ctx, self.group)
         views = self.inner.views(ctx.inputs[1], self.layout_of_grad)
         for name, t in views.items():
-            if self.fields is None or name in self.fields:
+            if (self.fields is None or name in self.fields) and name not in self.skip:
                 g.all_reduce(t)
         self.inner.run(ctx)
 

@@ -113,6 +113,13 @@ class EpGroup:
                 self.err.zero_()
                 raise RuntimeError(f"fused expert-parallel kernel gave up: phase {code >> 8}, peer/rank {code & 255}")
 
+    def all_reduce(self, t):
+        """Sum over the group (gradients of the parameters every rank holds in full)."""
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.all_reduce(t)
+        return t
+
     # -- symmetric buffers (this rank's views)
     def _view(self, off: int, shape, dtype: str):
         from ..ops import native
@@ -184,14 +191,14 @@ class EpGroup:
         return plan
 
     # -- fused ops
-    def dispatch_mm(self, x, w, plan: EpPlan, transpose_w: bool = False):
+    def dispatch_mm(self, x, w, plan: EpPlan, transpose_w: bool = False, out=None):
         """``x``: this rank's (T, d) rows — ideally ``x_buffer()`` itself; ``w``: this rank's experts, (E_local, d, N)
         (or (E_local, N, d) with ``transpose_w``).  Returns ``(xp (C, d), y (C, N))``: the gathered rows and their
         products.  On the first call of a layer also resolves ``plan.rows_local``."""
         import torch
         n = w.shape[1] if transpose_w else w.shape[2]
         xp = torch.empty(self.C, self.d, dtype=x.dtype, device=x.device)
-        y = torch.empty(self.C, n, dtype=x.dtype, device=x.device)
+        y = out if out is not None else torch.empty(self.C, n, dtype=x.dtype, device=x.device)
         if self.lane != "p2p":
             return self._dispatch_mm_collective(x, w, plan, transpose_w, xp, y)
         from ..ops import native
@@ -210,12 +217,12 @@ class EpGroup:
             LAUNCHES.total += 1
         return xp, y
 
-    def combine(self, rows, plan: EpPlan, base=None, weighted: bool = True, scal=None):
+    def combine(self, rows, plan: EpPlan, base=None, weighted: bool = True, scal=None, out=None):
         """``rows``: this rank's (C, d) expert rows — ideally ``rows_buffer()`` itself.  Returns ``y`` (T, d) with
         ``y[t] = base[t] + sum_k w[t, k] rows_owner[row]`` (weights 1 when not ``weighted``); with ``scal`` (C,) fp32
         per-row values also returns the (T, K) values of this rank's slots."""
         import torch
-        out = torch.empty(self.T, self.d, dtype=rows.dtype, device=rows.device)
+        out = out if out is not None else torch.empty(self.T, self.d, dtype=rows.dtype, device=rows.device)
         out_s = torch.empty(self.T, self.K, dtype=torch.float32, device=rows.device) if scal is not None else None
         if self.lane != "p2p":
             return self._combine_collective(rows, plan, base, weighted, scal, out, out_s)

@@ -99,6 +99,20 @@ def plan_at_budget(family, cfg, budget_bytes: int | None, hw: ShapedHardware | N
                         leeway_bytes=DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else leeway_bytes)
 
 
+def _agree_across_ranks(value):
+    """Every rank of a job must plan the SAME program (the same recompute choices give the same task list, hence the
+    same order of collectives): planning inputs that were measured per rank are replaced by rank 0's."""
+    try:
+        import torch.distributed as dist
+    except ImportError:
+        return value
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return value
+    box = [value]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
 class Trainer:
     """Single-process engine training loop over one device (or the CPU backend)."""
 
@@ -141,6 +155,7 @@ class Trainer:
                 from .profiling import profile_program
                 bare = self.fam.lower(cfg, hw=self.hw, **dict(lower_kwargs or {}))
                 measured = profile_program(self, bare)
+                measured = _agree_across_ranks(measured)
             planned = plan_at_budget(self.fam, cfg, budget, self.hw, recompute=recompute, measured=measured,
                                      leeway_bytes=leeway_bytes, lower_kwargs=lower_kwargs)
         self.planned = planned
@@ -207,7 +222,8 @@ class Trainer:
                                 int(self.zero["rank"]), int(self.zero["world"]), int(self.zero["stage"]))
         else:
             # a tensor-parallel family cuts the same seeded full model differently on every rank
-            kw = {"rank": self.groups["tp"].rank} if "tp" in self.groups else {}
+            sliced = next((self.groups[k] for k in ("tp", "ep") if k in self.groups), None)
+            kw = {"rank": sliced.rank} if sliced is not None else {}
             self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts, **kw)
 
     # -- data

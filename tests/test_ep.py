@@ -72,3 +72,60 @@ def test_ep_fused_kernels_match_dense_oracle(lane, tmp_path):
     assert got["dropped"] == 0
     for k, v in got["max_rel"].items():
         assert v < 2e-2, (k, v)
+
+
+def launch_family(world, device_kind, tmp_path, lane=None, port=29731, budget=None):
+    out = tmp_path / f"epfam_{device_kind}_{lane}_{budget}.json"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    env.pop("DATAFLOW_EP_LANE", None)
+    env.pop("EP_TEST_BUDGET", None)
+    if lane:
+        env["DATAFLOW_EP_LANE"] = lane
+    if budget:
+        env["EP_TEST_BUDGET"] = str(budget)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "dist_worker_epfam.py"), str(out), device_kind]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    if r.returncode:
+        at = r.stderr.find("Traceback")
+        raise AssertionError(r.stderr[at:at + 3000] if at >= 0 else r.stdout[-1500:] + r.stderr[-1500:])
+    return json.loads(out.read_text())
+
+
+def solo_olmoe_losses():
+    """One process, all experts, both ranks' data in one step (twice the rounds): the math the EP run must reproduce."""
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import Trainer, synthetic_rounds
+    fam = resolve_family("olmoe")
+    base = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
+    cfg = dataclasses.replace(base, grad_accum_rounds=base.grad_accum_rounds * 2)
+    tr = Trainer("olmoe", cfg, budget_gib=None, device=None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=5, leeway_bytes=0)
+    losses = []
+    try:
+        for s in range(3):
+            data = []
+            for rank in range(2):
+                data += synthetic_rounds(base, base.grad_accum_rounds, tr.T, 64, 100 + rank, s)
+            losses.append(tr.step(data))
+    finally:
+        tr.close()
+    return losses
+
+
+def test_olmoe_with_experts_split_over_two_cpu_ranks_matches_one_process(tmp_path):
+    got = launch_family(2, "cpu", tmp_path, port=29733)
+    ref = solo_olmoe_losses()
+    for a, b in zip(got["losses"], ref):
+        assert a == pytest.approx(b, rel=1e-3)
+    assert got["losses"][-1] < got["losses"][0]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+def test_olmoe_expert_parallel_fused_lane_trains_like_the_collective_lane(tmp_path):
+    p2p = launch_family(2, "cuda", tmp_path, lane="p2p", port=29735)
+    col = launch_family(2, "cuda", tmp_path, lane="collective", port=29737)
+    for a, b in zip(p2p["losses"], col["losses"]):
+        assert a == pytest.approx(b, rel=2e-2)
+    assert p2p["losses"][-1] < p2p["losses"][0]
