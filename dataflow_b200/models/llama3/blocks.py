@@ -151,8 +151,8 @@ def stage_ep_act(K, d, st):
 
 def stage_ep_down_combine(K, d, st):
     g, a = _ep_group(st), st["a"]
-    te = a["tile_expert"] if g.lane == "p2p" else a["tile_expert"].cpu()
-    yp = K.moe_grouped_mm(st["sp"], st["w"]["w2_experts"], te, out=g.rows_buffer() if g.lane == "p2p" else None)
+    # the table stays where the rows are: the native grouped GEMM reads it on the device, the eager one copies it itself
+    yp = K.moe_grouped_mm(st["sp"], st["w"]["w2_experts"], a["tile_expert"], out=g.rows_buffer() if g.lane == "p2p" else None)
     g.combine(yp, st["plan"], base=a["h_mid"], weighted=True, out=st["y"])
 
 
@@ -385,7 +385,7 @@ class BlockBwd(_Block):
         d(h2) and d(route_w) back in one combine."""
         K, d = self.K, self.dims
         plan = ep_plan_from_context(a, d)
-        te = a["tile_expert"] if grp.lane == "p2p" else a["tile_expert"].cpu()
+        te = a["tile_expert"]
         h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
         xp, h13p = grp.dispatch_mm(h2, w["w13_experts"], plan)
         sp = K.swiglu_packed_fwd(h13p)

@@ -10,9 +10,10 @@
 using at::Tensor;
 
 #define CHECK_CUDA(x) TORCH_CHECK((x).is_cuda(), #x " must be a CUDA tensor")
-#define CHECK_BF16(x) TORCH_CHECK((x).scalar_type() == at::kBFloat16, #x " must be bf16")
-#define CHECK_F32(x) TORCH_CHECK((x).scalar_type() == at::kFloat, #x " must be fp32")
-#define CHECK_I32(x) TORCH_CHECK((x).scalar_type() == at::kInt, #x " must be int32")
+// every kernel here dereferences its operands on the device: a host tensor is refused, never launched on
+#define CHECK_BF16(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kBFloat16, #x " must be a bf16 CUDA tensor")
+#define CHECK_F32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kFloat, #x " must be an fp32 CUDA tensor")
+#define CHECK_I32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kInt, #x " must be an int32 CUDA tensor")
 #define CHECK_CONTIG(x) TORCH_CHECK((x).is_contiguous(), #x " must be contiguous")
 
 static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }

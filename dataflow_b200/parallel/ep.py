@@ -316,7 +316,7 @@ def ep_moe_forward(g: EpGroup, h, ids, weights, w13, w2, base=None, ks=None):
     plan = g.plan(ids, weights)
     xp, h13 = g.dispatch_mm(h, w13, plan)
     sp = ks.swiglu_packed_fwd(h13)
-    te = plan.tile_expert if p2p else plan.tile_expert.cpu()
+    te = plan.tile_expert
     yp = ks.moe_grouped_mm(sp, w2, te, out=g.rows_buffer() if p2p else None)
     y = g.combine(yp, plan, base=base, weighted=True)
     # the peer-readable rows are overwritten by the next layer: the backward keeps its own copy
@@ -328,7 +328,7 @@ def ep_moe_backward(g: EpGroup, dy, saved, w13, w2, dw13, dw2, accumulate: bool 
     ks = _kernels(g, ks)
     p2p = g.lane == "p2p"
     plan, xp, h13, sp, yp = saved["plan"], saved["xp"], saved["h13"], saved["sp"], saved["yp"]
-    te = plan.tile_expert if p2p else plan.tile_expert.cpu()
+    te = plan.tile_expert
     # d(rows): every local row receives dy of the token it serves; the down-projection's dgrad is fused with that pull
     dyp, dsp_unscaled = g.dispatch_mm(dy, w2, plan, transpose_w=True)
     # router-weight gradient <dy, y_row>, computed where the row lives
