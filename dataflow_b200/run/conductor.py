@@ -35,7 +35,7 @@ class RunSpec:
     budget_gib: float | None = None
     device: int | None = 0                  # None = CPU backend
     world: int = 1
-    parallel: str = "fsdp"                  # fsdp | zero3 | zero1 (world > 1)
+    parallel: str = "fsdp"                  # fsdp | zero3 | zero1 | tp | ep (world > 1)
     seed: int = 0
     profile: bool = False
     recompute: bool = True

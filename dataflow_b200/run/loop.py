@@ -57,13 +57,19 @@ def _dist():
     return None
 
 
-def put_rank_rounds(trainer: Trainer, packed, rank: int, rounds: int) -> tuple[int, dict[int, list[int]], int]:
-    """Copy this rank's rounds of a packed step into the store.  Returns (bytes written, seq_lens, local valid rows)."""
+def put_rank_rounds(trainer: Trainer, packed, rank: int, rounds: int, row_shard: tuple[int, int] | None = None) -> tuple[int, dict[int, list[int]], int]:
+    """Copy this rank's rounds of a packed step into the store.  Returns (bytes written, seq_lens, local valid rows).
+    ``row_shard = (index, count)``: sequence parallelism — every rank takes the SAME rounds and keeps its slice of rows
+    (the sequence bounds stay those of the whole round: attention sees all rows)."""
     import torch
     nbytes, seq_lens, valid = 0, {}, 0
     for r in range(rounds):
-        rd = packed.rounds[rank * rounds + r]
-        nbytes += trainer.put_round(r, torch.from_numpy(rd.tokens), torch.from_numpy(rd.targets))
+        rd = packed.rounds[(0 if row_shard else rank * rounds) + r]
+        tk, tg = torch.from_numpy(rd.tokens), torch.from_numpy(rd.targets)
+        if row_shard:
+            n = len(rd.tokens) // row_shard[1]
+            tk, tg = tk[row_shard[0] * n:(row_shard[0] + 1) * n].contiguous(), tg[row_shard[0] * n:(row_shard[0] + 1) * n].contiguous()
+        nbytes += trainer.put_round(r, tk, tg)
         b = list(rd.bounds)
         if rd.content < len(rd.tokens):
             b.append(len(rd.tokens))          # the tail rides as one masked segment: defined values, zero loss
@@ -83,6 +89,10 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
     dist = _dist()
     rank = dist.get_rank() if dist else 0
     world = dist.get_world_size() if dist else 1
+    # data-parallel ranks (fsdp / zero / ep) consume different rounds; tensor-parallel ranks share them and split the rows
+    tp = int((trainer.program.metadata or {}).get("tp", 1))
+    row_shard = (rank, tp) if tp > 1 else None
+    data_world = 1 if row_shard else world
     stepper = factory(dict(cursor) if cursor else None)
     ahead = PackAhead(stepper)
     res = RunResult(losses=list(losses or []), tokens_per_step=trainer.T * trainer.rounds * world,
@@ -99,10 +109,10 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                 if log and rank == 0:
                     log(f"data source exhausted after {s} steps")
                 break
-            if len(packed.rounds) != trainer.rounds * world:
-                raise ValueError(f"packed step has {len(packed.rounds)} rounds, the job consumes {trainer.rounds * world}")
+            if len(packed.rounds) != trainer.rounds * data_world:
+                raise ValueError(f"packed step has {len(packed.rounds)} rounds, the job consumes {trainer.rounds * data_world}")
             t0 = time.perf_counter()
-            _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds)
+            _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds, row_shard)
             total_valid = packed.valid_rows          # every rank packed the whole job's step: no exchange needed
             loss = trainer.step(None, seq_lens=seq_lens, valid_rows=max(total_valid, 1))
             if dist:

@@ -42,12 +42,35 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         else:
             torch.cuda.set_device(device)
             dist.init_process_group("nccl", device_id=torch.device("cuda", device))
-        from ..parallel.zero import make_dp_group, zero_lower_kwargs
-        groups = {"dp": make_dp_group(rank, world, device)}
-        lower_kwargs = zero_lower_kwargs(spec.parallel, rank, world)
+        if spec.parallel not in ("tp", "ep"):
+            from ..parallel.zero import make_dp_group, zero_lower_kwargs
+            groups = {"dp": make_dp_group(rank, world, device)}
+            lower_kwargs = zero_lower_kwargs(spec.parallel, rank, world)
     elif spec.resident_params:
         lower_kwargs = {"resident_params": True}
     family, cfg = build_cfg(spec)
+    data_world = world
+    if world > 1 and spec.parallel == "tp":
+        # tensor + sequence parallelism: the dense llama block split over the ranks (family tp_mlp)
+        from ..parallel.tp import TpGroup
+        if family not in ("llama3", "tp_mlp"):
+            raise ValueError(f"--parallel tp covers the dense llama block (llama3 / tp_mlp presets), not {family!r}")
+        family, cfg = "tp_mlp", dataclasses.replace(cfg, tp=world, family="tp_mlp")
+        from ..models.families import resolve_family
+        d = resolve_family(family).derive_dims(cfg)
+        groups = {"tp": TpGroup(rank, world, device, max_rows=d.Ts, max_k=d.d, max_n=d.d)}
+        lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
+        data_world = 1
+    elif world > 1 and spec.parallel == "ep":
+        # expert parallelism: experts split over the ranks, everything else data-parallel
+        from ..models.families import resolve_family
+        from ..parallel.ep import EpGroup
+        cfg = dataclasses.replace(cfg, ep=world)
+        d = resolve_family(family).derive_dims(cfg)
+        if not getattr(d, "moe", False):
+            raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} is dense")
+        groups = {"ep": EpGroup(rank, world, device, tokens=d.T, d_model=d.d, n_experts=d.E, top_k=d.topk, capacity_factor=cfg.ep_capacity)}
+        lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
     recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
     say = log if rank == 0 else (lambda *a, **k: None)
     tr = Trainer(family, cfg, budget_gib=spec.budget_gib, device=device, hyper=recipe.hyper(), seed=spec.seed,
@@ -56,7 +79,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     say(f"plan: {tr.planned.policy}, predicted {tr.planned.makespan_us / 1e3:.1f} ms/step, peak fast "
         f"{tr.planned.peak_fast_bytes / 2 ** 30:.2f} GiB, planned in {tr.plan_s:.1f} s")
     # the job-wide pipeline: every rank packs all rounds of the step and keeps its own
-    wide = dataclasses.replace(cfg, grad_accum_rounds=cfg.grad_accum_rounds * world)
+    wide = dataclasses.replace(cfg, grad_accum_rounds=cfg.grad_accum_rounds * data_world)
     factory = pipeline_from_args(wide, spec.data, policy=spec.packing_policy, allow_round_split=spec.allow_round_split,
                                  capture=spec.capture if rank == 0 else None)
     start, cursor, losses = 0, None, []

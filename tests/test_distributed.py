@@ -119,3 +119,20 @@ def test_daemon_start_status_stop(tmp_path):
     finally:
         subprocess.call([sys.executable, os.path.join(ROOT, "tools/train/daemonize.py"), "--pidfile", sock[:-5] + ".pid", "--kill"],
                         stderr=subprocess.DEVNULL)
+
+
+@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny")])
+def test_train_cli_runs_tensor_and_expert_parallel_jobs_on_cpu_ranks(parallel, preset, tmp_path):
+    """`train.py train --gpus 2 --parallel tp|ep` end to end on two gloo ranks: packed data, loop, result file."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / f"{parallel}.json"
+    cmd = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", preset, "--steps", "3", "--device", "cpu",
+           "--gpus", "2", "--parallel", parallel, "--out", str(out), "--dtype-policy", "fp32"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
+    res = json.loads(out.read_text())
+    assert len(res["losses"]) == 3 and res["losses"][-1] < res["losses"][0]
+    assert res["meta"]["world"] == 2

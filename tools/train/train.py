@@ -39,7 +39,9 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--fast-budget", type=float, default=None, help="device memory budget in GiB")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--device", default="0", help="CUDA ordinal, or 'cpu'")
-    ap.add_argument("--opt-shard", default="fsdp", choices=["fsdp", "zero3", "zero1", "zero1rs"])
+    ap.add_argument("--opt-shard", "--parallel", dest="opt_shard", default="fsdp", choices=["fsdp", "zero3", "zero1", "zero1rs", "tp", "ep"],
+                    help="how --gpus N ranks split the job: fsdp / zero3 / zero1 shard parameters and optimizer state over data-parallel "
+                         "ranks; tp = tensor + sequence parallel llama blocks; ep = experts split over the ranks (MoE presets)")
     ap.add_argument("--kernels", default=None, help="kernel lane: sm100 | baseline | eager")
     ap.add_argument("--profile", action="store_true", help="plan from measured task costs")
     ap.add_argument("--no-recompute", action="store_true")
