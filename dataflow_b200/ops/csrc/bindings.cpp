@@ -331,6 +331,37 @@ static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c
   TORCH_CHECK(rc == 0, "tp_gemm_rs launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- fp8 lane
+static bool is_fp8_or_u8(const Tensor& t) {
+  return t.scalar_type() == at::kByte || t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kFloat8_e5m2;
+}
+static void quant_fp8_rowwise(const Tensor& x, Tensor& q, Tensor& scale) {
+  CHECK_BF16(x); CHECK_F32(scale);
+  TORCH_CHECK(q.is_cuda() && is_fp8_or_u8(q) && x.dim() == 2 && x.stride(1) == 1 && q.stride(1) == 1 && q.sizes() == x.sizes() &&
+              scale.numel() == x.size(0), "quant_fp8_rowwise: x (rows, K) bf16, q (rows, K) fp8, scale (rows)");
+  int rc = dfb::quant_fp8_rowwise(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), scale.data_ptr<float>(), x.size(0), x.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "quant_fp8_rowwise: K and the row strides must be multiples of 8 (code ", rc, ")");
+}
+static void gemm_fp8(const Tensor& a, const Tensor& b, Tensor& d, c10::optional<Tensor> row_scale, c10::optional<Tensor> col_scale,
+                     c10::optional<Tensor> addend, c10::optional<Tensor> bias) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda() && is_fp8_or_u8(a) && is_fp8_or_u8(b), "gemm_fp8: fp8 CUDA operands");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1) && d.size(0) == a.size(0) &&
+              d.size(1) == b.size(0) && d.stride(1) == 1, "gemm_fp8: a (M, K), b (N, K), d (M, N)");
+  const bool f32 = d.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || d.scalar_type() == at::kBFloat16, "gemm_fp8: d is bf16 or fp32");
+  if (row_scale.has_value()) { CHECK_F32((*row_scale)); TORCH_CHECK(row_scale->numel() == a.size(0), "row_scale has M entries"); }
+  if (col_scale.has_value()) { CHECK_F32((*col_scale)); TORCH_CHECK(col_scale->numel() == b.size(0), "col_scale has N entries"); }
+  if (addend.has_value()) TORCH_CHECK(addend->is_cuda() && addend->scalar_type() == d.scalar_type() && addend->sizes() == d.sizes(), "addend like d");
+  if (bias.has_value()) CHECK_BF16((*bias));
+  auto fmt = [](const Tensor& t) { return t.scalar_type() == at::kFloat8_e5m2 ? 1 : 0; };
+  int rc = dfb::gemm_fp8_2sm(a.data_ptr(), a.stride(0), fmt(a), b.data_ptr(), b.stride(0), fmt(b), d.data_ptr(), d.stride(0), f32,
+                             row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr,
+                             col_scale.has_value() ? col_scale->data_ptr<float>() : nullptr,
+                             addend.has_value() ? addend->data_ptr() : nullptr, addend.has_value() ? addend->stride(0) : 0,
+                             bias.has_value() ? bias->data_ptr() : nullptr, a.size(0), b.size(0), a.size(1), num_sms(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm_fp8 failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- sequence-mixing helpers
 static void l2norm_fwd(const Tensor& x, Tensor& y, Tensor& rstd, double eps) {
   CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(y); CHECK_F32(rstd);
@@ -484,6 +515,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rowdot", &moe_rowdot);
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
+  m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
+  m.def("gemm_fp8", &gemm_fp8);
   m.def("l2norm_fwd", &l2norm_fwd);
   m.def("l2norm_bwd", &l2norm_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);

@@ -51,6 +51,10 @@ struct Params {
   int group_m;
   int tma_epi;                  // epilogue through shared memory + TMA (needs addend dtype == D dtype)
   int* err;
+  // fp8 operands: D[m, n] = acc[m, n] * row_scale[m] * col_scale[n] (dequantisation; either may be null = 1)
+  const float* row_scale;
+  const float* col_scale;
+  int a_fmt, b_fmt;             // 0 = e4m3, 1 = e5m2
 };
 
 struct SharedBarriers {
@@ -73,7 +77,8 @@ DFB_DEVICE void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, i
   nb = r / gm;
 }
 
-template <bool A_MN, bool B_MN>
+// FP8: operands are one byte wide and K-major; a stage holds 128 elements of K (the same 128-byte swizzled rows)
+template <bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_add, Params p) {
@@ -86,7 +91,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const int m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;        // elements of K per stage (128 bytes per row either way)
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  const int k_blocks = (p.K + BKE - 1) / BKE;
   volatile int* abort_flag = &sb->abort;
 
   if (threadIdx.x == 0) {
@@ -133,14 +140,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int c = 0; c < HALF_M / 64; ++c)
               ptx::tma_load_2d_pair(sa + c * CHUNK_BYTES, &tmap_a, &sb->full[s], m0 + c * 64, kb * BK);
           } else {
-            ptx::tma_load_2d_pair(sa, &tmap_a, &sb->full[s], kb * BK, m0);
+            ptx::tma_load_2d_pair(sa, &tmap_a, &sb->full[s], kb * BKE, m0);
           }
           if (B_MN) {
 #pragma unroll
             for (int c = 0; c < HALF_N / 64; ++c)
               ptx::tma_load_2d_pair(sbm + c * CHUNK_BYTES, &tmap_b, &sb->full[s], n0 + c * 64, kb * BK);
           } else {
-            ptx::tma_load_2d_pair(sbm, &tmap_b, &sb->full[s], kb * BK, n0);
+            ptx::tma_load_2d_pair(sbm, &tmap_b, &sb->full[s], kb * BKE, n0);
           }
         }
       }
@@ -148,7 +155,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (cta == 0 && ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? ptx::idesc_f8_f32(BM, BN, p.a_fmt, p.b_fmt) : ptx::idesc_bf16_f32(BM, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       for (int tile = cluster_id; tile < num_tiles && !*abort_flag; tile += num_clusters, ++tcount) {
         int acc = tcount & 1;
@@ -169,8 +176,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           constexpr uint64_t a_step = (A_MN ? UK * 128 : UK * 2) >> 4;
           constexpr uint64_t b_step = (B_MN ? UK * 128 : UK * 2) >> 4;
 #pragma unroll
-          for (int k = 0; k < BK / UK; ++k)
-            ptx::umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UK; ++k) {
+            // one instruction consumes 32 bytes of K per row in both kinds: 16 bf16 or 32 fp8 elements
+            if (FP8) ptx::umma_f8_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
+            else ptx::umma_bf16_pair(tmem_d, adesc + k * a_step, bdesc + k * b_step, idesc, (kb | k) != 0);
+          }
           ptx::umma_commit_pair(&sb->empty[s], 0x3);        // both CTAs may refill this stage
         }
         if (failed) break;
@@ -227,6 +237,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+          }
+          if (FP8) {
+            const int row = row0 + lane;
+            const float rs = (p.row_scale && row < p.M) ? p.row_scale[row] : 1.f;
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (i < box_cols) f[i] *= rs * ((p.col_scale && col0 + i < p.N) ? p.col_scale[col0 + i] : 1.f);
           }
           if (p.bias) {
             const bf16* bp = reinterpret_cast<const bf16*>(p.bias) + col0;
@@ -399,14 +416,14 @@ static EncodeFn encode_fn() {
 }
 
 static bool make_map(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
-                     uint32_t box_outer, bool f32 = false) {
+                     uint32_t box_outer, bool f32 = false, bool u8 = false) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * (f32 ? 4 : 2)};
+  cuuint64_t strides[1] = {ld * (u8 ? 1 : f32 ? 4 : 2)};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
-  return fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return fn(m, u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -450,6 +467,7 @@ int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long lo
   p.group_m = 16;
   p.tma_epi = tma_epi ? 1 : 0;
   p.err = gemm_error_word_shared();
+  p.row_scale = nullptr; p.col_scale = nullptr; p.a_fmt = 0; p.b_fmt = 0;
   int grid = 2 * static_cast<int>(tiles < clusters ? tiles : clusters);
   auto launch = [&](auto kernel, int idx) {
     static bool configured[4] = {false, false, false, false};
@@ -466,6 +484,44 @@ int gemm_bf16_2sm(const void* A, long long lda, int a_mn, const void* B, long lo
     case 1: launch(gemm2_bf16_kernel<false, true>, 1); break;
     default: launch(gemm2_bf16_kernel<false, false>, 0); break;
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// fp8 GEMM with dequantising epilogue: D (M, N) bf16 or fp32 = (A (M, K) fp8  x  B (N, K)^T fp8) * row_scale[m] * col_scale[n]
+// (+ bias) (+ addend).  Both operands K-major (rows of K contiguous), K a multiple of 16, leading dimensions multiples of 16.
+int gemm_fp8_2sm(const void* A, long long lda, int a_fmt, const void* B, long long ldb, int b_fmt, void* D, long long ldd, int d_is_f32,
+                 const float* row_scale, const float* col_scale, const void* addend, long long ld_add, const void* bias, int M, int N,
+                 int K, int num_sms, cudaStream_t stream) {
+  using namespace gemm2;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -5;
+  if ((lda % 16) || (ldb % 16) || (K % 16) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -2;
+  if ((ldd % (d_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
+  if (addend && ((ld_add % (d_is_f32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(addend) & 15))) return -3;
+  long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int clusters = num_sms / 2;
+  CUtensorMap ta, tb, td, tadd;
+  bool ok = make_map(&ta, A, K, M, lda, 2 * BK, HALF_M, false, true) && make_map(&tb, B, K, N, ldb, 2 * BK, HALF_N, false, true);
+  const uint32_t bc = d_is_f32 ? 32 : 64;
+  ok = ok && make_map(&td, D, N, M, ldd, bc, 32, d_is_f32 != 0);
+  ok = ok && make_map(&tadd, addend ? addend : D, N, M, addend ? ld_add : ldd, bc, 32, d_is_f32 != 0);
+  if (!ok) return -4;
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.D = D; p.addend = addend; p.bias = bias;
+  p.ldd = ldd; p.ld_add = ld_add; p.d_is_f32 = d_is_f32; p.add_is_f32 = d_is_f32;
+  p.group_m = 16;
+  p.tma_epi = 1;
+  p.err = gemm_error_word_shared();
+  p.row_scale = row_scale; p.col_scale = col_scale; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  int grid = 2 * static_cast<int>(tiles < clusters ? tiles : clusters);
+  static bool configured = false;
+  auto kernel = gemm2_bf16_kernel<false, false, true>;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    configured = true;
+  }
+  kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, td, tadd, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -94,6 +94,11 @@ int moe_combine(const void* base, const void* yp, const float* w, const int* row
 int moe_dispatch_bwd(const void* dxp, const int* row_of, void* out, int t, int d, int K, int accumulate, cudaStream_t s);
 int moe_scale_rows(void* xp, const float* w, const int* row_of, int slots, int d, cudaStream_t s);
 int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int slots, int d, cudaStream_t s);
+// fp8 lane: row-wise e4m3 quantisation and the dequantising CTA-pair GEMM
+int quant_fp8_rowwise(const void* x, long long ldx, void* q, long long ldq, float* scale, long long rows, int K, cudaStream_t s);
+int gemm_fp8_2sm(const void* A, long long lda, int a_fmt, const void* B, long long ldb, int b_fmt, void* D, long long ldd, int d_is_f32,
+                 const float* row_scale, const float* col_scale, const void* addend, long long ld_add, const void* bias, int M, int N,
+                 int K, int num_sms, cudaStream_t stream);
 // sequence-mixing helpers of the linear / latent attention families (seqmix.cu)
 int l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, float eps, cudaStream_t s);
 int l2norm_bwd(const void* dy, const void* x, const float* rstd, void* dx, long long rows, int D, cudaStream_t s);

@@ -130,6 +130,12 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N, bool a_mn_ma
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// fp8 (e4m3 or e5m2) operands, fp32 accumulate, both K-major: kind::f8f6f4; format codes 0 = e4m3, 1 = e5m2
+__host__ __device__ constexpr uint32_t idesc_f8_f32(int M, int N, int a_fmt, int b_fmt) {
+  return (1u << 4) | (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // ------------------------------------------------------------------ tcgen05 mma / commit / ld
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 DFB_PTX void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -197,6 +203,12 @@ DFB_PTX void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* ba
       "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       : : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+DFB_PTX void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      : : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 DFB_PTX void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(

@@ -402,3 +402,20 @@ def moe_topk_sigmoid_noaux(logits, bias, top_k: int, n_group: int = 1, topk_grou
     native().router_sigmoid_noaux(logits.to(torch.bfloat16).contiguous(), bias.float().contiguous(), w, ids, int(n_group), int(topk_group),
                                   float(routed_scaling))
     return w, ids
+
+
+# ------------------------------------------------------------------ fp8 lane (fp8.cu, gemm_tcgen05_2sm.cu FP8)
+@reg("quant_fp8_rowwise")
+def quant_fp8_rowwise(x):
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    native().quant_fp8_rowwise(x, q, scale)
+    return q, scale
+
+
+@reg("linear_fp8")
+def linear_fp8(xq, x_scale, wq, w_scale, out=None, add=None, bias=None, out_dtype=torch.bfloat16):
+    if out is None:
+        out = torch.empty(xq.shape[0], wq.shape[0], dtype=out_dtype, device=xq.device)
+    native().gemm_fp8(xq, wq, out, x_scale, w_scale, add, bias)
+    return out

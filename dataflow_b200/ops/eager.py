@@ -706,3 +706,31 @@ def conv_silu_bwd(dy, x, w, seg_start):
         y = torch.nn.functional.silu(acc)
         gx, gw = torch.autograd.grad(y, [xf, wf], dy.float())
     return gx.to(x.dtype), gw
+
+
+# ------------------------------------------------------------------ fp8 lane (row-wise e4m3 scales)
+FP8_MAX = 448.0
+
+
+@register("quant_fp8_rowwise", "eager")
+def quant_fp8_rowwise(x):
+    """x (rows, K) -> (q (rows, K) float8_e4m3fn, scale (rows,) fp32) with x ~= q * scale[:, None]."""
+    amax = x.float().abs().amax(-1)
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = (x.float() / scale[:, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+@register("linear_fp8", "eager")
+def linear_fp8(xq, x_scale, wq, w_scale, out=None, add=None, bias=None, out_dtype=torch.bfloat16):
+    """y (M, N) = (xq * x_scale[:, None]) @ (wq * w_scale[:, None])^T (+ bias) (+ add); wq stored (N, K)."""
+    y = (xq.float() @ wq.float().t()) * x_scale[:, None] * w_scale[None, :]
+    if bias is not None:
+        y = y + bias.float()
+    if add is not None:
+        y = y + add.float()
+    y = y.to(out_dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y

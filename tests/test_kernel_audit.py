@@ -160,3 +160,42 @@ def test_moe_topk_sigmoid_noaux_matches_oracle(groups):
     assert same.float().mean() > 0.995                    # ties between nearly equal bf16 scores may break differently
     assert torch.allclose(w.cpu().sum(-1), torch.full((1000,), 2.5), atol=1e-4)
     assert torch.allclose(w.cpu()[same].sort(-1).values, w_ref[same].sort(-1).values, atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_quant_fp8_rowwise_matches_oracle():
+    native, oracle = _pair("quant_fp8_rowwise")
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = (torch.randn(300, 1024, device="cuda", generator=g) * torch.logspace(-2, 2, 300, device="cuda")[:, None]).bfloat16()
+    x[17].zero_()
+    q, s = native(x)
+    q_ref, s_ref = oracle(x.cpu())
+    assert torch.allclose(s.cpu(), s_ref, rtol=1e-6)
+    # conversions round to nearest in both lanes; allow the odd tie to land on the neighbouring code
+    same = (q.cpu().view(torch.uint8) == q_ref.view(torch.uint8)).float().mean()
+    assert same > 0.999
+    back = q.float() * s[:, None]
+    assert float((back - x.float()).norm() / x.float().norm()) < 0.04
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(512, 768, 1024), (4096, 4096, 4096), (300, 520, 272)])
+def test_linear_fp8_matches_oracle(shape):
+    """The tcgen05 fp8 GEMM (kind::f8f6f4, fp32 accumulate) with its dequantising epilogue against the same product in fp32."""
+    quant, _ = _pair("quant_fp8_rowwise")
+    native, oracle = _pair("linear_fp8")
+    m, n, k = shape
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    resid = torch.randn(m, n, device="cuda", generator=g).bfloat16()
+    xq, sx = quant(x)
+    wq, sw = quant(w)
+    y = native(xq, sx, wq, sw, add=resid)
+    y_ref = oracle(xq.cpu(), sx.cpu(), wq.cpu(), sw.cpu(), add=resid.cpu())
+    assert float((y.float().cpu() - y_ref.float()).norm() / y_ref.float().norm()) < 5e-3
+    # and the quantised product stays close to the bf16 one
+    full = x.float() @ w.float().t() + resid.float()
+    assert float((y.float() - full).norm() / full.norm()) < 0.06
+    from dataflow_b200.ops import native as _n
+    assert _n().gemm_last_error() == 0
