@@ -59,7 +59,24 @@ def resolve_resume(spec: str | None, root: str | None = None) -> str | None:
 
 def _world(trainer) -> tuple[int, int]:
     z = trainer.zero or {}
-    return int(z.get("rank", 0)), int(z.get("world", 1))
+    if z:
+        return int(z.get("rank", 0)), int(z.get("world", 1))
+    for key in ("tp", "ep"):                       # tensor / expert parallel jobs: the group knows the rank
+        g = (getattr(trainer, "groups", None) or {}).get(key)
+        if g is not None:
+            return int(g.rank), int(g.world)
+    return 0, 1
+
+
+def _private_scheme(trainer) -> str | None:
+    """``tp`` / ``ep``: every rank's persistent objects are its own cut of the model (or its own replica): they are
+    recorded per rank and a resume needs the same scheme and world size."""
+    md = trainer.program.metadata or {}
+    if int(md.get("tp", 1)) > 1:
+        return "tp"
+    if int(md.get("ep", 1)) > 1:
+        return "ep"
+    return None
 
 
 class TrainerSource:
@@ -87,8 +104,11 @@ class TrainerSource:
     def slices(self) -> list[SourceSlice]:
         out = []
         full = (self.t.program.metadata or {}).get("zero_full_bytes") or {}
+        private = _private_scheme(self.t) if self.world > 1 else None
         for oid, size in self.persistent().items():
-            if oid.startswith("Ws_") and self.world > 1:
+            if private:
+                out.append(SourceSlice(oid, 0, size, f"{oid}@{self.rank}", 0))
+            elif oid.startswith("Ws_") and self.world > 1:
                 logical = "W_" + oid[3:]
                 total = int(full.get(logical, size * self.world))
                 lo = min(size * self.rank, total)
@@ -154,7 +174,7 @@ def save_checkpoint(trainer, root: str, step: int, *, seed: int = 0, client_payl
                 for k, v in g["logical"].items():
                     logical[k] = max(logical.get(k, 0), int(v))
             compose_checkpoint(sources, sdir, step=step, seed=seed, logical_objects=logical,
-                               scheme={"world": world, "zero": trainer.zero, **dict(scheme or {})},
+                               scheme={"world": world, "zero": trainer.zero, "parallel": _private_scheme(trainer), **dict(scheme or {})},
                                client_payload=client_payload, summary=summary, launch=launch)
         dist.barrier()
     if keep_last and rank == 0:

@@ -136,3 +136,23 @@ def test_train_cli_runs_tensor_and_expert_parallel_jobs_on_cpu_ranks(parallel, p
     res = json.loads(out.read_text())
     assert len(res["losses"]) == 3 and res["losses"][-1] < res["losses"][0]
     assert res["meta"]["world"] == 2
+
+
+@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny")])
+def test_tensor_and_expert_parallel_jobs_resume_bitwise(parallel, preset, tmp_path):
+    """Every rank's cut of the model is recorded per rank; a resumed run continues the interrupted curve exactly."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", preset, "--steps", "4", "--device", "cpu",
+            "--gpus", "2", "--parallel", parallel, "--dtype-policy", "fp32", "--checkpoint-dir", str(tmp_path / "ck")]
+    a = subprocess.run(base + ["--checkpoint-every", "2", "--out", str(tmp_path / "a.json")], capture_output=True, text=True, timeout=600, cwd=root)
+    assert a.returncode == 0, a.stdout[-1000:] + a.stderr[-2500:]
+    rec = json.loads((tmp_path / "ck" / "step_000002" / "checkpoint_record.json").read_text())
+    assert rec["scheme"]["world"] == 2 and rec["scheme"]["parallel"] == parallel
+    assert any(k.endswith("@1") for k in rec["logical_objects"])
+    b = subprocess.run(base + ["--resume", str(tmp_path / "ck" / "step_000002"), "--out", str(tmp_path / "b.json")], capture_output=True,
+                       text=True, timeout=600, cwd=root)
+    assert b.returncode == 0, b.stdout[-1000:] + b.stderr[-2500:]
+    assert json.loads((tmp_path / "a.json").read_text())["losses"] == json.loads((tmp_path / "b.json").read_text())["losses"]
