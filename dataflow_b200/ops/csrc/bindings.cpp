@@ -331,6 +331,22 @@ static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c
   TORCH_CHECK(rc == 0, "tp_gemm_rs launch failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- attention
+static void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out, Tensor& lse, const Tensor& cu_seqlens,
+                      int64_t max_seqlen, double scale) {
+  CHECK_BF16(q); CHECK_BF16(k); CHECK_BF16(v); CHECK_BF16(out); CHECK_F32(lse); CHECK_I32(cu_seqlens);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && out.dim() == 3, "flash_fwd: (tokens, heads, dim) tensors");
+  const int64_t T = q.size(0), hq = q.size(1), hd = q.size(2), hkv = k.size(1);
+  auto rows_ok = [&](const Tensor& t) { return t.stride(2) == 1 && t.stride(1) == hd; };
+  TORCH_CHECK(rows_ok(q) && rows_ok(k) && rows_ok(v) && rows_ok(out), "flash_fwd: heads must be contiguous inside a token row");
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T && v.size(1) == hkv && out.size(0) == T && out.size(1) == hq && lse.is_contiguous() &&
+              lse.size(0) == hq && lse.size(1) == T, "flash_fwd: shapes");
+  int rc = dfb::flash_fwd_sm100(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
+                                lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(), cu_seqlens.numel() - 1, max_seqlen, T, hq, hkv, hd, scale,
+                                cur_stream());
+  TORCH_CHECK(rc == 0, "flash_fwd: unsupported shape or alignment (head_dim must be 128; code ", rc, ")");
+}
+
 // ---------------------------------------------------------------- fp8 lane
 static bool is_fp8_or_u8(const Tensor& t) {
   return t.scalar_type() == at::kByte || t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kFloat8_e5m2;
@@ -515,6 +531,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rowdot", &moe_rowdot);
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
+  m.def("flash_fwd", &flash_fwd);
   m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("l2norm_fwd", &l2norm_fwd);

@@ -4,6 +4,8 @@ is missing there, resolution raises instead of silently falling back.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import native, native_available
@@ -419,3 +421,22 @@ def linear_fp8(xq, x_scale, wq, w_scale, out=None, add=None, bias=None, out_dtyp
         out = torch.empty(xq.shape[0], wq.shape[0], dtype=out_dtype, device=xq.device)
     native().gemm_fp8(xq, wq, out, x_scale, w_scale, add, bias)
     return out
+
+
+# ------------------------------------------------------------------ attention forward on tcgen05 (attention.cu)
+def _flash_fwd_native(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
+    """Causal varlen attention, head_dim 128; q (t, hq, 128), k / v (t, hkv, 128) — views into a packed qkv are taken as
+    they are.  Returns (out (t, hq, 128), lse (hq, t))."""
+    LAUNCHES.total += 1
+    scale = scale if scale is not None else q.shape[-1] ** -0.5
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty(q.shape[1], q.shape[0], dtype=torch.float32, device=q.device)
+    native().flash_fwd(q, k, v, out, lse, cu_seqlens.to(torch.int32), int(max_seqlen), float(scale))
+    return out, lse
+
+
+# The vendor attention (library lane) is the default on this device: it is faster than this kernel.  ``DFB_ATTN_FWD=sm100``
+# (or a registry override ``{"flash_fwd": "sm100"}``) selects the hand-written forward.
+register("flash_fwd", "sm100", _flash_fwd_native, priority=P if os.environ.get("DFB_ATTN_FWD") == "sm100" else 3,
+         requires=lambda caps: _native(caps) and True, native=True)
