@@ -5,10 +5,12 @@
 //     S(j)  = Q K_j^T            tcgen05.mma, both operands K-major from shared memory, accumulator in TMEM (two buffers)
 //     softmax reads S(j) from TMEM (tcgen05.ld, its own lane = its own row): running max / sum in registers, P(j) as bf16
 //            into shared memory in the 128-byte swizzled K-major layout the next MMA wants
-//     PV(j) = P(j) V_j           tcgen05.mma, V MN-major straight from its (keys, d) rows, fresh accumulator in TMEM
-//     O     = O * alpha + PV(j)  in registers (128 fp32 per thread), alpha = exp2(m_old - m_new)
-// so S(j+1) and PV(j-1) run on the tensor pipe while the softmax of tile j runs on the ALUs.  K and V tiles are
-// double-buffered TMA loads.  Every wait is a bounded mbarrier wait: on a timeout the CTA raises the error word and leaves.
+//     O    += P(j) V_j           tcgen05.mma, V MN-major straight from its (keys, d) rows, O accumulates in TMEM
+// The exponent base m of a row is only raised when the row maximum outgrows it by more than 2^8 (then O is rescaled in
+// tensor memory, tcgen05.ld / st, after the previous P V has finished); otherwise probabilities simply use the older,
+// slightly smaller base — exact in the final quotient O / l, and the common tile costs one pass over S and no read of O.
+// S(j+1) and P V(j-1) run on the tensor pipe while the softmax of tile j runs on the ALUs.  K, V and P tiles are
+// double-buffered.  Every wait is a bounded mbarrier wait: on a timeout the CTA raises the error word and leaves.
 // Output: out (tokens, heads, 128) bf16 and lse (heads, tokens) fp32 = log sum exp(scale * s), the statistics the backward
 // (library lane) consumes.
 // Reference role: src/dataflow_training/kernels/flash.py:59-172 (aten varlen flash attention forward).
@@ -26,14 +28,15 @@ namespace fa {
 constexpr int BM = 128, BN = 128, D = 128, UK = 16;
 constexpr int CH = 128 * 128;                    // one 128-row x 64-element (128-byte) swizzled chunk: 16 KiB
 constexpr int TILE = 2 * CH;                     // a 128 x 128 bf16 tile
-constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_P = 5 * TILE, OFF_BAR = 6 * TILE;
-constexpr int SMEM_BYTES = 6 * TILE + 256 + 1024;
+constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_P = 5 * TILE, OFF_BAR = 7 * TILE;
+constexpr int SMEM_BYTES = 7 * TILE + 256 + 1024;
+constexpr float kRescaleGap = 8.f;               // log2 units the row maximum may run ahead of the exponent base
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr float kNegBig = -1e30f;
 
 struct Bars {
-  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_full, pv_empty;
+  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -79,9 +82,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ptx::mbar_init(&bar->k_empty[b], 1); ptx::mbar_init(&bar->v_empty[b], 1);
       ptx::mbar_init(&bar->s_full[b], 1); ptx::mbar_init(&bar->s_empty[b], 4);
     }
-    ptx::mbar_init(&bar->p_full, 4);
-    ptx::mbar_init(&bar->pv_full, 1);
-    ptx::mbar_init(&bar->pv_empty, 4);
+    for (int b = 0; b < 2; ++b) { ptx::mbar_init(&bar->p_full[b], 4); ptx::mbar_init(&bar->pv_done[b], 1); }
     bar->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -151,22 +152,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (j >= 1) {
           const int jj = j - 1, b = jj & 1;
           const uint32_t ph = (jj >> 1) & 1;
-          if (!ptx::mbar_wait(&bar->p_full, jj & 1, abort_flag) || !ptx::mbar_wait(&bar->v_full[b], ph, abort_flag) ||
-              !ptx::mbar_wait(&bar->pv_empty, (jj & 1) ^ 1, abort_flag)) {
+          if (!ptx::mbar_wait(&bar->p_full[b], ph, abort_flag) || !ptx::mbar_wait(&bar->v_full[b], ph, abort_flag)) {
             bar->abort = 1; atomicExch(p.err, 65); ok = false; break;
           }
           ptx::tc_fence_after();
           const uint32_t v_addr = ptx::smem_u32(smem + OFF_V + b * TILE);
-          const uint32_t tmem_pv = tmem_base + 2 * BN;
+          const uint32_t tmem_o = tmem_base + 2 * BN;
 #pragma unroll
           for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t adesc = ptx::desc_kmajor_sw128(p_addr + kb * CH);
+            const uint64_t adesc = ptx::desc_kmajor_sw128(p_addr + b * TILE + kb * CH);
             const uint64_t bdesc = ptx::desc_mnmajor_sw128(v_addr + kb * CH, CH / 2);
 #pragma unroll
-            for (int k = 0; k < 64 / UK; ++k) ptx::umma_bf16(tmem_pv, adesc + k * k_step, bdesc + k * mn_step, idesc_pv, (kb | k) != 0);
+            for (int k = 0; k < 64 / UK; ++k)
+              ptx::umma_bf16(tmem_o, adesc + k * k_step, bdesc + k * mn_step, idesc_pv, (jj | kb | k) != 0);
           }
           ptx::umma_commit(&bar->v_empty[b]);
-          ptx::umma_commit(&bar->pv_full);
+          ptx::umma_commit(&bar->pv_done[b]);
         }
       }
     }
@@ -176,11 +177,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int r = q4 * 32 + lane;                 // row inside the tile == TMEM lane
     const int qi = qt * BM + r;                   // row inside the sequence
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-    uint8_t* p_row = smem + OFF_P + r * 128;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m = kNegBig, l = 0.f, alpha_prev = 1.f;
+    const uint32_t t_o = tmem_base + 2 * BN + lane_base;
+    float m = kNegBig, l = 0.f;                   // exponent base (log2 units) and the row sum relative to it
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int b = j & 1;
@@ -188,103 +186,99 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->s_full[b], (j >> 1) & 1, abort_flag))) { bar->abort = 1; atomicExch(p.err, 66); ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t t_s = tmem_base + b * BN + lane_base;
-      const bool masked = j == n_kv - 1;          // the diagonal tile (it also holds the end of the sequence)
-      const int key_base = j * BN;
-      // pass 1: row maximum
+      float t[BN];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(t_s + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bar->s_empty[b]);          // S(j) is in registers: its buffer may take S(j + 2)
       float mx = kNegBig;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(t_s + c * 32, v);
-        ptx::tmem_ld_wait();
+      if (j == n_kv - 1) {                        // the diagonal tile (it also holds the end of the sequence)
+        const int key_base = j * BN;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(v[i]) * p.sl2;
-          if (masked) {
-            const int kj = key_base + c * 32 + i;
-            if (kj > qi || kj >= seg_len) t = kNegBig;
+        for (int i = 0; i < BN; ++i) {
+          const int kj = key_base + i;
+          t[i] = (kj > qi || kj >= seg_len) ? kNegBig : t[i] * p.sl2;
+          mx = fmaxf(mx, t[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) { t[i] *= p.sl2; mx = fmaxf(mx, t[i]); }
+      }
+      // raise the exponent base only when the maximum ran away from it (always on the first tile); the decision is taken
+      // per warp because rescaling O touches tensor memory with warp-wide instructions
+      const bool raise = j == 0 || mx > m + kRescaleGap;
+      if (__any_sync(0xffffffffu, raise)) {
+        const float m_new = fmaxf(m, mx);
+        if (j > 0) {
+          // O must be complete up to tile j - 1 and no P V may be in flight while it is rescaled
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag))) {
+            bar->abort = 1; atomicExch(p.err, 67); ok = false; break;
           }
-          mx = fmaxf(mx, t);
+          ptx::tc_fence_after();
+          const float alpha = ex2(m - m_new);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(t_o + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            ptx::tmem_st_32x32(t_o + c * 32, v);
+          }
+          ptx::tmem_st_wait();
+          l *= alpha;
+        }
+        m = m_new;
+      }
+      // P(j) goes to the buffer P V(j - 2) read: that product must be finished
+      if (j >= 2) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[b], ((j - 2) >> 1) & 1, abort_flag))) {
+          bar->abort = 1; atomicExch(p.err, 68); ok = false; break;
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float alpha = ex2(m - m_new);
-      // the previous tile's P V: its result is needed before O changes scale, and P's buffer is free once it is done
-      if (j >= 1) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_full, (j - 1) & 1, abort_flag))) { bar->abort = 1; atomicExch(p.err, 67); ok = false; break; }
-        ptx::tc_fence_after();
-        const uint32_t t_pv = tmem_base + 2 * BN + lane_base;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32(t_pv + c * 32, v);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i]));
-        }
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bar->pv_empty);
-      }
-      // pass 2: probabilities -> shared memory (bf16, swizzled K-major rows), row sum
+      uint8_t* p_row = smem + OFF_P + b * TILE + r * 128;
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(t_s + c * 32, v);
-        ptx::tmem_ld_wait();
-        float pr[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(v[i]) * p.sl2;
-          if (masked) {
-            const int kj = key_base + c * 32 + i;
-            if (kj > qi || kj >= seg_len) t = kNegBig;
-          }
-          pr[i] = ex2(t - m_new);
-          rowsum += pr[i];
-        }
-        uint8_t* chunk = p_row + (c >> 1) * CH;
+      for (int g = 0; g < BN / 8; ++g) {
+        float pr[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const bf16x8 pk = pack8(pr + g * 8);
-          const int vec = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(chunk + ((vec ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4*>(&pk);
-        }
+        for (int i = 0; i < 8; ++i) { pr[i] = ex2(t[g * 8 + i] - m); rowsum += pr[i]; }
+        const bf16x8 pk = pack8(pr);
+        // key g*8 .. g*8+7: chunk g / 8 (64 keys each), 16-byte vector g % 8 inside the 128-byte row, XOR-swizzled by the row
+        *reinterpret_cast<uint4*>(p_row + (g >> 3) * CH + (((g & 7) ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4*>(&pk);
       }
-      l = fmaf(l, alpha, rowsum);
-      m = m_new;
-      alpha_prev = alpha;
+      l += rowsum;
       ptx::fence_proxy_async();           // the MMA reads P through the async proxy
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        ptx::mbar_arrive(&bar->p_full);
-        ptx::mbar_arrive(&bar->s_empty[b]);
-      }
+      if (lane == 0) ptx::mbar_arrive(&bar->p_full[b]);
     }
     if (ok) {
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_full, (n_kv - 1) & 1, abort_flag))) { bar->abort = 1; atomicExch(p.err, 68); ok = false; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag))) {
+        bar->abort = 1; atomicExch(p.err, 69); ok = false;
+      }
     }
     if (ok) {
       ptx::tc_fence_after();
-      const uint32_t t_pv = tmem_base + 2 * BN + lane_base;
       const float inv = 1.f / l;
-#pragma unroll
+      const long long tok = seg_start + qi;
+      bf16* dst = p.out + tok * p.out_row_stride + static_cast<long long>(h) * D;
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        ptx::tmem_ld_32x32(t_pv + c * 32, v);
+        ptx::tmem_ld_32x32(t_o + c * 32, v);
         ptx::tmem_ld_wait();
+        if (qi < seg_len) {
+          float o[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(v[i])) * inv;
-      }
-      if (qi < seg_len) {
-        const long long tok = seg_start + qi;
-        bf16* dst = p.out + tok * p.out_row_stride + static_cast<long long>(h) * D;
+          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * inv;
 #pragma unroll
-        for (int g = 0; g < D / 8; ++g) st8(dst + g * 8, pack8(o + g * 8));
-        p.lse[static_cast<long long>(h) * p.T + tok] = (m + log2f(l)) * 0.6931471805599453f;
+          for (int g = 0; g < 4; ++g) st8(dst + c * 32 + g * 8, pack8(o + g * 8));
+        }
       }
+      if (qi < seg_len) p.lse[static_cast<long long>(h) * p.T + tok] = (m + log2f(l)) * 0.6931471805599453f;
     }
   }
 
