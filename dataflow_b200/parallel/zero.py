@@ -63,9 +63,13 @@ def zero_lower_kwargs(mode: str, rank: int, world: int, group: str = "dp") -> di
     ``fsdp``: stage 3 with re-gathering — gather in front of every use, reduce-scatter every backward into an
     fp32 slice, local split-master AdamW (6 bytes of state per parameter, divided by the world size).
     ``zero1`` / ``zero1rs``: whole weights everywhere, sharded optimizer state."""
+    if mode in ("co", "dp"):
+        # plain data parallelism (ZeRO-0): every rank holds everything; gradients are summed in front of the optimizer
+        # (``replicate_gradients``).  Nothing changes in the lowering.
+        return {}
     stage = {"zero3": 3, "fsdp": 3, "zero1": 1, "zero1rs": 1}.get(mode)
     if stage is None:
-        raise KeyError(f"unknown ZeRO mode {mode!r} (fsdp | zero3 | zero1)")
+        raise KeyError(f"unknown data-parallel mode {mode!r} (fsdp | zero3 | zero1 | co)")
     # fp32 master + two fp32 moments per bf16 parameter: 12 bytes per 2 parameter bytes, 256-byte aligned planes
     z = {"stage": stage, "rank": rank, "world": world, "group": group, "opt_bytes_per_param_byte": 6.0}
     if mode == "fsdp":
@@ -283,6 +287,13 @@ class DpGroup:
             if ln:
                 full[lo:lo + ln] = p[:ln]
 
+    def all_reduce(self, t):
+        """Sum over the group (plain data parallelism: whole gradient objects in front of the optimizer)."""
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.all_reduce(t)
+        return t
+
     def close(self) -> None:
         if self.lane == "p2p" and self.backend is not None:
             for r, (s, c) in enumerate(zip(self.slabs, self.ctrls)):
@@ -291,6 +302,35 @@ class DpGroup:
                     self.backend.ipc_close(c)
             self.backend.device_free(self.ctrl)
             self.slabs, self.ctrls = [], []
+
+
+def replicate_gradients(trainer, group_key: str = "dp") -> None:
+    """ZeRO-0 ("co"): wrap every optimizer executable of ``trainer`` so that it first sums the layer's gradient object over
+    the group; every rank then applies the identical update.  Replicas stay bitwise equal — which also makes this lane a
+    corruption tripwire.  Ranks may run different numbers of rounds (weighted data parallelism): only the optimizer
+    tasks, which every rank has in the same order, communicate."""
+    from ..models.tp_mlp.blocks import ReplicatedGradSum
+    table = trainer.resolver.table
+    lay = trainer.layouts
+    for key in list(table):
+        if not key.startswith("optimizer"):
+            continue
+        inner = table[key]
+        target = {"optimizer_embed": lay.embed_dw, "optimizer_head": lay.head_dw}.get(key)
+        table[key] = _LayerAwareGradSum(inner, target, lay, group_key) if target is None else ReplicatedGradSum(inner, target, None, group_key)
+
+
+class _LayerAwareGradSum:
+    """``ReplicatedGradSum`` for block optimizers of families whose layers have different layouts."""
+
+    def __init__(self, inner, layout, lay, group_key):
+        self.inner, self.lay, self.group_key = inner, lay, group_key
+
+    def launch(self, ctx):
+        from ..models.tp_mlp.blocks import ReplicatedGradSum
+        layer = ctx.task.block_params.get("layer", 0)
+        gl = self.lay.of_layer(layer)[1] if hasattr(self.lay, "of_layer") else self.lay.block_dw
+        ReplicatedGradSum(self.inner, gl, None, self.group_key).launch(ctx)
 
 
 def make_dp_group(rank: int, world: int, device: int | None, lane: str | None = None) -> DpGroup:

@@ -35,7 +35,8 @@ class RunSpec:
     budget_gib: float | None = None
     device: int | None = 0                  # None = CPU backend
     world: int = 1
-    parallel: str = "fsdp"                  # fsdp | zero3 | zero1 | tp | ep (world > 1)
+    parallel: str = "fsdp"                  # fsdp | zero3 | zero1 | co | tp | ep (world > 1)
+    rounds: list[int] | None = None         # weighted data parallelism (with ``co``): rounds each rank runs per step
     seed: int = 0
     profile: bool = False
     recompute: bool = True

@@ -57,14 +57,15 @@ def _dist():
     return None
 
 
-def put_rank_rounds(trainer: Trainer, packed, rank: int, rounds: int, row_shard: tuple[int, int] | None = None) -> tuple[int, dict[int, list[int]], int]:
+def put_rank_rounds(trainer: Trainer, packed, rank: int, rounds: int, row_shard: tuple[int, int] | None = None,
+                    first_round: int | None = None) -> tuple[int, dict[int, list[int]], int]:
     """Copy this rank's rounds of a packed step into the store.  Returns (bytes written, seq_lens, local valid rows).
     ``row_shard = (index, count)``: sequence parallelism — every rank takes the SAME rounds and keeps its slice of rows
     (the sequence bounds stay those of the whole round: attention sees all rows)."""
     import torch
     nbytes, seq_lens, valid = 0, {}, 0
     for r in range(rounds):
-        rd = packed.rounds[(0 if row_shard else rank * rounds) + r]
+        rd = packed.rounds[(0 if row_shard else (rank * rounds if first_round is None else first_round)) + r]
         tk, tg = torch.from_numpy(rd.tokens), torch.from_numpy(rd.targets)
         if row_shard:
             n = len(rd.tokens) // row_shard[1]
@@ -82,7 +83,7 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                start_step: int = 0, losses: list[float] | None = None, checkpoint_every: int = 0,
                checkpoint_dir: str | None = None, keep_last: int | None = None, seed: int = 0,
                launch: Mapping[str, Any] | None = None, log: Callable[[str], None] | None = print,
-               on_step: Callable[[int, float, Any], None] | None = None) -> RunResult:
+               on_step: Callable[[int, float, Any], None] | None = None, rank_rounds: list[int] | None = None) -> RunResult:
     """Run optimizer steps ``start_step + 1 .. steps``.  ``factory(cursor)`` builds the data stepper; its packed
     steps must hold ``trainer.rounds x world`` rounds of ``trainer.T`` tokens."""
     from .checkpointing import save_checkpoint
@@ -93,9 +94,12 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
     tp = int((trainer.program.metadata or {}).get("tp", 1))
     row_shard = (rank, tp) if tp > 1 else None
     data_world = 1 if row_shard else world
+    # weighted data parallelism: rank r runs rank_rounds[r] rounds of every step
+    job_rounds = sum(rank_rounds) if rank_rounds else trainer.rounds * data_world
+    first_round = sum(rank_rounds[:rank]) if rank_rounds else None
     stepper = factory(dict(cursor) if cursor else None)
     ahead = PackAhead(stepper)
-    res = RunResult(losses=list(losses or []), tokens_per_step=trainer.T * trainer.rounds * world,
+    res = RunResult(losses=list(losses or []), tokens_per_step=trainer.T * (job_rounds if rank_rounds else trainer.rounds * world),
                     meta={"family": trainer.fam.name, "preset": getattr(trainer.cfg, "name", ""), "world": world,
                           "plan_makespan_us": trainer.planned.makespan_us, "policy": trainer.planned.policy,
                           "peak_fast_bytes": trainer.planned.peak_fast_bytes,
@@ -109,10 +113,10 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                 if log and rank == 0:
                     log(f"data source exhausted after {s} steps")
                 break
-            if len(packed.rounds) != trainer.rounds * data_world:
-                raise ValueError(f"packed step has {len(packed.rounds)} rounds, the job consumes {trainer.rounds * data_world}")
+            if len(packed.rounds) != job_rounds:
+                raise ValueError(f"packed step has {len(packed.rounds)} rounds, the job consumes {job_rounds}")
             t0 = time.perf_counter()
-            _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds, row_shard)
+            _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds, row_shard, first_round)
             total_valid = packed.valid_rows          # every rank packed the whole job's step: no exchange needed
             loss = trainer.step(None, seq_lens=seq_lens, valid_rows=max(total_valid, 1))
             if dist:

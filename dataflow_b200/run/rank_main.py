@@ -44,12 +44,19 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
             dist.init_process_group("nccl", device_id=torch.device("cuda", device))
         if spec.parallel not in ("tp", "ep"):
             from ..parallel.zero import make_dp_group, zero_lower_kwargs
-            groups = {"dp": make_dp_group(rank, world, device)}
+            # plain data parallelism needs no peer-mapped slab: its one collective per optimizer task is a library all-reduce
+            groups = {"dp": make_dp_group(rank, world, device, "collective" if spec.parallel in ("co", "dp") else None)}
             lower_kwargs = zero_lower_kwargs(spec.parallel, rank, world)
+            if spec.parallel in ("co", "dp") and spec.resident_params and device is not None:
+                lower_kwargs = {"resident_params": True}
     elif spec.resident_params:
         lower_kwargs = {"resident_params": True}
     family, cfg = build_cfg(spec)
     data_world = world
+    if spec.rounds:
+        if world <= 1 or spec.parallel not in ("co", "dp") or len(spec.rounds) != world:
+            raise ValueError("--rounds a,b,... gives every rank its own number of rounds: it needs --parallel co and one entry per rank")
+        cfg = dataclasses.replace(cfg, grad_accum_rounds=int(spec.rounds[rank]))
     if world > 1 and spec.parallel == "tp":
         # tensor + sequence parallelism: the dense llama block split over the ranks (family tp_mlp)
         from ..parallel.tp import TpGroup
@@ -79,7 +86,11 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     say(f"plan: {tr.planned.policy}, predicted {tr.planned.makespan_us / 1e3:.1f} ms/step, peak fast "
         f"{tr.planned.peak_fast_bytes / 2 ** 30:.2f} GiB, planned in {tr.plan_s:.1f} s")
     # the job-wide pipeline: every rank packs all rounds of the step and keeps its own
-    wide = dataclasses.replace(cfg, grad_accum_rounds=cfg.grad_accum_rounds * data_world)
+    if world > 1 and spec.parallel in ("co", "dp"):
+        from ..parallel.zero import replicate_gradients
+        replicate_gradients(tr)
+    total_rounds = sum(spec.rounds) if spec.rounds else cfg.grad_accum_rounds * data_world
+    wide = dataclasses.replace(cfg, grad_accum_rounds=total_rounds)
     factory = pipeline_from_args(wide, spec.data, policy=spec.packing_policy, allow_round_split=spec.allow_round_split,
                                  capture=spec.capture if rank == 0 else None)
     start, cursor, losses = 0, None, []
@@ -93,7 +104,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
                                               "parallel": spec.parallel if world > 1 else "solo", **spec.overrides},
               "data": factory.describe(), "env": _env_facts()}
     try:
-        res = train_loop(tr, factory, spec.steps, cursor=cursor, start_step=start, losses=losses,
+        res = train_loop(tr, factory, spec.steps, cursor=cursor, start_step=start, losses=losses, rank_rounds=spec.rounds,
                          checkpoint_every=spec.checkpoint_every, checkpoint_dir=spec.checkpoint_dir,
                          keep_last=spec.checkpoint_keep_last, seed=spec.seed, launch=launch, log=say)
     finally:

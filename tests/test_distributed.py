@@ -156,3 +156,27 @@ def test_tensor_and_expert_parallel_jobs_resume_bitwise(parallel, preset, tmp_pa
                        text=True, timeout=600, cwd=root)
     assert b.returncode == 0, b.stdout[-1000:] + b.stderr[-2500:]
     assert json.loads((tmp_path / "a.json").read_text())["losses"] == json.loads((tmp_path / "b.json").read_text())["losses"]
+
+
+def test_plain_and_weighted_data_parallel_jobs_match_one_process(tmp_path):
+    """`--parallel co`: replicas with all-reduced gradients.  Two ranks running 2 + 2 rounds, or 3 + 1 rounds (weighted), walk
+    the same curve as one process running the 4 rounds of the same packed steps."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "3", "--device", "cpu",
+            "--dtype-policy", "fp32"]
+
+    def run(extra, name):
+        out = tmp_path / f"{name}.json"
+        r = subprocess.run(base + extra + ["--out", str(out)], capture_output=True, text=True, timeout=600, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2500:]
+        return json.loads(out.read_text())["losses"]
+
+    solo = run(["--ga-rounds", "4"], "solo")
+    even = run(["--gpus", "2", "--parallel", "co", "--ga-rounds", "2"], "even")
+    weighted = run(["--gpus", "2", "--parallel", "co", "--rounds", "3,1"], "weighted")
+    # the order in which round gradients are summed differs (per rank, then over ranks): noise of that size only
+    assert even == pytest.approx(solo, rel=2e-4)
+    assert weighted == pytest.approx(solo, rel=2e-4)

@@ -39,9 +39,11 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--fast-budget", type=float, default=None, help="device memory budget in GiB")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--device", default="0", help="CUDA ordinal, or 'cpu'")
-    ap.add_argument("--opt-shard", "--parallel", dest="opt_shard", default="fsdp", choices=["fsdp", "zero3", "zero1", "zero1rs", "tp", "ep"],
+    ap.add_argument("--opt-shard", "--parallel", dest="opt_shard", default="fsdp", choices=["fsdp", "zero3", "zero1", "zero1rs", "co", "tp", "ep"],
                     help="how --gpus N ranks split the job: fsdp / zero3 / zero1 shard parameters and optimizer state over data-parallel "
-                         "ranks; tp = tensor + sequence parallel llama blocks; ep = experts split over the ranks (MoE presets)")
+                         "ranks; co = plain data parallelism (replicas, gradients all-reduced); tp = tensor + sequence parallel llama "
+                         "blocks; ep = experts split over the ranks (MoE presets)")
+    ap.add_argument("--rounds", default=None, help="weighted data parallelism with --parallel co: rounds per rank, e.g. 6,2")
     ap.add_argument("--kernels", default=None, help="kernel lane: sm100 | baseline | eager")
     ap.add_argument("--profile", action="store_true", help="plan from measured task costs")
     ap.add_argument("--no-recompute", action="store_true")
@@ -73,7 +75,7 @@ def spec_from_args(a, argv):
         recipe["optimizer"] = a.opt
     return RunSpec(preset=a.preset, steps=a.steps, overrides=ov, recipe=recipe, data=a.data, packing_policy=a.packing_policy,
                    allow_round_split=a.allow_round_split, capture=a.capture, budget_gib=a.fast_budget,
-                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel=a.opt_shard, seed=a.seed,
+                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel=a.opt_shard, rounds=[int(x) for x in a.rounds.split(",")] if a.rounds else None, seed=a.seed,
                    profile=a.profile, recompute=not a.no_recompute, kernels=a.kernels,
                    resident_params=not a.no_resident_params, checkpoint_every=a.checkpoint_every,
                    checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, resume=a.resume, out=a.out,
