@@ -11,6 +11,7 @@ the step loss read back from the ``loss_*`` objects.  Role parity: reference
 from __future__ import annotations
 
 import json
+import os
 import time
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -121,7 +122,7 @@ class Trainer:
                  kernels=None, kernel_set: str | None = None, recompute: bool = True, profile: bool = False,
                  leeway_bytes: int | None = None, planned: PlannedProgram | None = None,
                  lower_kwargs: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
-                 init: bool = True, verbose: bool = False):
+                 init: bool = True, verbose: bool = False, static_placement: bool | None = None):
         import torch
         from ..ops import resolve_kernels
         self.fam = resolve_family(family)
@@ -196,6 +197,17 @@ class Trainer:
             self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0)
         self.step_index = 0
         self.last_result = None
+        # static placement: offsets of every device allocation of a step, computed from a dry run (runtime/placement.py)
+        self.placement = None
+        if static_placement is None:
+            static_placement = os.environ.get("DATAFLOW_STATIC_PLACEMENT") == "1"
+        if static_placement and device is not None:
+            from ..runtime.placement import PlacementError, plan_placement
+            try:
+                self.placement = plan_placement(self.program, int(self.session.native.fast_slab()[1]))
+            except PlacementError as e:
+                if verbose:
+                    print(f"static placement not used: {e}")
         self.zero = (self.program.metadata or {}).get("zero")
         # weights that end a step on the device stay there for the next one (Session.resident)
         self.keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
@@ -256,7 +268,7 @@ class Trainer:
         res = self.engine.execute(self.program, self.resolver, self.store.buffers(), run_args=args,
                                   groups=self.groups, manage_pools=self.device is None,
                                   keep_resident=self.keep_resident,
-                                  dispatch_ahead=self.dispatch_ahead)
+                                  dispatch_ahead=self.dispatch_ahead, placement=self.placement)
         self.last_result = res
         res.raise_if_failed()
         for g in self.groups.values():

@@ -33,6 +33,9 @@ static py::dict result_to_py(const RunResult& r) {
   py::list ev;
   for (auto& e : r.events) ev.append(py::make_tuple(e.kind, e.what, e.fast_bytes));
   d["events"] = ev;
+  py::list al;
+  for (auto& a : r.allocs) al.append(py::make_tuple(a.obj, a.size, a.ptr, a.kind));
+  d["allocs"] = al;
   py::dict s;
   s["makespan_us"] = r.stats.makespan_us;
   s["peak_fast_bytes"] = r.stats.peak_fast;
@@ -227,7 +230,8 @@ PYBIND11_MODULE(_runtime, m) {
       .def("execute",
            [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
               bool strict_final, bool poison, bool record_events, double headroom,
-              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident, int dispatch_ahead) {
+              std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident, int dispatch_ahead,
+              bool record_allocs, std::vector<std::vector<int64_t>> placement) {
              std::unordered_map<std::string, InitialBuffer> init;
              for (auto kv : initial) {
                auto t = kv.second.cast<py::tuple>();
@@ -242,6 +246,8 @@ PYBIND11_MODULE(_runtime, m) {
              opt.manage_pools = manage_pools;
              opt.keep_resident = keep_resident;
              opt.dispatch_ahead = dispatch_ahead;
+             opt.record_allocs = record_allocs;
+             if (!placement.empty()) opt.placement = &placement;
              LaunchFn fn;
              if (!launch.is_none()) {
                fn = [launch](const LaunchArgs& a) {
@@ -268,5 +274,6 @@ PYBIND11_MODULE(_runtime, m) {
            py::arg("strict_final_locations") = true, py::arg("poison_on_free") = false,
            py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
            py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true,
-           py::arg("keep_resident") = false, py::arg("dispatch_ahead") = 0);
+           py::arg("keep_resident") = false, py::arg("dispatch_ahead") = 0, py::arg("record_allocs") = false,
+           py::arg("placement") = std::vector<std::vector<int64_t>>());
 }

@@ -59,6 +59,15 @@ BufferRef BufferPool::get(size_t bytes) {
   return b;
 }
 
+BufferRef BufferPool::get_at(size_t bytes, size_t offset) {
+  BufferRef b;
+  if (!slab_ || offset % SlabAllocator::kAlign || !slab_->allocate_at(offset, bytes)) return b;
+  b.size = bytes;
+  b.ptr = static_cast<char*>(base_) + offset;
+  b.slab_off = offset;
+  return b;
+}
+
 void BufferPool::put(BufferRef& b) {
   if (!b.ptr || b.external) { b = BufferRef(); return; }
   if (b.slab_off != SlabAllocator::kNone) {
@@ -133,9 +142,27 @@ void Engine::free_slot(Slot& s, Location loc) {
   if (loc == FAST && opt_->poison_on_free && s.buf.ptr && !s.buf.external) {
     be_->memset_async(s.buf.ptr, 0xFF, s.buf.size, sess_->compute_stream);
   }
+  if (loc == FAST && opt_->record_allocs && s.buf.ptr) out_->allocs.push_back({-1, 0, reinterpret_cast<uint64_t>(s.buf.ptr), 0});
   (loc == FAST ? sess_->fast_pool : sess_->backing_pool).put(s.buf);
   s.state = SlotState::ABSENT;
   s.version = -1;
+}
+
+// A fast buffer for object ``obj``: at its planned offset when a static placement names one and those bytes are free
+// (otherwise the placement escape valve: the dynamic allocator), logged when the run records allocations.
+BufferRef Engine::get_fast(int obj, int64_t size) {
+  BufferRef b;
+  int k = alloc_count_[obj]++;
+  if (opt_->placement && obj < static_cast<int>(opt_->placement->size())) {
+    const auto& offs = (*opt_->placement)[obj];
+    if (k < static_cast<int>(offs.size()) && offs[k] >= 0) {
+      b = sess_->fast_pool.get_at(static_cast<size_t>(size), static_cast<size_t>(offs[k]));
+      if (!b.ptr) out_->stats.placement_escapes++;
+    }
+  }
+  if (!b.ptr) b = sess_->fast_pool.get(static_cast<size_t>(size));
+  if (opt_->record_allocs) out_->allocs.push_back({obj, size, reinterpret_cast<uint64_t>(b.ptr), 1});
+  return b;
 }
 
 double Engine::xfer_us(const Xfer& x) const {
@@ -167,7 +194,7 @@ bool Engine::try_start(int dir) {
   queue_[dir].pop_front();
   if (!exists) {
     charge(dst, x.size);
-    d.buf = (dst == FAST ? sess_->fast_pool : sess_->backing_pool).get(x.size);
+    d.buf = dst == FAST ? get_fast(x.obj, x.size) : sess_->backing_pool.get(x.size);
   }
   d.state = SlotState::INBOUND;
   Slot& s = dir == 0 ? o.backing : o.fast;
@@ -308,12 +335,14 @@ void Engine::load_initial(const std::unordered_map<std::string, InitialBuffer>& 
       auto held = sess_->resident.find(oi.id);
       if (held != sess_->resident.end() && static_cast<int64_t>(held->second.size) == oi.size) {
         o.fast.buf = held->second;               // bytes already on the device from the previous run
+        alloc_count_[i]++;
+        if (opt_->record_allocs) out_->allocs.push_back({static_cast<int>(i), oi.size, reinterpret_cast<uint64_t>(o.fast.buf.ptr), 2});
         sess_->resident.erase(held);
         o.fast.state = SlotState::LIVE;
         o.fast.version = 0;
         continue;
       }
-      o.fast.buf = sess_->fast_pool.get(oi.size);
+      o.fast.buf = get_fast(static_cast<int>(i), oi.size);
       o.fast.state = SlotState::LIVE;
       o.fast.version = 0;
       const void* src = nullptr;
@@ -341,6 +370,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
                           const ExecOptions& opt, const RangeFn& range, RunResult& out) {
   p_ = &p; opt_ = &opt; out_ = &out;
   objs_.assign(p.objs.size(), ObjState());
+  alloc_count_.assign(p.objs.size(), 0);
   used_[0] = used_[1] = 0; workspace_ = 0;
   queue_[0].clear(); queue_[1].clear(); flight_[0].reset(); flight_[1].reset();
   deferred_.clear(); xfer_seq_.clear(); pending_intervals_.clear(); events_to_release_.clear();
@@ -413,7 +443,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
         s.buf.size = it->second.size;
         s.buf.external = true;
       } else {
-        s.buf = (loc == FAST ? sess_->fast_pool : sess_->backing_pool).get(p.objs[o.obj].size);
+        s.buf = loc == FAST ? get_fast(o.obj, p.objs[o.obj].size) : sess_->backing_pool.get(p.objs[o.obj].size);
       }
       s.state = SlotState::RESERVED;
       args.output_ptrs.push_back(reinterpret_cast<uint64_t>(s.buf.ptr));

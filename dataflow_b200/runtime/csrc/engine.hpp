@@ -68,6 +68,8 @@ class BufferPool {
   BufferPool(Backend* be, Location loc) : be_(be), loc_(loc) {}
   ~BufferPool();
   void ensure_slab(size_t capacity);
+  // static placement: the buffer at a planned slab offset; an empty ref (ptr == nullptr) when those bytes are taken
+  BufferRef get_at(size_t bytes, size_t offset);
   BufferRef get(size_t bytes);
   void put(BufferRef& b);
   void trim();
@@ -130,6 +132,8 @@ struct RunStats {
   double wait_us_total = 0;          // host time spent blocked on completions
 };
 
+struct AllocRecord { int obj; int64_t size; uint64_t ptr; int kind; };   // kind: 1 allocated, 2 held from the previous run, 0 released
+
 struct FinalBuffer { std::string id; int loc; uint64_t ptr; size_t size; bool external; };
 
 struct RunResult {
@@ -137,6 +141,7 @@ struct RunResult {
   std::string message, failed_task, error_kind;
   std::vector<Interval> intervals;
   std::vector<TraceEvent> events;
+  std::vector<AllocRecord> allocs;
   RunStats stats;
   std::vector<FinalBuffer> finals;
 };
@@ -162,6 +167,9 @@ struct ExecOptions {
   bool manage_pools = true;         // size the session's slabs from the program's capacities
   bool keep_resident = false;       // final-fast objects stay in Session::resident for the next execute()
   int dispatch_ahead = 0;           // tasks that may be launched behind an unfinished predecessor (0 = strict pacing)
+  bool record_allocs = false;       // log every fast-memory allocation and release (placement recorder)
+  // static placement: per object index, the slab offset of its k-th fast allocation in this run (missing = dynamic)
+  const std::vector<std::vector<int64_t>>* placement = nullptr;
   std::atomic<bool>* cancel = nullptr;
 };
 
@@ -190,6 +198,7 @@ class Engine {
   void uncharge(Location loc, int64_t bytes);
   int64_t free_bytes(Location loc) const;
   void free_slot(Slot& s, Location loc);
+  BufferRef get_fast(int obj, int64_t size);
   double xfer_us(const Xfer& x) const;
   void note(const std::string& kind, const std::string& what);
   [[noreturn]] void deadlock(const std::string& why);
@@ -201,6 +210,7 @@ class Engine {
   const ExecOptions* opt_ = nullptr;
   RunResult* out_ = nullptr;
   std::vector<ObjState> objs_;
+  std::vector<int> alloc_count_;       // fast allocations of each object so far in this run (indexes the placement)
   int64_t used_[2] = {0, 0};
   int64_t workspace_ = 0;
   std::deque<Xfer> queue_[2];

@@ -159,6 +159,7 @@ class ChainIndex:
             ir.add_task(tr)
         self.ir = ir
         self.index = index
+        self.ir_object_ids = [o.id for o in objs]
         self.program = program
 
 
@@ -189,7 +190,9 @@ class Engine:
                 run_args: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
                 cancel_event: threading.Event | None = None, record_events: bool = False,
                 slab_headroom: float = 0.0, manage_pools: bool = True, keep_resident: bool = False,
-                dispatch_ahead: int = 0) -> RunResult:
+                dispatch_ahead: int = 0, record_allocs: bool = False, placement=None) -> RunResult:
+        """``placement``: a ``runtime.placement.Placement`` for this program (static offsets of every fast allocation);
+        ``record_allocs`` returns the allocation log the placement is computed from (``result.stats["allocs"]``)."""
         ci = self.chain_index(program)
         tasks = program.tasks
         run_values: dict[str, Any] = {}
@@ -235,7 +238,8 @@ class Engine:
         try:
             raw = self._native.execute(ci.ir, launch, initial, self.strict_final_locations,
                                        self.poison_on_free, record_events, slab_headroom, cancel, manage_pools,
-                                       keep_resident, int(dispatch_ahead))
+                                       keep_resident, int(dispatch_ahead), bool(record_allocs),
+                                       placement.for_index(ci) if placement is not None else [])
         finally:
             if watcher is not None:
                 stop.set()
@@ -246,6 +250,9 @@ class Engine:
         outcome = RunOutcome(RunOutcomeKind(raw["outcome"]), raw["message"], raw["failed_task"],
                              raw["error_kind"], failure.get("traceback", ""))
         finals = {k: Buffer(v[1], v[2], "fast" if v[0] == FAST else "backing", k) for k, v in raw["finals"].items()}
+        if record_allocs:
+            st = dict(st)
+            st["allocs"] = [(ci.ir_object_ids[o] if o >= 0 else None, size, ptr, kind) for o, size, ptr, kind in raw["allocs"]]
         return RunResult(outcome, trace, st["makespan_us"], st["peak_fast_bytes"], st["peak_backing_bytes"],
                          st["slab_overflows"], st["pressure_evictions"], st["placement_escapes"],
                          st["vendor_allocs"], dict(st), finals)

@@ -44,3 +44,27 @@ def test_resident_object_is_adopted_in_place_and_host_copy_is_not_reread():
     # without the held copy the object is loaded from the host bytes again
     res = eng.execute(prog, lambda t: _AddOne(), bufs, keep_resident=False).raise_if_failed()
     assert eng.session.resident() == {}
+
+
+@pytest.mark.gpu
+def test_static_placement_on_the_device_gives_the_same_losses_with_no_overflow_and_no_escape():
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import Trainer, synthetic_rounds
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), n_layers=4, dtype_policy="bf16_master")
+
+    def run(static):
+        tr = Trainer("llama3", cfg, budget_gib=0.5, device=0, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=3, static_placement=static,
+                     lower_kwargs={"resident_params": True})
+        try:
+            losses = [tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, 64, 11, s)) for s in range(4)]
+            return losses, tr.last_result, tr.placement
+        finally:
+            tr.close()
+
+    dyn, _, none = run(False)
+    sta, res, pl = run(True)
+    assert none is None and pl is not None and pl.top > 0
+    assert sta == dyn                                         # placement moves buffers, never values
+    assert res.slab_overflows == 0 and res.placement_escapes == 0

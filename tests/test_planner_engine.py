@@ -120,3 +120,63 @@ def test_dispatch_ahead_keeps_results_and_capacity(cap):
     ahead = Engine(FakeBackend()).execute(prog, dispatch_ahead=2).raise_if_failed()
     assert ahead.peak_fast_bytes <= cap          # (virtual time is only meaningful under strict pacing: no makespan claim)
     assert [iv.name for iv in ahead.trace.by_track("compute")] == [iv.name for iv in strict.trace.by_track("compute")]
+
+
+def test_static_placement_packs_lifetimes_and_the_engine_honours_it():
+    """Dry-run lifetimes -> offsets with no overlap in (time, address); a run with the placement allocates exactly there,
+    escapes nothing, and reproduces the dynamic run's schedule and peak."""
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import plan_at_budget
+    from dataflow_b200.runtime import Engine, FakeBackend, Session, synthetic_resolver
+    from dataflow_b200.runtime.placement import PlacementError, compute_placement, peak_live_bytes, record_lifetimes
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), n_layers=4)
+    planned = plan_at_budget(fam, cfg, int(0.016 * (1 << 30)), leeway_bytes=0)
+    prog = planned.program
+    lts = record_lifetimes(prog)
+    assert len(lts) > 40 and any(lt.occurrence > 0 for lt in lts)            # something was evicted and came back
+    pl = compute_placement(lts)
+    for i, a in enumerate(lts):
+        for b in lts[i + 1:]:
+            if a.start < b.end and b.start < a.end:
+                oa, ob = pl.offsets[(a.object_id, a.occurrence)], pl.offsets[(b.object_id, b.occurrence)]
+                assert oa + a.size <= ob or ob + b.size <= oa
+    peak = peak_live_bytes(lts)
+    assert peak <= pl.top <= 1.15 * peak                                    # little is lost to packing
+    with pytest.raises(PlacementError):
+        compute_placement(lts, capacity=peak - 512)
+    be = FakeBackend()
+    sess = Session(be)
+    sess.native.ensure_pools(pl.top, 0, 0.0)
+    eng = Engine(be, session=sess)
+    base = Engine(FakeBackend()).execute(prog, synthetic_resolver)
+    res = eng.execute(prog, synthetic_resolver, manage_pools=False, record_allocs=True, placement=pl)
+    res.raise_if_failed()
+    assert res.placement_escapes == 0 and res.slab_overflows == 0
+    assert res.makespan_us == pytest.approx(base.makespan_us) and res.peak_fast_bytes == base.peak_fast_bytes
+    slab_base = sess.native.fast_slab()[0]
+    seen = {}
+    for oid, size, ptr, kind in res.stats["allocs"]:
+        if kind == 1:
+            k = seen.get(oid, 0)
+            seen[oid] = k + 1
+            assert ptr - slab_base == pl.offsets[(oid, k)]
+
+
+def test_placement_escape_valve_keeps_a_run_alive_when_the_plan_does_not_match():
+    """A placement whose offsets collide (here: everything at offset 0) cannot be honoured; the engine falls back to the
+    dynamic allocator for the colliding buffers, counts the escapes, and finishes with the same result."""
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import plan_at_budget
+    from dataflow_b200.runtime import Engine, FakeBackend, synthetic_resolver
+    from dataflow_b200.runtime.placement import Placement, record_lifetimes
+    fam = resolve_family("llama3")
+    prog = plan_at_budget(fam, fam.presets["tiny"](), None).program
+    lts = record_lifetimes(prog)
+    bad = Placement({(lt.object_id, lt.occurrence): 0 for lt in lts}, 0, lts)
+    base = Engine(FakeBackend()).execute(prog, synthetic_resolver)
+    res = Engine(FakeBackend()).execute(prog, synthetic_resolver, placement=bad)
+    res.raise_if_failed()
+    assert res.placement_escapes > 0
+    assert res.makespan_us == pytest.approx(base.makespan_us) and res.peak_fast_bytes == base.peak_fast_bytes
