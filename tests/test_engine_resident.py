@@ -1,5 +1,6 @@
 """Final-fast objects stay on the fast tier across execute() calls (Session.resident)."""
 import numpy as np
+import pytest
 import torch
 
 from dataflow_b200.core import ObjectSpec, OutputSpec, Program, TaskSpec
