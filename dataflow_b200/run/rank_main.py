@@ -37,11 +37,14 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     if world > 1:
         import torch
         import torch.distributed as dist
+        import datetime
+        # a rank that died is noticed by the others when their next collective runs out of time
+        timeout = datetime.timedelta(seconds=float(os.environ.get("DATAFLOW_PG_TIMEOUT_S", "1800")))
         if device is None:
-            dist.init_process_group("gloo")
+            dist.init_process_group("gloo", timeout=timeout)
         else:
             torch.cuda.set_device(device)
-            dist.init_process_group("nccl", device_id=torch.device("cuda", device))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", device), timeout=timeout)
         if spec.parallel not in ("tp", "ep"):
             from ..parallel.zero import make_dp_group, zero_lower_kwargs
             # plain data parallelism needs no peer-mapped slab: its one collective per optimizer task is a library all-reduce
@@ -105,6 +108,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
               "data": factory.describe(), "env": _env_facts()}
     try:
         res = train_loop(tr, factory, spec.steps, cursor=cursor, start_step=start, losses=losses, rank_rounds=spec.rounds,
+                         on_step=_host_fault_plan(rank),
                          checkpoint_every=spec.checkpoint_every, checkpoint_dir=spec.checkpoint_dir,
                          keep_last=spec.checkpoint_keep_last, seed=spec.seed, launch=launch, log=say)
     finally:
@@ -116,6 +120,26 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     if spec.out and rank == 0:
         res.save(spec.out)
     return res
+
+
+def _host_fault_plan(rank: int):
+    """Host-side fault injection for failure-detection drills: ``DATAFLOW_FAULT_PLAN="rank=1,step=2,kind=raise"`` makes that
+    rank raise (or ``kind=exit``: leave without a word) right after the named step, between steps, with nothing of its own
+    in flight.  Nothing is injected on a device."""
+    plan = os.environ.get("DATAFLOW_FAULT_PLAN")
+    if not plan:
+        return None
+    kv = dict(item.split("=", 1) for item in plan.split(","))
+    if int(kv.get("rank", -1)) != rank:
+        return None
+    at, kind = int(kv.get("step", 1)), kv.get("kind", "raise")
+
+    def on_step(step, loss, packed):
+        if step == at:
+            if kind == "exit":
+                os._exit(17)
+            raise RuntimeError(f"fault plan: rank {rank} fails after step {step}")
+    return on_step
 
 
 def _env_facts() -> dict:

@@ -1,0 +1,61 @@
+"""Failure detection without faulting a GPU: failures are made on the host (a rank raises or leaves between steps) and the
+surviving ranks must notice within the process-group timeout and end with an error instead of hanging; on a device, a
+kernel whose wait can never be satisfied must return a status and leave the context usable."""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("kind", ["raise", "exit"])
+def test_a_rank_that_fails_between_steps_ends_the_job_quickly(kind, tmp_path):
+    env = dict(os.environ, DATAFLOW_FAULT_PLAN=f"rank=1,step=2,kind={kind}", DATAFLOW_PG_TIMEOUT_S="8", PYTHONPATH=ROOT)
+    cmd = [sys.executable, os.path.join(ROOT, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "6", "--device", "cpu",
+           "--gpus", "2", "--parallel", "co", "--dtype-policy", "fp32", "--out", str(tmp_path / "r.json")]
+    t0 = time.time()
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    took = time.time() - t0
+    assert r.returncode != 0                                      # the job does not pretend to have succeeded
+    assert not (tmp_path / "r.json").exists()
+    assert took < 120                                             # and does not wait out a 30-minute default
+    text = r.stdout + r.stderr
+    assert "step     2" in text and "step     6" not in text
+    if kind == "raise":
+        assert "fault plan: rank 1 fails after step 2" in text
+
+
+@pytest.mark.gpu
+def test_a_device_wait_that_cannot_be_satisfied_returns_a_status_and_the_context_stays_usable():
+    """The expert-parallel combine kernel of rank 0 of a 2-rank group whose peer never publishes its rows: the bounded wait
+    gives up, the error word names the phase and the peer, and the next kernel on the same context runs normally."""
+    import torch
+    from dataflow_b200.ops import native
+    n = native()
+    dev = torch.device("cuda", 0)
+    T, K, d, e_local = 64, 2, 128, 4
+    rows = [torch.zeros(256, d, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    words = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(2)]           # ready word at +0, ack counter at +16 ints
+    ids = torch.full((T, K), e_local, dtype=torch.int32, device=dev)                     # every slot belongs to the (silent) peer
+    rows_local = torch.zeros(T, K, dtype=torch.int32, device=dev)
+    out = torch.empty(T, d, dtype=torch.bfloat16, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    done = torch.zeros(1, dtype=torch.int32, device=dev)
+    t0 = time.time()
+    n.ep_combine([r.data_ptr() for r in rows], [], None, None, ids, rows_local, out, None, e_local, 0,
+                 [w.data_ptr() for w in words], [w.data_ptr() + 64 for w in words], 1, 0.25, err, done)
+    torch.cuda.synchronize()
+    took = time.time() - t0
+    code = int(err.item())
+    assert code != 0 and (code >> 8) in (51, 52)                  # gave up waiting for the peer's rows / for its acknowledgement
+    assert took < 5.0
+    assert int(words[0][0]) == 1                                  # this rank had published its own rows
+    # the context is alive: an ordinary kernel and a copy work
+    x = torch.randn(1024, 1024, device=dev, dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    n.gemm_bf16(x, False, x, True, y, None, None)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all()
