@@ -294,8 +294,20 @@ void Engine::on_task_done(int idx) {
 
 void Engine::handle(const Completion& c) {
   uint64_t kind = c.token >> 40;
-  if (kind == TOK_TASK) on_task_done(static_cast<int>(c.token & 0xFFFFFFFFFFull));
-  else on_transfer_done(kind == TOK_FROM ? 0 : 1);
+  if (kind == TOK_TASK) {
+    // Tasks retire in chain order.  With dispatch-ahead several tasks are in flight on one stream; a backend that polls
+    // may report the completion of a later one first (both events were already done) — it is held until its predecessors
+    // have retired, because a task's directives assume everything before it has taken effect.
+    int idx = static_cast<int>(c.token & 0xFFFFFFFFFFull);
+    done_early_.insert(idx);
+    while (!done_early_.empty() && *done_early_.begin() == task_done_upto_ + 1) {
+      int next = *done_early_.begin();
+      done_early_.erase(done_early_.begin());
+      on_task_done(next);
+    }
+  } else {
+    on_transfer_done(kind == TOK_FROM ? 0 : 1);
+  }
 }
 
 bool Engine::pump_one(bool block) {
@@ -375,6 +387,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
   queue_[0].clear(); queue_[1].clear(); flight_[0].reset(); flight_[1].reset();
   deferred_.clear(); xfer_seq_.clear(); pending_intervals_.clear(); events_to_release_.clear();
   task_done_upto_ = -1; running_task_ = -1;
+  done_early_.clear();
   if (opt.manage_pools) sess_->ensure_pools(p.fast_cap, p.backing_cap, opt.slab_headroom);
   int64_t of0 = sess_->fast_pool.slab_overflows + sess_->backing_pool.slab_overflows;
   int64_t va0 = sess_->fast_pool.vendor_allocs + sess_->backing_pool.vendor_allocs;

@@ -19,6 +19,7 @@
 #include <functional>
 #include <map>
 #include <memory>
+#include <set>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -210,6 +211,7 @@ class Engine {
   const ExecOptions* opt_ = nullptr;
   RunResult* out_ = nullptr;
   std::vector<ObjState> objs_;
+  std::set<int> done_early_;           // completed tasks whose predecessors have not retired yet
   std::vector<int> alloc_count_;       // fast allocations of each object so far in this run (indexes the placement)
   int64_t used_[2] = {0, 0};
   int64_t workspace_ = 0;

@@ -57,7 +57,7 @@ def test_static_placement_on_the_device_gives_the_same_losses_with_no_overflow_a
 
     def run(static):
         tr = Trainer("llama3", cfg, budget_gib=0.5, device=0, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=3, static_placement=static,
-                     lower_kwargs={"resident_params": True})
+                     lower_kwargs={"resident_params": True}, leeway_bytes=0)
         try:
             losses = [tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, 64, 11, s)) for s in range(4)]
             return losses, tr.last_result, tr.placement
