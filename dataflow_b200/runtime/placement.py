@@ -57,9 +57,11 @@ def _round(n: int) -> int:
     return (max(int(n), 1) + ALIGN - 1) // ALIGN * ALIGN
 
 
-def lifetimes_from_log(allocs) -> list[Lifetime]:
+def lifetimes_from_log(allocs, margin: int = 0) -> list[Lifetime]:
     """``allocs``: the (object id | None, size, pointer, kind) log of a run (kind 1 allocated, 2 held from the previous run,
-    0 released)."""
+    0 released).  ``margin`` widens every lifetime by that many log positions on both sides: on a device, copies finish at
+    slightly different points of the chain than in the dry run, and a widened lifetime keeps its bytes clear of neighbours
+    that arrive a little early or leave a little late."""
     open_by_ptr: dict[int, tuple[str, int, int, int]] = {}
     count: dict[str, int] = {}
     out: list[Lifetime] = []
@@ -72,19 +74,19 @@ def lifetimes_from_log(allocs) -> list[Lifetime]:
         else:
             rec = open_by_ptr.pop(ptr, None)
             if rec is not None:
-                out.append(Lifetime(rec[0], rec[1], rec[2], rec[3], pos))
+                out.append(Lifetime(rec[0], rec[1], rec[2], max(rec[3] - margin, 0), min(pos + margin, n)))
     for oid, k, size, start in open_by_ptr.values():
-        out.append(Lifetime(oid, k, size, start, n))
+        out.append(Lifetime(oid, k, size, max(start - margin, 0), n))
     out.sort(key=lambda lt: (lt.start, lt.object_id, lt.occurrence))
     return out
 
 
-def record_lifetimes(program) -> list[Lifetime]:
+def record_lifetimes(program, margin: int = 0) -> list[Lifetime]:
     """Dry run on the virtual-time backend (synthetic executables occupy the compute lane for the planned durations)."""
     from . import Engine, FakeBackend, synthetic_resolver
     res = Engine(FakeBackend()).execute(program, synthetic_resolver, record_allocs=True)
     res.raise_if_failed()
-    return lifetimes_from_log(res.stats["allocs"])
+    return lifetimes_from_log(res.stats["allocs"], margin)
 
 
 def _first_fit(order: list[Lifetime], capacity: int | None) -> tuple[dict, int] | None:
@@ -173,5 +175,11 @@ def peak_live_bytes(lifetimes: list[Lifetime]) -> int:
     return peak
 
 
-def plan_placement(program, capacity: int | None = None, **kw) -> Placement:
-    return compute_placement(record_lifetimes(program), capacity, **kw)
+def plan_placement(program, capacity: int | None = None, margin: int = 6, **kw) -> Placement:
+    """Placement for a real device: lifetimes widened by ``margin`` log positions (exact lifetimes if that does not fit)."""
+    try:
+        return compute_placement(record_lifetimes(program, margin), capacity, **kw)
+    except PlacementError:
+        if not margin:
+            raise
+        return compute_placement(record_lifetimes(program, 0), capacity, **kw)
