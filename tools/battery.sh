@@ -22,5 +22,5 @@ if [ "${1:-}" = "local" ]; then
   exit 0
 fi
 host="${1:?remote host}"; path="${2:?remote path}"
-rsync -a --delete --exclude .git --exclude gpurun_out --exclude _work "$(dirname "$0")/../" "$host:$path/"
+rsync -a --delete --exclude .git --exclude _work "$(dirname "$0")/../" "$host:$path/"
 ssh "$host" "cd '$path' && bash -c '$run_battery'"
