@@ -1,8 +1,7 @@
 // Causal varlen flash attention, forward, on tcgen05 (head_dim 128, bf16, GQA).
 //
 // One CTA per (128-row query tile, head, sequence).  Roles: warp 0 = TMA producer, warp 1 = MMA issuer (and TMEM owner),
-// warps 2-9 = softmax: two threads per query row, 64 keys of every tile each (two warps per scheduler hide the latency
-// of tensor-memory loads and of ex2; the pair agrees on the row maximum through shared memory).  Per 128-key tile j
+// warps 2-5 = softmax: one thread per query row.  Per 128-key tile j
 //     S(j)  = Q K_j^T            tcgen05.mma, both operands K-major from shared memory, accumulator in TMEM (two buffers)
 //     softmax reads S(j) from TMEM (tcgen05.ld, its own lane = its own row): running max / sum in registers, P(j) as bf16
 //            into shared memory in the 128-byte swizzled K-major layout the next MMA wants
@@ -30,11 +29,9 @@ constexpr int BM = 128, BN = 128, D = 128, UK = 16;
 constexpr int CH = 128 * 128;                    // one 128-row x 64-element (128-byte) swizzled chunk: 16 KiB
 constexpr int TILE = 2 * CH;                     // a 128 x 128 bf16 tile
 constexpr int OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_P = 5 * TILE, OFF_BAR = 7 * TILE;
-constexpr int BAR_BYTES = 2560;                  // barriers + the softmax pairs' exchange words
-constexpr int SMEM_BYTES = 7 * TILE + BAR_BYTES;
+constexpr int SMEM_BYTES = 7 * TILE + 256 + 1024;
 constexpr float kRescaleGap = 8.f;               // log2 units the row maximum may run ahead of the exponent base
-constexpr int THREADS = 320;
-constexpr int HALF = BN / 2;                     // keys per softmax thread and tile
+constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr float kNegBig = -1e30f;
 
@@ -42,7 +39,6 @@ struct Bars {
   uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort;
-  float xchg[2][2][BM];          // [tile parity][half][row]: the pair's row maxima (and, at the end, row sums)
 };
 
 struct Params {
@@ -73,12 +69,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int n_kv = qt + 1;
   const int kvh = h / (p.hq / p.hkv);
 
-  extern __shared__ __align__(1024) uint8_t smem[];           // swizzled tiles need 1024-byte alignment; no static shared memory precedes it
-  static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block outgrew its reservation");
-  if (ptx::smem_u32(smem) & 1023u) {                            // never expected; refuse rather than feed misaligned tiles to the MMA
-    if (threadIdx.x == 0) atomicExch(p.err, 60);
-    return;
-  }
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Bars* bar = reinterpret_cast<Bars*>(smem + OFF_BAR);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &bar->abort;
@@ -88,9 +80,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&bar->k_full[b], 1); ptx::mbar_init(&bar->v_full[b], 1);
       ptx::mbar_init(&bar->k_empty[b], 1); ptx::mbar_init(&bar->v_empty[b], 1);
-      ptx::mbar_init(&bar->s_full[b], 1); ptx::mbar_init(&bar->s_empty[b], 8);
+      ptx::mbar_init(&bar->s_full[b], 1); ptx::mbar_init(&bar->s_empty[b], 4);
     }
-    for (int b = 0; b < 2; ++b) { ptx::mbar_init(&bar->p_full[b], 8); ptx::mbar_init(&bar->pv_done[b], 1); }
+    for (int b = 0; b < 2; ++b) { ptx::mbar_init(&bar->p_full[b], 4); ptx::mbar_init(&bar->pv_done[b], 1); }
     bar->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -180,56 +172,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + output: two threads per query row
-    const int q4 = warp & 3;                      // TMEM lane quadrant this warp may touch
-    const int half = (warp - 2) >> 2;             // which 64 keys of every tile (and which 64 columns of O) this thread owns
+    // ------------------------------------------------------------------ softmax + output: one thread per query row
+    const int q4 = warp & 3;
     const int r = q4 * 32 + lane;                 // row inside the tile == TMEM lane
     const int qi = qt * BM + r;                   // row inside the sequence
     const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
-    const uint32_t t_o = tmem_base + 2 * BN + half * HALF + lane_base;
-    float m = kNegBig, l = 0.f;                   // exponent base (log2 units, shared by the pair) and this thread's part of the row sum
+    const uint32_t t_o = tmem_base + 2 * BN + lane_base;
+    float m = kNegBig, l = 0.f;                   // exponent base (log2 units) and the row sum relative to it
     bool ok = true;
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q4) : "memory"); };
     for (int j = 0; j < n_kv && ok; ++j) {
       const int b = j & 1;
       // waits are made warp-uniform: the tensor-memory loads below are warp-wide instructions
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->s_full[b], (j >> 1) & 1, abort_flag))) { bar->abort = 1; atomicExch(p.err, 66); ok = false; }
-      // the pair must leave together (the partner waits at the pair barrier): agree on failure through shared memory
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->s_full[b], (j >> 1) & 1, abort_flag))) { bar->abort = 1; atomicExch(p.err, 66); ok = false; break; }
       ptx::tc_fence_after();
-      float t[HALF];
-      if (ok) {
-        const uint32_t t_s = tmem_base + b * BN + half * HALF + lane_base;
+      const uint32_t t_s = tmem_base + b * BN + lane_base;
+      float t[BN];
 #pragma unroll
-        for (int c = 0; c < HALF / 32; ++c) ptx::tmem_ld_32x32(t_s + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
-        ptx::tmem_ld_wait();
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&bar->s_empty[b]);        // S(j) is in registers: its buffer may take S(j + 2)
-      }
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(t_s + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bar->s_empty[b]);          // S(j) is in registers: its buffer may take S(j + 2)
       float mx = kNegBig;
-      if (ok) {
-        if (j == n_kv - 1) {                      // the diagonal tile (it also holds the end of the sequence)
-          const int key_base = j * BN + half * HALF;
+      if (j == n_kv - 1) {                        // the diagonal tile (it also holds the end of the sequence)
+        const int key_base = j * BN;
 #pragma unroll
-          for (int i = 0; i < HALF; ++i) {
-            const int kj = key_base + i;
-            t[i] = (kj > qi || kj >= seg_len) ? kNegBig : t[i] * p.sl2;
-            mx = fmaxf(mx, t[i]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < HALF; ++i) { t[i] *= p.sl2; mx = fmaxf(mx, t[i]); }
+        for (int i = 0; i < BN; ++i) {
+          const int kj = key_base + i;
+          t[i] = (kj > qi || kj >= seg_len) ? kNegBig : t[i] * p.sl2;
+          mx = fmaxf(mx, t[i]);
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) { t[i] *= p.sl2; mx = fmaxf(mx, t[i]); }
       }
-      // exchange: a failed thread publishes +inf-like poison so that its partner fails too instead of waiting forever
-      bar->xchg[b][half][r] = ok ? mx : 3e38f;
-      pair_sync();
-      const float other = bar->xchg[b][half ^ 1][r];
-      if (!__all_sync(0xffffffffu, ok && other < 1e38f)) { ok = false; break; }
-      mx = fmaxf(mx, other);
       // raise the exponent base only when the maximum ran away from it (always on the first tile); the decision is taken
-      // per warp because rescaling O touches tensor memory with warp-wide instructions (both warps of a pair see the same
-      // numbers, so they decide alike)
+      // per warp because rescaling O touches tensor memory with warp-wide instructions
       const bool raise = j == 0 || mx > m + kRescaleGap;
       if (__any_sync(0xffffffffu, raise)) {
         const float m_new = fmaxf(m, mx);
@@ -241,7 +219,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           ptx::tc_fence_after();
           const float alpha = ex2(m - m_new);
 #pragma unroll 1
-          for (int c = 0; c < HALF / 32; ++c) {
+          for (int c = 0; c < 4; ++c) {
             uint32_t v[32];
             ptx::tmem_ld_32x32(t_o + c * 32, v);
             ptx::tmem_ld_wait();
@@ -260,16 +238,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           bar->abort = 1; atomicExch(p.err, 68); ok = false; break;
         }
       }
-      // this thread's 64 keys are exactly one 64-key chunk of the K-major operand: row r, eight 16-byte vectors, XOR-swizzled
-      uint8_t* p_row = smem + OFF_P + b * TILE + half * CH + r * 128;
+      uint8_t* p_row = smem + OFF_P + b * TILE + r * 128;
       float rowsum = 0.f;
 #pragma unroll
-      for (int g = 0; g < HALF / 8; ++g) {
+      for (int g = 0; g < BN / 8; ++g) {
         float pr[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { pr[i] = ex2(t[g * 8 + i] - m); rowsum += pr[i]; }
         const bf16x8 pk = pack8(pr);
-        *reinterpret_cast<uint4*>(p_row + ((g ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4*>(&pk);
+        // key g*8 .. g*8+7: chunk g / 8 (64 keys each), 16-byte vector g % 8 inside the 128-byte row, XOR-swizzled by the row
+        *reinterpret_cast<uint4*>(p_row + (g >> 3) * CH + (((g & 7) ^ (r & 7)) << 4)) = *reinterpret_cast<const uint4*>(&pk);
       }
       l += rowsum;
       ptx::fence_proxy_async();           // the MMA reads P through the async proxy
@@ -282,18 +260,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         bar->abort = 1; atomicExch(p.err, 69); ok = false;
       }
     }
-    // the row sum is the sum of the pair's parts (same exponent base)
-    bar->xchg[n_kv & 1][half][r] = ok ? l : -1.f;
-    pair_sync();
-    const float l_other = bar->xchg[n_kv & 1][half ^ 1][r];
-    if (ok && l_other >= 0.f) {
+    if (ok) {
       ptx::tc_fence_after();
-      const float l_row = l + l_other;
-      const float inv = 1.f / l_row;
+      const float inv = 1.f / l;
       const long long tok = seg_start + qi;
-      bf16* dst = p.out + tok * p.out_row_stride + static_cast<long long>(h) * D + half * HALF;
+      bf16* dst = p.out + tok * p.out_row_stride + static_cast<long long>(h) * D;
 #pragma unroll 1
-      for (int c = 0; c < HALF / 32; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(t_o + c * 32, v);
         ptx::tmem_ld_wait();
@@ -305,7 +278,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int g = 0; g < 4; ++g) st8(dst + c * 32 + g * 8, pack8(o + g * 8));
         }
       }
-      if (half == 0 && qi < seg_len) p.lse[static_cast<long long>(h) * p.T + tok] = (m + log2f(l_row)) * 0.6931471805599453f;
+      if (qi < seg_len) p.lse[static_cast<long long>(h) * p.T + tok] = (m + log2f(l)) * 0.6931471805599453f;
     }
   }
 
