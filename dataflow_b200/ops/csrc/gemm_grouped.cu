@@ -348,10 +348,13 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       asm volatile("bar.sync 2, 128;" ::: "memory");
       uint4* dst = reinterpret_cast<uint4*>(p.x_dst) + r0 * row_vecs;
       const long long n_vec = static_cast<long long>(HALF_M) * row_vecs;
-      for (long long v = t; v < n_vec; v += 4 * COPY_THREADS) {
-        uint4 x[4];
+      // sixteen 16-byte loads in flight per thread: a peer load takes microseconds, and 128 threads x 16 x 16 bytes per CTA
+      // are what it takes to keep NVLink busy while the GEMM warps of the same CTA multiply
+      constexpr int UNR = 16;
+      for (long long v = t; v < n_vec; v += UNR * COPY_THREADS) {
+        uint4 x[UNR];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UNR; ++u) {
           const long long vv = v + u * COPY_THREADS;
           x[u] = make_uint4(0, 0, 0, 0);
           if (vv < n_vec) {
@@ -364,7 +367,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UNR; ++u) {
           const long long vv = v + u * COPY_THREADS;
           if (vv < n_vec) dst[vv] = x[u];
         }
