@@ -129,11 +129,20 @@ __global__ void __launch_bounds__(512) zero_rs_adamw_kernel(RsAdamwParams p) {
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int r = 0; r < W; ++r) {                         // fixed rank order: deterministic sum
-        float f[8];
-        unpack8(ld8(src[r] + g0), f);
+      // every rank's vector is requested before the first one is used (a peer load takes microseconds); the sum still runs
+      // in rank order: deterministic
+      bf16x8 pv[kMaxWorld];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      for (int r = 0; r < kMaxWorld; ++r)
+        if (r < W) pv[r] = ld8(src[r] + g0);
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r < W) {
+          float f[8];
+          unpack8(pv[r], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
       }
       if (p.gacc) {
         float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -233,13 +242,28 @@ __global__ void __launch_bounds__(512) param_gather_kernel(GatherParams p) {
   }
   __syncthreads();
   if (!failed) {
-    for (long long vi = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vi < p.total_vec;
-         vi += static_cast<long long>(gridDim.x) * blockDim.x) {
-      // start with the slice after mine so that the ranks do not all hit the same peer at once
-      long long rot = (vi + (static_cast<long long>(me) + 1) * p.per_vec) % p.total_vec;
-      int r = static_cast<int>(rot / p.per_vec);
-      if (r >= W) r = W - 1;
-      p.full[rot] = src[r][rot - static_cast<long long>(r) * p.per_vec];
+    // eight vectors in flight per thread (a peer load takes microseconds)
+    constexpr int UNR = 8;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < p.total_vec; v0 += UNR * stride) {
+      uint4 x[UNR];
+      long long at[UNR];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long vi = v0 + u * stride;
+        at[u] = -1;
+        if (vi < p.total_vec) {
+          // start with the slice after mine so that the ranks do not all hit the same peer at once
+          long long rot = (vi + (static_cast<long long>(me) + 1) * p.per_vec) % p.total_vec;
+          int r = static_cast<int>(rot / p.per_vec);
+          if (r >= W) r = W - 1;
+          at[u] = rot;
+          x[u] = src[r][rot - static_cast<long long>(r) * p.per_vec];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u)
+        if (at[u] >= 0) p.full[at[u]] = x[u];
     }
   }
   __threadfence_system();
