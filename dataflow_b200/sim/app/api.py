@@ -6,13 +6,17 @@
     POST /api/simulate             same input + memory budget + policy -> plan, simulate, summary, timelines
 
 Reference role: ``src/dataflow_sim/app/server/main.py:78-211`` (request models), ``:216,221,346,552`` (the four routes).
-The browser front end of the reference is not rebuilt; every panel's data is in the ``/api/simulate`` response.
+``GET /`` serves a single-page front end (``static/index.html``: inputs, summary, compute / copy timeline, device-memory
+curve, time by phase, planner comparison — plain JavaScript and SVG over the four routes; the reference's is a React app).
 """
 from __future__ import annotations
 
 from typing import Any
 
+import os
+
 from fastapi import FastAPI, HTTPException
+from fastapi.responses import HTMLResponse
 from pydantic import BaseModel, Field
 
 from ..policies import get_all_policies
@@ -86,6 +90,11 @@ def _program(req: WorkloadRequest) -> WorkloadProgram:
 
 def create_app() -> FastAPI:
     app = FastAPI(title="dataflow_b200 simulator", version=VERSION)
+
+    @app.get("/", response_class=HTMLResponse)
+    def index():
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "static", "index.html"), encoding="utf-8") as f:
+            return f.read()
 
     @app.get("/api/health")
     def health():

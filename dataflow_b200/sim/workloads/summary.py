@@ -36,4 +36,4 @@ def compute_summary(chain: TaskChain, log: EventLog, program=None) -> dict:
 
 def _moved(chain: TaskChain, log: EventLog, direction: str) -> int:
     sizes = chain.sizes()
-    return int(sum(sizes.get(iv.task_id, 0) for iv in log.transfer_intervals(direction)))
+    return int(sum(sizes.get(iv.task_id.split(":", 1)[-1], 0) for iv in log.transfer_intervals(direction)))

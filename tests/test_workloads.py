@@ -74,6 +74,10 @@ def test_http_api_preview_and_simulate():
     from dataflow_b200.sim.app.api import create_app
     c = TestClient(create_app())
     assert c.get("/api/health").json()["ok"]
+    page = c.get("/")
+    assert page.status_code == 200 and "text/html" in page.headers["content-type"]
+    for needle in ('id="timeline"', 'id="memory"', "/api/simulate", "/api/presets", 'id="compare"'):
+        assert needle in page.text
     presets = c.get("/api/presets").json()
     assert "B200" in presets["hardware"] and "llama3_8b" in presets["models"] and "pressurefit" in presets["policies"]
     body = {"model": "llama3_8b", "training": {"rounds": 2, "tokens_per_round": 8192}, "hardware": "B200"}
@@ -82,6 +86,7 @@ def test_http_api_preview_and_simulate():
     sim = c.post("/api/simulate", json={**body, "fast_memory_gib": 40, "policy": "pressurefit", "memory_trace": True}).json()
     assert sim["summary"]["peak_fast_bytes"] <= 40 * (1 << 30)
     assert sim["summary"]["tokens_per_s"] > 0 and sim["timeline"] and sim["memory_trace"]
+    assert sim["summary"]["from_slow_bytes"] > 0 and sim["summary"]["to_slow_bytes"] > 0      # a 40 GiB budget forces traffic
     assert c.post("/api/simulate", json={**body, "policy": "nope"}).status_code == 404
     assert c.post("/api/workloads/preview", json={"hardware": "B200"}).status_code == 422
     assert c.post("/api/workloads/preview", json={**body, "hardware": "abacus"}).status_code == 404
