@@ -133,14 +133,24 @@ def dsa_topk_mask(scores, causal, k: int):
     return torch.zeros_like(causal).scatter_(1, idx, True) & causal
 
 
-def dsa_indexer_kl(scores, probs, causal):
-    """KL(attention distribution summed over heads || softmax of the index scores), mean over queries; the attention
-    side is a constant target."""
+def dsa_attention_target(probs):
+    """The indexer's training target of one layer: attention probabilities summed over heads, L1-normalised per query,
+    detached.  probs (heads, n, n) -> (n, n)."""
     target = probs.detach().sum(0)
-    target = target / (target.sum(-1, keepdim=True) + 1e-20)
+    return target / (target.sum(-1, keepdim=True) + 1e-20)
+
+
+def dsa_indexer_kl_to(scores, target, causal):
+    """KL(target || softmax of the index scores over the causal prefix), mean over queries; ``target`` is a constant."""
     logq = torch.log_softmax(scores.masked_fill(~causal, float("-inf")), dim=-1)
     term = torch.where(target > 0, target * (torch.log(target.clamp_min(1e-20)) - logq), torch.zeros_like(target))
     return term.sum(-1).mean()
+
+
+def dsa_indexer_kl(scores, probs, causal):
+    """KL(attention distribution summed over heads || softmax of the index scores), mean over queries; the attention
+    side is a constant target."""
+    return dsa_indexer_kl_to(scores, dsa_attention_target(probs), causal)
 
 
 _KS = {}

@@ -57,6 +57,12 @@ class TorchFamilySpec:
     # gets that dict as the ``shared`` argument of its block function, forward and backward
     ctx_fields: Callable[[Any, int], Sequence[Field]] | None = None     # (cfg, tokens) -> fields of A
     leader_of: Callable[[Any, int], int | None] | None = None
+    # backward-time accumulation inside a group: a follower's block function may return, under the key ``"_deposit"`` of
+    # its third value, a dict of tensors (fields from ``accum_fields``); the followers' BACKWARD tasks sum them into the
+    # group's accumulator object ``G_{step}_{round}_{leader}`` (created by the first backward of the group to run,
+    # mutated by the others), and the leader's backward passes the sums to its block function as ``accum`` together with
+    # ``group_size`` (members of the group, the leader included)
+    accum_fields: Callable[[Any, int], Sequence[Field]] | None = None   # (cfg, tokens) -> fields of G
 
 
 CTX = PackedLayout((Field("stamp", (4,), "fp32"),))
@@ -109,6 +115,8 @@ class MultiKindLayouts:
                 return self.of_layer(int(tail))[2]
         if oid.startswith("A_"):
             return self.ctx
+        if oid.startswith("G_"):
+            return self.extra.get("accum")
         return None
 
     def object_layouts(self, program):
@@ -157,7 +165,13 @@ class _TorchBlock(_Base):
                 return {k: v[:n] for k, v in self.views(b, self.lay.ctx).items() if k != "stamp"}
         raise RuntimeError(f"task {ctx.task.id}: the context of leader layer {leader} is not among the inputs")
 
-    def call(self, ctx, x, w, layer, grad: bool):
+    def followers_of(self, layer):
+        spec, d = self.spec, self.dims
+        if spec.leader_of is None:
+            return []
+        return [i for i in range(d.n_layers) if spec.leader_of(d.x, i) == layer]
+
+    def call(self, ctx, x, w, layer, grad: bool, **extra):
         import torch
         d = self.dims
         seg = self.segments(ctx)
@@ -169,7 +183,7 @@ class _TorchBlock(_Base):
             wl = {k: v.detach().requires_grad_(True) for k, v in wl.items()}
         shared = self.shared_from_leader(ctx, layer, x.shape[0])
         with torch.set_grad_enabled(grad):
-            res = self.spec.block_fn(d.x, d.kinds[layer], xin, wl, seg, layer, **({"shared": shared} if shared is not None else {}))
+            res = self.spec.block_fn(d.x, d.kinds[layer], xin, wl, seg, layer, **({"shared": shared} if shared is not None else {}), **extra)
         self.emitted = res[2] if len(res) > 2 else None
         return xin, wl, res[0], res[1]
 
@@ -188,7 +202,8 @@ class TorchBlockFwd(_TorchBlock):
         a = self.views(ctx.outputs[1], self.lay.ctx)
         a["stamp"].zero_()
         for k, v in (self.emitted or {}).items():
-            a[k][:n].copy_(v)
+            if not k.startswith("_"):
+                a[k][:n].copy_(v)
 
 
 class TorchBlockBwd(_TorchBlock):
@@ -204,7 +219,20 @@ class TorchBlockBwd(_TorchBlock):
         dx = self.tview(ctx.outputs[0], (d.T, d.d))[:n]
         acc = not self.creating(ctx, "dW_")
         g = self.views(self.by_id(ctx, "dW_"), self.lay.of_layer(layer)[1])
-        xin, wl, y, aux = self.call(ctx, x, self.weights(ctx.inputs[3], layer), layer, True)
+        extra = {}
+        gbuf = self.by_id(ctx, "G_")
+        if gbuf is not None and self.spec.leader_of(d.x, layer) is None:      # the leader consumes the group's sums
+            extra = {"accum": {k: v[:n] for k, v in self.views(gbuf, self.lay.extra["accum"]).items()},
+                     "group_size": 1 + len(self.followers_of(layer))}
+        xin, wl, y, aux = self.call(ctx, x, self.weights(ctx.inputs[3], layer), layer, True, **extra)
+        if gbuf is not None and not extra:                                     # a follower adds its share
+            dep = (self.emitted or {}).get("_deposit") or {}
+            create = self.creating(ctx, "G_")
+            for k, v in self.views(gbuf, self.lay.extra["accum"]).items():
+                if create:
+                    v.zero_()
+                if k in dep:
+                    v[:n].add_(dep[k].detach().to(v.dtype))
         total = (y * dy.to(y.dtype)).sum()
         if aux is not None:
             # the auxiliary loss enters every round with the weight the main loss has: 1 / (rows of the whole step)
@@ -249,24 +277,42 @@ def make_twin(spec: TorchFamilySpec, cfg):
                     m.register_parameter(f.name, torch.nn.Parameter(torch.zeros(tuple(f.shape))))
                 self.layers.append(m)
 
-        def loss(self, tokens, targets, bounds, total_rows=None):
-            from ..data.segments import make_segments
+        def run_layers(self, tokens, n, seg, sums, collect):
             d = self.d
-            tokens, targets = torch.as_tensor(tokens).long(), torch.as_tensor(targets).long()
-            n = int(bounds[-1])
-            seg = make_segments(list(bounds), None)
             x = self.wte[tokens[:n]]
             aux_total = 0.0
             emitted = {}
             for i, m in enumerate(self.layers):
                 w = dict(m.named_parameters())
                 leader = spec.leader_of(cfg, i) if spec.leader_of else None
-                res = spec.block_fn(cfg, d.kinds[i], x, w, seg, i, **({"shared": emitted[leader]} if leader is not None else {}))
+                kw = {"shared": emitted[leader]} if leader is not None else {}
+                if leader is None and i in sums:
+                    kw.update(accum=sums[i], group_size=1 + sum(1 for j in range(d.n_layers) if spec.leader_of(cfg, j) == i))
+                res = spec.block_fn(cfg, d.kinds[i], x, w, seg, i, **kw)
                 x, aux = res[0], res[1]
                 if len(res) > 2 and res[2]:
                     emitted[i] = res[2]
+                    dep = res[2].get("_deposit")
+                    if collect is not None and dep and leader is not None:
+                        tgt = collect.setdefault(leader, {})
+                        for k, v in dep.items():
+                            tgt[k] = tgt[k] + v if k in tgt else v.clone()
                 if aux is not None:
                     aux_total = aux_total + aux
+            return x, aux_total
+
+        def loss(self, tokens, targets, bounds, total_rows=None):
+            from ..data.segments import make_segments
+            d = self.d
+            tokens, targets = torch.as_tensor(tokens).long(), torch.as_tensor(targets).long()
+            n = int(bounds[-1])
+            seg = make_segments(list(bounds), None)
+            sums = {}
+            if spec.accum_fields is not None:
+                # what the followers deposit is a detached function of the forward values: collect it in a first pass
+                with torch.no_grad():
+                    self.run_layers(tokens, n, seg, {}, sums)
+            x, aux_total = self.run_layers(tokens, n, seg, sums, None)
             xn = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + d.eps) * self.final_norm
             logits = xn @ self.w_head
             tg = targets[:n]
@@ -312,8 +358,9 @@ def layouts(spec: TorchFamilySpec, d: TorchDims, policy=None, optimizer: str = "
         by_kind[kind] = (weight_layout(f, policy), grad_layout(f, policy), opt_state_layout(f, policy, rule_of=rule))
     ef, hf = embed_fields(d), head_fields(d)
     ctx = CTX if spec.ctx_fields is None else PackedLayout(tuple(CTX.fields) + tuple(spec.ctx_fields(d.x, d.T)))
+    extra = {} if spec.accum_fields is None else {"accum": PackedLayout(tuple(spec.accum_fields(d.x, d.T)))}
     return MultiKindLayouts(d, policy, by_kind, weight_layout(ef, policy), grad_layout(ef, policy), opt_state_layout(ef, policy, rule_of=rule),
-                            weight_layout(hf, policy), grad_layout(hf, policy), opt_state_layout(hf, policy, rule_of=rule), ctx)
+                            weight_layout(hf, policy), grad_layout(hf, policy), opt_state_layout(hf, policy, rule_of=rule), ctx, extra)
 
 
 def _subop(name, flops=0.0, nbytes=0.0, eff="matmul"):
@@ -354,23 +401,46 @@ def lower(spec: TorchFamilySpec, cfg, recompute_levels=None, hw: ShapedHardware 
         resident_params=resident_params,
         metadata={"family": spec.name, "preset": cfg.name, "flops_per_token": 3.0 * (total_mm + 2.0 * d.d * d.vocab),
                   "seq_len": cfg.seq_len, "batch": cfg.batch, "block_lane": "autograd"})
-    return share_leader_contexts(spec, cfg, prog)
+    return share_leader_contexts(spec, cfg, prog, lay.extra["accum"].size_bytes if "accum" in lay.extra else 0)
 
 
-def share_leader_contexts(spec: TorchFamilySpec, cfg, prog):
+def share_leader_contexts(spec: TorchFamilySpec, cfg, prog, accum_bytes: int = 0):
     """Lowering post-pass: forward and backward tasks of a follower layer also read the context object of their leader
-    (same step, same round), which keeps it alive until the last follower's backward has run."""
+    (same step, same round), which keeps it alive until the last follower's backward has run.  With ``accum_bytes``
+    every group that has followers also gets its accumulator ``G_{step}_{round}_{leader}``: the backward of the group's
+    last layer (the first to run) creates it, the other followers' backwards mutate it, the leader's backward reads it."""
     if spec.leader_of is None:
         return prog
+    from ..core.program import OutputSpec
+    n_layers = int(cfg.n_layers)
+    last_member = {}
+    for i in range(n_layers):
+        lead = spec.leader_of(cfg, i)
+        if lead is not None:
+            last_member[lead] = i
     tasks = []
     for t in prog.tasks:
         layer, key = t.block_params.get("layer") if t.block_params else None, t.compute_block_key or ""
-        leader = spec.leader_of(cfg, int(layer)) if layer is not None and key.endswith(("_fwd", "_bwd")) else None
-        if leader is None:
+        if layer is None or not key.endswith(("_fwd", "_bwd")):
             tasks.append(t)
             continue
+        layer = int(layer)
+        leader = spec.leader_of(cfg, layer)
         own = next(o for o in (list(t.inputs) + [x.id for x in t.outputs]) if o.startswith("A_"))
-        tasks.append(dataclasses.replace(t, inputs=tuple(t.inputs) + (own.rsplit("_", 1)[0] + f"_{leader}",)))
+        stem = own.rsplit("_", 1)[0]
+        if leader is None:
+            if accum_bytes and key.endswith("_bwd") and layer in last_member:
+                t = dataclasses.replace(t, inputs=tuple(t.inputs) + ("G" + stem[1:] + f"_{layer}",))
+            tasks.append(t)
+            continue
+        t = dataclasses.replace(t, inputs=tuple(t.inputs) + (stem + f"_{leader}",))
+        if accum_bytes and key.endswith("_bwd"):
+            gid = "G" + stem[1:] + f"_{leader}"
+            if layer == last_member[leader]:
+                t = dataclasses.replace(t, outputs=tuple(t.outputs) + (OutputSpec(gid, int(accum_bytes)),))
+            else:
+                t = dataclasses.replace(t, inputs=tuple(t.inputs) + (gid,), mutates=tuple(t.mutates) + (gid,))
+        tasks.append(t)
     return dataclasses.replace(prog, tasks=tuple(tasks))
 
 

@@ -4,9 +4,11 @@ mixture of experts after the first dense layers) with CROSS-LAYER INDEX SHARING:
 object, the others (followers) carry no indexer weights and attend over the leader's selection.  Kinds ``gdl`` / ``gdf``
 (dense leader / follower) and ``gml`` / ``gmf`` (mixture-of-experts leader / follower).  A lowering post-pass makes the
 followers' forward and backward tasks read the leader's context object.
-The indexer is trained by the KL term of its own (leader) layer; the reference additionally accumulates the followers'
-attention distributions into that target (``src/dataflow_training/model_families/glm52/{blocks.py,model.py}``), which
-this lane leaves out.
+The indexer is trained against the attention of EVERY layer that uses its selection: each follower's backward adds its
+target (head-summed attention probabilities, L1-normalised per query, gathered at the shared selection) to the group's
+accumulator object, and the leader's backward — the last of the group to run — takes the KL of its index distribution
+to ``(own target + the followers' sum) / group size``.  A leader without followers keeps dsv32's per-layer rule.
+Reference role: ``src/dataflow_training/model_families/glm52/{blocks.py,model.py}``.
 """
 from __future__ import annotations
 
@@ -43,7 +45,11 @@ def ctx_fields(c: Glm52Config, tokens: int):
     return (Field("sel", (tokens, min(c.index_topk, c.seq_len)), "int32"),)
 
 
-def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None):
+def accum_fields(c: Glm52Config, tokens: int):
+    return (Field("kl_target", (tokens, min(c.index_topk, c.seq_len)), "fp32"),)
+
+
+def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=None, group_size=1):
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
@@ -59,8 +65,16 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None):
         sel = shared["sel"].long()[:, :min(c.index_topk, c.seq_len, n)]
     mask = torch.zeros_like(causal).scatter_(1, sel.clamp(max=n - 1), True) & causal
     o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
-    if shared is None and c.index_kl_coef:
-        aux = c.index_kl_coef * F.dsa_indexer_kl(scores, probs, mask) * n
+    if c.index_kl_coef:
+        target = F.dsa_attention_target(probs)
+        cols = sel.clamp(max=n - 1)
+        if shared is not None:                                      # follower: its share of the leader's target
+            width = min(c.index_topk, c.seq_len)
+            emit = {"_deposit": {"kl_target": torch.nn.functional.pad(target.gather(1, cols), (0, width - cols.shape[1]))}}
+        else:
+            if accum is not None:
+                target = (target + torch.zeros_like(target).scatter_add_(1, cols, accum["kl_target"][:, :cols.shape[1]].to(target.dtype))) / group_size
+            aux = c.index_kl_coef * F.dsa_indexer_kl_to(scores, target, mask) * n
     h_mid = x + o.reshape(n, -1) @ w["wo"]
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if kind.startswith("gd"):
@@ -94,5 +108,5 @@ PRESETS = {
 }
 
 SPEC = TorchFamilySpec("glm52", Glm52Config, {k: (lambda kw=v: Glm52Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,
-                       block_fn, kind_flops, ctx_fields=ctx_fields, leader_of=leader_of)
+                       block_fn, kind_flops, ctx_fields=ctx_fields, leader_of=leader_of, accum_fields=accum_fields)
 FAMILY = register_torch_family(SPEC)

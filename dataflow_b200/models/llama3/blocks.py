@@ -15,6 +15,12 @@ from ...blocks.base_blocks import _Base, common_executables
 
 
 # --------------------------------------------------------------------------- stages
+def _lin(K, st):
+    """The forward linear of the four large dense projections: bf16, or e4m3 operands with fp32 accumulation when the
+    training configuration asks for ``linear_precision: fp8`` (backward GEMMs stay bf16; router logits stay bf16)."""
+    return K.linear_fwd_fp8 if st.get("fp8") else K.linear_fwd_bf16
+
+
 def stage_attn_norm(K, d, st):
     st["h"], rstd = K.rmsnorm_fwd(st["x"], st["w"]["attn_norm"], d.eps)
     st["a"]["rstd_attn"].copy_(rstd)
@@ -29,7 +35,7 @@ def _qkv_views(d, qkv, n):
 
 def stage_qkv_rope(K, d, st):
     qkv = st["a"]["qkv"]
-    K.linear_fwd_bf16(st["h"], st["w"]["w_qkv"], out=qkv)
+    _lin(K, st)(st["h"], st["w"]["w_qkv"], out=qkv)
     q, k, v = _qkv_views(d, qkv, st["n"])
     if d.qk_norm:
         a = st["a"]
@@ -55,13 +61,13 @@ def stage_attn(K, d, st):
 
 def stage_resid1_norm2(K, d, st):
     h_mid = st["a"]["h_mid"]
-    K.linear_fwd_bf16(st["a"]["attn_out"], st["w"]["wo"], out=h_mid, add=st["x"])
+    _lin(K, st)(st["a"]["attn_out"], st["w"]["wo"], out=h_mid, add=st["x"])
     st["h2"], rstd = K.rmsnorm_fwd(h_mid, st["w"]["ffn_norm"], d.eps)
     st["a"]["rstd_ffn"].copy_(rstd)
 
 
 def stage_up_proj(K, d, st):
-    K.linear_fwd_bf16(st["h2"], st["w"]["w13"], out=st["a"]["h13"])
+    _lin(K, st)(st["h2"], st["w"]["w13"], out=st["a"]["h13"])
 
 
 def stage_swiglu(K, d, st):
@@ -69,7 +75,7 @@ def stage_swiglu(K, d, st):
 
 
 def stage_down_resid(K, d, st):
-    K.linear_fwd_bf16(st["s"], st["w"]["w2"], out=st["y"], add=st["a"]["h_mid"])
+    _lin(K, st)(st["s"], st["w"]["w2"], out=st["y"], add=st["a"]["h_mid"])
 
 
 # ---- mixture-of-experts MLP (olmoe / qwen3moe variants): route -> dispatch + grouped up-projection -> SwiGLU ->
@@ -228,7 +234,8 @@ class _Block(_Base):
         d = self.dims
         seg = self.segments(ctx)
         n = seg.n_tokens
-        st = {"seg": seg, "n": n, "x": self.tview(x_buf, (d.T, d.d))[:n], "w": self.views(w_buf, self.lay.block_w)}
+        st = {"seg": seg, "n": n, "x": self.tview(x_buf, (d.T, d.d))[:n], "w": self.views(w_buf, self.lay.block_w),
+              "fp8": self.hyper.get("linear_precision", "bf16") == "fp8"}
         if getattr(d, "ep", 1) > 1:
             if n != d.T:
                 raise ValueError("expert-parallel blocks need full rounds (the peers pull exactly T rows from each rank)")

@@ -423,6 +423,15 @@ def linear_fp8(xq, x_scale, wq, w_scale, out=None, add=None, bias=None, out_dtyp
     return out
 
 
+@reg("linear_fwd_fp8", launches=3)
+def linear_fwd_fp8(x, w, out=None, add=None, bias=None):
+    """Forward linear on the fp8 tensor-core path: quantise x per row and w (stored (in, out)) per output column, run the
+    ``kind::f8f6f4`` GEMM, dequantise in its epilogue.  The weight is transposed to (out, in) on the way (one copy)."""
+    xq, sx = quant_fp8_rowwise(x)
+    wq, sw = quant_fp8_rowwise(w.t().contiguous())
+    return linear_fp8(xq, sx, wq, sw, out=out, add=add, bias=bias, out_dtype=out.dtype if out is not None else x.dtype)
+
+
 # ------------------------------------------------------------------ attention forward on tcgen05 (attention.cu)
 def flash_fwd_tcgen05(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
     """Causal varlen attention on the hand-written kernel, head_dim 128; q (t, hq, 128), k / v (t, hkv, 128) — views into a

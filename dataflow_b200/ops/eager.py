@@ -721,6 +721,15 @@ def quant_fp8_rowwise(x):
     return q, scale
 
 
+@register("linear_fwd_fp8", "eager")
+def linear_fwd_fp8(x, w, out=None, add=None, bias=None):
+    """``linear_fwd_bf16`` with both operands rounded to e4m3 first: x (M, K) per row, w (K, N) stored (in, out) per output
+    column; fp32 accumulation, scales applied to the accumulator, one rounding to the output dtype."""
+    xq, sx = quant_fp8_rowwise(x)
+    wq, sw = quant_fp8_rowwise(w.t().contiguous())
+    return linear_fp8(xq, sx, wq, sw, out=out, add=add, bias=bias, out_dtype=out.dtype if out is not None else x.dtype)
+
+
 @register("linear_fp8", "eager")
 def linear_fp8(xq, x_scale, wq, w_scale, out=None, add=None, bias=None, out_dtype=torch.bfloat16):
     """y (M, N) = (xq * x_scale[:, None]) @ (wq * w_scale[:, None])^T (+ bias) (+ add); wq stored (N, K)."""

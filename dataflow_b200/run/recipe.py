@@ -26,6 +26,11 @@ class Recipe:
     optimizer: str = "adamw"
     muon_lr: float | None = None
     momentum: float = 0.95
+    linear_precision: str = "bf16"      # bf16 | fp8: operand precision of the dense forward projections (llama-like families)
+
+    def __post_init__(self):
+        if self.linear_precision not in ("bf16", "fp8"):
+            raise ValueError(f"linear_precision must be bf16 or fp8, not {self.linear_precision!r}")
 
     def lr_schedule(self) -> LRSchedule:
         return LRSchedule(self.schedule, self.peak_lr, self.min_lr, self.warmup_steps, self.total_steps, self.decay_steps)
@@ -38,6 +43,8 @@ class Recipe:
              "beta2": self.beta2, "eps": self.eps, "weight_decay": self.weight_decay, "momentum": self.momentum}
         if self.muon_lr is not None:
             h["muon_lr"] = self.muon_lr
+        if self.linear_precision != "bf16":
+            h["linear_precision"] = self.linear_precision
         return h
 
     def to_dict(self) -> dict:

@@ -199,3 +199,21 @@ def test_linear_fp8_matches_oracle(shape):
     assert float((y.float() - full).norm() / full.norm()) < 0.06
     from dataflow_b200.ops import native as _n
     assert _n().gemm_last_error() == 0
+
+
+@pytest.mark.gpu
+def test_linear_fwd_fp8_matches_oracle():
+    """The composed forward linear (quantise activations per row, the (in, out) weight per output column, fp8 GEMM) against
+    the same composition in the oracle, and against the bf16 product."""
+    native, oracle = _pair("linear_fwd_fp8")
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(1000, 1024, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(1024, 768, device="cuda", generator=g) * 0.03).bfloat16()
+    resid = torch.randn(1000, 768, device="cuda", generator=g).bfloat16()
+    out = torch.empty(1000, 768, device="cuda", dtype=torch.bfloat16)
+    y = native(x, w, out=out, add=resid)
+    assert y.data_ptr() == out.data_ptr()
+    y_ref = oracle(x.cpu(), w.cpu(), add=resid.cpu())
+    assert float((y.float().cpu() - y_ref.float()).norm() / y_ref.float().norm()) < 5e-3
+    full = x.float() @ w.float() + resid.float()
+    assert float((y.float() - full).norm() / full.norm()) < 0.06

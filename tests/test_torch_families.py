@@ -56,6 +56,48 @@ def test_glm52_followers_read_their_leaders_selection_and_budget_does_not_change
     assert tight["engine"] == pytest.approx(free["engine"], rel=1e-6)
 
 
+def test_glm52_indexer_target_sums_over_the_group():
+    """Groups of three: the last member's backward creates the accumulator, the middle one mutates it, the leader's reads
+    it; the engine and the twin (which collects the followers' targets in a first pass) train the indexer alike."""
+    fam = resolve_family("glm52")
+    over = {"index_share": 3, "n_layers": 6, "n_dense": 2}
+    import dataclasses
+    cfg = dataclasses.replace(fam.presets["tiny"](), **over)
+    prog = fam.lower(cfg)
+    assert fam.derive_dims(cfg).kinds == ("gdl", "gdf", "gmf", "gml", "gmf", "gmf")
+    by = {(t.block_params["layer"], t.block_params["round"]): t for t in prog.tasks
+          if (t.compute_block_key or "").endswith("_bwd") and "layer" in t.block_params}
+    for r in range(cfg.grad_accum_rounds):
+        for lead in (0, 3):
+            gid = f"G_0_{r}_{lead}"
+            assert gid in [o.id for o in by[(lead + 2, r)].outputs]
+            assert gid in by[(lead + 1, r)].mutates and gid in by[(lead, r)].inputs
+    assert prog.object_sizes()["G_0_0_0"] == 4 * cfg.seq_len * cfg.batch * min(cfg.index_topk, cfg.seq_len)
+    res = run_pair("glm52", steps=3, overrides=over)
+    assert res["max_loss_rel"] < 1e-3
+    # three AdamW steps amplify rounding differences into a few percent of weight distance in every field of this gate;
+    # an engine that left the followers' share out lands at 0.16 - 0.17 on these four fields
+    idx = {k: v for k, v in res["weight_rel_l2"].items() if k.endswith((".wi_q", ".wi_k"))}
+    assert len(idx) == 4 and max(idx.values()) < 0.05
+    # the followers' share moves the leader's auxiliary loss
+    from dataflow_b200.data.segments import make_segments
+    from dataflow_b200.models.glm52 import block_fn, kind_fields
+    c = fam.presets["tiny"]()
+    g = torch.Generator().manual_seed(0)
+    n = c.seq_len
+    w = {f.name: torch.randn(tuple(f.shape), generator=g) * (0.3 if len(f.shape) > 1 else 1.0) for f in kind_fields(c, "gdl")}
+    x = torch.randn(n, c.d_model, generator=g)
+    seg = make_segments([0, n], None)
+    _, aux_own, emit = block_fn(c, "gdl", x, w, seg, 0)
+    wf = {k: v for k, v in w.items() if not k.startswith("wi_")}
+    _, aux_f, emit_f = block_fn(c, "gdf", torch.randn(n, c.d_model, generator=g), wf, seg, 1, shared=emit)
+    assert aux_f is None and set(emit_f) == {"_deposit"}
+    dep = emit_f["_deposit"]["kl_target"]
+    assert dep.shape == (n, min(c.index_topk, c.seq_len)) and torch.allclose(dep.sum(-1), torch.ones(n), atol=1e-4)
+    _, aux_group, _ = block_fn(c, "gdl", x, w, seg, 0, accum=emit_f["_deposit"], group_size=2)
+    assert abs(float(aux_group) - float(aux_own)) > 1e-6
+
+
 def test_delta_rule_with_full_write_strength_stores_and_recalls_an_association():
     # one head, orthonormal keys, beta = 1, no decay: after writing (k_i -> v_i) the state returns v_i for q = k_i
     dk = dv = 4

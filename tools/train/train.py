@@ -35,6 +35,8 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-seq-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--dtype-policy", default=None)
+    ap.add_argument("--linear-precision", default=None, choices=["bf16", "fp8"],
+                    help="operand precision of the dense forward projections (fp8: e4m3 with per-row / per-column scales)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--fast-budget", type=float, default=None, help="device memory budget in GiB")
     ap.add_argument("--gpus", type=int, default=1)
@@ -71,6 +73,8 @@ def spec_from_args(a, argv):
               "warmup_steps": a.warmup_steps}
     if a.muon_lr is not None:
         recipe["muon_lr"] = a.muon_lr
+    if a.linear_precision is not None:
+        recipe["linear_precision"] = a.linear_precision
     if a.opt:
         recipe["optimizer"] = a.opt
     return RunSpec(preset=a.preset, steps=a.steps, overrides=ov, recipe=recipe, data=a.data, packing_policy=a.packing_policy,
