@@ -43,6 +43,8 @@ def parse_args(argv=None):
                     help="bf16 weights with an exact fp32 master stored split (low halves + bf16 moments as optimizer state)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: cut the model (the result is not a valid bench)")
     ap.add_argument("--kernels", default=None, help="kernel lane override (e.g. baseline)")
+    ap.add_argument("--linear-precision", default="bf16", choices=["bf16", "fp8"],
+                    help="fp8: e4m3 forward projections (an extra data point; the headline metric is the bf16 run)")
     ap.add_argument("--no-profile", action="store_true", help="plan from roofline seeds instead of measured task costs")
     ap.add_argument("--parallel", default=None, help="fsdp | zero3 | zero1 (default: fsdp when --gpus > 1)")
     return ap.parse_args(argv)
@@ -123,6 +125,8 @@ def bench_ours(a) -> dict:
         groups = {"dp": make_dp_group(rank, world, local)}
         lower_kwargs = zero_lower_kwargs(parallel, rank, world)
     hyper = {"lr": 3e-4, "weight_decay": 0.1, "beta1": 0.9, "beta2": 0.95}
+    if a.linear_precision != "bf16":
+        hyper["linear_precision"] = a.linear_precision
     from dataflow_b200.lowering import resolve_hardware
     hw = resolve_hardware(None).shared(world)        # all ranks of the node stream through one host memory
     tr = Trainer(a.family, cfg, budget_gib=budget, device=local, hyper=hyper, seed=0, kernel_set=a.kernels, hw=hw,
@@ -171,7 +175,8 @@ def bench_ours(a) -> dict:
     out = {
         "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
         "warmup": a.warmup, "ms_per_step": dev_s / a.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16" if a.linear_precision == "bf16" else "bf16 (fp8 forward projections)",
+        "data": "synthetic", "impl": "ours",
         "config": {"model": a.preset + (f"-cut{a.layers}L" if a.layers else ""), "global_batch": tokens_step * world // a.seq_len,
                    "seq_len": a.seq_len, "tokens_per_step": tokens_step * world,
                    "parallelism": parallel if world > 1 else "solo", "fast_budget_gib": budget,
