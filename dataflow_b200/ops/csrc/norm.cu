@@ -201,6 +201,86 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const bf16* __restrict__ 
   }
 }
 
+// RMSNorm backward for rows that fit the block's registers (cols = 2048 * VPT): every row is read from memory once —
+// the next row's x / dy / addend are requested before the current row's reduction, so the loads overlap the block-wide
+// sum — and the arithmetic (per-thread order of the row sum, the dx and dw expressions) is the generic kernel's.
+template <int VPT>
+__global__ void __launch_bounds__(256, VPT <= 2 ? 2 : 1) rmsnorm_bwd_regs_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                                   bf16* __restrict__ dx, const bf16* __restrict__ dx_add,
+                                                                   float* __restrict__ partial, int rows, int cols) {
+  __shared__ float scratch[33];
+  const int tid = threadIdx.x;
+  bf16x8 wv[VPT];                       // the weight strip stays packed; it is unpacked where it is used
+  float dwacc[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    wv[j] = ld8(w + (tid + j * 256) * 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  }
+  bf16x8 nx[VPT], nd[VPT], na[VPT];
+  int row = blockIdx.x;
+  if (row < rows) {
+    size_t off = static_cast<size_t>(row) * cols;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      nx[j] = ld8(x + off + (tid + j * 256) * 8);
+      nd[j] = ld8(dy + off + (tid + j * 256) * 8);
+      if (dx_add) na[j] = ld8(dx_add + off + (tid + j * 256) * 8);
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
+    bf16x8 cx[VPT], cd[VPT], ca[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) { cx[j] = nx[j]; cd[j] = nd[j]; ca[j] = na[j]; }
+    float r = rstd[row];
+    int nrow = row + gridDim.x;
+    if (nrow < rows) {
+      size_t off = static_cast<size_t>(nrow) * cols;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        nx[j] = ld8(x + off + (tid + j * 256) * 8);
+        nd[j] = ld8(dy + off + (tid + j * 256) * 8);
+        if (dx_add) na[j] = ld8(dx_add + off + (tid + j * 256) * 8);
+      }
+    }
+    float c1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      float fx[8], fd[8], fw[8];
+      unpack8(cx[j], fx);
+      unpack8(cd[j], fd);
+      unpack8(wv[j], fw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) c1 += fd[i] * fw[i] * fx[i] * r;
+    }
+    c1 = block_sum(c1, scratch) / cols;
+    bf16* dxr = dx + static_cast<size_t>(row) * cols;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      float fx[8], fd[8], fa[8], fw[8], o[8];
+      unpack8(cx[j], fx);
+      unpack8(cd[j], fd);
+      unpack8(wv[j], fw);
+      if (dx_add) unpack8(ca[j], fa);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float xh = fx[i] * r;
+        o[i] = (fd[i] * fw[i] - xh * c1) * r;
+        if (dx_add) o[i] += fa[i];
+        dwacc[j][i] += fd[i] * fx[i] * r;
+      }
+      st8(dxr + (tid + j * 256) * 8, pack8(o));
+    }
+  }
+  float* pw = partial + static_cast<size_t>(blockIdx.x) * 2 * cols;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pw[(tid + j * 256) * 8 + i] = dwacc[j][i];
+}
+
 // Sum the per-CTA partials in index order; optionally accumulate into the existing gradient.
 __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int cols, bf16* __restrict__ dw,
                                         bf16* __restrict__ db, int accumulate) {
@@ -260,8 +340,18 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  void* dw, int dw_is_f32, int accumulate, float* partial, int rows, int cols, cudaStream_t s) {
   if (rows == 0) return;
   int parts = norm_bwd_parts(rows);
-  norm_bwd_kernel<false><<<parts, 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, nullptr, (bf16*)dx,
-                                               (const bf16*)dx_add, partial, rows, cols);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+                         reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dx_add)) & 15) == 0;
+#define DFB_RMS_BWD_REGS(V)                                                                                                  \
+  rmsnorm_bwd_regs_kernel<V><<<parts, 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (bf16*)dx,         \
+                                                   (const bf16*)dx_add, partial, rows, cols)
+  if (aligned && cols == 2048) DFB_RMS_BWD_REGS(1);
+  else if (aligned && cols == 4096) DFB_RMS_BWD_REGS(2);
+  else if (aligned && cols == 8192) DFB_RMS_BWD_REGS(4);
+  else
+    norm_bwd_kernel<false><<<parts, 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, nullptr, (bf16*)dx,
+                                                 (const bf16*)dx_add, partial, rows, cols);
+#undef DFB_RMS_BWD_REGS
   if (dw) {
     if (dw_is_f32) norm_bwd_reduce_f32_kernel<<<ceil_div(cols, 256), 256, 0, s>>>(partial, parts, cols, (float*)dw, nullptr, accumulate);
     else norm_bwd_reduce_kernel<<<ceil_div(cols, 256), 256, 0, s>>>(partial, parts, cols, (bf16*)dw, nullptr, accumulate);

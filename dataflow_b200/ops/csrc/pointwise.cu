@@ -35,10 +35,70 @@ __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ positi
   }
 }
 
+// The same rotation with 16-byte accesses: a thread takes 8 consecutive pairs (i, i + rot_dim/2) of HPT heads of one
+// token, so the 8 sines / cosines of its column strip are computed once per HPT heads.  Needs 16-byte aligned strips.
+template <int HPT>
+__global__ void rope_vec_kernel(bf16* __restrict__ x, const int* __restrict__ positions, int tokens, int heads,
+                                int rot_dim, long long row_stride, int head_stride, int col_base, float log2_theta,
+                                float sign) {
+  const int half = rot_dim >> 1, vecs = half >> 3, hgroups = heads / HPT;
+  const long long total = static_cast<long long>(tokens) * hgroups * vecs;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int iv = static_cast<int>(idx % vecs);
+    const long long th = idx / vecs;
+    const int hg = static_cast<int>(th % hgroups);
+    const int t = static_cast<int>(th / hgroups);
+    bf16* p = x + t * row_stride + static_cast<long long>(hg * HPT) * head_stride + col_base + iv * 8;
+    bf16x8 lo[HPT], hi[HPT];
+#pragma unroll
+    for (int h = 0; h < HPT; ++h) {
+      lo[h] = ld8(p + static_cast<long long>(h) * head_stride);
+      hi[h] = ld8(p + static_cast<long long>(h) * head_stride + half);
+    }
+    const float pos = static_cast<float>(positions[t]);
+    float sn[8], cs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int i = iv * 8 + j;
+      float inv_freq = exp2f(-log2_theta * (2.0f * i / rot_dim));
+      sincosf(pos * inv_freq, &sn[j], &cs[j]);
+      sn[j] *= sign;
+    }
+#pragma unroll
+    for (int h = 0; h < HPT; ++h) {
+      float a[8], b[8], oa[8], ob[8];
+      unpack8(lo[h], a);
+      unpack8(hi[h], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        oa[j] = a[j] * cs[j] - b[j] * sn[j];
+        ob[j] = b[j] * cs[j] + a[j] * sn[j];
+      }
+      st8(p + static_cast<long long>(h) * head_stride, pack8(oa));
+      st8(p + static_cast<long long>(h) * head_stride + half, pack8(ob));
+    }
+  }
+}
+
 void rope_inplace(void* x, const int* positions, int tokens, int heads, int rot_dim, long long row_stride,
                   int head_stride, int col_base, float theta, int backward, cudaStream_t s) {
   long long total = static_cast<long long>(tokens) * heads * (rot_dim / 2);
   if (total == 0) return;
+  const int half = rot_dim / 2;
+  if (half % 8 == 0 && row_stride % 8 == 0 && head_stride % 8 == 0 && col_base % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int hpt = heads % 4 == 0 ? 4 : 1;
+    long long work = static_cast<long long>(tokens) * (heads / hpt) * (half / 8);
+    int vblocks = static_cast<int>(std::min<long long>((work + 255) / 256, 148 * 32));
+    if (hpt == 4)
+      rope_vec_kernel<4><<<vblocks, 256, 0, s>>>((bf16*)x, positions, tokens, heads, rot_dim, row_stride, head_stride, col_base,
+                                                 log2f(theta), backward ? -1.f : 1.f);
+    else
+      rope_vec_kernel<1><<<vblocks, 256, 0, s>>>((bf16*)x, positions, tokens, heads, rot_dim, row_stride, head_stride, col_base,
+                                                 log2f(theta), backward ? -1.f : 1.f);
+    return;
+  }
   int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
   rope_kernel<<<blocks, 256, 0, s>>>((bf16*)x, positions, tokens, heads, rot_dim, row_stride, head_stride, col_base,
                                      log2f(theta), backward ? -1.f : 1.f);

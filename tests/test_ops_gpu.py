@@ -27,7 +27,7 @@ def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("rows,cols", [(7, 64), (300, 4096), (1000, 768), (33, 200)])
+@pytest.mark.parametrize("rows,cols", [(7, 64), (300, 4096), (1000, 768), (33, 200), (700, 2048), (310, 8192), (5000, 4096)])
 def test_rmsnorm_fwd_bwd(K, rows, cols):
     torch.manual_seed(0)
     x, w, dy, add = bf(rows, cols), bf(cols) + 1, bf(rows, cols), bf(rows, cols)
@@ -70,6 +70,16 @@ def test_rope_strided_and_inverse(K):
     eager.rope_fwd(ref[:, :hq * hd].unflatten(1, (hq, hd)), pos, 500000.0)
     assert rel(qkv, ref) < 5e-3
     assert torch.equal(qkv[:, hq * hd:].float(), ref[:, hq * hd:])        # untouched columns
+    k = qkv[:, hq * hd:(hq + hkv) * hd].unflatten(1, (hkv, hd))             # two heads: one head per thread
+    K.rope_fwd(k, pos, 500000.0)
+    eager.rope_fwd(ref[:, hq * hd:(hq + hkv) * hd].unflatten(1, (hkv, hd)), pos, 500000.0)
+    assert rel(qkv, ref) < 5e-3
+    assert torch.equal(qkv[:, (hq + hkv) * hd:].float(), ref[:, (hq + hkv) * hd:])
+    z = bf(t, 3, 20)                                                          # pairs too short for 16-byte accesses
+    zr = z.float().clone()
+    K.rope_fwd(z, pos, 10000.0)
+    eager.rope_fwd(zr, pos, 10000.0)
+    assert rel(z, zr) < 5e-3
     orig = bf(t, hq, hd)
     x = orig.clone()
     K.rope_fwd(x, pos, 10000.0)
@@ -91,6 +101,8 @@ def test_swiglu_gelu_add(K):
     assert rel(s, eager.swiglu_packed_fwd(h13)) < 2e-3
     d = K.swiglu_packed_bwd(ds, h13)
     assert rel(d, eager.swiglu_packed_bwd(ds.float(), h13.float())) < 5e-3
+    big = bf(2048, 2 * 8192)                                                  # more vectors than one pass of the grid holds
+    assert rel(K.swiglu_packed_fwd(big), eager.swiglu_packed_fwd(big)) < 2e-3
     x, dy = bf(rows, F), bf(rows, F)
     assert rel(K.gelu_fwd_out(x), eager.gelu_fwd_out(x.float())) < 5e-3
     assert rel(K.gelu_bwd(dy, x), eager.gelu_bwd(dy.float(), x.float())) < 5e-3
