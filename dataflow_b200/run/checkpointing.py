@@ -61,7 +61,7 @@ def _world(trainer) -> tuple[int, int]:
     z = trainer.zero or {}
     if z:
         return int(z.get("rank", 0)), int(z.get("world", 1))
-    for key in ("tp", "ep"):                       # tensor / expert parallel jobs: the group knows the rank
+    for key in ("tp", "ep", "dp"):                 # tensor / expert parallel jobs and plain replicas: the group knows the rank
         g = (getattr(trainer, "groups", None) or {}).get(key)
         if g is not None:
             return int(g.rank), int(g.world)
@@ -121,6 +121,15 @@ class TrainerSource:
                 out.append(SourceSlice(oid, 0, size, oid, 0))
         return out
 
+    def write_slices(self, redundancy: int | None = None) -> list[SourceSlice]:
+        """What this rank writes at a save.  Objects every rank holds in full (replicas: their logical id is the object
+        id) are written by the first ``redundancy`` ranks only; ``None`` = by every rank, which lets the composer check
+        all replicas against each other for drift."""
+        out = self.slices()
+        if redundancy and self.world > 1 and self.rank >= int(redundancy):
+            out = [s for s in out if s.logical_id != s.object_id]
+        return out
+
     def resident_objects(self) -> dict[str, int]:
         return self.persistent()
 
@@ -146,8 +155,10 @@ class TrainerSource:
 
 
 def save_checkpoint(trainer, root: str, step: int, *, seed: int = 0, client_payload: Any = None, summary: Any = None,
-                    launch: Any = None, keep_last: int | None = None, scheme: Mapping[str, Any] | None = None) -> str:
-    """Every rank of the job calls this at the same step.  Returns the step directory."""
+                    launch: Any = None, keep_last: int | None = None, scheme: Mapping[str, Any] | None = None,
+                    redundancy: int | None = None) -> str:
+    """Every rank of the job calls this at the same step.  Returns the step directory.  ``redundancy``: how many ranks
+    write their copy of the replicated objects (default: all of them)."""
     src = TrainerSource(trainer)
     sdir = step_dir(root, step)
     rank, world = src.rank, src.world
@@ -159,10 +170,11 @@ def save_checkpoint(trainer, root: str, step: int, *, seed: int = 0, client_payl
                            launch=launch)
     else:
         import torch.distributed as dist
+        wr = src.write_slices(redundancy)
         manifest = src.start_snapshot(os.path.join(sdir, f"rank{rank}"),
-                                      [{"id": s.object_id, "offset": s.offset, "size": s.size} for s in src.slices()],
+                                      [{"id": s.object_id, "offset": s.offset, "size": s.size} for s in wr],
                                       {"step": step, "source": src.name})
-        mine = {"name": src.name, "slices": [vars(s) for s in src.slices()], "resident": src.resident_objects(),
+        mine = {"name": src.name, "slices": [vars(s) for s in wr], "resident": src.resident_objects(),
                 "hashes": {f"{e['as']}@{e['offset']}": e["hash"] for e in manifest["slices"]}, "spec": src.engine_spec(),
                 "logical": src.logical_objects()}
         gathered: list[Any] = [None] * world
@@ -174,7 +186,8 @@ def save_checkpoint(trainer, root: str, step: int, *, seed: int = 0, client_payl
                 for k, v in g["logical"].items():
                     logical[k] = max(logical.get(k, 0), int(v))
             compose_checkpoint(sources, sdir, step=step, seed=seed, logical_objects=logical,
-                               scheme={"world": world, "zero": trainer.zero, "parallel": _private_scheme(trainer), **dict(scheme or {})},
+                               scheme={"world": world, "zero": trainer.zero, "parallel": _private_scheme(trainer),
+                                       "replica_copies": min(int(redundancy), world) if redundancy else world, **dict(scheme or {})},
                                client_payload=client_payload, summary=summary, launch=launch)
         dist.barrier()
     if keep_last and rank == 0:

@@ -45,8 +45,17 @@ class RunSpec:
     checkpoint_every: int = 0
     checkpoint_dir: str | None = None
     checkpoint_keep_last: int | None = None
+    checkpoint_redundancy: int | None = None   # ranks that write their copy of replicated objects (default: all)
     resume: str | None = None
     out: str | None = None
+    devices: list[int] | None = None        # CUDA ordinal of every rank (from a topology group); default: rank r on device r
+    backend: str = "auto"                   # auto | peer (kernels over peer memory) | nccl (library collectives around library ops)
+    backing_budget_gib: float | None = None # refuse the run when its pinned host store would exceed this
+    prof_dir: str | None = None             # per-step engine traces of the steps in the window land here
+    profile_start_before_step: int = 0      # 1-indexed; 0 = no window
+    profile_stop_after_step: int = 0
+    warm_profiles: bool = False             # measure and cache the task costs, then stop
+    refresh_profiles: bool = False          # ignore cached task costs
     argv: list[str] = dataclasses.field(default_factory=list)
 
     def to_json(self) -> str:

@@ -83,7 +83,8 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                start_step: int = 0, losses: list[float] | None = None, checkpoint_every: int = 0,
                checkpoint_dir: str | None = None, keep_last: int | None = None, seed: int = 0,
                launch: Mapping[str, Any] | None = None, log: Callable[[str], None] | None = print,
-               on_step: Callable[[int, float, Any], None] | None = None, rank_rounds: list[int] | None = None) -> RunResult:
+               on_step: Callable[[int, float, Any], None] | None = None, rank_rounds: list[int] | None = None,
+               window=None, checkpoint_redundancy: int | None = None) -> RunResult:
     """Run optimizer steps ``start_step + 1 .. steps``.  ``factory(cursor)`` builds the data stepper; its packed
     steps must hold ``trainer.rounds x world`` rounds of ``trainer.T`` tokens."""
     from .checkpointing import save_checkpoint
@@ -115,6 +116,8 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                 break
             if len(packed.rounds) != job_rounds:
                 raise ValueError(f"packed step has {len(packed.rounds)} rounds, the job consumes {job_rounds}")
+            if window:
+                window.before(s + 1, trainer)
             t0 = time.perf_counter()
             _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds, row_shard, first_round)
             total_valid = packed.valid_rows          # every rank packed the whole job's step: no exchange needed
@@ -125,6 +128,8 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                 dist.all_reduce(t)
                 loss = float(t[0])
             dt = time.perf_counter() - t0
+            if window:
+                window.after(s + 1, trainer)
             res.losses.append(loss)
             res.step_wall_s.append(dt)
             content_total += packed.content_tokens
@@ -135,6 +140,7 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
                 on_step(s + 1, loss, packed)
             if checkpoint_every and checkpoint_dir and (s + 1) % checkpoint_every == 0:
                 save_checkpoint(trainer, checkpoint_dir, s + 1, seed=seed, keep_last=keep_last, launch=launch,
+                                redundancy=checkpoint_redundancy,
                                 client_payload={"losses": res.losses, "cursor": dict(packed.cursor_after)},
                                 summary={"last_loss": loss, "steps_recorded": len(res.losses)})
     finally:

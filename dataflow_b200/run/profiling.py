@@ -68,7 +68,7 @@ def profile_program(trainer, program: Program | None = None, *, steps: int = 3, 
     cfg = trainer.cfg
     key = profile_key(trainer, cfg)
     path = _cache_path(key)
-    if use_cache and path.exists():
+    if use_cache and path.exists() and os.environ.get("DATAFLOW_PROFILE_REFRESH") != "1":
         return json.loads(path.read_text())
     out: dict[str, list[float]] = {}
     for levels in (None, {0: 1}, {0: 2}):
@@ -91,3 +91,48 @@ def profile_program(trainer, program: Program | None = None, *, steps: int = 3, 
     if use_cache:
         path.write_text(json.dumps(med, indent=1))
     return med
+
+
+class ProfileWindow:
+    """Steps ``start .. stop`` (1-indexed, inclusive) of a run under observation: the CUDA profiler API is switched on before
+    step ``start`` and off after step ``stop`` (an external profiler attached with capture-range = profiler API sees exactly
+    those steps), and each step's engine trace — every task and copy with its start and end — is written beside a summary
+    to ``<dir>/step_<n>.rank<r>.json``.  Reference role: ``--profile-start-before-step`` / ``--profile-stop-after-step`` /
+    ``--prof-dir`` of ``tools/train/train.py:408-457``."""
+
+    def __init__(self, directory: str | None, start: int, stop: int, rank: int = 0):
+        self.dir, self.start, self.stop, self.rank = directory, int(start), int(stop or start), int(rank)
+        self.active = False
+        self.written: list[str] = []
+
+    def __bool__(self):
+        return self.start > 0
+
+    def before(self, step: int, trainer) -> None:
+        if step == self.start and not self.active:
+            self.active = True
+            if trainer.device is not None:
+                import torch
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+
+    def after(self, step: int, trainer) -> None:
+        if not self.active:
+            return
+        if self.dir:
+            from ..runtime import trace_to_dict
+            from .trace_report import summarize_trace
+            os.makedirs(self.dir, exist_ok=True)
+            res = trainer.last_result
+            path = os.path.join(self.dir, f"step_{step:06d}.rank{self.rank}.json")
+            with open(path, "w") as f:
+                json.dump({"step": step, "rank": self.rank, "predicted_makespan_us": trainer.planned.makespan_us,
+                           "measured_makespan_us": res.makespan_us, "summary": summarize_trace(trainer.program, res),
+                           "trace": trace_to_dict(res.trace)}, f)
+            self.written.append(path)
+        if step >= self.stop:
+            self.active = False
+            if trainer.device is not None:
+                import torch
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()

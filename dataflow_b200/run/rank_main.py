@@ -32,8 +32,17 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     world = int(os.environ.get("WORLD_SIZE", 1)) if spec.world > 1 else 1
     local = int(os.environ.get("LOCAL_RANK", 0))
     device = None if spec.device is None else (local if world > 1 else spec.device)
+    if device is not None and spec.devices:
+        if len(spec.devices) != max(world, 1):
+            raise ValueError(f"{len(spec.devices)} devices named for a job of {world} ranks")
+        device = int(spec.devices[local])
     groups: dict[str, Any] = {}
     lower_kwargs: dict[str, Any] = {}
+    if spec.backend not in ("auto", "peer", "nccl"):
+        raise ValueError(f"--backend is auto, peer or nccl, not {spec.backend!r}")
+    lane = "collective" if spec.backend == "nccl" else ("p2p" if spec.backend == "peer" else None)
+    if spec.refresh_profiles:
+        os.environ["DATAFLOW_PROFILE_REFRESH"] = "1"
     if world > 1:
         import torch
         import torch.distributed as dist
@@ -48,7 +57,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         if spec.parallel not in ("tp", "ep"):
             from ..parallel.zero import make_dp_group, zero_lower_kwargs
             # plain data parallelism needs no peer-mapped slab: its one collective per optimizer task is a library all-reduce
-            groups = {"dp": make_dp_group(rank, world, device, "collective" if spec.parallel in ("co", "dp") else None)}
+            groups = {"dp": make_dp_group(rank, world, device, "collective" if spec.parallel in ("co", "dp") else lane)}
             lower_kwargs = zero_lower_kwargs(spec.parallel, rank, world)
             if spec.parallel in ("co", "dp") and spec.resident_params and device is not None:
                 lower_kwargs = {"resident_params": True}
@@ -68,7 +77,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         family, cfg = "tp_mlp", dataclasses.replace(cfg, tp=world, family="tp_mlp")
         from ..models.families import resolve_family
         d = resolve_family(family).derive_dims(cfg)
-        groups = {"tp": TpGroup(rank, world, device, max_rows=d.Ts, max_k=d.d, max_n=d.d)}
+        groups = {"tp": TpGroup(rank, world, device, max_rows=d.Ts, max_k=d.d, max_n=d.d, lane=lane)}
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
         data_world = 1
     elif world > 1 and spec.parallel == "ep":
@@ -79,13 +88,26 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         d = resolve_family(family).derive_dims(cfg)
         if not getattr(d, "moe", False):
             raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} is dense")
-        groups = {"ep": EpGroup(rank, world, device, tokens=d.T, d_model=d.d, n_experts=d.E, top_k=d.topk, capacity_factor=cfg.ep_capacity)}
+        groups = {"ep": EpGroup(rank, world, device, tokens=d.T, d_model=d.d, n_experts=d.E, top_k=d.topk, capacity_factor=cfg.ep_capacity,
+                                lane=lane)}
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
     recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
     say = log if rank == 0 else (lambda *a, **k: None)
     tr = Trainer(family, cfg, budget_gib=spec.budget_gib, device=device, hyper=recipe.hyper(), seed=spec.seed,
                  kernel_set=spec.kernels, recompute=spec.recompute, profile=spec.profile and device is not None,
                  groups=groups, lower_kwargs=lower_kwargs or None)
+    if spec.backing_budget_gib is not None and tr.store.total > spec.backing_budget_gib * 2 ** 30:
+        need = tr.store.total / 2 ** 30
+        tr.close()
+        raise ValueError(f"the run's host store needs {need:.2f} GiB of pinned memory, --backing-budget allows {spec.backing_budget_gib:g}")
+    if spec.warm_profiles:
+        say(f"task costs measured and cached ({tr.program.metadata.get('costs', 'roofline seeds')}); --warm-profiles stops here")
+        tr.close()
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        from .driver import RunResult
+        return RunResult(losses=[], tokens_per_step=tr.T * tr.rounds * world, meta={"warm_profiles": True})
     say(f"plan: {tr.planned.policy}, predicted {tr.planned.makespan_us / 1e3:.1f} ms/step, peak fast "
         f"{tr.planned.peak_fast_bytes / 2 ** 30:.2f} GiB, planned in {tr.plan_s:.1f} s")
     # the job-wide pipeline: every rank packs all rounds of the step and keeps its own
@@ -106,17 +128,21 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     launch = {"argv": spec.argv, "resolved": {"preset": spec.preset, "seed": spec.seed, "world": world,
                                               "parallel": spec.parallel if world > 1 else "solo", **spec.overrides},
               "data": factory.describe(), "env": _env_facts()}
+    from .profiling import ProfileWindow
+    window = ProfileWindow(spec.prof_dir, spec.profile_start_before_step, spec.profile_stop_after_step, rank)
     try:
         res = train_loop(tr, factory, spec.steps, cursor=cursor, start_step=start, losses=losses, rank_rounds=spec.rounds,
-                         on_step=_host_fault_plan(rank),
+                         on_step=_host_fault_plan(rank), window=window,
                          checkpoint_every=spec.checkpoint_every, checkpoint_dir=spec.checkpoint_dir,
-                         keep_last=spec.checkpoint_keep_last, seed=spec.seed, launch=launch, log=say)
+                         keep_last=spec.checkpoint_keep_last, checkpoint_redundancy=spec.checkpoint_redundancy, seed=spec.seed, launch=launch, log=say)
     finally:
         tr.close()
         if world > 1:
             import torch.distributed as dist
             dist.destroy_process_group()
     res.meta["launch"] = launch
+    if window.written:
+        res.meta["traces"] = list(window.written)
     if spec.out and rank == 0:
         res.save(spec.out)
     return res

@@ -45,6 +45,17 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
                     help="how --gpus N ranks split the job: fsdp / zero3 / zero1 shard parameters and optimizer state over data-parallel "
                          "ranks; co = plain data parallelism (replicas, gradients all-reduced); tp = tensor + sequence parallel llama "
                          "blocks; ep = experts split over the ranks (MoE presets)")
+    ap.add_argument("--topology", default=None, help="topology file (TOML: [hosts.*], [groups.*]); with --group it names the ranks' devices")
+    ap.add_argument("--group", default=None, help="group of the topology to run on (default: its only group)")
+    ap.add_argument("--tp-mlp", action="store_true", help="same as --parallel tp (the reference's flag name)")
+    ap.add_argument("--backend", default="auto", choices=["auto", "peer", "nccl"],
+                    help="how the ranks exchange data: peer = kernels over peer memory (default on GPUs), nccl = library collectives")
+    ap.add_argument("--backing-budget", type=float, default=None, help="pinned host memory the run may use, GiB")
+    ap.add_argument("--prof-dir", default=None, help="write the engine trace of every step of the profile window here")
+    ap.add_argument("--profile-start-before-step", type=int, default=0, help="first step (1-indexed) of the profile window")
+    ap.add_argument("--profile-stop-after-step", type=int, default=0, help="last step of the profile window")
+    ap.add_argument("--warm-profiles", action="store_true", help="measure and cache the task costs, then stop")
+    ap.add_argument("--refresh-profiles", action="store_true", help="measure task costs again even if cached")
     ap.add_argument("--rounds", default=None, help="weighted data parallelism with --parallel co: rounds per rank, e.g. 6,2")
     ap.add_argument("--kernels", default=None, help="kernel lane: sm100 | baseline | eager")
     ap.add_argument("--profile", action="store_true", help="plan from measured task costs")
@@ -53,6 +64,8 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--checkpoint-every", type=int, default=0)
     ap.add_argument("--checkpoint-dir", default=None)
     ap.add_argument("--checkpoint-keep-last", type=int, default=None)
+    ap.add_argument("--checkpoint-redundancy", type=int, default=None,
+                    help="how many ranks write their copy of replicated objects (default: all, which also checks them for drift)")
     ap.add_argument("--resume", default=None, help="step directory, checkpoint root, or 'latest'")
     ap.add_argument("--data", default=None, help="scheme:main[,k=v...] (synthetic | shards | jsonl | txt | parquet | capture)")
     ap.add_argument("--packing-policy", default="ffd", choices=["ffd", "greedy"])
@@ -61,8 +74,25 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--out", default=None, help="write the run curve JSON here")
 
 
+def ranks_from_topology(path: str, group: str | None):
+    """(world, CUDA ordinal of every rank, backend) of a topology group.  One job runs on ONE box here (the ranks talk through
+    peer memory and NCCL over NVLink), so every member must sit on a local host."""
+    from dataflow_b200.distributed.topology import load_topology
+    topo = load_topology(path)
+    g = topo.group(group)
+    far = [m.key for m in g.members if not topo.host_of(m).local]
+    if far:
+        raise SystemExit(f"group {g.name!r} names remote members {far}: a job spans one box (cross-box lanes are not built)")
+    return g.world, [int(m.device) for m in g.members], g.backend
+
+
 def spec_from_args(a, argv):
     from dataflow_b200.run.conductor import RunSpec
+    devices = None
+    if a.topology:
+        a.gpus, devices, backend = ranks_from_topology(a.topology, a.group)
+        if a.backend == "auto" and backend in ("peer", "nccl"):
+            a.backend = backend
     ov = {}
     for flag, fieldname in (("ga_rounds", "grad_accum_rounds"), ("batch", "batch"), ("max_seq_len", "seq_len"),
                             ("layers", "n_layers"), ("dtype_policy", "dtype_policy"), ("opt", "optimizer")):
@@ -79,10 +109,13 @@ def spec_from_args(a, argv):
         recipe["optimizer"] = a.opt
     return RunSpec(preset=a.preset, steps=a.steps, overrides=ov, recipe=recipe, data=a.data, packing_policy=a.packing_policy,
                    allow_round_split=a.allow_round_split, capture=a.capture, budget_gib=a.fast_budget,
-                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel=a.opt_shard, rounds=[int(x) for x in a.rounds.split(",")] if a.rounds else None, seed=a.seed,
-                   profile=a.profile, recompute=not a.no_recompute, kernels=a.kernels,
+                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel="tp" if a.tp_mlp else a.opt_shard, rounds=[int(x) for x in a.rounds.split(",")] if a.rounds else None, seed=a.seed,
+                   profile=a.profile or a.warm_profiles or a.refresh_profiles, recompute=not a.no_recompute, kernels=a.kernels,
+                   backend=a.backend, devices=devices, backing_budget_gib=a.backing_budget, prof_dir=a.prof_dir,
+                   profile_start_before_step=a.profile_start_before_step, profile_stop_after_step=a.profile_stop_after_step,
+                   warm_profiles=a.warm_profiles, refresh_profiles=a.refresh_profiles,
                    resident_params=not a.no_resident_params, checkpoint_every=a.checkpoint_every,
-                   checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, resume=a.resume, out=a.out,
+                   checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, checkpoint_redundancy=a.checkpoint_redundancy, resume=a.resume, out=a.out,
                    argv=list(argv))
 
 
