@@ -22,6 +22,7 @@ def test_predict_step_grid_and_infeasible_rows(capsys, tmp_path):
     assert tool("bench/predict_step.py").main(["--preset", "llama3:tiny", "--budget", "0.0001,0.02,1", "--top", "2", "--json", str(out)]) == 0
     rows = json.loads(out.read_text())
     assert "INFEASIBLE" in rows[0]["note"] and rows[1]["tok_s"] > 0 and rows[2]["fast_gib"] <= 1
+    assert rows[1]["link_gb"] > 0 and rows[1]["link_pct"] > 0            # the tight budget streams through the host link
     assert "most expensive tasks" in capsys.readouterr().out
 
 

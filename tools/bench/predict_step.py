@@ -44,7 +44,7 @@ def predict_cell(fam, cfg, budget_gib, hw, recompute=True, measured=None):
     h2d = sum(iv.end - iv.start for iv in log.transfer_intervals("from_slow"))
     d2h = sum(iv.end - iv.start for iv in log.transfer_intervals("to_slow"))
     sizes = planned.program.object_sizes()
-    moved = sum(sizes.get(iv.task_id, 0) for iv in log.transfer_intervals())
+    moved = sum(sizes.get(iv.task_id.split(":", 1)[-1], 0) for iv in log.transfer_intervals())
     row.update(s_step=planned.makespan_us / 1e6, tok_s=tokens / planned.makespan_us * 1e6, eff_tf=fr["effective_tflops"],
                hw_tf=fr["hardware_tflops"], fast_gib=planned.peak_fast_bytes / 2 ** 30, backing_gib=planned.peak_backing_bytes / 2 ** 30,
                link_gb=moved / 1e9, link_pct=100.0 * max(h2d, d2h) / planned.makespan_us, recomp_pct=100.0 * rec / max(busy, 1e-9),
