@@ -342,12 +342,11 @@ class BlockBwd(_Block):
     def bwd_mlp(self, a, w, g, dy, acc, wgrad):
         K = self.K
         h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
-        s = K.swiglu_packed_fwd(a["h13"])
-        wgrad("w2", s, dy)
         ds = K.linear_dgrad_bf16(dy, w["w2"])
-        del s
-        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
+        dh13, s = K.swiglu_packed_bwd(ds, a["h13"], with_s=True)      # one pass over h13 gives dh13 and the product s
         del ds
+        wgrad("w2", s, dy)
+        del s
         wgrad("w13", h2, dh13)
         dh2 = K.linear_dgrad_bf16(dh13, w["w13"])
         del dh13, h2

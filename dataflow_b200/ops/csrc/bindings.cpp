@@ -84,9 +84,15 @@ static void swiglu_fwd(const Tensor& x1, const Tensor& x3, Tensor& out, int64_t 
   dfb::swiglu_fwd(x1.data_ptr(), x3.data_ptr(), out.data_ptr(), rows, (int)F, ld1, ld3, cur_stream());
 }
 static void swiglu_bwd(const Tensor& ds, const Tensor& x1, const Tensor& x3, Tensor& dx1, Tensor& dx3, int64_t rows,
-                       int64_t F, int64_t ld1, int64_t ld3, int64_t ldd1, int64_t ldd3) {
+                       int64_t F, int64_t ld1, int64_t ld3, int64_t ldd1, int64_t ldd3, c10::optional<Tensor> s_out) {
   TORCH_CHECK(F % 8 == 0, "swiglu: F must be a multiple of 8");
-  dfb::swiglu_bwd(ds.data_ptr(), x1.data_ptr(), x3.data_ptr(), dx1.data_ptr(), dx3.data_ptr(), rows, (int)F, ld1, ld3, ldd1,
+  void* sp = nullptr;
+  if (s_out.has_value()) {
+    CHECK_BF16(s_out.value());
+    TORCH_CHECK(s_out->is_contiguous() && s_out->numel() == rows * F, "swiglu_bwd: s_out is a contiguous (rows, F) bf16 tensor");
+    sp = s_out->data_ptr();
+  }
+  dfb::swiglu_bwd(ds.data_ptr(), x1.data_ptr(), x3.data_ptr(), dx1.data_ptr(), dx3.data_ptr(), sp, rows, (int)F, ld1, ld3, ldd1,
                   ldd3, cur_stream());
 }
 static void gelu_fwd(const Tensor& x, Tensor& y) { TORCH_CHECK(x.numel() % 8 == 0); dfb::gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), cur_stream()); }

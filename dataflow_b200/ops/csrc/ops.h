@@ -24,7 +24,7 @@ void layernorm_bwd(const void* dy, const void* x, const void* w, const float* me
 void rope_inplace(void* x, const int* positions, int tokens, int heads, int rot_dim, long long row_stride,
                   int head_stride, int col_base, float theta, int backward, cudaStream_t s);
 void swiglu_fwd(const void* x1, const void* x3, void* out, long long rows, int F, long long ld1, long long ld3, cudaStream_t s);
-void swiglu_bwd(const void* ds, const void* x1, const void* x3, void* dx1, void* dx3, long long rows, int F,
+void swiglu_bwd(const void* ds, const void* x1, const void* x3, void* dx1, void* dx3, void* s_out, long long rows, int F,
                 long long ld1, long long ld3, long long ldd1, long long ldd3, cudaStream_t s);
 void gelu_fwd(const void* x, void* y, long long n, cudaStream_t s);
 void gelu_bwd(const void* dy, const void* x, void* dx, long long n, cudaStream_t s);

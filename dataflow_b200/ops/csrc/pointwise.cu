@@ -128,9 +128,11 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ a, const bf16* __rest
   }
 }
 
+// ``s_out`` (optional, rows x F): the forward product silu(x1) * x3 with the forward's rounding, for the caller that needs
+// it as a GEMM operand in the same backward (saves re-reading x1 / x3 in a separate forward launch).
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ ds, const bf16* __restrict__ a, const bf16* __restrict__ b,
-                                  bf16* __restrict__ da, bf16* __restrict__ db, long long rows, int F, long long lda,
-                                  long long ldb, long long ldda, long long lddb) {
+                                  bf16* __restrict__ da, bf16* __restrict__ db, bf16* __restrict__ s_out, long long rows,
+                                  int F, long long lda, long long ldb, long long ldda, long long lddb) {
   int vec_per_row = F >> 3;
   long long total = rows * vec_per_row;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -150,6 +152,11 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ ds, const bf16* __res
     }
     st8(da + r * ldda + v, pack8(o1));
     st8(db + r * lddb + v, pack8(o3));
+    if (s_out) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o1[i] = bf2f(f2bf(f1[i] * sigmoidf_(f1[i]))) * f3[i];
+      st8(s_out + r * F + v, pack8(o1));
+    }
   }
 }
 
@@ -160,11 +167,11 @@ void swiglu_fwd(const void* x1, const void* x3, void* out, long long rows, int F
   swiglu_fwd_kernel<<<ew_blocks(rows * (F / 8)), 256, 0, s>>>((const bf16*)x1, (const bf16*)x3, (bf16*)out, rows, F, ld1, ld3);
 }
 
-void swiglu_bwd(const void* ds, const void* x1, const void* x3, void* dx1, void* dx3, long long rows, int F,
+void swiglu_bwd(const void* ds, const void* x1, const void* x3, void* dx1, void* dx3, void* s_out, long long rows, int F,
                 long long ld1, long long ld3, long long ldd1, long long ldd3, cudaStream_t s) {
   if (rows == 0) return;
   swiglu_bwd_kernel<<<ew_blocks(rows * (F / 8)), 256, 0, s>>>((const bf16*)ds, (const bf16*)x1, (const bf16*)x3, (bf16*)dx1,
-                                                              (bf16*)dx3, rows, F, ld1, ld3, ldd1, ldd3);
+                                                              (bf16*)dx3, (bf16*)s_out, rows, F, ld1, ld3, ldd1, ldd3);
 }
 
 // ---------------------------------------------------------------------------- GELU (tanh form)

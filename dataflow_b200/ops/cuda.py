@@ -139,14 +139,14 @@ def swiglu_fwd_out(x1, x3, out=None):
 
 
 @reg("swiglu_bwd")
-def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None):
+def swiglu_bwd(ds, x1, x3, dx1=None, dx3=None, s_out=None):
     rows, F, ld1 = _rows_ld(x1)
     _, _, ld3 = _rows_ld(x3)
     if dx1 is None:
         dx1 = torch.empty(*x1.shape, dtype=x1.dtype, device=x1.device)
     if dx3 is None:
         dx3 = torch.empty(*x3.shape, dtype=x3.dtype, device=x3.device)
-    native().swiglu_bwd(ds, x1, x3, dx1, dx3, rows, F, ld1, ld3, _rows_ld(dx1)[2], _rows_ld(dx3)[2])
+    native().swiglu_bwd(ds, x1, x3, dx1, dx3, rows, F, ld1, ld3, _rows_ld(dx1)[2], _rows_ld(dx3)[2], s_out)
     return dx1, dx3
 
 
@@ -157,12 +157,15 @@ def swiglu_packed_fwd(h13, out=None):
 
 
 @reg("swiglu_packed_bwd")
-def swiglu_packed_bwd(ds, h13, dh13=None):
+def swiglu_packed_bwd(ds, h13, dh13=None, with_s=False):
+    """dh13 from ds; ``with_s``: also the forward product s = silu(x1) * x3 (the same bytes ``swiglu_packed_fwd`` gives),
+    written by the same launch."""
     F = h13.shape[-1] // 2
     if dh13 is None:
         dh13 = torch.empty_like(h13)
-    swiglu_bwd(ds, h13[..., :F], h13[..., F:], dh13[..., :F], dh13[..., F:])
-    return dh13
+    s = torch.empty(*h13.shape[:-1], F, dtype=h13.dtype, device=h13.device) if with_s else None
+    swiglu_bwd(ds, h13[..., :F], h13[..., F:], dh13[..., :F], dh13[..., F:], s)
+    return (dh13, s) if with_s else dh13
 
 
 @reg("gelu_fwd_out")

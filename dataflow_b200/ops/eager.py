@@ -252,12 +252,12 @@ def swiglu_packed_fwd(h13, out=None):
 
 
 @register("swiglu_packed_bwd", "eager")
-def swiglu_packed_bwd(ds, h13, dh13=None):
+def swiglu_packed_bwd(ds, h13, dh13=None, with_s=False):
     F = h13.shape[-1] // 2
     if dh13 is None:
         dh13 = torch.empty_like(h13)
     swiglu_bwd(ds, h13[..., :F], h13[..., F:], dh13[..., :F], dh13[..., F:])
-    return dh13
+    return (dh13, swiglu_packed_fwd(h13)) if with_s else dh13
 
 
 @register("gelu_fwd_out", "eager")

@@ -101,6 +101,8 @@ def test_swiglu_gelu_add(K):
     assert rel(s, eager.swiglu_packed_fwd(h13)) < 2e-3
     d = K.swiglu_packed_bwd(ds, h13)
     assert rel(d, eager.swiglu_packed_bwd(ds.float(), h13.float())) < 5e-3
+    d2, s2 = K.swiglu_packed_bwd(ds, h13, with_s=True)
+    assert torch.equal(d2, d) and torch.equal(s2, s)                          # the product rides along, same bytes as the forward
     big = bf(2048, 2 * 8192)                                                  # more vectors than one pass of the grid holds
     assert rel(K.swiglu_packed_fwd(big), eager.swiglu_packed_fwd(big)) < 2e-3
     x, dy = bf(rows, F), bf(rows, F)
