@@ -126,12 +126,11 @@ class TpBlockBwd(_TpBlock):
                 K.linear_wgrad_bf16(xin, dout, gr[name], accumulate=acc)
 
         # ---- MLP
-        s = K.swiglu_packed_fwd(a["h13"])
         ds = g.ag_gemm(dy, w["w2"], w_is_kn=False)                      # dy (all rows) x W2^T, gather fused
+        dh13, s = K.swiglu_packed_bwd(ds, a["h13"], with_s=True)        # one pass over h13: dh13 and the forward product
+        del ds
         wgrad("w2", s, g.last_gathered(d.Ts, d.d))
         del s
-        dh13 = K.swiglu_packed_bwd(ds, a["h13"])
-        del ds
         h2 = K.rmsnorm_apply(a["h_mid"], w["ffn_norm"], a["rstd_ffn"])
         wgrad("w13", g.all_gather(h2), dh13)
         del h2
