@@ -7,7 +7,8 @@
 
 Reference role: ``src/dataflow_sim/app/server/main.py:78-211`` (request models), ``:216,221,346,552`` (the four routes).
 ``GET /`` serves a single-page front end (``static/index.html``: inputs, summary, compute / copy timeline, device-memory
-curve, time by phase, planner comparison — plain JavaScript and SVG over the four routes; the reference's is a React app).
+curve, time by phase, work by phase, planner comparison, budget sweep, measured-run overlay from a trace file — plain JavaScript and SVG
+over the four routes; the reference's is a React app).
 """
 from __future__ import annotations
 

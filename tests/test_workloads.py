@@ -76,7 +76,7 @@ def test_http_api_preview_and_simulate():
     assert c.get("/api/health").json()["ok"]
     page = c.get("/")
     assert page.status_code == 200 and "text/html" in page.headers["content-type"]
-    for needle in ('id="timeline"', 'id="memory"', "/api/simulate", "/api/presets", 'id="compare"'):
+    for needle in ('id="timeline"', 'id="memory"', "/api/simulate", "/api/presets", 'id="compare"', 'id="sweep"', 'id="measured"', 'id="subops"'):
         assert needle in page.text
     presets = c.get("/api/presets").json()
     assert "B200" in presets["hardware"] and "llama3_8b" in presets["models"] and "pressurefit" in presets["policies"]
