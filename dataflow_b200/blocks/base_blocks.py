@@ -11,6 +11,8 @@ number.  Contract parity: reference ``src/dataflow_training/blocks/base_blocks.p
 """
 from __future__ import annotations
 
+import fnmatch
+
 import math
 from typing import Any, Mapping
 
@@ -204,9 +206,12 @@ class OptimizerStep(_Base):
         b1, b2 = hy.get("beta1", 0.9), hy.get("beta2", 0.95)
         eps, wd = hy.get("eps", 1e-8), hy.get("weight_decay", 0.0)
         rule = hy.get("optimizer", "adamw")
+        only = tuple(hy.get("train_only") or ())
         for f in wl.fields:
             if f.name not in g:
                 continue            # frozen field: no gradient storage, no update
+            if only and not any(fnmatch.fnmatchcase(f.name, pat) for pat in only):
+                continue            # the run updates a named subset of fields only (e.g. an indexer warm-up)
             wf, gf = w[f.name], g[f.name]
             f_wd = wd if (f.kind in ("matrix", "embedding") or hy.get("wd_all")) else 0.0
             if rule == "adamw" and f"{f.name}.mlo" in o:

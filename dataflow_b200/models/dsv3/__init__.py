@@ -50,6 +50,14 @@ class Dsv3Config:
     index_dim: int = 0
     index_topk: int = 0
     index_kl_coef: float = 0.0
+    # dense warm-up of the indexer (dsv32): attention stays DENSE, the indexer learns the full-prefix attention
+    # distribution through its KL term, and nothing but the indexer's fields is updated
+    dsa_warmup: bool = False
+
+    @property
+    def trainable_patterns(self) -> tuple[str, ...]:
+        """fnmatch patterns of the only fields the optimizer updates (empty: all of them)."""
+        return ("wi_*",) if self.dsa_warmup else ()
 
     def policy(self) -> DTypePolicy:
         return self.dtype_policy if isinstance(self.dtype_policy, DTypePolicy) else DTypePolicy.from_dict(self.dtype_policy)
@@ -98,7 +106,8 @@ def attention_part(c: Dsv3Config, x, w, seg):
     aux, mask = None, causal
     if c.index_topk:
         scores = F.dsa_index_scores(h.detach(), {k_: w[k_] for k_ in ("wi_q", "wi_k", "wi_w")}, c, pos)
-        mask = F.dsa_topk_mask(scores.detach(), causal, c.index_topk)
+        if not c.dsa_warmup:
+            mask = F.dsa_topk_mask(scores.detach(), causal, c.index_topk)
     o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
     if c.index_topk and c.index_kl_coef:
         aux = c.index_kl_coef * F.dsa_indexer_kl(scores, probs, mask) * n

@@ -2,8 +2,9 @@
 shared key, ReLU scores) ranks the visible keys of every query, attention runs over the ``index_topk`` best, and the
 indexer is trained by a KL term towards the attention distribution (gradient injected in the block backward; the
 attention side is a constant target).  Kinds ``dsadense`` / ``dsamoe``.
-Family parity: reference ``src/dataflow_training/model_families/dsv32/{blocks.py,model.py}``; the reference's dense
-warm-up mode (only the indexer trains) is the optimizer policy ``freeze(...)`` of every field but ``wi_*`` here.
+Dense warm-up (``dsa_warmup=True``, presets ``*_warmup``): attention stays dense, the indexer learns the full-prefix
+attention distribution through the same KL term and the optimizer updates nothing but the indexer's fields (``wi_*``).
+Family parity: reference ``src/dataflow_training/model_families/dsv32/{blocks.py,model.py}`` (warm-up variants :584-658).
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ def layer_kinds(c: Dsv3Config):
 BASE = dict(index_heads=2, index_dim=16, index_topk=32, index_kl_coef=0.1, family="dsv32")
 PRESETS = {
     "tiny": dict(name="tiny", **BASE),
+    "tiny_warmup": dict(name="tiny_warmup", dsa_warmup=True, **BASE),
     "dsv32_mini": dict(name="dsv32_mini", n_layers=6, n_dense=1, d_model=512, n_heads=8, q_lora=192, kv_lora=128, d_nope=64, d_rope=32, d_v=64,
                        d_ff=1408, n_experts=16, top_k=4, d_ff_expert=256, n_group=4, topk_group=2, vocab_size=32000, seq_len=1024, batch=4,
                        grad_accum_rounds=4, **{**BASE, "index_heads": 4, "index_dim": 32, "index_topk": 256}),

@@ -455,6 +455,9 @@ def sharded_optimizer_step(exe, ctx, wl, gl, ol, w, g, o) -> bool:
     shard = ctx.task.block_params.get("shard")
     if not shard:
         return False
+    if exe.hyper.get("train_only"):
+        raise NotImplementedError("a run that updates a named subset of fields (train_only) cannot shard its optimizer: "
+                                  "the sharded step works on flat slices of the packed object, not on fields")
     grp = _group(ctx)
     stage, rank, world = int(shard["stage"]), grp.rank, grp.world
     bp = ctx.task.block_params

@@ -131,6 +131,8 @@ class Trainer:
         self.verbose = verbose
         self.hyper = {"optimizer": getattr(cfg, "optimizer", "adamw"),
                       "dtype_policy": cfg.policy().to_dict() if hasattr(cfg, "policy") else "bf16", **dict(hyper or {})}
+        if getattr(cfg, "trainable_patterns", ()) and "train_only" not in self.hyper:
+            self.hyper["train_only"] = list(cfg.trainable_patterns)
         self.groups = dict(groups or {})
         if device is None:
             self.backend = CpuBackend()

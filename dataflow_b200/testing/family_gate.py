@@ -43,8 +43,12 @@ def run_pair(family: str, *, device: int | None = None, policy: str = "fp32", st
                             v.mul_(hot_mult)
         twin = fam.twin(cfg)
         twin.load_state_dict(fam.bridge(cfg, tr.views_of))
-        decay = [p for _, p in twin.named_parameters() if p.dim() >= 2]
-        plain = [p for _, p in twin.named_parameters() if p.dim() < 2]
+        import fnmatch
+        only = tuple(getattr(cfg, "trainable_patterns", ()) or ())          # runs that update a named subset of fields
+        live = [(n, p) for n, p in twin.named_parameters()
+                if not only or any(fnmatch.fnmatchcase(n.rsplit(".", 1)[-1], pat) for pat in only)]
+        decay = [p for _, p in live if p.dim() >= 2]
+        plain = [p for _, p in live if p.dim() < 2]
         opt = torch.optim.AdamW([{"params": decay, "weight_decay": hyper.get("weight_decay", 0.0)},
                                  {"params": plain, "weight_decay": 0.0}], lr=hyper["lr"], betas=(0.9, 0.95), eps=1e-8)
         eng, ref = [], []

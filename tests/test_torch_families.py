@@ -56,6 +56,33 @@ def test_glm52_followers_read_their_leaders_selection_and_budget_does_not_change
     assert tight["engine"] == pytest.approx(free["engine"], rel=1e-6)
 
 
+def test_dsv32_dense_warmup_trains_the_indexer_and_nothing_else():
+    """Warm-up: dense attention, KL of the indexer to the full-prefix attention distribution, updates for ``wi_*`` only."""
+    res = run_pair("dsv32", steps=3, preset="tiny_warmup")
+    assert res["max_loss_rel"] < 1e-3
+    moved = {k: v for k, v in res["weight_rel_l2"].items()}
+    fam = resolve_family("dsv32")
+    cfg = fam.presets["tiny_warmup"]()
+    assert cfg.trainable_patterns == ("wi_*",)
+    # the engine's final weights against ITS OWN initial weights: only the indexer moved
+    import dataclasses
+    from dataflow_b200.run.driver import Trainer, synthetic_rounds
+    c32 = dataclasses.replace(cfg, dtype_policy="fp32")
+    tr = Trainer("dsv32", c32, budget_gib=None, device=None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=3)
+    before = fam.bridge(c32, tr.views_of)
+    losses = [tr.step(synthetic_rounds(c32, tr.rounds, tr.T, 64, 11, 0)) for _ in range(2)]        # the same batch twice
+    tr.sync_to_host()
+    after = fam.bridge(c32, tr.views_of)
+    tr.close()
+    changed = {k for k in before if not torch.equal(before[k], after[k])}
+    assert changed and all(".wi_" in k for k in changed)
+    assert {k.rsplit(".", 1)[-1] for k in changed} == {"wi_q", "wi_k", "wi_w"}
+    assert abs(losses[1] - losses[0]) < 1e-6        # dense attention does not see the indexer: a frozen main model repeats its loss
+    # dense attention: the sparse preset and the warm-up preset differ in their forward
+    sparse = run_pair("dsv32", steps=1)["engine"][0]
+    assert abs(sparse - res["engine"][0]) > 1e-7
+
+
 def test_glm52_indexer_target_sums_over_the_group():
     """Groups of three: the last member's backward creates the accumulator, the middle one mutates it, the leader's reads
     it; the engine and the twin (which collects the followers' targets in a first pass) train the indexer alike."""
