@@ -87,6 +87,34 @@ def moe_mlp(x, w13_experts, w2_experts, weights, ids):
     return y
 
 
+class _EpMoE(torch.autograd.Function):
+    """Routed experts with the experts split over the ranks of an expert-parallel group: the forward is dispatch +
+    grouped up-projection, SwiGLU, grouped down-projection + weighted combine (``parallel/ep.py``), the backward the same
+    two exchanges with the roles of the matrices swapped.  Every rank calls it at the same point of its program."""
+
+    @staticmethod
+    def forward(ctx, x, w13, w2, weights, ids, group):
+        from ..parallel.ep import ep_moe_forward
+        y, saved = ep_moe_forward(group, x.contiguous(), ids.to(torch.int32).contiguous(), weights.float().contiguous(), w13, w2)
+        ctx.group, ctx.kept, ctx.wdtype = group, saved, weights.dtype
+        ctx.save_for_backward(w13, w2)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..parallel.ep import ep_moe_backward
+        w13, w2 = ctx.saved_tensors
+        dw13, dw2 = torch.zeros_like(w13), torch.zeros_like(w2)
+        dh, dwts = ep_moe_backward(ctx.group, dy.contiguous(), ctx.kept, w13, w2, dw13, dw2, accumulate=False)
+        return dh, dw13, dw2, dwts.to(ctx.wdtype), None, None
+
+
+def moe_mlp_ep(x, w13_local, w2_local, weights, ids, group):
+    """``moe_mlp`` when this rank holds ``E / world`` of the experts (``w13_local`` (E_local, d, 2F)); ``ids`` name
+    experts of the whole model."""
+    return _EpMoE.apply(x, w13_local, w2_local, weights, ids, group)
+
+
 def load_balance_aux(logits, ids, coef: float):
     """Switch-style balance loss coef * E * sum_e f_e * p_e (f: fraction of slots, p: mean router probability)."""
     if not coef:

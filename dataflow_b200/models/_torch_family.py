@@ -63,6 +63,10 @@ class TorchFamilySpec:
     # mutated by the others), and the leader's backward passes the sums to its block function as ``accum`` together with
     # ``group_size`` (members of the group, the leader included)
     accum_fields: Callable[[Any, int], Sequence[Field]] | None = None   # (cfg, tokens) -> fields of G
+    # expert parallelism (``cfg.ep`` > 1): these fields carry the expert axis first and hold this rank's E / ep experts;
+    # the block function then receives the group as ``ep`` and routes through ``_forms.moe_mlp_ep``.  Everything else is
+    # replicated and fed different data per rank: its gradients are summed over the group in front of the optimizer
+    ep_fields: tuple[str, ...] = ()
 
 
 CTX = PackedLayout((Field("stamp", (4,), "fp32"),))
@@ -182,6 +186,13 @@ class _TorchBlock(_Base):
             xin = xin.detach().requires_grad_(True)
             wl = {k: v.detach().requires_grad_(True) for k, v in wl.items()}
         shared = self.shared_from_leader(ctx, layer, x.shape[0])
+        if int(getattr(d.x, "ep", 1) or 1) > 1:
+            grp = ctx.groups.get(ctx.task.comm_groups.get("ep", "ep"))
+            if grp is None:
+                raise RuntimeError(f"task {ctx.task.id} needs the group 'ep' (pass groups={{'ep': ...}})")
+            if x.shape[0] != d.T:
+                raise ValueError("expert-parallel blocks need full rounds (the peers exchange exactly T rows with each rank)")
+            extra = dict(extra, ep=grp)
         with torch.set_grad_enabled(grad):
             res = self.spec.block_fn(d.x, d.kinds[layer], xin, wl, seg, layer, **({"shared": shared} if shared is not None else {}), **extra)
         self.emitted = res[2] if len(res) > 2 else None
@@ -256,6 +267,19 @@ class KindOptimizerStep(OptimizerStep):
         if ctx.task.block_params.get("target", "block") == "block" and "layer" in ctx.task.block_params:
             return self.lay.of_layer(int(ctx.task.block_params["layer"]))
         return super().layouts_for(ctx)
+
+
+class _KindGradSum:
+    """Block optimizer under expert parallelism: the gradients of the replicated fields of the task's layer (all but the
+    expert stacks) are summed over the group first."""
+
+    def __init__(self, inner, lay, skip):
+        self.inner, self.lay, self.skip = inner, lay, tuple(skip)
+
+    def launch(self, ctx):
+        from .tp_mlp.blocks import ReplicatedGradSum
+        gl = self.lay.of_layer(int(ctx.task.block_params.get("layer", 0)))[1]
+        ReplicatedGradSum(self.inner, gl, None, "ep", skip=self.skip).launch(ctx)
 
 
 # ------------------------------------------------------------------------------------------------- twin
@@ -397,10 +421,11 @@ def lower(spec: TorchFamilySpec, cfg, recompute_levels=None, hw: ShapedHardware 
         sc, kinds, list(d.kinds),
         embed_w_bytes=lay.embed_w.size_bytes, embed_dw_bytes=lay.embed_dw.size_bytes, embed_o_bytes=lay.embed_o.size_bytes,
         head_w_bytes=lay.head_w.size_bytes, head_dw_bytes=lay.head_dw.size_bytes, head_o_bytes=lay.head_o.size_bytes,
-        loose=loose, hw=hw, recompute_levels=None, block_params=block_params, comm_groups=comm_groups, zero=zero,
+        loose=loose, hw=hw, recompute_levels=None, block_params=block_params,
+        comm_groups=({"ep": "ep", **dict(comm_groups or {})} if int(getattr(cfg, "ep", 1) or 1) > 1 else comm_groups), zero=zero,
         resident_params=resident_params,
         metadata={"family": spec.name, "preset": cfg.name, "flops_per_token": 3.0 * (total_mm + 2.0 * d.d * d.vocab),
-                  "seq_len": cfg.seq_len, "batch": cfg.batch, "block_lane": "autograd"})
+                  "seq_len": cfg.seq_len, "batch": cfg.batch, "block_lane": "autograd", "ep": int(getattr(cfg, "ep", 1) or 1)})
     return share_leader_contexts(spec, cfg, prog, lay.extra["accum"].size_bytes if "accum" in lay.extra else 0)
 
 
@@ -444,12 +469,15 @@ def share_leader_contexts(spec: TorchFamilySpec, cfg, prog, accum_bytes: int = 0
     return dataclasses.replace(prog, tasks=tuple(tasks))
 
 
-def initial_values(spec: TorchFamilySpec, program, cfg, views_of, seed: int = 0, layouts_=None) -> None:
+def initial_values(spec: TorchFamilySpec, program, cfg, views_of, seed: int = 0, layouts_=None, rank: int = 0) -> None:
+    """Seeded initial values.  Under expert parallelism every rank draws the FULL expert stacks from the generator (so the
+    same seed gives the same model at every world size) and keeps the experts it owns (``rank``)."""
     import torch
     from .llama3.model import init_field
     d = derive(spec, cfg)
     lay = layouts_ or layouts(spec, d, cfg.policy() if hasattr(cfg, "policy") else None, getattr(cfg, "optimizer", "adamw"))
     gen = torch.Generator(device="cpu").manual_seed(int(seed))
+    ep = int(getattr(cfg, "ep", 1) or 1)
     ids = {o.id for o in program.initial_objects}
     for oid in ["W_embed"] + [f"W_{i}" for i in range(d.n_layers)] + ["W_head"]:
         if oid not in ids:
@@ -457,7 +485,12 @@ def initial_values(spec: TorchFamilySpec, program, cfg, views_of, seed: int = 0,
         wl = lay.layout_of(oid)
         wv = views_of(oid, wl)
         for f in wl.fields:
-            init_field(wv[f.name], f, gen, d.n_layers)
+            if ep > 1 and f.name in spec.ep_fields:
+                full = torch.empty((f.shape[0] * ep,) + tuple(f.shape[1:]), dtype=torch.float32)
+                init_field(full, f, gen, d.n_layers)
+                wv[f.name].copy_(full[rank * f.shape[0]:(rank + 1) * f.shape[0]])
+            else:
+                init_field(wv[f.name], f, gen, d.n_layers)
         oname = "O" + oid[1:]
         if oname in ids:
             ov = views_of(oname, lay.layout_of(oname))
@@ -477,6 +510,11 @@ def build_resolver(spec: TorchFamilySpec, dims, hyper, kernels, device, layouts_
     fwd.spec = bwd.spec = spec
     for kind in dict.fromkeys(dims.kinds):
         table[f"{kind}_fwd"], table[f"{kind}_bwd"] = fwd, bwd
+    if int(getattr(dims.x, "ep", 1) or 1) > 1:
+        from .tp_mlp.blocks import ReplicatedGradSum
+        table["optimizer_block"] = _KindGradSum(table["optimizer_block"], lay, spec.ep_fields)
+        table["optimizer_embed"] = ReplicatedGradSum(table["optimizer_embed"], lay.embed_dw, None, "ep")
+        table["optimizer_head"] = ReplicatedGradSum(table["optimizer_head"], lay.head_dw, None, "ep")
 
     def resolver(task):
         try:
@@ -491,7 +529,8 @@ def register_torch_family(spec: TorchFamilySpec) -> ModelFamily:
     return register_family(ModelFamily(
         name=spec.name, config_type=spec.config_type, derive_dims=lambda cfg: derive(spec, cfg),
         lower=lambda cfg, **kw: lower(spec, cfg, **kw),
-        initial_values=lambda program, cfg, views_of, seed=0, layouts=None: initial_values(spec, program, cfg, views_of, seed, layouts),
+        initial_values=lambda program, cfg, views_of, seed=0, layouts=None, rank=0: initial_values(spec, program, cfg, views_of, seed, layouts,
+                                                                                                   rank),
         build_resolver=lambda dims, hyper, kernels, device, layouts=None, policy=None: build_resolver(spec, dims, hyper, kernels, device, layouts, policy),
         family_layouts=lambda dims, policy=None, optimizer="adamw": layouts(spec, dims, policy, optimizer),
         presets=dict(spec.presets), twin=lambda cfg: make_twin(spec, cfg), bridge=lambda cfg, views_of: bridge(spec, cfg, views_of),

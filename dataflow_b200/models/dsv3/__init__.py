@@ -53,6 +53,9 @@ class Dsv3Config:
     # dense warm-up of the indexer (dsv32): attention stays DENSE, the indexer learns the full-prefix attention
     # distribution through its KL term, and nothing but the indexer's fields is updated
     dsa_warmup: bool = False
+    # expert parallelism: this rank holds n_experts / ep routed experts and serves rows of every rank's tokens
+    ep: int = 1
+    ep_capacity: float = 2.0
 
     @property
     def trainable_patterns(self) -> tuple[str, ...]:
@@ -89,7 +92,8 @@ def kind_fields(c: Dsv3Config, kind: str):
         f += [Field("w13", (d, 2 * c.d_ff)), Field("w2", (c.d_ff, d), "bf16", "matrix", "residual")]
     else:
         f += [Field("w_router", (d, c.n_experts)), Field("router_bias", (c.n_experts,), "bf16", "vector", "zeros"),
-              Field("w13_experts", (c.n_experts, d, 2 * c.d_ff_expert)), Field("w2_experts", (c.n_experts, c.d_ff_expert, d), "bf16", "matrix", "residual")]
+              Field("w13_experts", (c.n_experts // c.ep, d, 2 * c.d_ff_expert)),
+              Field("w2_experts", (c.n_experts // c.ep, c.d_ff_expert, d), "bf16", "matrix", "residual")]
         if c.n_shared:
             f += [Field("w13_shared", (d, 2 * c.n_shared * c.d_ff_expert)),
                   Field("w2_shared", (c.n_shared * c.d_ff_expert, d), "bf16", "matrix", "residual")]
@@ -114,14 +118,25 @@ def attention_part(c: Dsv3Config, x, w, seg):
     return x + o.reshape(n, -1) @ w["wo"], aux
 
 
-def block_fn(c: Dsv3Config, kind: str, x, w, seg, layer):
+EP_FIELDS = ("w13_experts", "w2_experts")
+
+
+def routed_experts(h2, w, wts, ids, ep=None):
+    """The routed experts' output: all experts here, or (``ep``: an expert-parallel group) this rank's share of them with
+    the rows exchanged through the group."""
+    if ep is not None:
+        return F.moe_mlp_ep(h2, w["w13_experts"], w["w2_experts"], wts, ids, ep)
+    return F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
+
+
+def block_fn(c: Dsv3Config, kind: str, x, w, seg, layer, ep=None):
     h_mid, aux = attention_part(c, x, w, seg)
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if kind.endswith("dense"):
         return h_mid + F.swiglu_mlp(h2, w["w13"], w["w2"]), aux
     logits = h2 @ w["w_router"]
     wts, ids = F.route_sigmoid_noaux(logits, w["router_bias"].detach(), c.top_k, c.n_group, c.topk_group, c.routed_scaling)
-    y = F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
+    y = routed_experts(h2, w, wts, ids, ep)
     if c.n_shared:
         y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
     return h_mid + y, aux
@@ -156,5 +171,5 @@ PRESETS = {
 }
 
 SPEC = TorchFamilySpec("dsv3", Dsv3Config, {k: (lambda kw=v: Dsv3Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,
-                       block_fn, kind_flops)
+                       block_fn, kind_flops, ep_fields=EP_FIELDS)
 FAMILY = register_torch_family(SPEC)

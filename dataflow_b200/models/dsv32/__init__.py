@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import dataclasses
 
-from ..dsv3 import Dsv3Config, block_fn as _block_fn, kind_fields as _kind_fields, kind_flops
+from ..dsv3 import EP_FIELDS, Dsv3Config, block_fn as _block_fn, kind_fields as _kind_fields, kind_flops
 from .._torch_family import TorchFamilySpec, register_torch_family
 
 
@@ -32,5 +32,5 @@ PRESETS = {
 }
 
 SPEC = TorchFamilySpec("dsv32", Dsv3Config, {k: (lambda kw=v: Dsv3Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, _kind_fields,
-                       _block_fn, kind_flops)
+                       _block_fn, kind_flops, ep_fields=EP_FIELDS)
 FAMILY = register_torch_family(SPEC)

@@ -18,7 +18,7 @@ import torch
 
 from ...blocks.layouts import Field
 from .. import _forms as F
-from ..dsv3 import Dsv3Config, kind_fields as _dsv3_fields, kind_flops as _dsv3_flops
+from ..dsv3 import EP_FIELDS, Dsv3Config, kind_fields as _dsv3_fields, kind_flops as _dsv3_flops, routed_experts
 from .._torch_family import TorchFamilySpec, register_torch_family
 
 
@@ -49,7 +49,7 @@ def accum_fields(c: Glm52Config, tokens: int):
     return (Field("kl_target", (tokens, min(c.index_topk, c.seq_len)), "fp32"),)
 
 
-def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=None, group_size=1):
+def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=None, group_size=1, ep=None):
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
@@ -81,7 +81,7 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
         y = F.swiglu_mlp(h2, w["w13"], w["w2"])
     else:
         wts, ids = F.route_sigmoid_noaux(h2 @ w["w_router"], w["router_bias"].detach(), c.top_k, c.n_group, c.topk_group, c.routed_scaling)
-        y = F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
+        y = routed_experts(h2, w, wts, ids, ep)
         if c.n_shared:
             y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
     return h_mid + y, aux, emit
@@ -108,5 +108,5 @@ PRESETS = {
 }
 
 SPEC = TorchFamilySpec("glm52", Glm52Config, {k: (lambda kw=v: Glm52Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,
-                       block_fn, kind_flops, ctx_fields=ctx_fields, leader_of=leader_of, accum_fields=accum_fields)
+                       block_fn, kind_flops, ctx_fields=ctx_fields, leader_of=leader_of, accum_fields=accum_fields, ep_fields=EP_FIELDS)
 FAMILY = register_torch_family(SPEC)

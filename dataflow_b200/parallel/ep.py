@@ -309,6 +309,23 @@ def _kernels(g: EpGroup, ks):
     return resolve_kernels(kernel_set=None if g.lane == "p2p" else "eager")
 
 
+def ep_group_for(family, cfg, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 30.0) -> EpGroup:
+    """The expert-parallel group of a job that trains ``cfg`` (with ``cfg.ep == world``) of ``family`` (a ``ModelFamily``):
+    reads the token / width / expert counts from the family's dims, whichever lane the family is written in."""
+    d = family.derive_dims(cfg)
+    x = getattr(d, "x", None)                        # reference-form families keep their config there
+    if x is not None:
+        if not getattr(x, "n_experts", 0):
+            raise ValueError(f"{family.name}: expert parallelism needs a mixture-of-experts preset")
+        n_experts, top_k = int(x.n_experts), int(x.top_k)
+    else:
+        if not getattr(d, "moe", False):
+            raise ValueError(f"{family.name}: expert parallelism needs a mixture-of-experts preset")
+        n_experts, top_k = int(d.E), int(d.topk)
+    return EpGroup(rank, world, device, tokens=int(d.T), d_model=int(d.d), n_experts=n_experts, top_k=top_k,
+                   capacity_factor=float(getattr(cfg, "ep_capacity", 2.0)), lane=lane, timeout_s=timeout_s)
+
+
 def ep_moe_forward(g: EpGroup, h, ids, weights, w13, w2, base=None, ks=None):
     """``h`` (T, d) block input (normalised), ``w13`` (E_local, d, 2 F), ``w2`` (E_local, F, d).  Returns ``(y, saved)``."""
     ks = _kernels(g, ks)

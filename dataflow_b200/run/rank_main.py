@@ -83,13 +83,14 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     elif world > 1 and spec.parallel == "ep":
         # expert parallelism: experts split over the ranks, everything else data-parallel
         from ..models.families import resolve_family
-        from ..parallel.ep import EpGroup
+        from ..parallel.ep import ep_group_for
+        if "ep" not in {f.name for f in dataclasses.fields(cfg)}:
+            raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} has no experts to split")
         cfg = dataclasses.replace(cfg, ep=world)
-        d = resolve_family(family).derive_dims(cfg)
-        if not getattr(d, "moe", False):
-            raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} is dense")
-        groups = {"ep": EpGroup(rank, world, device, tokens=d.T, d_model=d.d, n_experts=d.E, top_k=d.topk, capacity_factor=cfg.ep_capacity,
-                                lane=lane)}
+        try:
+            groups = {"ep": ep_group_for(resolve_family(family), cfg, rank, world, device, lane)}
+        except ValueError as e:
+            raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} is dense ({e})") from None
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
     recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
     say = log if rank == 0 else (lambda *a, **k: None)

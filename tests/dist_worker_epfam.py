@@ -1,5 +1,5 @@
-"""Worker for the expert-parallel family test (spawned by test_ep.py): trains olmoe with its experts split over the ranks;
-every rank feeds its own data; writes the summed loss curve."""
+"""Worker for the expert-parallel family tests (spawned by test_ep.py): trains a mixture-of-experts family (``EP_TEST_FAMILY``,
+default olmoe) with its experts split over the ranks; every rank feeds its own data; writes the summed loss curve."""
 import dataclasses
 import json
 import os
@@ -21,17 +21,17 @@ def main():
     else:
         dist.init_process_group("gloo")
     from dataflow_b200.models.families import resolve_family
-    from dataflow_b200.parallel.ep import EpGroup
+    from dataflow_b200.parallel.ep import ep_group_for
     from dataflow_b200.run.driver import Trainer, synthetic_rounds
-    fam = resolve_family("olmoe")
+    name = os.environ.get("EP_TEST_FAMILY", "olmoe")
+    fam = resolve_family(name)
     cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32" if not gpu else "bf16_master", ep=world)
     d = fam.derive_dims(cfg)
     lane = os.environ.get("DATAFLOW_EP_LANE") or ("p2p" if gpu else "collective")
-    grp = EpGroup(rank, world, rank if gpu else None, tokens=d.T, d_model=d.d, n_experts=d.E, top_k=d.topk, capacity_factor=cfg.ep_capacity,
-                  lane=lane, timeout_s=20.0)
-    assert grp.C == d.Mp
+    grp = ep_group_for(fam, cfg, rank, world, rank if gpu else None, lane, timeout_s=20.0)
+    assert not hasattr(d, "Mp") or grp.C == d.Mp
     budget = float(os.environ["EP_TEST_BUDGET"]) if os.environ.get("EP_TEST_BUDGET") else None
-    tr = Trainer("olmoe", cfg, budget_gib=budget, device=rank if gpu else None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=5,
+    tr = Trainer(name, cfg, budget_gib=budget, device=rank if gpu else None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=5,
                  groups={"ep": grp}, leeway_bytes=0)
     losses = []
     for s in range(3):

@@ -121,7 +121,7 @@ def test_daemon_start_status_stop(tmp_path):
                         stderr=subprocess.DEVNULL)
 
 
-@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny")])
+@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny"), ("ep", "dsv32:tiny")])
 def test_train_cli_runs_tensor_and_expert_parallel_jobs_on_cpu_ranks(parallel, preset, tmp_path):
     """`train.py train --gpus 2 --parallel tp|ep` end to end on two gloo ranks: packed data, loop, result file."""
     import json
@@ -138,7 +138,7 @@ def test_train_cli_runs_tensor_and_expert_parallel_jobs_on_cpu_ranks(parallel, p
     assert res["meta"]["world"] == 2
 
 
-@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny")])
+@pytest.mark.parametrize("parallel,preset", [("tp", "llama3:tiny"), ("ep", "olmoe:tiny"), ("ep", "dsv3:tiny")])
 def test_tensor_and_expert_parallel_jobs_resume_bitwise(parallel, preset, tmp_path):
     """Every rank's cut of the model is recorded per rank; a resumed run continues the interrupted curve exactly."""
     import json

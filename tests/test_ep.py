@@ -74,9 +74,9 @@ def test_ep_fused_kernels_match_dense_oracle(lane, tmp_path):
         assert v < 2e-2, (k, v)
 
 
-def launch_family(world, device_kind, tmp_path, lane=None, port=29731, budget=None):
-    out = tmp_path / f"epfam_{device_kind}_{lane}_{budget}.json"
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def launch_family(world, device_kind, tmp_path, lane=None, port=29731, budget=None, family="olmoe"):
+    out = tmp_path / f"epfam_{family}_{device_kind}_{lane}_{budget}.json"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", EP_TEST_FAMILY=family)
     env.pop("DATAFLOW_EP_LANE", None)
     env.pop("EP_TEST_BUDGET", None)
     if lane:
@@ -92,15 +92,15 @@ def launch_family(world, device_kind, tmp_path, lane=None, port=29731, budget=No
     return json.loads(out.read_text())
 
 
-def solo_olmoe_losses():
+def solo_olmoe_losses(family="olmoe"):
     """One process, all experts, both ranks' data in one step (twice the rounds): the math the EP run must reproduce."""
     import dataclasses
     from dataflow_b200.models.families import resolve_family
     from dataflow_b200.run.driver import Trainer, synthetic_rounds
-    fam = resolve_family("olmoe")
+    fam = resolve_family(family)
     base = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
     cfg = dataclasses.replace(base, grad_accum_rounds=base.grad_accum_rounds * 2)
-    tr = Trainer("olmoe", cfg, budget_gib=None, device=None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=5, leeway_bytes=0)
+    tr = Trainer(family, cfg, budget_gib=None, device=None, hyper={"lr": 2e-3, "weight_decay": 0.1}, seed=5, leeway_bytes=0)
     losses = []
     try:
         for s in range(3):
@@ -116,6 +116,17 @@ def solo_olmoe_losses():
 def test_olmoe_with_experts_split_over_two_cpu_ranks_matches_one_process(tmp_path):
     got = launch_family(2, "cpu", tmp_path, port=29733)
     ref = solo_olmoe_losses()
+    for a, b in zip(got["losses"], ref):
+        assert a == pytest.approx(b, rel=1e-3)
+    assert got["losses"][-1] < got["losses"][0]
+
+
+@pytest.mark.parametrize("family,port", [("dsv3", 29741), ("glm52", 29743)])
+def test_reference_form_families_with_experts_split_over_two_cpu_ranks_match_one_process(family, port, tmp_path):
+    """Multi-head latent attention families (autograd lane): the routed experts go through the expert-parallel exchange
+    as an autograd function; replicated fields' gradients are summed over the group."""
+    got = launch_family(2, "cpu", tmp_path, port=port, family=family)
+    ref = solo_olmoe_losses(family)
     for a, b in zip(got["losses"], ref):
         assert a == pytest.approx(b, rel=1e-3)
     assert got["losses"][-1] < got["losses"][0]
