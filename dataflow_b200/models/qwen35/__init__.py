@@ -41,6 +41,9 @@ class Qwen35Config:
     d_ff_expert: int = 0
     shared_expert: bool = False
     aux_coef: float = 0.0
+    # expert parallelism (qwen35moe): this rank holds n_experts / ep routed experts
+    ep: int = 1
+    ep_capacity: float = 2.0
     vocab_size: int = 1024
     rope_theta: float = 10000.0
     rms_eps: float = 1e-6
@@ -65,8 +68,8 @@ def mlp_fields(c: Qwen35Config):
     d = c.d_model
     f = [Field("ffn_norm", (d,), "bf16", "vector", "ones")]
     if c.n_experts:
-        f += [Field("w_router", (d, c.n_experts)), Field("w13_experts", (c.n_experts, d, 2 * c.d_ff_expert)),
-              Field("w2_experts", (c.n_experts, c.d_ff_expert, d), "bf16", "matrix", "residual")]
+        f += [Field("w_router", (d, c.n_experts)), Field("w13_experts", (c.n_experts // c.ep, d, 2 * c.d_ff_expert)),
+              Field("w2_experts", (c.n_experts // c.ep, c.d_ff_expert, d), "bf16", "matrix", "residual")]
         if c.shared_expert:
             f += [Field("w_shared_gate", (d, 1)), Field("w13_shared", (d, 2 * c.d_ff_expert)),
                   Field("w2_shared", (c.d_ff_expert, d), "bf16", "matrix", "residual")]
@@ -133,21 +136,24 @@ def gated_attention(c: Qwen35Config, x, w, seg):
     return x + o.reshape(n, -1) @ w["wo"]
 
 
-def mlp_part(c: Qwen35Config, h_mid, w):
+def mlp_part(c: Qwen35Config, h_mid, w, ep=None):
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if not c.n_experts:
         return h_mid + F.swiglu_mlp(h2, w["w13"], w["w2"]), None
     logits = h2 @ w["w_router"]
     wts, ids = F.route_softmax_topk(logits, c.top_k)
-    y = F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
+    if ep is not None:
+        y = F.moe_mlp_ep(h2, w["w13_experts"], w["w2_experts"], wts, ids, ep)
+    else:
+        y = F.moe_mlp(h2, w["w13_experts"], w["w2_experts"], wts, ids)
     if c.shared_expert:
         y = y + torch.sigmoid((h2 @ w["w_shared_gate"]).float()).to(y.dtype) * F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
     return h_mid + y, F.load_balance_aux(logits, ids, c.aux_coef)
 
 
-def block_fn(c: Qwen35Config, kind: str, x, w, seg, layer):
+def block_fn(c: Qwen35Config, kind: str, x, w, seg, layer, ep=None):
     h_mid = linear_attention(c, x, w, seg) if kind.startswith("lin") else gated_attention(c, x, w, seg)
-    return mlp_part(c, h_mid, w)
+    return mlp_part(c, h_mid, w, ep)
 
 
 def kind_flops(c: Qwen35Config, kind: str, tokens: int):

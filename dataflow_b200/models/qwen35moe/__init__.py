@@ -20,5 +20,5 @@ PRESETS = {
 }
 
 SPEC = TorchFamilySpec("qwen35moe", Qwen35Config, {k: (lambda kw=v: Qwen35Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,
-                       block_fn, kind_flops)
+                       block_fn, kind_flops, ep_fields=("w13_experts", "w2_experts"))
 FAMILY = register_torch_family(SPEC)

@@ -121,7 +121,7 @@ def test_olmoe_with_experts_split_over_two_cpu_ranks_matches_one_process(tmp_pat
     assert got["losses"][-1] < got["losses"][0]
 
 
-@pytest.mark.parametrize("family,port", [("dsv3", 29741), ("glm52", 29743)])
+@pytest.mark.parametrize("family,port", [("dsv3", 29741), ("glm52", 29743), ("qwen35moe", 29745)])
 def test_reference_form_families_with_experts_split_over_two_cpu_ranks_match_one_process(family, port, tmp_path):
     """Multi-head latent attention families (autograd lane): the routed experts go through the expert-parallel exchange
     as an autograd function; replicated fields' gradients are summed over the group."""
