@@ -44,10 +44,34 @@ def attention(q, k, v, mask, scale: float):
     return torch.einsum("hij,jhd->ihd", p, v.float()).to(q.dtype), p
 
 
-def swiglu_mlp(x, w13, w2):
-    h = x @ w13
+class _LinearFp8(torch.autograd.Function):
+    """y = x @ w with both operands rounded to e4m3 (per-row scales for x, per-output-column scales for w, fp32
+    accumulation) in the forward; the backward products run in the storage dtype on the unquantised operands."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from ..ops import resolve_kernels
+        ks = _native(x) or resolve_kernels(kernel_set="eager")
+        ctx.save_for_backward(x, w)
+        return ks.linear_fwd_fp8(x.contiguous(), w.contiguous())
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        return dy @ w.t(), x.t() @ dy
+
+
+def linear(x, w, precision: str = "bf16"):
+    """x (n, k) @ w (k, m); ``precision="fp8"``: e4m3 operands in the forward (see ``ops`` ``linear_fwd_fp8``)."""
+    if precision == "fp8" and x.dim() == 2 and x.shape[1] % 16 == 0 and w.shape[1] % 16 == 0:
+        return _LinearFp8.apply(x, w)
+    return x @ w
+
+
+def swiglu_mlp(x, w13, w2, precision: str = "bf16"):
+    h = linear(x, w13, precision)
     f = h.shape[-1] // 2
-    return (F.silu(h[..., :f].float()).to(x.dtype) * h[..., f:]) @ w2
+    return linear(F.silu(h[..., :f].float()).to(x.dtype) * h[..., f:], w2, precision)
 
 
 def route_softmax_topk(logits, k: int):

@@ -56,6 +56,9 @@ class Dsv3Config:
     # expert parallelism: this rank holds n_experts / ep routed experts and serves rows of every rank's tokens
     ep: int = 1
     ep_capacity: float = 2.0
+    # "fp8": the dense and shared-expert MLP projections and the attention output projection run their forward on e4m3
+    # operands (per-row / per-column scales); the routed experts' grouped GEMMs and every backward product stay bf16
+    linear_precision: str = "bf16"
 
     @property
     def trainable_patterns(self) -> tuple[str, ...]:
@@ -115,7 +118,7 @@ def attention_part(c: Dsv3Config, x, w, seg):
     o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
     if c.index_topk and c.index_kl_coef:
         aux = c.index_kl_coef * F.dsa_indexer_kl(scores, probs, mask) * n
-    return x + o.reshape(n, -1) @ w["wo"], aux
+    return x + F.linear(o.reshape(n, -1), w["wo"], c.linear_precision), aux
 
 
 EP_FIELDS = ("w13_experts", "w2_experts")
@@ -133,12 +136,12 @@ def block_fn(c: Dsv3Config, kind: str, x, w, seg, layer, ep=None):
     h_mid, aux = attention_part(c, x, w, seg)
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if kind.endswith("dense"):
-        return h_mid + F.swiglu_mlp(h2, w["w13"], w["w2"]), aux
+        return h_mid + F.swiglu_mlp(h2, w["w13"], w["w2"], c.linear_precision), aux
     logits = h2 @ w["w_router"]
     wts, ids = F.route_sigmoid_noaux(logits, w["router_bias"].detach(), c.top_k, c.n_group, c.topk_group, c.routed_scaling)
     y = routed_experts(h2, w, wts, ids, ep)
     if c.n_shared:
-        y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
+        y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"], c.linear_precision)
     return h_mid + y, aux
 
 

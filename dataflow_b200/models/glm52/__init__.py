@@ -75,15 +75,15 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
             if accum is not None:
                 target = (target + torch.zeros_like(target).scatter_add_(1, cols, accum["kl_target"][:, :cols.shape[1]].to(target.dtype))) / group_size
             aux = c.index_kl_coef * F.dsa_indexer_kl_to(scores, target, mask) * n
-    h_mid = x + o.reshape(n, -1) @ w["wo"]
+    h_mid = x + F.linear(o.reshape(n, -1), w["wo"], c.linear_precision)
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if kind.startswith("gd"):
-        y = F.swiglu_mlp(h2, w["w13"], w["w2"])
+        y = F.swiglu_mlp(h2, w["w13"], w["w2"], c.linear_precision)
     else:
         wts, ids = F.route_sigmoid_noaux(h2 @ w["w_router"], w["router_bias"].detach(), c.top_k, c.n_group, c.topk_group, c.routed_scaling)
         y = routed_experts(h2, w, wts, ids, ep)
         if c.n_shared:
-            y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"])
+            y = y + F.swiglu_mlp(h2, w["w13_shared"], w["w2_shared"], c.linear_precision)
     return h_mid + y, aux, emit
 
 

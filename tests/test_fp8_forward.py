@@ -60,3 +60,23 @@ def test_recipe_carries_the_option():
     assert Recipe(linear_precision="fp8").hyper()["linear_precision"] == "fp8"
     with pytest.raises(ValueError):
         Recipe(linear_precision="fp4")
+
+
+def test_reference_form_families_take_the_option_too():
+    """dsv32 (autograd lane): fp8 forward for the dense / shared-expert MLPs and the attention output projection, through an
+    autograd function whose backward runs on the unquantised operands."""
+    from dataflow_b200.testing.family_gate import run_pair
+    base = run_pair("dsv32", steps=3)["engine"]
+    f8 = run_pair("dsv32", steps=3, overrides={"linear_precision": "fp8"})
+    assert f8["engine"] != base and f8["max_loss_rel"] < 1e-3          # the twin runs the same forms, so it quantises too
+    for a, b in zip(base, f8["engine"]):
+        assert abs(a - b) / a < 0.02
+    from dataflow_b200.models import _forms as F
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(48, 64, generator=g, requires_grad=True)
+    w = (torch.randn(64, 32, generator=g) * 0.1).requires_grad_(True)
+    y = F.linear(x, w, "fp8")
+    y.sum().backward()
+    assert float((y - x @ w).detach().norm() / (x @ w).detach().norm()) < 0.05
+    assert torch.allclose(x.grad, torch.ones(48, 32) @ w.t().detach(), atol=1e-5)       # backward: exact products
+    assert F.linear(x[:, :60], w[:60], "fp8").shape == (48, 32)                          # odd widths fall back to the plain product
