@@ -29,6 +29,12 @@ PRESETS = {
                        d_v=128, d_ff=18432, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5,
                        vocab_size=129280, seq_len=4096, batch=1, grad_accum_rounds=16, dtype_policy="bf16_split_master",
                        **{**BASE, "index_heads": 64, "index_dim": 128, "index_topk": 2048}),
+    # the 12-layer cut used as a multi-GPU benchmark configuration: 3 dense layers, 256 routed experts (top-8) + 1 shared,
+    # indexer top-2048 at 16k tokens per sequence, experts split over the ranks (``ep`` set by ``--parallel ep``)
+    "dsv32_12l": dict(name="dsv32_12l", n_layers=12, n_dense=3, d_model=7168, n_heads=128, q_lora=1536, kv_lora=512, d_nope=128, d_rope=64,
+                      d_v=128, d_ff=18432, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5,
+                      vocab_size=129280, seq_len=16384, batch=1, grad_accum_rounds=8, dtype_policy="bf16_split_master",
+                      linear_precision="fp8", **{**BASE, "index_heads": 64, "index_dim": 128, "index_topk": 2048}),
 }
 
 SPEC = TorchFamilySpec("dsv32", Dsv3Config, {k: (lambda kw=v: Dsv3Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, _kind_fields,
