@@ -172,6 +172,11 @@ class ReplicatedGradSum:
     def __init__(self, inner, layout_of_grad, fields, group: str = "tp", skip=()):
         self.inner, self.layout_of_grad, self.fields, self.group, self.skip = inner, layout_of_grad, fields, group, tuple(skip)
 
+    def __getattr__(self, name):
+        # wrappers stack (sum over the tensor-parallel group, then over the data-parallel replicas): the layout helpers and the
+        # device of the innermost executable show through
+        return getattr(self.__dict__["inner"], name)
+
     def launch(self, ctx):
         inner = self.inner
         if inner.device is None:

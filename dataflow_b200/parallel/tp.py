@@ -22,10 +22,11 @@ CTRL_BYTES = 1 << 18          # rendezvous words, handed out per operand shape (
 
 class TpGroup:
     def __init__(self, rank: int, world: int, device: int | None, *, max_rows: int, max_k: int, max_n: int,
-                 lane: str | None = None, timeout_s: float = 30.0):
+                 lane: str | None = None, timeout_s: float = 30.0, pg=None):
         """``max_rows``: rows per rank (the sequence shard); ``max_k`` / ``max_n``: widest gathered operand and widest
-        reduce-scattered output this group will see (they size the workspace)."""
-        self.rank, self.world, self.device = rank, world, device
+        reduce-scattered output this group will see (they size the workspace).  ``pg``: the ``torch.distributed`` process
+        group of the members when they are a subset of the job (a dp x tp mesh); ``rank`` is the rank inside it."""
+        self.rank, self.world, self.device, self.pg = rank, world, device, pg
         self.lane = lane or os.environ.get("DATAFLOW_TP_LANE") or ("p2p" if device is not None else "collective")
         self.timeout_s = timeout_s
         self.max_rows, self.max_k, self.max_n = int(max_rows), int(max_k), int(max_n)
@@ -53,12 +54,12 @@ class TpGroup:
         self.backend = backend
         self.base = backend.device_alloc_zeroed(self.ws_bytes)
         handles: list[Any] = [None] * self.world
-        dist.all_gather_object(handles, backend.ipc_handle(self.base))
+        dist.all_gather_object(handles, backend.ipc_handle(self.base), group=self.pg)
         self.ws = [self.base if r == self.rank else backend.ipc_open(h) for r, h in enumerate(handles)]
         dev = torch.device("cuda", self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
-        dist.barrier()
+        dist.barrier(group=self.pg)
 
     def close(self) -> None:
         if self.lane == "p2p" and self.backend is not None and self.ws:
@@ -119,13 +120,13 @@ class TpGroup:
         if self.world == 1:
             out.copy_(x)
         else:
-            dist.all_gather_into_tensor(out, x.contiguous())
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.pg)
         return out
 
     def all_reduce(self, t):
         import torch.distributed as dist
         if self.world > 1:
-            dist.all_reduce(t)
+            dist.all_reduce(t, group=self.pg)
         return t
 
     # -- fused ops
@@ -140,7 +141,7 @@ class TpGroup:
         if self.lane != "p2p":
             import torch.distributed as dist
             parts = [torch.empty_like(x) for _ in range(self.world)]
-            dist.all_gather(parts, x.contiguous())
+            dist.all_gather(parts, x.contiguous(), group=self.pg)
             full = torch.cat(parts, 0)
             self._last_full = full
             out.copy_(torch.matmul(full.float(), (w if w_is_kn else w.t()).float()).to(out.dtype))
@@ -173,11 +174,11 @@ class TpGroup:
             import torch.distributed as dist
             part = torch.matmul(x.float(), (w if w_is_kn else w.t()).float())
             if dist.get_backend() == "gloo":
-                dist.all_reduce(part)
+                dist.all_reduce(part, group=self.pg)
                 mine = part[self.rank * rows:(self.rank + 1) * rows]
             else:
                 mine = torch.empty(rows, n, dtype=torch.float32, device=x.device)
-                dist.reduce_scatter_tensor(mine, part)
+                dist.reduce_scatter_tensor(mine, part, group=self.pg)
             if addend is not None:
                 mine = mine + addend.float()
             out.copy_(mine.to(out.dtype))

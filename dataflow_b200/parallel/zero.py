@@ -88,8 +88,9 @@ class DpGroup:
 
     SLOTS = 512
 
-    def __init__(self, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 60.0):
+    def __init__(self, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 60.0, pg=None):
         self.rank, self.world, self.device = rank, world, device
+        self.pg = pg            # process group of the members when they are a subset of the job (used by ``all_reduce``)
         self.lane = lane or ("p2p" if device is not None else "collective")
         self.timeout_s = timeout_s
         self.calls: dict[int, int] = {}
@@ -291,7 +292,7 @@ class DpGroup:
         """Sum over the group (plain data parallelism: whole gradient objects in front of the optimizer)."""
         import torch.distributed as dist
         if self.world > 1:
-            dist.all_reduce(t)
+            dist.all_reduce(t, group=self.pg)
         return t
 
     def close(self) -> None:
@@ -333,9 +334,9 @@ class _LayerAwareGradSum:
         ReplicatedGradSum(self.inner, gl, None, self.group_key).launch(ctx)
 
 
-def make_dp_group(rank: int, world: int, device: int | None, lane: str | None = None) -> DpGroup:
+def make_dp_group(rank: int, world: int, device: int | None, lane: str | None = None, pg=None) -> DpGroup:
     lane = lane or os.environ.get("DATAFLOW_DP_LANE")
-    return DpGroup(rank, world, device, lane)
+    return DpGroup(rank, world, device, lane, pg=pg)
 
 
 def slot_of(target: str, layer: int | None, kind: int) -> int:

@@ -61,8 +61,12 @@ def _world(trainer) -> tuple[int, int]:
     z = trainer.zero or {}
     if z:
         return int(z.get("rank", 0)), int(z.get("world", 1))
+    groups = getattr(trainer, "groups", None) or {}
+    if "tp" in groups and "dp" in groups:          # a dp x tp mesh: consecutive ranks form a tensor-parallel group
+        tp, dp = groups["tp"], groups["dp"]
+        return int(dp.rank) * int(tp.world) + int(tp.rank), int(dp.world) * int(tp.world)
     for key in ("tp", "ep", "dp"):                 # tensor / expert parallel jobs and plain replicas: the group knows the rank
-        g = (getattr(trainer, "groups", None) or {}).get(key)
+        g = groups.get(key)
         if g is not None:
             return int(g.rank), int(g.world)
     return 0, 1

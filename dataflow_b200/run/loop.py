@@ -60,12 +60,13 @@ def _dist():
 def put_rank_rounds(trainer: Trainer, packed, rank: int, rounds: int, row_shard: tuple[int, int] | None = None,
                     first_round: int | None = None) -> tuple[int, dict[int, list[int]], int]:
     """Copy this rank's rounds of a packed step into the store.  Returns (bytes written, seq_lens, local valid rows).
-    ``row_shard = (index, count)``: sequence parallelism — every rank takes the SAME rounds and keeps its slice of rows
-    (the sequence bounds stay those of the whole round: attention sees all rows)."""
+    ``rank``: the DATA rank (which block of ``rounds`` rounds of the step is this rank's).  ``row_shard = (index, count)``:
+    sequence parallelism — the ranks of one tensor-parallel group share a data rank, take the SAME rounds and keep their
+    slice of rows (the sequence bounds stay those of the whole round: attention sees all rows)."""
     import torch
     nbytes, seq_lens, valid = 0, {}, 0
     for r in range(rounds):
-        rd = packed.rounds[(0 if row_shard else (rank * rounds if first_round is None else first_round)) + r]
+        rd = packed.rounds[(rank * rounds if first_round is None else first_round) + r]
         tk, tg = torch.from_numpy(rd.tokens), torch.from_numpy(rd.targets)
         if row_shard:
             n = len(rd.tokens) // row_shard[1]
@@ -93,14 +94,15 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
     world = dist.get_world_size() if dist else 1
     # data-parallel ranks (fsdp / zero / ep) consume different rounds; tensor-parallel ranks share them and split the rows
     tp = int((trainer.program.metadata or {}).get("tp", 1))
-    row_shard = (rank, tp) if tp > 1 else None
-    data_world = 1 if row_shard else world
+    row_shard = (rank % tp, tp) if tp > 1 else None
+    data_world = world // tp if row_shard else world          # > 1 with tp: a dp x tp mesh, replicas consume different rounds
+    data_rank = rank // tp if row_shard else rank
     # weighted data parallelism: rank r runs rank_rounds[r] rounds of every step
     job_rounds = sum(rank_rounds) if rank_rounds else trainer.rounds * data_world
     first_round = sum(rank_rounds[:rank]) if rank_rounds else None
     stepper = factory(dict(cursor) if cursor else None)
     ahead = PackAhead(stepper)
-    res = RunResult(losses=list(losses or []), tokens_per_step=trainer.T * (job_rounds if rank_rounds else trainer.rounds * world),
+    res = RunResult(losses=list(losses or []), tokens_per_step=trainer.T * (job_rounds if rank_rounds else trainer.rounds * world),     # T is this rank's rows of a round
                     meta={"family": trainer.fam.name, "preset": getattr(trainer.cfg, "name", ""), "world": world,
                           "plan_makespan_us": trainer.planned.makespan_us, "policy": trainer.planned.policy,
                           "peak_fast_bytes": trainer.planned.peak_fast_bytes,
@@ -119,7 +121,7 @@ def train_loop(trainer: Trainer, factory: Callable, steps: int, *, cursor: Mappi
             if window:
                 window.before(s + 1, trainer)
             t0 = time.perf_counter()
-            _, seq_lens, valid = put_rank_rounds(trainer, packed, rank, trainer.rounds, row_shard, first_round)
+            _, seq_lens, valid = put_rank_rounds(trainer, packed, data_rank, trainer.rounds, row_shard, first_round)
             total_valid = packed.valid_rows          # every rank packed the whole job's step: no exchange needed
             loss = trainer.step(None, seq_lens=seq_lens, valid_rows=max(total_valid, 1))
             if dist:

@@ -74,12 +74,32 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         from ..parallel.tp import TpGroup
         if family not in ("llama3", "tp_mlp"):
             raise ValueError(f"--parallel tp covers the dense llama block (llama3 / tp_mlp presets), not {family!r}")
-        family, cfg = "tp_mlp", dataclasses.replace(cfg, tp=world, family="tp_mlp")
+        tp = int(spec.tp_size or world)
+        if tp < 2 or world % tp:
+            raise ValueError(f"--tp-size {tp} does not divide the job's {world} ranks into tensor-parallel groups")
+        dp = world // tp
+        family, cfg = "tp_mlp", dataclasses.replace(cfg, tp=tp, family="tp_mlp")
         from ..models.families import resolve_family
         d = resolve_family(family).derive_dims(cfg)
-        groups = {"tp": TpGroup(rank, world, device, max_rows=d.Ts, max_k=d.d, max_n=d.d, lane=lane)}
+        tp_pg = dp_pg = None
+        if dp > 1:
+            # a dp x tp mesh: consecutive ranks form a tensor-parallel group, ranks with the same place in their groups are
+            # data-parallel replicas of each other.  Every rank creates every subgroup, in the same order.
+            import torch.distributed as dist
+            for g in range(dp):
+                pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
+                if g == rank // tp:
+                    tp_pg = pg
+            for j in range(tp):
+                pg = dist.new_group(list(range(j, world, tp)))
+                if j == rank % tp:
+                    dp_pg = pg
+        groups = {"tp": TpGroup(rank % tp, tp, device, max_rows=d.Ts, max_k=d.d, max_n=d.d, lane=lane, pg=tp_pg)}
+        if dp > 1:
+            from ..parallel.zero import make_dp_group
+            groups["dp"] = make_dp_group(rank // tp, dp, device, "collective", pg=dp_pg)
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
-        data_world = 1
+        data_world = dp
     elif world > 1 and spec.parallel == "ep":
         # expert parallelism: experts split over the ranks, everything else data-parallel
         from ..models.families import resolve_family
@@ -112,7 +132,7 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     say(f"plan: {tr.planned.policy}, predicted {tr.planned.makespan_us / 1e3:.1f} ms/step, peak fast "
         f"{tr.planned.peak_fast_bytes / 2 ** 30:.2f} GiB, planned in {tr.plan_s:.1f} s")
     # the job-wide pipeline: every rank packs all rounds of the step and keeps its own
-    if world > 1 and spec.parallel in ("co", "dp"):
+    if world > 1 and (spec.parallel in ("co", "dp") or (spec.parallel == "tp" and "dp" in groups)):
         from ..parallel.zero import replicate_gradients
         replicate_gradients(tr)
     total_rounds = sum(spec.rounds) if spec.rounds else cfg.grad_accum_rounds * data_world

@@ -180,3 +180,31 @@ def test_plain_and_weighted_data_parallel_jobs_match_one_process(tmp_path):
     # the order in which round gradients are summed differs (per rank, then over ranks): noise of that size only
     assert even == pytest.approx(solo, rel=2e-4)
     assert weighted == pytest.approx(solo, rel=2e-4)
+
+
+def test_data_parallel_replicas_of_a_tensor_parallel_group_match_one_process(tmp_path):
+    """A 2 x 2 mesh on four CPU ranks: two tensor-parallel groups of two ranks, the groups data-parallel replicas of each
+    other (gradients summed over the replicas in front of the optimizer), against one process running all the rounds."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "3", "--device", "cpu",
+            "--dtype-policy", "fp32"]
+
+    def run(extra, name):
+        out = tmp_path / f"{name}.json"
+        r = subprocess.run(base + extra + ["--out", str(out)], capture_output=True, text=True, timeout=900, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2500:]
+        return json.loads(out.read_text())
+
+    solo = run(["--ga-rounds", "4"], "solo")
+    mesh = run(["--gpus", "4", "--parallel", "tp", "--tp-size", "2", "--ga-rounds", "2", "--checkpoint-dir", str(tmp_path / "ck"),
+                "--checkpoint-every", "2"], "mesh")
+    assert mesh["meta"]["world"] == 4 and mesh["tokens_per_step"] == solo["tokens_per_step"]
+    assert mesh["losses"] == pytest.approx(solo["losses"], rel=5e-4)
+    rec = json.loads((tmp_path / "ck" / "step_000002" / "checkpoint_record.json").read_text())
+    assert rec["scheme"]["world"] == 4 and sorted(os.listdir(tmp_path / "ck" / "step_000002" / "programs")) == [f"rank{i}.json" for i in range(4)]
+    again = run(["--gpus", "4", "--parallel", "tp", "--tp-size", "2", "--ga-rounds", "2", "--checkpoint-dir", str(tmp_path / "ck"),
+                 "--resume", str(tmp_path / "ck" / "step_000002")], "again")
+    assert again["losses"] == pytest.approx(mesh["losses"], rel=1e-5)
