@@ -1,6 +1,6 @@
 """One-command family correctness: structure check (lowering validates, every compute key resolves, layouts agree with
-object sizes), the engine-versus-twin model step on uniform and ragged shapes, plan invariance under a tight budget,
-and an audit that the family has its canonical tests in ``tests/``.
+object sizes), the engine-versus-twin model step on uniform and ragged shapes, per-tensor gradients against autograd
+through the twin, plan invariance under a tight budget, and an audit that the family has its canonical tests in ``tests/``.
 
     python tools/verify/verify_family.py --family olmoe
     python tools/verify/verify_family.py --list
@@ -71,6 +71,15 @@ def main(argv=None) -> int:
             bad.append(f"model step {shape}")
         if shape == "uniform":
             base = r["engine"]
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.testing.gradcheck import check_model_step
+    cfg0 = resolve_family(a.family).presets["tiny"]()
+    routed = bool(getattr(cfg0, "n_experts", 0) or getattr(cfg0, "moe", False))
+    rep = check_model_step(a.family, device=device, policy="fp32" if device is None else "bf16_master",
+                           tol=(0.25 if routed else 2e-2) if device is None else 0.35)
+    print(f"gradients   : {rep.summary()}  {'ok' if rep else 'FAIL'}")
+    if not rep:
+        bad.append(f"gradients {sorted(rep.failures())[:4]}")
     tight = run_pair(a.family, device=device, policy="fp32" if device is None else "bf16_master", budget_gib=0.03)
     same = max(abs(x - y) / abs(y) for x, y in zip(tight["engine"], base)) < 1e-5
     print(f"plan invariance at 0.03 GiB: {'ok' if same else 'FAIL'}")
