@@ -59,7 +59,8 @@ def check_model_step(family: str, *, preset: str = "tiny", overrides: Mapping[st
     ``tol``: activations and saved context are bf16 under every dtype policy (the policy governs parameters, gradients
     and optimizer state), while the twin computes in fp32 throughout: dense families agree to about 0.5 % per tensor.
     Mixture-of-experts families need a looser bound (0.25): a token whose two best router scores nearly tie may be
-    routed differently by the two sides, which moves a few rows between experts.  A wrong backward is off by O(1)."""
+    routed differently by the two sides, which moves a few rows between experts (with ``top_k = n_experts`` in
+    ``overrides`` nothing can flip and the same families agree to about 1 %).  A wrong backward is off by O(1)."""
     import torch
     from ..models.families import resolve_family
     from ..run.driver import Trainer, synthetic_rounds

@@ -20,6 +20,15 @@ def test_moe_families_match_autograd_within_the_routing_band(family):
     assert dense and max(dense.values()) < 5e-2
 
 
+@pytest.mark.parametrize("family,over", [("dsv3", {"top_k": 8, "n_group": 1, "topk_group": 1}), ("olmoe", {"top_k": 8})])
+def test_moe_gradients_are_dense_tight_once_routing_cannot_flip(family, over):
+    """With every expert selected there is no discrete choice left for rounding to flip: the dispatch, grouped GEMMs, combine
+    and router backward then agree with autograd as closely as the dense blocks do."""
+    rep = check_model_step(family, overrides=over)
+    assert rep, rep.summary()
+    assert max(rep.grad_rel_l2.values()) < 2e-2
+
+
 def test_block_backward_reports_one_layers_fields_and_ragged_rounds_pass():
     rep = check_block_backward("llama3", shape="ragged")
     assert rep, rep.summary()
