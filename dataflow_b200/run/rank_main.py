@@ -83,17 +83,16 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         d = resolve_family(family).derive_dims(cfg)
         tp_pg = dp_pg = None
         if dp > 1:
-            # a dp x tp mesh: consecutive ranks form a tensor-parallel group, ranks with the same place in their groups are
-            # data-parallel replicas of each other.  Every rank creates every subgroup, in the same order.
+            # a dp x tp mesh (tp the fastest-varying axis): the scheme names every rank's partners; every rank creates every
+            # subgroup, in the same order
             import torch.distributed as dist
-            for g in range(dp):
-                pg = dist.new_group(list(range(g * tp, (g + 1) * tp)))
-                if g == rank // tp:
-                    tp_pg = pg
-            for j in range(tp):
-                pg = dist.new_group(list(range(j, world, tp)))
-                if j == rank % tp:
-                    dp_pg = pg
+            from ..distributed.parallelism import scheme_from_flags
+            scheme = scheme_from_flags(world, opt_shard="co", tp=tp)
+            for axis in ("tp", "dp"):
+                for members in sorted({tuple(scheme.group_members(axis, r)) for r in range(world)}):
+                    pg = dist.new_group(list(members))
+                    if rank in members:
+                        tp_pg, dp_pg = (pg, dp_pg) if axis == "tp" else (tp_pg, pg)
         groups = {"tp": TpGroup(rank % tp, tp, device, max_rows=d.Ts, max_k=d.d, max_n=d.d, lane=lane, pg=tp_pg)}
         if dp > 1:
             from ..parallel.zero import make_dp_group
