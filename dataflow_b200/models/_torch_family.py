@@ -271,15 +271,24 @@ class KindOptimizerStep(OptimizerStep):
 
 class _KindGradSum:
     """Block optimizer under expert parallelism: the gradients of the replicated fields of the task's layer (all but the
-    expert stacks) are summed over the group first."""
+    expert stacks) are summed over the job first."""
 
     def __init__(self, inner, lay, skip):
         self.inner, self.lay, self.skip = inner, lay, tuple(skip)
 
-    def launch(self, ctx):
+    def __getattr__(self, name):
+        return getattr(self.__dict__["inner"], name)        # layout helpers and device of the wrapped executable
+
+    def _summed(self, ctx):
         from .tp_mlp.blocks import ReplicatedGradSum
         gl = self.lay.of_layer(int(ctx.task.block_params.get("layer", 0)))[1]
-        ReplicatedGradSum(self.inner, gl, None, "ep", skip=self.skip).launch(ctx)
+        return ReplicatedGradSum(self.inner, gl, None, "ep", skip=self.skip)
+
+    def launch(self, ctx):
+        self._summed(ctx).launch(ctx)
+
+    def run(self, ctx):
+        self._summed(ctx).run(ctx)
 
 
 # ------------------------------------------------------------------------------------------------- twin

@@ -51,7 +51,11 @@ class EpPlan:
 
 class EpGroup:
     def __init__(self, rank: int, world: int, device: int | None, *, tokens: int, d_model: int, n_experts: int, top_k: int,
-                 capacity_factor: float = 2.0, lane: str | None = None, timeout_s: float = 30.0):
+                 capacity_factor: float = 2.0, lane: str | None = None, timeout_s: float = 30.0, pg=None):
+        """``pg``: the ``torch.distributed`` process group of the members when they are a subset of the job (a dp x ep mesh);
+        ``rank`` is the rank inside it.  ``all_reduce`` (gradients of the replicated parameters) always spans the whole job:
+        every rank of the job sees different tokens."""
+        self.pg = pg
         if n_experts % world:
             raise ValueError(f"{n_experts} experts do not split over {world} ranks")
         self.rank, self.world, self.device = rank, world, device
@@ -87,14 +91,14 @@ class EpGroup:
         self.backend = backend
         self.base = backend.device_alloc_zeroed(self.ws_bytes)
         handles: list[Any] = [None] * self.world
-        dist.all_gather_object(handles, backend.ipc_handle(self.base))
+        dist.all_gather_object(handles, backend.ipc_handle(self.base), group=self.pg)
         self.ws = [self.base if r == self.rank else backend.ipc_open(h) for r, h in enumerate(handles)]
         dev = torch.device("cuda", self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=dev)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
         self.tile_flags = torch.zeros(self.C // MOE_TILE_ROWS, dtype=torch.int32, device=dev)
         self.tables_dev = torch.tensor([p + self.off_table for p in self.ws], dtype=torch.int64, device=dev)
-        dist.barrier()
+        dist.barrier(group=self.pg)
 
     def close(self) -> None:
         if self.lane == "p2p" and self.backend is not None and self.ws:
@@ -116,8 +120,8 @@ class EpGroup:
     def all_reduce(self, t):
         """Sum over the group (gradients of the parameters every rank holds in full)."""
         import torch.distributed as dist
-        if self.world > 1:
-            dist.all_reduce(t)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(t)                      # the whole job, not only this group
         return t
 
     # -- symmetric buffers (this rank's views)
@@ -146,8 +150,8 @@ class EpGroup:
         all_ids = torch.empty(self.world * t, k, dtype=torch.int32, device=ids.device)
         all_w = torch.empty(self.world * t, k, dtype=torch.float32, device=ids.device)
         if self.world > 1:
-            dist.all_gather_into_tensor(all_ids, ids.contiguous())
-            dist.all_gather_into_tensor(all_w, weights.float().contiguous())
+            dist.all_gather_into_tensor(all_ids, ids.contiguous(), group=self.pg)
+            dist.all_gather_into_tensor(all_w, weights.float().contiguous(), group=self.pg)
         else:
             all_ids.copy_(ids)
             all_w.copy_(weights)
@@ -248,7 +252,7 @@ class EpGroup:
         from ..ops.eager import moe_grouped_mm
         all_x = torch.empty(self.world * self.T, self.d, dtype=x.dtype, device=x.device)
         if self.world > 1:
-            dist.all_gather_into_tensor(all_x, x.contiguous())
+            dist.all_gather_into_tensor(all_x, x.contiguous(), group=self.pg)
         else:
             all_x.copy_(x)
         src = plan.row_src.long()
@@ -258,7 +262,7 @@ class EpGroup:
             lo = self.rank * self.T
             tables = [torch.empty_like(plan._table) for _ in range(self.world)]
             if self.world > 1:
-                dist.all_gather(tables, plan._table.contiguous())
+                dist.all_gather(tables, plan._table.contiguous(), group=self.pg)
             else:
                 tables[0] = plan._table
             owner = (plan.ids // self.e_local).long()
@@ -271,7 +275,7 @@ class EpGroup:
         import torch.distributed as dist
         all_rows = torch.empty(self.world, self.C, self.d, dtype=rows.dtype, device=rows.device)
         if self.world > 1:
-            dist.all_gather_into_tensor(all_rows.view(-1, self.d), rows.contiguous())
+            dist.all_gather_into_tensor(all_rows.view(-1, self.d), rows.contiguous(), group=self.pg)
         else:
             all_rows[0].copy_(rows)
         owner = (plan.ids // self.e_local).long()
@@ -287,7 +291,7 @@ class EpGroup:
             return out
         all_s = torch.empty(self.world, self.C, dtype=torch.float32, device=rows.device)
         if self.world > 1:
-            dist.all_gather_into_tensor(all_s.view(-1), scal.float().contiguous())
+            dist.all_gather_into_tensor(all_s.view(-1), scal.float().contiguous(), group=self.pg)
         else:
             all_s[0].copy_(scal)
         out_s.copy_(all_s[owner, rl.clamp(min=0)] * ok)
@@ -309,7 +313,28 @@ def _kernels(g: EpGroup, ks):
     return resolve_kernels(kernel_set=None if g.lane == "p2p" else "eager")
 
 
-def ep_group_for(family, cfg, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 30.0) -> EpGroup:
+class ExpertReplicaGradSum:
+    """Block optimizer of a dp x ep mesh: the expert stacks' gradients are summed over the replicas that hold the same
+    experts (group ``dp``) before the inner executable (which sums the replicated fields over the whole job) runs."""
+
+    def __init__(self, inner, lay, group_key: str = "dp"):
+        self.inner, self.lay, self.group_key = inner, lay, group_key
+
+    def launch(self, ctx):
+        from ..models.tp_mlp.blocks import ReplicatedGradSum
+        layer = ctx.task.block_params.get("layer", 0)
+        gl = self.lay.of_layer(layer)[1] if hasattr(self.lay, "of_layer") else self.lay.block_dw
+        fields = [n for n in gl.names() if n.endswith("_experts")]
+        ReplicatedGradSum(self.inner, gl, fields, self.group_key).launch(ctx)
+
+
+def sum_expert_gradients_over_replicas(trainer, group_key: str = "dp") -> None:
+    table = trainer.resolver.table
+    table["optimizer_block"] = ExpertReplicaGradSum(table["optimizer_block"], trainer.layouts, group_key)
+
+
+def ep_group_for(family, cfg, rank: int, world: int, device: int | None, lane: str | None = None, timeout_s: float = 30.0,
+                 pg=None) -> EpGroup:
     """The expert-parallel group of a job that trains ``cfg`` (with ``cfg.ep == world``) of ``family`` (a ``ModelFamily``):
     reads the token / width / expert counts from the family's dims, whichever lane the family is written in."""
     d = family.derive_dims(cfg)
@@ -323,7 +348,7 @@ def ep_group_for(family, cfg, rank: int, world: int, device: int | None, lane: s
             raise ValueError(f"{family.name}: expert parallelism needs a mixture-of-experts preset")
         n_experts, top_k = int(d.E), int(d.topk)
     return EpGroup(rank, world, device, tokens=int(d.T), d_model=int(d.d), n_experts=n_experts, top_k=top_k,
-                   capacity_factor=float(getattr(cfg, "ep_capacity", 2.0)), lane=lane, timeout_s=timeout_s)
+                   capacity_factor=float(getattr(cfg, "ep_capacity", 2.0)), lane=lane, timeout_s=timeout_s, pg=pg)
 
 
 def ep_moe_forward(g: EpGroup, h, ids, weights, w13, w2, base=None, ks=None):

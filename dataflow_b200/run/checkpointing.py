@@ -62,9 +62,10 @@ def _world(trainer) -> tuple[int, int]:
     if z:
         return int(z.get("rank", 0)), int(z.get("world", 1))
     groups = getattr(trainer, "groups", None) or {}
-    if "tp" in groups and "dp" in groups:          # a dp x tp mesh: consecutive ranks form a tensor-parallel group
-        tp, dp = groups["tp"], groups["dp"]
-        return int(dp.rank) * int(tp.world) + int(tp.rank), int(dp.world) * int(tp.world)
+    for inner in ("tp", "ep"):                     # a dp x tp / dp x ep mesh: consecutive ranks form the inner group
+        if inner in groups and "dp" in groups:
+            g, dp = groups[inner], groups["dp"]
+            return int(dp.rank) * int(g.world) + int(g.rank), int(dp.world) * int(g.world)
     for key in ("tp", "ep", "dp"):                 # tensor / expert parallel jobs and plain replicas: the group knows the rank
         g = groups.get(key)
         if g is not None:

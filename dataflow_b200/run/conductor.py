@@ -37,6 +37,7 @@ class RunSpec:
     world: int = 1
     parallel: str = "fsdp"                  # fsdp | zero3 | zero1 | co | tp | ep (world > 1)
     tp_size: int | None = None              # with ``tp``: ranks per tensor-parallel group; the job is a (world / tp_size) x tp_size mesh
+    ep_size: int | None = None              # with ``ep``: ranks per expert-parallel group; the groups are replicas of each other
     rounds: list[int] | None = None         # weighted data parallelism (with ``co``): rounds each rank runs per step
     seed: int = 0
     profile: bool = False

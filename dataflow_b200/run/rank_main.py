@@ -105,11 +105,29 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         from ..parallel.ep import ep_group_for
         if "ep" not in {f.name for f in dataclasses.fields(cfg)}:
             raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} has no experts to split")
-        cfg = dataclasses.replace(cfg, ep=world)
+        ep = int(spec.ep_size or world)
+        if ep < 2 or world % ep:
+            raise ValueError(f"--ep-size {ep} does not divide the job's {world} ranks into expert-parallel groups")
+        cfg = dataclasses.replace(cfg, ep=ep)
+        ep_pg = dp_pg = None
+        if world > ep:
+            # a dp x ep mesh (ep the fastest-varying axis): consecutive ranks share one copy of the experts; ranks with the
+            # same place in their groups hold the same experts and sum those gradients among themselves
+            import torch.distributed as dist
+            from ..distributed.parallelism import scheme_from_flags
+            scheme = scheme_from_flags(world, opt_shard="co", ep=ep)
+            for axis in ("ep", "dp"):
+                for members in sorted({tuple(scheme.group_members(axis, r)) for r in range(world)}):
+                    pg = dist.new_group(list(members))
+                    if rank in members:
+                        ep_pg, dp_pg = (pg, dp_pg) if axis == "ep" else (ep_pg, pg)
         try:
-            groups = {"ep": ep_group_for(resolve_family(family), cfg, rank, world, device, lane)}
+            groups = {"ep": ep_group_for(resolve_family(family), cfg, rank % ep, ep, device, lane, pg=ep_pg)}
         except ValueError as e:
             raise ValueError(f"--parallel ep needs a mixture-of-experts preset, {spec.preset!r} is dense ({e})") from None
+        if world > ep:
+            from ..parallel.zero import make_dp_group
+            groups["dp"] = make_dp_group(rank // ep, world // ep, device, "collective", pg=dp_pg)
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
     recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
     say = log if rank == 0 else (lambda *a, **k: None)
@@ -134,6 +152,9 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     if world > 1 and (spec.parallel in ("co", "dp") or (spec.parallel == "tp" and "dp" in groups)):
         from ..parallel.zero import replicate_gradients
         replicate_gradients(tr)
+    if spec.parallel == "ep" and "dp" in groups:
+        from ..parallel.ep import sum_expert_gradients_over_replicas
+        sum_expert_gradients_over_replicas(tr)
     total_rounds = sum(spec.rounds) if spec.rounds else cfg.grad_accum_rounds * data_world
     wide = dataclasses.replace(cfg, grad_accum_rounds=total_rounds)
     factory = pipeline_from_args(wide, spec.data, policy=spec.packing_policy, allow_round_split=spec.allow_round_split,

@@ -208,3 +208,41 @@ def test_data_parallel_replicas_of_a_tensor_parallel_group_match_one_process(tmp
     again = run(["--gpus", "4", "--parallel", "tp", "--tp-size", "2", "--ga-rounds", "2", "--checkpoint-dir", str(tmp_path / "ck"),
                  "--resume", str(tmp_path / "ck" / "step_000002")], "again")
     assert again["losses"] == pytest.approx(mesh["losses"], rel=1e-5)
+
+
+@pytest.mark.parametrize("preset", ["olmoe:tiny", "dsv3:tiny"])
+def test_replicas_of_an_expert_parallel_group_match_one_process(preset, tmp_path):
+    """A 2 x 2 mesh on four CPU ranks: the experts are split over pairs of ranks, the pairs are replicas of each other.
+    Replicated parameters sum their gradients over all four ranks, expert stacks over the two ranks that hold the same
+    experts.  Oracle: one process with all experts running every rank's rounds."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", preset, "--steps", "3", "--device", "cpu",
+            "--dtype-policy", "fp32"]
+
+    def run(extra, name):
+        out = tmp_path / f"{name}.json"
+        r = subprocess.run(base + extra + ["--out", str(out)], capture_output=True, text=True, timeout=900, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2500:]
+        return json.loads(out.read_text())
+
+    solo = run(["--ga-rounds", "4"], "solo")
+    ck = tmp_path / "ck"
+    mesh = run(["--gpus", "4", "--parallel", "ep", "--ep-size", "2", "--ga-rounds", "1", "--checkpoint-dir", str(ck), "--checkpoint-every", "3"],
+               "mesh")
+    assert mesh["meta"]["world"] == 4 and mesh["tokens_per_step"] == solo["tokens_per_step"]
+    assert mesh["losses"] == pytest.approx(solo["losses"], rel=1e-3)
+    assert mesh["losses"][-1] < mesh["losses"][0]
+
+    # ranks 0 and 2 (1 and 3) hold the same experts and every replicated parameter: after three steps their weights and
+    # optimizer state are the same bytes; ranks 0 and 1 hold different experts
+    def hashes(r):
+        m = json.loads((ck / "step_000003" / f"rank{r}" / "snapshot_manifest.json").read_text())
+        return {e["id"]: e["hash"] for e in m["slices"]}
+    h = [hashes(r) for r in range(4)]
+    assert h[0] == h[2] and h[1] == h[3]
+    assert h[0]["W_embed"] == h[1]["W_embed"] and h[0]["O_head"] == h[1]["O_head"]
+    moe_layers = [k for k in h[0] if k.startswith("W_") and h[0][k] != h[1][k]]
+    assert moe_layers and all(k[2:].isdigit() for k in moe_layers)

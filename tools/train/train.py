@@ -49,6 +49,8 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--group", default=None, help="group of the topology to run on (default: its only group)")
     ap.add_argument("--tp-size", type=int, default=None,
                     help="with --parallel tp: ranks per tensor-parallel group; --gpus N then runs N / tp-size data-parallel replicas of it")
+    ap.add_argument("--ep-size", type=int, default=None,
+                    help="with --parallel ep: ranks per expert-parallel group; --gpus N then runs N / ep-size replicas of the experts")
     ap.add_argument("--tp-mlp", action="store_true", help="same as --parallel tp (the reference's flag name)")
     ap.add_argument("--backend", default="auto", choices=["auto", "peer", "nccl"],
                     help="how the ranks exchange data: peer = kernels over peer memory (default on GPUs), nccl = library collectives")
@@ -111,7 +113,7 @@ def spec_from_args(a, argv):
         recipe["optimizer"] = a.opt
     return RunSpec(preset=a.preset, steps=a.steps, overrides=ov, recipe=recipe, data=a.data, packing_policy=a.packing_policy,
                    allow_round_split=a.allow_round_split, capture=a.capture, budget_gib=a.fast_budget,
-                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel="tp" if a.tp_mlp else a.opt_shard, tp_size=a.tp_size, rounds=[int(x) for x in a.rounds.split(",")] if a.rounds else None, seed=a.seed,
+                   device=None if a.device == "cpu" else int(a.device), world=a.gpus, parallel="tp" if a.tp_mlp else a.opt_shard, tp_size=a.tp_size, ep_size=a.ep_size, rounds=[int(x) for x in a.rounds.split(",")] if a.rounds else None, seed=a.seed,
                    profile=a.profile or a.warm_profiles or a.refresh_profiles, recompute=not a.no_recompute, kernels=a.kernels,
                    backend=a.backend, devices=devices, backing_budget_gib=a.backing_budget, prof_dir=a.prof_dir,
                    profile_start_before_step=a.profile_start_before_step, profile_stop_after_step=a.profile_stop_after_step,
