@@ -48,6 +48,9 @@ class ShapedLlama3Config:
     # tensor + sequence parallelism (tp_mlp family): heads and FFN columns split over ``tp`` ranks, the residual
     # stream split by rows
     tp: int = 1
+    # with tp > 1: split the output projection's vocabulary columns over the ranks too (softmax statistics are exchanged
+    # instead of holding the whole matrix, its gradient and its optimizer state on every rank)
+    vocab_parallel: bool = False
     # expert parallelism: experts split over ``ep`` ranks (each keeps its own tokens); dispatched matrices hold
     # ``ep_capacity`` times the balanced share of rows
     ep: int = 1
@@ -88,6 +91,12 @@ class Llama3Dims:
     tp: int = 1                          # > 1: hq / hkv / F are this rank's share; the residual stream holds Ts rows
     ep: int = 1                          # > 1: this rank holds E / ep experts and serves rows of every rank's tokens
     ep_capacity: float = 2.0
+    head_shard: int = 1                  # > 1 (vocab-parallel head under tp): ``w_head`` holds vocab / head_shard columns
+
+    @property
+    def vocab_local(self) -> int:
+        """Columns of the output projection this rank holds."""
+        return self.vocab // self.head_shard
 
     @property
     def El(self) -> int:
@@ -159,7 +168,7 @@ def embed_fields(d: Llama3Dims) -> tuple[Field, ...]:
 
 def head_fields(d: Llama3Dims) -> tuple[Field, ...]:
     return (Field("final_norm", (d.d,), "bf16", "vector", "ones"),
-            Field("w_head", (d.d, d.vocab), "bf16", "matrix", "normal"))
+            Field("w_head", (d.d, d.vocab_local), "bf16", "matrix", "normal"))
 
 
 def context_layout(d: Llama3Dims, level: int = 0) -> PackedLayout:

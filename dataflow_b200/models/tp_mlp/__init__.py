@@ -32,7 +32,10 @@ def derive_tp_dims(cfg: ShapedLlama3Config):
     for what, v in (("n_heads", d.hq), ("n_kv_heads", d.hkv), ("d_ff", d.F), ("tokens per round", d.T)):
         if v % p:
             raise ValueError(f"{what} = {v} does not split over tp = {p}")
-    return dataclasses.replace(d, hq=d.hq // p, hkv=d.hkv // p, F=d.F // p, tp=p, head_chunk=min(d.head_chunk, d.T // p))
+    shard = p if getattr(cfg, "vocab_parallel", False) else 1
+    if d.vocab % shard:
+        raise ValueError(f"vocab_size = {d.vocab} does not split over tp = {p}")
+    return dataclasses.replace(d, hq=d.hq // p, hkv=d.hkv // p, F=d.F // p, tp=p, head_chunk=min(d.head_chunk, d.T // p), head_shard=shard)
 
 
 def shard_dims(d):
@@ -61,7 +64,7 @@ def lower_tp(cfg: ShapedLlama3Config, recompute_levels: Mapping[int, int] | None
                   "batch": cfg.batch, "tp": d.tp, "tokens_per_round_global": d.T})
 
 
-def slice_for_rank(name: str, full, d_full, rank: int, p: int):
+def slice_for_rank(name: str, full, d_full, rank: int, p: int, head_shard: int = 1):
     """This rank's part of a full-model field (``d_full``: the unsharded dims)."""
     import torch
     hd = d_full.hd
@@ -79,6 +82,9 @@ def slice_for_rank(name: str, full, d_full, rank: int, p: int):
     if name == "w2":
         fl = d_full.F // p
         return full[rank * fl:(rank + 1) * fl]
+    if name == "w_head" and head_shard > 1:
+        vl = d_full.vocab // head_shard
+        return full[:, rank * vl:(rank + 1) * vl]
     return full
 
 
@@ -100,7 +106,7 @@ def initial_values_tp(program, cfg: ShapedLlama3Config, views_of, seed: int = 0,
         for f in fl.fields:
             t = torch.empty(tuple(f.shape), dtype=torch.float32)
             init_field(t, f, gen, d.n_layers)
-            wv[f.name].copy_(slice_for_rank(f.name, t, d_full, rank, d.tp).to(wv[f.name].dtype))
+            wv[f.name].copy_(slice_for_rank(f.name, t, d_full, rank, d.tp, d.head_shard).to(wv[f.name].dtype))
         oname = "O" + oid[1:]
         if oname in ids:
             ol = lay.layout_of(oname)

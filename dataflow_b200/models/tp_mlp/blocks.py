@@ -155,6 +155,56 @@ class TpBlockBwd(_TpBlock):
         K.rmsnorm_bwd(dh, x, w["attn_norm"], a["rstd_attn"], dx_add=dh_mid, dw=gr.get("attn_norm"), accumulate=acc, out=dx)
 
 
+class VocabParallelHeadLoss(_Base):
+    """(y, targets, W_head) -> (dy, loss[, dW_head]) with the vocabulary columns of the output projection split over the
+    group: the normalised rows are all-gathered, every rank computes the logits of its columns, and the softmax statistics
+    (row maximum, sum of exponentials, the target's logit) are exchanged — two sums and one maximum of ``T`` floats per
+    chunk — so neither the full logits nor the full matrix exist on any rank.  The gradient of the gathered rows is summed
+    over the group and every rank keeps its rows.  Written with library collectives around the GEMM ops (no fused kernel)."""
+
+    def run(self, ctx):
+        import torch
+        d, K, g = self.dims, self.K, _group(ctx)
+        Ts, Vl = d.Ts, d.vocab_local
+        y = self.tview(ctx.inputs[0], (Ts, d.d))
+        tgt = self.tview(ctx.inputs[1], (Ts,), "int32")
+        w = self.views(ctx.inputs[2], self.lay.head_w)
+        dy = self.tview(ctx.outputs[0], (Ts, d.d))
+        loss = self.tview(ctx.outputs[1], (1,), "fp32")
+        create = self.creating(ctx, "dW_head")
+        dw = self.views(self.by_id(ctx, "dW_head"), self.lay.head_dw)
+        total_rows = float(ctx.run_args.get("valid_rows", d.T))
+        xn, rstd = K.rmsnorm_fwd(y, w["final_norm"], d.eps)
+        xg = g.all_gather(xn)                                               # (T, d): every row, this rank's columns follow
+        tg = g.all_gather(tgt.reshape(-1, 1).contiguous()).reshape(-1).long()
+        v0 = g.rank * Vl
+        dxg = torch.empty(d.T, d.d, dtype=torch.float32, device=y.device)
+        total = torch.zeros((), dtype=torch.float32, device=y.device)
+        first = True
+        for lo in range(0, d.T, max(int(d.head_chunk), 1)):
+            hi = min(lo + max(int(d.head_chunk), 1), d.T)
+            logits = K.linear_fwd_bf16(xg[lo:hi], w["w_head"]).float()      # (rows, Vl)
+            m = g.all_reduce(logits.max(-1).values.contiguous(), op="max")
+            e = torch.exp(logits - m[:, None])
+            se = g.all_reduce(e.sum(-1))
+            t = tg[lo:hi]
+            valid = (t >= 0).float()
+            mine = (t >= v0) & (t < v0 + Vl)
+            idx = (t - v0).clamp(0, Vl - 1)[:, None]
+            tl = g.all_reduce(torch.where(mine, logits.gather(1, idx)[:, 0], torch.zeros_like(m)))
+            total += (((m + torch.log(se)) - tl) * valid).sum() / total_rows
+            p = e / se[:, None]
+            p.scatter_add_(1, idx, -mine.float()[:, None])
+            dl = (p * (valid / total_rows)[:, None]).to(xg.dtype)
+            K.linear_wgrad_bf16(xg[lo:hi], dl, dw["w_head"], accumulate=not (create and first))
+            dxg[lo:hi] = K.linear_dgrad_bf16(dl, w["w_head"]).float()
+            first = False
+        g.all_reduce(dxg)
+        K.rmsnorm_bwd(dxg[g.rank * Ts:(g.rank + 1) * Ts].to(y.dtype).contiguous(), y, w["final_norm"], rstd, dw=dw["final_norm"],
+                      accumulate=not create, out=dy)
+        loss.copy_((total / g.world).reshape(1), non_blocking=True)        # every rank holds the round's loss: the job sums ranks
+
+
 class _ShardRows:
     """Row-sharded executables see one segment of ``Ts`` rows (they need the row count, not the sequence structure)."""
 
@@ -208,6 +258,9 @@ def build_tp_resolver(dims, hyper: Mapping[str, Any] | None, kernels, device, la
     table["optimizer_block"] = ReplicatedGradSum(table["optimizer_block"], lay.block_dw, ("attn_norm", "ffn_norm"))
     table["optimizer_embed"] = ReplicatedGradSum(table["optimizer_embed"], lay.embed_dw, None)
     table["optimizer_head"] = ReplicatedGradSum(table["optimizer_head"], lay.head_dw, None)
+    if int(getattr(dims, "head_shard", 1)) > 1:
+        table["head_loss"] = VocabParallelHeadLoss(dims, lay, kernels, device, hyper)
+        table["optimizer_head"] = ReplicatedGradSum(table["optimizer_head"].inner, lay.head_dw, ("final_norm",))
     table.update({"block_fwd": TpBlockFwd(dims, lay, kernels, device, hyper),
                   "block_recompute": TpBlockRecompute(dims, lay, kernels, device, hyper),
                   "block_bwd": TpBlockBwd(dims, lay, kernels, device, hyper)})

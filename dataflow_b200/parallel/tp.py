@@ -123,10 +123,10 @@ class TpGroup:
             dist.all_gather_into_tensor(out, x.contiguous(), group=self.pg)
         return out
 
-    def all_reduce(self, t):
+    def all_reduce(self, t, op: str = "sum"):
         import torch.distributed as dist
         if self.world > 1:
-            dist.all_reduce(t, group=self.pg)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM, group=self.pg)
         return t
 
     # -- fused ops

@@ -95,3 +95,34 @@ def test_fused_kernels_train_like_the_collective_lane(tmp_path):
     for a, b in zip(p2p["losses"], col["losses"]):
         assert a == pytest.approx(b, rel=2e-2)
     assert p2p["losses"][-1] < p2p["losses"][0]
+
+
+def test_vocab_parallel_head_matches_the_replicated_head(tmp_path):
+    """`--vocab-parallel`: every rank holds half of the output projection's columns and exchanges softmax statistics; the
+    curve is the replicated head's (and one process's), and the head objects are half the size."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "4", "--device", "cpu",
+            "--dtype-policy", "fp32"]
+
+    def run(extra, name):
+        out = tmp_path / f"{name}.json"
+        r = subprocess.run(base + extra + ["--out", str(out)], capture_output=True, text=True, timeout=900, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2500:]
+        return json.loads(out.read_text())["losses"]
+
+    solo = run([], "solo")
+    rep = run(["--gpus", "2", "--parallel", "tp"], "rep")
+    vp = run(["--gpus", "2", "--parallel", "tp", "--vocab-parallel"], "vp")
+    assert vp == pytest.approx(rep, rel=2e-4) and vp == pytest.approx(solo, rel=5e-4)
+    assert vp[-1] < vp[0]
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    fam = resolve_family("tp_mlp")
+    cfg = fam.presets["tiny"]()
+    full = fam.lower(cfg).object_sizes()
+    half = fam.lower(dataclasses.replace(cfg, vocab_parallel=True)).object_sizes()
+    assert half["W_head"] < 0.51 * full["W_head"] + 4096 and half["O_head"] < 0.51 * full["O_head"] + 4096
+    assert half["W_embed"] == full["W_embed"]

@@ -49,6 +49,8 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--group", default=None, help="group of the topology to run on (default: its only group)")
     ap.add_argument("--tp-size", type=int, default=None,
                     help="with --parallel tp: ranks per tensor-parallel group; --gpus N then runs N / tp-size data-parallel replicas of it")
+    ap.add_argument("--vocab-parallel", action="store_true",
+                    help="with --parallel tp: split the output projection's vocabulary columns over the group (softmax statistics exchanged)")
     ap.add_argument("--ep-size", type=int, default=None,
                     help="with --parallel ep: ranks per expert-parallel group; --gpus N then runs N / ep-size replicas of the experts")
     ap.add_argument("--tp-mlp", action="store_true", help="same as --parallel tp (the reference's flag name)")
@@ -103,6 +105,8 @@ def spec_from_args(a, argv):
         v = getattr(a, flag)
         if v is not None:
             ov[fieldname] = v
+    if a.vocab_parallel:
+        ov["vocab_parallel"] = True
     recipe = {"peak_lr": a.peak_lr, "min_lr": a.min_lr if a.min_lr is not None else a.peak_lr * 0.1,
               "warmup_steps": a.warmup_steps}
     if a.muon_lr is not None:
