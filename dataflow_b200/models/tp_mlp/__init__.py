@@ -123,6 +123,10 @@ PRESETS = {
                  seq_len=128, batch=2, grad_accum_rounds=2, tp=2),
     "llama3_70b_tp8": dict(name="llama3_70b_tp8", n_layers=80, d_model=8192, n_heads=64, n_kv_heads=8, head_dim=128, d_ff=28672,
                            vocab_size=128256, seq_len=8192, batch=2, grad_accum_rounds=8, tp=8, dtype_policy="bf16_split_master"),
+    # the same with the output projection's columns split over the group: 1/8 of the head matrix, gradient and optimizer state
+    "llama3_70b_tp8_vp": dict(name="llama3_70b_tp8_vp", n_layers=80, d_model=8192, n_heads=64, n_kv_heads=8, head_dim=128, d_ff=28672,
+                              vocab_size=128256, seq_len=8192, batch=2, grad_accum_rounds=8, tp=8, vocab_parallel=True,
+                              dtype_policy="bf16_split_master"),
 }
 
 FAMILY = register_family(ModelFamily(
