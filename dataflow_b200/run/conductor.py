@@ -49,6 +49,7 @@ class RunSpec:
     checkpoint_keep_last: int | None = None
     checkpoint_redundancy: int | None = None   # ranks that write their copy of replicated objects (default: all)
     resume: str | None = None
+    max_restarts: int = 0                   # relaunch a failed multi-rank job from its newest complete checkpoint, this many times
     out: str | None = None
     devices: list[int] | None = None        # CUDA ordinal of every rank (from a topology group); default: rank r on device r
     backend: str = "auto"                   # auto | peer (kernels over peer memory) | nccl (library collectives around library ops)
@@ -105,14 +106,29 @@ def run(spec: RunSpec, log=print) -> RunResult:
             return run_rank(spec, log=log)
         out = spec.out or os.path.join(tempfile.mkdtemp(prefix="dataflow_run_"), "result.json")
         spec = dataclasses.replace(spec, out=out)
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={spec.world}",
-               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-               "-m", "dataflow_b200.run.rank_main", "--spec", spec.to_json()]
         env = dict(os.environ)
         root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
         env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
-        proc = subprocess.run(cmd, env=env)
-        if proc.returncode != 0:
-            raise RuntimeError(f"the {spec.world}-rank job exited with code {proc.returncode}")
+        attempt = 0
+        while True:
+            # a fresh port per attempt: the previous rendezvous may still hold its own
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={spec.world}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+                   "-m", "dataflow_b200.run.rank_main", "--spec", spec.to_json()]
+            proc = subprocess.run(cmd, env=env)
+            if proc.returncode == 0:
+                break
+            from .checkpointing import resolve_resume
+            newest = resolve_resume("latest", spec.checkpoint_dir) if spec.checkpoint_dir else None
+            if attempt >= int(spec.max_restarts) or not newest:
+                raise RuntimeError(f"the {spec.world}-rank job exited with code {proc.returncode}"
+                                   + (f" after {attempt} restart(s)" if attempt else ""))
+            attempt += 1
+            log(f"the job exited with code {proc.returncode}: restart {attempt} of {spec.max_restarts} from {newest}")
+            spec = dataclasses.replace(spec, resume=newest)
         d = json.loads(open(out).read())
+        d["meta"]["restarts"] = attempt
+        if attempt:
+            with open(out, "w") as f:                   # the result file says how the job got to its end
+                json.dump(d, f)
         return RunResult(d["losses"], d["step_wall_s"], d["tokens_per_step"], d["meta"])

@@ -192,17 +192,22 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
 def _host_fault_plan(rank: int):
     """Host-side fault injection for failure-detection drills: ``DATAFLOW_FAULT_PLAN="rank=1,step=2,kind=raise"`` makes that
     rank raise (or ``kind=exit``: leave without a word) right after the named step, between steps, with nothing of its own
-    in flight.  Nothing is injected on a device."""
+    in flight.  ``once=<path>``: the fault fires only while that marker file does not exist and creates it (a restarted job
+    then runs through).  Nothing is injected on a device."""
     plan = os.environ.get("DATAFLOW_FAULT_PLAN")
     if not plan:
         return None
     kv = dict(item.split("=", 1) for item in plan.split(","))
     if int(kv.get("rank", -1)) != rank:
         return None
-    at, kind = int(kv.get("step", 1)), kv.get("kind", "raise")
+    at, kind, once = int(kv.get("step", 1)), kv.get("kind", "raise"), kv.get("once")
 
     def on_step(step, loss, packed):
         if step == at:
+            if once:
+                if os.path.exists(once):
+                    return
+                open(once, "w").close()
             if kind == "exit":
                 os._exit(17)
             raise RuntimeError(f"fault plan: rank {rank} fails after step {step}")

@@ -28,6 +28,30 @@ def test_a_rank_that_fails_between_steps_ends_the_job_quickly(kind, tmp_path):
         assert "fault plan: rank 1 fails after step 2" in text
 
 
+def test_a_failed_job_restarts_from_its_newest_checkpoint_and_finishes_the_same_curve(tmp_path):
+    """`--max-restarts 1`: rank 1 dies after step 3 (once); the conductor relaunches the job from the checkpoint of step 2
+    and the finished curve is the one an undisturbed run produces."""
+    import json
+    base = [sys.executable, os.path.join(ROOT, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "5", "--device", "cpu",
+            "--gpus", "2", "--parallel", "co", "--dtype-policy", "fp32", "--checkpoint-every", "2"]
+    calm = subprocess.run(base + ["--checkpoint-dir", str(tmp_path / "ck0"), "--out", str(tmp_path / "calm.json")], capture_output=True,
+                          text=True, timeout=600, cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT))
+    assert calm.returncode == 0, calm.stderr[-2000:]
+    env = dict(os.environ, DATAFLOW_FAULT_PLAN=f"rank=1,step=3,kind=exit,once={tmp_path / 'fired'}", DATAFLOW_PG_TIMEOUT_S="8", PYTHONPATH=ROOT)
+    r = subprocess.run(base + ["--checkpoint-dir", str(tmp_path / "ck1"), "--out", str(tmp_path / "hit.json"), "--max-restarts", "1"],
+                       capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
+    assert (tmp_path / "fired").exists() and "restart 1 of 1" in r.stdout and "resumed from" in r.stdout
+    hit, ref = json.loads((tmp_path / "hit.json").read_text()), json.loads((tmp_path / "calm.json").read_text())
+    assert hit["meta"].get("restarts") == 1 and len(hit["losses"]) == 5
+    assert hit["losses"] == pytest.approx(ref["losses"], rel=1e-5)
+    # without the allowance the same fault ends the job
+    os.remove(tmp_path / "fired")
+    r2 = subprocess.run(base + ["--checkpoint-dir", str(tmp_path / "ck2"), "--out", str(tmp_path / "dead.json")], capture_output=True,
+                        text=True, timeout=600, cwd=ROOT, env=env)
+    assert r2.returncode != 0 and not (tmp_path / "dead.json").exists()
+
+
 @pytest.mark.gpu
 def test_a_device_wait_that_cannot_be_satisfied_returns_a_status_and_the_context_stays_usable():
     """The expert-parallel combine kernel of rank 0 of a 2-rank group whose peer never publishes its rows: the bounded wait

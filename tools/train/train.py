@@ -72,6 +72,8 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--checkpoint-keep-last", type=int, default=None)
     ap.add_argument("--checkpoint-redundancy", type=int, default=None,
                     help="how many ranks write their copy of replicated objects (default: all, which also checks them for drift)")
+    ap.add_argument("--max-restarts", type=int, default=0,
+                    help="relaunch a failed multi-rank job from its newest complete checkpoint, up to this many times")
     ap.add_argument("--resume", default=None, help="step directory, checkpoint root, or 'latest'")
     ap.add_argument("--data", default=None, help="scheme:main[,k=v...] (synthetic | shards | jsonl | txt | parquet | capture)")
     ap.add_argument("--packing-policy", default="ffd", choices=["ffd", "greedy"])
@@ -123,7 +125,7 @@ def spec_from_args(a, argv):
                    profile_start_before_step=a.profile_start_before_step, profile_stop_after_step=a.profile_stop_after_step,
                    warm_profiles=a.warm_profiles, refresh_profiles=a.refresh_profiles,
                    resident_params=not a.no_resident_params, checkpoint_every=a.checkpoint_every,
-                   checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, checkpoint_redundancy=a.checkpoint_redundancy, resume=a.resume, out=a.out,
+                   checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, checkpoint_redundancy=a.checkpoint_redundancy, resume=a.resume, max_restarts=a.max_restarts, out=a.out,
                    argv=list(argv))
 
 
