@@ -225,13 +225,16 @@ class _Recorded:
         return dict(self.g["spec"])
 
 
-def load_checkpoint(trainer, sdir: str) -> dict:
+def load_checkpoint(trainer, sdir: str, only_prefixes: tuple[str, ...] | None = None) -> dict:
     """Fill the trainer's host store from a step directory; returns the record (``client_payload`` has the
-    caller's resume state).  Device-resident copies are dropped so the next step reloads from the store."""
+    caller's resume state).  Device-resident copies are dropped so the next step reloads from the store.
+    ``only_prefixes``: restore only objects whose id starts with one of these (``("W_",)``: the weights alone, which
+    is what an evaluation needs and what restores across world sizes and optimizer-sharding modes)."""
     import ctypes
     rec = read_record(sdir)
     src = TrainerSource(trainer)
-    want: dict[str, SourceSlice] = {s.object_id: s for s in src.slices()}
+    want: dict[str, SourceSlice] = {s.object_id: s for s in src.slices()
+                                    if only_prefixes is None or s.object_id.startswith(tuple(only_prefixes))}
     store = trainer.store
     for oid, s in want.items():
         logical = s.logical_id

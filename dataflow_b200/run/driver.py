@@ -211,6 +211,12 @@ class Trainer:
                 if verbose:
                     print(f"static placement not used: {e}")
         self.zero = (self.program.metadata or {}).get("zero")
+        if self.zero and int(self.zero.get("world", 1)) > 1 and hasattr(cfg, "policy"):
+            # the sharded lanes cut the packed objects into flat slices of bf16 elements and keep fp32 state per slice
+            dt = cfg.policy().for_field("w", 0)
+            if dt.param != "bf16" or dt.grad != "bf16":
+                raise ValueError(f"sharded data parallelism (fsdp / zero*) needs bf16 parameters and gradients (dtype policies bf16, "
+                                 f"bf16_master, bf16_split_master); this run asks for {dt.param} / {dt.grad} — use --parallel co for replicas")
         # weights that end a step on the device stay there for the next one (Session.resident)
         self.keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
         # on a device, launch up to two tasks behind an unfinished one: host dispatch hides behind device work

@@ -97,3 +97,22 @@ def test_reproducibility_drivers_run_staged_and_resume(tmp_path, capsys):
     spec.loader.exec_module(thr)
     assert thr.main(["--preset", "llama3:tiny", "--device", "cpu", "--budgets", "0.02", "--steps", "4", "--out", str(tmp_path / "thr")]) == 0
     assert "measured / predicted" in (tmp_path / "thr" / "report.md").read_text()
+
+
+def test_eval_checkpoint_reads_solo_and_sharded_checkpoints_alike(tmp_path, capsys):
+    """The same training run as one process and as two FSDP ranks: both checkpoints load into the twin (weights only) and
+    give the same held-out loss."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, os.path.join(root, "tools", "train", "train.py"), "train", "--preset", "llama3:tiny", "--steps", "2", "--device", "cpu",
+            "--dtype-policy", "bf16_master", "--checkpoint-every", "2"]
+    for name, extra in (("solo", ["--ga-rounds", "4"]), ("fsdp", ["--gpus", "2", "--parallel", "fsdp", "--ga-rounds", "2"])):
+        r = subprocess.run(base + extra + ["--checkpoint-dir", str(tmp_path / name)], capture_output=True, text=True, timeout=600, cwd=root)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2500:]
+    got = {}
+    for name in ("solo", "fsdp"):
+        assert tool("train/eval_checkpoint.py").main(["--checkpoint", str(tmp_path / name / "step_000002"), "--preset", "llama3:tiny", "--steps", "2"]) == 0
+        got[name] = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert got["solo"]["tokens"] == got["fsdp"]["tokens"] > 0 and got["solo"]["checkpoint"] == 2
+    assert got["fsdp"]["loss"] == pytest.approx(got["solo"]["loss"], rel=2e-3) and 1.0 < got["solo"]["loss"] < 8.0

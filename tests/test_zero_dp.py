@@ -76,3 +76,15 @@ def test_published_buffers_outside_the_slab_go_through_the_staging_tail(tmp_path
     for a, b in zip(p2p["losses"], col["losses"]):
         assert a == pytest.approx(b, rel=2e-3)
     assert p2p["w0_abs"] == pytest.approx(col["w0_abs"], rel=1e-4)
+
+
+def test_sharded_modes_refuse_fp32_parameter_policies():
+    """The sharded lanes slice packed objects as bf16 elements: an fp32 parameter policy is refused by name, not mis-read."""
+    import dataclasses
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.parallel.zero import zero_lower_kwargs
+    from dataflow_b200.run.driver import Trainer
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
+    with pytest.raises(ValueError, match="needs bf16 parameters"):
+        Trainer("llama3", cfg, budget_gib=None, device=None, lower_kwargs=zero_lower_kwargs("fsdp", 0, 2), init=False)

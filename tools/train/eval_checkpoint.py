@@ -3,6 +3,9 @@ report the mean token loss and perplexity over held-out data.
 
     python tools/train/eval_checkpoint.py --checkpoint ckpt/step_000100 --preset llama3:tiny --data 'shards:data/mine,split=val' --steps 20
 
+Only the weights are read, so checkpoints of solo, replica (``co``) and sharded (``fsdp`` / ``zero*``) runs of any world size
+evaluate alike; tensor- and expert-parallel checkpoints hold per-rank cuts of the model and are not assembled here.
+
 Reference role: ``tools/train/eval_checkpoint.py``.
 """
 from __future__ import annotations
@@ -33,8 +36,16 @@ def main(argv=None) -> int:
     from dataflow_b200.run.presets import resolve_preset
     fam_name, cfg = resolve_preset(a.preset)
     fam = resolve_family(fam_name)
+    # the run's own overrides of the preset (dtype policy, layers, sequence length, ...) are in the checkpoint's launch record
+    import dataclasses
+    from dataflow_b200.checkpoint.record import read_record
+    resolved = dict(((read_record(a.checkpoint).get("launch") or {}).get("resolved")) or {})
+    known = {f.name for f in dataclasses.fields(cfg)}
+    over = {k: v for k, v in resolved.items() if k in known and k not in ("name", "tp", "ep", "grad_accum_rounds")}
+    if over:
+        cfg = dataclasses.replace(cfg, **over)
     tr = Trainer(fam_name, cfg, budget_gib=None, device=None, init=True)
-    info = load_checkpoint(tr, a.checkpoint)
+    info = load_checkpoint(tr, a.checkpoint, only_prefixes=("W_",))       # weights alone: any data-parallel sharding restores
     twin = fam.twin(cfg)
     twin.load_state_dict(fam.bridge(cfg, tr.views_of))
     dev = torch.device("cpu" if a.device == "cpu" else f"cuda:{a.device}")
