@@ -103,3 +103,10 @@ def test_checkpoint_redundancy_limits_who_writes_replicas_and_resume_still_works
         assert b.returncode == 0, b.stdout[-1500:] + b.stderr[-2500:]
         assert json.loads((tmp_path / f"a{red}.json").read_text())["losses"] == json.loads((tmp_path / f"b{red}.json").read_text())["losses"]
     assert sizes[1] < 0.2 * sizes[None]                 # rank 1 wrote (almost) nothing
+
+
+def test_warm_profiles_prices_the_tasks_and_stops(tmp_path):
+    out = tmp_path / "never.json"
+    r = _run("--steps", "3", "--warm-profiles", "--out", str(out))
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
+    assert "--warm-profiles stops here" in r.stdout and "no steps ran" in r.stdout and "step     1" not in r.stdout
