@@ -40,6 +40,8 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
     lower_kwargs: dict[str, Any] = {}
     if spec.backend not in ("auto", "peer", "nccl"):
         raise ValueError(f"--backend is auto, peer or nccl, not {spec.backend!r}")
+    if spec.backend == "peer" and device is None:
+        raise ValueError("--backend peer moves data with kernels over peer GPU memory: it needs --device on GPUs (CPU ranks use nccl / auto)")
     lane = "collective" if spec.backend == "nccl" else ("p2p" if spec.backend == "peer" else None)
     if spec.refresh_profiles:
         os.environ["DATAFLOW_PROFILE_REFRESH"] = "1"
