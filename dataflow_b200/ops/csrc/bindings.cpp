@@ -16,6 +16,28 @@ using at::Tensor;
 #define CHECK_I32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kInt, #x " must be an int32 CUDA tensor")
 #define CHECK_CONTIG(x) TORCH_CHECK((x).is_contiguous(), #x " must be contiguous")
 
+// One operand check used by every binding below: the kernels dereference raw pointers with 16-byte
+// vector accesses, so an operand that is on the host, of another dtype, strided, too short or not
+// 16-byte aligned is refused here, before anything is launched.
+static void need(const Tensor& t, const char* name, at::ScalarType dt, int64_t numel = -1, bool contiguous = true) {
+  TORCH_CHECK(t.defined(), name, " is undefined");
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (got a host tensor)");
+  TORCH_CHECK(t.scalar_type() == dt, name, " must have dtype ", dt, " (got ", t.scalar_type(), ")");
+  if (contiguous) TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  if (numel >= 0) TORCH_CHECK(t.numel() == numel, name, " must have ", numel, " elements (got ", t.numel(), ")");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, " must be 16-byte aligned");
+}
+static void need_opt(const c10::optional<Tensor>& t, const char* name, at::ScalarType dt, int64_t numel = -1) {
+  if (t.has_value()) need(*t, name, dt, numel);
+}
+// gradient-like operands may be bf16 or fp32
+static void need_grad(const Tensor& t, const char* name, int64_t numel) {
+  TORCH_CHECK(t.defined() && t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat, name, " must be bf16 or fp32");
+  TORCH_CHECK(t.numel() == numel, name, " must have ", numel, " elements (got ", t.numel(), ")");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name, " must be 16-byte aligned");
+}
+
 static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 static const void* optp(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 static int num_sms() {
@@ -25,21 +47,28 @@ static int num_sms() {
 
 // ---------------------------------------------------------------- norms
 static void rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& w, Tensor& y, c10::optional<Tensor> rstd, double eps) {
-  CHECK_CUDA(x); CHECK_BF16(x); CHECK_CONTIG(x); CHECK_BF16(y); CHECK_CONTIG(y);
+  need(x, "x", at::kBFloat16); need(y, "y", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "rmsnorm_fwd needs cols % 8 == 0");
+  need_opt(w, "w", at::kBFloat16, cols); need_opt(rstd, "rstd", at::kFloat, rows);
   dfb::rmsnorm_fwd(x.data_ptr(), optp(w), y.data_ptr(), rstd.has_value() ? rstd->data_ptr<float>() : nullptr, rows, cols,
                    (float)eps, cur_stream());
 }
 static void rmsnorm_apply(const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& y) {
-  CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(rstd); CHECK_CONTIG(y);
+  need(x, "x", at::kBFloat16); need(y, "y", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "rmsnorm_apply needs cols % 8 == 0");
+  need(w, "w", at::kBFloat16, cols); need(rstd, "rstd", at::kFloat, rows);
   dfb::rmsnorm_apply(x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), y.data_ptr(), rows, cols, cur_stream());
 }
 static void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, Tensor& dx,
                         const c10::optional<Tensor>& dx_add, c10::optional<Tensor> dw, bool accumulate, Tensor& partial) {
-  CHECK_BF16(dy); CHECK_CONTIG(dy); CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(rstd); CHECK_F32(partial);
+  need(x, "x", at::kBFloat16); need(dy, "dy", at::kBFloat16, x.numel()); need(dx, "dx", at::kBFloat16, x.numel());
+  need_opt(dx_add, "dx_add", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
   TORCH_CHECK(cols % 8 == 0, "rmsnorm_bwd needs cols % 8 == 0");
+  need(w, "w", at::kBFloat16, cols); need(rstd, "rstd", at::kFloat, rows); need(partial, "partial", at::kFloat);
+  if (dw.has_value()) need_grad(*dw, "dw", cols);
   TORCH_CHECK(partial.numel() >= (int64_t)dfb::norm_bwd_parts(rows) * 2 * cols, "rmsnorm_bwd scratch too small");
   dfb::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), optp(dx_add),
                    dw.has_value() ? dw->data_ptr() : nullptr, dw.has_value() && dw->scalar_type() == at::kFloat,
@@ -47,22 +76,38 @@ static void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, cons
 }
 static void layernorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, Tensor& y, Tensor& mean,
                           Tensor& rstd, double eps) {
-  CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(mean); CHECK_F32(rstd);
+  need(x, "x", at::kBFloat16); need(y, "y", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "layernorm_fwd needs cols % 8 == 0");
+  need(w, "w", at::kBFloat16, cols); need_opt(b, "b", at::kBFloat16, cols);
+  need(mean, "mean", at::kFloat, rows); need(rstd, "rstd", at::kFloat, rows);
   dfb::layernorm_fwd(x.data_ptr(), w.data_ptr(), optp(b), y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
                      rows, cols, (float)eps, cur_stream());
 }
 static void layernorm_apply(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& b, const Tensor& mean,
                             const Tensor& rstd, Tensor& y) {
+  need(x, "x", at::kBFloat16); need(y, "y", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
+  TORCH_CHECK(cols % 8 == 0, "layernorm_apply needs cols % 8 == 0");
+  need(w, "w", at::kBFloat16, cols); need_opt(b, "b", at::kBFloat16, cols);
+  need(mean, "mean", at::kFloat, rows); need(rstd, "rstd", at::kFloat, rows);
   dfb::layernorm_apply(x.data_ptr(), w.data_ptr(), optp(b), mean.data_ptr<float>(), rstd.data_ptr<float>(), y.data_ptr(),
                        rows, cols, cur_stream());
 }
 static void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean, const Tensor& rstd,
                           Tensor& dx, const c10::optional<Tensor>& dx_add, c10::optional<Tensor> dw,
                           c10::optional<Tensor> db, bool accumulate, Tensor& partial) {
+  need(x, "x", at::kBFloat16); need(dy, "dy", at::kBFloat16, x.numel()); need(dx, "dx", at::kBFloat16, x.numel());
+  need_opt(dx_add, "dx_add", at::kBFloat16, x.numel());
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
   TORCH_CHECK(cols % 8 == 0, "layernorm_bwd needs cols % 8 == 0");
+  need(w, "w", at::kBFloat16, cols); need(mean, "mean", at::kFloat, rows); need(rstd, "rstd", at::kFloat, rows);
+  need(partial, "partial", at::kFloat);
+  if (dw.has_value()) need_grad(*dw, "dw", cols);
+  if (db.has_value()) {
+    need_grad(*db, "db", cols);
+    TORCH_CHECK(dw.has_value() && db->scalar_type() == dw->scalar_type(), "layernorm_bwd: db needs dw of the same dtype");
+  }
   TORCH_CHECK(partial.numel() >= (int64_t)dfb::norm_bwd_parts(rows) * 2 * cols, "layernorm_bwd scratch too small");
   dfb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
                      dx.data_ptr(), optp(dx_add), dw.has_value() ? dw->data_ptr() : nullptr,
@@ -95,9 +140,21 @@ static void swiglu_bwd(const Tensor& ds, const Tensor& x1, const Tensor& x3, Ten
   dfb::swiglu_bwd(ds.data_ptr(), x1.data_ptr(), x3.data_ptr(), dx1.data_ptr(), dx3.data_ptr(), sp, rows, (int)F, ld1, ld3, ldd1,
                   ldd3, cur_stream());
 }
-static void gelu_fwd(const Tensor& x, Tensor& y) { TORCH_CHECK(x.numel() % 8 == 0); dfb::gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), cur_stream()); }
-static void gelu_bwd(const Tensor& dy, const Tensor& x, Tensor& dx) { TORCH_CHECK(x.numel() % 8 == 0); dfb::gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), cur_stream()); }
-static void add_bf16(const Tensor& a, const Tensor& b, Tensor& out) { TORCH_CHECK(a.numel() % 8 == 0); dfb::add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream()); }
+static void gelu_fwd(const Tensor& x, Tensor& y) {
+  need(x, "x", at::kBFloat16); need(y, "y", at::kBFloat16, x.numel());
+  TORCH_CHECK(x.numel() % 8 == 0, "gelu_fwd needs numel % 8 == 0");
+  dfb::gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), cur_stream());
+}
+static void gelu_bwd(const Tensor& dy, const Tensor& x, Tensor& dx) {
+  need(x, "x", at::kBFloat16); need(dy, "dy", at::kBFloat16, x.numel()); need(dx, "dx", at::kBFloat16, x.numel());
+  TORCH_CHECK(x.numel() % 8 == 0, "gelu_bwd needs numel % 8 == 0");
+  dfb::gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), cur_stream());
+}
+static void add_bf16(const Tensor& a, const Tensor& b, Tensor& out) {
+  need(a, "a", at::kBFloat16); need(b, "b", at::kBFloat16, a.numel()); need(out, "out", at::kBFloat16, a.numel());
+  TORCH_CHECK(a.numel() % 8 == 0, "add_bf16 needs numel % 8 == 0");
+  dfb::add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream());
+}
 static void colsum_bf16(const Tensor& x, Tensor& partial, Tensor& out, bool accumulate) {
   CHECK_BF16(x); CHECK_CONTIG(x); CHECK_F32(partial);
   int cols = x.size(-1), rows = x.numel() / std::max(cols, 1);
@@ -106,13 +163,15 @@ static void colsum_bf16(const Tensor& x, Tensor& partial, Tensor& out, bool accu
 }
 static void adamw_bf16(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
                        double wd, int64_t step, double gscale) {
-  CHECK_BF16(w); CHECK_BF16(m); CHECK_BF16(v);
+  need(w, "w", at::kBFloat16); need(m, "m", at::kBFloat16, w.numel()); need(v, "v", at::kBFloat16, w.numel());
+  need_grad(g, "g", w.numel());
   dfb::adamw_bf16(w.data_ptr(), g.data_ptr(), g.scalar_type() == at::kFloat, m.data_ptr(), v.data_ptr(), w.numel(), lr, b1,
                   b2, eps, wd, (int)step, gscale, cur_stream());
 }
 static void adamw_master(Tensor& master, Tensor& w_out, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1,
                          double b2, double eps, double wd, int64_t step, double gscale) {
-  CHECK_F32(master); CHECK_BF16(w_out); CHECK_F32(m); CHECK_F32(v);
+  need(master, "master", at::kFloat); need(w_out, "w_out", at::kBFloat16, master.numel());
+  need(m, "m", at::kFloat, master.numel()); need(v, "v", at::kFloat, master.numel()); need_grad(g, "g", master.numel());
   dfb::adamw_master(master.data_ptr<float>(), w_out.data_ptr(), g.data_ptr(), g.scalar_type() == at::kFloat,
                     m.data_ptr<float>(), v.data_ptr<float>(), master.numel(), lr, b1, b2, eps, wd, (int)step, gscale,
                     cur_stream());
@@ -130,7 +189,8 @@ static void adamw_split(Tensor& w, Tensor& lo, const Tensor& g, Tensor& m, Tenso
 }
 static void adamw_f32(Tensor& w, const Tensor& g, Tensor& m, Tensor& v, double lr, double b1, double b2, double eps,
                       double wd, int64_t step, double gscale) {
-  CHECK_F32(w); CHECK_F32(g); CHECK_F32(m); CHECK_F32(v);
+  need(w, "w", at::kFloat); need(g, "g", at::kFloat, w.numel()); need(m, "m", at::kFloat, w.numel());
+  need(v, "v", at::kFloat, w.numel());
   dfb::adamw_f32(w.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), w.numel(), lr, b1, b2,
                  eps, wd, (int)step, gscale, cur_stream());
 }
@@ -146,23 +206,42 @@ static void ce_loss_fwd_bwd(Tensor& logits, const Tensor& targets, Tensor& nll_r
                             bool accumulate, double scale) {
   CHECK_CUDA(logits); CHECK_BF16(logits); CHECK_I32(targets); CHECK_F32(nll_rows);
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.stride(0) % 8 == 0, "logits must be (rows, vocab), row stride % 8 == 0");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(logits.data_ptr()) & 15) == 0, "logits must be 16-byte aligned");
+  TORCH_CHECK(targets.is_contiguous() && targets.numel() == logits.size(0), "targets: one int32 per logits row");
+  TORCH_CHECK(nll_rows.is_contiguous() && nll_rows.numel() >= logits.size(0), "nll_rows: one fp32 per logits row");
+  need_opt(loss, "loss", at::kFloat);
   dfb::ce_loss_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), nll_rows.data_ptr<float>(),
                        loss.has_value() ? loss->data_ptr<float>() : nullptr, accumulate, logits.size(0), logits.size(1),
                        logits.stride(0), (float)scale, cur_stream());
 }
 static void embed_fwd(const Tensor& tok, const Tensor& table, Tensor& out, const c10::optional<Tensor>& positions,
                       const c10::optional<Tensor>& pos_table) {
-  CHECK_I32(tok); CHECK_BF16(table); CHECK_CONTIG(table);
+  CHECK_I32(tok); CHECK_CONTIG(tok); need(table, "table", at::kBFloat16);
+  TORCH_CHECK(table.dim() == 2, "table must be (vocab, d)");
   int d = table.size(1);
   TORCH_CHECK(d % 8 == 0, "embedding width must be a multiple of 8");
-  dfb::embed_fwd(tok.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tok.numel(), d,
-                 positions.has_value() ? positions->data_ptr<int>() : nullptr, optp(pos_table), cur_stream());
+  need(out, "out", at::kBFloat16, tok.numel() * (int64_t)d);
+  int pos_rows = 0;
+  if (pos_table.has_value()) {
+    need(*pos_table, "pos_table", at::kBFloat16);
+    TORCH_CHECK(pos_table->dim() == 2 && pos_table->size(1) == d && positions.has_value(), "pos_table must be (positions, d) and come with positions");
+    CHECK_I32(*positions);
+    TORCH_CHECK(positions->is_contiguous() && positions->numel() == tok.numel(), "positions: one int32 per token");
+    pos_rows = pos_table->size(0);
+  }
+  dfb::embed_fwd(tok.data_ptr<int>(), table.data_ptr(), out.data_ptr(), tok.numel(), d, (int)table.size(0),
+                 pos_table.has_value() ? positions->data_ptr<int>() : nullptr, optp(pos_table), pos_rows, cur_stream());
 }
 static void embed_bwd_sorted(const Tensor& sorted_key, const Tensor& order, const Tensor& dy, Tensor& dtable, bool accumulate) {
-  CHECK_I32(sorted_key); CHECK_I32(order); CHECK_BF16(dy); CHECK_CONTIG(dy);
+  CHECK_I32(sorted_key); CHECK_I32(order); CHECK_CONTIG(sorted_key); CHECK_CONTIG(order); need(dy, "dy", at::kBFloat16);
   int d = dy.size(-1);
+  TORCH_CHECK(d % 8 == 0, "embed_bwd_sorted needs a width that is a multiple of 8");
+  TORCH_CHECK(order.numel() == sorted_key.numel() && dy.numel() == sorted_key.numel() * (int64_t)d, "embed_bwd_sorted: one dy row per key");
+  TORCH_CHECK(dtable.is_cuda() && dtable.is_contiguous() && dtable.dim() == 2 && dtable.size(1) == d &&
+              (dtable.scalar_type() == at::kFloat || dtable.scalar_type() == at::kBFloat16) &&
+              (reinterpret_cast<uintptr_t>(dtable.data_ptr()) & 15) == 0, "dtable must be a contiguous, 16-byte aligned (vocab, d) bf16 or fp32 CUDA tensor");
   dfb::embed_bwd_sorted(sorted_key.data_ptr<int>(), order.data_ptr<int>(), dy.data_ptr(), dtable.data_ptr(),
-                        dtable.scalar_type() == at::kFloat, sorted_key.numel(), d, accumulate, cur_stream());
+                        dtable.scalar_type() == at::kFloat, sorted_key.numel(), d, (int)dtable.size(0), accumulate, cur_stream());
 }
 
 // ---------------------------------------------------------------- GEMM

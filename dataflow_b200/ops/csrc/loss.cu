@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(bf16* __restrict__ logi
   if (row >= rows) return;
   bf16* lr = logits + static_cast<long long>(row) * ld;
   int tgt = targets[row];
+  if (tgt >= vocab) tgt = -1;          // an id outside the vocabulary is ignored like a negative one, never dereferenced
   float keep = tgt >= 0 ? 1.f : 0.f;
   int nvec = vocab >> 3;
   // pass 1: per-thread online (max, sum)

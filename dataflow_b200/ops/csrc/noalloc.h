@@ -26,13 +26,20 @@ extern "C" {
 //   dw = sum over rows of dy * xhat                   (bf16, cols)       xhat = x * rstd
 // dy, x, dx: bf16 (rows x cols, contiguous); w, dw: bf16 (cols); rstd: fp32 (rows), as produced by the forward.
 // All pointers are device pointers on the current device; work is enqueued on `stream`.
+// dy, x, w, dx and dw must be 16-byte aligned (the kernels move 16-byte vectors; since cols is a
+// multiple of 8 every row then is too) and rstd 4-byte aligned: a view that starts in the middle
+// of a caller's arena has to respect this.
 //
 // Return value: 0 on success; -1 if cols is not a multiple of 8 or exceeds DFB_NOALLOC_RMSNORM_MAX_COLS
-// or rows < 0; -2 if a pointer is null; -3 if the CUDA runtime reported an error (set-up or launch).
+// or rows < 0; -2 if a pointer is null; -3 if the CUDA runtime reported an error (one already pending
+// on this thread when the call came in, in which case nothing is launched, or one from set-up or launch);
+// -4 if a pointer is misaligned.
 // dfb_noalloc_strerror() turns the code into text.
 //
 // The first call on each device looks up the device address of the scratch array
-// (cudaGetSymbolAddress).  Make that first call outside of any stream capture.
+// (cudaGetSymbolAddress).  Make that first call outside of any stream capture.  The address is
+// cached for the life of the process: after cudaDeviceReset the cache is stale and this entry point
+// must not be used again in that process.
 // The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
 // Every call on a device shares the one scratch array.  The kernel overwrites the part it uses
 // before reading it, so stale contents from an earlier call are harmless and nothing needs to be

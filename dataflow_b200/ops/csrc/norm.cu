@@ -340,6 +340,8 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  void* dw, int dw_is_f32, int accumulate, float* partial, int rows, int cols, cudaStream_t s) {
   if (rows == 0) return;
   int parts = norm_bwd_parts(rows);
+  // every path below moves 16-byte vectors: callers (the torch binding, the C entry point) refuse operands that are not
+  // 16-byte aligned or whose width is not a multiple of 8; ``aligned`` only selects the register-resident variant
   const bool aligned = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
                          reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dx_add)) & 15) == 0;
 #define DFB_RMS_BWD_REGS(V)                                                                                                  \

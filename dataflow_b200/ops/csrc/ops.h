@@ -48,10 +48,10 @@ void ce_loss_fwd_bwd(void* logits, const int* targets, float* nll_rows, float* l
                      long long ld, float scale, cudaStream_t s);
 
 // ---- embedding (embed.cu)
-void embed_fwd(const int* tok, const void* table, void* out, int tokens, int d, const int* positions,
-               const void* pos_table, cudaStream_t s);
+void embed_fwd(const int* tok, const void* table, void* out, int tokens, int d, int vocab, const int* positions,
+               const void* pos_table, int pos_rows, cudaStream_t s);
 void embed_bwd_sorted(const int* sorted_key, const int* order, const void* dy, void* dtable, int dtable_is_f32, int n,
-                      int d, int accumulate, cudaStream_t s);
+                      int d, int table_rows, int accumulate, cudaStream_t s);
 
 // ---- GEMM (gemm_tcgen05.cu)
 int gemm_bf16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* D, long long ldd,

@@ -99,6 +99,22 @@ class RunLock:
             self.f.close()
 
 
+def _failure_markers(out: str) -> list[str]:
+    import glob
+    return sorted(glob.glob(glob.escape(out) + ".failure.rank*"))
+
+
+def _read_failure_kinds(out: str) -> list[tuple[str, str]]:
+    kinds = []
+    for path in _failure_markers(out):
+        try:
+            d = json.loads(open(path).read())
+            kinds.append((str(d.get("kind", "host")), str(d.get("message", ""))))
+        except (OSError, ValueError):
+            kinds.append(("host", "unreadable failure marker"))
+    return kinds
+
+
 def run(spec: RunSpec, log=print) -> RunResult:
     with RunLock(spec.checkpoint_dir if spec.checkpoint_every else None):
         if spec.world <= 1:
@@ -115,9 +131,17 @@ def run(spec: RunSpec, log=print) -> RunResult:
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={spec.world}",
                    "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
                    "-m", "dataflow_b200.run.rank_main", "--spec", spec.to_json()]
+            for stale in _failure_markers(out):
+                os.unlink(stale)
             proc = subprocess.run(cmd, env=env)
             if proc.returncode == 0:
                 break
+            # a rank that failed in Python says what kind of failure it was; only host-side failures (an exception, a rank
+            # that left, a peer that timed out) are worth a relaunch — a device error would be re-run unchanged
+            kinds = _read_failure_kinds(out)
+            device = [m for k, m in kinds if k == "device"]
+            if device:
+                raise RuntimeError(f"the {spec.world}-rank job stopped on a device error and is not restarted: {device[0]}")
             from .checkpointing import resolve_resume
             newest = resolve_resume("latest", spec.checkpoint_dir) if spec.checkpoint_dir else None
             if attempt >= int(spec.max_restarts) or not newest:

@@ -221,11 +221,40 @@ def _env_facts() -> dict:
     return {"torch": torch.__version__, "cuda": torch.version.cuda, "python": sys.version.split()[0]}
 
 
+def failure_kind(exc: BaseException) -> str:
+    """``device``: the GPU context or a fused kernel reported the failure (a CUDA error, a kernel's error word) — running
+    the same job again would run the same faulty work on a shared GPU.  ``timeout``: a collective gave up waiting for a
+    peer.  ``host``: anything else (an exception in Python code, a fault plan)."""
+    from ..parallel.zero import CommTimeout
+    text = f"{type(exc).__name__}: {exc}"
+    if isinstance(exc, CommTimeout):
+        return "timeout"
+    low = text.lower()
+    if any(k in low for k in ("cuda error", "acceleratorerror", "illegal memory", "illegal instruction", "misaligned address",
+                              "device-side assert", "unspecified launch failure", "error word", "kernel gave up")):
+        return "device"
+    if "timeout" in low or "timed out" in low:
+        return "timeout"
+    return "host"
+
+
+def failure_marker(out: str, rank: int) -> str:
+    return f"{out}.failure.rank{rank}"
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--spec", required=True)
     a = ap.parse_args(argv)
-    run_rank(RunSpec.from_json(a.spec))
+    spec = RunSpec.from_json(a.spec)
+    try:
+        run_rank(spec)
+    except BaseException as e:          # noqa: BLE001 - classified for the conductor, then re-raised
+        if spec.out and not isinstance(e, (SystemExit, KeyboardInterrupt)):
+            import json
+            with open(failure_marker(spec.out, int(os.environ.get("RANK", 0))), "w") as f:
+                json.dump({"kind": failure_kind(e), "message": f"{type(e).__name__}: {e}"[:2000]}, f)
+        raise
     return 0
 
 

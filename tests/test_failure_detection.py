@@ -52,6 +52,37 @@ def test_a_failed_job_restarts_from_its_newest_checkpoint_and_finishes_the_same_
     assert r2.returncode != 0 and not (tmp_path / "dead.json").exists()
 
 
+def test_only_host_side_failures_are_restarted(tmp_path, monkeypatch):
+    """A rank's failure marker says whether the failure came from Python code, from a peer that timed out or from the device;
+    the conductor relaunches for the first two and stops on the third."""
+    import json
+    from dataflow_b200.parallel.zero import CommTimeout
+    from dataflow_b200.run import conductor
+    from dataflow_b200.run.rank_main import failure_kind, failure_marker
+    assert failure_kind(RuntimeError("fault plan: rank 1 fails after step 2")) == "host"
+    assert failure_kind(CommTimeout("fused communication kernel gave up: phase 1, peer/rank 3")) == "timeout"
+    assert failure_kind(RuntimeError("CUDA error: an illegal memory access was encountered")) == "device"
+    assert failure_kind(RuntimeError("gemm_bf16: kernel gave up (error word 17)")) == "device"
+    assert failure_kind(RuntimeError("[Rank 0] Watchdog caught collective operation timeout")) == "timeout"
+    out = str(tmp_path / "r.json")
+    calls = []
+
+    class P:
+        returncode = 1
+
+    def fake_run(cmd, env=None):
+        calls.append(cmd)
+        with open(failure_marker(out, 1), "w") as f:
+            json.dump({"kind": "device", "message": "CUDA error: an illegal memory access was encountered"}, f)
+        return P()
+
+    monkeypatch.setattr(conductor.subprocess, "run", fake_run)
+    spec = conductor.RunSpec(preset="llama3:tiny", world=2, steps=2, out=out, max_restarts=3, checkpoint_dir=str(tmp_path / "ck"))
+    with pytest.raises(RuntimeError, match="device error and is not restarted"):
+        conductor.run(spec, log=lambda *_: None)
+    assert len(calls) == 1
+
+
 @pytest.mark.gpu
 def test_a_device_wait_that_cannot_be_satisfied_returns_a_status_and_the_context_stays_usable():
     """The expert-parallel combine kernel of rank 0 of a 2-rank group whose peer never publishes its rows: the bounded wait

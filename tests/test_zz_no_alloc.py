@@ -64,3 +64,7 @@ def test_noalloc_rejects_unsupported_sizes():
     assert lib.dfb_rmsnorm_bwd_noalloc(p, p, p, p, p, p, 4, 100, None) == -1       # not a multiple of 8
     assert lib.dfb_rmsnorm_bwd_noalloc(None, p, p, p, p, p, 4, 64, None) == -2
     assert b"8192" in lib.dfb_noalloc_strerror(-1)
+    # a pointer into the middle of a 16-byte vector is refused before anything launches
+    assert lib.dfb_rmsnorm_bwd_noalloc(p + 2, p, p, p, p, p, 4, 64, None) == -4
+    assert lib.dfb_rmsnorm_bwd_noalloc(p, p, p, p + 2, p, p, 4, 64, None) == -4
+    assert b"aligned" in lib.dfb_noalloc_strerror(-4)
