@@ -151,7 +151,7 @@ def bench_ours(a) -> dict:
     barrier()
     t0 = time.perf_counter()
     e0.record()
-    dev_us = 0.0
+    dev_us = exposed_us = 0.0
     losses = []
     for s in range(a.steps):
         for r, (tk, tg) in enumerate(data[s]):
@@ -159,16 +159,19 @@ def bench_ours(a) -> dict:
         losses.append(tr.step(None, valid_rows=tokens_step * world))     # reads the loss words back from pinned memory
         d2h += 4 * len(tr.loss_ids)
         dev_us += tr.last_result.makespan_us
+        exposed_us += float(tr.last_result.stats.get("exposed_comm_us", 0.0))
     e1.record()
     barrier()
     wall_s = time.perf_counter() - t0
     ev_s = e0.elapsed_time(e1) / 1e3
     clocks = sampler.stop()
     launches = cuda_lane.LAUNCHES.total
-    t = torch.tensor([dev_us / 1e6, max(ev_s, wall_s)], dtype=torch.float64, device="cuda")
+    t = torch.tensor([dev_us / 1e6, max(ev_s, wall_s), exposed_us / 1e3], dtype=torch.float64, device="cuda")
+    lsum = torch.tensor([losses[-1] if losses else 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    dev_s, e2e_s = float(t[0]), float(t[1])
+        torch.distributed.all_reduce(lsum)          # every rank holds its share of the step's mean loss
+    dev_s, e2e_s, exposed_ms = float(t[0]), float(t[1]), float(t[2])
     total_tokens = tokens_step * world * a.steps
     value = total_tokens / dev_s
     res = tr.last_result
@@ -186,10 +189,14 @@ def bench_ours(a) -> dict:
         "e2e": {"value": total_tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d // a.steps,
                 "d2h_bytes_per_step": d2h // a.steps},
         "gpu_launches": launches,
-        "loss": losses[-1] if losses else None,
+        # device-timed: what the compute stream spent waiting on parameter gathers / gradient reduce-scatters that run on
+        # the communication stream (max over ranks, per step); 0 on one GPU, where nothing is communicated
+        "exposed_comm_ms_per_step": exposed_ms / a.steps,
+        "loss": float(lsum[0]) if losses else None,
         "plan": {"predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
                  "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
                  "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows,
+                 "placement_escapes": res.placement_escapes, "pressure_evictions": res.pressure_evictions,
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},
     }

@@ -39,11 +39,18 @@ class _Base:
             pending = ctx.run_values.get("_ready")
             if pending:
                 # inputs produced on another stream (asynchronous gathers / reduce-scatters): wait on-stream
+                # The stall is timed on the device: an event in front of the wait fires when the compute stream gets there,
+                # one behind it when the transfer's event has fired too; their distance is communication the step could
+                # not hide (``exposed_comm_us`` of the run's statistics).
                 cur = torch.cuda.current_stream()
-                for b in ctx.inputs:
-                    ev = pending.pop(b.object_id, None)
-                    if ev is not None:
+                evs = [ev for ev in (pending.pop(b.object_id, None) for b in ctx.inputs) if ev is not None]
+                if evs:
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0.record(cur)
+                    for ev in evs:
                         cur.wait_event(ev)
+                    t1.record(cur)
+                    ctx.run_values.setdefault("_comm_waits", []).append((t0, t1))
             self.run(ctx)
 
     def run(self, ctx) -> None:      # pragma: no cover - abstract

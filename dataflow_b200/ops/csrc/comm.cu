@@ -21,6 +21,8 @@
 //
 // The reference has no such kernels: its ZeRO lane is NCCL reduce-scatter -> Triton AdamW -> NCCL
 // all-gather (src/dataflow_training/blocks/adamw/rs.py:34-105).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ops.h"
 
@@ -28,6 +30,12 @@ namespace dfb {
 
 constexpr int kMaxWorld = 8;
 constexpr int kMaxFields = 16;
+// These kernels run on a communication stream WHILE the persistent GEMMs hold every SM (one 192-thread CTA of about 180
+// registers per thread and 225 KiB of shared memory per SM).  What an SM has left is about 30 K registers and a few
+// hundred bytes of shared memory: a 256-thread CTA of at most 112 registers per thread fits beside the GEMM, a
+// 512-thread one does not and would only ever run in the gaps between GEMMs.
+constexpr int kCommThreads = 256;
+constexpr int kCommRegs = 112;
 
 struct PeerTable {
   unsigned char* slab[kMaxWorld];     // peer-mapped base of each rank's fast slab
@@ -93,7 +101,9 @@ struct RsAdamwParams {
   unsigned int* done_ctr;       // local counter for "last CTA" detection (zeroed by the kernel's last CTA)
 };
 
-__global__ void __launch_bounds__(512) zero_rs_adamw_kernel(RsAdamwParams p) {
+// V 16-byte vectors per thread and iteration from each of at most WMAX ranks: V x world peer loads in flight
+template <int V, int WMAX>
+__global__ void __maxnreg__(kCommRegs) zero_rs_adamw_kernel(RsAdamwParams p) {
   __shared__ const bf16* src[kMaxWorld];
   __shared__ int failed;
   const int me = p.peers.rank, W = p.peers.world;
@@ -122,71 +132,82 @@ __global__ void __launch_bounds__(512) zero_rs_adamw_kernel(RsAdamwParams p) {
   __syncthreads();
   if (!failed) {
     const long long nvec = p.slice_len >> 3;
-    for (long long vi = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vi < nvec;
-         vi += static_cast<long long>(gridDim.x) * blockDim.x) {
-      const long long e0 = vi << 3;                         // element inside the slice
-      const long long g0 = p.slice_begin + e0;              // element inside the flat object
-      float acc[8];
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += V * stride) {
+      // every rank's vectors are requested before the first one is used (a peer load takes microseconds); the sum still
+      // runs in rank order: deterministic
+      bf16x8 pv[V][WMAX];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      // every rank's vector is requested before the first one is used (a peer load takes microseconds); the sum still runs
-      // in rank order: deterministic
-      bf16x8 pv[kMaxWorld];
+      for (int u = 0; u < V; ++u) {
+        const long long vi = v0 + u * stride;
+        if (vi < nvec) {
 #pragma unroll
-      for (int r = 0; r < kMaxWorld; ++r)
-        if (r < W) pv[r] = ld8(src[r] + g0);
-#pragma unroll
-      for (int r = 0; r < kMaxWorld; ++r) {
-        if (r < W) {
-          float f[8];
-          unpack8(pv[r], f);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          for (int r = 0; r < WMAX; ++r)
+            if (r < W) pv[u][r] = ld8(src[r] + p.slice_begin + (vi << 3));
         }
       }
-      if (p.gacc) {
-        float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        if (!p.gacc_first) {
-          const float4 c = *reinterpret_cast<const float4*>(p.gacc + e0), d = *reinterpret_cast<const float4*>(p.gacc + e0 + 4);
-          a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
-        }
-        *reinterpret_cast<float4*>(p.gacc + e0) = a;
-        *reinterpret_cast<float4*>(p.gacc + e0 + 4) = b;
-        continue;
-      }
-      float wd = 0.f;
-      for (int k = 0; k < p.n_fields; ++k)
-        if (g0 >= p.fields[k].begin && g0 < p.fields[k].end) wd = p.fields[k].wd;
-      float wv[8];
-      if (p.master) {
-        float4 a = *reinterpret_cast<const float4*>(p.master + e0), b = *reinterpret_cast<const float4*>(p.master + e0 + 4);
-        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-      } else {
-        unpack8(ld8(p.shard_out + e0), wv);
-      }
-      float mv[8], vv[8];
-      {
-        float4 a = *reinterpret_cast<const float4*>(p.m + e0), b = *reinterpret_cast<const float4*>(p.m + e0 + 4);
-        mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
-        float4 c = *reinterpret_cast<const float4*>(p.v + e0), d = *reinterpret_cast<const float4*>(p.v + e0 + 4);
-        vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
-      }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float g = acc[i] * p.gscale;
-        mv[i] = p.b1 * mv[i] + (1.f - p.b1) * g;
-        vv[i] = p.b2 * vv[i] + (1.f - p.b2) * g * g;
-        wv[i] -= p.lr * ((mv[i] / p.bc1) / (sqrtf(vv[i] / p.bc2) + p.eps) + wd * wv[i]);
+      for (int u = 0; u < V; ++u) {
+        const long long vi = v0 + u * stride;
+        if (vi >= nvec) continue;
+        const long long e0 = vi << 3;                         // element inside the slice
+        const long long g0 = p.slice_begin + e0;              // element inside the flat object
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int r = 0; r < WMAX; ++r) {
+          if (r < W) {
+            float f[8];
+            unpack8(pv[u][r], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          }
+        }
+        if (p.gacc) {
+          float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+          if (!p.gacc_first) {
+            const float4 c = *reinterpret_cast<const float4*>(p.gacc + e0), d = *reinterpret_cast<const float4*>(p.gacc + e0 + 4);
+            a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+          }
+          *reinterpret_cast<float4*>(p.gacc + e0) = a;
+          *reinterpret_cast<float4*>(p.gacc + e0 + 4) = b;
+          continue;
+        }
+        float wd = 0.f;
+        for (int k = 0; k < p.n_fields; ++k)
+          if (g0 >= p.fields[k].begin && g0 < p.fields[k].end) wd = p.fields[k].wd;
+        float wv[8];
+        if (p.master) {
+          float4 a = *reinterpret_cast<const float4*>(p.master + e0), b = *reinterpret_cast<const float4*>(p.master + e0 + 4);
+          wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+        } else {
+          unpack8(ld8(p.shard_out + e0), wv);
+        }
+        float mv[8], vv[8];
+        {
+          float4 a = *reinterpret_cast<const float4*>(p.m + e0), b = *reinterpret_cast<const float4*>(p.m + e0 + 4);
+          mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
+          float4 c = *reinterpret_cast<const float4*>(p.v + e0), d = *reinterpret_cast<const float4*>(p.v + e0 + 4);
+          vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float g = acc[i] * p.gscale;
+          mv[i] = p.b1 * mv[i] + (1.f - p.b1) * g;
+          vv[i] = p.b2 * vv[i] + (1.f - p.b2) * g * g;
+          wv[i] -= p.lr * ((mv[i] / p.bc1) / (sqrtf(vv[i] / p.bc2) + p.eps) + wd * wv[i]);
+        }
+        *reinterpret_cast<float4*>(p.m + e0) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+        *reinterpret_cast<float4*>(p.m + e0 + 4) = make_float4(mv[4], mv[5], mv[6], mv[7]);
+        *reinterpret_cast<float4*>(p.v + e0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        *reinterpret_cast<float4*>(p.v + e0 + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        if (p.master) {
+          *reinterpret_cast<float4*>(p.master + e0) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+          *reinterpret_cast<float4*>(p.master + e0 + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+        }
+        st8(p.shard_out + e0, pack8(wv));
       }
-      *reinterpret_cast<float4*>(p.m + e0) = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      *reinterpret_cast<float4*>(p.m + e0 + 4) = make_float4(mv[4], mv[5], mv[6], mv[7]);
-      *reinterpret_cast<float4*>(p.v + e0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-      *reinterpret_cast<float4*>(p.v + e0 + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
-      if (p.master) {
-        *reinterpret_cast<float4*>(p.master + e0) = make_float4(wv[0], wv[1], wv[2], wv[3]);
-        *reinterpret_cast<float4*>(p.master + e0 + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
-      }
-      st8(p.shard_out + e0, pack8(wv));
     }
   }
   // last CTA of the grid: ack every peer (we are done reading them), then hold until every peer acked us
@@ -216,7 +237,7 @@ struct GatherParams {
   unsigned int* done_ctr;
 };
 
-__global__ void __launch_bounds__(512) param_gather_kernel(GatherParams p) {
+__global__ void __maxnreg__(kCommRegs) param_gather_kernel(GatherParams p) {
   __shared__ const uint4* src[kMaxWorld];
   __shared__ int failed, is_last;
   const int me = p.peers.rank, W = p.peers.world;
@@ -279,6 +300,16 @@ __global__ void __launch_bounds__(512) param_gather_kernel(GatherParams p) {
 }
 
 // ---------------------------------------------------------------------------- host entry points
+// CTAs per communication kernel: one per SM unless DATAFLOW_COMM_CTAS names a smaller budget (the kernels are grid-stride
+// loops, so any count is correct; fewer CTAs leave more issue slots to the GEMM they run beside).
+static int comm_grid(int num_sms) {
+  static int budget = [] {
+    const char* e = getenv("DATAFLOW_COMM_CTAS");
+    return e ? atoi(e) : 0;
+  }();
+  return budget > 0 && budget < num_sms ? budget : num_sms;
+}
+
 static PeerTable make_table(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world) {
   PeerTable t{};
   for (int i = 0; i < world && i < kMaxWorld; ++i) {
@@ -311,7 +342,11 @@ int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctr
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.err = err; p.done_ctr = done_ctr;
   p.gacc = gacc; p.gacc_first = gacc_first;
-  zero_rs_adamw_kernel<<<num_sms, 512, 0, s>>>(p);
+  // peer loads in flight per thread: V vectors x world ranks, about eight either way
+  const int grid = comm_grid(num_sms);
+  if (world <= 2) zero_rs_adamw_kernel<4, 2><<<grid, kCommThreads, 0, s>>>(p);
+  else if (world <= 4) zero_rs_adamw_kernel<2, 4><<<grid, kCommThreads, 0, s>>>(p);
+  else zero_rs_adamw_kernel<1, 8><<<grid, kCommThreads, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -327,7 +362,7 @@ int param_gather(const unsigned long long* slabs, const unsigned long long* ctrl
   p.per_vec = per_bytes >> 4; p.total_vec = total_bytes >> 4;
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.err = err; p.done_ctr = done_ctr;
-  param_gather_kernel<<<num_sms, 512, 0, s>>>(p);
+  param_gather_kernel<<<comm_grid(num_sms), kCommThreads, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -244,6 +244,16 @@ class Engine:
             if watcher is not None:
                 stop.set()
         st = raw["stats"]
+        waits = run_values.get("_comm_waits")
+        if waits:
+            # device-timed stalls of the compute stream on transfers issued on another stream (both events have fired:
+            # the run is complete)
+            st = dict(st)
+            try:
+                st["exposed_comm_us"] = 1e3 * sum(max(a.elapsed_time(b), 0.0) for a, b in waits)
+                st["comm_waits"] = len(waits)
+            except RuntimeError:
+                pass
         trace = RunTrace([Interval(n, tr, a, b) for n, tr, a, b in raw["intervals"]],
                          [TraceEvent(k, w, f) for k, w, f in raw["events"]],
                          st["peak_fast_bytes"], st["peak_backing_bytes"])
