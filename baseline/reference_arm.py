@@ -68,14 +68,44 @@ def run_reference_arm(a) -> dict:
         from dataflow_training.lowering import shaped_program as ref_sp
         ref_sp.HW_PRESETS.setdefault("b200", dict(peak_bf16_tflops=1669.0, matmul_eff=0.75, attn_eff=0.45,
                                                   mem_bw_gbs=6524.0, mem_eff=0.8, pcie_gbs=52.0))
-        planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=False, backing_gib=150.0)
+        # The reference's own training entry prices the tasks by profiling them on the device before it plans
+        # (run/loop.py -> run/profiling.py load_or_profile); the arm does the same unless DFB_REF_COSTS=roofline asks for
+        # the hardware-row estimate.  If the profiling pass fails on this device the arm falls back to the estimate and
+        # says so in ``plan.costs``.
+        costs = "measured" if os.environ.get("DFB_REF_COSTS", "measured") != "roofline" else "roofline"
+        planned = None
+        if costs == "measured":
+            try:
+                planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=True, backing_gib=150.0)
+            except Exception as e:       # noqa: BLE001
+                costs = f"roofline (measured profiling failed: {type(e).__name__}: {str(e)[:120]})"
+        if planned is None:
+            planned = plan_at_budget(replace(cfg, num_steps=1), budget, measured=False, backing_gib=150.0)
         plan_s = time.perf_counter() - t_plan
+        stamps: list[float] = []
+
+        def on_log(*x, **k):
+            line = " ".join(map(str, x))
+            logs.append(line)
+            if "] step " in line and "tok/s" in line:
+                stamps.append(time.perf_counter())        # one line per step (log_every=1), printed right after the step's run
+
         with engine_client(backing_gib=150.0, log=lambda *x, **k: None) as client:
             res = run_engine(client, cfg, recipe, factory, steps, budget_gib=budget, seed=11, planned=planned,
-                             log=lambda *x, **k: logs.append(" ".join(map(str, x))))
+                             log=on_log, log_every=1)
         tail = res.step_wall_s[a.warmup:] or res.step_wall_s
         s_per_step = sum(tail) / len(tail)
         value = tokens_step / s_per_step
+        # End to end: the whole loop iteration of the reference's step loop — staging the step's tokens and targets into
+        # the daemon's pinned store (put_object), the run (whose first transfers copy them to the device) and the loss
+        # fetch — taken from the time between consecutive per-step log lines.
+        e2e = None
+        if len(stamps) == steps and steps - a.warmup >= 1 and a.warmup >= 1:
+            span = stamps[-1] - stamps[a.warmup - 1]
+            e2e = {"value": tokens_step * (steps - a.warmup) / span, "unit": "tokens/s",
+                   "h2d_bytes_per_step": 2 * 4 * tokens_step, "d2h_bytes_per_step": 4 * cfg.grad_accum_rounds,
+                   "how": "wall clock between the reference's per-step log lines: put_object of the step's ids into its "
+                          "pinned store + run + loss fetch"}
         return {
             "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": len(tail),
             "warmup": a.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -85,7 +115,8 @@ def run_reference_arm(a) -> dict:
                        "dtype_policy": "all-bf16 (the reference has no fp32-master lane)", "optimizer": "adamw",
                        "hw_preset": "b200 row added to the reference's HW_PRESETS table at run time",
                        "timing": "reference's own per-step wall clock (its step loop blocks on the loss fetch)"},
-            "plan": {"predicted_ms_per_step": planned.makespan_us / 1e3, "plan_s": plan_s},
+            "plan": {"predicted_ms_per_step": planned.makespan_us / 1e3, "plan_s": plan_s, "costs": costs},
+            "e2e": e2e,
             "loss": res.losses[-1] if res.losses else None,
             "gpu_launches": None, "torch": torch.__version__,
         }

@@ -14,13 +14,10 @@
 // Output: out (tokens, heads, 128) bf16 and lse (heads, tokens) fp32 = log sum exp(scale * s), the statistics the backward
 // (library lane) consumes.
 // Reference role: src/dataflow_training/kernels/flash.py:59-172 (aten varlen flash attention forward).
-#include <cuda.h>
+#include <cstdlib>
 
-#include <mutex>
-
-#include "common.cuh"
+#include "attention_common.cuh"
 #include "ops.h"
-#include "ptx.cuh"
 
 namespace dfb {
 namespace fa {
@@ -50,12 +47,6 @@ struct Params {
   float sl2;            // scale * log2(e)
   int* err;
 };
-
-DFB_DEVICE float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -287,34 +278,283 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<EncodeFn>(p);
-  });
-  return fn;
-}
-
-// (tokens, heads * 128) bf16 with ``ld`` elements between tokens; boxes of 64 columns x ``box_rows`` tokens
-static bool make_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t ld, uint32_t box_rows) {
-  EncodeFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace fa
+
+
+// ============================================================================ two query tiles per CTA
+// The kernel above keeps the tensor pipe waiting for its single softmax warpgroup.  This one gives a CTA TWO 128-row query
+// tiles (256 consecutive queries of one head) and one softmax warpgroup per tile, so that while one tile's scores are being
+// exponentiated on the ALUs the tensor pipe runs the other tile's products:
+//     per key tile j:   S0(j) = Q0 K_j^T,  S1(j) = Q1 K_j^T,  O0 += P0(j-1) V_(j-1),  O1 += P1(j-1) V_(j-1)
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each.  Shared memory: Q0, Q1, a ring of three K/V tiles (K_j, V_j alternate),
+// one P tile per query tile: 7 x 32 KiB.  A softmax thread owns one query row: it pulls its 128 scores out of tensor memory
+// (freeing S for the next product at once), keeps the running maximum / sum, and writes P as bf16 into the swizzled K-major
+// tile the P V product reads.  The exponent base is raised lazily as in the kernel above.
+namespace fa2 {
+
+constexpr int BM = 128, BN = 128, D = 128, UK = 16;
+constexpr int CH = 128 * 128;                    // one 128-row x 64-element (128-byte) swizzled chunk: 16 KiB
+constexpr int TILE = 2 * CH;
+constexpr int KV_SLOTS = 3;
+constexpr int OFF_Q = 0, OFF_KV = 2 * TILE, OFF_P = OFF_KV + KV_SLOTS * TILE, OFF_BAR = OFF_P + 2 * TILE;
+constexpr int SMEM_BYTES = OFF_BAR + 512 + 1024;
+constexpr float kRescaleGap = 8.f;
+constexpr int THREADS = 320;                     // warp 0: TMA, warp 1: MMA, warps 2-5 / 6-9: softmax of query tile 0 / 1
+constexpr int TMEM_COLS = 512;
+constexpr float kNegBig = -1e30f;
+
+struct Bars {
+  uint64_t q_full[2], kv_full[KV_SLOTS], kv_empty[KV_SLOTS], s_full[2], s_empty[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+using fa::Params;
+using fa::ex2;
+
+#define DFB_FA_FAIL(code) do { bar->abort = 1; atomicExch(p.err, (code)); } while (0)
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, Params p) {
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int seg_start = p.cu_seqlens[seg];
+  const int seg_len = p.cu_seqlens[seg + 1] - seg_start;
+  const int n_pairs = (seg_len + 2 * BM - 1) / (2 * BM);
+  const int pt = n_pairs - 1 - static_cast<int>(blockIdx.x);      // heavy pairs first
+  if (pt < 0) return;                                            // the whole CTA leaves before any barrier or TMEM exists
+  const bool has1 = (2 * pt + 1) * BM < seg_len;                 // does the second query tile hold any row of the sequence
+  const int n0 = 2 * pt + 1, n1 = has1 ? 2 * pt + 2 : 0;         // key tiles each query tile attends to
+  const int n_tot = has1 ? n1 : n0;
+  const int kvh = h / (p.hq / p.hkv);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Bars* bar = reinterpret_cast<Bars*>(smem + OFF_BAR);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bar->abort;
+
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(&bar->q_full[t], 1);
+      ptx::mbar_init(&bar->s_full[t], 1); ptx::mbar_init(&bar->s_empty[t], 4);
+      ptx::mbar_init(&bar->p_full[t], 4); ptx::mbar_init(&bar->pv_done[t], 1);
+    }
+    for (int b = 0; b < KV_SLOTS; ++b) { ptx::mbar_init(&bar->kv_full[b], 1); ptx::mbar_init(&bar->kv_empty[b], 1); }
+    bar->abort = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmap_q);
+    ptx::prefetch_tmap(&tmap_k);
+    ptx::prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&bar->tmem_base, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bar->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      for (int t = 0; t < (has1 ? 2 : 1); ++t) {
+        const int row0 = seg_start + (2 * pt + t) * BM;
+        ptx::mbar_expect_tx(&bar->q_full[t], TILE);
+        for (int c = 0; c < 2; ++c) ptx::tma_load_2d(smem + OFF_Q + t * TILE + c * CH, &tmap_q, &bar->q_full[t], h * D + c * 64, row0);
+      }
+      // loads alternate K_0, V_0, K_1, V_1, ...: load L goes to ring slot L % 3
+      for (int L = 0; L < 2 * n_tot && !*abort_flag; ++L) {
+        const int slot = L % KV_SLOTS, use = L / KV_SLOTS, j = L >> 1;
+        const int key0 = seg_start + j * BN;
+        if (use > 0 && !ptx::mbar_wait(&bar->kv_empty[slot], (use - 1) & 1, abort_flag)) { DFB_FA_FAIL(71); break; }
+        uint8_t* dst = smem + OFF_KV + slot * TILE;
+        ptx::mbar_expect_tx(&bar->kv_full[slot], TILE);
+        if ((L & 1) == 0) {
+          for (int c = 0; c < 2; ++c) ptx::tma_load_2d(dst + c * CH, &tmap_k, &bar->kv_full[slot], kvh * D + c * 64, key0);
+        } else {
+          // V as the MN-major operand of P V: per 64-key block, two 64-column chunks of (64 keys x 128 bytes)
+          for (int kb = 0; kb < 2; ++kb)
+            for (int c = 0; c < 2; ++c)
+              ptx::tma_load_2d(dst + kb * CH + c * (CH / 2), &tmap_v, &bar->kv_full[slot], kvh * D + c * 64, key0 + kb * 64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc_s = ptx::idesc_bf16_f32(BM, BN, false, false);
+      constexpr uint32_t idesc_pv = ptx::idesc_bf16_f32(BM, D, false, true);
+      constexpr uint64_t k_step = (UK * 2) >> 4;             // K-major operand: 16 elements = 32 bytes along the row
+      constexpr uint64_t mn_step = (UK * 128) >> 4;          // MN-major operand: 16 k-rows of 128 bytes
+      const uint32_t q_addr = ptx::smem_u32(smem + OFF_Q), p_addr = ptx::smem_u32(smem + OFF_P);
+      const uint32_t kv_addr = ptx::smem_u32(smem + OFF_KV);
+      bool ok = ptx::mbar_wait(&bar->q_full[0], 0, abort_flag) && (!has1 || ptx::mbar_wait(&bar->q_full[1], 0, abort_flag));
+      if (!ok) DFB_FA_FAIL(73);
+      for (int j = 0; j <= n_tot && ok; ++j) {
+        if (j < n_tot) {
+          const int L = 2 * j, slot = L % KV_SLOTS;
+          if (!ptx::mbar_wait(&bar->kv_full[slot], (L / KV_SLOTS) & 1, abort_flag)) { DFB_FA_FAIL(74); ok = false; break; }
+          const uint32_t k_addr = kv_addr + slot * TILE;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j >= (t ? n1 : n0)) continue;
+            if (j >= 1 && !ptx::mbar_wait(&bar->s_empty[t], (j - 1) & 1, abort_flag)) { DFB_FA_FAIL(75); ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t tmem_s = tmem_base + t * BN;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const uint64_t adesc = ptx::desc_kmajor_sw128(q_addr + t * TILE + c * CH), bdesc = ptx::desc_kmajor_sw128(k_addr + c * CH);
+#pragma unroll
+              for (int k = 0; k < 64 / UK; ++k) ptx::umma_bf16(tmem_s, adesc + k * k_step, bdesc + k * k_step, idesc_s, (c | k) != 0);
+            }
+            ptx::umma_commit(&bar->s_full[t]);
+          }
+          if (!ok) break;
+          ptx::umma_commit(&bar->kv_empty[slot]);
+        }
+        if (j >= 1) {
+          const int jj = j - 1, L = 2 * jj + 1, slot = L % KV_SLOTS;
+          if (!ptx::mbar_wait(&bar->kv_full[slot], (L / KV_SLOTS) & 1, abort_flag)) { DFB_FA_FAIL(76); ok = false; break; }
+          const uint32_t v_addr = kv_addr + slot * TILE;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (jj >= (t ? n1 : n0)) continue;
+            if (!ptx::mbar_wait(&bar->p_full[t], jj & 1, abort_flag)) { DFB_FA_FAIL(77); ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t tmem_o = tmem_base + (2 + t) * BN;
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb) {
+              const uint64_t adesc = ptx::desc_kmajor_sw128(p_addr + t * TILE + kb * CH);
+              const uint64_t bdesc = ptx::desc_mnmajor_sw128(v_addr + kb * CH, CH / 2);
+#pragma unroll
+              for (int k = 0; k < 64 / UK; ++k)
+                ptx::umma_bf16(tmem_o, adesc + k * k_step, bdesc + k * mn_step, idesc_pv, (jj | kb | k) != 0);
+            }
+            ptx::umma_commit(&bar->pv_done[t]);
+          }
+          if (!ok) break;
+          ptx::umma_commit(&bar->kv_empty[slot]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output: one thread per query row
+    const int t = (warp - 2) >> 2;                // query tile of this warpgroup
+    const int q4 = warp & 3;                      // the quarter of tensor-memory lanes this warp may touch
+    const int r = q4 * 32 + lane;                 // row inside the tile == TMEM lane
+    const int n_kv = t ? n1 : n0;
+    const int qi = (2 * pt + t) * BM + r;         // row inside the sequence
+    const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+    const uint32_t t_s = tmem_base + t * BN + lane_base;
+    const uint32_t t_o = tmem_base + (2 + t) * BN + lane_base;
+    uint8_t* p_tile = smem + OFF_P + t * TILE;
+    float m = kNegBig, l = 0.f;                   // exponent base (log2 units, scaled) and the row sum relative to it
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      // waits are made warp-uniform: the tensor-memory loads below are warp-wide instructions
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->s_full[t], j & 1, abort_flag))) { DFB_FA_FAIL(78); ok = false; break; }
+      ptx::tc_fence_after();
+      float sc[BN];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32(t_s + c * 32, reinterpret_cast<uint32_t*>(sc) + c * 32);
+      ptx::tmem_ld_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bar->s_empty[t]);          // S(j) is in registers: tensor memory may take S(j + 1)
+      float mx = kNegBig;
+      if (j == n_kv - 1) {                        // the diagonal tile (it also holds the end of the sequence)
+        const int key_base = j * BN;
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int kj = key_base + i;
+          if (kj > qi || kj >= seg_len) sc[i] = kNegBig;
+          mx = fmaxf(mx, sc[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sc[i]);
+      }
+      mx *= p.sl2;                                // the scale is positive: the maximum commutes with it
+      const bool raise = j == 0 || mx > m + kRescaleGap;
+      if (__any_sync(0xffffffffu, raise)) {
+        const float m_new = fmaxf(m, mx);
+        if (j > 0) {
+          // O must be complete up to tile j - 1 and no P V may be in flight while it is rescaled
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[t], (j - 1) & 1, abort_flag))) { DFB_FA_FAIL(79); ok = false; break; }
+          ptx::tc_fence_after();
+          const float alpha = ex2(m - m_new);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(t_o + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            ptx::tmem_st_32x32(t_o + c * 32, v);
+          }
+          ptx::tmem_st_wait();
+          l *= alpha;
+        }
+        m = m_new;
+      }
+      // exponentials first (registers), then the wait for the P tile: P V(j - 1) read it
+      const float neg_m = -m;
+      float rowsum = 0.f;
+      uint32_t pk[BN / 2];
+#pragma unroll
+      for (int i = 0; i < BN; i += 2) {
+        const float e0 = ex2(fmaf(sc[i], p.sl2, neg_m)), e1 = ex2(fmaf(sc[i + 1], p.sl2, neg_m));
+        rowsum += e0 + e1;
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+        pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+      }
+      l += rowsum;
+      if (j >= 1) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[t], (j - 1) & 1, abort_flag))) { DFB_FA_FAIL(80); ok = false; break; }
+      }
+      uint8_t* p_row = p_tile + r * 128;
+#pragma unroll
+      for (int g = 0; g < BN / 8; ++g) {
+        // key g*8 .. g*8+7: chunk g / 8 (64 keys each), 16-byte vector g % 8 inside the 128-byte row, XOR-swizzled by the row
+        *reinterpret_cast<uint4*>(p_row + (g >> 3) * CH + (((g & 7) ^ (r & 7)) << 4)) =
+            make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+      }
+      ptx::fence_proxy_async();           // the MMA reads P through the async proxy
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&bar->p_full[t]);
+    }
+    if (ok && n_kv > 0) {
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->pv_done[t], (n_kv - 1) & 1, abort_flag))) { DFB_FA_FAIL(81); ok = false; }
+    }
+    if (ok && n_kv > 0) {
+      ptx::tc_fence_after();
+      const float inv = 1.f / l;
+      const long long tok = seg_start + qi;
+      bf16* dst = p.out + tok * p.out_row_stride + static_cast<long long>(h) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(t_o + c * 32, v);
+        ptx::tmem_ld_wait();
+        if (qi < seg_len) {
+          float o[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * inv;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) st8(dst + c * 32 + g * 8, pack8(o + g * 8));
+        }
+      }
+      if (qi < seg_len) p.lse[static_cast<long long>(h) * p.T + tok] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace fa2
 
 int* gemm_error_word_shared();
 
@@ -334,13 +574,20 @@ int flash_fwd_sm100(const void* q, long long ldq, const void* k, long long ldk, 
   Params p;
   p.cu_seqlens = cu_seqlens; p.out = reinterpret_cast<bf16*>(out); p.lse = lse; p.out_row_stride = ldo;
   p.T = T; p.hq = hq; p.hkv = hkv; p.sl2 = scale * 1.4426950408889634f; p.err = gemm_error_word_shared();
+  static const bool one_tile = [] { const char* e = getenv("DATAFLOW_FLASH_ONE_TILE"); return e && e[0] == '1'; }();
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(fa2::flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa2::SMEM_BYTES);
     configured = true;
   }
-  dim3 grid((max_seqlen + BM - 1) / BM, hq, nseg);
-  flash_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  if (one_tile) {
+    dim3 grid((max_seqlen + BM - 1) / BM, hq, nseg);
+    flash_fwd_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  } else {
+    dim3 grid((max_seqlen + 2 * BM - 1) / (2 * BM), hq, nseg);
+    fa2::flash_fwd2_kernel<<<grid, fa2::THREADS, fa2::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -432,6 +432,27 @@ static void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor&
   TORCH_CHECK(rc == 0, "flash_fwd: unsupported shape or alignment (head_dim must be 128; code ", rc, ")");
 }
 
+static void flash_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse,
+                      Tensor& dq, Tensor& dk, Tensor& dv, Tensor& scratch, const Tensor& cu_seqlens, int64_t max_seqlen, double scale) {
+  CHECK_BF16(dout); CHECK_BF16(q); CHECK_BF16(k); CHECK_BF16(v); CHECK_BF16(out); CHECK_BF16(dq); CHECK_BF16(dk); CHECK_BF16(dv);
+  CHECK_F32(lse); CHECK_F32(scratch); CHECK_I32(cu_seqlens);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "flash_bwd: (tokens, heads, dim) tensors");
+  const int64_t T = q.size(0), hq = q.size(1), hd = q.size(2), hkv = k.size(1);
+  auto like = [&](const Tensor& t, int64_t heads) {
+    return t.dim() == 3 && t.size(0) == T && t.size(1) == heads && t.size(2) == hd && t.stride(2) == 1 && t.stride(1) == hd;
+  };
+  TORCH_CHECK(like(q, hq) && like(dout, hq) && like(out, hq) && like(dq, hq) && like(k, hkv) && like(v, hkv) && like(dk, hkv) && like(dv, hkv),
+              "flash_bwd: shapes (heads must be contiguous inside a token row)");
+  TORCH_CHECK(lse.is_contiguous() && lse.size(0) == hq && lse.size(1) == T, "flash_bwd: lse is (heads, tokens)");
+  TORCH_CHECK(scratch.is_contiguous() && scratch.numel() >= 2 * hq * T, "flash_bwd: scratch holds 2 floats per (head, token)");
+  TORCH_CHECK(cu_seqlens.is_contiguous() && cu_seqlens.numel() >= 2, "flash_bwd: cu_seqlens");
+  int rc = dfb::flash_bwd_sm100(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
+                                dout.data_ptr(), dout.stride(0), lse.data_ptr<float>(), dq.data_ptr(), dq.stride(0), dk.data_ptr(),
+                                dk.stride(0), dv.data_ptr(), dv.stride(0), scratch.data_ptr(), cu_seqlens.data_ptr<int>(),
+                                cu_seqlens.numel() - 1, max_seqlen, T, hq, hkv, hd, scale, cur_stream());
+  TORCH_CHECK(rc == 0, "flash_bwd: unsupported shape or alignment (head_dim must be 128; code ", rc, ")");
+}
+
 // ---------------------------------------------------------------- fp8 lane
 static bool is_fp8_or_u8(const Tensor& t) {
   return t.scalar_type() == at::kByte || t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kFloat8_e5m2;
@@ -617,6 +638,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
   m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
   m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("l2norm_fwd", &l2norm_fwd);

@@ -98,6 +98,11 @@ int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int 
 int flash_fwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, void* out, long long ldo,
                     float* lse, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim, float scale,
                     cudaStream_t stream);
+// causal varlen flash attention backward on tcgen05 (attention_bwd.cu); ld2: scratch of hq * T float2
+int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* o, long long ldo,
+                    const void* dout, long long lddo, const float* lse, void* dq, long long lddq, void* dk, long long lddk, void* dv,
+                    long long lddv, void* ld2, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim,
+                    float scale, cudaStream_t stream);
 // fp8 lane: row-wise e4m3 quantisation and the dequantising CTA-pair GEMM
 int quant_fp8_rowwise(const void* x, long long ldx, void* q, long long ldq, float* scale, long long rows, int K, cudaStream_t s);
 int gemm_fp8_2sm(const void* A, long long lda, int a_fmt, const void* B, long long ldb, int b_fmt, void* D, long long ldd, int d_is_f32,

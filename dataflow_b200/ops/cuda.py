@@ -448,16 +448,42 @@ def flash_fwd_tcgen05(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
     return out, lse
 
 
+def _own_attention(q) -> bool:
+    """Shapes the hand-written attention kernels take: bf16, head_dim 128, heads contiguous inside a token row."""
+    return q.shape[-1] == 128 and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == 128
+
+
 def _flash_fwd(q, k, v, cu_seqlens, max_seqlen, scale=None, out=None):
-    """Attention forward of the default lane.  Measured on this device for 4 x 4096 tokens, 32 / 8 heads of 128: the vendor's
-    fused attention 0.45 ms, this repository's tcgen05 kernel 0.84 ms, the varlen flash kernels 1.55 ms — so rounds whose
-    sequences all have the same length go to the vendor kernel (which takes only such rounds), ragged rounds and everything
-    else with head_dim 128 to the tcgen05 kernel.  ``DFB_ATTN_FWD=sm100`` sends every round to the tcgen05 kernel."""
+    """Attention forward of the default lane: the tcgen05 kernel of this repository for head_dim 128 (uniform and ragged
+    rounds alike).  Other head sizes, and every round when ``DFB_ATTN_FWD=library`` is set, go to the vendor kernels of the
+    baseline lane."""
     from . import library
-    own = q.shape[-1] == 128 and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == 128
-    if own and (os.environ.get("DFB_ATTN_FWD") == "sm100" or not library._uniform(q, cu_seqlens, max_seqlen)):
+    if _own_attention(q) and os.environ.get("DFB_ATTN_FWD") != "library":
         return flash_fwd_tcgen05(q, k, v, cu_seqlens, max_seqlen, scale, out)
     return library.flash_fwd(q, k, v, cu_seqlens, max_seqlen, scale, out)
 
 
+def flash_bwd_tcgen05(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale=None, dq=None, dk=None, dv=None):
+    """Causal varlen attention backward on the hand-written kernels (attention_bwd.cu): deterministic, GQA summed inside the
+    dK / dV kernel.  Gradient buffers may be views into a packed (tokens, (hq + 2 hkv) * 128) buffer."""
+    LAUNCHES.total += 3
+    scale = scale if scale is not None else q.shape[-1] ** -0.5
+    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
+    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
+    scratch = torch.empty(2 * q.shape[1] * q.shape[0], dtype=torch.float32, device=q.device)
+    native().flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, scratch, cu_seqlens.to(torch.int32), int(max_seqlen), float(scale))
+    return dq, dk, dv
+
+
+def _flash_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale=None, dq=None, dk=None, dv=None):
+    from . import library
+    ok = _own_attention(q) and all(t is None or (t.stride(-1) == 1 and t.stride(1) == 128) for t in (dq, dk, dv)) and \
+        dout.stride(2) == 1 and dout.stride(1) == 128 and out.stride(2) == 1 and out.stride(1) == 128
+    if ok and os.environ.get("DFB_ATTN_BWD") != "library":
+        return flash_bwd_tcgen05(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale, dq, dk, dv)
+    return library.flash_bwd(dout, q, k, v, out, lse, cu_seqlens, max_seqlen, scale, dq, dk, dv)
+
+
 register("flash_fwd", "sm100", _flash_fwd, priority=P, requires=_native, native=True)
+register("flash_bwd", "sm100", _flash_bwd, priority=P, requires=_native, native=True, workspace=Workspace.internal())

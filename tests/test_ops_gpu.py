@@ -224,7 +224,7 @@ def test_attention_library_lane_matches_the_reference(shape):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", ["uniform", "ragged", "long"])
+@pytest.mark.parametrize("shape", ["uniform", "ragged", "long", "short"])
 def test_flash_fwd_tcgen05_kernel_matches_the_reference(shape):
     """The hand-written tcgen05 forward (TMA loads, S and P V in tensor memory, online softmax in registers) against the fp32
     reference: output and log-sum-exp, GQA, strided views of a packed qkv, sequences that end inside a tile."""
@@ -233,7 +233,7 @@ def test_flash_fwd_tcgen05_kernel_matches_the_reference(shape):
     resolve_kernels()
     impls = {k.name: k.fn for k in registered_ops()["flash_fwd"]}
     hq, hkv, d = 8, 2, 128
-    bounds = {"uniform": [0, 256, 512, 768, 1024], "ragged": [0, 100, 457, 460, 1024], "long": [0, 2048]}[shape]
+    bounds = {"uniform": [0, 256, 512, 768, 1024], "ragged": [0, 100, 457, 460, 1024], "long": [0, 2048], "short": [0, 1, 64, 65, 193]}[shape]
     t = bounds[-1]
     g = torch.Generator(device="cuda").manual_seed(9)
     qkv = (torch.randn(t, (hq + 2 * hkv) * d, device="cuda", generator=g) * 0.7).bfloat16()
@@ -253,3 +253,46 @@ def test_flash_fwd_tcgen05_kernel_matches_the_reference(shape):
     assert torch.allclose(lse.cpu(), lse_ref, atol=3e-3, rtol=3e-3)
     assert float((o.float().cpu() - o_ref.float()).norm() / o_ref.float().norm()) < 1e-2
     assert torch.allclose(o.float().cpu(), o_ref.float(), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", ["uniform", "ragged", "long", "short"])
+def test_flash_bwd_tcgen05_kernels_match_the_reference(shape):
+    """The hand-written tcgen05 backward (dK / dV kernel with keys as accumulator rows, dQ kernel, both recomputing the
+    scores in tensor memory) against the fp32 reference: dq, dk, dv, GQA summed over the group, strided views of packed
+    qkv / dqkv buffers, sequences that end inside a tile; the result is bitwise repeatable and covers every output byte."""
+    import torch
+    from dataflow_b200.ops import native, registered_ops, resolve_kernels
+    from dataflow_b200.ops.cuda import flash_bwd_tcgen05, flash_fwd_tcgen05
+    resolve_kernels()
+    impls = {op: {k.name: k.fn for k in registered_ops()[op]} for op in ("flash_fwd", "flash_bwd")}
+    hq, hkv, d = 8, 2, 128
+    bounds = {"uniform": [0, 256, 512, 768, 1024], "ragged": [0, 100, 457, 460, 1024], "long": [0, 2048], "short": [0, 1, 64, 65, 193]}[shape]
+    t = bounds[-1]
+    g = torch.Generator(device="cuda").manual_seed(11)
+    qkv = (torch.randn(t, (hq + 2 * hkv) * d, device="cuda", generator=g) * 0.7).bfloat16()
+    q = qkv[:, :hq * d].unflatten(1, (hq, d))
+    k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+    v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
+    cu = torch.tensor(bounds, dtype=torch.int32, device="cuda")
+    mx = max(b - a for a, b in zip(bounds[:-1], bounds[1:]))
+    o, lse = flash_fwd_tcgen05(q, k, v, cu, mx)
+    do = (torch.randn(t, hq, d, device="cuda", generator=g) * 0.5).bfloat16()
+    outs = []
+    for poison in (3.0, -7.0):
+        dqkv = torch.full((t, (hq + 2 * hkv) * d), poison, device="cuda", dtype=torch.bfloat16)
+        dq = dqkv[:, :hq * d].unflatten(1, (hq, d))
+        dk = dqkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+        dv = dqkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
+        flash_bwd_tcgen05(do, q, k, v, o, lse, cu, mx, dq=dq, dk=dk, dv=dv)
+        torch.cuda.synchronize()
+        assert native().gemm_last_error() == 0
+        outs.append(dqkv)
+    assert torch.equal(outs[0], outs[1])                    # every byte written, the same way, whatever was there before
+    o_ref, lse_ref = impls["flash_fwd"]["eager"](q.cpu(), k.cpu(), v.cpu(), torch.tensor(bounds), mx)
+    rq, rk, rv = impls["flash_bwd"]["eager"](do.cpu(), q.cpu(), k.cpu(), v.cpu(), o_ref, lse_ref, torch.tensor(bounds), mx)
+    for name, a, b in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+        err = float((a.float().cpu() - b.float()).norm() / b.float().norm())
+        assert err < 2e-2, (name, err)
+    d2 = impls["flash_bwd"]["sm100"](do, q, k, v, o, lse, cu, mx)       # the default lane is this kernel
+    assert torch.equal(d2[0], dq) and torch.equal(d2[1], dk) and torch.equal(d2[2], dv)
