@@ -418,7 +418,10 @@ static void tp_gemm_rs(const Tensor& x, const Tensor& w, bool b_mn, Tensor& d, c
 
 // ---------------------------------------------------------------- attention
 static void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& out, Tensor& lse, const Tensor& cu_seqlens,
-                      int64_t max_seqlen, double scale) {
+                      int64_t max_seqlen, double scale, const c10::optional<Tensor>& trace) {
+  if (trace.has_value())
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 3 * 32 * 8,
+                "flash_fwd: trace is a CUDA int64 tensor of at least 768 elements");
   CHECK_BF16(q); CHECK_BF16(k); CHECK_BF16(v); CHECK_BF16(out); CHECK_F32(lse); CHECK_I32(cu_seqlens);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && out.dim() == 3, "flash_fwd: (tokens, heads, dim) tensors");
   const int64_t T = q.size(0), hq = q.size(1), hd = q.size(2), hkv = k.size(1);
@@ -428,7 +431,7 @@ static void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor&
               lse.size(0) == hq && lse.size(1) == T, "flash_fwd: shapes");
   int rc = dfb::flash_fwd_sm100(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
                                 lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(), cu_seqlens.numel() - 1, max_seqlen, T, hq, hkv, hd, scale,
-                                cur_stream());
+                                cur_stream(), trace.has_value() ? reinterpret_cast<long long*>(trace->data_ptr<int64_t>()) : nullptr);
   TORCH_CHECK(rc == 0, "flash_fwd: unsupported shape or alignment (head_dim must be 128; code ", rc, ")");
 }
 
@@ -637,7 +640,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rowdot", &moe_rowdot);
   m.def("moe_grouped_mm", &moe_grouped_mm);
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
-  m.def("flash_fwd", &flash_fwd);
+  m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("cu_seqlens"),
+        py::arg("max_seqlen"), py::arg("scale"), py::arg("trace") = py::none());
   m.def("flash_bwd", &flash_bwd);
   m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
   m.def("gemm_fp8", &gemm_fp8);

@@ -97,7 +97,7 @@ int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int 
 // causal varlen flash attention forward on tcgen05 (attention.cu)
 int flash_fwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, void* out, long long ldo,
                     float* lse, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim, float scale,
-                    cudaStream_t stream);
+                    cudaStream_t stream, long long* trace = nullptr);
 // causal varlen flash attention backward on tcgen05 (attention_bwd.cu); ld2: scratch of hq * T float2
 int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* o, long long ldo,
                     const void* dout, long long lddo, const float* lse, void* dq, long long lddq, void* dk, long long lddk, void* dv,

@@ -224,6 +224,7 @@ void Engine::on_transfer_done(int dir) {
   if (dir == 0) {
     o.fast.state = SlotState::LIVE;
     o.fast.version = o.backing.version;
+    evicted_[fl->x.obj] = 0;
   } else {
     o.backing.state = SlotState::LIVE;
     o.backing.version = o.fast.version;
@@ -237,6 +238,64 @@ void Engine::on_transfer_done(int dir) {
   }
   note("transfer_end", fl->name);
   poke();
+}
+
+// ----------------------------------------------------------------------------- pressure-eviction valve
+int Engine::next_use(int obj, int from_task) const {
+  for (int i = from_task; i < static_cast<int>(p_->tasks.size()); ++i) {
+    const TaskIR& t = p_->tasks[i];
+    for (int in : t.inputs) if (in == obj) return i;
+    for (auto& d : t.offloads) if (d.obj == obj) return i;
+  }
+  return static_cast<int>(p_->tasks.size()) + (p_->objs[obj].final_loc == FAST ? 0 : 1);   // never again: best victim
+}
+
+// Called with nothing in flight and task ``task`` not admissible.  Evicts ONE resident that the task does not touch:
+// the one whose next use is farthest (Belady).  Returns false when there is nothing to evict.
+bool Engine::evict_for_pressure(int task, bool) {
+  const TaskIR& t = p_->tasks[task];
+  int victim = -1, victim_use = -1;
+  for (int o = 0; o < static_cast<int>(objs_.size()); ++o) {
+    if (objs_[o].fast.state != SlotState::LIVE || objs_[o].fast.buf.external) continue;
+    bool touched = false;
+    for (int in : t.inputs) touched |= in == o;
+    for (int m : t.mutates) touched |= m == o;
+    for (auto& out : t.outputs) touched |= out.obj == o;
+    if (touched) continue;
+    // it must be possible to bring it back: the backing tier has to admit a copy if there is none yet
+    bool has_copy = objs_[o].backing.state == SlotState::LIVE && objs_[o].backing.version == objs_[o].version;
+    if (!has_copy && objs_[o].backing.state == SlotState::ABSENT && free_bytes(BACKING) < p_->objs[o].size) continue;
+    if (!has_copy && objs_[o].backing.state != SlotState::ABSENT && objs_[o].backing.state != SlotState::LIVE) continue;
+    int use = next_use(o, task);
+    if (use > victim_use) { victim = o; victim_use = use; }
+  }
+  if (victim < 0) return false;
+  ObjState& o = objs_[victim];
+  out_->stats.pressure_evictions++;
+  evicted_[victim] = 1;
+  bool has_copy = o.backing.state == SlotState::LIVE && o.backing.version == o.version;
+  if (has_copy) {
+    uncharge(FAST, p_->objs[victim].size);
+    free_slot(o.fast, FAST);
+    note("evict", p_->objs[victim].id);
+  } else {
+    o.fast.state = SlotState::PENDING_OUTBOUND;
+    queue_[1].push_front({victim, 1, p_->objs[victim].size, -1.0});
+    note("evict_writeback", p_->objs[victim].id);
+  }
+  poke();
+  return true;
+}
+
+// An input that the valve evicted: queue its reload in front of everything else.  False when it is not such an object.
+bool Engine::reload_evicted(int obj) {
+  ObjState& o = objs_[obj];
+  if (!evicted_[obj] || o.fast.state != SlotState::ABSENT || o.backing.state != SlotState::LIVE) return false;
+  for (auto& x : queue_[0]) if (x.obj == obj) return true;
+  queue_[0].push_front({obj, 0, p_->objs[obj].size, -1.0});
+  note("evict_reload", p_->objs[obj].id);
+  poke();
+  return true;
 }
 
 // ----------------------------------------------------------------------------- task completion
@@ -257,6 +316,20 @@ void Engine::on_task_done(int idx) {
   note("task_end", t.id);
   for (int r : t.releases) {
     ObjState& o = objs_[r];
+    if (evicted_[r] && o.fast.state != SlotState::LIVE) {
+      // the valve already took it out of fast memory; a reload that has not started yet is dropped, one in flight lands
+      // first (the release is then applied by on_transfer_done through ``release_on_arrival``)
+      for (auto it = queue_[0].begin(); it != queue_[0].end(); ++it)
+        if (it->obj == r) { queue_[0].erase(it); break; }
+      if (o.fast.state == SlotState::INBOUND || o.fast.state == SlotState::PENDING_OUTBOUND || o.fast.state == SlotState::OUTBOUND)
+        throw EngineError("ExecutionError", "task " + t.id + " releases " + p_->objs[r].id + " while the eviction valve is moving it");
+      evicted_[r] = 0;
+      if (idx >= p_->objs[r].last_ref && p_->objs[r].final_loc < 0 && o.backing.state == SlotState::LIVE) {
+        uncharge(BACKING, p_->objs[r].size);
+        free_slot(o.backing, BACKING);
+      }
+      continue;
+    }
     if (o.fast.state != SlotState::LIVE)
       throw EngineError("ExecutionError", "task " + t.id + " releases " + p_->objs[r].id + " which is not live in fast memory");
     uncharge(FAST, p_->objs[r].size);
@@ -268,6 +341,12 @@ void Engine::on_task_done(int idx) {
   }
   for (auto& d : t.offloads) {
     ObjState& o = objs_[d.obj];
+    if (evicted_[d.obj] && o.fast.state == SlotState::ABSENT && o.backing.state == SlotState::LIVE && o.backing.version == o.version) {
+      evicted_[d.obj] = 0;             // the valve has done this offload already
+      for (auto it = queue_[0].begin(); it != queue_[0].end(); ++it)
+        if (it->obj == d.obj) { queue_[0].erase(it); break; }
+      continue;
+    }
     if (o.fast.state != SlotState::LIVE)
       throw EngineError("ExecutionError", "task " + t.id + " offloads " + p_->objs[d.obj].id + " which is not live in fast memory");
     if (o.backing.state != SlotState::ABSENT && o.backing.state != SlotState::LIVE)
@@ -277,6 +356,13 @@ void Engine::on_task_done(int idx) {
   }
   for (auto& d : t.prefetches) {
     ObjState& o = objs_[d.obj];
+    if (evicted_[d.obj]) {
+      // the plan brings it back itself: the valve's own reload (if it queued one) is that prefetch
+      evicted_[d.obj] = 0;
+      bool queued = false;
+      for (auto& x : queue_[0]) queued |= x.obj == d.obj;
+      if (queued || o.fast.state == SlotState::INBOUND || o.fast.state == SlotState::LIVE) continue;
+    }
     if (o.fast.state == SlotState::LIVE || o.fast.state == SlotState::INBOUND || o.fast.state == SlotState::RESERVED)
       throw EngineError("ExecutionError", "task " + t.id + " prefetches " + p_->objs[d.obj].id + " which already has a fast copy");
     bool going_out = o.fast.state == SlotState::PENDING_OUTBOUND || o.fast.state == SlotState::OUTBOUND ||
@@ -383,6 +469,7 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
   p_ = &p; opt_ = &opt; out_ = &out;
   objs_.assign(p.objs.size(), ObjState());
   alloc_count_.assign(p.objs.size(), 0);
+  evicted_.assign(p.objs.size(), 0);
   used_[0] = used_[1] = 0; workspace_ = 0;
   queue_[0].clear(); queue_[1].clear(); flight_[0].reset(); flight_[1].reset();
   deferred_.clear(); xfer_seq_.clear(); pending_intervals_.clear(); events_to_release_.clear();
@@ -426,7 +513,13 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
       if (!short_mem && p.fast_cap >= 0 && task_done_upto_ < i - 1 && !queue_[0].empty() && !flight_[0])
         short_mem = used_[FAST] + need + queue_[0].front().size > p.fast_cap;
       if (ready && !short_mem) break;
+      // an input the valve evicted earlier comes back in front of everything else queued
+      bool reloading = false;
+      for (int in : t.inputs) reloading |= reload_evicted(in);
       if (!pump_one(true)) {
+        // Nothing in flight and the task still cannot start: the realised order has left the plan.  Make room by
+        // evicting the resident whose next use is farthest, as often as it takes; give up only when nothing is left.
+        if (evict_for_pressure(i, reloading)) continue;
         deadlock("task " + t.id + (missing.empty() ? std::string(" needs ") + std::to_string(need) + " fast bytes"
                                                     : " waits for input " + missing));
       }

@@ -8,6 +8,11 @@
 //   h2d done   : fast copy live -> poke lanes
 //   d2h done   : fast copy freed, backing copy live, deferred prefetches join the
 //                h2d queue -> poke lanes
+// When the realised order of completions diverges from the plan (a copy that finishes early takes the room a task's
+// outputs were planned into), the pressure-eviction valve keeps the run alive: with nothing in flight and the next task
+// still not admissible, the resident object whose next use is farthest is evicted (dropped if its backing copy is current,
+// else written back first) and reloaded in front of the task that needs it next; directives that later name the evicted
+// object tolerate its absence.  Each eviction is counted (RunStats::pressure_evictions; a healthy run has none).
 // Dispatch is strictly paced: task i+1 is launched only after task i's token was
 // observed, all its inputs are live in fast memory and the ledger admits its fast
 // outputs.  Two FIFO transfer lanes, one transfer in flight each, destination bytes
@@ -200,6 +205,10 @@ class Engine {
   int64_t free_bytes(Location loc) const;
   void free_slot(Slot& s, Location loc);
   BufferRef get_fast(int obj, int64_t size);
+  // pressure-eviction valve (see run_dispatch): pick and evict the resident whose next use is farthest; queue reloads
+  bool evict_for_pressure(int task, bool need_reload_room);
+  bool reload_evicted(int obj);
+  int next_use(int obj, int from_task) const;
   double xfer_us(const Xfer& x) const;
   void note(const std::string& kind, const std::string& what);
   [[noreturn]] void deadlock(const std::string& why);
@@ -213,6 +222,7 @@ class Engine {
   std::vector<ObjState> objs_;
   std::set<int> done_early_;           // completed tasks whose predecessors have not retired yet
   std::vector<int> alloc_count_;       // fast allocations of each object so far in this run (indexes the placement)
+  std::vector<char> evicted_;          // objects the valve took out of fast memory although the plan keeps them there
   int64_t used_[2] = {0, 0};
   int64_t workspace_ = 0;
   std::deque<Xfer> queue_[2];

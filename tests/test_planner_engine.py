@@ -180,3 +180,47 @@ def test_placement_escape_valve_keeps_a_run_alive_when_the_plan_does_not_match()
     res.raise_if_failed()
     assert res.placement_escapes > 0
     assert res.makespan_us == pytest.approx(base.makespan_us) and res.peak_fast_bytes == base.peak_fast_bytes
+
+
+# ---------------------------------------------------------------- pressure-eviction valve
+def test_pressure_eviction_valve_pages_an_unplanned_program_through_a_small_memory():
+    """No directives at all and a capacity that cannot hold what the chain leaves resident: without the valve this is a
+    deadlock; with it the engine evicts the resident whose next use is farthest (writing it back first when it has no
+    current backing copy), reloads it in front of the task that reads it, and counts every eviction."""
+    from dataflow_b200.core import ObjectSpec, OutputSpec, Program, TaskSpec
+    p = Program("paging",
+                (ObjectSpec("A", 10, "fast"), ObjectSpec("R", 40, "fast")),
+                (TaskSpec("t0", inputs=("A",), outputs=(OutputSpec("Z", 60),), runtime_us=5.0),
+                 TaskSpec("t1", inputs=("A", "R"), outputs=(OutputSpec("W", 10),), runtime_us=5.0),
+                 TaskSpec("t2", inputs=("Z", "W"), outputs=(OutputSpec("V", 10),), runtime_us=5.0)),
+                final_locations={"V": "fast"}, fast_memory_capacity=100, backing_memory_capacity=1000,
+                bandwidth_from_slow=10, bandwidth_to_slow=10)
+    res = Engine(FakeBackend()).execute(p, record_events=True)
+    res.raise_if_failed()
+    assert res.pressure_evictions >= 2                    # R made room for Z, then Z made room for R
+    assert res.peak_fast_bytes <= 100
+    kinds = [e.kind for e in res.trace.events]
+    assert "evict_writeback" in kinds and "evict_reload" in kinds
+    names = [iv.name for iv in res.trace.intervals]
+    # R leaves before t0 can write Z, and is back before t1 reads it
+    assert names.index("to_slow:R") < names.index("t0") < names.index("from_slow:R") < names.index("t1")
+
+
+def test_pressure_eviction_valve_survives_a_plan_made_for_a_larger_memory():
+    """A planned chain run in less memory than it was planned for (the realised state has left the plan): the valve keeps
+    it alive inside the smaller capacity, the final locations still hold, and the same plan in its own capacity needs no
+    eviction at all."""
+    import dataclasses
+    r = pressurefit(train_chain(L=4, rounds=2), 3000)
+    prog = from_sim_chain(r.chain)
+    calm = Engine(FakeBackend()).execute(prog).raise_if_failed()
+    assert calm.pressure_evictions == 0
+    tight = dataclasses.replace(prog, fast_memory_capacity=int(calm.peak_fast_bytes * 0.93))
+    res = Engine(FakeBackend()).execute(tight)
+    res.raise_if_failed()
+    assert res.pressure_evictions > 0 and res.peak_fast_bytes <= tight.fast_memory_capacity
+    assert res.makespan_us >= calm.makespan_us
+    # a task whose own inputs and outputs exceed the capacity still ends in a reported deadlock, not a hang
+    impossible = dataclasses.replace(prog, fast_memory_capacity=1000)
+    bad = Engine(FakeBackend()).execute(impossible)
+    assert bad.outcome.error_kind in ("DeadlockError", "LedgerError")

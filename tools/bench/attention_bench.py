@@ -25,6 +25,8 @@ def main(argv=None) -> int:
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None, help="own | library: time one lane only (e.g. for a profiler capture)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the forward kernel's own per-key-tile clock stamps (one CTA: its MMA thread and one softmax thread per query tile)")
     a = ap.parse_args(argv)
     import torch
     from dataflow_b200.ops import native, registered_ops, resolve_kernels
@@ -61,12 +63,35 @@ def main(argv=None) -> int:
             total += e0.elapsed_time(e1)
         return total / a.iters
 
+    if a.timeline:
+        trace = torch.zeros(3 * 32 * 8, dtype=torch.int64, device="cuda")
+        o = torch.empty(q.shape, dtype=q.dtype, device="cuda")
+        lse = torch.empty(HQ, T, dtype=torch.float32, device="cuda")
+        for _ in range(2):
+            native().flash_fwd(q, k, v, o, lse, cu, S, D ** -0.5, trace)
+        torch.cuda.synchronize()
+        tr = trace.view(3, 32, 8).cpu()
+        t0 = int(tr[tr > 0].min())
+        names = ["softmax tile 0: wait S | S seen | loaded | max done | exp done | arrived",
+                 "softmax tile 1: same", "MMA thread: [tile0: wait P | P seen | issued] [tile1: ...]"]
+        for who in range(3):
+            print(names[who])
+            for j in range(2, 12):
+                print("  j=%2d " % j + " ".join("%7d" % (int(x) - t0 if x > 0 else -1) for x in tr[who, j]))
+        return 0
     fwd_flops = 4.0 * T * S * HQ * D / 2
     res = {"shape": {"batch": B, "seq": S, "hq": HQ, "hkv": HKV, "d": D}, "l2": "flushed between iterations"}
     if a.only != "library":
         o, lse = flash_fwd_tcgen05(q, k, v, cu, S)
         t = timed(lambda: flash_fwd_tcgen05(q, k, v, cu, S))
         res["own_fwd_ms"], res["own_fwd_tflops"] = t, fwd_flops / t / 1e9
+        torch.cuda.synchronize()
+        if native().gemm_last_error():
+            raise SystemExit(f"the forward kernel raised error word {native().gemm_last_error()}")
+        flash_bwd_tcgen05(do, q, k, v, o, lse, cu, S, dq=dq, dk=dk, dv=dv)
+        torch.cuda.synchronize()
+        if native().gemm_last_error():          # a kernel that gave up once would give up in every timed launch too
+            raise SystemExit(f"the backward kernels raised error word {native().gemm_last_error()}")
         t = timed(lambda: flash_bwd_tcgen05(do, q, k, v, o, lse, cu, S, dq=dq, dk=dk, dv=dv))
         res["own_bwd_ms"], res["own_bwd_tflops"] = t, 2.5 * fwd_flops / t / 1e9
         res["error_word"] = native().gemm_last_error()
