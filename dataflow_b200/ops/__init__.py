@@ -16,6 +16,9 @@ def _load():
         import importlib
         import torch  # noqa: F401  (libtorch must be loaded before the extension)
         _mod = importlib.import_module(__name__ + "._ops")
+        # device buffers of the engine become tensors through the extension's ``at::from_blob`` from now on
+        from ..runtime import interop
+        interop.register_device_view_factory(_mod.tensor_from_ptr)
     except Exception as e:  # missing build or missing CUDA libs
         _load_error = e
     return _mod

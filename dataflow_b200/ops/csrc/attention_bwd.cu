@@ -312,9 +312,17 @@ struct Bars {
   int abort;
 };
 
+// kTrace: CTA (0, 0, 0) records clock64() stamps of its first 32 tiles into ``trace`` — per tile 8 slots for each of three
+// observers (thread 0 of either math group, the MMA thread).  A profiling aid: the regular launch passes false.
+constexpr int kTraceTiles = 32, kTraceSlots = 8;
+#define DFB_BSTAMP(who, it, slot)                                                                                       \
+  do { if (kTrace && trace_on && (it) < kTraceTiles) trace[((who) * kTraceTiles + (it)) * kTraceSlots + (slot)] = clock64(); } while (0)
+
+template <bool kTrace>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
-                      const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, Params p) {
+                      const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, Params p, long long* trace) {
+  const bool trace_on = kTrace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
   const int seg = blockIdx.y, kvh = blockIdx.x;
   const int seg_start = p.cu_seqlens[seg];
   const int seg_len = p.cu_seqlens[seg + 1] - seg_start;
@@ -416,7 +424,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (ok && !(issue_sdp(0) && (n_it < 2 || issue_sdp(1)))) { DFB_FAB_FAIL(103); ok = false; }
         for (int it = 0; it < n_it && ok; ++it) {
           const int st = it % STAGES, b = it & 1;
+          DFB_BSTAMP(2, it, 0);
           if (!ptx::mbar_wait(&bar->pds_full[b], (it >> 1) & 1, abort_flag)) { DFB_FAB_FAIL(104); ok = false; break; }
+          DFB_BSTAMP(2, it, 1);
           ptx::tc_fence_after();
           const uint32_t q_addr = ptx::smem_u32(smem + OFF_QDO + st * 2 * TILE64), do_addr = q_addr + TILE64;
           // Q_i / dO_i once more, as MN-major operands: 64-column chunks CH64 apart, queries 128 bytes apart; P^T and dS^T
@@ -427,7 +437,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
           for (int k = 0; k < 4; ++k) ptx::umma_bf16_ts(tmem_dk, tmem_dpt + b * 64 + packed_col(k), b_q + k * mn_step, idesc_acc, (it | k) != 0);
           ptx::umma_commit(&bar->qdo_empty[st]);
+          DFB_BSTAMP(2, it, 2);
           if (it + 2 < n_it && !issue_sdp(it + 2)) { DFB_FAB_FAIL(103); ok = false; break; }   // ordered behind the products that read buffer b
+          DFB_BSTAMP(2, it, 3);
         }
         if (ok) ptx::umma_commit(&bar->acc_done);
       }
@@ -445,6 +457,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     for (int it = grp; it < n_it && ok; it += 2) {
       const int st = it % STAGES, b = grp;
       const int g = it / per, i = i0 + it - g * per;
+      const bool me = trace_on && (threadIdx.x & 255) == 128;          // thread 0 of the group's first warp
+#define DFB_BSTAMP_M(slot) do { if (kTrace && me && it < kTraceTiles) trace[(grp * kTraceTiles + it) * kTraceSlots + (slot)] = clock64(); } while (0)
+      DFB_BSTAMP_M(0);
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bar->sdp_full[b], (it >> 1) & 1, abort_flag) &&
                                        ptx::mbar_wait(&bar->qdo_full[st], (it / STAGES) & 1, abort_flag))) { DFB_FAB_FAIL(105); ok = false; break; }
       ptx::tc_fence_after();
@@ -452,7 +467,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const uint32_t col = lane_base + b * 64 + hh * 32;
       ptx::tmem_ld_32x32(tmem_st + col, reinterpret_cast<uint32_t*>(s));
       ptx::tmem_ld_32x32(tmem_dpt + col, reinterpret_cast<uint32_t*>(dp));
+      DFB_BSTAMP_M(1);
       ptx::tmem_ld_wait();
+      DFB_BSTAMP_M(2);
       const float2* ld = reinterpret_cast<const float2*>(smem + OFF_LD + st * 64 * 8) + hh * 32;
       uint32_t pp[16], pd[16];
       const int q_base = i * 64 + hh * 32;
@@ -463,12 +480,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       else
         prob_and_ds<false, true>(s, dp, p.sl2, lse_delta, [&](int) { return false; }, pp, pd);
       // P^T and dS^T as packed pairs over the first half of this thread's own S^T / dP^T columns
+      DFB_BSTAMP_M(3);
       ptx::tmem_st_32x16(tmem_st + col, pp);
       ptx::tmem_st_32x16(tmem_dpt + col, pd);
       ptx::tmem_st_wait();
+      DFB_BSTAMP_M(4);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&bar->pds_full[b]);
+      DFB_BSTAMP_M(5);
     }
     if (ok && !__all_sync(0xffffffffu, ptx::mbar_wait(&bar->acc_done, 0, abort_flag))) { DFB_FAB_FAIL(107); ok = false; }
     if (ok) {
@@ -509,7 +529,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* o, long long ldo,
                     const void* dout, long long lddo, const float* lse, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                     long long lddv, void* ld2, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim,
-                    float scale, cudaStream_t stream) {
+                    float scale, cudaStream_t stream, long long* trace) {
   using namespace fab;
   if (head_dim != D || hkv <= 0 || hq % hkv || nseg <= 0 || T <= 0 || max_seqlen <= 0) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 4) || (lddo % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -2;
@@ -531,14 +551,16 @@ int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, 
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(dq::flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dq::SMEM_BYTES);
-    cudaFuncSetAttribute(dkv::flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_BYTES);
+    cudaFuncSetAttribute(dkv::flash_bwd_dkdv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_BYTES);
+    cudaFuncSetAttribute(dkv::flash_bwd_dkdv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_BYTES);
     configured = true;
   }
   const long long warps = static_cast<long long>(T) * hq;
   flash_bwd_prep_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const bf16*>(o), ldo, reinterpret_cast<const bf16*>(dout), lddo, lse, reinterpret_cast<float2*>(ld2), T, hq);
   const int n_t = (max_seqlen + 127) / 128;
-  dkv::flash_bwd_dkdv_kernel<<<dim3(hkv, nseg, n_t), THREADS, dkv::SMEM_BYTES, stream>>>(tq64, tdo64, tk, tv, p);
+  if (trace) dkv::flash_bwd_dkdv_kernel<true><<<dim3(hkv, nseg, n_t), THREADS, dkv::SMEM_BYTES, stream>>>(tq64, tdo64, tk, tv, p, trace);
+  else dkv::flash_bwd_dkdv_kernel<false><<<dim3(hkv, nseg, n_t), THREADS, dkv::SMEM_BYTES, stream>>>(tq64, tdo64, tk, tv, p, nullptr);
   dq::flash_bwd_dq_kernel<<<dim3(hq, nseg, n_t), THREADS, dq::SMEM_BYTES, stream>>>(tq, tdo, tk64, tv64, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -436,7 +436,11 @@ static void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor&
 }
 
 static void flash_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse,
-                      Tensor& dq, Tensor& dk, Tensor& dv, Tensor& scratch, const Tensor& cu_seqlens, int64_t max_seqlen, double scale) {
+                      Tensor& dq, Tensor& dk, Tensor& dv, Tensor& scratch, const Tensor& cu_seqlens, int64_t max_seqlen, double scale,
+                      const c10::optional<Tensor>& trace) {
+  if (trace.has_value())
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 3 * 32 * 8,
+                "flash_bwd: trace is a CUDA int64 tensor of at least 768 elements");
   CHECK_BF16(dout); CHECK_BF16(q); CHECK_BF16(k); CHECK_BF16(v); CHECK_BF16(out); CHECK_BF16(dq); CHECK_BF16(dk); CHECK_BF16(dv);
   CHECK_F32(lse); CHECK_F32(scratch); CHECK_I32(cu_seqlens);
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "flash_bwd: (tokens, heads, dim) tensors");
@@ -452,8 +456,16 @@ static void flash_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, cons
   int rc = dfb::flash_bwd_sm100(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
                                 dout.data_ptr(), dout.stride(0), lse.data_ptr<float>(), dq.data_ptr(), dq.stride(0), dk.data_ptr(),
                                 dk.stride(0), dv.data_ptr(), dv.stride(0), scratch.data_ptr(), cu_seqlens.data_ptr<int>(),
-                                cu_seqlens.numel() - 1, max_seqlen, T, hq, hkv, hd, scale, cur_stream());
+                                cu_seqlens.numel() - 1, max_seqlen, T, hq, hkv, hd, scale, cur_stream(),
+                                trace.has_value() ? reinterpret_cast<long long*>(trace->data_ptr<int64_t>()) : nullptr);
   TORCH_CHECK(rc == 0, "flash_bwd: unsupported shape or alignment (head_dim must be 128; code ", rc, ")");
+}
+
+static Tensor umma_probe(int64_t kind, int64_t n, int64_t count, int64_t nacc) {
+  Tensor out = at::zeros({3}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA));
+  int rc = dfb::umma_probe((int)kind, (int)n, (int)count, (int)nacc, reinterpret_cast<long long*>(out.data_ptr<int64_t>()), cur_stream());
+  TORCH_CHECK(rc == 0, "umma_probe: kind 0..3, n a multiple of 16 up to 256, nacc * n <= 448 (code ", rc, ")");
+  return out;
 }
 
 // ---------------------------------------------------------------- fp8 lane
@@ -642,7 +654,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_grouped_wgrad", &moe_grouped_wgrad);
   m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("cu_seqlens"),
         py::arg("max_seqlen"), py::arg("scale"), py::arg("trace") = py::none());
-  m.def("flash_bwd", &flash_bwd);
+  m.def("umma_probe", &umma_probe);
+  m.def("flash_bwd", &flash_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("dq"),
+        py::arg("dk"), py::arg("dv"), py::arg("scratch"), py::arg("cu_seqlens"), py::arg("max_seqlen"), py::arg("scale"),
+        py::arg("trace") = py::none());
   m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("l2norm_fwd", &l2norm_fwd);

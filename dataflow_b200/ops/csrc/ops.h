@@ -94,6 +94,9 @@ int moe_combine(const void* base, const void* yp, const float* w, const int* row
 int moe_dispatch_bwd(const void* dxp, const int* row_of, void* out, int t, int d, int K, int accumulate, cudaStream_t s);
 int moe_scale_rows(void* xp, const float* w, const int* row_of, int slots, int d, cudaStream_t s);
 int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int slots, int d, cudaStream_t s);
+// tensor-pipe step cost by shape and operand source (umma_probe.cu); out: 3 int64 (issue cycles, total cycles, timed out)
+int umma_probe(int kind, int n, int count, int nacc, long long* out, cudaStream_t stream);
+
 // causal varlen flash attention forward on tcgen05 (attention.cu)
 int flash_fwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, void* out, long long ldo,
                     float* lse, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim, float scale,
@@ -102,7 +105,7 @@ int flash_fwd_sm100(const void* q, long long ldq, const void* k, long long ldk, 
 int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* o, long long ldo,
                     const void* dout, long long lddo, const float* lse, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                     long long lddv, void* ld2, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim,
-                    float scale, cudaStream_t stream);
+                    float scale, cudaStream_t stream, long long* trace = nullptr);
 // fp8 lane: row-wise e4m3 quantisation and the dequantising CTA-pair GEMM
 int quant_fp8_rowwise(const void* x, long long ldx, void* q, long long ldq, float* scale, long long rows, int K, cudaStream_t s);
 int gemm_fp8_2sm(const void* A, long long lda, int a_fmt, const void* B, long long ldb, int b_fmt, void* D, long long ldd, int d_is_f32,

@@ -33,6 +33,34 @@ def dtype_name(torch_dtype) -> str:
 
 _view_cache: dict[tuple, object] = {}
 
+# How a device address becomes a tensor.  The runtime itself knows one way that needs nothing but torch (the CUDA array
+# interface); a package that has a faster native factory (``at::from_blob`` inside an extension) registers it here when it
+# is imported.  The runtime never imports such a package itself.
+_device_factory = None
+
+
+def register_device_view_factory(fn) -> None:
+    """``fn(address, shape_list, dtype_name, device_ordinal) -> tensor`` aliasing device memory."""
+    global _device_factory
+    _device_factory = fn
+
+
+class _DeviceWindow:
+    """``nbytes`` of device memory at ``ptr`` through the CUDA array interface (a zero-copy import for torch)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _device_view(ptr: int, shape, dtype: str, nbytes: int, device: int):
+    import torch
+    if _device_factory is not None:
+        return _device_factory(ptr, list(shape), dtype, device)
+    if nbytes == 0:
+        return torch.empty(shape, dtype=_dtypes()[dtype], device=torch.device("cuda", device))
+    raw = torch.as_tensor(_DeviceWindow(ptr, nbytes), device=torch.device("cuda", device))
+    return raw.view(_dtypes()[dtype]).reshape(shape)
+
 
 def torch_view(buffer, shape: Sequence[int], dtype: str = "bf16", offset_bytes: int = 0, device: int | None = None):
     """Tensor aliasing ``buffer`` (an object with ``ptr`` and ``size``, or a raw address).
@@ -62,8 +90,7 @@ def torch_view(buffer, shape: Sequence[int], dtype: str = "bf16", offset_bytes: 
             window = (ctypes.c_char * nbytes).from_address(ptr)
             t = torch.frombuffer(window, dtype=torch.uint8).view(_dtypes()[dtype]).reshape(shape)
     else:
-        from ..ops import native
-        t = native().tensor_from_ptr(ptr, list(shape), dtype, int(device))
+        t = _device_view(ptr, shape, dtype, nbytes, int(device))
     if len(_view_cache) > 65536:
         _view_cache.clear()
     _view_cache[key] = t

@@ -78,6 +78,19 @@ def main(argv=None) -> int:
             print(names[who])
             for j in range(2, 12):
                 print("  j=%2d " % j + " ".join("%7d" % (int(x) - t0 if x > 0 else -1) for x in tr[who, j]))
+        # the dK / dV kernel of the backward: math group 0 / 1 (wait S | S seen | loaded | math done | stored | arrived) and the
+        # MMA thread (wait P | P seen | dV dK issued | next S^T dP^T issued)
+        trace.zero_()
+        scratch = torch.empty(2 * HQ * T, dtype=torch.float32, device="cuda")
+        for _ in range(2):
+            native().flash_bwd(do, q, k, v, o, lse, dq, dk, dv, scratch, cu, S, D ** -0.5, trace)
+        torch.cuda.synchronize()
+        tr = trace.view(3, 32, 8).cpu()
+        t0 = int(tr[tr > 0].min())
+        for who, name in enumerate(["dK/dV math group 0", "dK/dV math group 1", "dK/dV MMA thread"]):
+            print(name)
+            for j in range(4, 16):
+                print("  it=%2d " % j + " ".join("%7d" % (int(x) - t0 if x > 0 else -1) for x in tr[who, j]))
         return 0
     fwd_flops = 4.0 * T * S * HQ * D / 2
     res = {"shape": {"batch": B, "seq": S, "hq": HQ, "hkv": HKV, "d": D}, "l2": "flushed between iterations"}
