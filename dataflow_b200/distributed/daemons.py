@@ -22,16 +22,19 @@ def profiler_command(prefix: str, argv: list[str]) -> list[str]:
     return ["env", "DATAFLOW_NVTX=1", f"DATAFLOW_TRACE_PREFIX={prefix}", *argv]
 
 
-def daemon_paths(member: Member, root: str = "/tmp") -> dict[str, str]:
-    stem = f"{root}/dataflowd.{member.host}.{member.device}"
+def daemon_paths(member: Member, root: str = "/tmp", tag: str | None = None) -> dict[str, str]:
+    """Runtime files of one daemon.  ``tag`` tells daemons apart that share a host and a device (CPU ranks of one box)."""
+    stem = f"{root}/dataflowd.{member.host}.{member.device}" + (f".{tag}" if tag else "")
     return {"socket": stem + ".sock", "pidfile": stem + ".pid", "logfile": stem + ".log"}
 
 
 def launch(host: HostSpec, member: Member, *, backing_gib: float | str | None = None, kernels: str | None = None,
            fake: bool = False, peer_name: str | None = None, peer_listen: str | None = None, root: str = "/tmp",
-           env: Mapping[str, str] | None = None, wait_s: float = 60.0) -> dict[str, str]:
-    """Start one daemon for ``member`` and wait until its socket answers."""
-    paths = daemon_paths(member, root)
+           env: Mapping[str, str] | None = None, wait_s: float = 60.0, tag: str | None = None,
+           device: str | None = None) -> dict[str, str]:
+    """Start one daemon for ``member`` and wait until its socket answers.  ``device``: what the daemon is told to run on when
+    that is not the member's CUDA ordinal (``"cpu"``: the host backend)."""
+    paths = daemon_paths(member, root, tag)
     repo = host.repo or REPO_ROOT
     py = sys.executable if host.local else host.python
     argv = [py, os.path.join(repo, "tools/train/daemonize.py"), "--pidfile", paths["pidfile"], "--logfile", paths["logfile"],
@@ -40,7 +43,7 @@ def launch(host: HostSpec, member: Member, *, backing_gib: float | str | None = 
         argv += ["env", f"{k}={v}"] if argv[-1] == "--" else [f"{k}={v}"]
     argv += [py, os.path.join(repo, "tools/train/dataflowd.py"), "start", "--foreground", "--socket", paths["socket"],
              "--backing-gib", str(backing_gib if backing_gib is not None else host.backing_gib)]
-    argv += ["--fake"] if fake else ["--device", str(member.device)]
+    argv += ["--fake"] if fake else ["--device", str(device if device is not None else member.device)]
     if kernels:
         argv += ["--kernels", kernels]
     if peer_name:
@@ -50,14 +53,14 @@ def launch(host: HostSpec, member: Member, *, backing_gib: float | str | None = 
     run_on(host, argv, timeout=wait_s)
     deadline = time.time() + wait_s
     while time.time() < deadline:
-        if alive(host, member, root):
+        if alive(host, member, root, tag):
             return paths
         time.sleep(0.2)
     raise TimeoutError(f"daemon for {member.key} did not come up within {wait_s:.0f} s (log: {paths['logfile']})")
 
 
-def alive(host: HostSpec, member: Member, root: str = "/tmp") -> bool:
-    paths = daemon_paths(member, root)
+def alive(host: HostSpec, member: Member, root: str = "/tmp", tag: str | None = None) -> bool:
+    paths = daemon_paths(member, root, tag)
     py = sys.executable if host.local else host.python
     repo = host.repo or REPO_ROOT
     r = run_on(host, [py, os.path.join(repo, "tools/train/dataflowd.py"), "status", "--socket", paths["socket"]],
@@ -65,18 +68,18 @@ def alive(host: HostSpec, member: Member, root: str = "/tmp") -> bool:
     return r.returncode == 0
 
 
-def wait_exit(host: HostSpec, member: Member, root: str = "/tmp", timeout: float = 60.0) -> bool:
+def wait_exit(host: HostSpec, member: Member, root: str = "/tmp", timeout: float = 60.0, tag: str | None = None) -> bool:
     deadline = time.time() + timeout
     while time.time() < deadline:
-        if not alive(host, member, root):
+        if not alive(host, member, root, tag):
             return True
         time.sleep(0.2)
     return False
 
 
-def kill(host: HostSpec, member: Member, root: str = "/tmp") -> None:
+def kill(host: HostSpec, member: Member, root: str = "/tmp", tag: str | None = None) -> None:
     """Stop by pidfile: signal, wait, escalate, verify the process group is gone (``daemonize.py --kill``)."""
-    paths = daemon_paths(member, root)
+    paths = daemon_paths(member, root, tag)
     py = sys.executable if host.local else host.python
     repo = host.repo or REPO_ROOT
     run_on(host, [py, os.path.join(repo, "tools/train/daemonize.py"), "--pidfile", paths["pidfile"], "--kill"], check=False,

@@ -41,8 +41,8 @@ class StepRun(threading.Thread):
             self.result = out
             total = 0.0
             for k in self.state.loss_ids:
-                raw = out["fetched"][k]
-                total += struct.unpack("<f", raw[:4])[0]
+                raw = out["fetched"][k]               # the daemon decodes 4-byte objects; raw bytes come from older daemons
+                total += float(raw) if isinstance(raw, (int, float)) else struct.unpack("<f", raw[:4])[0]
             self.loss = total
         except BaseException as e:       # noqa: BLE001
             self.error = e

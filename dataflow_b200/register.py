@@ -43,7 +43,18 @@ def build_model_family_resolver(spec: Mapping[str, Any], env):
     hyper.setdefault("optimizer", getattr(cfg, "optimizer", "adamw"))
     if hasattr(cfg, "policy"):
         hyper.setdefault("dtype_policy", cfg.policy().to_dict())
-    inner = fam.build_resolver(fam.derive_dims(cfg), hyper, K, device)
+    dims = fam.derive_dims(cfg)
+    inner = fam.build_resolver(dims, hyper, K, device)
+    dp = spec.get("dp")
+    if dp and dp.get("mode", "co") in ("co", "dp"):
+        # replicas over a peer group of the daemons (fleet mode): every optimizer task first sums its gradient object over
+        # the group named here; the handle comes from the daemon's peer plane (``ctx.groups[name]``)
+        from types import SimpleNamespace
+        from .parallel.zero import replicate_gradients
+        layouts = fam.family_layouts(dims, cfg.policy() if hasattr(cfg, "policy") else None, hyper["optimizer"])
+        replicate_gradients(SimpleNamespace(resolver=inner, layouts=layouts), dp.get("group", "dp"))
+    elif dp:
+        raise ValueError(f"fleet mode runs replicas (dp mode 'co'); {dp.get('mode')!r} needs the in-process launcher")
     init = FamilyInitExecutable(fam, cfg, int(spec.get("seed", 0)))
 
     def resolver(task):

@@ -57,6 +57,7 @@ class RunSpec:
     prof_dir: str | None = None             # per-step engine traces of the steps in the window land here
     profile_start_before_step: int = 0      # 1-indexed; 0 = no window
     profile_stop_after_step: int = 0
+    launcher: str = "process"               # process: one rank per process under torch.distributed.run; fleet: one dataflowd per rank (run/fleet.py)
     warm_profiles: bool = False             # measure and cache the task costs, then stop
     refresh_profiles: bool = False          # ignore cached task costs
     argv: list[str] = dataclasses.field(default_factory=list)
@@ -116,6 +117,11 @@ def _read_failure_kinds(out: str) -> list[tuple[str, str]]:
 
 
 def run(spec: RunSpec, log=print) -> RunResult:
+    if spec.launcher == "fleet":
+        from .fleet import run_fleet
+        return run_fleet(spec, log=log)
+    if spec.launcher != "process":
+        raise ValueError(f"--launcher is process or fleet, not {spec.launcher!r}")
     with RunLock(spec.checkpoint_dir if spec.checkpoint_every else None):
         if spec.world <= 1:
             from .rank_main import run_rank

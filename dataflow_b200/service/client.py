@@ -129,7 +129,8 @@ class EngineClient:
             if time.time() - t0 > timeout:
                 raise TimeoutError(transfer_id)
             time.sleep(0.01)
-    def create_peer_group(self, name: str, members, backend: str = "auto"): return self.call("create_peer_group", name=name, members=list(members), backend=backend)
+    def create_peer_group(self, name: str, members, backend: str = "auto", timeout: float = 30.0):
+        return self.call("create_peer_group", name=name, members=list(members), backend=backend, timeout=timeout)
     def destroy_peer_group(self, name: str): return self.call("destroy_peer_group", name=name)
     def list_peer_groups(self): return self.call("list_peer_groups")["groups"]
     def p2p_bench(self, peer: str, nbytes: int = 1 << 24): return self.call("p2p_bench", peer=peer, nbytes=nbytes)

@@ -39,9 +39,76 @@ class Link:
             self.bytes_out += 0 if payload is None else len(payload)
 
 
+class HostGroupHandle:
+    """What a task sees of a peer group on the ``hostmem`` lane (``ctx.groups[name]``): SUM collectives over the peer plane's
+    TCP links.  Tensors on a device are staged through host memory around the exchange, which synchronises the calling
+    stream — this is the plumbing lane for CPU ranks and for tests, the counterpart of the reference's hostmem lane
+    (``src/dataflow/service/peer/comm.py:139-603``), not a fast path.  Role: ``src/dataflow/runtime/groups.py:22-63``."""
+
+    def __init__(self, nm: "NetworkManager", name: str, timeout: float = 120.0):
+        self.nm, self.name, self.timeout = nm, name, timeout
+        g = nm.groups.get(name)
+        self.rank, self.world, self.lane = g.rank_of(nm.name), len(g.members), "collective"
+
+    def _exchange(self, t):
+        import torch
+        host = t.detach()
+        if host.is_cuda:
+            torch.cuda.current_stream(host.device).synchronize()
+            host = host.cpu()
+        wide = host.float() if host.dtype in (torch.bfloat16, torch.float16) else host
+        out = self.nm.all_reduce(self.name, np.ascontiguousarray(wide.contiguous().numpy()), self.timeout)
+        return torch.from_numpy(out).to(t.dtype)
+
+    def all_reduce(self, t):
+        if self.world > 1:
+            t.copy_(self._exchange(t).reshape(t.shape))
+        return t
+
+    allreduce = all_reduce
+
+    def reduce_scatter(self, full, out):
+        """``out`` receives this rank's ``1 / world`` slice of the sum of ``full`` (sum first, slice after: the lane is for
+        correctness, not for bandwidth)."""
+        total = self._exchange(full).reshape(-1)
+        n = out.numel()
+        out.copy_(total[self.rank * n:(self.rank + 1) * n].reshape(out.shape))
+        return out
+
+    def all_gather(self, own, full):
+        import torch
+        wide = torch.zeros(full.shape, dtype=full.dtype)
+        n = own.numel()
+        wide.reshape(-1)[self.rank * n:(self.rank + 1) * n] = own.detach().reshape(-1).cpu()
+        full.copy_(self._exchange(wide).reshape(full.shape))
+        return full
+
+    def broadcast(self, t, root: int = 0):
+        import torch
+        src = t if self.rank == root else torch.zeros_like(t)
+        t.copy_(self._exchange(src).reshape(t.shape))
+        return t
+
+    def reduce(self, t, root: int = 0):
+        total = self._exchange(t)
+        if self.rank == root:
+            t.copy_(total.reshape(t.shape))
+        return t
+
+    def check(self) -> None:
+        g = self.nm.groups.get(self.name)
+        if g.state == "ERROR":
+            raise ServiceError("GROUP_DESYNC", f"peer group {self.name!r}: {g.error}")
+
+    def close(self) -> None:
+        pass
+
+
 class NetworkManager:
-    def __init__(self, name: str, listen: str | None, store, state, chunk_bytes: int = P.CHUNK):
+    def __init__(self, name: str, listen: str | None, store, state, chunk_bytes: int = P.CHUNK, device: int | None = None):
         self.name, self.listen_addr, self.store, self.state = name, listen, store, state
+        self.device = device                 # CUDA ordinal of this daemon (None: CPU / virtual backend)
+        self.handles: dict[str, Any] = {}    # group name -> what tasks see as ctx.groups[name]
         self.links: dict[str, Link] = {}
         self.lock = threading.RLock()
         self.groups = GroupTable()
@@ -299,24 +366,66 @@ class NetworkManager:
         except KeyError:
             raise ServiceError("GROUP_EXISTS", f"peer group {name!r} already exists") from None
         self.coll[name] = CollectiveQueue(name)
+        extra = dict(extra or {})
+        if backend == "nccl":
+            from .ncclcomm import NcclComm
+            extra["nccl_uid"] = NcclComm.new_unique_id().hex()      # the unique id rides the join frame
         for m in members[1:]:
-            self.links[m].send({"kind": "GROUP_JOIN", "group": name, "members": members, "backend": backend, "extra": extra or {}})
+            self.links[m].send({"kind": "GROUP_JOIN", "group": name, "members": members, "backend": backend, "extra": extra})
         if len(members) == 1:
             self.groups.get(name).state = "READY"
+        # the attachment barrier: every member builds its side of the backend before it acknowledges, this one meanwhile
+        try:
+            self._attach_backend(name, members, backend, extra)
+        except Exception as e:      # noqa: BLE001
+            self.groups.mark_error(name, f"backend {backend!r} did not attach on {self.name}: {e}")
+            self._fan_out_group_error(name, self.groups.get(name).error)
+            raise ServiceError("GROUP_DESYNC", self.groups.get(name).error) from None
         try:
             g = self.groups.wait_ready(name, timeout)
         except RuntimeError as e:
             raise ServiceError("GROUP_DESYNC", str(e)) from None
         return {"group": name, "members": list(g.members), "backend": backend, "rank": 0}
 
+    def _attach_backend(self, name: str, members: list[str], backend: str, extra: dict) -> None:
+        """This daemon's side of a group's collective backend; the result is what tasks get as ``ctx.groups[name]``."""
+        rank = list(members).index(self.name)
+        if backend == "nccl":
+            from .ncclcomm import NcclComm
+            if self.device is None:
+                raise ServiceError("BAD_REQUEST", "the nccl lane needs a daemon on a CUDA device (CPU daemons use hostmem)")
+            comm = NcclComm(name, rank, len(members), bytes.fromhex(extra["nccl_uid"]), int(self.device))
+            comm.lane = "collective"
+            comm.warm_up()
+            self.handles[name] = comm
+        else:
+            self.handles[name] = HostGroupHandle(self, name)
+        self.groups.get(name).comm = self.handles[name]
+
+    def group_handles(self) -> dict:
+        """Ready groups by name, as tasks see them (``TaskSpec.comm_groups`` names a group; ``ctx.groups[name]``)."""
+        return {k: v for k, v in self.handles.items() if k in self.groups.groups and self.groups.get(k).state == "READY"}
+
     def _on_group_join(self, link: Link, frame: dict) -> None:
         name = frame["group"]
         self.groups.adopt(name, frame["members"], frame["backend"], link.peer)
         self.coll[name] = CollectiveQueue(name)
+        try:
+            self._attach_backend(name, list(frame["members"]), frame["backend"], dict(frame.get("extra") or {}))
+        except Exception as e:      # noqa: BLE001
+            self.groups.mark_error(name, f"backend {frame['backend']!r} did not attach on {self.name}: {e}")
+            link.send({"kind": "GROUP_ERROR", "group": name, "why": self.groups.get(name).error})
+            return
         link.send({"kind": "GROUP_ACK", "group": name})
         self.state.emit("peer_group_joined", group=name)
 
     def destroy_group(self, name: str) -> None:
+        h = self.handles.pop(name, None)
+        if h is not None and hasattr(h, "close"):
+            try:
+                h.close()
+            except Exception:       # noqa: BLE001
+                pass
         self.groups.drop(name)
         self.coll.pop(name, None)
 

@@ -175,7 +175,7 @@ class Server:
             from .peer.nm import NetworkManager
             from . import handlers_peers
             self.nm = NetworkManager(cfg.peer_name, cfg.peer_listen, self.store, self.state,
-                                     chunk_bytes=cfg.peer_chunk_bytes)
+                                     chunk_bytes=cfg.peer_chunk_bytes, device=None if cfg.fake else cfg.device)
             self.nm.start()
             handlers_peers.install(self)
 

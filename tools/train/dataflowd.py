@@ -42,7 +42,8 @@ def cmd_start(a) -> int:
                        peer_name=a.peer_name, peer_listen=a.peer_listen)
     srv = Server(cfg)
     if not a.no_default_workloads:
-        import dataflow_b200.register  # noqa: F401  registers the built-in families' resolvers
+        from dataflow_b200.register import register_all
+        register_all()                 # the built-in families' resolver kind ("model_family")
     for mod in a.plugin or ():
         __import__(mod)
     srv.serve_forever()

@@ -72,6 +72,9 @@ def add_run_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--checkpoint-keep-last", type=int, default=None)
     ap.add_argument("--checkpoint-redundancy", type=int, default=None,
                     help="how many ranks write their copy of replicated objects (default: all, which also checks them for drift)")
+    ap.add_argument("--launcher", default="process", choices=["process", "fleet"],
+                    help="process: one rank per process under torch.distributed.run (fused peer-memory lanes); fleet: one dataflowd "
+                         "daemon per rank driven by this process over unix sockets (replicas, --opt-shard co)")
     ap.add_argument("--max-restarts", type=int, default=0,
                     help="relaunch a failed multi-rank job from its newest complete checkpoint, up to this many times")
     ap.add_argument("--resume", default=None, help="step directory, checkpoint root, or 'latest'")
@@ -126,7 +129,7 @@ def spec_from_args(a, argv):
                    warm_profiles=a.warm_profiles, refresh_profiles=a.refresh_profiles,
                    resident_params=not a.no_resident_params, checkpoint_every=a.checkpoint_every,
                    checkpoint_dir=a.checkpoint_dir, checkpoint_keep_last=a.checkpoint_keep_last, checkpoint_redundancy=a.checkpoint_redundancy, resume=a.resume, max_restarts=a.max_restarts, out=a.out,
-                   argv=list(argv))
+                   launcher=a.launcher, argv=list(argv))
 
 
 def cmd_train(a, argv) -> int:
