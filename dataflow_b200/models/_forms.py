@@ -293,8 +293,9 @@ def causal_conv1d_silu(x, w, seg_start):
     return F.silu(out.float()).to(x.dtype)
 
 
-def gated_delta_rule(q, k, v, g, beta, seg_start):
-    """Sequential form: S <- exp(g_t) S (I - beta_t k_t k_t^T) + beta_t v_t k_t^T;  o_t = S q_t.
+def gated_delta_rule_sequential(q, k, v, g, beta, seg_start):
+    """Sequential form, one token at a time (the oracle of the chunked form below):
+    S <- exp(g_t) S (I - beta_t k_t k_t^T) + beta_t v_t k_t^T;  o_t = S q_t.
     q, k (n, h, dk) l2-normalised; v (n, h, dv); g (n, h) log-decay <= 0; beta (n, h) in (0, 1).  State resets at
     segment starts."""
     n, h, dk = q.shape
@@ -311,3 +312,80 @@ def gated_delta_rule(q, k, v, g, beta, seg_start):
         S = S + torch.einsum("hv,hk->hvk", bt * (vt - pred), kt)
         outs.append(torch.einsum("hvk,hk->hv", S, qf[t]))
     return torch.stack(outs, 0).to(q.dtype)
+
+
+def _delta_rule_chunks(q, k, v, g, beta, chunk: int):
+    """The chunk-parallel form over a batch of equal-length sequences.  q, k (b, L, h, dk), v (b, L, h, dv), g / beta (b, L, h),
+    fp32, L a multiple of ``chunk`` (padding rows carry beta = 0, g = 0: they change nothing).  Returns o (b, L, h, dv).
+
+    Inside a chunk with state S0 at its start, cumulative decay G_t = sum_{i <= t} g_i and pseudo-values u_t defined by
+    S_t = exp(g_t) S_{t-1} + u_t k_t^T, the recurrence unrolls to a triangular system (the WY form of the delta rule):
+        (I + diag(beta) L) U = diag(beta) (V - (exp(G) * K) S0^T),   L[t, s] = exp(G_t - G_s) (k_t . k_s) for s < t
+        O = (exp(G) * Q) S0^T + (A * mask_{s <= t}) U,                A[t, s] = exp(G_t - G_s) (q_t . k_s)
+        S_end = exp(G_end) S0 + U^T (exp(G_end - G) * K)
+    so a chunk costs a handful of matrix products and one triangular solve, and only S crosses chunk borders."""
+    b, L, h, dk = q.shape
+    dv = v.shape[-1]
+    C = chunk
+    nc = L // C
+    # (b, h, nc, C, d): heads become a batch axis of the matrix products
+    qc = q.permute(0, 2, 1, 3).reshape(b, h, nc, C, dk)
+    kc = k.permute(0, 2, 1, 3).reshape(b, h, nc, C, dk)
+    vc = v.permute(0, 2, 1, 3).reshape(b, h, nc, C, dv)
+    gc = g.permute(0, 2, 1).reshape(b, h, nc, C)
+    bc = beta.permute(0, 2, 1).reshape(b, h, nc, C)
+    G = gc.cumsum(-1)                                                    # (b, h, nc, C), <= 0 and non-increasing
+    diff = G[..., :, None] - G[..., None, :]                             # G_t - G_s
+    idx = torch.arange(C, device=q.device)
+    lower = idx[:, None] > idx[None, :]
+    lower_eq = idx[:, None] >= idx[None, :]
+    decay = torch.exp(diff.masked_fill(~lower_eq, 0.0)) * lower_eq       # exp(G_t - G_s) for s <= t, else 0 (never overflows)
+    kk = kc @ kc.transpose(-1, -2)
+    Lm = decay * kk * lower                                              # strictly lower
+    sysm = torch.eye(C, device=q.device, dtype=q.dtype) + bc[..., :, None] * Lm
+    eG = torch.exp(G)[..., None]
+    rhs = torch.cat([bc[..., None] * vc, bc[..., None] * (eG * kc)], dim=-1)       # solve for T V and T (exp(G) K) together
+    sol = torch.linalg.solve_triangular(sysm, rhs, upper=False)
+    U0, W = sol[..., :dv], sol[..., dv:]                                 # U = U0 - W S0^T
+    A = decay * (qc @ kc.transpose(-1, -2))                              # s <= t, diagonal included
+    eQ = eG * qc
+    k_end = torch.exp(G[..., -1:, None] - G[..., None]) * kc             # exp(G_end - G_s) k_s
+    g_end = torch.exp(G[..., -1])[..., None, None]
+    S = torch.zeros(b, h, dv, dk, dtype=q.dtype, device=q.device)
+    outs = []
+    for c in range(nc):                                                  # only the state crosses chunk borders
+        U = U0[:, :, c] - W[:, :, c] @ S.transpose(-1, -2)               # (b, h, C, dv)
+        outs.append(eQ[:, :, c] @ S.transpose(-1, -2) + A[:, :, c] @ U)
+        S = g_end[:, :, c] * S + U.transpose(-1, -2) @ k_end[:, :, c]
+    o = torch.stack(outs, 2).reshape(b, h, L, dv)
+    return o.permute(0, 2, 1, 3)
+
+
+def gated_delta_rule(q, k, v, g, beta, seg_start, chunk: int = 64):
+    """Gated delta rule in chunk-parallel form (differentiable; fp32 inside):
+    S <- exp(g_t) S (I - beta_t k_t k_t^T) + beta_t v_t k_t^T;  o_t = S q_t, the state reset at segment starts.
+    q, k (n, h, dk) l2-normalised; v (n, h, dv); g (n, h) log-decay <= 0; beta (n, h) in (0, 1); seg_start (n,) the index of
+    the first token of each token's segment.  Segments of equal length run as one batch; a ragged round runs one batch per
+    length.  Same mathematics as :func:`gated_delta_rule_sequential`, which stays as its oracle; the reference calls the
+    chunked kernels of the ``fla`` package here (``src/dataflow_training/model_families/qwen35/blocks.py:137-160,249-357``)."""
+    n, h, dk = q.shape
+    starts = torch.unique_consecutive(seg_start).tolist()               # host-known on this lane (it runs under autograd)
+    bounds = starts + [n]
+    lens = [bounds[i + 1] - bounds[i] for i in range(len(starts))]
+    qf, kf, vf = q.float() * dk ** -0.5, k.float(), v.float()
+    gf, bf = g.float(), beta.float()
+    out = torch.empty(n, h, v.shape[-1], dtype=torch.float32, device=q.device)
+    pieces = []
+    for length in sorted(set(lens)):
+        segs = [i for i, x in enumerate(lens) if x == length]
+        pad = (-length) % chunk
+        rows = torch.cat([torch.arange(bounds[i], bounds[i] + length, device=q.device) for i in segs])
+
+        def take(t, fill=0.0):
+            x = t[rows].reshape(len(segs), length, *t.shape[1:])
+            return F.pad(x, (0, 0) * (x.dim() - 2) + (0, pad), value=fill) if pad else x
+        o = _delta_rule_chunks(take(qf), take(kf), take(vf), take(gf), take(bf), chunk)
+        pieces.append((rows, o[:, :length].reshape(len(segs) * length, h, -1)))
+    for rows, o in pieces:
+        out = out.index_copy(0, rows, o)
+    return out.to(q.dtype)
