@@ -151,12 +151,14 @@ def load_balance_aux(logits, ids, coef: float):
 
 def mla_qkv(x, w, cfg, positions):
     """Multi-head latent attention projections: two low-rank stacks, decoupled RoPE with one shared rope key.
-    Returns q (n, h, nope + rope), k (n, h, nope + rope), v (n, h, dv) and the compressed latents."""
+    Returns q (n, h, nope + rope), k (n, h, nope + rope), v (n, h, dv) and the normalised q latent (``x`` itself when the
+    query has no low-rank stack), which is what the sparse-attention indexer reads."""
     n, h = x.shape[0], cfg.n_heads
     if cfg.q_lora:
         cq = rmsnorm(x @ w["wq_a"], w["q_norm"], cfg.rms_eps)
         q = (cq @ w["wq_b"]).view(n, h, cfg.d_nope + cfg.d_rope)
     else:
+        cq = x
         q = (x @ w["wq"]).view(n, h, cfg.d_nope + cfg.d_rope)
     kv_a = x @ w["wkv_a"]                                           # (n, kv_lora + rope)
     ckv = rmsnorm(kv_a[:, :cfg.kv_lora], w["kv_norm"], cfg.rms_eps)
@@ -164,16 +166,26 @@ def mla_qkv(x, w, cfg, positions):
     kv = (ckv @ w["wkv_b"]).view(n, h, cfg.d_nope + cfg.d_v)
     q = torch.cat([q[..., :cfg.d_nope], rope(q[..., cfg.d_nope:], positions, cfg.rope_theta)], -1)
     k = torch.cat([kv[..., :cfg.d_nope], k_rope.expand(n, h, cfg.d_rope)], -1)
-    return q, k, kv[..., cfg.d_nope:], ckv
+    return q, k, kv[..., cfg.d_nope:], cq
 
 
-def dsa_index_scores(x, w, cfg, positions):
-    """Lightning indexer: I[i, j] = sum_h wgt[i, h] * relu(<q_idx[i, h], k_idx[j]>), a few small heads, one shared key."""
+def _rope_first(t, positions, cfg):
+    """Rotate the first ``d_rope`` dims of the last axis, leave the rest (the indexer's rope-first layout)."""
+    r = min(cfg.d_rope, t.shape[-1])
+    return torch.cat([rope(t[..., :r], positions, cfg.rope_theta), t[..., r:]], -1) if r else t
+
+
+def dsa_index_scores(x, cq, w, cfg, positions, ln_eps: float = 1e-5):
+    """Lightning indexer: I[i, j] = sum_h wgt[i, h] * relu(<q_idx[i, h], k_idx[j]>), a few small heads, one shared key.
+    Queries come from the normalised q latent ``cq``, the key from ``x`` through a LayerNorm (gain and bias), both rotated
+    on their first ``d_rope`` dims only; the head weights wgt = (x w_w) * heads^-1/2 * dim^-1/2; everything in fp32.
+    Form parity: reference ``src/dataflow_training/blocks/modules/dsa_forms.py:47-110``."""
     n = x.shape[0]
-    qi = rope((x @ w["wi_q"]).view(n, cfg.index_heads, cfg.index_dim), positions, cfg.rope_theta)
-    ki = rope((x @ w["wi_k"]).view(n, 1, cfg.index_dim), positions, cfg.rope_theta)[:, 0]
-    wgt = (x @ w["wi_w"]).float() * cfg.index_heads ** -0.5
-    s = torch.relu(torch.einsum("ihd,jd->ihj", qi.float(), ki.float())) * cfg.index_dim ** -0.5
+    qi = _rope_first((cq @ w["wi_q"]).view(n, cfg.index_heads, cfg.index_dim), positions, cfg).float()
+    ki = F.layer_norm((x @ w["wi_k"]).float(), (cfg.index_dim,), w["wi_k_gain"].float(), w["wi_k_bias"].float(), ln_eps)
+    ki = _rope_first(ki.view(n, 1, cfg.index_dim), positions, cfg)[:, 0].float()
+    wgt = (x.float() @ w["wi_w"].float()) * cfg.index_heads ** -0.5 * cfg.index_dim ** -0.5
+    s = torch.relu(torch.einsum("ihd,jd->ihj", qi, ki))
     return (s * wgt[:, :, None]).sum(1)
 
 
@@ -192,10 +204,11 @@ def dsa_attention_target(probs):
     return target / (target.sum(-1, keepdim=True) + 1e-20)
 
 
-def dsa_indexer_kl_to(scores, target, causal):
-    """KL(target || softmax of the index scores over the causal prefix), mean over queries; ``target`` is a constant."""
-    logq = torch.log_softmax(scores.masked_fill(~causal, float("-inf")), dim=-1)
-    term = torch.where(target > 0, target * (torch.log(target.clamp_min(1e-20)) - logq), torch.zeros_like(target))
+def dsa_indexer_kl_to(scores, target, live):
+    """KL(target || softmax of the index scores over the live set), mean over queries; ``target`` is a constant and ``live``
+    the keys a query attends to (its selection; the whole causal prefix during the dense warm-up)."""
+    logq = torch.log_softmax(scores.masked_fill(~live, float("-inf")), dim=-1)
+    term = torch.where(target > 0, target * (torch.log(target.clamp_min(1e-20)) - logq.masked_fill(~live, 0.0)), torch.zeros_like(target))
     return term.sum(-1).mean()
 
 

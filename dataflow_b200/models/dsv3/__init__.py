@@ -84,7 +84,10 @@ def attention_fields(c: Dsv3Config):
     f += [Field("wkv_a", (d, c.kv_lora + c.d_rope)), Field("kv_norm", (c.kv_lora,), "bf16", "vector", "ones"),
           Field("wkv_b", (c.kv_lora, h * (c.d_nope + c.d_v))), Field("wo", (h * c.d_v, d), "bf16", "matrix", "residual")]
     if c.index_topk:
-        f += [Field("wi_q", (d, c.index_heads * c.index_dim)), Field("wi_k", (d, c.index_dim)), Field("wi_w", (d, c.index_heads))]
+        # the indexer reads the normalised q latent (the residual stream when the query has no low-rank stack)
+        f += [Field("wi_q", (c.q_lora or d, c.index_heads * c.index_dim)), Field("wi_k", (d, c.index_dim)),
+              Field("wi_k_gain", (c.index_dim,), "bf16", "vector", "ones"), Field("wi_k_bias", (c.index_dim,), "bf16", "vector", "zeros"),
+              Field("wi_w", (d, c.index_heads))]
     return f
 
 
@@ -108,11 +111,11 @@ def attention_part(c: Dsv3Config, x, w, seg):
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
-    q, k, v, _ = F.mla_qkv(h, w, c, pos)
+    q, k, v, cq = F.mla_qkv(h, w, c, pos)
     causal = F.segment_causal_mask(seg, n, x.device)
     aux, mask = None, causal
     if c.index_topk:
-        scores = F.dsa_index_scores(h.detach(), {k_: w[k_] for k_ in ("wi_q", "wi_k", "wi_w")}, c, pos)
+        scores = F.dsa_index_scores(h.detach(), cq.detach(), {k_: w[k_] for k_ in INDEXER_FIELDS}, c, pos)
         if not c.dsa_warmup:
             mask = F.dsa_topk_mask(scores.detach(), causal, c.index_topk)
     o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
@@ -122,6 +125,7 @@ def attention_part(c: Dsv3Config, x, w, seg):
 
 
 EP_FIELDS = ("w13_experts", "w2_experts")
+INDEXER_FIELDS = ("wi_q", "wi_k", "wi_k_gain", "wi_k_bias", "wi_w")
 
 
 def routed_experts(h2, w, wts, ids, ep=None):
@@ -150,7 +154,7 @@ def kind_flops(c: Dsv3Config, kind: str, tokens: int):
     attn_p = (d * c.q_lora + c.q_lora * h * (c.d_nope + c.d_rope) if c.q_lora else d * h * (c.d_nope + c.d_rope)) + \
         d * (c.kv_lora + c.d_rope) + c.kv_lora * h * (c.d_nope + c.d_v) + h * c.d_v * d
     if c.index_topk:
-        attn_p += d * (c.index_heads * c.index_dim + c.index_dim + c.index_heads)
+        attn_p += (c.q_lora or d) * c.index_heads * c.index_dim + d * (c.index_dim + c.index_heads)
     mlp_p = 3 * d * c.d_ff if kind.endswith("dense") else d * c.n_experts + 3 * d * c.d_ff_expert * (c.top_k + c.n_shared)
     keys = min(c.index_topk, c.seq_len) if c.index_topk else c.seq_len / 2
     attn = 2.0 * tokens * keys * h * (c.d_nope + c.d_rope + c.d_v)

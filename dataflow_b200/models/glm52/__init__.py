@@ -18,18 +18,43 @@ import torch
 
 from ...blocks.layouts import Field
 from .. import _forms as F
-from ..dsv3 import EP_FIELDS, Dsv3Config, kind_fields as _dsv3_fields, kind_flops as _dsv3_flops, routed_experts
+from ..dsv3 import EP_FIELDS, INDEXER_FIELDS, Dsv3Config, kind_fields as _dsv3_fields, kind_flops as _dsv3_flops, routed_experts
 from .._torch_family import TorchFamilySpec, register_torch_family
 
 
 @dataclasses.dataclass(frozen=True)
 class Glm52Config(Dsv3Config):
     index_share: int = 2
+    # One role per layer, "full" (runs the indexer) or "shared" (attends over the nearest earlier full layer's selection);
+    # empty = regular groups of ``index_share`` layers.  Published checkpoints carry a searched, irregular pattern.
+    indexer_types: tuple = ()
+
+    def __post_init__(self):
+        parent = getattr(super(), "__post_init__", None)
+        if parent is not None:
+            parent()
+        t = tuple(self.indexer_types)
+        if t:
+            if len(t) != self.n_layers or t[0] != "full" or any(r not in ("full", "shared") for r in t):
+                raise ValueError("indexer_types needs one of full|shared per layer, and layer 0 must be full")
+            object.__setattr__(self, "indexer_types", t)
+
+
+def roles(c: Glm52Config):
+    """Per layer ``"full"`` or ``"shared"``."""
+    if c.indexer_types:
+        return tuple(c.indexer_types)
+    return tuple("full" if i % c.index_share == 0 else "shared" for i in range(c.n_layers))
 
 
 def leader_of(c: Glm52Config, layer: int):
-    lead = layer - layer % c.index_share
-    return None if lead == layer else lead
+    r = roles(c)
+    if r[layer] == "full":
+        return None
+    lead = layer
+    while r[lead] != "full":
+        lead -= 1
+    return lead
 
 
 def layer_kinds(c: Glm52Config):
@@ -53,11 +78,11 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
-    q, k, v, _ = F.mla_qkv(h, w, c, pos)
+    q, k, v, cq = F.mla_qkv(h, w, c, pos)
     causal = F.segment_causal_mask(seg, n, x.device)
     aux, emit = None, None
     if shared is None:                                              # leader: rank the keys, publish the selection
-        scores = F.dsa_index_scores(h.detach(), {k_: w[k_] for k_ in ("wi_q", "wi_k", "wi_w")}, c, pos)
+        scores = F.dsa_index_scores(h.detach(), cq.detach(), {k_: w[k_] for k_ in INDEXER_FIELDS}, c, pos)
         kk = min(c.index_topk, c.seq_len, n)
         sel = scores.detach().masked_fill(~causal, float("-inf")).topk(kk, dim=-1).indices
         emit = {"sel": torch.nn.functional.pad(sel, (0, min(c.index_topk, c.seq_len) - kk)).to(torch.int32)}
@@ -90,9 +115,17 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
 def kind_flops(c: Glm52Config, kind: str, tokens: int):
     mm, at = _dsv3_flops(c, "x_dense" if kind.startswith("gd") else "x_moe", tokens)
     if kind.endswith("f"):                                          # followers run no indexer
-        mm -= 2.0 * tokens * c.d_model * (c.index_heads * c.index_dim + c.index_dim + c.index_heads)
+        mm -= 2.0 * tokens * ((c.q_lora or c.d_model) * c.index_heads * c.index_dim + c.d_model * (c.index_dim + c.index_heads))
         at -= 2.0 * tokens * c.seq_len / 2 * c.index_heads * c.index_dim
     return mm, at
+
+
+def pattern(*runs):
+    """("full", 3), ("shared", 3), (("full", "shared", "shared", "shared"), 18) -> the flat tuple of roles."""
+    out = []
+    for what, times in runs:
+        out += (list(what) if isinstance(what, tuple) else [what]) * times
+    return tuple(out)
 
 
 BASE = dict(index_heads=2, index_dim=16, index_topk=32, index_kl_coef=0.1, index_share=2, family="glm52")
@@ -101,10 +134,13 @@ PRESETS = {
     "glm52_mini": dict(name="glm52_mini", n_layers=8, n_dense=2, d_model=512, n_heads=8, q_lora=192, kv_lora=128, d_nope=64, d_rope=32, d_v=64,
                        d_ff=1408, n_experts=16, top_k=4, d_ff_expert=256, n_group=4, topk_group=2, vocab_size=32000, seq_len=1024, batch=4,
                        grad_accum_rounds=4, **{**BASE, "index_heads": 4, "index_dim": 32, "index_topk": 256, "index_share": 4}),
-    "glm52": dict(name="glm52", n_layers=78, n_dense=3, d_model=6144, n_heads=64, q_lora=2048, kv_lora=512, d_nope=128, d_rope=64, d_v=128,
-                  d_ff=12288, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5, vocab_size=154880,
+    # the published model: wide heads (192 + 64 query/key dims, 256 value dims), one routing group, and a searched sharing
+    # pattern — three full layers, three shared, then eighteen groups of one full and three shared
+    "glm52": dict(name="glm52", n_layers=78, n_dense=3, d_model=6144, n_heads=64, q_lora=2048, kv_lora=512, d_nope=192, d_rope=64, d_v=256,
+                  d_ff=12288, n_experts=256, top_k=8, d_ff_expert=2048, n_group=1, topk_group=1, routed_scaling=2.5, vocab_size=154880,
                   seq_len=4096, batch=1, grad_accum_rounds=16, dtype_policy="bf16_split_master",
-                  **{**BASE, "index_heads": 32, "index_dim": 128, "index_topk": 2048, "index_share": 3}),
+                  indexer_types=pattern(("full", 3), ("shared", 3), (("full", "shared", "shared", "shared"), 18)),
+                  **{**BASE, "index_heads": 32, "index_dim": 128, "index_topk": 2048, "index_share": 4}),
 }
 
 SPEC = TorchFamilySpec("glm52", Glm52Config, {k: (lambda kw=v: Glm52Config(**kw)) for k, v in PRESETS.items()}, layer_kinds, kind_fields,

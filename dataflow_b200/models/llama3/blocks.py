@@ -33,6 +33,12 @@ def _qkv_views(d, qkv, n):
     return q, k, v
 
 
+def _norm_rows(d, t):
+    """(tokens, heads, head_dim) -> the contiguous 2-D matrix whose rows the q / k RMSNorm normalises."""
+    t = t.contiguous()
+    return t.view(t.shape[0], -1) if d.qk_norm == "full" else t.view(-1, d.hd)
+
+
 def stage_qkv_rope(K, d, st):
     qkv = st["a"]["qkv"]
     _lin(K, st)(st["h"], st["w"]["w_qkv"], out=qkv)
@@ -40,12 +46,14 @@ def stage_qkv_rope(K, d, st):
     if d.qk_norm:
         a = st["a"]
         a["qk_pre"].copy_(qkv[:, :d.q_dim + d.kv_dim])
-        qn, qr = K.rmsnorm_fwd(q.contiguous(), st["w"]["q_norm"], d.eps)
-        kn, kr = K.rmsnorm_fwd(k.contiguous(), st["w"]["k_norm"], d.eps)
-        q.copy_(qn)
-        k.copy_(kn)
-        a["q_rstd"].copy_(qr.view(-1, d.hq))
-        a["k_rstd"].copy_(kr.view(-1, d.hkv))
+        # rows of the norm: one head ("per head") or the whole projected row ("full")
+        qrows, krows = _norm_rows(d, q), _norm_rows(d, k)
+        qn, qr = K.rmsnorm_fwd(qrows, st["w"]["q_norm"], d.eps)
+        kn, kr = K.rmsnorm_fwd(krows, st["w"]["k_norm"], d.eps)
+        q.copy_(qn.view_as(q))
+        k.copy_(kn.view_as(k))
+        a["q_rstd"].copy_(qr.view(a["q_rstd"].shape))
+        a["k_rstd"].copy_(kr.view(a["k_rstd"].shape))
     pos = st["seg"].positions
     K.rope_fwd(q, pos, d.theta)
     K.rope_fwd(k, pos, d.theta)
@@ -329,10 +337,10 @@ class BlockBwd(_Block):
         K.rope_bwd(dk, seg.positions, d.theta)
         if d.qk_norm:
             pre = a["qk_pre"]
-            qp = pre[:, :d.q_dim].unflatten(1, (d.hq, d.hd)).contiguous()
-            kp = pre[:, d.q_dim:].unflatten(1, (d.hkv, d.hd)).contiguous()
-            dq.copy_(K.rmsnorm_bwd(dq.contiguous(), qp, w["q_norm"], a["q_rstd"].reshape(-1), dw=g.get("q_norm"), accumulate=acc))
-            dk.copy_(K.rmsnorm_bwd(dk.contiguous(), kp, w["k_norm"], a["k_rstd"].reshape(-1), dw=g.get("k_norm"), accumulate=acc))
+            qp = _norm_rows(d, pre[:, :d.q_dim].unflatten(1, (d.hq, d.hd)))
+            kp = _norm_rows(d, pre[:, d.q_dim:].unflatten(1, (d.hkv, d.hd)))
+            dq.copy_(K.rmsnorm_bwd(_norm_rows(d, dq), qp, w["q_norm"], a["q_rstd"].reshape(-1), dw=g.get("q_norm"), accumulate=acc).view_as(dq))
+            dk.copy_(K.rmsnorm_bwd(_norm_rows(d, dk), kp, w["k_norm"], a["k_rstd"].reshape(-1), dw=g.get("k_norm"), accumulate=acc).view_as(dk))
         h = K.rmsnorm_apply(x, w["attn_norm"], a["rstd_attn"])
         wgrad("w_qkv", h, dqkv)
         dh = K.linear_dgrad_bf16(dqkv, w["w_qkv"])

@@ -37,7 +37,7 @@ class ShapedLlama3Config:
     optimizer: str = "adamw"
     optimizer_placement: str = "interleaved"
     head_chunk_tokens: int = 2048
-    qk_norm: bool = False                # qwen3 variant: per-head RMSNorm on q and k
+    qk_norm: bool | str = False          # True: RMSNorm per head on q and k (qwen3); "full": over the whole q / k row (olmoe)
     family: str = "llama3"
     # mixture-of-experts MLP (olmoe / qwen3moe variants): n_experts > 0 replaces the dense SwiGLU MLP
     n_experts: int = 0
@@ -82,7 +82,7 @@ class Llama3Dims:
     T: int                               # max tokens per round
     seq_len: int
     head_chunk: int
-    qk_norm: bool = False
+    qk_norm: bool | str = False
     E: int = 0                           # experts (0: dense MLP)
     topk: int = 0
     Fe: int = 0                          # expert FFN width
@@ -149,7 +149,8 @@ def block_fields(d: Llama3Dims) -> tuple[Field, ...]:
     f = [Field("attn_norm", (d.d,), "bf16", "vector", "ones"),
          Field("w_qkv", (d.d, d.qkv_dim), "bf16", "matrix", "normal")]
     if d.qk_norm:
-        f += [Field("q_norm", (d.hd,), "bf16", "vector", "ones"), Field("k_norm", (d.hd,), "bf16", "vector", "ones")]
+        qn, kn = (d.q_dim, d.kv_dim) if d.qk_norm == "full" else (d.hd, d.hd)
+        f += [Field("q_norm", (qn,), "bf16", "vector", "ones"), Field("k_norm", (kn,), "bf16", "vector", "ones")]
     f += [Field("wo", (d.q_dim, d.d), "bf16", "matrix", "normal"),
           Field("ffn_norm", (d.d,), "bf16", "vector", "ones")]
     if d.moe:
@@ -187,7 +188,8 @@ def _context_layout_full(d: Llama3Dims) -> PackedLayout:
     # MLP intermediates see every row of this rank's heads / columns
     f = [Field("rstd_attn", (d.Ts,), "fp32"), Field("qkv", (d.T, d.qkv_dim), "bf16")]
     if d.qk_norm:
-        f += [Field("q_rstd", (d.T, d.hq), "fp32"), Field("k_rstd", (d.T, d.hkv), "fp32"),
+        per_row = (1, 1) if d.qk_norm == "full" else (d.hq, d.hkv)
+        f += [Field("q_rstd", (d.T, per_row[0]), "fp32"), Field("k_rstd", (d.T, per_row[1]), "fp32"),
               Field("qk_pre", (d.T, d.q_dim + d.kv_dim), "bf16")]
     f += [Field("lse", (d.hq, d.T), "fp32"), Field("attn_out", (d.T, d.q_dim), "bf16"),
           Field("h_mid", (d.Ts, d.d), "bf16"), Field("rstd_ffn", (d.Ts,), "fp32")]

@@ -1,4 +1,5 @@
-"""olmoe family: llama-style attention with per-head q/k RMSNorm and a mixture-of-experts MLP (softmax over all
+"""olmoe family: llama-style attention with an RMSNorm over the whole projected q row and k row
+(all heads at once, ``qk_norm="full"``) and a mixture-of-experts MLP (softmax over all
 experts, then top-k, un-normalised), load-balance auxiliary gradient.  ``olmoe_1b_7b`` is the 16-layer, 64-expert,
 top-8 model.  Family parity: reference ``src/dataflow_training/model_families/olmoe/``."""
 from .._llama_like import register_llama_like
@@ -12,4 +13,4 @@ PRESETS = {
                         vocab_size=50304, rope_theta=10000.0, seq_len=4096, batch=4, grad_accum_rounds=4, n_experts=64,
                         top_k=8, d_ff_expert=1024, aux_coef=0.01, dtype_policy="bf16_split_master"),
 }
-FAMILY = register_llama_like("olmoe", PRESETS, qk_norm=True, routing_mode="softmax_then_topk")
+FAMILY = register_llama_like("olmoe", PRESETS, qk_norm="full", routing_mode="softmax_then_topk")

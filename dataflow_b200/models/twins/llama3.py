@@ -45,7 +45,7 @@ class Llama3Twin(nn.Module):
             else:
                 l.w13, l.w2 = P(d.d, 2 * d.F), P(d.F, d.d)
             if d.qk_norm:
-                l.q_norm, l.k_norm = P(d.hd), P(d.hd)
+                l.q_norm, l.k_norm = (P(d.q_dim), P(d.kv_dim)) if d.qk_norm == "full" else (P(d.hd), P(d.hd))
             self.layers.append(l)
         self.final_norm, self.w_head = P(d.d), P(d.d, d.vocab)
 
@@ -61,7 +61,9 @@ class Llama3Twin(nn.Module):
             q = qkv[:, :d.q_dim].unflatten(1, (d.hq, d.hd))
             k = qkv[:, d.q_dim:d.q_dim + d.kv_dim].unflatten(1, (d.hkv, d.hd))
             v = qkv[:, d.q_dim + d.kv_dim:].unflatten(1, (d.hkv, d.hd))
-            if d.qk_norm:
+            if d.qk_norm == "full":
+                q, k = _rms(q.flatten(1), l.q_norm, d.eps).view_as(q), _rms(k.flatten(1), l.k_norm, d.eps).view_as(k)
+            elif d.qk_norm:
                 q, k = _rms(q, l.q_norm, d.eps), _rms(k, l.k_norm, d.eps)
             q, k = _rope(q, pos, d.theta), _rope(k, pos, d.theta)
             outs = []

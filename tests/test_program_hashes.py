@@ -2,8 +2,9 @@
 
 Refactors of the lowering, the layouts or the planner must not change WHAT a family lowers to: same tasks, same compute
 keys, same block parameters, same byte sizes, same order.  This gate pins the sha256 of the canonical JSON of every
-family's ``tiny`` preset — bare (what the family's lowering says) and planned at a fixed budget (the planner is
-deterministic) — against a committed fixture.  Regenerate ONLY when a content change is intended:
+family's ``tiny`` preset — bare (what the family's lowering says), planned with room to spare, and planned under pressure
+(70 % of the roomy plan's peak, where the planner has to offload, prefetch or recompute; the planner is deterministic) —
+against a committed fixture.  Regenerate ONLY when a content change is intended:
 
     DATAFLOW_REGEN_HASHES=1 python -m pytest tests/test_program_hashes.py
 
@@ -28,6 +29,7 @@ def program_hash(program) -> str:
 
 def current_hashes() -> dict:
     from dataflow_b200.lowering import resolve_hardware
+    from dataflow_b200.lowering.planning import PlanningError
     from dataflow_b200.models.families import all_families
     from dataflow_b200.run.driver import plan_at_budget
     hw = resolve_hardware("b200")            # a fixed hardware row: the hashes must not depend on the machine
@@ -37,8 +39,12 @@ def current_hashes() -> dict:
             continue
         cfg = fam.presets["tiny"]()
         bare = fam.lower(cfg, hw=hw)
-        planned = plan_at_budget(fam, cfg, PLAN_BUDGET, hw).program
-        out[name] = {"bare": program_hash(bare), "planned": program_hash(planned), "tasks": len(bare.tasks)}
+        roomy = plan_at_budget(fam, cfg, PLAN_BUDGET, hw, leeway_bytes=0)
+        try:
+            tight = program_hash(plan_at_budget(fam, cfg, roomy.max_workspace + int(0.7 * roomy.peak_fast_bytes), hw, leeway_bytes=0).program)
+        except PlanningError:
+            tight = "infeasible"
+        out[name] = {"bare": program_hash(bare), "planned": program_hash(roomy.program), "tight": tight, "tasks": len(bare.tasks)}
     return out
 
 

@@ -76,7 +76,7 @@ def test_dsv32_dense_warmup_trains_the_indexer_and_nothing_else():
     tr.close()
     changed = {k for k in before if not torch.equal(before[k], after[k])}
     assert changed and all(".wi_" in k for k in changed)
-    assert {k.rsplit(".", 1)[-1] for k in changed} == {"wi_q", "wi_k", "wi_w"}
+    assert {k.rsplit(".", 1)[-1] for k in changed} == {"wi_q", "wi_k", "wi_k_gain", "wi_k_bias", "wi_w"}
     assert abs(losses[1] - losses[0]) < 1e-6        # dense attention does not see the indexer: a frozen main model repeats its loss
     # dense attention: the sparse preset and the warm-up preset differ in their forward
     sparse = run_pair("dsv32", steps=1)["engine"][0]
