@@ -10,8 +10,11 @@ What the reference can run of the configuration: its ``llama3_8b`` preset at seq
 lane), one GPU per daemon.  It has no B200 hardware preset and raises on an unknown device;
 the harness adds a ``b200`` row to its ``HW_PRESETS`` table at run time (the route its own
 error message names) and touches none of its files.
-Multi-GPU (its ZeRO-1 ``zero1rs`` lane through the conductor / fleet loop) is not driven
-from here; for N > 1 the arm reports ``unavailable``.
+Multi-GPU: rank 0 of the launch acts as the reference's conductor — its ``run/conductor.run`` starts one ``dataflowd`` per GPU
+(the reference's own ``tools/train/{daemonize,dataflowd}.py``, copied beside the installed packages together with its
+``pyproject.toml`` because the conductor looks them up under the repository root), links them, creates the NCCL peer group and
+runs its lock-step fleet loop with data parallelism over its ``zero1rs`` optimizer sharding, the same rounds per GPU as at
+N = 1 (weak scaling).  The other ranks of the launch have nothing to do and exit.
 """
 from __future__ import annotations
 
@@ -34,8 +37,7 @@ def run_reference_arm(a) -> dict:
     if not os.path.isdir(os.path.join(ref, "dataflow_training")):
         return _unavailable("baseline/_ref is not installed on this machine") if rank == 0 else {}
     if world > 1 or a.gpus > 1:
-        return _unavailable("the reference's multi-GPU lane (conductor + one daemon per GPU, ZeRO-1 over NCCL) is not "
-                            "driven by this harness; single-GPU only") if rank == 0 else {}
+        return _run_fleet(a, max(world, a.gpus), here, ref) if rank == 0 else {}
     sys.path.insert(0, ref)
     try:
         import torch
@@ -128,3 +130,141 @@ def run_reference_arm(a) -> dict:
             with open(dump, "w") as f:
                 f.write("\n".join(tb) + "\n\n" + "\n".join(logs if "logs" in dir() else []))
         return _unavailable(f"reference run failed: {type(e).__name__}: {e} | {tb[-3] if len(tb) > 2 else ''}")
+
+
+def _host_backing_gib(n: int) -> float:
+    """Pinned host store per daemon: the reference's 150 GiB default where the box has it, else an equal share of 60 % of the
+    memory that is free now (the planner is told the capacity and plans within it)."""
+    avail = None
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    avail = int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    for p in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+        try:
+            v = open(p).read().strip()
+            if v.isdigit() and int(v) < (1 << 60):
+                avail = min(avail, int(v)) if avail else int(v)
+        except OSError:
+            pass
+    if not avail:
+        return 64.0
+    return max(min(150.0, 0.6 * avail / n / 2 ** 30), 8.0)
+
+
+def _ensure_git(ref: str) -> None:
+    """The reference's conductor refuses to start a fleet unless ``git rev-parse HEAD`` answers at its repository root (its
+    mixed-version guard).  The installed tree is no checkout, so it gets an empty history of its own; no file changes."""
+    import subprocess
+    if os.path.isdir(os.path.join(ref, ".git")):
+        return
+    env = dict(os.environ, GIT_AUTHOR_NAME="bench", GIT_AUTHOR_EMAIL="bench@localhost", GIT_COMMITTER_NAME="bench",
+               GIT_COMMITTER_EMAIL="bench@localhost")
+    for cmd in (["git", "init", "-q"], ["git", "add", "-A"], ["git", "commit", "-q", "-m", "installed reference"]):
+        subprocess.run(cmd, cwd=ref, env=env, check=True, capture_output=True)
+
+
+def _run_fleet(a, world: int, here: str, ref: str) -> dict:
+    import socket
+    import tempfile
+    for need in ("tools/train/dataflowd.py", "tools/train/daemonize.py", "pyproject.toml"):
+        if not os.path.exists(os.path.join(ref, need)):
+            return _unavailable(f"baseline/_ref/{need} is missing: copy the reference's tools/ and pyproject.toml beside the "
+                                f"installed packages")
+    sys.path.insert(0, ref)
+    os.environ["PYTHONPATH"] = ref + os.pathsep + os.environ.get("PYTHONPATH", "")
+    os.environ.pop("OMP_NUM_THREADS", None)       # the launcher's one-thread default would also bind the daemons it never sees
+    logs: list[str] = []
+    cwd = os.getcwd()
+    try:
+        import torch
+        from dataflow_training.data.pipeline import pipeline_from_args
+        from dataflow_training.distributed.parallelism import ParallelismScheme
+        from dataflow_training.distributed.topology import GroupSpec, HostSpec, Topology
+        from dataflow_training.lowering import shaped_program as ref_sp
+        from dataflow_training.run import presets as P
+        from dataflow_training.run.conductor import run as conductor_run
+        from dataflow_training.run.recipe import Recipe
+    except Exception as e:       # noqa: BLE001
+        return _unavailable(f"reference import failed: {type(e).__name__}: {e}")
+    try:
+        if torch.cuda.device_count() < world:
+            return _unavailable(f"{world} GPUs asked, {torch.cuda.device_count()} visible")
+        sys.path.insert(0, here)
+        from ref_launch import B200_ROW
+        _ensure_git(ref)
+        ref_sp.HW_PRESETS.setdefault("b200", dict(B200_ROW))          # the conductor prices tasks in this process
+        base = P.resolve_preset(a.preset)
+        per_rank = max(a.tokens_per_gpu // (a.seq_len * a.batch), 1)
+        cfg = replace(base, seq_len=a.seq_len, batch=a.batch, grad_accum_rounds=per_rank * world)
+        budget = a.budget_gib if a.budget_gib is not None else 60.0
+        steps = a.warmup + a.steps
+        recipe = Recipe(peak_lr=3e-4, min_lr=3e-5, warmup_steps=max(1, steps // 3), total_steps=steps)
+        tokens_step = cfg.max_tokens * cfg.grad_accum_rounds
+        feed = pipeline_from_args(cfg, f"synthetic:mean_len={8 * a.seq_len},seed=0,long_policy=trim")
+        backing = _host_backing_gib(world)
+        interpreter = f"{sys.executable} {os.path.join(here, 'ref_launch.py')}"
+
+        def free_port():
+            with socket.socket() as s:
+                s.bind(("127.0.0.1", 0))
+                return s.getsockname()[1]
+
+        names = [f"gpu{i}" for i in range(world)]
+        hosts = {n: HostSpec(name=n, peer_listen=f"127.0.0.1:{free_port()}", ssh=None, python=interpreter, repo=ref,
+                             backing_gib=backing, budget_gib=budget, device=i) for i, n in enumerate(names)}
+        topo = Topology(conductor=names[0], hosts=hosts,
+                        groups={"dp": GroupSpec(name="dp", members=tuple(names), backend="nccl")}, source="<bench: one box>")
+        scheme = ParallelismScheme.data_parallel((per_rank,) * world, responsibility="zero1rs")
+        stamps: list[float] = []
+
+        def on_log(*x, **k):
+            line = " ".join(map(str, x))
+            logs.append(line)
+            if "[fleet] step " in line and "tok/s" in line:
+                stamps.append(time.perf_counter())
+
+        work = tempfile.mkdtemp(prefix="dfb_ref_fleet_")
+        os.chdir(work)                 # the reference writes its profile cache and run files relative to the cwd
+        t0 = time.perf_counter()
+        res = conductor_run(cfg, recipe, feed, steps, scheme=scheme, budgets=(budget,) * world, backing=(backing,) * world,
+                            topology=topo, group="dp", seed=11, log=on_log, log_every=1, warm_profiles=True,
+                            prof_dir=os.path.join(work, "prof"))
+        total_s = time.perf_counter() - t0
+        tail = res.step_wall_s[a.warmup:] or res.step_wall_s
+        s_per_step = sum(tail) / len(tail)
+        value = tokens_step / s_per_step
+        e2e = None
+        if len(stamps) == steps and steps - a.warmup >= 1 and a.warmup >= 1:
+            span = stamps[-1] - stamps[a.warmup - 1]
+            e2e = {"value": tokens_step * (steps - a.warmup) / span, "unit": "tokens/s", "h2d_bytes_per_step": 2 * 4 * tokens_step,
+                   "d2h_bytes_per_step": 4 * cfg.grad_accum_rounds,
+                   "how": "wall clock between the conductor's per-step log lines: put_object of every rank's ids into its daemon's "
+                          "pinned store + the lock-step runs + loss fetches"}
+        return {
+            "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": len(tail),
+            "warmup": a.warmup, "ms_per_step": s_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / 12618.0, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+            "config": {"model": a.preset, "global_batch": tokens_step // a.seq_len, "seq_len": a.seq_len, "tokens_per_step": tokens_step,
+                       "parallelism": f"dp{world} zero1rs over NCCL, one dataflowd per GPU", "fast_budget_gib": budget,
+                       "host_backing_gib_per_rank": backing,
+                       "dtype_policy": "all-bf16 (the reference has no fp32-master lane)", "optimizer": "adamw",
+                       "hw_preset": "b200 row added to the reference's HW_PRESETS table at run time (conductor and daemons)",
+                       "timing": "the conductor's own per-step wall clock (upload + lock-step runs + loss fetch)"},
+            "plan": {"costs": "measured (its --warm-profiles stage)", "total_s": total_s},
+            "e2e": e2e, "loss": res.losses[-1] if res.losses else None, "gpu_launches": None, "torch": torch.__version__,
+        }
+    except Exception as e:       # noqa: BLE001
+        import traceback
+        tb = traceback.format_exc().strip().splitlines()
+        dump = os.environ.get("DFB_REF_TRACEBACK")
+        if dump:
+            os.chdir(cwd)
+            with open(dump, "w") as f:
+                f.write("\n".join(tb) + "\n\n" + "\n".join(logs))
+        return _unavailable(f"reference fleet run failed: {type(e).__name__}: {e} | {tb[-3] if len(tb) > 2 else ''}")
+    finally:
+        os.chdir(cwd)

@@ -197,6 +197,111 @@ def dsa_topk_mask(scores, causal, k: int):
     return torch.zeros_like(causal).scatter_(1, idx, True) & causal
 
 
+def mla_latents(x, w, cfg, positions):
+    """The inputs of the latent ("absorbed") form of multi-head latent attention: q (n, h, nope + rope) rotated, the
+    normalised kv latent (n, kv_lora), the rotated shared rope key (n, rope) and the normalised q latent."""
+    n, h = x.shape[0], cfg.n_heads
+    if cfg.q_lora:
+        cq = rmsnorm(x @ w["wq_a"], w["q_norm"], cfg.rms_eps)
+        q = (cq @ w["wq_b"]).view(n, h, cfg.d_nope + cfg.d_rope)
+    else:
+        cq = x
+        q = (x @ w["wq"]).view(n, h, cfg.d_nope + cfg.d_rope)
+    kv_a = x @ w["wkv_a"]
+    ckv = rmsnorm(kv_a[:, :cfg.kv_lora], w["kv_norm"], cfg.rms_eps)
+    k_rope = rope(kv_a[:, None, cfg.kv_lora:], positions, cfg.rope_theta)[:, 0]
+    q = torch.cat([q[..., :cfg.d_nope], rope(q[..., cfg.d_nope:], positions, cfg.rope_theta)], -1)
+    return q, ckv, k_rope, cq
+
+
+def _indexer_inputs(x, cq, w, cfg, positions):
+    n = x.shape[0]
+    qi = _rope_first((cq @ w["wi_q"]).view(n, cfg.index_heads, cfg.index_dim), positions, cfg).float()
+    ki = F.layer_norm((x @ w["wi_k"]).float(), (cfg.index_dim,), w["wi_k_gain"].float(), w["wi_k_bias"].float(), 1e-5)
+    ki = _rope_first(ki.view(n, 1, cfg.index_dim), positions, cfg)[:, 0].float()
+    wgt = (x.float() @ w["wi_w"].float()) * cfg.index_heads ** -0.5 * cfg.index_dim ** -0.5
+    return qi, ki, wgt
+
+
+def dsa_select(x, cq, w, cfg, positions, k: int, chunk: int = 256):
+    """Top-``k`` visible keys of every query WITHOUT the (n, n) score matrix: index scores are formed for ``chunk`` queries at
+    a time against the keys up to the chunk's end, and only the selection leaves.  Returns ``sel`` (n, kk) int64 key rows and
+    ``live`` (n, kk) bool — false where a query sees fewer than kk keys (those slots name arbitrary rows).  No gradient.
+    Role parity: reference ``src/dataflow_training/kernels/dsa.py`` (index scores + top-k)."""
+    n = x.shape[0]
+    with torch.no_grad():
+        qi, ki, wgt = _indexer_inputs(x, cq, w, cfg, positions)
+        idx = torch.arange(n, device=x.device)
+        start = idx - positions[:n].long()
+        kk = min(k, n)
+        sel = torch.empty(n, kk, dtype=torch.long, device=x.device)
+        live = torch.empty(n, kk, dtype=torch.bool, device=x.device)
+        for a in range(0, n, chunk):
+            b = min(a + chunk, n)
+            lo = int(start[a])                                   # the earliest sequence start any query of the chunk sees
+            s = torch.relu(torch.einsum("ihd,jd->ihj", qi[a:b], ki[lo:b]))
+            s = (s * wgt[a:b, :, None]).sum(1)                   # (chunk, keys lo..b)
+            cols = idx[lo:b]
+            vis = (cols[None, :] <= idx[a:b, None]) & (cols[None, :] >= start[a:b, None])
+            s = s.masked_fill(~vis, float("-inf"))
+            if s.shape[1] < kk:
+                s = torch.nn.functional.pad(s, (0, kk - s.shape[1]), value=float("-inf"))
+            top = s.topk(kk, dim=-1)
+            live[a:b] = top.values > float("-inf")
+            sel[a:b] = (top.indices + lo).clamp(max=n - 1)
+    return sel, live
+
+
+def dsa_scores_at(x, cq, w, cfg, positions, sel):
+    """Index scores at the selected keys only, (n, kk), differentiable with respect to the indexer's fields."""
+    qi, ki, wgt = _indexer_inputs(x, cq, w, cfg, positions)
+    s = torch.relu(torch.einsum("ihd,ikd->ihk", qi, ki[sel]))
+    return (s * wgt[:, :, None]).sum(1)
+
+
+def mla_sparse_attention(q, ckv, k_rope, wkv_b, sel, live, cfg, chunk: int = 256, want_target: bool = False):
+    """Attention of every query over ITS selected keys in the latent form: with k_j = [W_kb^T c_j | r_j] and
+    v_j = W_vb^T c_j, the logits are (W_kb q_nope) . c_j + q_rope . r_j and the output is W_vb^T (sum_j p_j c_j) — one
+    gathered (kk, kv_lora + rope) block per query serves every head, and nothing of size (n, n) exists.  Queries are
+    processed ``chunk`` at a time (each chunk re-run in the backward).  Returns (n, h, dv) and, when asked, the
+    head-summed probabilities at the selection (n, kk), detached.
+    Role parity: reference ``src/dataflow_training/kernels/dsa.py`` (sparse attention forward / backward)."""
+    from torch.utils.checkpoint import checkpoint
+    n, h = q.shape[0], cfg.n_heads
+    wb = wkv_b.view(cfg.kv_lora, h, cfg.d_nope + cfg.d_v)
+    w_kb, w_vb = wb[..., :cfg.d_nope], wb[..., cfg.d_nope:]
+    scale = (cfg.d_nope + cfg.d_rope) ** -0.5
+
+    def part(qc, selc, livec, ckv_, kr_, w_kb_, w_vb_):
+        q_abs = torch.einsum("ihd,chd->ihc", qc[..., :cfg.d_nope].float(), w_kb_.float())          # (c, h, kv_lora)
+        kc, kr = ckv_[selc].float(), kr_[selc].float()                                               # (c, kk, kv_lora / rope)
+        s = (torch.einsum("ihc,ikc->ihk", q_abs, kc) + torch.einsum("ihr,ikr->ihk", qc[..., cfg.d_nope:].float(), kr)) * scale
+        p = torch.softmax(s.masked_fill(~livec[:, None, :], float("-inf")), dim=-1)
+        o = torch.einsum("ihc,chd->ihd", torch.einsum("ihk,ikc->ihc", p, kc), w_vb_.float())
+        return o.to(qc.dtype), p.detach().sum(1)
+
+    outs, targets = [], []
+    for a in range(0, n, chunk):
+        b = min(a + chunk, n)
+        args = (q[a:b], sel[a:b], live[a:b], ckv, k_rope, w_kb, w_vb)
+        o, t = checkpoint(part, *args, use_reentrant=False) if torch.is_grad_enabled() and n > chunk else part(*args)
+        outs.append(o)
+        targets.append(t)
+    out = torch.cat(outs)
+    if not want_target:
+        return out, None
+    t = torch.cat(targets)
+    return out, t / (t.sum(-1, keepdim=True) + 1e-20)
+
+
+def dsa_indexer_kl_at(scores_sel, target_sel, live):
+    """``dsa_indexer_kl_to`` on (n, kk) tensors that hold the selected keys only."""
+    logq = torch.log_softmax(scores_sel.masked_fill(~live, float("-inf")), dim=-1)
+    term = torch.where(target_sel > 0, target_sel * (torch.log(target_sel.clamp_min(1e-20)) - logq.masked_fill(~live, 0.0)),
+                       torch.zeros_like(target_sel))
+    return term.sum(-1).mean()
+
+
 def dsa_attention_target(probs):
     """The indexer's training target of one layer: attention probabilities summed over heads, L1-normalised per query,
     detached.  probs (heads, n, n) -> (n, n)."""

@@ -50,6 +50,9 @@ class Dsv3Config:
     index_dim: int = 0
     index_topk: int = 0
     index_kl_coef: float = 0.0
+    # "mask": the selection as an (n, n) mask over dense attention (short rounds); "gather": every query attends over its
+    # gathered keys in the latent form and nothing of size (n, n) exists (long context); "auto" picks by the round's length
+    sparse_impl: str = "auto"
     # dense warm-up of the indexer (dsv32): attention stays DENSE, the indexer learns the full-prefix attention
     # distribution through its KL term, and nothing but the indexer's fields is updated
     dsa_warmup: bool = False
@@ -106,11 +109,29 @@ def kind_fields(c: Dsv3Config, kind: str):
     return tuple(f)
 
 
+def sparse_attention_gathered(c: Dsv3Config, h, w, pos):
+    """Sparse attention without anything of size (n, n): chunked index scores -> top-k rows, attention over the gathered keys
+    in the latent form, and the indexer's KL objective evaluated at the selection.  Returns (o (n, heads, dv), aux)."""
+    n = h.shape[0]
+    q, ckv, k_rope, cq = F.mla_latents(h, w, c, pos)
+    iw = {k_: w[k_] for k_ in INDEXER_FIELDS}
+    sel, live = F.dsa_select(h.detach(), cq.detach(), iw, c, pos, c.index_topk)
+    o, target = F.mla_sparse_attention(q, ckv, k_rope, w["wkv_b"], sel, live, c, want_target=bool(c.index_kl_coef))
+    aux = None
+    if c.index_kl_coef:
+        scores = F.dsa_scores_at(h.detach(), cq.detach(), iw, c, pos, sel)
+        aux = c.index_kl_coef * F.dsa_indexer_kl_at(scores, target, live) * n
+    return o, aux
+
+
 def attention_part(c: Dsv3Config, x, w, seg):
     """Pre-norm MLA (dense, or sparse through the indexer) + residual.  Returns (h_mid, aux)."""
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
+    if c.index_topk and not c.dsa_warmup and (c.sparse_impl == "gather" or (c.sparse_impl == "auto" and n > 2048)):
+        o, aux = sparse_attention_gathered(c, h, w, pos)
+        return x + F.linear(o.reshape(n, -1), w["wo"], c.linear_precision), aux
     q, k, v, cq = F.mla_qkv(h, w, c, pos)
     causal = F.segment_causal_mask(seg, n, x.device)
     aux, mask = None, causal

@@ -78,28 +78,49 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
     n = x.shape[0]
     pos = seg.positions[:n]
     h = F.rmsnorm(x, w["attn_norm"], c.rms_eps)
-    q, k, v, cq = F.mla_qkv(h, w, c, pos)
-    causal = F.segment_causal_mask(seg, n, x.device)
     aux, emit = None, None
-    if shared is None:                                              # leader: rank the keys, publish the selection
-        scores = F.dsa_index_scores(h.detach(), cq.detach(), {k_: w[k_] for k_ in INDEXER_FIELDS}, c, pos)
-        kk = min(c.index_topk, c.seq_len, n)
-        sel = scores.detach().masked_fill(~causal, float("-inf")).topk(kk, dim=-1).indices
-        emit = {"sel": torch.nn.functional.pad(sel, (0, min(c.index_topk, c.seq_len) - kk)).to(torch.int32)}
-    else:
-        sel = shared["sel"].long()[:, :min(c.index_topk, c.seq_len, n)]
-    mask = torch.zeros_like(causal).scatter_(1, sel.clamp(max=n - 1), True) & causal
-    o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
-    if c.index_kl_coef:
-        target = F.dsa_attention_target(probs)
-        cols = sel.clamp(max=n - 1)
-        if shared is not None:                                      # follower: its share of the leader's target
-            width = min(c.index_topk, c.seq_len)
-            emit = {"_deposit": {"kl_target": torch.nn.functional.pad(target.gather(1, cols), (0, width - cols.shape[1]))}}
+    width = min(c.index_topk, c.seq_len)
+    if c.sparse_impl == "gather" or (c.sparse_impl == "auto" and n > 2048):
+        # long context: nothing of size (n, n); dead slots of the published selection hold -1
+        q, ckv, k_rope, cq = F.mla_latents(h, w, c, pos)
+        pad = torch.nn.functional.pad
+        if shared is None:
+            iw = {k_: w[k_] for k_ in INDEXER_FIELDS}
+            sel, live = F.dsa_select(h.detach(), cq.detach(), iw, c, pos, width)
+            emit = {"sel": pad(torch.where(live, sel, torch.full_like(sel, -1)), (0, width - sel.shape[1]), value=-1).to(torch.int32)}
         else:
-            if accum is not None:
-                target = (target + torch.zeros_like(target).scatter_add_(1, cols, accum["kl_target"][:, :cols.shape[1]].to(target.dtype))) / group_size
-            aux = c.index_kl_coef * F.dsa_indexer_kl_to(scores, target, mask) * n
+            got = shared["sel"].long()[:, :min(width, n)]
+            sel, live = got.clamp(min=0), got >= 0
+        o, target = F.mla_sparse_attention(q, ckv, k_rope, w["wkv_b"], sel, live, c, want_target=bool(c.index_kl_coef))
+        if c.index_kl_coef:
+            if shared is not None:
+                emit = {"_deposit": {"kl_target": pad(target, (0, width - target.shape[1]))}}
+            else:
+                if accum is not None:
+                    target = (target + accum["kl_target"][:, :target.shape[1]].to(target.dtype)) / group_size
+                aux = c.index_kl_coef * F.dsa_indexer_kl_at(F.dsa_scores_at(h.detach(), cq.detach(), iw, c, pos, sel), target, live) * n
+    else:
+        q, k, v, cq = F.mla_qkv(h, w, c, pos)
+        causal = F.segment_causal_mask(seg, n, x.device)
+        if shared is None:                                              # leader: rank the keys, publish the selection
+            scores = F.dsa_index_scores(h.detach(), cq.detach(), {k_: w[k_] for k_ in INDEXER_FIELDS}, c, pos)
+            kk = min(c.index_topk, c.seq_len, n)
+            sel = scores.detach().masked_fill(~causal, float("-inf")).topk(kk, dim=-1).indices
+            emit = {"sel": torch.nn.functional.pad(sel, (0, min(c.index_topk, c.seq_len) - kk)).to(torch.int32)}
+        else:
+            sel = shared["sel"].long()[:, :min(c.index_topk, c.seq_len, n)]
+        mask = torch.zeros_like(causal).scatter_(1, sel.clamp(max=n - 1), True) & causal
+        o, probs = F.attention(q, k, v, mask, (c.d_nope + c.d_rope) ** -0.5)
+        if c.index_kl_coef:
+            target = F.dsa_attention_target(probs)
+            cols = sel.clamp(max=n - 1)
+            if shared is not None:                                      # follower: its share of the leader's target
+                width = min(c.index_topk, c.seq_len)
+                emit = {"_deposit": {"kl_target": torch.nn.functional.pad(target.gather(1, cols), (0, width - cols.shape[1]))}}
+            else:
+                if accum is not None:
+                    target = (target + torch.zeros_like(target).scatter_add_(1, cols, accum["kl_target"][:, :cols.shape[1]].to(target.dtype))) / group_size
+                aux = c.index_kl_coef * F.dsa_indexer_kl_to(scores, target, mask) * n
     h_mid = x + F.linear(o.reshape(n, -1), w["wo"], c.linear_precision)
     h2 = F.rmsnorm(h_mid, w["ffn_norm"], c.rms_eps)
     if kind.startswith("gd"):

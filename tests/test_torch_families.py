@@ -204,3 +204,57 @@ def test_chunked_gated_delta_rule_matches_the_sequential_form(bounds):
     w = torch.randn_like(o_seq)
     for a, b in zip(torch.autograd.grad((o_seq * w).sum(), [q, k, v, g, beta]), torch.autograd.grad((o_chk * w).sum(), [q, k, v, g, beta])):
         assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+
+
+def test_dsa_gathered_forms_equal_the_masked_forms():
+    """Long-context sparse attention (chunked index scores -> top-k rows, latent-form attention over the gathered keys, KL at the
+    selection) gives the loss and every gradient of the (n, n)-mask forms; uniform and ragged rounds, chunks smaller than a
+    sequence."""
+    import dataclasses
+    from dataflow_b200.models import _forms as F
+    from dataflow_b200.data.segments import make_segments
+    g = torch.Generator().manual_seed(5)
+    B, L = 2, 40
+    for family, bounds in (("dsv32", [0, 40, 80]), ("dsv32", [0, 13, 51, 80]), ("glm52", [0, 13, 51, 80])):
+        fam = resolve_family(family)          # glm52: followers read the leader's published rows, targets flow back to it
+        base = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32", index_topk=12, index_kl_coef=1.0)
+        tokens = torch.randint(0, base.vocab_size, (B * L,), generator=g)
+        targets = torch.randint(0, base.vocab_size, (B * L,), generator=g)
+        got = {}
+        for impl in ("mask", "gather"):
+            m = fam.twin(dataclasses.replace(base, sparse_impl=impl))
+            gg = torch.Generator().manual_seed(3)
+            with torch.no_grad():
+                for p in m.parameters():
+                    p.copy_(torch.randn(p.shape, generator=gg) * (p.shape[-2] ** -0.5 if p.dim() > 1 else 0.1) + (1.0 if p.dim() == 1 else 0.0))
+            loss = m.loss(tokens, targets, bounds, total_rows=B * L)
+            loss.backward()
+            got[impl] = (loss.item(), {k: p.grad for k, p in m.named_parameters()})
+        assert got["mask"][0] == pytest.approx(got["gather"][0], rel=1e-6)
+        for k, ga in got["mask"][1].items():
+            gb = got["gather"][1][k]
+            assert (ga is None) == (gb is None), k
+            if ga is not None:
+                assert float((ga - gb).norm() / (ga.norm() + 1e-12)) < 1e-4, k
+    # the chunked pieces against their dense counterparts, chunks of 16 queries
+    c = base
+    n = 80
+    seg = make_segments([0, 13, 51, 80], None)
+    pos = seg.positions[:n]
+    x, cq = torch.randn(n, c.d_model, generator=g), torch.randn(n, c.q_lora or c.d_model, generator=g)
+    w = {k: torch.randn(s, generator=g) * 0.2 for k, s in (("wi_q", (cq.shape[1], c.index_heads * c.index_dim)), ("wi_k", (c.d_model, c.index_dim)),
+                                                         ("wi_k_gain", (c.index_dim,)), ("wi_k_bias", (c.index_dim,)), ("wi_w", (c.d_model, c.index_heads)))}
+    causal = F.segment_causal_mask(seg, n, x.device)
+    dense = F.dsa_index_scores(x, cq, w, c, pos)
+    sel, live = F.dsa_select(x, cq, w, c, pos, 12, chunk=16)
+    want = F.dsa_topk_mask(dense, causal, 12)
+    have = torch.zeros_like(causal)
+    have[torch.arange(n)[:, None].expand_as(sel)[live], sel[live]] = True
+    # ReLU leaves exact zeros, and which of several tied keys a top-k keeps is the library's business: the two selections must
+    # agree as multisets of scores, row by row
+    assert torch.equal(have.sum(1), want.sum(1))
+    a = dense.masked_fill(~have, float("-inf")).sort(dim=1, descending=True).values[:, :12]
+    b = dense.masked_fill(~want, float("-inf")).sort(dim=1, descending=True).values[:, :12]
+    assert torch.allclose(a, b, atol=1e-6)
+    at = F.dsa_scores_at(x, cq, w, c, pos, sel)
+    assert torch.allclose(at[live], dense.gather(1, sel)[live], atol=1e-5)
