@@ -234,6 +234,16 @@ def dsa_select(x, cq, w, cfg, positions, k: int, chunk: int = 256):
         idx = torch.arange(n, device=x.device)
         start = idx - positions[:n].long()
         kk = min(k, n)
+        K = _native(x)
+        if K is not None and cfg.index_dim in (64, 128) and "dsa_index_scores" in K.native_ops():
+            # device kernels: scores of 1024 queries at a time on the tensor cores, then a deterministic row selection
+            qb, kb, st = qi.to(torch.bfloat16).contiguous(), ki.to(torch.bfloat16).contiguous(), start.to(torch.int32)
+            rows = []
+            for a in range(0, n, 1024):
+                b = min(a + 1024, n)
+                rows.append(K.dsa_topk_rows(K.dsa_index_scores(qb, kb, wgt, st, a, b, 0), kk, 0))
+            got = torch.cat(rows).long()
+            return got.clamp(min=0), got >= 0
         sel = torch.empty(n, kk, dtype=torch.long, device=x.device)
         live = torch.empty(n, kk, dtype=torch.bool, device=x.device)
         for a in range(0, n, chunk):

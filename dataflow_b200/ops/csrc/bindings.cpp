@@ -499,6 +499,36 @@ static void gemm_fp8(const Tensor& a, const Tensor& b, Tensor& d, c10::optional<
   TORCH_CHECK(rc == 0, "gemm_fp8 failed with code ", rc);
 }
 
+// ---------------------------------------------------------------- sparse-attention indexer
+// q (n, H, D) bf16, k (n, D) bf16, wgt (n, H) fp32, seg_start (n,) int32; out (q1 - q0, ld) fp32
+static void dsa_index_scores(const Tensor& q, const Tensor& k, const Tensor& wgt, const Tensor& seg_start, Tensor& out, int64_t q0,
+                             int64_t q1, int64_t key_lo) {
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 2 && out.dim() == 2, "dsa_index_scores: q (n, H, D), k (n, D), out (rows, ld)");
+  const int64_t n = q.size(0), H = q.size(1), D = q.size(2);
+  need(q, "q", at::kBFloat16, n * H * D);
+  need(k, "k", at::kBFloat16, n * D);
+  need(wgt, "wgt", at::kFloat, n * H);
+  need(seg_start, "seg_start", at::kInt, n);
+  need(out, "out", at::kFloat);
+  TORCH_CHECK(D == 64 || D == 128, "dsa_index_scores: index head dim 64 or 128 (got ", D, ")");
+  TORCH_CHECK(0 <= key_lo && key_lo <= q0 && q0 < q1 && q1 <= n, "dsa_index_scores: 0 <= key_lo <= q0 < q1 <= n");
+  TORCH_CHECK(out.size(0) >= q1 - q0 && out.size(1) >= q1 - key_lo, "dsa_index_scores: out too small");
+  int rc = dfb::dsa_index_scores(q.data_ptr(), H * D, k.data_ptr(), D, wgt.data_ptr<float>(), seg_start.data_ptr<int>(), out.data_ptr<float>(),
+                                 out.size(1), (int)n, (int)H, (int)D, (int)q0, (int)q1, (int)key_lo, nullptr, cur_stream());
+  TORCH_CHECK(rc == 0, "dsa_index_scores failed with code ", rc);
+}
+// scores (rows, ld) fp32, the first ``cols`` entries of every row are ranked; sel (rows, >= k) int32
+static void dsa_topk_rows(const Tensor& scores, int64_t rows, int64_t cols, int64_t col_base, int64_t k, Tensor& sel) {
+  need(scores, "scores", at::kFloat);
+  need(sel, "sel", at::kInt);
+  TORCH_CHECK(scores.dim() == 2 && sel.dim() == 2, "dsa_topk_rows: 2-D tensors");
+  TORCH_CHECK(rows <= scores.size(0) && cols <= scores.size(1) && rows <= sel.size(0) && k <= sel.size(1) && k > 0 && cols > 0,
+              "dsa_topk_rows: sizes");
+  int rc = dfb::dsa_topk_rows(scores.data_ptr<float>(), scores.size(1), (int)rows, (int)cols, (int)col_base, (int)k, sel.data_ptr<int>(),
+                              (int)sel.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "dsa_topk_rows failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- sequence-mixing helpers
 static void l2norm_fwd(const Tensor& x, Tensor& y, Tensor& rstd, double eps) {
   CHECK_CUDA(x); CHECK_BF16(x); CHECK_BF16(y); CHECK_F32(rstd);
@@ -660,6 +690,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("trace") = py::none());
   m.def("quant_fp8_rowwise", &quant_fp8_rowwise);
   m.def("gemm_fp8", &gemm_fp8);
+  m.def("dsa_index_scores", &dsa_index_scores);
+  m.def("dsa_topk_rows", &dsa_topk_rows);
   m.def("l2norm_fwd", &l2norm_fwd);
   m.def("l2norm_bwd", &l2norm_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);

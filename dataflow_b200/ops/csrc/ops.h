@@ -106,6 +106,11 @@ int flash_bwd_sm100(const void* q, long long ldq, const void* k, long long ldk, 
                     const void* dout, long long lddo, const float* lse, void* dq, long long lddq, void* dk, long long lddk, void* dv,
                     long long lddv, void* ld2, const int* cu_seqlens, int nseg, int max_seqlen, int T, int hq, int hkv, int head_dim,
                     float scale, cudaStream_t stream, long long* trace = nullptr);
+// sparse-attention indexer (dsa.cu): index scores of query rows [q0, q1) against keys [key_lo, q1) on tcgen05, -inf where a
+// query does not see a key; and the k largest entries of every row as ascending key indices (-1 = fewer than k finite entries)
+int dsa_index_scores(const void* q, long long ldq, const void* k, long long ldk, const float* wgt, const int* seg_start, float* out,
+                     long long ld, int n, int H, int D, int q0, int q1, int key_lo, int* err, cudaStream_t s);
+int dsa_topk_rows(const float* scores, long long ld, int rows, int cols, int col_base, int k, int* sel, int sel_ld, cudaStream_t s);
 // fp8 lane: row-wise e4m3 quantisation and the dequantising CTA-pair GEMM
 int quant_fp8_rowwise(const void* x, long long ldx, void* q, long long ldq, float* scale, long long rows, int K, cudaStream_t s);
 int gemm_fp8_2sm(const void* A, long long lda, int a_fmt, const void* B, long long ldb, int b_fmt, void* D, long long ldd, int d_is_f32,

@@ -341,6 +341,27 @@ def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
     return dw
 
 
+# ------------------------------------------------------------------ sparse-attention indexer (dsa.cu)
+@reg("dsa_index_scores")
+def dsa_index_scores(q, k, wgt, seg_start, q0: int, q1: int, key_lo: int):
+    D = q.shape[-1]
+    if q.dtype != torch.bfloat16 or D not in (64, 128):
+        from . import eager
+        return eager.dsa_index_scores(q, k, wgt, seg_start, q0, q1, key_lo)
+    out = torch.empty(q1 - q0, q1 - key_lo, dtype=torch.float32, device=q.device)
+    native().dsa_index_scores(q.contiguous(), k.contiguous(), wgt.float().contiguous(), seg_start.to(torch.int32).contiguous(), out,
+                              int(q0), int(q1), int(key_lo))
+    return out
+
+
+@reg("dsa_topk_rows")
+def dsa_topk_rows(scores, k: int, col_base: int = 0):
+    rows, cols = scores.shape
+    sel = torch.empty(rows, k, dtype=torch.int32, device=scores.device)
+    native().dsa_topk_rows(scores.float().contiguous(), rows, cols, int(col_base), int(k), sel)
+    return sel
+
+
 # ------------------------------------------------------------------ sequence-mixing helpers (seqmix.cu)
 @reg("l2norm_fwd")
 def l2norm_fwd(x, eps: float = 1e-6):

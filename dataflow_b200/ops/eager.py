@@ -641,6 +641,37 @@ def moe_grouped_wgrad(xp, dyp, offsets_pad, dw, accumulate: bool = False):
     return dw
 
 
+# ------------------------------------------------------------------ sparse-attention indexer
+@register("dsa_index_scores", "eager")
+def dsa_index_scores(q, k, wgt, seg_start, q0: int, q1: int, key_lo: int):
+    """I[i, j] = sum_h wgt[i, h] * relu(<q[i, h], k[j]>) for query rows [q0, q1) against keys [key_lo, q1); -inf where query i
+    does not see key j (another sequence, or j > i).  q (n, H, D), k (n, D), wgt (n, H) fp32, seg_start (n,) int: the first
+    row of every row's sequence.  Returns (q1 - q0, q1 - key_lo) fp32."""
+    s = torch.relu(torch.einsum("ihd,jd->ihj", q[q0:q1].float(), k[key_lo:q1].float()))
+    s = (s * wgt[q0:q1].float()[:, :, None]).sum(1)
+    rows = torch.arange(q0, q1, device=q.device)[:, None]
+    cols = torch.arange(key_lo, q1, device=q.device)[None, :]
+    return s.masked_fill(~((cols <= rows) & (cols >= seg_start[q0:q1].long()[:, None])), float("-inf"))
+
+
+@register("dsa_topk_rows", "eager")
+def dsa_topk_rows(scores, k: int, col_base: int = 0):
+    """The k largest entries of every row as ASCENDING key indices (+ col_base); ties go to the smaller index; -1 where a row
+    has fewer than k finite entries.  Returns (rows, k) int32."""
+    rows, cols = scores.shape
+    kk = min(k, cols)
+    # a stable sort by descending value keeps equal values in index order
+    order = torch.sort(scores, dim=1, descending=True, stable=True).indices[:, :kk]
+    vals = scores.gather(1, order)
+    idx = torch.where(vals > float("-inf"), order, torch.full_like(order, cols))
+    idx = torch.sort(idx, dim=1).values
+    idx = torch.where(idx >= cols, torch.full_like(idx, -1), idx + col_base)
+    # dead slots stay where the ascending order puts them: at the end
+    if kk < k:
+        idx = torch.nn.functional.pad(idx, (0, k - kk), value=-1)
+    return idx.to(torch.int32)
+
+
 # ------------------------------------------------------------------ sequence-mixing helpers (linear / latent attention families)
 @register("l2norm_fwd", "eager")
 def l2norm_fwd(x, eps: float = 1e-6):

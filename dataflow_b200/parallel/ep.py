@@ -61,6 +61,10 @@ class EpGroup:
         self.rank, self.world, self.device = rank, world, device
         self.lane = lane or os.environ.get("DATAFLOW_EP_LANE") or ("p2p" if device is not None else "collective")
         self.timeout_s = timeout_s
+        self.capacity_factor = float(capacity_factor)
+        self.allow_drops = os.environ.get("DATAFLOW_EP_ALLOW_DROPS", "0") == "1"
+        self.dropped_step = None          # device counter of this step's dropped slots (created with the first plan)
+        self.dropped_total = 0
         self.T, self.d, self.E, self.K = int(tokens), int(d_model), int(n_experts), int(top_k)
         self.e_local = self.E // world
         slots = self.T * self.K
@@ -111,11 +115,22 @@ class EpGroup:
             self.ws = []
 
     def check(self) -> None:
+        """Called once per step, after the engine has drained: raises on a kernel time-out, and on dropped token slots — a step
+        that dropped slots trained a different model than the one asked for (``allow_drops`` turns that into a count)."""
         if self.lane == "p2p":
             code = int(self.err.item())
             if code:
                 self.err.zero_()
                 raise RuntimeError(f"fused expert-parallel kernel gave up: phase {code >> 8}, peer/rank {code & 255}")
+        if self.dropped_step is not None:
+            n = int(self.dropped_step.item())
+            self.dropped_step.zero_()
+            self.dropped_total += n
+            if n and not self.allow_drops:
+                raise RuntimeError(
+                    f"expert-parallel dispatch dropped {n} token slots on rank {self.rank} this step: routing was more than "
+                    f"{self.capacity_factor:g}x out of balance for a dispatched matrix of {self.C} rows; raise the capacity factor "
+                    f"(ep_capacity; {self.world:g} can never drop) or set DATAFLOW_EP_ALLOW_DROPS=1 to train on with the loss")
 
     def all_reduce(self, t):
         """Sum over the group (gradients of the parameters every rank holds in full)."""
@@ -186,6 +201,9 @@ class EpGroup:
         counts = torch.zeros(self.E, dtype=torch.int32, device=ids.device)
         counts.scatter_add_(0, all_ids.reshape(-1).long(), torch.ones(all_ids.numel(), dtype=torch.int32, device=ids.device))
         dropped = (mine & ~keep).sum().to(torch.int32)
+        if self.dropped_step is None:
+            self.dropped_step = torch.zeros((), dtype=torch.int32, device=ids.device)
+        self.dropped_step += dropped
         plan = EpPlan(ids=ids.contiguous(), weights=weights.float().contiguous(), row_src=row_src.to(torch.int32).contiguous(),
                       row_slot=row_slot, row_w=row_w.float().contiguous(), tile_expert=tile_expert.to(torch.int32), offsets_pad=offsets,
                       counts=counts, dropped=dropped)

@@ -55,6 +55,14 @@ def test_capacity_drops_slots_past_the_dispatched_matrix():
     assert int(plan.dropped) == 1000 - 768
     assert int((plan._table >= 0).sum()) == 768
     assert int(plan.offsets_pad[-1]) == 768 and (plan.tile_expert == 0).all()
+    # a step that dropped slots fails at its end, with the count, unless drops are allowed; the counter restarts every step
+    with pytest.raises(RuntimeError, match="dropped 232 token slots"):
+        g.check()
+    g.check()
+    g.allow_drops = True
+    g.plan(torch.zeros(1000, 1, dtype=torch.int32), torch.ones(1000, 1))
+    g.check()
+    assert g.dropped_total == 2 * 232
 
 
 def test_ep_collective_lane_on_cpu_ranks_matches_dense_oracle(tmp_path):

@@ -296,3 +296,46 @@ def test_flash_bwd_tcgen05_kernels_match_the_reference(shape):
         assert err < 2e-2, (name, err)
     d2 = impls["flash_bwd"]["sm100"](do, q, k, v, o, lse, cu, mx)       # the default lane is this kernel
     assert torch.equal(d2[0], dq) and torch.equal(d2[1], dk) and torch.equal(d2[2], dv)
+
+
+@pytest.mark.parametrize("n,H,D,bounds", [(300, 4, 64, [0, 300]), (1000, 8, 128, [0, 137, 700, 1000]), (2500, 64, 128, [0, 2500]),
+                                           (130, 3, 128, [0, 5, 130])])
+def test_dsa_index_scores_on_tcgen05_match_the_fp32_form(K, n, H, D, bounds):
+    """Indexer scores (ReLU-weighted sum over heads fused behind the tensor-core product, visibility mask applied) against
+    the eager fp32 form of the same bf16 inputs; blocks of query rows; ragged sequences; written twice over different poison."""
+    torch.manual_seed(n)
+    q, k = bf(n, H, D, scale=D ** -0.25), bf(n, D, scale=D ** -0.25)
+    wgt = torch.randn(n, H, device=DEV)
+    seg_start = torch.cat([torch.full((b - a,), a, dtype=torch.int32) for a, b in zip(bounds[:-1], bounds[1:])]).to(DEV)
+    for q0, q1 in ((0, n), (128, min(n, 640)), (n - 70, n)):
+        if q0 >= q1:
+            continue
+        got = K.dsa_index_scores(q, k, wgt, seg_start, q0, q1, 0)
+        want = eager.dsa_index_scores(q, k, wgt, seg_start, q0, q1, 0)
+        fin = torch.isfinite(want)
+        assert torch.equal(torch.isfinite(got), fin)
+        assert torch.equal(got[~fin], want[~fin])               # -inf exactly where the query does not see the key
+        assert rel(got[fin], want[fin]) < 2e-3
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("rows,cols,k", [(5, 40, 12), (64, 3000, 256), (33, 16384, 2048), (9, 100, 100), (4, 50, 80)])
+def test_dsa_topk_rows_is_exact_and_deterministic(K, rows, cols, k):
+    """The selection kernel against a stable sort: the k largest of every row, ties to the smaller index, ascending indices,
+    -1 for rows with fewer finite entries; ReLU-like inputs with many exact ties; two runs over different poison agree."""
+    torch.manual_seed(cols)
+    s = torch.relu(torch.randn(rows, cols, device=DEV)) * (torch.rand(rows, cols, device=DEV) > 0.3)      # many zeros
+    s[:, int(cols * 0.8):] = float("-inf")
+    s[0] = float("-inf")
+    if rows > 2:
+        s[2, : cols // 2] = 1.5                                                                              # one long tie
+    want = eager.dsa_topk_rows(s, k, 7)
+    outs = []
+    for poison in (-3, 12345):
+        sel = torch.full((rows, k), poison, dtype=torch.int32, device=DEV)
+        from dataflow_b200.ops import native
+        native().dsa_topk_rows(s, rows, cols, 7, k, sel)
+        outs.append(sel)
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0].cpu(), want.cpu())
+    assert torch.equal(K.dsa_topk_rows(s, k, 7), outs[0])
