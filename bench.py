@@ -195,7 +195,7 @@ def bench_ours(a) -> dict:
         "loss": float(lsum[0]) if losses else None,
         "plan": {"predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
                  "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
-                 "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows,
+                 "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows, "pool": _pool_line(tr),
                  "placement_escapes": res.placement_escapes, "pressure_evictions": res.pressure_evictions,
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},
@@ -209,6 +209,15 @@ def bench_ours(a) -> dict:
     if world > 1:
         torch.distributed.destroy_process_group()
     return out if rank == 0 else {}
+
+
+def _pool_line(tr) -> dict:
+    """How the fast pool is backed, and (vmm mode) how many pages it mapped and moved so far."""
+    try:
+        st = tr.session.native.fast_pool_stats()
+    except Exception:       # noqa: BLE001
+        return {"mode": getattr(tr, "pool_mode", "slab")}
+    return {k: (int(v) if not isinstance(v, str) else v) for k, v in st.items() if k in ("mode", "maps", "reclaims", "phys_pages", "held_pages")}
 
 
 def main(argv=None) -> int:

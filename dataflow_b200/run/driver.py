@@ -122,7 +122,7 @@ class Trainer:
                  kernels=None, kernel_set: str | None = None, recompute: bool = True, profile: bool = False,
                  leeway_bytes: int | None = None, planned: PlannedProgram | None = None,
                  lower_kwargs: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
-                 init: bool = True, verbose: bool = False, static_placement: bool | None = None):
+                 init: bool = True, verbose: bool = False, static_placement: bool | None = None, pool_mode: str | None = None):
         import torch
         from ..ops import resolve_kernels
         self.fam = resolve_family(family)
@@ -196,7 +196,28 @@ class Trainer:
                 sizes_all = self.program.object_sizes()
                 pub = max((b for oid, b in sizes_all.items() if oid.startswith(("dW", "W", "dEmbed", "dHead", "Embed", "Head"))), default=0)
                 self.session.native.set_fast_tail(2 * (int(pub) + 4096))
-            self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0)
+            # pool mode: "vmm" backs the pool page by page behind twice its size of virtual addresses (fragmentation then costs
+            # address room, not memory: no overflow allocations); "slab" is one allocation, which is what peers can map, so the
+            # sharded data-parallel lanes (whose kernels read peers' slabs) keep it.  "auto" picks by that rule.
+            mode = pool_mode or os.environ.get("DATAFLOW_POOL_MODE", "auto")
+            if mode not in ("auto", "slab", "vmm"):
+                raise ValueError(f"pool mode {mode!r}: auto | slab | vmm")
+            peers_map_slab = bool(zero_md and int(zero_md.get("world", 1)) > 1)
+            if mode == "vmm" and peers_map_slab:
+                raise ValueError("pool mode 'vmm' cannot serve the sharded data-parallel lanes: their kernels read peers' slabs through "
+                                 "one mapping of one allocation")
+            self.pool_mode = "vmm" if mode == "vmm" or (mode == "auto" and not peers_map_slab) else "slab"
+            try:
+                self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, self.pool_mode == "vmm")
+            except RuntimeError as e:
+                if mode == "vmm":
+                    raise
+                if verbose:
+                    print(f"vmm pool not available ({e}); using one allocation")
+                self.pool_mode = "slab"
+                self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, False)
+        else:
+            self.pool_mode = "slab"
         self.step_index = 0
         self.last_result = None
         # static placement: offsets of every device allocation of a step, computed from a dry run (runtime/placement.py)

@@ -8,7 +8,7 @@ from .executable import (Buffer, Executable, SyntheticExecutable, TaskContext, s
 from .trace import Interval, RunTrace, compare_to_sim_eventlog, trace_from_dict, trace_to_dict
 
 CudaBackend = getattr(_runtime, "CudaBackend", None)
-VmmArena = getattr(_runtime, "VmmArena", None)
+PoolProbe = getattr(_runtime, "PoolProbe", None)
 
 
 def set_nvtx(on: bool) -> None:

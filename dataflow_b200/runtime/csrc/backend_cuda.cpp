@@ -1,4 +1,5 @@
 #include "backend_cuda.hpp"
+#include "vmm.hpp"
 
 #include <sched.h>
 #include <sys/mman.h>
@@ -100,6 +101,11 @@ void* CudaBackend::alloc(Location loc, size_t bytes) {
     return p;
   }
   return pin_region(bytes ? bytes : 1, true);
+}
+
+std::unique_ptr<VmSpace> CudaBackend::create_vm_space(size_t va_bytes, size_t phys_bytes) {
+  check(cudaSetDevice(device_), "cudaSetDevice");
+  return std::make_unique<CudaVmSpace>(device_, va_bytes, phys_bytes);
 }
 
 void CudaBackend::free(Location loc, void* p, size_t bytes) {

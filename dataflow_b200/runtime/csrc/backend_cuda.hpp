@@ -27,6 +27,7 @@ class CudaBackend : public Backend {
   void mark_epoch() override;
   void* alloc(Location loc, size_t bytes) override;
   void free(Location loc, void* p, size_t bytes) override;
+  std::unique_ptr<VmSpace> create_vm_space(size_t va_bytes, size_t phys_bytes) override;
   void memcpy_async(void* dst, const void* src, size_t bytes, int stream, double) override;
   void memset_async(void* dst, int value, size_t bytes, int stream) override;
   void busy(int stream, double us) override;

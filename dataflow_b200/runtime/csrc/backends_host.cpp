@@ -51,6 +51,24 @@ void* FakeBackend::alloc(Location, size_t bytes) {
 
 void FakeBackend::free(Location, void*, size_t) {}
 
+HostVmSpace::HostVmSpace(size_t va_bytes, size_t phys_bytes, bool real, uintptr_t fake_base, size_t page) : real_(real) {
+  init(page, va_bytes, phys_bytes);
+  if (real) {
+    if (posix_memalign(&base_, 4096, this->va_bytes()) != 0) throw EngineError("AllocError", "host range of " + std::to_string(va_bytes) + " bytes failed");
+  } else {
+    base_ = reinterpret_cast<void*>(fake_base);
+  }
+}
+HostVmSpace::~HostVmSpace() {
+  if (real_) std::free(base_);
+}
+
+std::unique_ptr<VmSpace> FakeBackend::create_vm_space(size_t va_bytes, size_t phys_bytes) {
+  uintptr_t p = next_addr_;
+  next_addr_ += (va_bytes + (2u << 20)) / 4096 * 4096 + 4096;
+  return std::make_unique<HostVmSpace>(va_bytes, phys_bytes, false, p);
+}
+
 void FakeBackend::memcpy_async(void*, const void*, size_t, int stream, double planned_us) {
   busy(stream, planned_us * transfer_time_scale);
 }
@@ -105,6 +123,10 @@ void* CpuBackend::alloc(Location, size_t bytes) {
 }
 
 void CpuBackend::free(Location, void* p, size_t) { std::free(p); }
+
+std::unique_ptr<VmSpace> CpuBackend::create_vm_space(size_t va_bytes, size_t phys_bytes) {
+  return std::make_unique<HostVmSpace>(va_bytes, phys_bytes, true, 0);
+}
 
 void CpuBackend::memcpy_async(void* dst, const void* src, size_t bytes, int, double) {
   if (bytes) std::memcpy(dst, src, bytes);

@@ -9,6 +9,25 @@
 
 namespace dfb {
 
+// Paged range of the host backends: the accounting of the VMM pool mode without a driver.  ``real`` backs the whole range
+// with (lazily committed) host memory; otherwise the range is a span of made-up addresses that nothing dereferences.
+class HostVmSpace : public VmSpace {
+ public:
+  HostVmSpace(size_t va_bytes, size_t phys_bytes, bool real, uintptr_t fake_base, size_t page = 2u << 20);
+  ~HostVmSpace() override;
+  void* base() const override { return base_; }
+  int64_t unmaps = 0;
+
+ protected:
+  bool map_page(size_t) override { return true; }
+  void unmap_page(size_t) override { ++unmaps; }
+  void grant(size_t, size_t) override {}
+
+ private:
+  void* base_ = nullptr;
+  bool real_ = false;
+};
+
 // Virtual-time backend: per-stream clocks, a heap of (time, priority, seq) completions.
 class FakeBackend : public Backend {
  public:
@@ -22,6 +41,7 @@ class FakeBackend : public Backend {
   void mark_epoch() override;
   void* alloc(Location, size_t bytes) override;
   void free(Location, void*, size_t) override;
+  std::unique_ptr<VmSpace> create_vm_space(size_t va_bytes, size_t phys_bytes) override;
   void memcpy_async(void*, const void*, size_t, int stream, double planned_us) override;
   void memset_async(void*, int, size_t, int) override;
   void busy(int stream, double us) override;
@@ -64,6 +84,7 @@ class CpuBackend : public Backend {
   void mark_epoch() override;
   void* alloc(Location, size_t bytes) override;
   void free(Location, void* p, size_t) override;
+  std::unique_ptr<VmSpace> create_vm_space(size_t va_bytes, size_t phys_bytes) override;
   void memcpy_async(void* dst, const void* src, size_t bytes, int, double) override;
   void memset_async(void* dst, int value, size_t bytes, int) override;
   void busy(int, double us) override;

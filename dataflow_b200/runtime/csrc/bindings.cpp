@@ -13,7 +13,6 @@
 #include <nvtx3/nvToolsExt.h>
 
 #include "backend_cuda.hpp"
-#include "vmm.hpp"
 #endif
 
 namespace py = pybind11;
@@ -54,6 +53,24 @@ static py::dict result_to_py(const RunResult& r) {
   py::dict f;
   for (auto& b : r.finals) f[py::str(b.id)] = py::make_tuple(b.loc, b.ptr, b.size, b.external);
   d["finals"] = f;
+  return d;
+}
+
+static py::dict pool_stats(BufferPool& pool) {
+  py::dict d;
+  d["mode"] = pool.vm_active() ? "vmm" : "slab";
+  d["capacity"] = pool.slab_capacity();
+  d["overflows"] = pool.slab_overflows;
+  d["vendor_allocs"] = pool.vendor_allocs;
+  if (const VmSpace* vm = pool.vm()) {
+    d["page"] = vm->page();
+    d["va_bytes"] = vm->va_bytes();
+    d["phys_pages"] = vm->phys_pages();
+    d["held_pages"] = vm->held_pages();
+    d["mapped_pages"] = vm->mapped_pages();
+    d["maps"] = vm->maps;
+    d["reclaims"] = vm->reclaims;
+  }
   return d;
 }
 
@@ -146,17 +163,33 @@ PYBIND11_MODULE(_runtime, m) {
         return d;
       }, py::arg("bytes") = (256u << 20), py::arg("repeats") = 4);
 
-  py::class_<VmmArena, std::shared_ptr<VmmArena>>(m, "VmmArena")
-      .def(py::init<int, size_t>(), py::arg("device"), py::arg("va_bytes"))
-      .def("available", &VmmArena::available)
-      .def("granule", &VmmArena::granule)
-      .def("base", &VmmArena::base)
-      .def("map", &VmmArena::map)
-      .def("unmap", &VmmArena::unmap)
-      .def("mapped_bytes", &VmmArena::mapped_bytes)
-      .def("parked_bytes", &VmmArena::parked_bytes)
-      .def("trim", &VmmArena::trim)
-      .def("driver_calls", &VmmArena::driver_calls);
+  // One buffer pool on its own (tests of the pool modes; the engine owns its pools through Session).
+  struct PoolProbe {
+    std::shared_ptr<Backend> be;
+    BufferPool pool;
+    std::map<int, BufferRef> live;
+    int next = 0;
+    PoolProbe(std::shared_ptr<Backend> b, size_t capacity, bool vm, double va_factor) : be(std::move(b)), pool(be.get(), FAST) {
+      pool.set_vm_mode(vm, va_factor);
+      pool.ensure_slab(capacity);
+    }
+  };
+  py::class_<PoolProbe>(m, "PoolProbe")
+      .def(py::init<std::shared_ptr<Backend>, size_t, bool, double>(), py::arg("backend"), py::arg("capacity"), py::arg("vm") = false,
+           py::arg("va_factor") = 2.0)
+      .def("get", [](PoolProbe& p, size_t bytes) {
+        BufferRef b = p.pool.get(bytes);
+        int h = p.next++;
+        p.live[h] = b;
+        return py::make_tuple(h, reinterpret_cast<uint64_t>(b.ptr), b.overflow);
+      })
+      .def("put", [](PoolProbe& p, int h) {
+        auto it = p.live.find(h);
+        if (it == p.live.end()) throw std::runtime_error("unknown pool handle");
+        p.pool.put(it->second);
+        p.live.erase(it);
+      })
+      .def("stats", [](PoolProbe& p) { return pool_stats(p.pool); });
   m.def("set_nvtx", [](bool on) { g_nvtx.store(on); });
   m.def("nvtx_mark", [](const std::string& s) { if (g_nvtx.load()) nvtxMarkA(s.c_str()); });
 #else
@@ -205,7 +238,9 @@ PYBIND11_MODULE(_runtime, m) {
       .def_readonly("compute_stream", &Session::compute_stream)
       .def_readonly("h2d_stream", &Session::h2d_stream)
       .def_readonly("d2h_stream", &Session::d2h_stream)
-      .def("ensure_pools", &Session::ensure_pools, py::arg("fast_cap"), py::arg("backing_cap"), py::arg("headroom") = 0.0)
+      .def("ensure_pools", &Session::ensure_pools, py::arg("fast_cap"), py::arg("backing_cap"), py::arg("headroom") = 0.0,
+           py::arg("fast_vm") = false)
+      .def("fast_pool_stats", [](Session& s) { return pool_stats(s.fast_pool); })
       .def("fast_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.fast_pool.slab_base()), s.fast_pool.slab_capacity()); })
       .def("set_fast_tail", [](Session& s, size_t bytes) { s.fast_pool.set_tail(bytes); })
       .def("fast_tail", [](Session& s) { return s.fast_pool.slab_tail(); })

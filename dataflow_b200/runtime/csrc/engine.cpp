@@ -14,17 +14,32 @@ static inline double host_now_us() {
 // ----------------------------------------------------------------------------- BufferPool
 BufferPool::~BufferPool() {
   trim();
+  if (vm_) { vm_.reset(); base_ = nullptr; }
   if (base_) be_->free(loc_, base_, alloc_bytes_);
 }
 
 void BufferPool::ensure_slab(size_t capacity) {
   capacity = SlabAllocator::round_up(capacity, SlabAllocator::kAlign);   // the slab's usable extent is aligned
-  if (slab_ && slab_->capacity() >= capacity) return;
+  if (slab_ && slab_capacity() >= capacity) return;
   if (slab_) {
     if (slab_->live_blocks()) return;   // cannot grow under live buffers; overflow handles the rest
-    be_->free(loc_, base_, alloc_bytes_);
+    if (vm_) vm_.reset();
+    else be_->free(loc_, base_, alloc_bytes_);
     slab_.reset();
     base_ = nullptr;
+  }
+  if (vm_mode_ && tail_bytes_ == 0) {
+    // a tail (staging that peers address through one mapping of the slab) needs the classic single allocation
+    auto space = be_->create_vm_space(static_cast<size_t>(capacity * va_factor_), capacity);
+    if (space) {
+      vm_ = std::move(space);
+      base_ = vm_->base();
+      phys_capacity_ = capacity;
+      alloc_bytes_ = 0;
+      vendor_allocs++;
+      slab_ = std::make_unique<SlabAllocator>(vm_->va_bytes());
+      return;
+    }
   }
   // the tail (set_tail) lies behind the managed extent, in the same allocation: whoever maps the slab for peers
   // gets it too, and the allocator never hands it out
@@ -39,6 +54,10 @@ BufferRef BufferPool::get(size_t bytes) {
   b.size = bytes;
   if (slab_) {
     size_t off = slab_->allocate(bytes);
+    if (off != SlabAllocator::kNone && vm_ && !vm_->hold(off, slab_->block_size(off))) {
+      slab_->release(off);              // address room but no physical page left
+      off = SlabAllocator::kNone;
+    }
     if (off != SlabAllocator::kNone) {
       b.ptr = static_cast<char*>(base_) + off;
       b.slab_off = off;
@@ -62,6 +81,7 @@ BufferRef BufferPool::get(size_t bytes) {
 BufferRef BufferPool::get_at(size_t bytes, size_t offset) {
   BufferRef b;
   if (!slab_ || offset % SlabAllocator::kAlign || !slab_->allocate_at(offset, bytes)) return b;
+  if (vm_ && !vm_->hold(offset, slab_->block_size(offset))) { slab_->release(offset); return b; }
   b.size = bytes;
   b.ptr = static_cast<char*>(base_) + offset;
   b.slab_off = offset;
@@ -71,6 +91,7 @@ BufferRef BufferPool::get_at(size_t bytes, size_t offset) {
 void BufferPool::put(BufferRef& b) {
   if (!b.ptr || b.external) { b = BufferRef(); return; }
   if (b.slab_off != SlabAllocator::kNone) {
+    if (vm_) vm_->drop(b.slab_off, slab_->block_size(b.slab_off));
     slab_->release(b.slab_off);
   } else {
     free_exact_.insert({SlabAllocator::round_up(b.size ? b.size : 1, SlabAllocator::kAlign), b.ptr});
@@ -93,7 +114,8 @@ Session::Session(std::shared_ptr<Backend> be)
 
 Session::~Session() { backend->synchronize(); }
 
-void Session::ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom) {
+void Session::ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom, bool fast_vm) {
+  if (fast_vm) fast_pool.set_vm_mode(true);
   if (fast_cap > 0) fast_pool.ensure_slab(static_cast<size_t>(fast_cap * (1.0 + headroom)) + (1 << 20));
   if (backing_cap > 0) backing_pool.ensure_slab(static_cast<size_t>(backing_cap) + (1 << 20));
 }

@@ -74,16 +74,21 @@ class BufferPool {
   BufferPool(Backend* be, Location loc) : be_(be), loc_(loc) {}
   ~BufferPool();
   void ensure_slab(size_t capacity);
+  // VMM mode (before the first ensure_slab): the slab allocator then manages ``va_factor`` times the capacity of VIRTUAL
+  // addresses and the capacity is a budget of physical pages, so fragmentation costs address space, not memory
+  void set_vm_mode(bool on, double va_factor = 2.0) { vm_mode_ = on; va_factor_ = va_factor; }
+  bool vm_active() const { return vm_ != nullptr; }
+  const VmSpace* vm() const { return vm_.get(); }
   // static placement: the buffer at a planned slab offset; an empty ref (ptr == nullptr) when those bytes are taken
   BufferRef get_at(size_t bytes, size_t offset);
   BufferRef get(size_t bytes);
   void put(BufferRef& b);
   void trim();
-  size_t slab_capacity() const { return slab_ ? slab_->capacity() : 0; }
+  size_t slab_capacity() const { return vm_ ? phys_capacity_ : (slab_ ? slab_->capacity() : 0); }
   void* slab_base() const { return base_; }
   // bytes kept behind the managed extent of the NEXT slab allocation (staging that peers must be able to address)
   void set_tail(size_t bytes) { tail_bytes_ = SlabAllocator::round_up(bytes, SlabAllocator::kAlign); }
-  size_t slab_tail() const { return base_ ? alloc_bytes_ - slab_->capacity() : 0; }
+  size_t slab_tail() const { return base_ && !vm_ ? alloc_bytes_ - slab_->capacity() : 0; }
   int64_t slab_overflows = 0;
   int64_t vendor_allocs = 0;
  private:
@@ -92,6 +97,10 @@ class BufferPool {
   void* base_ = nullptr;
   size_t alloc_bytes_ = 0, tail_bytes_ = 0;
   std::unique_ptr<SlabAllocator> slab_;
+  std::unique_ptr<VmSpace> vm_;
+  bool vm_mode_ = false;
+  double va_factor_ = 2.0;
+  size_t phys_capacity_ = 0;
   std::multimap<size_t, void*> free_exact_;
 };
 
@@ -103,7 +112,7 @@ class Session {
   std::shared_ptr<Backend> backend;
   int compute_stream, h2d_stream, d2h_stream;
   BufferPool fast_pool, backing_pool;
-  void ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom);
+  void ensure_pools(int64_t fast_cap, int64_t backing_cap, double headroom, bool fast_vm = false);
   // Fast copies of objects whose final location is "fast", kept out of the pool between execute() calls
   // (ExecOptions::keep_resident).  The next program that starts such an object in fast adopts the bytes
   // in place: parameters stay on the device across steps with no transfer.

@@ -1,6 +1,5 @@
 #include "vmm.hpp"
 
-#include <stdexcept>
 #include <string>
 
 namespace dfb {
@@ -14,7 +13,7 @@ static bool entry(const char* name, F*& fn) {
   return true;
 }
 
-bool VmmArena::resolve() {
+bool CudaVmSpace::resolve() {
   return entry("cuMemAddressReserve", memAddressReserve_) && entry("cuMemAddressFree", memAddressFree_) &&
          entry("cuMemCreate", memCreate_) && entry("cuMemRelease", memRelease_) && entry("cuMemMap", memMap_) &&
          entry("cuMemUnmap", memUnmap_) && entry("cuMemSetAccess", memSetAccess_) &&
@@ -29,72 +28,68 @@ static CUmemAllocationProp device_prop(int device) {
   return prop;
 }
 
-VmmArena::VmmArena(int device, size_t va_bytes) : device_(device) {
-  if (cudaSetDevice(device) != cudaSuccess) return;
+CudaVmSpace::CudaVmSpace(int device, size_t va_bytes, size_t phys_bytes) : device_(device) {
+  if (cudaSetDevice(device) != cudaSuccess) throw EngineError("AllocError", "cudaSetDevice failed");
   cudaFree(nullptr);   // make sure the primary context exists
-  if (!resolve()) return;
+  if (!resolve()) throw EngineError("AllocError", "the driver exposes no virtual-memory management API");
   CUmemAllocationProp prop = device_prop(device);
   size_t g = 0;
-  if (memGetGranularity_(&g, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) != CUDA_SUCCESS || g == 0) return;
-  granule_ = g;
-  va_bytes_ = (va_bytes + g - 1) / g * g;
-  if (memAddressReserve_(&base_, va_bytes_, g, 0, 0) != CUDA_SUCCESS) return;
-  driver_calls_++;
-  ok_ = true;
+  if (memGetGranularity_(&g, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) != CUDA_SUCCESS || g == 0)
+    throw EngineError("AllocError", "cuMemGetAllocationGranularity failed");
+  init(g, va_bytes, phys_bytes);
+  reserved_ = this->va_bytes();
+  if (memAddressReserve_(&base_, reserved_, g, 0, 0) != CUDA_SUCCESS)
+    throw EngineError("AllocError", "cuMemAddressReserve of " + std::to_string(reserved_) + " bytes failed");
+  ++driver_calls;
+  handle_of_.assign(reserved_ / g, 0);
 }
 
-VmmArena::~VmmArena() {
-  if (!ok_) return;
-  for (auto& kv : mapped_) {
-    memUnmap_(base_ + kv.first * granule_, granule_);
-    memRelease_(kv.second);
+CudaVmSpace::~CudaVmSpace() {
+  if (!base_) return;
+  for (size_t p = 0; p < handle_of_.size(); ++p) {
+    if (!handle_of_[p]) continue;
+    memUnmap_(base_ + p * page(), page());
+    memRelease_(handle_of_[p]);
   }
   for (auto h : parked_) memRelease_(h);
-  memAddressFree_(base_, va_bytes_);
+  memAddressFree_(base_, reserved_);
 }
 
-uint64_t VmmArena::map(size_t offset, size_t bytes) {
-  if (!ok_) throw std::runtime_error("VMM arena unavailable");
-  if (offset % granule_) throw std::runtime_error("VMM map offset is not granule aligned");
-  size_t first = offset / granule_, count = (bytes + granule_ - 1) / granule_;
-  if ((first + count) * granule_ > va_bytes_) throw std::runtime_error("VMM map exceeds the reserved range");
-  CUmemAllocationProp prop = device_prop(device_);
+bool CudaVmSpace::map_page(size_t p) {
+  CUmemGenericAllocationHandle h = 0;
+  if (!parked_.empty()) {
+    h = parked_.back();
+    parked_.pop_back();
+  } else {
+    CUmemAllocationProp prop = device_prop(device_);
+    ++driver_calls;
+    if (memCreate_(&h, page(), &prop, 0) != CUDA_SUCCESS) return false;          // the device itself is out of memory
+  }
+  ++driver_calls;
+  if (memMap_(base_ + p * page(), page(), 0, h, 0) != CUDA_SUCCESS) {
+    parked_.push_back(h);
+    return false;
+  }
+  handle_of_[p] = h;
+  return true;
+}
+
+void CudaVmSpace::unmap_page(size_t p) {
+  if (!handle_of_[p]) return;
+  ++driver_calls;
+  memUnmap_(base_ + p * page(), page());
+  parked_.push_back(handle_of_[p]);
+  handle_of_[p] = 0;
+}
+
+void CudaVmSpace::grant(size_t p0, size_t count) {
   CUmemAccessDesc acc = {};
-  acc.location = prop.location;
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device_;
   acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
-  for (size_t g = first; g < first + count; ++g) {
-    if (mapped_.count(g)) continue;
-    CUmemGenericAllocationHandle h;
-    if (!parked_.empty()) { h = parked_.back(); parked_.pop_back(); }
-    else {
-      if (memCreate_(&h, granule_, &prop, 0) != CUDA_SUCCESS) throw std::runtime_error("cuMemCreate failed");
-      driver_calls_++;
-    }
-    CUdeviceptr at = base_ + g * granule_;
-    if (memMap_(at, granule_, 0, h, 0) != CUDA_SUCCESS) { parked_.push_back(h); throw std::runtime_error("cuMemMap failed"); }
-    if (memSetAccess_(at, granule_, &acc, 1) != CUDA_SUCCESS) throw std::runtime_error("cuMemSetAccess failed");
-    driver_calls_ += 2;
-    mapped_[g] = h;
-  }
-  return static_cast<uint64_t>(base_ + offset);
-}
-
-void VmmArena::unmap(size_t offset, size_t bytes) {
-  if (!ok_) return;
-  size_t first = offset / granule_, count = (bytes + granule_ - 1) / granule_;
-  for (size_t g = first; g < first + count; ++g) {
-    auto it = mapped_.find(g);
-    if (it == mapped_.end()) continue;
-    memUnmap_(base_ + g * granule_, granule_);
-    driver_calls_++;
-    parked_.push_back(it->second);
-    mapped_.erase(it);
-  }
-}
-
-void VmmArena::trim() {
-  for (auto h : parked_) { memRelease_(h); driver_calls_++; }
-  parked_.clear();
+  ++driver_calls;
+  if (memSetAccess_(base_ + p0 * page(), count * page(), &acc, 1) != CUDA_SUCCESS)
+    throw EngineError("AllocError", "cuMemSetAccess failed");
 }
 
 }  // namespace dfb
