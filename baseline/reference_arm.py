@@ -206,7 +206,12 @@ def _run_fleet(a, world: int, here: str, ref: str) -> dict:
         tokens_step = cfg.max_tokens * cfg.grad_accum_rounds
         feed = pipeline_from_args(cfg, f"synthetic:mean_len={8 * a.seq_len},seed=0,long_policy=trim")
         backing = _host_backing_gib(world)
-        interpreter = f"{sys.executable} {os.path.join(here, 'ref_launch.py')}"
+        # One GPU per daemon through CUDA_VISIBLE_DEVICES (device 0 inside each): the reference's NCCL bring-up thread never
+        # selects a device, so on a box where every daemon sees every GPU all ranks would open the communicator on GPU 0.
+        visible = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v] or [str(i) for i in range(world)]
+
+        def interpreter(i):
+            return f"env CUDA_VISIBLE_DEVICES={visible[i]} {sys.executable} {os.path.join(here, 'ref_launch.py')}"
 
         def free_port():
             with socket.socket() as s:
@@ -214,8 +219,8 @@ def _run_fleet(a, world: int, here: str, ref: str) -> dict:
                 return s.getsockname()[1]
 
         names = [f"gpu{i}" for i in range(world)]
-        hosts = {n: HostSpec(name=n, peer_listen=f"127.0.0.1:{free_port()}", ssh=None, python=interpreter, repo=ref,
-                             backing_gib=backing, budget_gib=budget, device=i) for i, n in enumerate(names)}
+        hosts = {n: HostSpec(name=n, peer_listen=f"127.0.0.1:{free_port()}", ssh=None, python=interpreter(i), repo=ref,
+                             backing_gib=backing, budget_gib=budget, device=0) for i, n in enumerate(names)}
         topo = Topology(conductor=names[0], hosts=hosts,
                         groups={"dp": GroupSpec(name="dp", members=tuple(names), backend="nccl")}, source="<bench: one box>")
         scheme = ParallelismScheme.data_parallel((per_rank,) * world, responsibility="zero1rs")
