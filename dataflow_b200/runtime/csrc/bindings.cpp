@@ -192,9 +192,13 @@ PYBIND11_MODULE(_runtime, m) {
       .def("stats", [](PoolProbe& p) { return pool_stats(p.pool); });
   m.def("set_nvtx", [](bool on) { g_nvtx.store(on); });
   m.def("nvtx_mark", [](const std::string& s) { if (g_nvtx.load()) nvtxMarkA(s.c_str()); });
+  m.def("nvtx_push", [](const std::string& s) { nvtxRangePushA(s.c_str()); });
+  m.def("nvtx_pop", []() { nvtxRangePop(); });
 #else
   m.def("set_nvtx", [](bool) {});
   m.def("nvtx_mark", [](const std::string&) {});
+  m.def("nvtx_push", [](const std::string&) {});
+  m.def("nvtx_pop", []() {});
 #endif
 
   py::class_<SlabAllocator>(m, "SlabAllocator")
@@ -266,7 +270,7 @@ PYBIND11_MODULE(_runtime, m) {
            [](Engine& e, std::shared_ptr<ProgramIR> p, py::object launch, py::dict initial,
               bool strict_final, bool poison, bool record_events, double headroom,
               std::shared_ptr<std::atomic<bool>> cancel, bool manage_pools, bool keep_resident, int dispatch_ahead,
-              bool record_allocs, std::vector<std::vector<int64_t>> placement) {
+              bool record_allocs, std::vector<std::vector<int64_t>> placement, py::object annotate) {
              std::unordered_map<std::string, InitialBuffer> init;
              for (auto kv : initial) {
                auto t = kv.second.cast<py::tuple>();
@@ -291,8 +295,15 @@ PYBIND11_MODULE(_runtime, m) {
                };
              }
              RangeFn range;
+             if (!annotate.is_none()) {
+               // a Python annotator (recording, renaming, or NVTX through nvtx_push / nvtx_pop): called with the GIL
+               range = [annotate](const std::string& name, bool push) {
+                 py::gil_scoped_acquire gil;
+                 annotate(name, push);
+               };
+             }
 #ifdef DFB_WITH_CUDA
-             if (g_nvtx.load()) {
+             else if (g_nvtx.load()) {
                range = [](const std::string& name, bool push) {
                  if (push) nvtxRangePushA(name.c_str()); else nvtxRangePop();
                };
@@ -310,5 +321,5 @@ PYBIND11_MODULE(_runtime, m) {
            py::arg("record_events") = false, py::arg("slab_headroom") = 0.0,
            py::arg("cancel") = std::shared_ptr<std::atomic<bool>>(), py::arg("manage_pools") = true,
            py::arg("keep_resident") = false, py::arg("dispatch_ahead") = 0, py::arg("record_allocs") = false,
-           py::arg("placement") = std::vector<std::vector<int64_t>>());
+           py::arg("placement") = std::vector<std::vector<int64_t>>(), py::arg("annotate") = py::none());
 }

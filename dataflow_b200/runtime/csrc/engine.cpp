@@ -227,9 +227,11 @@ bool Engine::try_start(int dir) {
   int n = xfer_seq_[{dir, x.obj}]++;
   fl->name = std::string(dir == 0 ? "from_slow:" : "to_slow:") + p_->objs[x.obj].id;
   if (n) fl->name += "#" + std::to_string(n);
+  if (range_) (*range_)("xfer:" + fl->name, true);
   fl->start_ev = be_->record_event(stream);
   be_->memcpy_async(d.buf.ptr, s.buf.ptr, static_cast<size_t>(x.size), stream, xfer_us(x));
   fl->end_ev = be_->record_event(stream);
+  if (range_) (*range_)("xfer:" + fl->name, false);
   be_->notify_after(fl->end_ev, make_token(dir == 0 ? TOK_FROM : TOK_TO, 0), dir == 0 ? PRIO_H2D_DONE : PRIO_D2H_DONE);
   pending_intervals_.push_back({fl->name, dir == 0 ? "from_slow" : "to_slow", fl->start_ev, fl->end_ev});
   if (dir == 0) { out_->stats.h2d_bytes += x.size; out_->stats.h2d_count++; }
@@ -488,7 +490,7 @@ void Engine::load_initial(const std::unordered_map<std::string, InitialBuffer>& 
 void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
                           const std::unordered_map<std::string, InitialBuffer>& initial,
                           const ExecOptions& opt, const RangeFn& range, RunResult& out) {
-  p_ = &p; opt_ = &opt; out_ = &out;
+  p_ = &p; opt_ = &opt; out_ = &out; range_ = range ? &range : nullptr;
   objs_.assign(p.objs.size(), ObjState());
   alloc_count_.assign(p.objs.size(), 0);
   evicted_.assign(p.objs.size(), 0);

@@ -228,6 +228,7 @@ class Engine {
   const ProgramIR* p_ = nullptr;
   const ExecOptions* opt_ = nullptr;
   RunResult* out_ = nullptr;
+  const RangeFn* range_ = nullptr;      // annotation hook of the run in progress (tasks by id, transfers as "xfer:<name>")
   std::vector<ObjState> objs_;
   std::set<int> done_early_;           // completed tasks whose predecessors have not retired yet
   std::vector<int> alloc_count_;       // fast allocations of each object so far in this run (indexes the placement)

@@ -190,9 +190,14 @@ class Engine:
                 run_args: Mapping[str, Any] | None = None, groups: Mapping[str, Any] | None = None,
                 cancel_event: threading.Event | None = None, record_events: bool = False,
                 slab_headroom: float = 0.0, manage_pools: bool = True, keep_resident: bool = False,
-                dispatch_ahead: int = 0, record_allocs: bool = False, placement=None) -> RunResult:
+                dispatch_ahead: int = 0, record_allocs: bool = False, placement=None, annotator=None,
+                annotate_rename: Callable[[str, str], str] | None = None) -> RunResult:
         """``placement``: a ``runtime.placement.Placement`` for this program (static offsets of every fast allocation);
-        ``record_allocs`` returns the allocation log the placement is computed from (``result.stats["allocs"]``)."""
+        ``record_allocs`` returns the allocation log the placement is computed from (``result.stats["allocs"]``).
+        ``annotator`` (``runtime.annotate``; default: what ``DATAFLOW_ANNOTATE`` names) is told every task launch and
+        transfer issue as a range; ``annotate_rename(name, kind)`` gives the displayed names only."""
+        from .annotate import annotator_from_env, make_hook
+        hook = make_hook(annotator if annotator is not None else annotator_from_env(), annotate_rename)
         ci = self.chain_index(program)
         tasks = program.tasks
         run_values: dict[str, Any] = {}
@@ -239,7 +244,7 @@ class Engine:
             raw = self._native.execute(ci.ir, launch, initial, self.strict_final_locations,
                                        self.poison_on_free, record_events, slab_headroom, cancel, manage_pools,
                                        keep_resident, int(dispatch_ahead), bool(record_allocs),
-                                       placement.for_index(ci) if placement is not None else [])
+                                       placement.for_index(ci) if placement is not None else [], hook)
         finally:
             if watcher is not None:
                 stop.set()

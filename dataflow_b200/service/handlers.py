@@ -42,7 +42,8 @@ def install(server) -> None:
     H["health"] = lambda req, p: {"status": "ok", "uptime_s": time.time() - server.state.started}
     H["engine_status"] = lambda req, p: {"backend": server.backend.name(), "device": server.config.device,
                                           "programs": len(server.programs), "runs": len(server.runs),
-                                          "counters": dict(server.state.counters), "store": st.query()}
+                                          "counters": dict(server.state.counters), "store": st.query(),
+                                          "host_bw_gbs": dict(getattr(server, "host_bw", {}))}
     H["session_status"] = lambda req, p: {"vendor_allocs": server._session.vendor_allocs()
                                           if getattr(server, "_session", None) else 0}
     H["subscribe_events"] = lambda req, p: {"events": server.state.events_since(int(req.get("since", 0)))}

@@ -168,6 +168,13 @@ class Server:
         pin = self.backend if (not cfg.fake and self.config.device is not None) else None
         self.slab = HostSlab(nbytes, pin)
         self.store = Store(self.slab)
+        self.host_bw = {}
+        if not cfg.fake and cfg.host_bw_probe_mib:
+            from .hostbw import measure_host_bw
+            try:
+                self.host_bw = measure_host_bw(self.slab, cfg.host_bw_probe_mib, self.config.device)
+            except Exception as e:       # noqa: BLE001  (a probe never keeps a daemon from booting)
+                self.host_bw = {"error": f"{type(e).__name__}: {e}"}
         from . import handlers, snapshots
         handlers.install(self)
         snapshots.install(self)

@@ -224,3 +224,20 @@ def test_pressure_eviction_valve_survives_a_plan_made_for_a_larger_memory():
     impossible = dataclasses.replace(prog, fast_memory_capacity=1000)
     bad = Engine(FakeBackend()).execute(impossible)
     assert bad.outcome.error_kind in ("DeadlockError", "LedgerError")
+
+
+def test_annotators_see_every_task_and_transfer_under_renamed_labels():
+    """A recording annotator gets one balanced range per task launch and per transfer issue; ``annotate_rename`` changes the
+    displayed names only (the run's trace keeps the program's ids)."""
+    from dataflow_b200.runtime.annotate import RecordingAnnotator
+    r = pressurefit(train_chain(L=3, rounds=1), 2500)
+    prog = from_sim_chain(r.chain)
+    rec = RecordingAnnotator()
+    res = Engine(FakeBackend()).execute(prog, annotator=rec, annotate_rename=lambda n, k: f"[{k}] {n}").raise_if_failed()
+    assert rec.depth_ok()
+    assert rec.names("[task] ") == [f"[task] {t.id}" for t in prog.tasks]
+    moved = [i.name for i in res.trace.intervals if i.track in ("from_slow", "to_slow")]
+    assert sorted(rec.names("[transfer] ")) == sorted(f"[transfer] {n}" for n in moved) and moved
+    assert all(not i.name.startswith("[") for i in res.trace.intervals)
+    plain = Engine(FakeBackend()).execute(prog).raise_if_failed()
+    assert plain.makespan_us == res.makespan_us

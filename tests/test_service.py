@@ -179,3 +179,14 @@ def test_train_tiny_llama3_through_the_daemon():
                         fetch=[f"loss_0_{r}" for r in range(R)])
             losses.append(sum(out["fetched"].values()))
         assert losses[-1] < losses[0] and 6.5 < losses[0] < 7.5
+
+
+def test_boot_probe_reports_host_bandwidth():
+    """The daemon measures what its own slab delivers (copy, bf16 add) at boot; a slab too small for the probe skips it."""
+    from dataflow_b200.service.hostbw import measure_host_bw
+    from dataflow_b200.service.store import HostSlab
+    slab = HostSlab(40 << 20)
+    got = measure_host_bw(slab, mib=16)
+    assert set(got) == {"host_copy_gbs", "host_bf16_add_gbs"} and all(v > 0 for v in got.values())
+    assert bytes(slab.bytes_view(0, 64)) == bytes(64)            # the probe leaves the slab zeroed
+    assert measure_host_bw(slab, mib=32) == {} and measure_host_bw(slab, mib=0) == {}
