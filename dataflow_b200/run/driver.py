@@ -196,17 +196,18 @@ class Trainer:
                 sizes_all = self.program.object_sizes()
                 pub = max((b for oid, b in sizes_all.items() if oid.startswith(("dW", "W", "dEmbed", "dHead", "Embed", "Head"))), default=0)
                 self.session.native.set_fast_tail(2 * (int(pub) + 4096))
-            # pool mode: "vmm" backs the pool page by page behind twice its size of virtual addresses (fragmentation then costs
-            # address room, not memory: no overflow allocations); "slab" is one allocation, which is what peers can map, so the
-            # sharded data-parallel lanes (whose kernels read peers' slabs) keep it.  "auto" picks by that rule.
-            mode = pool_mode or os.environ.get("DATAFLOW_POOL_MODE", "auto")
+            # pool mode: "slab" (default) is one allocation under an offset allocator; "vmm" backs the pool page by page behind
+            # twice its size of virtual addresses, so fragmentation costs address room instead of failing — at the price of
+            # driver calls whenever pages move.  At the 8B headline configuration (plan fills 98 % of the pool) that price was
+            # 25 k page moves and 5 s per step, so the mode is opt-in: it suits plans with slack and long-lived layouts.
+            mode = pool_mode or os.environ.get("DATAFLOW_POOL_MODE", "slab")
             if mode not in ("auto", "slab", "vmm"):
                 raise ValueError(f"pool mode {mode!r}: auto | slab | vmm")
             peers_map_slab = bool(zero_md and int(zero_md.get("world", 1)) > 1)
             if mode == "vmm" and peers_map_slab:
                 raise ValueError("pool mode 'vmm' cannot serve the sharded data-parallel lanes: their kernels read peers' slabs through "
                                  "one mapping of one allocation")
-            self.pool_mode = "vmm" if mode == "vmm" or (mode == "auto" and not peers_map_slab) else "slab"
+            self.pool_mode = "vmm" if mode == "vmm" else "slab"           # "auto" = the default
             try:
                 self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, self.pool_mode == "vmm")
             except RuntimeError as e:

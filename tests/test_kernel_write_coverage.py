@@ -148,7 +148,7 @@ def c_gelu_bwd(K, g, small):
 def c_ce_loss(K, g, small):
     r, v = (1, 64) if small else (301, 1000)
     logits = g.bf(r, v)
-    tg = g.ints(v, r).long()
+    tg = g.ints(v, r)
     if not small:
         tg[::7] = -1
     loss = K.ce_loss_fwd_bwd(logits, tg, total_rows=r)
@@ -177,7 +177,7 @@ def c_adamw(K, g, small):
 def c_adamw_split(K, g, small):
     n = 8 if small else 10007 * 8
     w, lo = g.bf(n), torch.zeros(n, device=g.dev, dtype=torch.int16)
-    m, v = torch.zeros(n, device=g.dev, dtype=F32), torch.zeros(n, device=g.dev, dtype=F32)
+    m, v = torch.zeros(n, device=g.dev, dtype=BF), torch.zeros(n, device=g.dev, dtype=BF)
     K.adamw_split_step(w, lo, g.bf(n), m, v, lr=1e-3, wd=0.1, step=3)
     return w, lo, m, v
 
@@ -271,7 +271,8 @@ def _rowdot(K, g, t, E, topk, d, ids, row_of, row_src, off, tile_e):
 
 def _grouped_mm(K, g, t, E, topk, d, ids, row_of, row_src, off, tile_e):
     xp = K.moe_dispatch(g.bf(t, d, scale=0.2), row_src)
-    return K.moe_grouped_mm(xp, g.bf(E, d, 2 * d, scale=0.1), tile_e)
+    # row tiles past the last expert's rows (tile_expert == -1) are nobody's: the op leaves them as they are
+    return K.moe_grouped_mm(xp, g.bf(E, d, 2 * d, scale=0.1), tile_e)[: int(off[-1])]
 
 
 def _grouped_wgrad(K, g, t, E, topk, d, ids, row_of, row_src, off, tile_e):
