@@ -282,12 +282,15 @@ def mla_sparse_attention(q, ckv, k_rope, wkv_b, sel, live, cfg, chunk: int = 256
     w_kb, w_vb = wb[..., :cfg.d_nope], wb[..., cfg.d_nope:]
     scale = (cfg.d_nope + cfg.d_rope) ** -0.5
 
+    # products in the storage dtype on a device (bf16 tensor cores, fp32 accumulation), softmax in fp32; fp32 inputs stay fp32
+    cd = q.dtype if q.is_cuda else torch.float32
+
     def part(qc, selc, livec, ckv_, kr_, w_kb_, w_vb_):
-        q_abs = torch.einsum("ihd,chd->ihc", qc[..., :cfg.d_nope].float(), w_kb_.float())          # (c, h, kv_lora)
-        kc, kr = ckv_[selc].float(), kr_[selc].float()                                               # (c, kk, kv_lora / rope)
-        s = (torch.einsum("ihc,ikc->ihk", q_abs, kc) + torch.einsum("ihr,ikr->ihk", qc[..., cfg.d_nope:].float(), kr)) * scale
+        q_abs = torch.einsum("ihd,chd->ihc", qc[..., :cfg.d_nope].to(cd), w_kb_.to(cd))            # (c, h, kv_lora)
+        kc, kr = ckv_[selc].to(cd), kr_[selc].to(cd)                                                 # (c, kk, kv_lora / rope)
+        s = (torch.einsum("ihc,ikc->ihk", q_abs, kc) + torch.einsum("ihr,ikr->ihk", qc[..., cfg.d_nope:].to(cd), kr)).float() * scale
         p = torch.softmax(s.masked_fill(~livec[:, None, :], float("-inf")), dim=-1)
-        o = torch.einsum("ihc,chd->ihd", torch.einsum("ihk,ikc->ihc", p, kc), w_vb_.float())
+        o = torch.einsum("ihc,chd->ihd", torch.einsum("ihk,ikc->ihc", p.to(cd), kc), w_vb_.to(cd))
         return o.to(qc.dtype), p.detach().sum(1)
 
     outs, targets = [], []

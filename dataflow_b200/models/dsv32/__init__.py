@@ -31,6 +31,12 @@ PRESETS = {
                        **{**BASE, "index_heads": 64, "index_dim": 128, "index_topk": 2048}),
     # the 12-layer cut used as a multi-GPU benchmark configuration: 3 dense layers, 256 routed experts (top-8) + 1 shared,
     # indexer top-2048 at 16k tokens per sequence, experts split over the ranks (``ep`` set by ``--parallel ep``)
+    # long-context exercise of the sparse lane on one GPU: full-size indexer (64 heads of 128, top-2048) and latent widths, a
+    # narrow model around them
+    "dsv32_long16k": dict(name="dsv32_long16k", n_layers=4, n_dense=1, d_model=2048, n_heads=32, q_lora=768, kv_lora=512, d_nope=128, d_rope=64,
+                          d_v=128, d_ff=8192, n_experts=16, top_k=4, d_ff_expert=1024, n_group=4, topk_group=2, routed_scaling=2.5,
+                          vocab_size=32000, seq_len=16384, batch=1, grad_accum_rounds=1, dtype_policy="bf16",
+                          **{**BASE, "index_heads": 64, "index_dim": 128, "index_topk": 2048}),
     "dsv32_12l": dict(name="dsv32_12l", n_layers=12, n_dense=3, d_model=7168, n_heads=128, q_lora=1536, kv_lora=512, d_nope=128, d_rope=64,
                       d_v=128, d_ff=18432, n_experts=256, top_k=8, d_ff_expert=2048, n_group=8, topk_group=4, routed_scaling=2.5,
                       vocab_size=129280, seq_len=16384, batch=1, grad_accum_rounds=8, dtype_policy="bf16_split_master",

@@ -116,3 +116,17 @@ def test_eval_checkpoint_reads_solo_and_sharded_checkpoints_alike(tmp_path, caps
         got[name] = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert got["solo"]["tokens"] == got["fsdp"]["tokens"] > 0 and got["solo"]["checkpoint"] == 2
     assert got["fsdp"]["loss"] == pytest.approx(got["solo"]["loss"], rel=2e-3) and 1.0 < got["solo"]["loss"] < 8.0
+
+
+def test_planner_quality_gate_quick_corpus_holds_its_baseline(capsys):
+    """The quick corpus of the planner quality gate (12 scenarios of the workload library, every registered policy): no plan
+    over its cap, and the training entry's planner (the better of Lookahead and PressureFit) is no worse than recorded."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tools", "bench", "planner_quality_gate.py")
+    spec = importlib.util.spec_from_file_location("planner_quality_gate", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.main(["--quick", "--check"]) == 0
+    out = capsys.readouterr().out
+    assert "12 scenarios" in out and "REGRESSION" not in out

@@ -258,3 +258,28 @@ def test_dsa_gathered_forms_equal_the_masked_forms():
     assert torch.allclose(a, b, atol=1e-6)
     at = F.dsa_scores_at(x, cq, w, c, pos, sel)
     assert torch.allclose(at[live], dense.gather(1, sel)[live], atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_dsv32_trains_a_step_at_sequence_16384_on_one_gpu():
+    """Long context on the sparse lane: full-size indexer (64 heads of 128, top-2048) at 16 384 tokens.  The index scores run on
+    the tensor cores, the selection in the radix kernel, attention over the gathered keys in the latent form; nothing of size
+    (n, n) is ever allocated (the dense forms would need 68 GB of probabilities per layer)."""
+    import dataclasses
+    import time
+    from dataflow_b200.run.driver import Trainer, synthetic_rounds
+    fam = resolve_family("dsv32")
+    cfg = dataclasses.replace(fam.presets["dsv32_long16k"](), n_layers=2)
+    torch.cuda.reset_peak_memory_stats()
+    tr = Trainer("dsv32", cfg, budget_gib=40.0, device=0, hyper={"lr": 1e-3, "weight_decay": 0.0}, seed=1)
+    losses = []
+    t0 = time.perf_counter()
+    for s in range(2):
+        losses.append(tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, cfg.vocab_size, 5, s)))
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / 2
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    tr.close()
+    print(f"dsv32 long context: {dt:.2f} s per step of {cfg.seq_len} tokens, framework allocator peak {peak:.1f} GiB, losses {losses}")
+    assert all(l == l and 0 < l < 20 for l in losses)
+    assert peak < 30.0          # far below what one dense (heads, n, n) tensor would take
