@@ -30,6 +30,7 @@ from dataclasses import dataclass
 from typing import Any
 
 from ..ops.eager import MOE_TILE_ROWS
+from .group_abi import GroupCollectives
 
 CTRL_BYTES = 1 << 12
 
@@ -49,7 +50,7 @@ class EpPlan:
     dropped: Any = None      # () int32 number of slots of this rank's experts that did not fit
 
 
-class EpGroup:
+class EpGroup(GroupCollectives):
     def __init__(self, rank: int, world: int, device: int | None, *, tokens: int, d_model: int, n_experts: int, top_k: int,
                  capacity_factor: float = 2.0, lane: str | None = None, timeout_s: float = 30.0, pg=None):
         """``pg``: the ``torch.distributed`` process group of the members when they are a subset of the job (a dp x ep mesh);

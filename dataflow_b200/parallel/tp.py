@@ -16,11 +16,12 @@ from __future__ import annotations
 
 import os
 from typing import Any
+from .group_abi import GroupCollectives
 
 CTRL_BYTES = 1 << 18          # rendezvous words, handed out per operand shape (see ``_words``)
 
 
-class TpGroup:
+class TpGroup(GroupCollectives):
     def __init__(self, rank: int, world: int, device: int | None, *, max_rows: int, max_k: int, max_n: int,
                  lane: str | None = None, timeout_s: float = 30.0, pg=None):
         """``max_rows``: rows per rank (the sequence shard); ``max_k`` / ``max_n``: widest gathered operand and widest
@@ -112,10 +113,13 @@ class TpGroup:
         from ..ops import native
         return native().tensor_from_ptr(self.base + self.off_gathered, [rows * self.world, k], "bf16", self.device)
 
-    def all_gather(self, x):
-        """(rows, k) -> (world * rows, k), no GEMM attached (operands of weight gradients in the backward)."""
+    def all_gather(self, x, full=None):
+        """(rows, k) -> (world * rows, k), no GEMM attached (operands of weight gradients in the backward).  With ``full``
+        given this is the group ABI's form: every rank's ``x`` lands in ``full``, rank order."""
         import torch
         import torch.distributed as dist
+        if full is not None:
+            return GroupCollectives.all_gather(self, x, full)
         out = torch.empty(x.shape[0] * self.world, x.shape[1], dtype=x.dtype, device=x.device)
         if self.world == 1:
             out.copy_(x)

@@ -26,6 +26,7 @@ from typing import Any, Mapping
 from ..blocks.base_blocks import _Base
 from ..blocks.layouts import Field, PackedLayout
 from ..blocks.optim import lr_at
+from .group_abi import GroupCollectives
 
 
 class CommTimeout(RuntimeError):
@@ -83,7 +84,7 @@ class _Slot:
     calls: int = 0
 
 
-class DpGroup:
+class DpGroup(GroupCollectives):
     """One data-parallel group as seen by this rank."""
 
     SLOTS = 512

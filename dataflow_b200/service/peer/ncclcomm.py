@@ -80,6 +80,15 @@ class NcclComm:
             self.lib.check(self.lib.lib.ncclBroadcast(t.data_ptr(), t.data_ptr(), t.numel(), self._dt(t), root, self.comm, s), "ncclBroadcast")
         return t
 
+    def reduce(self, t, root: int = 0, op: str = "sum"):
+        """Sum lands in ``root``'s tensor; the other ranks' tensors keep their values (reduced into a scratch copy there)."""
+        self.guard()
+        dst = t if self.rank == root else t.clone()
+        with self._edges() as s:
+            self.lib.check(self.lib.lib.ncclReduce(t.data_ptr(), dst.data_ptr(), t.numel(), self._dt(t), OPS[op], root,
+                                                   self.comm, s), "ncclReduce")
+        return t
+
     def send(self, t, peer: int):
         """Point-to-point (pipeline stages): stays on NCCL, overlapped on the group's stream."""
         self.guard()

@@ -246,3 +246,41 @@ def test_replicas_of_an_expert_parallel_group_match_one_process(preset, tmp_path
     assert h[0]["W_embed"] == h[1]["W_embed"] and h[0]["O_head"] == h[1]["O_head"]
     moe_layers = [k for k in h[0] if k.startswith("W_") and h[0][k] != h[1][k]]
     assert moe_layers and all(k[2:].isdigit() for k in moe_layers)
+
+
+def _abi_worker(rank, world, port, out):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dataflow_b200.parallel.zero import DpGroup
+    g = DpGroup(rank, world, None)
+    t = torch.full((4,), float(rank + 1))
+    g.all_reduce(t)
+    b = torch.full((3,), float(rank))
+    g.broadcast(b, root=1)
+    r = torch.full((2,), float(rank + 1))
+    g.reduce(r, root=0)
+    full = torch.zeros(world * 2)
+    g.all_gather(torch.full((2,), float(rank)), full)
+    rs = torch.zeros(2)
+    g.reduce_scatter(torch.arange(world * 2, dtype=torch.float32) * (rank + 1), rs)
+    out[rank] = (t.tolist(), b.tolist(), r.tolist(), full.tolist(), rs.tolist())
+    dist.destroy_process_group()
+
+
+def test_group_objects_answer_the_whole_collective_abi():
+    """all_reduce / broadcast / reduce / all_gather / reduce_scatter through a group object on two CPU ranks: the list an
+    executable may rely on under every launcher (reduce leaves non-root tensors untouched)."""
+    import torch.multiprocessing as mp
+    world = 2
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_abi_worker, args=(world, 29733, out), nprocs=world, join=True)
+        got = dict(out)
+    assert got[0][0] == got[1][0] == [3.0] * 4
+    assert got[0][1] == got[1][1] == [1.0] * 3
+    assert got[0][2] == [3.0, 3.0] and got[1][2] == [2.0, 2.0]
+    assert got[0][3] == got[1][3] == [0.0, 0.0, 1.0, 1.0]
+    assert got[0][4] == [0.0, 3.0] and got[1][4] == [6.0, 9.0]
