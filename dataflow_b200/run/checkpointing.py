@@ -4,8 +4,9 @@ lowered programs (``programs/rank{i}.json``) and the checkpoint record, which is
 ``save_checkpoint(trainer, ...)`` works for a solo trainer and, when ``torch.distributed`` is initialised, for
 every rank of a job calling it at the same step: each rank snapshots its own persistent objects, rank 0 gathers
 the slice hashes and writes the record.  Sharded weights (``Ws_*``) are recorded as byte ranges of the logical
-``W_*`` object, so a checkpoint taken at one world size restores its weights at another; sharded optimizer state
-is recorded per source (``O_*@rank``) and restores at the same world size.  ``load_checkpoint`` reads the record,
+``W_*`` object, so a checkpoint taken at one world size restores its weights at another; sharded optimizer state is
+recorded as spans of logical planes (``O_3.master``, ``O_3.m``, ``O_3.v``: one plane per state field of the whole
+parameter), so it restores at another world size too.  ``load_checkpoint`` reads the record,
 verifies every slice hash, fills the host store and drops device-resident copies; the returned payload carries
 the losses and the data cursor, so a resumed curve continues exactly.
 Role parity: reference ``src/dataflow_training/run/checkpointing.py:25-420``.
@@ -121,9 +122,34 @@ class TrainerSource:
                 if n:
                     out.append(SourceSlice(oid, 0, n, logical, lo))
             elif self.world > 1 and oid.startswith("O_") and (self.t.zero or {}).get("stage"):
-                out.append(SourceSlice(oid, 0, size, f"{oid}@{self.rank}", 0))
+                out += self._optimizer_planes(oid, size, full)
             else:
                 out.append(SourceSlice(oid, 0, size, oid, 0))
+        return out
+
+    def _optimizer_planes(self, oid: str, size: int, full: Mapping[str, int]) -> list[SourceSlice]:
+        """A rank's sharded optimizer state as spans of LOGICAL planes: ``O_3.m`` is the first-moment plane of the whole
+        ``W_3``, and this rank holds the elements of its slice of the parameter.  Recorded this way the state restores
+        at any world size (every rank of the new job reads the spans that cover its new slice).  State that does not
+        follow a plane layout this function knows is recorded per rank, as before."""
+        from ..parallel.zero import slice_bytes, slice_range, split_opt_layout, zero_opt_layout
+        name = oid[2:]
+        sizes = self.persistent()
+        total = int(full.get("W_" + name) or sizes.get("W_" + name) or 0)
+        if not total:
+            return [SourceSlice(oid, 0, size, f"{oid}@{self.rank}", 0)]
+        per = slice_bytes(total, self.world)
+        regather = bool((self.t.zero or {}).get("regather"))
+        lay = split_opt_layout(per) if (regather and name.isdigit()) else zero_opt_layout(per)
+        if lay.size_bytes != size:
+            return [SourceSlice(oid, 0, size, f"{oid}@{self.rank}", 0)]
+        lo, ln = slice_range(total, self.world, self.rank)           # bytes of the bf16 parameter
+        offs = lay.offsets()
+        out = []
+        for f in lay.fields:
+            eb = f.nbytes // max(per // 2, 1)                         # bytes per element of this plane
+            if ln:
+                out.append(SourceSlice(oid, offs[f.name], (ln // 2) * eb, f"{oid}.{f.name}", (lo // 2) * eb))
         return out
 
     def write_slices(self, redundancy: int | None = None) -> list[SourceSlice]:
@@ -233,10 +259,10 @@ def load_checkpoint(trainer, sdir: str, only_prefixes: tuple[str, ...] | None = 
     import ctypes
     rec = read_record(sdir)
     src = TrainerSource(trainer)
-    want: dict[str, SourceSlice] = {s.object_id: s for s in src.slices()
-                                    if only_prefixes is None or s.object_id.startswith(tuple(only_prefixes))}
+    want = [s for s in src.slices() if only_prefixes is None or s.object_id.startswith(tuple(only_prefixes))]
     store = trainer.store
-    for oid, s in want.items():
+    for s in want:                                   # an object may be several spans (the planes of sharded optimizer state)
+        oid = s.object_id
         logical = s.logical_id
         if logical not in rec["logical_objects"]:
             raise KeyError(f"checkpoint {sdir} has no object {logical!r} (needed for {oid!r} of rank {src.rank})")
