@@ -22,6 +22,28 @@ def profiler_command(prefix: str, argv: list[str]) -> list[str]:
     return ["env", "DATAFLOW_NVTX=1", f"DATAFLOW_TRACE_PREFIX={prefix}", *argv]
 
 
+TIMELINE_TRACE = "cuda,nvtx,osrt,cublas"
+
+
+def timeline_profiler(host: HostSpec | None = None) -> str | None:
+    """Path of the timeline profiler on this machine (``nsys`` on PATH, or what ``DATAFLOW_NSYS`` names), else None."""
+    import shutil
+    name = os.environ.get("DATAFLOW_NSYS") or getattr(host, "nsys", None) or "nsys"
+    return shutil.which(name)
+
+
+def timeline_command(profiler: str, out_path: str) -> list[str]:
+    """The wrap that records one daemon's timeline between the profiler API's start and stop calls (the conductor sends
+    ``profiler_control`` to every daemon around the chosen steps, so the report holds those steps only and the NVTX
+    ranges of their tasks and transfers).  ``DATAFLOW_NSYS_EXTRA`` appends capture options without touching this line."""
+    argv = [profiler, "profile", f"--trace={TIMELINE_TRACE}", "--capture-range=cudaProfilerApi", "--capture-range-end=stop",
+            "-o", out_path, "--force-overwrite", "true"]
+    extra = os.environ.get("DATAFLOW_NSYS_EXTRA")
+    if extra:
+        argv[-4:-4] = extra.split()
+    return argv
+
+
 def daemon_paths(member: Member, root: str = "/tmp", tag: str | None = None) -> dict[str, str]:
     """Runtime files of one daemon.  ``tag`` tells daemons apart that share a host and a device (CPU ranks of one box)."""
     stem = f"{root}/dataflowd.{member.host}.{member.device}" + (f".{tag}" if tag else "")
@@ -31,9 +53,10 @@ def daemon_paths(member: Member, root: str = "/tmp", tag: str | None = None) -> 
 def launch(host: HostSpec, member: Member, *, backing_gib: float | str | None = None, kernels: str | None = None,
            fake: bool = False, peer_name: str | None = None, peer_listen: str | None = None, root: str = "/tmp",
            env: Mapping[str, str] | None = None, wait_s: float = 60.0, tag: str | None = None,
-           device: str | None = None) -> dict[str, str]:
+           device: str | None = None, wrap: list[str] | None = None) -> dict[str, str]:
     """Start one daemon for ``member`` and wait until its socket answers.  ``device``: what the daemon is told to run on when
-    that is not the member's CUDA ordinal (``"cpu"``: the host backend)."""
+    that is not the member's CUDA ordinal (``"cpu"``: the host backend).  ``wrap``: a command prefix that runs INSIDE the
+    detached session, around the daemon (``timeline_command(...)``), so a profiler's helpers never hold the launcher open."""
     paths = daemon_paths(member, root, tag)
     repo = host.repo or REPO_ROOT
     py = sys.executable if host.local else host.python
@@ -41,6 +64,7 @@ def launch(host: HostSpec, member: Member, *, backing_gib: float | str | None = 
             "--cwd", repo, "--"]
     for k, v in {**NCCL_DEFAULT_ENV, **dict(env or {})}.items():
         argv += ["env", f"{k}={v}"] if argv[-1] == "--" else [f"{k}={v}"]
+    argv += list(wrap or [])
     argv += [py, os.path.join(repo, "tools/train/dataflowd.py"), "start", "--foreground", "--socket", paths["socket"],
              "--backing-gib", str(backing_gib if backing_gib is not None else host.backing_gib)]
     argv += ["--fake"] if fake else ["--device", str(device if device is not None else member.device)]

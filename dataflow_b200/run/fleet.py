@@ -81,6 +81,16 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
     rspec = canonical_spec(family, cfg, hyper, seed=spec.seed)
     if world > 1:
         rspec["dp"] = {"mode": "co", "group": "dp"}
+    # profile window (--prof-dir with --profile-start-before-step / --profile-stop-after-step): NVTX ranges on in every daemon,
+    # each wrapped in the timeline profiler when this machine has one; without one the window still switches the ranges
+    window = None
+    profiler = None
+    if getattr(spec, "prof_dir", None) and int(getattr(spec, "profile_start_before_step", 0) or 0) > 0:
+        window = (int(spec.profile_start_before_step), int(spec.profile_stop_after_step or spec.profile_start_before_step))
+        os.makedirs(spec.prof_dir, exist_ok=True)
+        profiler = daemons.timeline_profiler(host)
+        log(f"[fleet] profile window steps {window[0]}..{window[1]}: " + (f"timelines by {profiler}" if profiler else
+            "no timeline profiler on this machine; NVTX ranges only"))
     states: list[RankState] = []
     paths = []
     clients: list[Any] = []
@@ -88,9 +98,14 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
     try:
         for r in range(world):
             # every daemon gets its own runtime files: several ranks share a host (and, on CPU, a "device")
+            wrap = None
+            if window is not None and profiler is not None:
+                # the capture window is opened and closed through the daemons' profiler-control verb (below)
+                wrap = daemons.timeline_command(profiler, os.path.join(spec.prof_dir, f"timeline_rank{r}"))
             p = daemons.launch(host, members[r], backing_gib=spec.backing_budget_gib or store_gib, kernels=spec.kernels,
                                peer_name=names[r], peer_listen=f"127.0.0.1:{ports[r]}", root=root, tag=f"r{r}",
-                               device="cpu" if cpu else str(members[r].device))
+                               device="cpu" if cpu else str(members[r].device), wrap=wrap,
+                               env={"DATAFLOW_NVTX": "1"} if window is not None else None)
             paths.append(p)
             clients.append(EngineClient(p["socket"], f"fleet-rank{r}", timeout=600.0))
             log(f"[fleet] rank {r} up ({'cpu' if cpu else 'cuda:' + str(members[r].device)}, socket {p['socket']})")
@@ -121,6 +136,9 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
                 if packed is None:
                     log(f"data source exhausted after {s} steps")
                     break
+                if window is not None and s + 1 == window[0]:
+                    for c in clients:
+                        c.profiler_control("start")
                 t0 = time.perf_counter()
                 jobs = []
                 for st in states:
@@ -138,6 +156,9 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
                 res.losses.append(loss)
                 res.step_wall_s.append(dt)
                 log(f"step {s + 1:5d}  loss {loss:.4f}  {packed.content_tokens / dt:,.0f} tok/s")
+                if window is not None and s + 1 == window[1]:
+                    for c in clients:
+                        c.profiler_control("stop")
         finally:
             if hasattr(stepper, "close"):
                 stepper.close()

@@ -46,6 +46,22 @@ def install(server) -> None:
                                           "host_bw_gbs": dict(getattr(server, "host_bw", {}))}
     H["session_status"] = lambda req, p: {"vendor_allocs": server._session.vendor_allocs()
                                           if getattr(server, "_session", None) else 0}
+    def profiler_control(req, p):
+        """Open or close the capture window: NVTX ranges of tasks and transfers on / off, and the CUDA profiler API's start /
+        stop (what a timeline profiler started with ``--capture-range=cudaProfilerApi`` waits for)."""
+        from ..runtime import set_nvtx
+        on = req.get("action", "start") in ("start", "on", True)
+        set_nvtx(on)
+        api = False
+        if server.config.device is not None and not server.config.fake:
+            try:
+                import torch
+                (torch.cuda.profiler.start if on else torch.cuda.profiler.stop)()
+                api = True
+            except Exception:       # noqa: BLE001
+                api = False
+        return {"nvtx": on, "profiler_api": api}
+    H["profiler_control"] = profiler_control
     H["subscribe_events"] = lambda req, p: {"events": server.state.events_since(int(req.get("since", 0)))}
     H["run_events"] = H["subscribe_events"]
     H["list_resolvers"] = lambda req, p: {"resolvers": list_resolvers()}

@@ -86,12 +86,6 @@ def install(server) -> None:
         want = float(sum(range(1, len(g.members) + 1)))
         return {"ok": bool(np.all(y == want)), "seconds": dt, "bytes": int(x.nbytes), "expected": want, "got": float(y[0])}
 
-    def profiler_control(req, payload):
-        from ..runtime import set_nvtx
-        on = req.get("action", "start") in ("start", "on", True)
-        set_nvtx(on)
-        return {"nvtx": on}
-
     def debug_sever(req, payload):
         need_nm()
         nm.debug_sever(req["peer"])
@@ -101,4 +95,4 @@ def install(server) -> None:
               "transfer_status": transfer_status, "create_peer_group": create_peer_group,
               "destroy_peer_group": destroy_peer_group, "list_peer_groups": list_peer_groups, "list_peers": list_peers,
               "peer_status": peer_status, "p2p_bench": p2p_bench, "coll_bench": coll_bench,
-              "profiler_control": profiler_control, "debug_sever": debug_sever})
+              "debug_sever": debug_sever})

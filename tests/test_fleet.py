@@ -44,3 +44,20 @@ def test_fleet_mode_refuses_sharded_modes_by_name(tmp_path):
            "--opt-shard", "fsdp", "--launcher", "fleet", "--out", str(tmp_path / "x.json")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(tmp_path), env=dict(os.environ, PYTHONPATH=ROOT))
     assert r.returncode != 0 and "fleet mode runs replicas" in (r.stdout + r.stderr)
+
+
+def test_timeline_wrap_and_profile_window(tmp_path):
+    """The daemon launcher's profiler wrap is the capture-by-API command line, and a fleet run with a profile window opens and
+    closes it through every daemon's ``profiler_control`` (no timeline profiler on this machine: NVTX ranges only)."""
+    from dataflow_b200.distributed import daemons
+    cmd = daemons.timeline_command("/opt/nsys/bin/nsys", "/tmp/out/timeline_rank0")
+    assert cmd[:2] == ["/opt/nsys/bin/nsys", "profile"] and "--capture-range=cudaProfilerApi" in cmd and "--capture-range-end=stop" in cmd
+    assert cmd[cmd.index("-o") + 1] == "/tmp/out/timeline_rank0"
+    from dataflow_b200.run.conductor import RunSpec
+    from dataflow_b200.run.fleet import run_fleet
+    lines = []
+    spec = RunSpec(preset="llama3:tiny", steps=3, device=None, world=2, parallel="co", launcher="fleet", overrides={"dtype_policy": "fp32"},
+                   prof_dir=str(tmp_path / "prof"), profile_start_before_step=2, profile_stop_after_step=2)
+    res = run_fleet(spec, log=lines.append)
+    assert len(res.losses) == 3
+    assert any("profile window steps 2..2" in l for l in lines)
