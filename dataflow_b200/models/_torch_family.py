@@ -16,6 +16,8 @@ block functions restate.
 """
 from __future__ import annotations
 
+from ..blocks.init_policy import set_init_layer
+
 import dataclasses
 from dataclasses import dataclass, field
 from typing import Any, Callable, Mapping, Sequence
@@ -491,6 +493,7 @@ def initial_values(spec: TorchFamilySpec, program, cfg, views_of, seed: int = 0,
     for oid in ["W_embed"] + [f"W_{i}" for i in range(d.n_layers)] + ["W_head"]:
         if oid not in ids:
             continue
+        set_init_layer(oid)
         wl = lay.layout_of(oid)
         wv = views_of(oid, wl)
         for f in wl.fields:

@@ -7,6 +7,8 @@ runs end to end on the host backend.  Family parity: reference
 """
 from __future__ import annotations
 
+from ...blocks.init_policy import set_init_layer
+
 from dataclasses import dataclass
 from typing import Any, Mapping
 
@@ -188,6 +190,7 @@ def initial_values(program: Program, cfg: ShapedGpt2Config, views_of, seed: int 
     for oid in ["W_embed"] + [f"W_{i}" for i in range(d.n_layers)] + ["W_head"]:
         if oid not in ids:
             continue
+        set_init_layer(oid)
         wl = lay.layout_of(oid)
         wv = views_of(oid, wl)
         for f in wl.fields:

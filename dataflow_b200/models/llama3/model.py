@@ -9,6 +9,8 @@ tcgen05 GEMMs instead of seven.  Saved context per token matches the reference's
 """
 from __future__ import annotations
 
+from ...blocks.init_policy import set_init_layer
+
 from dataclasses import dataclass, field, replace
 from typing import Any, Mapping
 
@@ -349,6 +351,9 @@ def lower_llama3(cfg: ShapedLlama3Config, recompute_levels: Mapping[int, int] | 
 def init_field(t, f: Field, gen, n_layers: int, std: float = 0.02) -> None:
     """Fill tensor ``t`` (any dtype) for field ``f`` from the seeded CPU generator."""
     import torch
+    from ...blocks.init_policy import fill_by_policy
+    if fill_by_policy(t, f.name, gen):            # a run-level init policy (blocks/init_policy.py) names a rule for this field
+        return
     if f.init == "ones":
         t.fill_(1.0)
     elif f.init == "zeros":
@@ -377,6 +382,7 @@ def initial_values(program: Program, cfg: ShapedLlama3Config, views_of, seed: in
     for oid in order:
         if oid not in ids:
             continue
+        set_init_layer(oid)
         wl = lay.layout_of(oid)
         wv = views_of(oid, wl)
         for f in wl.fields:

@@ -4,7 +4,7 @@
 //     query may see (same sequence, j <= i); -inf elsewhere.  One CTA per (128 queries, 128 keys) tile.  Roles: warps 0-7 =
 //     epilogue (row = TMEM lane, warps 0-3 take columns 0-63, warps 4-7 columns 64-127), warp 8 = TMA producer, warp 9 = MMA
 //     issuer and TMEM owner.  The key tile stays in shared memory; the heads stream through a ring of query tiles:
-//         S_h = Q_h K^T          tcgen05.mma, both operands K-major, accumulator in tensor memory (two buffers)
+//         S_h = Q_h K^T          tcgen05.mma, both operands K-major, accumulator in tensor memory (four buffers)
 //         acc += w_h * relu(S_h) epilogue threads, tcgen05.ld of their own row, head weights staged in shared memory
 //     so the (heads, queries, keys) intermediate of the eager form never exists.  Tiles no query of which sees a key are
 //     filled with -inf without touching the tensor pipe.  Every wait is a bounded mbarrier wait; on a time-out the CTA
@@ -28,10 +28,11 @@ constexpr int BM = 128, BN = 128, UK = 16;
 constexpr int CH = 128 * 128;                    // one 128-row x 64-element (128-byte) swizzled chunk: 16 KiB
 constexpr int ST = 3;                            // query-tile ring stages
 constexpr int EPI_WARPS = 8, THREADS = (EPI_WARPS + 2) * 32;
-constexpr int TMEM_COLS = 256;
+constexpr int NB = 4;                            // accumulator buffers in tensor memory: the issuer runs up to three heads ahead
+constexpr int TMEM_COLS = NB * BN;
 
 struct Bars {
-  uint64_t k_full, q_full[ST], q_empty[ST], s_full[2], s_empty[2];
+  uint64_t k_full, q_full[ST], q_empty[ST], s_full[NB], s_empty[NB];
   uint32_t tmem_base;
   int abort;
 };
@@ -82,7 +83,7 @@ index_scores_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (threadIdx.x == 0) {
     ptx::mbar_init(&bar->k_full, 1);
     for (int s = 0; s < ST; ++s) { ptx::mbar_init(&bar->q_full[s], 1); ptx::mbar_init(&bar->q_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { ptx::mbar_init(&bar->s_full[b], 1); ptx::mbar_init(&bar->s_empty[b], EPI_WARPS); }
+    for (int b = 0; b < NB; ++b) { ptx::mbar_init(&bar->s_full[b], 1); ptx::mbar_init(&bar->s_empty[b], EPI_WARPS); }
     bar->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -124,8 +125,8 @@ index_scores_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = ptx::mbar_wait(&bar->k_full, 0, abort_flag);
       if (!ok) { bar->abort = 1; atomicExch(p.err, 82); }
       for (int h = 0; h < p.H && ok; ++h) {
-        const int s = h % ST, b = h & 1;
-        if (!ptx::mbar_wait(&bar->q_full[s], (h / ST) & 1, abort_flag) || !ptx::mbar_wait(&bar->s_empty[b], ((h >> 1) & 1) ^ 1, abort_flag)) {
+        const int s = h % ST, b = h % NB;
+        if (!ptx::mbar_wait(&bar->q_full[s], (h / ST) & 1, abort_flag) || !ptx::mbar_wait(&bar->s_empty[b], ((h / NB) & 1) ^ 1, abort_flag)) {
           bar->abort = 1; atomicExch(p.err, 83); ok = false; break;
         }
         ptx::tc_fence_after();
@@ -151,8 +152,8 @@ index_scores_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int c = 0; c < 64; ++c) acc[c] = 0.f;
     bool ok = true;
     for (int h = 0; h < p.H; ++h) {
-      const int b = h & 1;
-      if (!ptx::mbar_wait(&bar->s_full[b], (h >> 1) & 1, abort_flag)) { bar->abort = 1; atomicExch(p.err, 84); ok = false; break; }
+      const int b = h % NB;
+      if (!ptx::mbar_wait(&bar->s_full[b], (h / NB) & 1, abort_flag)) { bar->abort = 1; atomicExch(p.err, 84); ok = false; break; }
       ptx::tc_fence_after();
       const float w = s_w[h * BM + rl];
       uint32_t v[64];

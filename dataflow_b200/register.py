@@ -16,8 +16,8 @@ def canonical_spec(family: str, cfg, hyper: Mapping[str, Any] | None = None, see
 
 
 class FamilyInitExecutable:
-    def __init__(self, fam, cfg, seed: int):
-        self.fam, self.cfg, self.seed = fam, cfg, seed
+    def __init__(self, fam, cfg, seed: int, init_policy=None):
+        self.fam, self.cfg, self.seed, self.init_policy = fam, cfg, seed, init_policy
 
     def launch(self, ctx) -> None:
         bufs = {b.object_id: b for b in ctx.inputs}
@@ -27,7 +27,9 @@ class FamilyInitExecutable:
             return layout.views(bufs[oid], None)
         import dataclasses
         keep = tuple(o for o in program.initial_objects if o.id in bufs)
-        self.fam.initial_values(dataclasses.replace(program, initial_objects=keep), self.cfg, views_of, self.seed)
+        from .blocks.init_policy import init_scope
+        with init_scope(self.init_policy):           # the resolver spec's hyper["init_policy"]: rules by field name and layer
+            self.fam.initial_values(dataclasses.replace(program, initial_objects=keep), self.cfg, views_of, self.seed)
 
 
 def build_model_family_resolver(spec: Mapping[str, Any], env):
@@ -55,7 +57,7 @@ def build_model_family_resolver(spec: Mapping[str, Any], env):
         replicate_gradients(SimpleNamespace(resolver=inner, layouts=layouts), dp.get("group", "dp"))
     elif dp:
         raise ValueError(f"fleet mode runs replicas (dp mode 'co'); {dp.get('mode')!r} needs the in-process launcher")
-    init = FamilyInitExecutable(fam, cfg, int(spec.get("seed", 0)))
+    init = FamilyInitExecutable(fam, cfg, int(spec.get("seed", 0)), (spec.get("hyper") or {}).get("init_policy"))
 
     def resolver(task):
         if task.compute_block_key == "family_init":

@@ -258,15 +258,19 @@ class Trainer:
         return torch_view(self.store.buffer(oid), shape, dtype, 0, None)
 
     def init_model(self, seed: int = 0) -> None:
-        if self.zero:
-            from ..parallel.zero import zero_initial_values
-            zero_initial_values(self.fam, self.cfg, self.program, self.store, seed, self.layouts,
-                                int(self.zero["rank"]), int(self.zero["world"]), int(self.zero["stage"]))
-        else:
-            # a tensor-parallel family cuts the same seeded full model differently on every rank
-            sliced = next((self.groups[k] for k in ("tp", "ep") if k in self.groups), None)
-            kw = {"rank": sliced.rank} if sliced is not None else {}
-            self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts, **kw)
+        """Seeded initial parameters and optimizer state.  ``hyper["init_policy"]`` (``blocks/init_policy.py``: rules by field name
+        and layer, as data) overrides the fills the layouts name."""
+        from ..blocks.init_policy import init_scope
+        with init_scope(self.hyper.get("init_policy")):
+            if self.zero:
+                from ..parallel.zero import zero_initial_values
+                zero_initial_values(self.fam, self.cfg, self.program, self.store, seed, self.layouts,
+                                    int(self.zero["rank"]), int(self.zero["world"]), int(self.zero["stage"]))
+            else:
+                # a tensor-parallel family cuts the same seeded full model differently on every rank
+                sliced = next((self.groups[k] for k in ("tp", "ep") if k in self.groups), None)
+                kw = {"rank": sliced.rank} if sliced is not None else {}
+                self.fam.initial_values(self.program, self.cfg, self.views_of, seed, layouts=self.layouts, **kw)
 
     # -- data
     def put_round(self, r: int, tokens, targets) -> int:
