@@ -196,6 +196,7 @@ def bench_ours(a) -> dict:
         "plan": {"predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
                  "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
                  "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows, "pool": _pool_line(tr),
+                 "static_placement": tr.placement is not None,
                  "placement_escapes": res.placement_escapes, "pressure_evictions": res.pressure_evictions,
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},

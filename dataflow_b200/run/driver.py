@@ -153,6 +153,7 @@ class Trainer:
         budget = None if budget_gib is None else int(budget_gib * GiB)
         measured = None
         t0 = time.time()
+        planned_by_caller = planned
         if planned is None:
             if profile and device is not None:
                 from .profiling import profile_program
@@ -226,12 +227,7 @@ class Trainer:
         if static_placement is None:
             static_placement = os.environ.get("DATAFLOW_STATIC_PLACEMENT") == "1"
         if static_placement and device is not None:
-            from ..runtime.placement import PlacementError, plan_placement
-            try:
-                self.placement = plan_placement(self.program, int(self.session.native.fast_slab()[1]))
-            except PlacementError as e:
-                if verbose:
-                    print(f"static placement not used: {e}")
+            self._fit_static_extent(cfg, budget, recompute, measured, leeway_bytes, lower_kwargs, replan=planned_by_caller is None)
         self.zero = (self.program.metadata or {}).get("zero")
         if self.zero and int(self.zero.get("world", 1)) > 1 and hasattr(cfg, "policy"):
             # the sharded lanes cut the packed objects into flat slices of bf16 elements and keep fp32 state per slice
@@ -256,6 +252,37 @@ class Trainer:
     def host_tensor(self, oid: str, shape, dtype: str):
         from ..runtime.interop import torch_view
         return torch_view(self.store.buffer(oid), shape, dtype, 0, None)
+
+    def _fit_static_extent(self, cfg, budget, recompute, measured, leeway_bytes, lower_kwargs, replan: bool, rounds: int = 4) -> None:
+        """Static placement with a replan loop: pack the plan's allocations into the pool; when no packing fits (the plan's peak
+        leaves too little room for the holes a packing needs), plan again with the budget lowered by the excess plus a margin,
+        and try again.  The pool keeps the size the FIRST plan gave it, so every round gains room.  Ends with a placement
+        (``self.placement``, and possibly a new ``self.program``) or with the dynamic allocator and a note.
+        Role parity: reference ``src/dataflow_training/lowering/planning.py`` (``fit_static_extent``)."""
+        from ..runtime.placement import PlacementError, compute_placement, plan_placement, record_lifetimes
+        capacity = int(self.session.native.fast_slab()[1])
+        cut = 0
+        for attempt in range(rounds):
+            try:
+                self.placement = plan_placement(self.program, capacity)
+                if self.verbose and attempt:
+                    print(f"static placement fits after {attempt} replans (budget lowered by {cut / 2 ** 30:.2f} GiB)")
+                return
+            except PlacementError as e:
+                if not replan or budget is None or attempt == rounds - 1:
+                    if self.verbose:
+                        print(f"static placement not used: {e}")
+                    return
+                top = compute_placement(record_lifetimes(self.program, 0), None).top          # what the best packing needs
+                cut += max(top - capacity, 0) + (256 << 20)
+                planned = plan_at_budget(self.fam, cfg, budget - cut, self.hw, recompute=recompute, measured=measured,
+                                         leeway_bytes=leeway_bytes, lower_kwargs=lower_kwargs)
+                ids_old = {(o.id, o.size_bytes) for o in self.program.initial_objects}
+                if {(o.id, o.size_bytes) for o in planned.program.initial_objects} != ids_old:
+                    if self.verbose:
+                        print("static placement not used: the replanned program has other persistent objects")
+                    return
+                self.planned, self.program = planned, planned.program
 
     def init_model(self, seed: int = 0) -> None:
         """Seeded initial parameters and optimizer state.  ``hyper["init_policy"]`` (``blocks/init_policy.py``: rules by field name
