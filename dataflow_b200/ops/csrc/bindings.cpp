@@ -319,6 +319,19 @@ static void param_gather(std::vector<int64_t> slabs, std::vector<int64_t> ctrls,
   TORCH_CHECK(rc == 0, "param_gather launch failed with code ", rc);
 }
 
+static void param_gather_dma(std::vector<int64_t> slabs, std::vector<int64_t> ctrls, int64_t rank, int64_t slots, int64_t slot,
+                             int64_t seq, int64_t ack_expect, int64_t shard_ptr, std::vector<int64_t> expect_off, int64_t full_ptr,
+                             int64_t per_bytes, int64_t total_bytes, double timeout_s, Tensor& err) {
+  int world = slabs.size();
+  TORCH_CHECK((int)expect_off.size() == world && (int)ctrls.size() == world, "param_gather_dma: one offset and one control block per rank");
+  need(err, "err", at::kInt, 1);
+  std::vector<unsigned long long> sl(slabs.begin(), slabs.end()), ct(ctrls.begin(), ctrls.end()), eo(expect_off.begin(), expect_off.end());
+  int rc = dfb::param_gather_dma(sl.data(), ct.data(), rank, world, slots, slot, (unsigned)seq, (unsigned)ack_expect,
+                                 reinterpret_cast<const void*>(shard_ptr), eo.data(), reinterpret_cast<void*>(full_ptr), per_bytes,
+                                 total_bytes, timeout_s, err.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "param_gather_dma failed with code ", rc);
+}
+
 // ---------------------------------------------------------------- mixture of experts
 static int mode_id(const std::string& mode) {
   if (mode == "topk_then_softmax") return 0;
@@ -705,4 +718,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_ag_gemm", &tp_ag_gemm);
   m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("param_gather", &param_gather);
+  m.def("param_gather_dma", &param_gather_dma);
 }

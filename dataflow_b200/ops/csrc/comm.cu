@@ -299,6 +299,54 @@ __global__ void __maxnreg__(kCommRegs) param_gather_kernel(GatherParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------- parameter gather by the copy engines
+// The gather is a pure copy, so its bytes can ride the copy engines instead of SM threads (no issue slots, registers or L1
+// taken from the GEMM that runs beside it).  What still needs a kernel is the rendezvous, and that is two one-warp
+// launches around the copies:
+//   open : publish this rank's shard address for the slot, wait (bounded) until every peer has published this sequence
+//          number, and CHECK that each peer's shard still lies where the host believes it does (the copies that follow were
+//          issued with those addresses; a shard that moved raises the error word, it is never read silently from the wrong place)
+//   copies: one cudaMemcpyAsync per rank, peer slab -> this rank's gathered buffer, on the same stream
+//   close: tell every peer this rank has finished reading, wait (bounded) for their acknowledgements
+struct GatherDmaParams {
+  PeerTable peers;
+  int slots, slot;
+  unsigned int seq, ack_expect;
+  unsigned long long my_off;
+  unsigned long long expect_off[kMaxWorld];
+  unsigned long long timeout_ns;
+  int* err;
+};
+
+__global__ void gather_open_kernel(GatherDmaParams p) {
+  const int me = p.peers.rank, W = p.peers.world;
+  if (threadIdx.x == 0) {
+    *mail_off(p.peers.ctrl[me], p.slots, p.slot) = p.my_off;
+    __threadfence_system();
+    st_release_sys(mail_seq(p.peers.ctrl[me], p.slots, p.slot), p.seq);
+  }
+  __syncwarp();
+  const int r = threadIdx.x;
+  if (r < W && r != me) {
+    if (wait_ge(mail_seq(p.peers.ctrl[r], p.slots, p.slot), p.seq, p.timeout_ns)) {
+      const unsigned long long off = *reinterpret_cast<volatile unsigned long long*>(mail_off(p.peers.ctrl[r], p.slots, p.slot));
+      if (off != p.expect_off[r]) atomicExch(p.err, (5 << 8) | r);          // the peer's shard is not where the copies will read
+    } else {
+      atomicExch(p.err, (3 << 8) | r);
+    }
+  }
+}
+
+__global__ void gather_close_kernel(GatherDmaParams p) {
+  const int me = p.peers.rank, W = p.peers.world;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < W; ++r)
+      if (r != me) atomicAdd_system(ack_ctr(p.peers.ctrl[r], p.slots, p.slot), 1u);
+    if (!wait_ge(ack_ctr(p.peers.ctrl[me], p.slots, p.slot), p.ack_expect, p.timeout_ns)) atomicExch(p.err, (4 << 8) | me);
+  }
+}
+
 // ---------------------------------------------------------------------------- host entry points
 // CTAs per communication kernel: one per SM unless DATAFLOW_COMM_CTAS names a smaller budget (the kernels are grid-stride
 // loops, so any count is correct; fewer CTAs leave more issue slots to the GEMM they run beside).
@@ -363,6 +411,31 @@ int param_gather(const unsigned long long* slabs, const unsigned long long* ctrl
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.err = err; p.done_ctr = done_ctr;
   param_gather_kernel<<<comm_grid(num_sms), kCommThreads, 0, s>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int param_gather_dma(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                     unsigned int seq, unsigned int ack_expect, const void* shard, const unsigned long long* expect_off, void* full,
+                     long long per_bytes, long long total_bytes, double timeout_s, int* err, cudaStream_t s) {
+  if (world > kMaxWorld || per_bytes <= 0 || total_bytes <= 0) return -2;
+  GatherDmaParams p{};
+  p.peers = make_table(slabs, ctrls, rank, world);
+  p.slots = slots; p.slot = slot; p.seq = seq; p.ack_expect = ack_expect;
+  p.my_off = static_cast<unsigned long long>(reinterpret_cast<const unsigned char*>(shard) - p.peers.slab[rank]);
+  for (int r = 0; r < world; ++r) p.expect_off[r] = expect_off[r];
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.err = err;
+  gather_open_kernel<<<1, 32, 0, s>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return -1;
+  for (int i = 0; i < world; ++i) {
+    const int r = (rank + 1 + i) % world;                   // start with the next rank so that the ranks do not all read one peer at once
+    const long long lo = static_cast<long long>(r) * per_bytes;
+    const long long n = lo >= total_bytes ? 0 : (total_bytes - lo < per_bytes ? total_bytes - lo : per_bytes);
+    if (n <= 0) continue;
+    const void* src = r == rank ? shard : static_cast<const void*>(p.peers.slab[r] + expect_off[r]);
+    if (cudaMemcpyAsync(static_cast<unsigned char*>(full) + lo, src, static_cast<size_t>(n), cudaMemcpyDeviceToDevice, s) != cudaSuccess) return -3;
+  }
+  gather_close_kernel<<<1, 32, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

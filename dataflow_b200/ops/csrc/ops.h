@@ -71,6 +71,11 @@ int zero_rs_adamw(const unsigned long long* slabs, const unsigned long long* ctr
 int param_gather(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
                  unsigned int seq, unsigned int ack_expect, const void* shard, void* full, long long per_bytes,
                  long long total_bytes, double timeout_s, int* err, unsigned int* done_ctr, int num_sms, cudaStream_t s);
+// the same gather with the bytes on the copy engines: two one-warp rendezvous launches around one cudaMemcpyAsync per rank;
+// expect_off[r] = where rank r's shard lies in its slab (checked on the device against what r publishes)
+int param_gather_dma(const unsigned long long* slabs, const unsigned long long* ctrls, int rank, int world, int slots, int slot,
+                     unsigned int seq, unsigned int ack_expect, const void* shard, const unsigned long long* expect_off, void* full,
+                     long long per_bytes, long long total_bytes, double timeout_s, int* err, cudaStream_t s);
 
 
 // Tensor-parallel GEMMs fused with their collective (gemm_tp.cu)
