@@ -338,6 +338,22 @@ static int mode_id(const std::string& mode) {
   if (mode == "softmax_then_topk") return 1;
   TORCH_CHECK(false, "unknown routing mode ", mode);
 }
+static void moe_sort(const Tensor& ids, int64_t E, int64_t tile_rows, Tensor& row_of, Tensor& row_src, Tensor& offsets_pad,
+                     Tensor& tile_expert, Tensor& counts, Tensor& scratch) {
+  TORCH_CHECK(ids.dim() == 2, "moe_sort: route ids (t, K)");
+  const int64_t t = ids.size(0), K = ids.size(1), n = t * K, mp = row_src.numel();
+  need(ids, "route_ids", at::kInt, n);
+  need(row_of, "row_of", at::kInt, n);
+  need(row_src, "row_src", at::kInt);
+  need(offsets_pad, "offsets_pad", at::kInt, E + 1);
+  need(tile_expert, "tile_expert", at::kInt, mp / tile_rows);
+  need(counts, "counts", at::kInt, E);
+  need(scratch, "scratch", at::kInt, ((n + 1023) / 1024) * E);
+  TORCH_CHECK(mp % tile_rows == 0 && mp >= (n + tile_rows - 1) / tile_rows * tile_rows + E * tile_rows, "moe_sort: row_src too small for the padded layout");
+  int rc = dfb::moe_sort(ids.data_ptr<int>(), (int)t, (int)K, (int)E, (int)tile_rows, (int)mp, row_of.data_ptr<int>(), row_src.data_ptr<int>(),
+                         offsets_pad.data_ptr<int>(), tile_expert.data_ptr<int>(), counts.data_ptr<int>(), scratch.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "moe_sort: unsupported shape (1 <= E <= 1024), code ", rc);
+}
 static void moe_topk_softmax(const Tensor& logits, Tensor& route_w, Tensor& route_ids, const std::string& mode) {
   CHECK_F32(route_w); CHECK_I32(route_ids);
   TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "logits must be a contiguous (t, E) matrix");
@@ -686,6 +702,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("zero_rs_adamw", &zero_rs_adamw);
   m.def("zero_rs_accum", &zero_rs_accum);
+  m.def("moe_sort", &moe_sort);
   m.def("moe_topk_softmax", &moe_topk_softmax);
   m.def("moe_router_bwd", &moe_router_bwd);
   m.def("moe_dispatch", &moe_dispatch);

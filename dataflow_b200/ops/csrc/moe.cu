@@ -254,3 +254,104 @@ int moe_rowdot(const void* a, const void* b, const int* row_of, float* out, int 
 }
 
 }  // namespace dfb
+
+// ---------------------------------------------------------------------------- moe_sort: the padded expert-major layout
+// A stable counting sort of the t*K routed slots by expert, without a library sort and without a host sync:
+//   pass 1  per chunk of kSortChunk consecutive slots: how many go to each expert            (chunk_counts[chunk][e])
+//   pass 2  one CTA: per expert, exclusive scan over the chunks; totals -> counts, padded offsets, the expert of every row
+//           tile; row_src cleared to -1
+//   pass 3  per chunk again: a slot's row = padded offset of its expert + slots of that expert in earlier chunks + slots
+//           of that expert EARLIER IN THE CHUNK (counted by comparison: stable, hence deterministic)
+namespace dfb {
+
+constexpr int kSortChunk = 1024;
+constexpr int kSortMaxE = 1024;
+
+__global__ void moe_sort_count_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ chunk_counts) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kSortChunk;
+  for (int i = threadIdx.x; i < kSortChunk && base + i < n; i += blockDim.x) {
+    const int e = ids[base + i];
+    if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_counts[static_cast<long long>(blockIdx.x) * E + e] = hist[e];
+}
+
+__global__ void moe_sort_scan_kernel(int* __restrict__ chunk_counts, int chunks, int E, int tile_rows, int mp, int* __restrict__ counts,
+                                     int* __restrict__ offsets_pad, int* __restrict__ tile_expert, int* __restrict__ row_src) {
+  __shared__ int s_off[kSortMaxE + 1];
+  // per expert: chunk_counts[c][e] becomes the number of that expert's slots in chunks before c
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const long long at = static_cast<long long>(c) * E + e;
+      const int v = chunk_counts[at];
+      chunk_counts[at] = run;
+      run += v;
+    }
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = off;
+      offsets_pad[e] = off;
+      off += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
+    }
+    s_off[E] = off;
+    offsets_pad[E] = off;
+  }
+  __syncthreads();
+  const int tiles = mp / tile_rows;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const int row = t * tile_rows;
+    int e = -1;
+    if (row < s_off[E]) {
+      int lo = 0, hi = E;                       // the last expert whose padded offset is <= row and that owns rows
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_off[mid] <= row) lo = mid; else hi = mid;
+      }
+      e = lo;
+    }
+    tile_expert[t] = e;
+  }
+  for (int r = threadIdx.x; r < mp; r += blockDim.x) row_src[r] = -1;
+}
+
+__global__ void moe_sort_place_kernel(const int* __restrict__ ids, int n, int K, int E, const int* __restrict__ chunk_counts,
+                                      const int* __restrict__ offsets_pad, int* __restrict__ row_of, int* __restrict__ row_src) {
+  __shared__ int s_ids[kSortChunk];
+  const int base = blockIdx.x * kSortChunk;
+  const int len = min(kSortChunk, n - base);
+  for (int i = threadIdx.x; i < len; i += blockDim.x) s_ids[i] = ids[base + i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+    const int e = s_ids[i];
+    if (e < 0 || e >= E) { row_of[base + i] = -1; continue; }
+    int before = 0;
+    for (int j = 0; j < i; ++j) before += (s_ids[j] == e);
+    const int row = offsets_pad[e] + chunk_counts[static_cast<long long>(blockIdx.x) * E + e] + before;
+    row_of[base + i] = row;
+    row_src[row] = (base + i) / K;
+  }
+}
+
+// scratch: chunks * E ints.  Two experts may share a padded offset only when the first has no rows (then it has no tiles and
+// the binary search lands on the later one, which is the owner).
+int moe_sort(const int* ids, int t, int K, int E, int tile_rows, int mp, int* row_of, int* row_src, int* offsets_pad, int* tile_expert,
+             int* counts, int* scratch, cudaStream_t s) {
+  const int n = t * K;
+  if (E < 1 || E > kSortMaxE || n <= 0 || tile_rows <= 0 || mp % tile_rows) return -1;
+  const int chunks = (n + kSortChunk - 1) / kSortChunk;
+  moe_sort_count_kernel<<<chunks, 256, E * sizeof(int), s>>>(ids, n, E, scratch);
+  moe_sort_scan_kernel<<<1, 1024, 0, s>>>(scratch, chunks, E, tile_rows, mp, counts, offsets_pad, tile_expert, row_src);
+  moe_sort_place_kernel<<<chunks, 256, 0, s>>>(ids, n, K, E, scratch, offsets_pad, row_of, row_src);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace dfb

@@ -93,6 +93,9 @@ int moe_topk_softmax(const void* logits, int logits_f32, float* route_w, int* ro
                      cudaStream_t s);
 int moe_router_bwd(const float* dprob, const float* route_w, const int* route_ids, const void* logits, int logits_f32,
                    float* dlogits, int t, int E, int K, int mode, cudaStream_t s);
+// padded expert-major layout of the routed slots (stable counting sort on the device; scratch: ceil(t K / 1024) * E ints)
+int moe_sort(const int* ids, int t, int K, int E, int tile_rows, int mp, int* row_of, int* row_src, int* offsets_pad, int* tile_expert,
+             int* counts, int* scratch, cudaStream_t s);
 int moe_dispatch(const void* x, long long ldx, const int* row_src, void* xp, int rows, int d, cudaStream_t s);
 int moe_combine(const void* base, const void* yp, const float* w, const int* row_of, void* out, int t, int d, int K,
                 cudaStream_t s);

@@ -326,6 +326,24 @@ def moe_rowdot(a, b, row_of):
     return out
 
 
+@reg("moe_sort", launches=3)
+def moe_sort(route_ids, n_experts: int, tile_rows: int = 256):
+    """The padded expert-major layout by a stable counting sort on the device (three small kernels, no library sort)."""
+    t, k = route_ids.shape
+    n = t * k
+    if n_experts > 1024 or n == 0:
+        from . import eager
+        return eager.moe_sort(route_ids, n_experts, tile_rows)
+    dev = route_ids.device
+    mp = (n + tile_rows - 1) // tile_rows * tile_rows + n_experts * tile_rows
+    i32 = dict(dtype=torch.int32, device=dev)
+    row_of, row_src = torch.empty(t, k, **i32), torch.empty(mp, **i32)
+    offsets_pad, tile_expert, counts = torch.empty(n_experts + 1, **i32), torch.empty(mp // tile_rows, **i32), torch.empty(n_experts, **i32)
+    scratch = torch.empty(((n + 1023) // 1024) * n_experts, **i32)
+    native().moe_sort(route_ids.to(torch.int32).contiguous(), int(n_experts), int(tile_rows), row_of, row_src, offsets_pad, tile_expert, counts, scratch)
+    return row_of, row_src, offsets_pad, tile_expert, counts
+
+
 @reg("moe_grouped_mm")
 def moe_grouped_mm(xp, w, tile_expert, out=None, transpose_w: bool = False):
     """``tile_expert``: the per-row-tile expert table of ``moe_sort`` (device int32)."""

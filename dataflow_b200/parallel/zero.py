@@ -100,12 +100,9 @@ class DpGroup(GroupCollectives):
         self.backend = None
         self.err = None
         self.done = None
-        # parameter gathers: "dma" moves the bytes with the copy engines once the shards' addresses are known to hold still
-        # (the SM kernel stays for the first calls of a slot and whenever a shard moves); "kernel" never leaves the SM kernel
+        # parameter gathers: "dma" moves the bytes with the copy engines (each rank stages its shard at a fixed address behind its
+        # slab first); "kernel" pulls them with SM threads from wherever the shards lie
         self.gather_mode = os.environ.get("DATAFLOW_GATHER", "dma")
-        self.peer_offs: dict[int, list[int]] = {}
-        self._own_seen: dict[int, tuple[int, int]] = {}
-        self._probe: dict[int, Any] = {}
         self.comm_stream = None
         self.done_async = None
         self.async_comm = False
@@ -192,38 +189,19 @@ class DpGroup(GroupCollectives):
                 ready[oid] = ev
         return scope()
 
-    def _peer_offsets(self, slot: int, sptr: int):
-        """Where every rank's shard of this slot lies in its slab, once that is known and has held still; ``None`` sends the
-        call through the SM kernel (which needs no foreknowledge: it reads the peers' mailboxes on the device).  A slot
-        qualifies after two calls in a row found this rank's own shard at the same address (every rank runs the same plan, so
-        the peers' shards hold still when this one does); the peers' addresses are then read from their mailboxes once, after
-        the last kernel-path gather of the slot has finished.  A shard that moves later sends the slot back here."""
-        if self.gather_mode != "dma":
-            return None
-        my = int(sptr) - int(self.slab_base)
-        cached = self.peer_offs.get(slot)
-        if cached is not None:
-            if cached[self.rank] == my:
-                return cached
-            del self.peer_offs[slot]
-            self._own_seen.pop(slot, None)
-        seen, count = self._own_seen.get(slot, (None, 0))
-        count = count + 1 if seen == my else 1
-        self._own_seen[slot] = (my, count)
-        ev = self._probe.pop(slot, None)
-        if count < 3 or ev is None:               # this call and the two before it: the same address
-            return None
+    def _stage(self, t, nbytes: int, asynchronous: bool) -> int:
+        """Copy ``t``'s first ``nbytes`` into the staging half of the calling stream (behind the slab, inside the peers' mapping of
+        it) and return that address — the same on every rank, in every step.  The kernel that closes a gather holds the stream
+        until every peer has finished reading, so the next copy into the half cannot overtake a reader."""
+        import torch
         from ..ops import native
-        ev.synchronize()
-        offs = []
-        for r in range(self.world):
-            if r == self.rank:
-                offs.append(my)
-            else:
-                words = native().tensor_from_ptr(self.ctrls[r], [self.SLOTS], "int64", self.device)
-                offs.append(int(words[slot].item()))
-        self.peer_offs[slot] = offs
-        return offs
+        half = self.tail_bytes // 2
+        if nbytes > half:
+            return 0
+        dst_ptr = self.slab_base + self.slab_cap + (half if asynchronous else 0)
+        dst = native().tensor_from_ptr(dst_ptr, [nbytes], "uint8", self.device)
+        dst.copy_(t.reshape(-1).view(torch.uint8)[:nbytes])
+        return dst_ptr
 
     def _next(self, slot: int) -> tuple[int, int]:
         c = self.calls.get(slot, 0) + 1
@@ -310,22 +288,22 @@ class DpGroup(GroupCollectives):
             from ..ops import native
             from ..ops.cuda import LAUNCHES
             seq, ack = self._next(slot)
-            sptr = self._in_slab(shard, min(per_bytes, shard.numel()), asynchronous)
-            offs = self._peer_offsets(slot, sptr)
-            if offs is not None:
-                # the bytes ride the copy engines; two one-warp kernels do the rendezvous around them
-                native().param_gather_dma(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, sptr, offs, full.data_ptr(),
-                                          per_bytes, total, self.timeout_s, self.err)
-                LAUNCHES.total += 2
-                return
+            n_mine = min(per_bytes, shard.numel())
+            if self.gather_mode == "dma":
+                # The bytes ride the copy engines, which need the peers' source addresses on the HOST when the copies are issued.
+                # Shards live wherever the engine's allocator put them (differently on every rank, and anew after every optimizer
+                # step), so every rank first copies its shard to the one address all ranks know: the staging half behind its slab.
+                sptr = self._stage(shard, n_mine, asynchronous)
+                if sptr:
+                    offs = [sptr - self.slab_base] * self.world
+                    native().param_gather_dma(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, sptr, offs, full.data_ptr(),
+                                              per_bytes, total, self.timeout_s, self.err)
+                    LAUNCHES.total += 3
+                    return
+            sptr = self._in_slab(shard, n_mine, asynchronous)
             native().param_gather(self.slabs, self.ctrls, self.rank, self.SLOTS, slot, seq, ack, sptr,
                                   full.data_ptr(), per_bytes, total, self.timeout_s, self.err,
                                   self.done_async if asynchronous else self.done)
-            if self.gather_mode == "dma":
-                import torch
-                ev = torch.cuda.Event()
-                ev.record(torch.cuda.current_stream())
-                self._probe[slot] = ev
             LAUNCHES.total += 1
             return
         import torch

@@ -222,6 +222,12 @@ def c_add(K, g, small):
     return K.add(g.bf(r, c), g.bf(r, c))
 
 
+def c_moe_sort(K, g, small):
+    t, E, topk = (1, 4, 2) if small else (700, 64, 8)
+    ids = torch.stack([torch.randperm(E, device=g.dev, generator=g.g)[:topk] for _ in range(t)]).to(I32)
+    return K.moe_sort(ids, E)
+
+
 def c_moe_topk_softmax(K, g, small):
     t, E = (1, 8) if small else (301, 64)
     return K.moe_topk_softmax(g.bf(t, E), 2, "topk_then_softmax")
@@ -350,7 +356,7 @@ CASES = {
     "swiglu_packed_bwd": c_swiglu_packed_bwd, "gelu_fwd_out": c_gelu_fwd_out, "gelu_bwd": c_gelu_bwd,
     "ce_loss_fwd_bwd": c_ce_loss, "embed_fwd": c_embed_fwd, "embed_bwd_accum": c_embed_bwd, "adamw_step": c_adamw,
     "adamw_split_step": c_adamw_split, "sgd_step": c_sgd, "linear_fwd_bf16": c_linear_fwd, "linear_dgrad_bf16": c_linear_dgrad,
-    "linear_wgrad_bf16": c_linear_wgrad, "bias_grad": c_bias_grad, "add": c_add, "moe_topk_softmax": c_moe_topk_softmax,
+    "linear_wgrad_bf16": c_linear_wgrad, "bias_grad": c_bias_grad, "add": c_add, "moe_sort": c_moe_sort, "moe_topk_softmax": c_moe_topk_softmax,
     "moe_topk_sigmoid_noaux": c_moe_topk_sigmoid, "moe_router_bwd": c_moe_router_bwd, "moe_dispatch": moe_case(_dispatch),
     "moe_combine": moe_case(_combine), "moe_dispatch_bwd": moe_case(_dispatch_bwd), "moe_scale_rows": moe_case(_scale_rows),
     "moe_rowdot": moe_case(_rowdot), "moe_grouped_mm": moe_case(_grouped_mm), "moe_grouped_wgrad": moe_case(_grouped_wgrad),

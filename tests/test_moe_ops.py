@@ -121,3 +121,21 @@ def test_gpu_grouped_gemms_match_eager():
     assert ((dW.float() - refw.float()).norm() / refw.float().norm()) < 5e-3
     C.moe_grouped_wgrad(xp, h, offp, dW, accumulate=True)
     assert ((dW.float() - 2 * refw.float()).norm() / (2 * refw.float()).norm()) < 8e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t,n_experts,k", [(1, 4, 2), (700, 64, 8), (5000, 8, 2), (16384, 64, 8), (333, 256, 8), (100, 16, 1)])
+def test_gpu_moe_sort_equals_the_stable_sort_oracle(t, n_experts, k):
+    """The device counting sort (three kernels) gives exactly the eager layout: the same row for every slot (stable within an
+    expert), the same source tokens, padded offsets, per-tile experts and counts; skewed routing included."""
+    from dataflow_b200.ops import resolve_kernels
+    K = resolve_kernels()
+    g = torch.Generator(device="cuda").manual_seed(t)
+    ids = torch.stack([torch.randperm(n_experts, device="cuda", generator=g)[:k] for _ in range(min(t, 64))])
+    ids = ids[torch.randint(0, ids.shape[0], (t,), device="cuda", generator=g)].to(torch.int32)
+    if t > 100:
+        ids[: t // 2, 0] = 0                              # half of the tokens pile onto expert 0
+    got = K.moe_sort(ids, n_experts)
+    want = E.moe_sort(ids, n_experts)
+    for a, b, name in zip(got, want, ("row_of", "row_src", "offsets_pad", "tile_expert", "counts")):
+        assert a.dtype == torch.int32 and torch.equal(a, b.to(a.device)), name

@@ -88,38 +88,3 @@ def test_sharded_modes_refuse_fp32_parameter_policies():
     cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
     with pytest.raises(ValueError, match="needs bf16 parameters"):
         Trainer("llama3", cfg, budget_gib=None, device=None, lower_kwargs=zero_lower_kwargs("fsdp", 0, 2), init=False)
-
-
-def test_copy_engine_gather_waits_for_addresses_that_hold_still(monkeypatch):
-    """The host-side gate of the copy-engine parameter gather: a slot goes through the SM kernel until this rank's own shard
-    was found at the same address three calls in a row, then the peers' addresses are read once from their mailboxes; a
-    shard that moves later sends the slot back to the kernel path; ``DATAFLOW_GATHER=kernel`` never leaves it."""
-    import torch
-    from dataflow_b200.parallel.zero import DpGroup
-    import dataflow_b200.ops as ops
-
-    class Ev:
-        waited = 0
-
-        def synchronize(self):
-            Ev.waited += 1
-
-    mail = {1: torch.zeros(DpGroup.SLOTS, dtype=torch.int64)}
-
-    class Native:
-        @staticmethod
-        def tensor_from_ptr(ptr, shape, dtype, device):
-            return mail[ptr]
-    monkeypatch.setattr(ops, "native", lambda: Native)
-    g = DpGroup(0, 2, None, lane="p2p")
-    g.gather_mode = "dma"
-    g.slab_base, g.ctrls, g.device = 1000, [0, 1], 0
-    mail[1][7] = 4096                                   # the peer's shard of slot 7 lies 4096 bytes into its slab
-    for call in range(2):
-        assert g._peer_offsets(7, 1000 + 512) is None   # first and second sighting of the address
-        g._probe[7] = Ev()                              # what the kernel path leaves behind
-    assert g._peer_offsets(7, 1000 + 512) == [512, 4096] and Ev.waited == 1
-    assert g._peer_offsets(7, 1000 + 512) == [512, 4096] and Ev.waited == 1          # cached: no host wait in steady state
-    assert g._peer_offsets(7, 1000 + 768) is None and 7 not in g.peer_offs           # the shard moved
-    g.gather_mode = "kernel"
-    assert g._peer_offsets(7, 1000 + 768) is None
