@@ -53,6 +53,19 @@ def _upload_rounds(state: RankState, packed, first_round: int) -> tuple[dict[int
     return seq_lens, nbytes
 
 
+def check_fleet_versions(statuses: dict[str, dict], local_rev: str, local_env: str) -> None:
+    """Refuse a mixed fleet: every daemon must run the conductor's code (digest of the package's sources) and the conductor's
+    framework / CUDA versions.  Skewed code gives structurally mismatched collectives (a hang, or garbage that is summed
+    silently); skewed versions make replicas drift.  Role parity: reference ``src/dataflow_training/run/conductor.py:78-142``."""
+    for name, st in statuses.items():
+        rev, env = st.get("code_rev"), st.get("env")
+        if rev != local_rev:
+            raise RuntimeError(f"fleet version skew: {name} runs code {rev} but the conductor runs {local_rev} — bring every host to the "
+                               f"same revision before a fleet run")
+        if env != local_env:
+            raise RuntimeError(f"fleet environment skew: {name} runs [{env}] but the conductor runs [{local_env}]")
+
+
 def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
     """Train ``spec`` (a ``conductor.RunSpec`` with ``world`` ranks, replicas) through one daemon per rank on this box."""
     from ..data.pipeline import pipeline_from_args
@@ -109,6 +122,10 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
             paths.append(p)
             clients.append(EngineClient(p["socket"], f"fleet-rank{r}", timeout=600.0))
             log(f"[fleet] rank {r} up ({'cpu' if cpu else 'cuda:' + str(members[r].device)}, socket {p['socket']})")
+        from .. import code_revision
+        from ..service.handlers import _env_line
+        check_fleet_versions({names[r]: c.engine_status() for r, c in enumerate(clients)}, code_revision(), _env_line())
+        log(f"[fleet] version handshake ok ({code_revision()}, {_env_line()})")
         if world > 1:
             for r in range(1, world):
                 clients[0].peer_connect(names[r], f"127.0.0.1:{ports[r]}")

@@ -35,6 +35,21 @@ def close_engine(server) -> None:
         server.backend.synchronize()
 
 
+def _code_rev() -> str:
+    from .. import code_revision
+    return code_revision()
+
+
+def _env_line() -> str:
+    """What replicated compute must share besides the code: the framework and CUDA versions (a different version may pick
+    different kernels, and replicas then drift apart silently)."""
+    try:
+        import torch
+        return f"torch {torch.__version__} cuda {torch.version.cuda}"
+    except Exception:       # noqa: BLE001
+        return "torch absent"
+
+
 def install(server) -> None:
     st, H = server.store, server.handlers
 
@@ -43,7 +58,8 @@ def install(server) -> None:
     H["engine_status"] = lambda req, p: {"backend": server.backend.name(), "device": server.config.device,
                                           "programs": len(server.programs), "runs": len(server.runs),
                                           "counters": dict(server.state.counters), "store": st.query(),
-                                          "host_bw_gbs": dict(getattr(server, "host_bw", {}))}
+                                          "host_bw_gbs": dict(getattr(server, "host_bw", {})),
+                                          "code_rev": _code_rev(), "env": _env_line()}
     H["session_status"] = lambda req, p: {"vendor_allocs": server._session.vendor_allocs()
                                           if getattr(server, "_session", None) else 0}
     def profiler_control(req, p):

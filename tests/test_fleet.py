@@ -61,3 +61,16 @@ def test_timeline_wrap_and_profile_window(tmp_path):
     res = run_fleet(spec, log=lines.append)
     assert len(res.losses) == 3
     assert any("profile window steps 2..2" in l for l in lines)
+
+
+def test_mixed_fleets_are_refused():
+    from dataflow_b200 import code_revision
+    from dataflow_b200.run.fleet import check_fleet_versions
+    rev = code_revision()
+    assert len(rev) == 16 and rev == code_revision()
+    ok = {"rank0": {"code_rev": rev, "env": "torch 2 cuda 12"}, "rank1": {"code_rev": rev, "env": "torch 2 cuda 12"}}
+    check_fleet_versions(ok, rev, "torch 2 cuda 12")
+    with pytest.raises(RuntimeError, match="rank1 runs code deadbeef"):
+        check_fleet_versions({**ok, "rank1": {"code_rev": "deadbeef", "env": "torch 2 cuda 12"}}, rev, "torch 2 cuda 12")
+    with pytest.raises(RuntimeError, match="environment skew"):
+        check_fleet_versions({**ok, "rank1": {"code_rev": rev, "env": "torch 3 cuda 13"}}, rev, "torch 2 cuda 12")
