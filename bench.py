@@ -197,6 +197,7 @@ def bench_ours(a) -> dict:
                  "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
                  "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows, "pool": _pool_line(tr),
                  "static_placement": tr.placement is not None,
+                 "param_gather": getattr(groups.get("dp"), "gather_mode", None),
                  "placement_escapes": res.placement_escapes, "pressure_evictions": res.pressure_evictions,
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},

@@ -33,3 +33,13 @@ def code_revision() -> str:
 
 
 _CODE_REV = None
+
+
+def environment_line() -> str:
+    """What replicated compute must share besides the code: the framework and CUDA versions (another version may pick other
+    kernels, and replicas then drift apart silently)."""
+    try:
+        import torch
+        return f"torch {torch.__version__} cuda {torch.version.cuda}"
+    except Exception:       # noqa: BLE001
+        return "torch absent"

@@ -102,7 +102,7 @@ class DpGroup(GroupCollectives):
         self.done = None
         # parameter gathers: "dma" moves the bytes with the copy engines (each rank stages its shard at a fixed address behind its
         # slab first); "kernel" pulls them with SM threads from wherever the shards lie
-        self.gather_mode = os.environ.get("DATAFLOW_GATHER", "dma")
+        self.gather_mode = os.environ.get("DATAFLOW_GATHER", "auto")      # "auto" is settled in attach() from the plan
         self.comm_stream = None
         self.done_async = None
         self.async_comm = False
@@ -145,6 +145,16 @@ class DpGroup(GroupCollectives):
         self.comm_stream = torch.cuda.Stream(device=dev)
         self.done_async = torch.zeros(1, dtype=torch.int32, device=dev)
         self.async_comm = os.environ.get("DATAFLOW_ASYNC_COMM", "1") != "0"
+        if self.gather_mode == "auto":
+            # The copy engines also carry the plan's host traffic.  Measured on the 8B step: at 2 GPUs the host lanes are busy half
+            # of the step and gathers on the copy engines cost 11 % (prefetches fall behind); where the lanes are nearly idle the
+            # copy engines are free and the SM kernel's interference with the GEMM is what costs.  So: copy engines only when the
+            # planned host-to-device lane is busy less than a quarter of the step (8 GPUs: 15 %).
+            planned = getattr(trainer, "planned", None)
+            busy = 1.0
+            if planned is not None and planned.makespan_us:
+                busy = float((planned.transfer or {}).get("from_slow", {}).get("busy_us", planned.makespan_us)) / float(planned.makespan_us)
+            self.gather_mode = "dma" if busy < 0.25 else "kernel"
         dist.barrier()
 
     def _in_slab(self, t, nbytes: int, asynchronous: bool = False) -> int:

@@ -122,10 +122,9 @@ def run_fleet(spec, log: Callable[[str], None] = print) -> RunResult:
             paths.append(p)
             clients.append(EngineClient(p["socket"], f"fleet-rank{r}", timeout=600.0))
             log(f"[fleet] rank {r} up ({'cpu' if cpu else 'cuda:' + str(members[r].device)}, socket {p['socket']})")
-        from .. import code_revision
-        from ..service.handlers import _env_line
-        check_fleet_versions({names[r]: c.engine_status() for r, c in enumerate(clients)}, code_revision(), _env_line())
-        log(f"[fleet] version handshake ok ({code_revision()}, {_env_line()})")
+        from .. import code_revision, environment_line
+        check_fleet_versions({names[r]: c.engine_status() for r, c in enumerate(clients)}, code_revision(), environment_line())
+        log(f"[fleet] version handshake ok ({code_revision()}, {environment_line()})")
         if world > 1:
             for r in range(1, world):
                 clients[0].peer_connect(names[r], f"127.0.0.1:{ports[r]}")

@@ -41,13 +41,8 @@ def _code_rev() -> str:
 
 
 def _env_line() -> str:
-    """What replicated compute must share besides the code: the framework and CUDA versions (a different version may pick
-    different kernels, and replicas then drift apart silently)."""
-    try:
-        import torch
-        return f"torch {torch.__version__} cuda {torch.version.cuda}"
-    except Exception:       # noqa: BLE001
-        return "torch absent"
+    from .. import environment_line
+    return environment_line()
 
 
 def install(server) -> None:
