@@ -269,6 +269,31 @@ def dsa_scores_at(x, cq, w, cfg, positions, sel):
     return (s * wgt[:, :, None]).sum(1)
 
 
+def dsa_indexer_kl_selected(x, cq, w, cfg, positions, sel, live, target, chunk: int = 512):
+    """KL(target || softmax of the index scores over the selection), mean over queries, without the (n, heads, kk) scores of
+    the whole round in memory: queries go ``chunk`` at a time and every chunk is re-run in the backward.  Equals
+    ``dsa_indexer_kl_at(dsa_scores_at(...), target, live)``."""
+    from torch.utils.checkpoint import checkpoint
+    n = x.shape[0]
+    qi, ki, wgt = _indexer_inputs(x, cq, w, cfg, positions)
+    if n <= chunk:
+        s = (torch.relu(torch.einsum("ihd,ikd->ihk", qi, ki[sel])) * wgt[:, :, None]).sum(1)
+        return dsa_indexer_kl_at(s, target, live)
+
+    def part(qc, wc, selc, livec, tc, ki_):
+        s = (torch.relu(torch.einsum("ihd,ikd->ihk", qc, ki_[selc])) * wc[:, :, None]).sum(1)
+        logq = torch.log_softmax(s.masked_fill(~livec, float("-inf")), dim=-1)
+        term = torch.where(tc > 0, tc * (torch.log(tc.clamp_min(1e-20)) - logq.masked_fill(~livec, 0.0)), torch.zeros_like(tc))
+        return term.sum()
+
+    total = x.new_zeros((), dtype=torch.float32)
+    for a in range(0, n, chunk):
+        b = min(a + chunk, n)
+        args = (qi[a:b], wgt[a:b], sel[a:b], live[a:b], target[a:b], ki)
+        total = total + (checkpoint(part, *args, use_reentrant=False) if torch.is_grad_enabled() else part(*args))
+    return total / n
+
+
 def mla_sparse_attention(q, ckv, k_rope, wkv_b, sel, live, cfg, chunk: int = 256, want_target: bool = False):
     """Attention of every query over ITS selected keys in the latent form: with k_j = [W_kb^T c_j | r_j] and
     v_j = W_vb^T c_j, the logits are (W_kb q_nope) . c_j + q_rope . r_j and the output is W_vb^T (sum_j p_j c_j) — one

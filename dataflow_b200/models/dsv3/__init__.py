@@ -119,8 +119,7 @@ def sparse_attention_gathered(c: Dsv3Config, h, w, pos):
     o, target = F.mla_sparse_attention(q, ckv, k_rope, w["wkv_b"], sel, live, c, want_target=bool(c.index_kl_coef))
     aux = None
     if c.index_kl_coef:
-        scores = F.dsa_scores_at(h.detach(), cq.detach(), iw, c, pos, sel)
-        aux = c.index_kl_coef * F.dsa_indexer_kl_at(scores, target, live) * n
+        aux = c.index_kl_coef * F.dsa_indexer_kl_selected(h.detach(), cq.detach(), iw, c, pos, sel, live, target) * n
     return o, aux
 
 

@@ -98,7 +98,7 @@ def block_fn(c: Glm52Config, kind: str, x, w, seg, layer, shared=None, accum=Non
             else:
                 if accum is not None:
                     target = (target + accum["kl_target"][:, :target.shape[1]].to(target.dtype)) / group_size
-                aux = c.index_kl_coef * F.dsa_indexer_kl_at(F.dsa_scores_at(h.detach(), cq.detach(), iw, c, pos, sel), target, live) * n
+                aux = c.index_kl_coef * F.dsa_indexer_kl_selected(h.detach(), cq.detach(), iw, c, pos, sel, live, target) * n
     else:
         q, k, v, cq = F.mla_qkv(h, w, c, pos)
         causal = F.segment_causal_mask(seg, n, x.device)
