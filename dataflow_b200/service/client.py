@@ -93,10 +93,13 @@ class EngineClient:
     def wait_restore(self, job_id: str, timeout: float = 600.0): return self._wait(self.restore_status, job_id, timeout)
 
     # -- programs and runs
-    def register_program(self, program: Program | dict, resolver_spec: Mapping | None = None, expect_prog_id: str | None = None):
+    def register_program(self, program: Program | dict, resolver_spec: Mapping | None = None, expect_prog_id: str | None = None,
+                         prepare_placement: bool = False, placement_capacity: int | None = None):
+        """``prepare_placement``: the daemon also computes a static placement of the program's fast allocations by a dry run
+        (refused when none fits ``placement_capacity`` / the program's own capacity) and uses it for its runs."""
         d = program if isinstance(program, dict) else program_to_dict(program)
         return self.call("register_program", program=d, resolver_spec=dict(resolver_spec) if resolver_spec else None,
-                         expect_prog_id=expect_prog_id)
+                         expect_prog_id=expect_prog_id, prepare_placement=bool(prepare_placement), placement_capacity=placement_capacity)
     def validate_program(self, program: Program | dict):
         return self.call("validate_program", program=program if isinstance(program, dict) else program_to_dict(program))
     def unregister_program(self, prog_id: str): return self.call("unregister_program", prog_id=prog_id)

@@ -155,11 +155,29 @@ def install(server) -> None:
         pid = program_content_id(program_to_dict(prog))
         if req.get("expect_prog_id") and req["expect_prog_id"] != pid:
             raise ServiceError("VERSION_SKEW", f"client expected {req['expect_prog_id']}, server computed {pid}")
-        server.programs[pid] = {"program": prog, "resolver_spec": req.get("resolver_spec"), "registered": time.time(),
-                                "host": bool(prog.tasks and prog.tasks[0].host), "runs": 0}
+        entry = {"program": prog, "resolver_spec": req.get("resolver_spec"), "registered": time.time(),
+                 "host": bool(prog.tasks and prog.tasks[0].host), "runs": 0, "placement": None}
+        out = {"prog_id": pid, "tasks": len(prog.tasks), "host": entry["host"]}
+        if req.get("prepare_placement") and not entry["host"]:
+            # dry run on the virtual-time backend: every fast allocation of a run gets an offset ahead of time; the extent says
+            # how much pool the program needs when nothing fragments (refused here, not at run time, when it cannot fit)
+            out["placement"] = prepare_placement(entry, req.get("placement_capacity"))
+        server.programs[pid] = entry
         server.state.emit("program_registered", prog_id=pid, name=prog.name)
-        return {"prog_id": pid, "tasks": len(prog.tasks), "host": server.programs[pid]["host"]}
+        return out
     H["register_program"] = register_program
+
+    def prepare_placement(entry, capacity=None) -> dict:
+        from ..runtime.placement import PlacementError, peak_live_bytes, plan_placement
+        prog = entry["program"]
+        cap = int(capacity) if capacity else (int(prog.fast_memory_capacity) if prog.fast_memory_capacity else None)
+        try:
+            pl = plan_placement(prog, cap)
+        except PlacementError as e:
+            raise ServiceError("BAD_REQUEST", f"no static placement fits: {e}") from None
+        entry["placement"] = pl
+        return {"extent_bytes": int(pl.top), "peak_live_bytes": int(peak_live_bytes(pl.lifetimes)), "allocations": len(pl.lifetimes),
+                "capacity": cap}
 
     def validate_program(req, payload):
         try:
@@ -224,8 +242,15 @@ def install(server) -> None:
                         r = st.create(oid, sizes[oid], replace=True)
                         initial[oid] = Buffer(st.address(oid), r.size, "backing", oid)
                 groups = server.nm.group_handles() if server.nm is not None else {}
-                result = _engine(server).execute(prog, resolver, initial, run_args=args, groups=groups,
-                                                 cancel_event=cancel)
+                placement = entry.get("placement") if req.get("use_placement", True) else None
+                eng = _engine(server)
+                if placement is not None:
+                    # planned offsets need a pool that reaches them: the extent of the packing (a program without a capacity of
+                    # its own would otherwise run on exact-size vendor allocations, where offsets mean nothing)
+                    server._session.native.ensure_pools(int(placement.top) + (1 << 20), 0, 0.0)
+                result = eng.execute(prog, resolver, initial, run_args=args, groups=groups,
+                                                 cancel_event=cancel,
+                                                 placement=placement)
                 if result.outcome.kind.value == "SUCCESS":
                     for oid, b in result.finals.items():
                         if b.location == "backing" and oid in st.objects and b.ptr != st.address(oid):
@@ -258,7 +283,7 @@ def install(server) -> None:
                        slab_overflows=result.slab_overflows, pressure_evictions=result.pressure_evictions,
                        placement_escapes=result.placement_escapes)
             out.update(makespan_us=result.makespan_us, peak_fast_bytes=result.peak_fast_bytes,
-                       slab_overflows=result.slab_overflows)
+                       slab_overflows=result.slab_overflows, placement_escapes=result.placement_escapes)
             if req.get("trace"):
                 out["trace"] = trace_to_dict(result.trace)
             rec["trace"] = result.trace

@@ -168,7 +168,14 @@ def test_train_tiny_llama3_through_the_daemon():
         ireg = c.register_program(init, spec)
         assert ireg["host"] and c.run(ireg["prog_id"])["state"] == "done"
         c.unregister_program(ireg["prog_id"])
-        reg = c.register_program(prog, spec)
+        # registration with a placement dry run: the daemon packs every fast allocation of a run ahead of time, reports the
+        # extent, refuses a capacity that cannot hold it, and runs on the placement it found
+        with pytest.raises(ServiceError) as bad:
+            c.register_program(prog, spec, prepare_placement=True, placement_capacity=4096)
+        assert bad.value.code == "BAD_REQUEST" and "no static placement fits" in str(bad.value)
+        reg = c.register_program(prog, spec, prepare_placement=True)
+        pl = reg["placement"]
+        assert pl["allocations"] > 20 and pl["extent_bytes"] >= pl["peak_live_bytes"] > 0
         losses = []
         R = cfg.grad_accum_rounds
         for step in range(3):
@@ -178,6 +185,7 @@ def test_train_tiny_llama3_through_the_daemon():
             out = c.run(reg["prog_id"], args={"step": step + 1, "valid_rows": cfg.tokens_per_round * R},
                         fetch=[f"loss_0_{r}" for r in range(R)])
             losses.append(sum(out["fetched"].values()))
+            assert out["placement_escapes"] == 0 and out["slab_overflows"] == 0
         assert losses[-1] < losses[0] and 6.5 < losses[0] < 7.5
 
 
