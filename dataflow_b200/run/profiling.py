@@ -16,7 +16,7 @@ from typing import Any, Mapping
 
 from ..core import Program, TaskSpec
 
-PROFILE_CACHE_REV = 4
+PROFILE_CACHE_REV = 5
 
 
 def task_signature(t: TaskSpec) -> str:
@@ -62,11 +62,61 @@ def profile_key(trainer, cfg) -> str:
     return hashlib.sha256(json.dumps(desc, sort_keys=True).encode()).hexdigest()[:20]
 
 
-def profile_program(trainer, program: Program | None = None, *, steps: int = 3, use_cache: bool = True) -> dict[str, float]:
-    """signature → median measured µs, from a 1-layer 2-round cut of ``trainer.cfg`` on ``trainer.device``."""
+class PcieContender:
+    """Keeps both PCIe directions busy with pinned copies on two side streams while tasks are timed: in a real step the plan's
+    offloads and prefetches run beside the kernels and take memory bandwidth from them, so costs measured on an idle bus are
+    optimistic.  Off by default (``DATAFLOW_PROFILE_CONTENDER=1``); a no-op without a device."""
+
+    def __init__(self, device: int | None, mib: int = 256):
+        self.device, self.mib = device, int(mib)
+        self._stop = None
+        self._thread = None
+        self.copies = 0
+
+    def __enter__(self):
+        if self.device is None:
+            return self
+        import threading
+        import torch
+        self._stop = threading.Event()
+        n = self.mib << 20
+        host_a, host_b = torch.empty(n, dtype=torch.uint8).pin_memory(), torch.empty(n, dtype=torch.uint8).pin_memory()
+        dev = torch.device("cuda", self.device)
+        dev_a, dev_b = torch.empty(n, dtype=torch.uint8, device=dev), torch.empty(n, dtype=torch.uint8, device=dev)
+        up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+        def loop():
+            while not self._stop.is_set():
+                with torch.cuda.stream(up):
+                    dev_a.copy_(host_a, non_blocking=True)
+                with torch.cuda.stream(down):
+                    host_b.copy_(dev_b, non_blocking=True)
+                up.synchronize()
+                down.synchronize()
+                self.copies += 2
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self._stop is not None:
+            self._stop.set()
+            self._thread.join(timeout=30)
+        return False
+
+
+def profile_program(trainer, program: Program | None = None, *, steps: int = 3, use_cache: bool = True,
+                    soak_seconds: float | None = None, contender: bool | None = None) -> dict[str, float]:
+    """signature → median measured µs, from a 1-layer 2-round cut of ``trainer.cfg`` on ``trainer.device``.
+    ``soak_seconds`` (``DATAFLOW_PROFILE_SOAK``): keep stepping each cut until that much time has passed before the ``steps``
+    steps that count — a power-capped device settles at lower clocks than its first burst shows.  ``contender``
+    (``DATAFLOW_PROFILE_CONTENDER=1``): time the tasks beside busy PCIe lanes (``PcieContender``)."""
+    import time
     from .driver import Trainer, synthetic_rounds
     cfg = trainer.cfg
-    key = profile_key(trainer, cfg)
+    soak = float(os.environ.get("DATAFLOW_PROFILE_SOAK", 0.0)) if soak_seconds is None else float(soak_seconds)
+    contend = (os.environ.get("DATAFLOW_PROFILE_CONTENDER") == "1") if contender is None else bool(contender)
+    key = profile_key(trainer, cfg) + (f"-soak{soak:g}" if soak else "") + ("-contended" if contend else "")
     path = _cache_path(key)
     if use_cache and path.exists() and os.environ.get("DATAFLOW_PROFILE_REFRESH") != "1":
         return json.loads(path.read_text())
@@ -77,14 +127,20 @@ def profile_program(trainer, program: Program | None = None, *, steps: int = 3, 
                      kernels=trainer.K, recompute=False, profile=False,
                      lower_kwargs={"recompute_levels": levels} if levels else None)
         try:
-            for s in range(steps):
-                data = synthetic_rounds(small, tr.rounds, tr.T, getattr(small, "vocab_size"), 7, s)
-                tr.step(data)
-            by_id = {t.id: t for t in tr.program.tasks}
-            for iv in tr.last_result.trace.by_track("compute"):
-                t = by_id.get(iv.name)
-                if t is not None:
-                    out.setdefault(task_signature(t), []).append(iv.end_us - iv.start_us)
+            with PcieContender(trainer.device if contend else None):
+                t0, s = time.perf_counter(), 0
+                while soak and time.perf_counter() - t0 < soak:          # settle the clocks; these steps are not sampled
+                    tr.step(synthetic_rounds(small, tr.rounds, tr.T, getattr(small, "vocab_size"), 7, s))
+                    s += 1
+                by_id = {t.id: t for t in tr.program.tasks}
+                for k in range(steps):
+                    tr.step(synthetic_rounds(small, tr.rounds, tr.T, getattr(small, "vocab_size"), 7, s + k))
+                    if k == 0 and not soak:
+                        continue                                          # the first step of a cold cut warms kernels and pools
+                    for iv in tr.last_result.trace.by_track("compute"):
+                        t = by_id.get(iv.name)
+                        if t is not None:
+                            out.setdefault(task_signature(t), []).append(iv.end_us - iv.start_us)
         finally:
             tr.close()
     med = {k: sorted(v)[len(v) // 2] for k, v in out.items()}

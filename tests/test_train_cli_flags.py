@@ -110,3 +110,29 @@ def test_warm_profiles_prices_the_tasks_and_stops(tmp_path):
     r = _run("--steps", "3", "--warm-profiles", "--out", str(out))
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
     assert "--warm-profiles stops here" in r.stdout and "no steps ran" in r.stdout and "step     1" not in r.stdout
+
+
+def test_task_profiles_soak_first_and_cache_under_their_own_key(tmp_path, monkeypatch):
+    """``soak_seconds`` runs unsampled steps until the time is up before the steps that count (a power-capped device settles
+    below its first burst); a soaked or contended measurement never overwrites the plain one in the cache."""
+    import dataclasses
+    import time
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import Trainer
+    from dataflow_b200.run.profiling import PcieContender, profile_program
+    monkeypatch.setenv("DATAFLOW_PROFILE_CACHE", str(tmp_path))
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
+    tr = Trainer("llama3", cfg, budget_gib=None, device=None, hyper={"lr": 1e-3}, seed=0)
+    try:
+        plain = profile_program(tr)
+        t0 = time.perf_counter()
+        soaked = profile_program(tr, soak_seconds=0.5)
+        assert time.perf_counter() - t0 >= 1.5                     # three cuts, half a second of settling each
+        assert set(soaked) == set(plain) and all(v > 0 for v in soaked.values())
+        names = sorted(p.name for p in tmp_path.iterdir())
+        assert len(names) == 2 and any("-soak0.5" in n for n in names)
+        with PcieContender(None) as c:                             # no device: nothing to contend with
+            assert c.copies == 0
+    finally:
+        tr.close()
