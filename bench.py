@@ -128,7 +128,9 @@ def bench_ours(a) -> dict:
     if a.linear_precision != "bf16":
         hyper["linear_precision"] = a.linear_precision
     from dataflow_b200.lowering import resolve_hardware
-    hw = resolve_hardware(None).shared(world)        # all ranks of the node stream through one host memory
+    # all ranks of the node stream through one host memory: plan with what the host delivers to all of them at once (measured)
+    from dataflow_b200.run.scaling import hardware_as_shared
+    hw = hardware_as_shared(resolve_hardware(None), world, local)
     tr = Trainer(a.family, cfg, budget_gib=budget, device=local, hyper=hyper, seed=0, kernel_set=a.kernels, hw=hw,
                  profile=not a.no_profile, groups=groups, lower_kwargs=lower_kwargs)
     tokens_step = tr.T * tr.rounds
@@ -198,6 +200,7 @@ def bench_ours(a) -> dict:
                  "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows, "pool": _pool_line(tr),
                  "static_placement": tr.placement is not None,
                  "param_gather": getattr(groups.get("dp"), "gather_mode", None),
+                 "host_link_gbs_planned": [round(hw.h2d_gbs, 1), round(hw.d2h_gbs, 1)],
                  "placement_escapes": res.placement_escapes, "pressure_evictions": res.pressure_evictions,
                  "plan_s": tr.plan_s},
         "kernels": {"native_ops": len(tr.K.native_ops()), "lanes": sorted(set(tr.K.describe().values()))},

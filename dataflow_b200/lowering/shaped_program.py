@@ -37,6 +37,7 @@ class ShapedHardware:
     fast_gib: float = 80.0
     peak_tflops_fp8: float = 0.0
     host_gbs: float = 0.0              # host-memory bandwidth per direction shared by all GPUs of a node (0 = unknown)
+    link_gbs: float = 0.0              # what one GPU's host link does alone (set where h2d / d2h were lowered to a share)
 
     def shared(self, ranks_per_node: int) -> "ShapedHardware":
         """The preset as one of ``ranks_per_node`` GPUs sees it: the copy lanes of all GPUs of a node end in the
@@ -44,7 +45,7 @@ class ShapedHardware:
         if ranks_per_node <= 1 or not self.host_gbs:
             return self
         share = self.host_gbs / ranks_per_node
-        return replace(self, h2d_gbs=min(self.h2d_gbs, share), d2h_gbs=min(self.d2h_gbs, share))
+        return replace(self, h2d_gbs=min(self.h2d_gbs, share), d2h_gbs=min(self.d2h_gbs, share), link_gbs=self.link_gbs or self.h2d_gbs)
 
     def matmul_us(self, flops: float, dtype: str = "bf16") -> float:
         peak = self.peak_tflops_fp8 if dtype.startswith("fp8") and self.peak_tflops_fp8 else self.peak_tflops

@@ -149,11 +149,14 @@ class DpGroup(GroupCollectives):
             # The copy engines also carry the plan's host traffic.  Measured on the 8B step: at 2 GPUs the host lanes are busy half
             # of the step and gathers on the copy engines cost 11 % (prefetches fall behind); where the lanes are nearly idle the
             # copy engines are free and the SM kernel's interference with the GEMM is what costs.  So: copy engines only when the
-            # planned host-to-device lane is busy less than a quarter of the step (8 GPUs: 15 %).
+            # planned host-to-device traffic would keep the GPU's own link busy less than a quarter of the step (8 GPUs: 6 %).
             planned = getattr(trainer, "planned", None)
             busy = 1.0
             if planned is not None and planned.makespan_us:
                 busy = float((planned.transfer or {}).get("from_slow", {}).get("busy_us", planned.makespan_us)) / float(planned.makespan_us)
+                hw = getattr(trainer, "hw", None)
+                if hw is not None and getattr(hw, "link_gbs", 0.0):
+                    busy *= float(hw.h2d_gbs) / float(hw.link_gbs)     # lane time at a shared rate -> share of what the link can do
             self.gather_mode = "dma" if busy < 0.25 else "kernel"
         dist.barrier()
 

@@ -133,9 +133,14 @@ def run_rank(spec: RunSpec, log=print) -> RunResult:
         lower_kwargs = {"resident_params": True} if spec.resident_params and device is not None else {}
     recipe = Recipe(**{"total_steps": spec.steps, **spec.recipe})
     say = log if rank == 0 else (lambda *a, **k: None)
+    hw = None
+    if device is not None and world > 1:
+        from ..lowering import resolve_hardware
+        from .scaling import hardware_as_shared
+        hw = hardware_as_shared(resolve_hardware(None), world, device)          # what the host gives all ranks at once
     tr = Trainer(family, cfg, budget_gib=spec.budget_gib, device=device, hyper=recipe.hyper(), seed=spec.seed,
                  kernel_set=spec.kernels, recompute=spec.recompute, profile=spec.profile and device is not None,
-                 groups=groups, lower_kwargs=lower_kwargs or None)
+                 groups=groups, lower_kwargs=lower_kwargs or None, hw=hw)
     if spec.backing_budget_gib is not None and tr.store.total > spec.backing_budget_gib * 2 ** 30:
         need = tr.store.total / 2 ** 30
         tr.close()

@@ -310,3 +310,33 @@ def test_sharded_optimizer_state_restores_at_another_world_size(tmp_path):
     assert len(la) == len(lb) == 4 and la[:2] == lb[:2]
     for x, y in zip(la[2:], lb[2:]):
         assert abs(x - y) / x < 2e-3, (la, lb)
+
+
+def _probe_worker(rank, world, port, out):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from dataflow_b200.lowering import resolve_hardware
+    from dataflow_b200.run.scaling import hardware_as_shared
+    hw = hardware_as_shared(resolve_hardware("b200"), world, 0, probe=lambda dev: (40.0 - 10.0 * rank, 30.0 + 5.0 * rank))
+    out[rank] = (hw.h2d_gbs, hw.d2h_gbs, hw.link_gbs)
+    dist.destroy_process_group()
+
+
+def test_multi_rank_plans_are_priced_with_the_measured_concurrent_host_rate():
+    """Every rank measures its host link while the others do the same; the slowest figure (times 0.95) caps the hardware row all
+    ranks plan with, so the plans stay identical; one rank alone, or ``DATAFLOW_PCIE_PROBE=0``, keeps the preset."""
+    import torch.multiprocessing as mp
+    from dataflow_b200.lowering import resolve_hardware
+    from dataflow_b200.run.scaling import hardware_as_shared
+    base = resolve_hardware("b200")
+    assert hardware_as_shared(base, 1, 0) == base
+    assert hardware_as_shared(base, 4, None) == base.shared(4)
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_probe_worker, args=(2, 29741, out), nprocs=2, join=True)
+        got = dict(out)
+    assert got[0] == got[1]
+    h2d, d2h, link = got[0]
+    assert h2d == pytest.approx(0.95 * 30.0) and d2h == pytest.approx(0.95 * 30.0) and link == base.h2d_gbs
