@@ -1,7 +1,8 @@
 """Analytic training workloads: a model described by dimensions becomes a hardware-free ``WorkloadProgram``.
 
-No tensors are touched: every layer contributes closed-form FLOPs, bytes and saved-activation sizes, and
-``TrainingBuilder`` schedules them into forward / head / backward / recompute / optimizer tasks for a number of
+No tensors are touched: every layer is a module of the workload library (``modules.py``) traced on shape-only tensors
+(``tracing.py``), whose ops (``ops.py``) record forward and backward FLOPs, bytes, saved activations and parameter counts;
+``TrainingBuilder`` schedules the traces into forward / head / backward / recompute / optimizer tasks for a number of
 gradient-accumulation rounds.  The result is priced on any ``HardwareSpec`` (``schema.realize_workload``) and planned
 by any policy — the "what would this model do on that box" path that needs no GPU.
 Reference role: ``src/dataflow_sim/workloads/dataflow_builder/__init__.py:65-463`` (dtype policies, training and
@@ -99,77 +100,6 @@ class ModelSpec:
         return len(self.layers)
 
 
-# ------------------------------------------------------------------------------------------- per-module formulas
-def attn_params(a: AttnSpec, d: int) -> int:
-    if a.kind == "none":
-        return 0
-    if a.kind in ("mla", "dsa"):
-        dq = a.head_dim + a.rope_dim
-        q = (d * a.q_lora + a.q_lora * a.n_heads * dq) if a.q_lora else d * a.n_heads * dq
-        kv = d * (a.kv_lora + a.rope_dim) + a.kv_lora * a.n_heads * (a.head_dim + a.v_head_dim)
-        o = a.n_heads * a.v_head_dim * d
-        idx = d * a.index_heads * a.index_dim + d * a.index_dim + d * a.index_heads if a.kind == "dsa" else 0
-        return q + kv + o + idx
-    if a.kind in ("linear", "mamba"):
-        inner = a.n_heads * a.head_dim
-        return d * (2 * a.n_kv_heads * a.state_dim + 2 * inner) + inner * d + 2 * d * a.n_heads
-    return d * (a.n_heads + 2 * a.n_kv_heads) * a.head_dim + a.n_heads * a.head_dim * d
-
-
-def attn_core_flops(a: AttnSpec, tokens: int, seq: int) -> float:
-    """Forward FLOPs of the score / value part (projections are counted with the parameters)."""
-    if a.kind == "none":
-        return 0.0
-    if a.kind == "dense":
-        span = min(a.window, seq) if a.window else seq
-        causal = 0.5 if not a.window or a.window >= seq else 1.0
-        return 4.0 * tokens * span * a.n_heads * a.head_dim * causal
-    if a.kind == "mla":
-        return 2.0 * tokens * seq * a.n_heads * (a.head_dim + a.rope_dim + a.v_head_dim) * 0.5
-    if a.kind == "dsa":
-        keys = min(a.index_topk or seq, seq)
-        sparse = 2.0 * tokens * keys * a.n_heads * (a.kv_lora + a.rope_dim + a.kv_lora)        # absorbed form
-        index = 2.0 * tokens * seq * a.index_heads * a.index_dim * 0.5
-        return sparse + index
-    # chunked linear recurrences: state update + read per token
-    return 6.0 * tokens * a.n_heads * a.head_dim * max(a.state_dim, 1)
-
-
-def attn_saved_elems(a: AttnSpec, d: int) -> float:
-    """Activation elements saved per token for the backward (no recompute)."""
-    if a.kind == "none":
-        return 0.0
-    if a.kind in ("mla", "dsa"):
-        extra = a.index_topk / 8 + a.index_heads if a.kind == "dsa" else 0          # packed selection bits + index weights
-        return d + a.q_lora + a.kv_lora + a.rope_dim + a.n_heads * (a.head_dim + a.rope_dim) + a.n_heads * a.v_head_dim + extra
-    if a.kind in ("linear", "mamba"):
-        return d + 3 * a.n_heads * a.head_dim + 2 * a.n_kv_heads * a.state_dim
-    return d + (a.n_heads + 2 * a.n_kv_heads) * a.head_dim + a.n_heads * a.head_dim
-
-
-def mlp_params(m: MlpSpec, d: int) -> tuple[int, int]:
-    """(total, active per token)."""
-    gate = 3 if m.kind == "swiglu" else 2
-    if m.kind == "none":
-        return 0, 0
-    if m.kind != "moe":
-        p = gate * d * m.d_ff
-        return p, p
-    eg = 3 if m.expert_act == "swiglu" else 2
-    per = eg * d * m.d_expert
-    shared = m.n_shared * per
-    return m.n_experts * per + shared + d * m.n_experts, m.top_k * per + shared + d * m.n_experts
-
-
-def mlp_saved_elems(m: MlpSpec, d: int) -> float:
-    if m.kind == "none":
-        return 0.0
-    if m.kind != "moe":
-        return d + (2 if m.kind == "swiglu" else 1) * m.d_ff
-    width = (2 if m.expert_act == "swiglu" else 1) * m.d_expert
-    return d + (m.top_k + m.n_shared) * (d + width) + 2 * m.top_k
-
-
 # ------------------------------------------------------------------------------------------- the scheduler
 class TrainingBuilder:
     """Schedules one optimizer step of ``model`` under ``cfg`` into a ``WorkloadProgram``."""
@@ -179,44 +109,30 @@ class TrainingBuilder:
         self.act_b = DTYPE_BYTES[cfg.dtypes.activation]
         self.par_b = DTYPE_BYTES[cfg.dtypes.param]
         self.grad_b = DTYPE_BYTES[cfg.dtypes.grad]
+        self._traces: dict = {}
 
     # -- costs
     def _mm(self, name: str, flops: float, bytes_: float = 0.0) -> SubOp:
         return SubOp(name=name, kind="matmul", flops=flops, dtype=self.cfg.dtypes.compute, bytes=bytes_)
 
+    def trace(self, layer: LayerSpec):
+        """The recorded trace of one layer's block under this configuration (cached per distinct layer spec)."""
+        from .modules import block_from_spec
+        from .tracing import TraceContext, trace_block
+        got = self._traces.get(layer)
+        if got is None:
+            cfg = self.cfg
+            ctx = TraceContext(cfg.tokens_per_round, cfg.seq_len, act_dtype=cfg.dtypes.activation, param_dtype=cfg.dtypes.param,
+                               compute_dtype=cfg.dtypes.compute, grad_dtype=cfg.dtypes.grad, tp=cfg.parallel.tp,
+                               ep=cfg.parallel.ep_group_size, dp=cfg.parallel.dp)
+            got = self._traces[layer] = trace_block(block_from_spec(layer, self.m.d_model), ctx, self.m.d_model)
+        return got
+
     def _layer_cost(self, layer: LayerSpec, backward: bool) -> tuple[WorkloadCost, dict]:
-        cfg, d, T, S = self.cfg, self.m.d_model, self.cfg.tokens_per_round, self.cfg.seq_len
-        tp, ep = cfg.parallel.tp, cfg.parallel.ep_group_size
-        a, m = layer.attn, layer.mlp
-        mult = 2.0 if backward else 1.0                       # dgrad + wgrad
-        ops = []
-        ap = attn_params(a, d)
-        if ap:
-            ops.append(self._mm("attn_proj", mult * 2.0 * T * ap / tp, ap * self.par_b / tp))
-            core = attn_core_flops(a, T, S) / tp
-            ops.append(SubOp(name="attn_core", kind="attention", flops=(2.5 if backward else 1.0) * core, dtype=cfg.dtypes.compute))
-        total, active = mlp_params(m, d)
-        if total:
-            if m.kind == "moe":
-                routed = (active - m.n_shared * (3 if m.expert_act == "swiglu" else 2) * d * m.d_expert - d * m.n_experts)
-                ops.append(self._mm("experts", mult * 2.0 * T * routed, total * self.par_b / ep))
-                if m.n_shared:
-                    ops.append(self._mm("shared_experts", mult * 2.0 * T * (active - routed - d * m.n_experts) / tp))
-                ops.append(self._mm("router", mult * 2.0 * T * d * m.n_experts))
-                ops.append(SubOp(name="dispatch_combine_local", kind="memory", bytes=mult * 4.0 * T * m.top_k * d * self.act_b))
-                if ep > 1:
-                    # dispatch + combine cross the scale-up fabric once each way (and again in the backward)
-                    ops.append(SubOp(name="ep_all_to_all", kind="scale_up", bytes=2.0 * T * m.top_k * d * self.act_b * (ep - 1) / ep))
-            else:
-                ops.append(self._mm("mlp", mult * 2.0 * T * active / tp, total * self.par_b / tp))
-        if tp > 1:
-            # sequence-parallel all-gather + reduce-scatter around attention and around the MLP
-            ops.append(SubOp(name="tp_collectives", kind="scale_up", bytes=mult * 4.0 * T * d * self.act_b * (tp - 1) / tp))
-        elem = (attn_saved_elems(a, d) + mlp_saved_elems(m, d)) / max(tp, 1)
-        ops.append(SubOp(name="elementwise", kind="memory", bytes=(3.0 if backward else 2.0) * T * elem * self.act_b))
-        info = {"params": (ap + total), "local_params": ap / tp + (total / ep if m.kind == "moe" else total / tp),
-                "saved_bytes": int(T * elem * self.act_b)}
-        return WorkloadCost(ops=ops), info
+        tr = self.trace(layer)
+        info = {"params": tr.total_params, "local_params": tr.local_params, "active_params": tr.active_params,
+                "saved_bytes": int(tr.saved_bytes()), "saved_bytes_selective": int(tr.saved_bytes(selective=True))}
+        return WorkloadCost(ops=list(tr.bwd if backward else tr.fwd)), info
 
     # -- program
     def build(self) -> WorkloadProgram:
@@ -268,7 +184,8 @@ class TrainingBuilder:
                                       cost=WorkloadCost(ops=[SubOp(name="embed", kind="memory", bytes=2.0 * x_bytes)]), phase="fwd", tokens=T))
             for i, layer in enumerate(mdl.layers):
                 cost, info = self._layer_cost(layer, False)
-                saved = x_bytes if recompute == "full" else int(info["saved_bytes"] * (0.4 if recompute == "selective" else 1.0))
+                # full recompute keeps the block input only; selective drops what element-wise work rebuilds
+                saved = x_bytes if recompute == "full" else int(info["saved_bytes_selective" if recompute == "selective" else "saved_bytes"])
                 tasks.append(WorkloadTask(id=f"fwd_{r}_{i}", inputs=[f"X_{r}_{i}", f"W_{i}"],
                                           outputs=[WorkloadOutput(id=f"A_{r}_{i}", bytes=saved, type="activation"),
                                                    WorkloadOutput(id=f"X_{r}_{i + 1}", bytes=x_bytes, type="activation")],
@@ -286,9 +203,8 @@ class TrainingBuilder:
                 bcost, info = self._layer_cost(layer, True)
                 act_in = f"A_{r}_{i}"
                 if recompute != "none":
-                    fcost, _ = self._layer_cost(layer, False)
-                    frac = 1.0 if recompute == "full" else 0.35
-                    rc = WorkloadCost(ops=[replace_flops(op, frac) for op in fcost.ops])
+                    tr = self.trace(layer)
+                    rc = WorkloadCost(ops=list(tr.fwd if recompute == "full" else tr.recompute_cheap))
                     tasks.append(WorkloadTask(id=f"recompute_{r}_{i}", inputs=[f"A_{r}_{i}", f"W_{i}"],
                                               outputs=[WorkloadOutput(id=f"R_{r}_{i}", bytes=int(info["saved_bytes"]), type="activation")],
                                               cost=rc, phase="recompute", tokens=T))
@@ -315,15 +231,11 @@ class TrainingBuilder:
                                                                    bytes=(emb + head_params) / shard * (opt_b * 2 + self.par_b + self.grad_b))]),
                                       phase="optimizer"))
         total_params = sum(i["params"] for i in infos) + emb + head_params
-        active = sum(attn_params(l.attn, d) + mlp_params(l.mlp, d)[1] for l in mdl.layers) + emb + head_params
+        active = sum(i["active_params"] for i in infos) + emb + head_params
         md = {"model": mdl.name, "tokens_per_step": T * cfg.rounds, "seq_len": cfg.seq_len, "rounds": cfg.rounds,
               "total_params": int(total_params), "active_params": int(active), "optimizer": cfg.optimizer,
               "recompute": recompute, "parallel": asdict(cfg.parallel)}
         return WorkloadProgram(name=f"{mdl.name}-train", objects=objects, tasks=tasks, final_locations=final, metadata=md)
-
-
-def replace_flops(op: SubOp, frac: float) -> SubOp:
-    return op.model_copy(update={"flops": op.flops * frac, "bytes": op.bytes * frac})
 
 
 def trace_training_model(model: ModelSpec, cfg: TrainingConfig) -> WorkloadProgram:
