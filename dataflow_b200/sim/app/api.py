@@ -131,7 +131,7 @@ def create_app() -> FastAPI:
             log = simulate(planned, memory_trace=req.memory_trace)
         except Exception as e:                      # planner / simulator refusals are the caller's answer, not a crash
             raise HTTPException(status_code=422, detail=f"{type(e).__name__}: {e}") from e
-        out: dict[str, Any] = {"summary": compute_summary(planned, log, prog), "preview": preview_workload(prog, hw),
+        out: dict[str, Any] = {"summary": compute_summary(planned, log, prog, hw), "preview": preview_workload(prog, hw),
                                "policy": req.policy, "metadata": prog.metadata}
         if req.timeline:
             out["timeline"] = [{"id": iv.task_id, "track": iv.track, "start": iv.start, "end": iv.end} for iv in log.task_intervals]

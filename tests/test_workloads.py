@@ -59,6 +59,22 @@ def test_every_library_model_plans_and_simulates(name):
     assert s["makespan_us"] >= preview_workload(prog, hw)["compute_only_us"] * 0.999
 
 
+def test_summary_says_where_the_compute_time_goes():
+    prog = trace_training_model(get_model("llama3_8b"), TrainingConfig(tokens_per_round=16384, rounds=2, recompute="selective"))
+    hw = get_hardware("B200")
+    chain = realize_workload(prog, hw, int(150 * (1 << 30)))
+    planned = get_all_policies()["pressurefit"](chain, chain.fast_memory_capacity)
+    s = compute_summary(planned, simulate(planned), prog, hw)
+    assert abs(sum(s["compute_pct_by_kind"].values()) - 100.0) < 1e-6
+    # a dense transformer at 8k context: the matmuls take most of the time, attention a visible part, element-wise the rest
+    assert s["compute_pct_by_kind"]["matmul"] > 50 and s["compute_pct_by_kind"]["attention"] > 3
+    assert 0 < s["mfu_pct"] < 100 and s["hardware_peak_tflops"] == hw.tflops("bf16")
+    assert s["top_ops"][0]["us"] >= s["top_ops"][-1]["us"] and len(s["top_ops"]) == 10
+    assert s["top_ops"][0]["calls"] >= 32          # one entry per op NAME: 32 layers, two rounds
+    assert abs(sum(s["flops_by_phase"].values()) - s["total_flops"]) < 1e-6 * s["total_flops"]
+    assert 0 <= s["from_slow_util_pct"] <= 100 and s["primary_unit"] == "tokens" and s["primary_count"] == 2 * 16384
+
+
 def test_expert_parallel_is_priced_on_the_scale_up_fabric():
     model = get_model("olmoe_1b_7b")
     solo = trace_training_model(model, TrainingConfig())
