@@ -1,0 +1,139 @@
+"""One invalid chain per rule of the static validator, each made by one edit of a valid annotated chain, plus the property that
+what planners emit passes every stage."""
+from dataclasses import replace
+
+import pytest
+
+from chains import train_chain
+from dataflow_b200.sim import Object, OutputAlloc, Task, TaskChain, TransferTrigger, ValidationError, run, validate_chain
+from dataflow_b200.sim.validate import RULES, chain_problems, check_capacity, validate_planning_input
+
+T = TransferTrigger
+
+
+def base() -> TaskChain:
+    """w lives in backing and is fetched for b; y is parked in backing across b and fetched back for c; z must end in backing."""
+    return TaskChain(
+        [Object("w", 100, "backing", "weight"), Object("x", 10, "fast"), Object("k", 8, "fast"), Object("k", 8, "backing")],
+        [Task("a", ["x"], [OutputAlloc("y", 20)], 5, prefetch_after=[T("w")], offload_after=[T("y")]),
+         Task("b", ["x", "w"], [OutputAlloc("u", 20)], 5, releases_after=["w"], prefetch_after=[T("y")]),
+         Task("c", ["y", "u", "k"], [OutputAlloc("z", 20)], 5, mutates_inputs=["u"], releases_after=["y", "u", "k"], offload_after=[T("z")]),
+         Task("d", ["x"], [], 1, releases_after=["x"])],
+        {"z": "backing", "k": "backing"}, 200, 400, 10, 10)
+
+
+def edit(i: int, **kw):
+    def f(ch: TaskChain) -> TaskChain:
+        tasks = list(ch.tasks)
+        tasks[i] = replace(tasks[i], **kw)
+        return replace(ch, tasks=tasks)
+    return f
+
+
+def both(*fs):
+    def f(ch):
+        for g in fs:
+            ch = g(ch)
+        return ch
+    return f
+
+
+CASES = {
+    # ids
+    "bad-location": lambda ch: replace(ch, initial_memory=ch.initial_memory + [Object("q", 1, "disk")]),
+    "negative-size": edit(0, workspace_bytes=-1),
+    "duplicate-initial-object": lambda ch: replace(ch, initial_memory=ch.initial_memory + [Object("x", 10, "fast")]),
+    "duplicate-task-id": lambda ch: replace(ch, tasks=ch.tasks + [Task("a", ["x"], [], 1)]),
+    "duplicate-input": edit(3, inputs=["x", "x"]),
+    "unknown-input": edit(0, inputs=["x", "nope"]),
+    "output-reuses-id": edit(1, outputs=[OutputAlloc("y", 20)]),
+    "mutation-not-an-input": edit(1, mutates_inputs=["k"]),
+    "unknown-release-object": edit(0, releases_after=["u"]),           # u exists only from task b on
+    "unknown-transfer-object": edit(0, prefetch_after=[T("w"), T("z")]),
+    "unknown-final-object": lambda ch: replace(ch, final_locations={**ch.final_locations, "ghost": "fast"}),
+    "missing-bandwidth": lambda ch: replace(ch, bandwidth_to_slow=None),
+    # transfers
+    "prefetch-already-resident": edit(0, prefetch_after=[T("w"), T("x")]),
+    # x has only a fast copy; a drops it, b asks for it back
+    "prefetch-without-backing-copy": both(edit(0, releases_after=["x"]), edit(1, inputs=["w"], prefetch_after=[T("y"), T("x")]),
+                                          edit(3, inputs=[], releases_after=[])),
+    "offload-not-resident": edit(0, offload_after=[T("y"), T("w")], prefetch_after=[]),
+    "duplicate-transfer": edit(0, prefetch_after=[T("w"), T("w")]),
+    "release-and-offload": edit(2, releases_after=["y", "u", "k", "z"]),
+    "release-not-resident": edit(0, releases_after=["w"], prefetch_after=[]),
+    # lifetimes
+    # y was offloaded by a and never comes back for c
+    "input-not-resident": both(edit(1, prefetch_after=[]), edit(2, releases_after=["u", "k"])),
+    # u is read by c and was never offloaded
+    "release-loses-data": both(edit(1, releases_after=["w", "u"]), edit(2, releases_after=["y", "k"])),
+    "final-not-on-backing": edit(2, offload_after=[]),
+    "final-backing-stale": edit(2, mutates_inputs=["u", "k"], releases_after=["y", "u"]),
+    "final-not-on-fast": lambda ch: replace(ch, final_locations={**ch.final_locations, "w": "fast"}),
+    # capacity
+    "initial-overflow": lambda ch: replace(ch, backing_memory_capacity=50),
+    "task-cannot-fit": lambda ch: replace(ch, fast_memory_capacity=60),
+}
+
+
+def test_the_base_chain_is_valid_and_runs():
+    ch = validate_chain(base())
+    assert chain_problems(ch) == []
+    assert run(ch).makespan > 0
+
+
+@pytest.mark.parametrize("rule", sorted(CASES))
+def test_each_rule_is_reported_by_its_code(rule):
+    bad = CASES[rule](base())
+    with pytest.raises(ValidationError) as e:
+        validate_chain(bad)
+    assert rule in e.value.rules, e.value.problems
+    assert all(p.rule in RULES for p in e.value.found)
+    assert all(str(p).startswith(p.rule + ":") for p in e.value.found)
+
+
+def test_every_rule_has_a_case():
+    assert set(CASES) == set(RULES) - {"already-planned"}
+
+
+def test_a_stage_reports_all_of_its_problems_with_task_and_object():
+    bad = edit(0, inputs=["x", "nope"])(edit(1, mutates_inputs=["k"])(base()))
+    found = chain_problems(bad)
+    assert [(p.rule, p.task, p.obj) for p in found] == [("unknown-input", "a", "nope"), ("mutation-not-an-input", "b", "k")]
+    # a later stage does not run on a chain an earlier one rejected: the capacity problem stays hidden behind the id problems
+    worse = replace(bad, fast_memory_capacity=60)
+    assert {p.rule for p in chain_problems(worse)} == {"unknown-input", "mutation-not-an-input"}
+    assert {p.rule for p in check_capacity(worse)} == {"task-cannot-fit"}
+
+
+def test_release_then_prefetch_in_one_task_drops_and_refetches():
+    ch = TaskChain([Object("w", 40, "backing"), Object("x", 1, "fast")],
+                   [Task("p", ["x"], [], 1, prefetch_after=[T("w")]),
+                    Task("a", ["w"], [], 5, releases_after=["w"], prefetch_after=[T("w")]),
+                    Task("b", ["x"], [], 50),
+                    Task("c", ["w"], [], 5, releases_after=["w"])], {}, 100, None, 10, 10)
+    validate_chain(ch)
+    log = run(ch)
+    assert [iv.task_id for iv in log.task_intervals if iv.track == "from_slow"] == ["from_slow:w", "from_slow:w#1"]
+
+
+def test_planning_input_must_be_bare_and_feasible():
+    with pytest.raises(ValidationError) as e:
+        validate_planning_input(base())
+    assert e.value.rules == ["already-planned"]
+    bare = base().bare()
+    validate_planning_input(bare)
+    with pytest.raises(ValidationError) as e:
+        validate_planning_input(replace(bare, fast_memory_capacity=60))
+    assert e.value.rules == ["task-cannot-fit"] and {p.task for p in e.value.found} == {"b", "c"}
+
+
+@pytest.mark.parametrize("cap", [2500, 3000, 6000])
+def test_what_every_policy_emits_passes_every_stage(cap):
+    from dataflow_b200.sim.policies import get_all_policies
+    for name, policy in get_all_policies().items():
+        try:
+            planned = policy(train_chain(L=4, rounds=2), cap)
+        except Exception as exc:                          # a policy may find a capacity infeasible; that is not this test's subject
+            assert "Planning" in type(exc).__name__ or "Validation" in type(exc).__name__, (name, exc)
+            continue
+        assert chain_problems(planned) == [], name

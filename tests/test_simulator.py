@@ -1,7 +1,7 @@
 import pytest
 
 from dataflow_b200.sim import (Object, OutputAlloc, SimulationCapacityError, SimulationError, Task, TaskChain,
-                               TransferTrigger, run)
+                               TransferTrigger, ValidationError, run)
 
 
 def iv(log):
@@ -67,21 +67,30 @@ def test_workspace_is_charged_only_while_running():
 def test_deadlock_is_an_error_with_context():
     ch = TaskChain([Object("x", 90, "fast")], [Task("a", ["x"], [OutputAlloc("y", 20)], 5)], {}, 100)
     with pytest.raises(SimulationCapacityError) as e:
-        run(ch)
+        run(ch, validate=False)
     assert e.value.kind == "fast-deadlock" and e.value.overage_bytes == 10
+    with pytest.raises(ValidationError) as v:            # the static pass sees it before the clock starts
+        run(ch)
+    assert v.value.rules == ["task-cannot-fit"]
 
 
 def test_dirty_release_of_needed_object_is_refused():
     ch = TaskChain([Object("x", 10, "fast")],
                    [Task("a", ["x"], [], 5, mutates_inputs=["x"], releases_after=["x"]), Task("b", ["x"], [], 5)], {}, 100, None, 10, 10)
     with pytest.raises(SimulationError):
+        run(ch, validate=False)
+    with pytest.raises(ValidationError) as v:
         run(ch)
+    assert v.value.rules == ["release-loses-data", "input-not-resident"]      # both ends of the same mistake
 
 
 def test_final_location_checked():
     ch = TaskChain([Object("x", 10, "fast")], [Task("a", ["x"], [], 5, mutates_inputs=["x"])], {"x": "backing"}, 100, None, 10, 10)
     with pytest.raises(SimulationError):
+        run(ch, validate=False)
+    with pytest.raises(ValidationError) as v:
         run(ch)
+    assert v.value.rules == ["final-not-on-backing"]
 
 
 def test_stall_report_names_the_blocking_transfer():
