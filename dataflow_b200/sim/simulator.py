@@ -231,8 +231,9 @@ class Simulator:
             kind="fast-deadlock", task_id=task.id, capacity_bytes=cap, actual_need_bytes=actual,
             overage_bytes=over, missing_object_ids=tuple(missing), time=now, resident=resident)
 
-    def _finish_task(self, idx: int, task: Task, t: float) -> None:
-        pool, used = self.pool, self.used
+    def _settle_task(self, idx: int, task: Task, t: float) -> None:
+        """The task has ended: its workspace is gone, its outputs are live, what it wrote is dirty."""
+        pool = self.pool
         self.workspace = 0
         for out in task.outputs:
             e = pool[(out.id, out.location)]
@@ -241,7 +242,15 @@ class Simulator:
         for m in task.mutates_inputs:
             pool[(m, FAST)].dirty = True
         self._note("task_end", t, task_id=task.id)
+
+    def _finish_task(self, idx: int, task: Task, t: float) -> None:
+        self._settle_task(idx, task, t)
         self._before_directives(idx, task, t)
+        self._apply_directives(idx, task, t)
+
+    def _apply_directives(self, idx: int, task: Task, t: float) -> None:
+        """Releases first (they free at once), then offloads and prefetches join their lanes, then both lanes are retried."""
+        pool, used = self.pool, self.used
         if task.releases_after:
             for obj in task.releases_after:
                 e = pool.get((obj, FAST))
@@ -301,7 +310,8 @@ class Simulator:
             self._note("transfer_enqueue", t, transfer_obj=trig.obj_id, transfer_direction="from_slow")
         self._poke(t)
 
-    def run(self) -> EventLog:
+    def begin(self) -> None:
+        """Load the initial objects; the clock is at zero."""
         chain, pool, used = self.chain, self.pool, self.used
         for o in chain.initial_memory:
             if (o.id, o.location) in pool:
@@ -315,51 +325,67 @@ class Simulator:
                     kind="initial", location=loc, capacity_bytes=self.cap[loc],
                     actual_need_bytes=used[loc], overage_bytes=used[loc] - self.cap[loc])
         self.peak_fast, self.peak_backing = used[FAST], used[BACKING]
-        now = 0.0
-        for idx, task in enumerate(chain.tasks):
-            free_at = now
-            need = task.workspace_bytes
-            for out in task.outputs:
-                if out.location == FAST:
-                    need += out.size
-            self._advance(now)
-            while True:
-                missing, short = self._blocked_reason(task, need)
-                if not missing and not short:
-                    break
-                if task.id not in self.stall_causes:
-                    self.stall_causes[task.id] = (tuple(missing), bool(short))
-                t, d = self._next_completion()
-                if d is None:
-                    if self._on_deadlock(idx, task, now, need, missing):
-                        continue
-                    self._deadlock(task, now, need, missing)
-                now = self._complete(d)
-            b_need = sum(o.size for o in task.outputs if o.location == BACKING)
-            if b_need and self.cap[BACKING] is not None and used[BACKING] + b_need > self.cap[BACKING]:
-                raise SimulationCapacityError(
-                    f"task {task.id!r} cannot allocate {b_need} bytes on backing", kind="backing-output",
-                    task_id=task.id, location=BACKING, capacity_bytes=self.cap[BACKING],
-                    actual_need_bytes=used[BACKING] + b_need,
-                    overage_bytes=used[BACKING] + b_need - self.cap[BACKING])
-            for out in task.outputs:
-                key = (out.id, out.location)
-                if key in pool:
-                    raise SimulationError(f"task {task.id!r} output {out.id!r} collides with an existing object")
-                pool[key] = _Entry(out.size, "reserved", out.type)
-                used[out.location] += out.size
-            self.workspace = task.workspace_bytes
-            if now > free_at:
-                self.stalls[task.id] = now - free_at
-            else:
-                self.stall_causes.pop(task.id, None)
-            end = now + task.runtime
-            self.intervals.append(TaskInterval(task.id, now, end, "compute"))
-            self._note("task_start", now, task_id=task.id)
-            # transfers ending at exactly ``end`` retire before the task does
-            self._advance(end)
-            now = end
+        self.now = 0.0
+
+    def _run_task(self, idx: int, task: Task) -> float:
+        """Wait until the task can start, run it, retire the transfers that end while it runs; returns its end time.
+        The task is not settled yet (its outputs are reserved, its directives not applied)."""
+        pool, used = self.pool, self.used
+        now = self.now
+        free_at = now
+        need = task.workspace_bytes
+        for out in task.outputs:
+            if out.location == FAST:
+                need += out.size
+        self._advance(now)
+        while True:
+            missing, short = self._blocked_reason(task, need)
+            if not missing and not short:
+                break
+            if task.id not in self.stall_causes:
+                self.stall_causes[task.id] = (tuple(missing), bool(short))
+            t, d = self._next_completion()
+            if d is None:
+                if self._on_deadlock(idx, task, now, need, missing):
+                    continue
+                self._deadlock(task, now, need, missing)
+            now = self._complete(d)
+        b_need = sum(o.size for o in task.outputs if o.location == BACKING)
+        if b_need and self.cap[BACKING] is not None and used[BACKING] + b_need > self.cap[BACKING]:
+            raise SimulationCapacityError(
+                f"task {task.id!r} cannot allocate {b_need} bytes on backing", kind="backing-output",
+                task_id=task.id, location=BACKING, capacity_bytes=self.cap[BACKING],
+                actual_need_bytes=used[BACKING] + b_need,
+                overage_bytes=used[BACKING] + b_need - self.cap[BACKING])
+        for out in task.outputs:
+            key = (out.id, out.location)
+            if key in pool:
+                raise SimulationError(f"task {task.id!r} output {out.id!r} collides with an existing object")
+            pool[key] = _Entry(out.size, "reserved", out.type)
+            used[out.location] += out.size
+        self.workspace = task.workspace_bytes
+        if now > free_at:
+            self.stalls[task.id] = now - free_at
+        else:
+            self.stall_causes.pop(task.id, None)
+        end = now + task.runtime
+        self.intervals.append(TaskInterval(task.id, now, end, "compute"))
+        self._note("task_start", now, task_id=task.id)
+        # transfers ending at exactly ``end`` retire before the task does
+        self._advance(end)
+        self.now = end
+        return end
+
+    def run(self) -> EventLog:
+        self.begin()
+        for idx, task in enumerate(self.chain.tasks):
+            end = self._run_task(idx, task)
             self._finish_task(idx, task, end)
+        return self.finish()
+
+    def finish(self) -> EventLog:
+        """Drain the lanes, check the final locations, return the log."""
+        chain, pool, used = self.chain, self.pool, self.used
         while True:
             t, d = self._next_completion()
             if d is None:
