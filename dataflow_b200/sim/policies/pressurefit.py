@@ -165,8 +165,11 @@ def _xfer_us(size: int, bw: int | None) -> float:
 
 
 def residency_sweep(chain: TaskChain, facts: dict[str, ObjFacts], cap: int | None,
-                    spec: ResidencySpec) -> Residency:
+                    spec: ResidencySpec, extra_pressure: dict[int, int] | None = None) -> Residency:
+    """``extra_pressure``: bytes to hold free during given tasks on top of what the accounting sees (what a verified run
+    reported as in flight there)."""
     tasks = chain.tasks
+    extra_pressure = extra_pressure or {}
     n = len(tasks)
     start = [0.0] * (n + 1)
     for i, t in enumerate(tasks):
@@ -239,7 +242,7 @@ def residency_sweep(chain: TaskChain, facts: dict[str, ObjFacts], cap: int | Non
                 resident.add(inp)
                 dirty[inp] = False
                 charged += facts[inp].size
-        need_now = t.workspace_bytes
+        need_now = t.workspace_bytes + extra_pressure.get(i, 0)
         for out in t.outputs:
             if out.location == "fast":
                 need_now += out.size
@@ -410,6 +413,53 @@ class Candidate:
     peak_fast: int | None
     error: str | None = None
     repairs: int = 0
+    wall_s: float = 0.0
+
+    @property
+    def name(self) -> str:
+        return f"{self.spec}/{self.rule}"
+
+    @property
+    def status(self) -> str:
+        return "failed" if self.makespan is None else ("repaired" if self.repairs else "ok")
+
+
+@dataclass(frozen=True)
+class PressureFitDiagnostics:
+    """What one planning call did, for logs and for the planner panel: the size of the problem, every candidate with its
+    outcome and cost, which one won and by how much."""
+    planning_s: float
+    task_count: int
+    object_count: int
+    fast_memory_capacity: int | None
+    forced_peak_bytes: int                  # the largest inputs + outputs + workspace of any one task: no plan holds less
+    max_task_workspace_bytes: int
+    candidate_count: int
+    valid_candidate_count: int
+    repaired_candidate_count: int
+    selected: str
+    selected_makespan_us: float
+    lower_bound_us: float
+    spread: float                           # worst valid makespan / selected makespan
+    refined_moves: int
+    early_exit: bool
+    candidates: tuple[Candidate, ...]
+
+    def format(self, limit: int = 12) -> str:
+        cap = "unbounded" if self.fast_memory_capacity is None else f"{self.fast_memory_capacity / 2**30:.2f} GiB"
+        lines = [f"PressureFit: {self.task_count} tasks, {self.object_count} objects, fast memory {cap} "
+                 f"(largest task holds {self.forced_peak_bytes / 2**30:.2f} GiB), planned in {self.planning_s:.2f} s",
+                 f"  {self.valid_candidate_count}/{self.candidate_count} candidates valid ({self.repaired_candidate_count} after repair)"
+                 f"{', stopped early at the lower bound' if self.early_exit else ''}; selected {self.selected}: "
+                 f"{self.selected_makespan_us:.0f} us = {self.selected_makespan_us / max(self.lower_bound_us, 1e-9):.3f} x lower bound"
+                 f"{f', {self.refined_moves} fetches fired earlier' if self.refined_moves else ''}; spread {self.spread:.2f}x"]
+        ranked = sorted(self.candidates, key=lambda c: (c.makespan is None, c.makespan or 0.0))
+        for c in ranked[:limit]:
+            what = f"{c.makespan:.0f} us, peak {c.peak_fast / 2**30:.2f} GiB" if c.makespan is not None else f"failed: {(c.error or '')[:80]}"
+            lines.append(f"    {c.name:<28} {c.status:<9} {c.wall_s * 1e3:7.1f} ms  {what}")
+        if len(ranked) > limit:
+            lines.append(f"    ... {len(ranked) - limit} more")
+        return "\n".join(lines)
 
 
 @dataclass
@@ -421,49 +471,90 @@ class PressureFitResult:
     chosen: Candidate
     candidates: list[Candidate]
     early_exit: bool
+    planning_s: float = 0.0
+    refined_moves: int = 0
 
     @property
     def idle_fraction(self) -> float:
         return 0.0 if self.makespan <= 0 else 1.0 - self.lower_bound / self.makespan
 
+    def diagnostics(self) -> PressureFitDiagnostics:
+        from .spans import static_minimum
+        ch = self.chain
+        valid = [c for c in self.candidates if c.makespan is not None]
+        forced = static_minimum(ch.bare())
+        return PressureFitDiagnostics(
+            planning_s=self.planning_s, task_count=len(ch.tasks), object_count=len(ch.sizes()),
+            fast_memory_capacity=ch.fast_memory_capacity, forced_peak_bytes=int(forced.max(initial=0.0)),
+            max_task_workspace_bytes=max((t.workspace_bytes for t in ch.tasks), default=0),
+            candidate_count=len(self.candidates), valid_candidate_count=len(valid),
+            repaired_candidate_count=sum(1 for c in valid if c.repairs), selected=self.chosen.name,
+            selected_makespan_us=self.makespan, lower_bound_us=self.lower_bound,
+            spread=max((c.makespan for c in valid), default=self.makespan) / max(self.makespan, 1e-9),
+            refined_moves=self.refined_moves, early_exit=self.early_exit, candidates=tuple(self.candidates))
+
 
 def _build(chain: TaskChain, cap_eff: int | None, cap: int | None, spec: ResidencySpec,
-           rule: PrefetchRule) -> TaskChain:
+           rule: PrefetchRule, extra_pressure: dict[int, int] | None = None) -> TaskChain:
     facts = gather_facts(chain)
-    res = residency_sweep(chain, facts, cap_eff, spec)
+    res = residency_sweep(chain, facts, cap_eff, spec, extra_pressure)
     anchors = assign_anchors(chain, res.reloads, rule)
     return emit_plan(chain, facts, res, anchors, cap)
 
 
+LOCAL_REPAIRS = 8        # dead-locks answered by holding bytes free at the task that dead-locked
+GLOBAL_REPAIRS = 6       # then by planning against a smaller capacity everywhere
+
+
 def _verify_candidate(chain: TaskChain, cap: int | None, spec: ResidencySpec, rule: PrefetchRule,
-                      max_repairs: int = 6):
+                      max_repairs: int = GLOBAL_REPAIRS, local_repairs: int = LOCAL_REPAIRS):
+    """Build, simulate, repair.  The sweep accounts bytes task by task on the stall-free clock; the run can hold more (an
+    offload keeps its fast copy until it completes, a fetch that was fired early is charged from its start).  When the run
+    dead-locks on fast memory the simulator says at which task and by how many bytes: that much is first held free at
+    that task and the two before it (local repair: the rest of the plan is untouched); if the same run keeps failing, the
+    whole plan is rebuilt against a smaller capacity (global repair)."""
     cap_eff = cap
     last_err = None
-    for attempt in range(max_repairs + 1):
-        planned = _build(chain, cap_eff, cap, spec, rule)
+    extra: dict[int, int] = {}
+    index = {t.id: i for i, t in enumerate(chain.tasks)}
+    local_left = local_repairs if cap is not None else 0
+    attempt = 0
+    while attempt <= max_repairs + local_repairs:
+        planned = _build(chain, cap_eff, cap, spec, rule, extra)
         try:
             log = Simulator(planned).run()
             return planned, log, attempt, None
         except SimulationCapacityError as e:
             last_err = e
+            attempt += 1
             if cap is None:
                 break
             shrink = int(e.overage_bytes or 0)
+            j = index.get(e.task_id or "")
+            if local_left > 0 and e.kind == "fast-deadlock" and j is not None and shrink > 0:
+                local_left -= 1
+                for k in range(max(j - 2, 0), j + 1):
+                    extra[k] = extra.get(k, 0) + shrink + (cap >> 7)
+                continue
+            local_left = 0
             cap_eff = int(min(cap_eff - shrink, cap_eff * 0.94)) if cap_eff else cap_eff
-            if cap_eff is None or cap_eff <= 0:
+            if cap_eff is None or cap_eff <= 0 or attempt > max_repairs + local_repairs:
                 break
         except SimulationError as e:
             last_err = e
             break
-    return None, None, max_repairs, last_err
+    return None, None, attempt, last_err
 
 
 def pressurefit(chain: TaskChain, fast_memory_capacity: int | None = None, *,
                 specs: Sequence[ResidencySpec] | None = None,
                 rules: Sequence[PrefetchRule] | None = None,
                 early_exit: bool = True, validate: bool = True,
-                rel_tolerance: float = 1e-9) -> PressureFitResult:
-    """Plan ``chain`` under ``fast_memory_capacity`` (defaults to the chain's own field)."""
+                rel_tolerance: float = 1e-9, refine: bool = True) -> PressureFitResult:
+    """Plan ``chain`` under ``fast_memory_capacity`` (defaults to the chain's own field).  ``refine``: fire the fetches the
+    winning run waited for earlier where the simulator confirms a gain of more than 0.1 % (``policies.refine``)."""
+    import time
+    t_begin = time.perf_counter()
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
     if validate:
@@ -474,11 +565,13 @@ def pressurefit(chain: TaskChain, fast_memory_capacity: int | None = None, *,
     exited = False
     for spec in (specs or RESIDENCY_SPECS):
         for rule in (rules or PREFETCH_RULES):
+            t0 = time.perf_counter()
             planned, log, repairs, err = _verify_candidate(base, cap, spec, rule)
+            wall = time.perf_counter() - t0
             if planned is None:
-                cands.append(Candidate(spec.name, rule.name, None, None, str(err)[:300], repairs))
+                cands.append(Candidate(spec.name, rule.name, None, None, str(err)[:300], repairs, wall))
                 continue
-            c = Candidate(spec.name, rule.name, log.makespan, log.peak_fast_memory_bytes, None, repairs)
+            c = Candidate(spec.name, rule.name, log.makespan, log.peak_fast_memory_bytes, None, repairs, wall)
             cands.append(c)
             if best is None or log.makespan < best[1].makespan - 1e-12:
                 best = (planned, log, c)
@@ -491,7 +584,16 @@ def pressurefit(chain: TaskChain, fast_memory_capacity: int | None = None, *,
         detail = "; ".join(f"{c.spec}/{c.rule}: {c.error}" for c in cands[:3])
         raise PlanningError(f"no PressureFit candidate fits {cap} bytes of fast memory ({detail})")
     planned, log, c = best
-    return PressureFitResult(planned, log.makespan, log.peak_fast_memory_bytes, lower, c, cands, exited)
+    moves = 0
+    if refine and log.stalls:
+        from .refine import refine_leads
+        p2, l2, moves = refine_leads(planned, log)
+        if moves and l2.makespan < log.makespan * 0.999:
+            planned, log = p2, l2
+        else:
+            moves = 0
+    return PressureFitResult(planned, log.makespan, log.peak_fast_memory_bytes, lower, c, cands, exited,
+                             time.perf_counter() - t_begin, moves)
 
 
 def apply_pressurefit_policy(chain: TaskChain, fast_memory_capacity: int | None = None, **kw) -> TaskChain:

@@ -237,3 +237,50 @@ def test_reactive_fetches_late_and_keeps_the_lane_in_need_order():
             nxt = [u for u in need[tr.obj_id] if u > i]
             assert nxt and nxt[0] - i <= 64
     assert log.peak_fast_memory_bytes <= 3000
+
+
+# ------------------------------------------------------------------------------------------- refinement and diagnostics
+def test_lead_refinement_fires_a_late_fetch_earlier_and_only_keeps_gains():
+    from dataflow_b200.sim import TransferTrigger
+    from dataflow_b200.sim.policies.refine import refine_leads
+    # w is fetched right before its use: c waits 100 us.  Fired after a instead, it arrives in time.
+    ch = TaskChain([Object("w", 1000, "backing", "weight"), Object("x", 10, "fast")],
+                   [Task("a", ["x"], [], 60), Task("b", ["x"], [], 60, prefetch_after=[TransferTrigger("w")]),
+                    Task("c", ["x", "w"], [], 10, releases_after=["w"])], {}, 2000, None, 10, 10)
+    log = run(ch)
+    assert log.stalls == {"c": 100.0}
+    better, log2, moves = refine_leads(ch, log)
+    assert moves == 1 and log2.makespan == log.makespan - 60 and [t.obj_id for t in better.tasks[0].prefetch_after] == ["w"]
+    assert chain_problems(better) == []
+    # nothing waits any more: a second pass changes nothing and returns the same chain
+    again, log3, moves3 = refine_leads(better, log2)
+    assert moves3 == 0 and again is better
+    # where the earlier fetch does not fit (capacity leaves no room for w during a) the move is refused
+    tight = replace(ch, fast_memory_capacity=1010, tasks=[replace(ch.tasks[0], workspace_bytes=900)] + ch.tasks[1:])
+    same, _, moves4 = refine_leads(tight)
+    assert run(same).makespan <= run(tight).makespan and run(same).peak_fast_memory_bytes <= 1010
+
+
+def test_pressurefit_diagnostics_describe_the_search():
+    from dataflow_b200.sim.policies.pressurefit import pressurefit
+    r = pressurefit(train_chain(L=4, rounds=2), 3000)
+    d = r.diagnostics()
+    assert d.task_count == len(r.chain.tasks) and d.fast_memory_capacity == 3000 and d.forced_peak_bytes == 1600
+    assert d.candidate_count == len(r.candidates) and 0 < d.valid_candidate_count <= d.candidate_count
+    assert d.selected == r.chosen.name and d.selected_makespan_us == r.makespan and d.spread >= 1.0
+    assert {c.status for c in d.candidates} <= {"ok", "repaired", "failed"} and all(c.wall_s >= 0 for c in d.candidates)
+    text = d.format(4)
+    assert "candidates valid" in text and d.selected in text and "x lower bound" in text
+
+
+def test_pressurefit_repairs_locally_before_it_shrinks_the_capacity():
+    import importlib
+    pf = importlib.import_module("dataflow_b200.sim.policies.pressurefit")
+    ch = train_chain(L=6, rounds=2).bare()
+    spec = next(s for s in pf.RESIDENCY_SPECS if s.name == "belady")
+    rule = next(r for r in pf.PREFETCH_RULES if r.name == "window_2")
+    planned, log, repairs, err = pf._verify_candidate(ch, 2600, spec, rule)
+    only_global = pf._verify_candidate(ch, 2600, spec, rule, local_repairs=0)
+    assert planned is not None and log.peak_fast_memory_bytes <= 2600
+    if only_global[0] is not None:
+        assert log.makespan <= only_global[1].makespan * 1.05
