@@ -94,6 +94,20 @@ def test_plan_program_auto_takes_the_better_planner():
     assert c.policy.startswith("lookahead:")
 
 
+def test_plan_program_wide_adds_the_span_planners(monkeypatch):
+    from dataflow_b200.lowering.planning import plan_program
+    from dataflow_b200.runtime import Engine, FakeBackend
+    prog = from_sim_chain(train_chain())
+    a = plan_program(prog, 2500, leeway_bytes=0, policy="auto")
+    w = plan_program(prog, 2500, leeway_bytes=0, policy="wide")
+    assert w.makespan_us <= a.makespan_us + 1e-9 and w.candidates > a.candidates
+    monkeypatch.setenv("DATAFLOW_PLANNER", "wide")          # the run-wide switch replaces "auto"
+    e = plan_program(prog, 2500, leeway_bytes=0)
+    assert e.makespan_us == w.makespan_us and e.policy == w.policy
+    res = Engine(FakeBackend()).execute(w.program).raise_if_failed()        # what the wide portfolio picks runs on the engine
+    assert res.peak_fast_bytes <= 2500
+
+
 @pytest.mark.parametrize("cap", [None, 20000, 3000])
 def test_every_registered_policy_produces_a_plan_the_simulator_accepts(cap):
     from dataflow_b200.sim.policies import get_all_policies

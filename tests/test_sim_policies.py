@@ -284,3 +284,18 @@ def test_pressurefit_repairs_locally_before_it_shrinks_the_capacity():
     assert planned is not None and log.peak_fast_memory_bytes <= 2600
     if only_global[0] is not None:
         assert log.makespan <= only_global[1].makespan * 1.05
+
+
+@pytest.mark.parametrize("name", sorted(NEW))
+@pytest.mark.parametrize("cap", [6000, 3000])
+def test_the_engine_reproduces_the_simulated_log_of_every_planner(name, cap):
+    from dataflow_b200.core import from_sim_chain
+    from dataflow_b200.runtime import Engine, FakeBackend, compare_to_sim_eventlog
+    try:
+        planned = NEW[name](train_chain(L=6, rounds=2), cap)
+    except PlanningError:
+        pytest.skip("the fixed pattern does not fit this capacity")
+    log = run(planned)
+    res = Engine(FakeBackend()).execute(from_sim_chain(planned)).raise_if_failed()
+    assert compare_to_sim_eventlog(res.trace, log) == []
+    assert res.makespan_us == log.makespan and res.peak_fast_bytes <= cap
