@@ -54,6 +54,11 @@ def main(argv=None) -> int:
     ap.add_argument("--budgets", default=None, help="GiB list; or use --budget-range lo,hi with --budget-step")
     ap.add_argument("--budget-range", default=None)
     ap.add_argument("--budget-step", type=float, default=10.0)
+    ap.add_argument("--host-share", type=float, default=None,
+                    help="share of the host link this device gets (0-1]: predictions price transfers at that share (a device whose "
+                         "neighbours stream over the same host memory does not get the whole link)")
+    ap.add_argument("--backing-gib", type=float, default=None,
+                    help="host memory available to the run: cells whose plan needs more backing memory than this are predicted but not measured")
     ap.add_argument("--max-cells", "--target-cells", dest="max_cells", type=int, default=6)
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--device", default="0")
@@ -81,6 +86,11 @@ def main(argv=None) -> int:
                                 tflops=None, bw=None, pcie=None)
         cells_by_opt[opt] = (ns, list(grid_cells(ns)))
     hw = hardware_from(next(iter(cells_by_opt.values()))[0])
+    if a.host_share:
+        if not 0.0 < a.host_share <= 1.0:
+            ap.error("--host-share is a share of the link: give a value in (0, 1]")
+        import dataclasses
+        hw = dataclasses.replace(hw, h2d_gbs=hw.h2d_gbs * a.host_share, d2h_gbs=hw.d2h_gbs * a.host_share, link_gbs=hw.link_gbs or hw.h2d_gbs)
     flat = [(opt, c) for opt, (_, cells) in cells_by_opt.items() for c in cells]
     env = stage(a.out, "env_probe", a.resume, lambda: env_probe(device, ROOT)) if "env_probe" in stages else {}
     measured_costs = {}
@@ -105,7 +115,12 @@ def main(argv=None) -> int:
             rows.append(row)
         return rows
     pred = stage(a.out, "predict", a.resume, predict) if "predict" in stages else []
-    chosen = stage(a.out, "select", a.resume, lambda: select_cells(pred, a.max_cells)) if "select" in stages else []
+    def choose():
+        usable = pred
+        if a.backing_gib is not None:          # a plan that needs more host memory than the run may use is not measured
+            usable = [r if r.get("backing_gib", 0.0) <= a.backing_gib else {**r, "s_step": None, "note": "needs more backing memory"} for r in pred]
+        return select_cells(usable, a.max_cells)
+    chosen = stage(a.out, "select", a.resume, choose) if "select" in stages else []
     meas = []
     if "measure" in stages:
         def one(fam, cfg, budget):

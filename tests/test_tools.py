@@ -130,3 +130,35 @@ def test_planner_quality_gate_quick_corpus_holds_its_baseline(capsys):
     assert mod.main(["--quick", "--check"]) == 0
     out = capsys.readouterr().out
     assert "12 scenarios" in out and "REGRESSION" not in out
+
+
+def test_pretrain_report_tables_figures_and_band(tmp_path, capsys):
+    import math
+    import re
+    import xml.dom.minidom
+    rep = tool("train/pretrain_report.py")
+
+    def run(name, wobble, n=40, nan_at=None):
+        losses = [6 * math.exp(-i / 25) + 1 + wobble * ((i * 7919) % 13) / 13 for i in range(n)]
+        if nan_at is not None:
+            losses[nan_at] = float("nan")
+        p = tmp_path / name
+        p.write_text(json.dumps({"losses": losses, "step_wall_s": [0.5 + (3.0 if i == 0 else 0.0) + 0.001 * (i % 5) for i in range(n)],
+                                 "tokens_per_step": 4096, "meta": {"preset": "tiny", "world": 2, "policy": "lookahead:cost_aware"}}))
+        return str(p)
+    a, b, c = run("a.json", 0.01), run("b.json", 0.012), run("c.json", 0.9)
+    (tmp_path / "ev.jsonl").write_text(json.dumps({"checkpoint": 20, "loss": 3.9}) + "\nnot json\n")
+    page = tmp_path / "r.html"
+    assert rep.main([a, b, "--html", str(page), "--band", "0.05", "--evals", str(tmp_path / "ev.jsonl")]) == 0
+    out = capsys.readouterr().out
+    assert "band 5.0 %" in out and "inside" in out and "a.json" in out
+    text = page.read_text()
+    svgs = re.findall(r"<svg.*?</svg>", text, flags=re.S)
+    assert len(svgs) == 3
+    for s in svgs:
+        xml.dom.minidom.parseString(s)
+    assert "slowest steps: step 1" in text and "lookahead:cost_aware" in text and "<circle" in svgs[0]       # the warm-up step, the held-out point
+    assert rep.main([a, c, "--band", "0.05"]) == 1 and "outside from step" in capsys.readouterr().out            # a curve that leaves the band fails
+    r = rep.load_run(run("n.json", 0.0, nan_at=5), 3)
+    assert r["non_finite"] == 1 and r["tok_s"] == pytest.approx(4096 / r["s_step_p50"])
+    assert rep.band_report({"losses": []}, {"losses": [1.0]}, 0.1) == {"steps": 0}
