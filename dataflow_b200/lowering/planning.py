@@ -132,7 +132,7 @@ def plan_program(program: Program, fast_memory_capacity: int | None, *, recomput
                 try:
                     cand = table[name](chain, cap)
                     ms = simulate(cand, validate=False).makespan
-                except PlanningError as e:
+                except (PlanningError, ValueError) as e:          # no plan of this shape, or a chain this planner refuses
                     errors.append(str(e))
                     continue
                 ncand += 1

@@ -17,14 +17,12 @@ Reference role: ``src/dataflow_sim/policies/max_reduce.py`` (residency by accoun
 """
 from __future__ import annotations
 
-from dataclasses import replace
 
 import numpy as np
 
 from ..schema import TaskChain
-from ..validate import validate_planning_input
 from .pressurefit import PlanningError
-from .spans import SpanPlan, verify
+from .spans import SpanPlan, check_input, verify
 
 
 def reduce_to_fit(plan: SpanPlan, cap: float, slack: float = 1.0) -> int:
@@ -85,7 +83,7 @@ def reduce_to_fit(plan: SpanPlan, cap: float, slack: float = 1.0) -> int:
 def max_reduce(chain: TaskChain, fast_memory_capacity: int | None = None, slack: float = 1.0) -> TaskChain:
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
-    validate_planning_input(replace(base, fast_memory_capacity=cap))
+    check_input(base, cap, "max_reduce")
 
     def build(cap_eff):
         plan = SpanPlan(base).fill_max(slack=slack)

@@ -21,16 +21,15 @@ Reference role: ``src/dataflow_sim/policies/min_grow.py`` (plan search priced by
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, replace
+from dataclasses import dataclass
 
 import numpy as np
 
 from ..errors import SimulationCapacityError, SimulationError
 from ..schema import TaskChain
 from ..simulator import Simulator
-from ..validate import validate_planning_input
 from .pressurefit import PlanningError
-from .spans import SpanPlan
+from .spans import SpanPlan, check_input
 
 
 @dataclass(frozen=True)
@@ -137,7 +136,7 @@ def repair_stalls(plan: SpanPlan, log, cap: int | None, work: float | None) -> b
 def min_grow(chain: TaskChain, fast_memory_capacity: int | None = None, beam: int = 3, rounds: int = 4) -> TaskChain:
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
-    validate_planning_input(replace(base, fast_memory_capacity=cap))
+    check_input(base, cap, "min_grow")
     grid = [GrowKnobs(h, s, p) for p in ("time", "tasks") for h in (0.0, 0.03, 0.08, 0.15) for s in (1.0, 1.5, 2.5)]
     if cap is None:
         grid = [GrowKnobs(0.0, 1.5, "time")]

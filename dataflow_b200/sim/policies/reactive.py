@@ -19,13 +19,12 @@ Reference role: ``src/dataflow_sim/policies/belady_reactive.py`` (a forward walk
 """
 from __future__ import annotations
 
-from dataclasses import replace
 
 from ..errors import SimulationCapacityError, SimulationError
 from ..schema import TaskChain
-from ..validate import validate_planning_input
 from .pressurefit import PlanningError
 from .shadow import Shadow
+from .spans import check_input
 
 INF = float("inf")
 
@@ -58,7 +57,7 @@ class _Future:
 def belady_reactive(chain: TaskChain, fast_memory_capacity: int | None = None, horizon: int = 64, slack: float = 1.1) -> TaskChain:
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
-    validate_planning_input(replace(base, fast_memory_capacity=cap))
+    check_input(base, cap, "belady_reactive")
     tasks = base.tasks
     n = len(tasks)
     fut = _Future(base)

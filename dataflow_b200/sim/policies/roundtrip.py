@@ -24,14 +24,12 @@ trips packed on two stream timelines).
 """
 from __future__ import annotations
 
-from dataclasses import replace
 
 import numpy as np
 
 from ..schema import TaskChain
-from ..validate import validate_planning_input
 from .pressurefit import PlanningError
-from .spans import LaneTimeline, SpanPlan, verify
+from .spans import LaneTimeline, SpanPlan, check_input, verify
 
 
 def _task_at(plan: SpanPlan, t: float) -> int:
@@ -149,7 +147,7 @@ def build_plan(chain: TaskChain, cap: float | None, place_share: float = 0.9) ->
 def roundtrip_planner(chain: TaskChain, fast_memory_capacity: int | None = None) -> TaskChain:
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
-    validate_planning_input(replace(base, fast_memory_capacity=cap))
+    check_input(base, cap, "roundtrip")
     best = None
     err = None
     for share in (0.9, 0.7, 0.5):

@@ -14,14 +14,12 @@ Reference role: ``src/dataflow_sim/policies/sliding_window.py`` (a fixed release
 """
 from __future__ import annotations
 
-from dataclasses import replace
 
 from ..errors import SimulationCapacityError, SimulationError
 from ..schema import TaskChain
 from ..simulator import Simulator
-from ..validate import validate_planning_input
 from .pressurefit import PlanningError
-from .spans import SpanPlan
+from .spans import SpanPlan, check_input
 
 
 def window_plan(chain: TaskChain, window: int) -> SpanPlan:
@@ -46,7 +44,7 @@ def sliding_window(chain: TaskChain, fast_memory_capacity: int | None = None, wi
         raise ValueError("window_size must be at least 1")
     cap = fast_memory_capacity if fast_memory_capacity is not None else chain.fast_memory_capacity
     base = chain.bare()
-    validate_planning_input(replace(base, fast_memory_capacity=cap))
+    check_input(base, cap, "sliding_window")
     err = None
     for w in range(window_size, 0, -1):
         planned = window_plan(base, w).emit(cap)

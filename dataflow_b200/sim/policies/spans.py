@@ -223,6 +223,18 @@ class SpanPlan:
         return replace(chain, tasks=tasks, initial_memory=initial, fast_memory_capacity=cap)
 
 
+def check_input(chain: TaskChain, cap: int | None, name: str) -> None:
+    """Refuse a malformed chain (``ValidationError``) and say ``PlanningError`` when the chain is fine but some task's own
+    operands exceed the capacity: that is an answer about the capacity, which callers that search over budgets expect."""
+    from ..validate import ValidationError, validate_planning_input
+    try:
+        validate_planning_input(replace(chain, fast_memory_capacity=cap))
+    except ValidationError as e:
+        if set(e.rules) <= {"task-cannot-fit", "initial-overflow"}:
+            raise PlanningError(f"{name}: {e.problems[0]}") from None
+        raise
+
+
 def static_minimum(chain: TaskChain) -> np.ndarray:
     """Bytes no plan can avoid holding during each task: its inputs, its fast outputs and its workspace."""
     sizes = chain.sizes()
