@@ -50,6 +50,10 @@ def test_dispatch_floor_and_gap_census(capsys):
 def test_planners_match_the_exact_oracle_on_tiny_chains(capsys):
     assert tool("bench/pressurefit_exact_oracle.py").main(["--chains", "4", "--tasks", "6", "--tolerance", "0.05"]) == 0
     assert "worst excess" in capsys.readouterr().out
+    # the span planners against the same exhaustive optimum: accounting and growth land within a few per cent of it, the
+    # constructive one within 15 %
+    assert tool("bench/pressurefit_exact_oracle.py").main(["--chains", "4", "--tasks", "6", "--tolerance", "0.05", "--policies", "max_reduce,min_grow"]) == 0
+    assert tool("bench/pressurefit_exact_oracle.py").main(["--chains", "4", "--tasks", "6", "--tolerance", "0.15", "--policies", "roundtrip"]) == 0
 
 
 def test_verify_family_audit_and_listing(capsys):
