@@ -180,44 +180,10 @@ class Trainer:
         self.rounds = int(self.program.metadata.get("grad_accum_rounds", 1))
         self.T = int(self.program.metadata.get("tokens_per_round", self.dims.T))
         # size the session pools once: objects only (scratch lives in the framework allocator)
+        self.pool_demand = None
+        keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
         if device is not None:
-            store_bytes = sum(sizes.values())
-            transient_backing = max(planned.peak_backing_bytes - store_bytes, 0) + (64 << 20)
-            fast = planned.object_capacity or (planned.peak_fast_bytes + (256 << 20))
-            # the whole object share of the budget: the room above the planned peak absorbs slab fragmentation
-            # plus most of the budget's leeway share: the planner never counts on it, it only absorbs fragmentation
-            # (a buffer that overflows the slab cannot be read by peers, and costs a vendor allocation)
-            from ..lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
-            lee = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else int(leeway_bytes)
-            spare = min(lee * 3 // 4, 1 << 30) if budget is not None else 0
-            zero_md = (self.program.metadata or {}).get("zero")
-            if zero_md and int(zero_md.get("world", 1)) > 1:
-                # staging behind the slab, mapped by the peers with it: a published buffer (gradient, parameter slice)
-                # that overflowed the slab is copied there first; one region per stream that publishes
-                sizes_all = self.program.object_sizes()
-                pub = max((b for oid, b in sizes_all.items() if oid.startswith(("dW", "W", "dEmbed", "dHead", "Embed", "Head"))), default=0)
-                self.session.native.set_fast_tail(2 * (int(pub) + 4096))
-            # pool mode: "slab" (default) is one allocation under an offset allocator; "vmm" backs the pool page by page behind
-            # twice its size of virtual addresses, so fragmentation costs address room instead of failing — at the price of
-            # driver calls whenever pages move.  At the 8B headline configuration (plan fills 98 % of the pool) that price was
-            # 25 k page moves and 5 s per step, so the mode is opt-in: it suits plans with slack and long-lived layouts.
-            mode = pool_mode or os.environ.get("DATAFLOW_POOL_MODE", "slab")
-            if mode not in ("auto", "slab", "vmm"):
-                raise ValueError(f"pool mode {mode!r}: auto | slab | vmm")
-            peers_map_slab = bool(zero_md and int(zero_md.get("world", 1)) > 1)
-            if mode == "vmm" and peers_map_slab:
-                raise ValueError("pool mode 'vmm' cannot serve the sharded data-parallel lanes: their kernels read peers' slabs through "
-                                 "one mapping of one allocation")
-            self.pool_mode = "vmm" if mode == "vmm" else "slab"           # "auto" = the default
-            try:
-                self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, self.pool_mode == "vmm")
-            except RuntimeError as e:
-                if mode == "vmm":
-                    raise
-                if verbose:
-                    print(f"vmm pool not available ({e}); using one allocation")
-                self.pool_mode = "slab"
-                self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, False)
+            self._size_pools(cfg, sizes, budget, leeway_bytes, recompute, measured, lower_kwargs, planned_by_caller is None, pool_mode, keep_resident)
         else:
             self.pool_mode = "slab"
         self.step_index = 0
@@ -236,7 +202,7 @@ class Trainer:
                 raise ValueError(f"sharded data parallelism (fsdp / zero*) needs bf16 parameters and gradients (dtype policies bf16, "
                                  f"bf16_master, bf16_split_master); this run asks for {dt.param} / {dt.grad} — use --parallel co for replicas")
         # weights that end a step on the device stay there for the next one (Session.resident)
-        self.keep_resident = any(loc == "fast" for loc in self.program.final_locations.values())
+        self.keep_resident = keep_resident
         # on a device, launch up to two tasks behind an unfinished one: host dispatch hides behind device work
         self.dispatch_ahead = 2 if device is not None else 0
         for g in self.groups.values():
@@ -252,6 +218,92 @@ class Trainer:
     def host_tensor(self, oid: str, shape, dtype: str):
         from ..runtime.interop import torch_view
         return torch_view(self.store.buffer(oid), shape, dtype, 0, None)
+
+    def _size_pools(self, cfg, sizes, budget, leeway_bytes, recompute, measured, lower_kwargs, may_replan: bool, pool_mode, keep_resident: bool) -> None:
+        """Size the session's device and pinned pools for ``self.program`` (once, before the first step)."""
+        store_bytes = sum(sizes.values())
+        transient_backing = max(self.planned.peak_backing_bytes - store_bytes, 0) + (64 << 20)
+        fast = self.planned.object_capacity or (self.planned.peak_fast_bytes + (256 << 20))
+        # the whole object share of the budget: the room above the planned peak absorbs slab fragmentation
+        # plus most of the budget's leeway share: the planner never counts on it, it only absorbs fragmentation
+        # (a buffer that overflows the slab cannot be read by peers, and costs a vendor allocation)
+        from ..lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
+        lee = DEFAULT_PROGRAM_LEEWAY_BYTES if leeway_bytes is None else int(leeway_bytes)
+        spare = min(lee * 3 // 4, 1 << 30) if budget is not None else 0
+        zero_md = (self.program.metadata or {}).get("zero")
+        tail = 0
+        if zero_md and int(zero_md.get("world", 1)) > 1:
+            # staging behind the slab, mapped by the peers with it: a published buffer (gradient, parameter slice)
+            # that overflowed the slab is copied there first; one region per stream that publishes
+            sizes_all = self.program.object_sizes()
+            pub = max((b for oid, b in sizes_all.items() if oid.startswith(("dW", "W", "dEmbed", "dHead", "Embed", "Head"))), default=0)
+            tail = 2 * (int(pub) + 4096)
+            self.session.native.set_fast_tail(tail)
+        # what the pools are really asked for, from a run of the plan on the virtual-time backend: the backing pool is
+        # sized from its measured peak (the plan's backing peak minus the store's size under-counts it: the store holds
+        # every persistent object for the whole run, whatever the plan's ledger says about their backing copies), and a
+        # fast pool that overflows gets a plan made with a little less memory, in the pool it already has
+        if os.environ.get("DATAFLOW_POOL_FIT", "1") != "0":
+            transient_backing = self._fit_pools(cfg, sizes, int(fast) + spare, transient_backing, keep_resident, budget, recompute, measured,
+                                                leeway_bytes, lower_kwargs, replan=may_replan and not (zero_md and int(zero_md.get("world", 1)) > 1))
+        # pool mode: "slab" (default) is one allocation under an offset allocator; "vmm" backs the pool page by page behind
+        # twice its size of virtual addresses, so fragmentation costs address room instead of failing — at the price of
+        # driver calls whenever pages move.  At the 8B headline configuration (plan fills 98 % of the pool) that price was
+        # 25 k page moves and 5 s per step, so the mode is opt-in: it suits plans with slack and long-lived layouts.
+        mode = pool_mode or os.environ.get("DATAFLOW_POOL_MODE", "slab")
+        if mode not in ("auto", "slab", "vmm"):
+            raise ValueError(f"pool mode {mode!r}: auto | slab | vmm")
+        peers_map_slab = bool(zero_md and int(zero_md.get("world", 1)) > 1)
+        if mode == "vmm" and peers_map_slab:
+            raise ValueError("pool mode 'vmm' cannot serve the sharded data-parallel lanes: their kernels read peers' slabs through "
+                             "one mapping of one allocation")
+        self.pool_mode = "vmm" if mode == "vmm" else "slab"           # "auto" = the default
+        try:
+            self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, self.pool_mode == "vmm")
+        except RuntimeError as e:
+            if mode == "vmm":
+                raise
+            if self.verbose:
+                print(f"vmm pool not available ({e}); using one allocation")
+            self.pool_mode = "slab"
+            self.session.native.ensure_pools(int(fast) + spare, int(transient_backing), 0.0, False)
+
+    def _fit_pools(self, cfg, store_sizes, fast_capacity: int, transient_backing: int, keep_resident: bool, budget, recompute, measured,
+                   leeway_bytes, lower_kwargs, replan: bool, dispatch_ahead: int = 2, min_cut: int = 1 << 30) -> int:
+        """Dry-run the plan against the pools it will get (``runtime/pool_demand.py``).  Returns the bytes to give the backing pool.
+        When the fast pool overflows and ``replan`` allows it, the step is planned again with the budget lowered by the bytes
+        that did not fit (at least 1 GiB), the pool keeping its size; the new plan is taken when it overflows less and its
+        predicted step time is not worse by more than 1 %.  Any failure leaves the first plan and the first sizing in place."""
+        from ..runtime.pool_demand import dry_run_pools
+        from ..sim.policies.pressurefit import PlanningError
+        try:
+            d = dry_run_pools(self.program, store_sizes, fast_capacity, keep_resident=keep_resident, dispatch_ahead=dispatch_ahead)
+        except Exception as e:          # noqa: BLE001  (a dry run that cannot finish says nothing about the real run)
+            if self.verbose:
+                print(f"pool dry run failed ({type(e).__name__}: {e}); pools sized from the plan's peaks")
+            return transient_backing
+        self.pool_demand = d
+        if replan and budget is not None and d.fast_overflows:
+            cut = max(int(min_cut), int(d.fast_overflow_bytes * 0.5))
+            for _ in range(2):
+                try:
+                    p2 = plan_at_budget(self.fam, cfg, int(budget) - cut, self.hw, recompute=recompute, measured=measured,
+                                        leeway_bytes=leeway_bytes, lower_kwargs=lower_kwargs)
+                    same_store = {o.id: o.size_bytes for o in p2.program.initial_objects} == {o.id: o.size_bytes for o in self.program.initial_objects}
+                    if not same_store or p2.makespan_us > self.planned.makespan_us * 1.01:
+                        break
+                    d2 = dry_run_pools(p2.program, store_sizes, fast_capacity, keep_resident=keep_resident, dispatch_ahead=dispatch_ahead)
+                except (PlanningError, ValueError, RuntimeError):
+                    break
+                if d2.fast_overflows < d.fast_overflows:
+                    if self.verbose:
+                        print(f"fast pool: {d.fast_overflows} overflows per step with the first plan, {d2.fast_overflows} with a plan made for "
+                              f"{cut / 2 ** 30:.2f} GiB less (predicted step {self.planned.makespan_us / 1e6:.4f} -> {p2.makespan_us / 1e6:.4f} s)")
+                    self.planned, self.program, self.pool_demand, d = p2, p2.program, d2, d2
+                if d.fast_overflows == 0:
+                    break
+                cut *= 2
+        return max(transient_backing, int(d.backing_peak * 1.02) + (64 << 20))
 
     def _fit_static_extent(self, cfg, budget, recompute, measured, leeway_bytes, lower_kwargs, replan: bool, rounds: int = 4) -> None:
         """Static placement with a replan loop: pack the plan's allocations into the pool; when no packing fits (the plan's peak

@@ -62,6 +62,12 @@ static py::dict pool_stats(BufferPool& pool) {
   d["capacity"] = pool.slab_capacity();
   d["overflows"] = pool.slab_overflows;
   d["vendor_allocs"] = pool.vendor_allocs;
+  d["used"] = pool.slab_used();
+  d["peak"] = pool.slab_peak();
+  d["largest_free"] = pool.slab_largest_free();
+  py::list log;
+  for (auto& o : pool.overflow_log) log.append(py::make_tuple(o.asked, o.used, o.largest_free));
+  d["overflow_log"] = log;
   if (const VmSpace* vm = pool.vm()) {
     d["page"] = vm->page();
     d["va_bytes"] = vm->va_bytes();
@@ -245,6 +251,9 @@ PYBIND11_MODULE(_runtime, m) {
       .def("ensure_pools", &Session::ensure_pools, py::arg("fast_cap"), py::arg("backing_cap"), py::arg("headroom") = 0.0,
            py::arg("fast_vm") = false)
       .def("fast_pool_stats", [](Session& s) { return pool_stats(s.fast_pool); })
+      .def("backing_pool_stats", [](Session& s) { return pool_stats(s.backing_pool); })
+      .def("set_fast_policy", [](Session& s, size_t large_div, bool best_fit) { s.fast_pool.set_policy(large_div, best_fit); },
+           py::arg("large_div") = 48, py::arg("best_fit") = false)
       .def("fast_slab", [](Session& s) { return py::make_tuple(reinterpret_cast<uint64_t>(s.fast_pool.slab_base()), s.fast_pool.slab_capacity()); })
       .def("set_fast_tail", [](Session& s, size_t bytes) { s.fast_pool.set_tail(bytes); })
       .def("fast_tail", [](Session& s) { return s.fast_pool.slab_tail(); })

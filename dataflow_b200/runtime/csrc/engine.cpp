@@ -38,6 +38,7 @@ void BufferPool::ensure_slab(size_t capacity) {
       alloc_bytes_ = 0;
       vendor_allocs++;
       slab_ = std::make_unique<SlabAllocator>(vm_->va_bytes());
+      slab_->set_policy(large_div_, best_fit_);
       return;
     }
   }
@@ -47,6 +48,7 @@ void BufferPool::ensure_slab(size_t capacity) {
   base_ = be_->alloc(loc_, alloc_bytes_);
   vendor_allocs++;
   slab_ = std::make_unique<SlabAllocator>(capacity);
+  slab_->set_policy(large_div_, best_fit_);
 }
 
 BufferRef BufferPool::get(size_t bytes) {
@@ -64,6 +66,7 @@ BufferRef BufferPool::get(size_t bytes) {
       return b;
     }
     slab_overflows++;
+    if (overflow_log.size() < 64) overflow_log.push_back({bytes, slab_->used(), slab_->largest_free()});
   }
   size_t need = SlabAllocator::round_up(bytes ? bytes : 1, SlabAllocator::kAlign);
   auto it = free_exact_.find(need);
@@ -598,6 +601,16 @@ void Engine::run_dispatch(const ProgramIR& p, const LaunchFn& launch,
   // drain
   while (be_->pending() > 0 || flight_[0] || flight_[1]) {
     if (!pump_one(true)) break;
+  }
+  if (out.outcome == "SUCCESS") {
+    // what the pressure valve sent away and the program wants on the device at the end comes back now: nothing that reads it
+    // ran after the eviction (or it would have been reloaded for that task), so no later task asked for it
+    bool reloading = false;
+    for (size_t i = 0; i < p.objs.size(); ++i)
+      if (p.objs[i].final_loc == FAST && evicted_[i]) reloading |= reload_evicted(static_cast<int>(i));
+    while (reloading && (be_->pending() > 0 || flight_[0] || flight_[1])) {
+      if (!pump_one(true)) break;
+    }
   }
   if (out.outcome == "SUCCESS") {
     if (!queue_[0].empty() || !queue_[1].empty() || !deferred_.empty())

@@ -91,6 +91,15 @@ class BufferPool {
   size_t slab_tail() const { return base_ && !vm_ ? alloc_bytes_ - slab_->capacity() : 0; }
   int64_t slab_overflows = 0;
   int64_t vendor_allocs = 0;
+  // what the slab looked like at the first overflows: (bytes asked, bytes in use, largest free block).  Tells a pool that is
+  // too small (in use + asked > capacity) from one that is fragmented (largest free block < asked <= capacity - in use)
+  struct Overflow { size_t asked, used, largest_free; };
+  std::vector<Overflow> overflow_log;
+  // allocator policy of the current and every later slab (see SlabAllocator::set_policy)
+  void set_policy(size_t large_div, bool best_fit) { large_div_ = large_div; best_fit_ = best_fit; if (slab_) slab_->set_policy(large_div, best_fit); }
+  size_t slab_used() const { return slab_ ? slab_->used() : 0; }
+  size_t slab_peak() const { return slab_ ? slab_->peak() : 0; }
+  size_t slab_largest_free() const { return slab_ ? slab_->largest_free() : 0; }
  private:
   Backend* be_;
   Location loc_;
@@ -101,6 +110,8 @@ class BufferPool {
   bool vm_mode_ = false;
   double va_factor_ = 2.0;
   size_t phys_capacity_ = 0;
+  size_t large_div_ = 48;
+  bool best_fit_ = false;
   std::multimap<size_t, void*> free_exact_;
 };
 

@@ -24,6 +24,10 @@ class SlabAllocator {
 
   static size_t round_up(size_t n, size_t a) { return (n + a - 1) / a * a; }
 
+  // Requests of at least capacity / ``div`` count as large (lowest-address first fit); smaller ones are carved from the top.
+  // ``best_fit``: a large request takes the smallest hole that fits instead of the lowest one.
+  void set_policy(size_t div, bool best_fit) { large_div_ = div ? div : 48; best_fit_ = best_fit; }
+
   // returns an offset or kNone.  Exact-size holes are reused first (training chains allocate a handful of
   // sizes over and over).  Otherwise large requests (>= capacity / 48) take the lowest-address hole that fits
   // and small ones are carved from the END of the highest-address hole that fits, so the two size classes
@@ -36,10 +40,14 @@ class SlabAllocator {
     bool from_end = false;
     if (exact->first == need) {
       off = exact->second; len = exact->first;
-    } else if (need >= cap_ / 48) {
+    } else if (need >= cap_ / large_div_) {
       off = kNone; len = 0;
-      for (auto& kv : by_off_) {
-        if (kv.second >= need) { off = kv.first; len = kv.second; break; }
+      if (best_fit_) {
+        off = exact->second; len = exact->first;       // by_size_ is ordered by (length, offset): the smallest hole that fits
+      } else {
+        for (auto& kv : by_off_) {
+          if (kv.second >= need) { off = kv.first; len = kv.second; break; }
+        }
       }
       if (off == kNone) return kNone;
     } else {
@@ -127,6 +135,8 @@ class SlabAllocator {
     by_size_.erase({len, off});
   }
   size_t cap_, align_;
+  size_t large_div_ = 48;
+  bool best_fit_ = false;
   size_t used_ = 0, peak_ = 0;
   std::map<size_t, size_t> by_off_;                  // free: offset -> length
   std::set<std::pair<size_t, size_t>> by_size_;      // free: (length, offset)

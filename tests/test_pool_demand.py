@@ -1,0 +1,103 @@
+"""Pools sized from a dry run of the plan on the virtual-time backend, and the engine corner the dry run found."""
+import dataclasses
+from types import SimpleNamespace
+
+import pytest
+
+from dataflow_b200.lowering import resolve_hardware
+from dataflow_b200.models.families import resolve_family
+from dataflow_b200.run.driver import Trainer, plan_at_budget, synthetic_rounds
+from dataflow_b200.runtime import Engine, FakeBackend, Session
+from dataflow_b200.runtime.pool_demand import PoolDemand, dry_run_pools
+
+BUDGET = int(0.02 * (1 << 30))
+
+
+@pytest.fixture(scope="module")
+def tight():
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), n_layers=6, grad_accum_rounds=4)
+    planned = plan_at_budget(fam, cfg, BUDGET, resolve_hardware("b200"), leeway_bytes=0, lower_kwargs={"resident_params": True})
+    sizes = {}
+    for o in planned.program.initial_objects:
+        sizes.setdefault(o.id, o.size_bytes)
+    return fam, cfg, planned, sizes
+
+
+def test_the_dry_run_measures_what_the_plans_ledger_cannot(tight):
+    _, _, planned, sizes = tight
+    d = dry_run_pools(planned.program, sizes, planned.object_capacity, keep_resident=True, dispatch_ahead=2)
+    assert isinstance(d, PoolDemand) and d.backing_overflows == 0 and d.fast_peak <= d.fast_capacity
+    # the session's backing pool holds transient copies only; the plan's backing peak minus the store's size says less than they need
+    from_ledger = max(planned.peak_backing_bytes - sum(sizes.values()), 0)
+    assert d.backing_peak > from_ledger
+    small = dry_run_pools(planned.program, sizes, planned.object_capacity, backing_capacity=from_ledger + (1 << 20), keep_resident=True, dispatch_ahead=2)
+    right = dry_run_pools(planned.program, sizes, planned.object_capacity, backing_capacity=int(d.backing_peak * 1.02) + (1 << 20), keep_resident=True, dispatch_ahead=2)
+    assert small.backing_overflows > 0 and right.backing_overflows == 0
+    # under strict pacing this plan fragments the fast pool: requests fail for want of a hole, and the report prices them
+    strict = dry_run_pools(planned.program, sizes, planned.object_capacity, keep_resident=True, dispatch_ahead=0)
+    assert strict.fast_overflows > 0 and strict.fast_overflow_bytes >= strict.fast_overflows * 512 and not strict.fits
+
+
+def test_an_object_the_valve_evicted_ends_on_the_device_when_the_program_wants_it_there(tight):
+    """Dispatching ahead at a budget this tight makes the realised order leave the plan; the pressure valve then evicts a
+    weight whose last reader has run.  The program keeps weights on the device from step to step, so the engine brings it
+    back before it checks the final locations (it used to fail the run with FinalLocationError)."""
+    _, _, planned, sizes = tight
+    be = FakeBackend()
+    ses = Session(be)
+    ses.native.ensure_pools(int(planned.object_capacity), 1 << 30, 0.0, False)
+    eng = Engine(be, session=ses)
+    evictions = 0
+    for step in range(3):
+        res = eng.execute(planned.program, None, None, run_args={"step": step + 1}, manage_pools=False, keep_resident=True, dispatch_ahead=2)
+        res.raise_if_failed()
+        evictions += res.pressure_evictions
+    assert evictions > 0                                 # the case is the one the fix is for
+    held = ses.native.resident()
+    want = {o for o, loc in planned.program.final_locations.items() if loc == "fast"}
+    assert want and want <= set(held)
+
+
+def test_pool_fitting_keeps_the_first_plan_unless_the_second_is_better(tight):
+    fam, cfg, planned, sizes = tight
+    stub = SimpleNamespace(program=planned.program, planned=planned, fam=fam, hw=resolve_hardware("b200"), verbose=False, pool_demand=None)
+    got = Trainer._fit_pools(stub, cfg, sizes, planned.object_capacity, 1000, True, BUDGET, True, None, 0, {"resident_params": True},
+                             replan=True, dispatch_ahead=0, min_cut=1 << 20)
+    d = stub.pool_demand
+    assert got >= int(d.backing_peak * 1.02) and d.fast_capacity >= planned.object_capacity
+    if stub.planned is not planned:                    # a second plan is taken only when it overflows less and is not slower by more than 1 %
+        assert stub.planned.makespan_us <= planned.makespan_us * 1.01 and stub.program is stub.planned.program
+    # without permission to plan again, and without a budget, the plan is never touched
+    for kw in ({"replan": False}, {"replan": True}):
+        s2 = SimpleNamespace(program=planned.program, planned=planned, fam=fam, hw=stub.hw, verbose=False, pool_demand=None)
+        Trainer._fit_pools(s2, cfg, sizes, planned.object_capacity, 1000, True, BUDGET if not kw["replan"] else None, True, None, 0,
+                           {"resident_params": True}, dispatch_ahead=0, **kw)
+        assert s2.planned is planned
+    # a dry run that cannot finish leaves the sizing that was asked for
+    broken = SimpleNamespace(program=None, planned=planned, fam=fam, hw=stub.hw, verbose=False, pool_demand=None)
+    assert Trainer._fit_pools(broken, cfg, sizes, planned.object_capacity, 12345, True, BUDGET, True, None, 0, {}, replan=True) == 12345
+
+
+def test_pool_sizing_runs_on_a_trainer_and_training_goes_on(monkeypatch):
+    """The sizing a device run does before its first step, exercised on the CPU backend: dry run, backing pool from the
+    measured peak, one allocation for the fast pool; steps afterwards allocate nothing more."""
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), n_layers=4, dtype_policy="fp32")
+    tr = Trainer("llama3", cfg, budget_gib=0.03, device=None, hyper={"lr": 1e-3}, leeway_bytes=0, lower_kwargs={"resident_params": True})
+    try:
+        sizes = dict(tr.store.sizes)
+        tr._size_pools(cfg, sizes, int(0.03 * (1 << 30)), 0, True, None, {"resident_params": True}, True, None, tr.keep_resident)
+        assert tr.pool_mode == "slab" and tr.pool_demand is not None and tr.pool_demand.backing_overflows == 0
+        assert tr.session.native.backing_slab()[1] >= tr.pool_demand.backing_peak
+        assert tr.session.native.fast_slab()[1] >= tr.planned.peak_fast_bytes
+        losses = [tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, 64, 0, 0)) for _ in range(3)]
+        assert losses[-1] < losses[0]
+        monkeypatch.setenv("DATAFLOW_POOL_FIT", "0")             # the switch: sizes from the plan's peaks, no dry run
+        tr.pool_demand = None
+        tr._size_pools(cfg, sizes, int(0.03 * (1 << 30)), 0, True, None, {"resident_params": True}, True, None, tr.keep_resident)
+        assert tr.pool_demand is None
+        with pytest.raises(ValueError, match="pool mode"):
+            tr._size_pools(cfg, sizes, None, 0, True, None, None, False, "paged", tr.keep_resident)
+    finally:
+        tr.close()
