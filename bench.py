@@ -222,7 +222,17 @@ def _pool_line(tr) -> dict:
         st = tr.session.native.fast_pool_stats()
     except Exception:       # noqa: BLE001
         return {"mode": getattr(tr, "pool_mode", "slab")}
-    return {k: (int(v) if not isinstance(v, str) else v) for k, v in st.items() if k in ("mode", "maps", "reclaims", "phys_pages", "held_pages")}
+    out = {k: (int(v) if not isinstance(v, str) else v) for k, v in st.items() if k in ("mode", "maps", "reclaims", "phys_pages", "held_pages")}
+    try:
+        # overflows by pool since the run began, and what the dry run of the plan said the pools would be asked for
+        out["fast_overflows_total"] = int(st.get("overflows", 0))
+        out["backing_overflows_total"] = int(tr.session.native.backing_pool_stats().get("overflows", 0))
+        d = getattr(tr, "pool_demand", None)
+        if d is not None:
+            out["dry_run"] = {"fast_overflows_per_step": d.fast_overflows, "backing_peak_gib": round(d.backing_peak / 2 ** 30, 3)}
+    except Exception:       # noqa: BLE001
+        pass
+    return out
 
 
 def main(argv=None) -> int:
