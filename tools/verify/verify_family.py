@@ -111,8 +111,10 @@ def main(argv=None) -> int:
             return bool(rep), rep.summary() + (f"; failing {sorted(rep.failures())[:4]}" if not rep else "")
         rung("gradients", grads)
     if "block" in want:
-        kinds = list(getattr(cfg0, "pattern", lambda: [])() or []) if callable(getattr(cfg0, "pattern", None)) else []
-        layers = sorted({kinds.index(k) for k in set(kinds)}) if kinds else [0]
+        # the kind of every layer, read off the lowered program: the compute key of its forward task in the first round
+        fwd = sorted(((int(t.id.rsplit("_", 1)[1]), t.compute_block_key) for t in fam.lower(cfg0).tasks if t.id.startswith("block_fwd_0_0_")))
+        kinds = [k for _, k in fwd]
+        layers = sorted({kinds.index(k) for k in set(kinds)}) if kinds else [0]       # the first layer of every kind
         for i in layers:
             def block(i=i):
                 rep = gradcheck.check_block_backward(a.family, device=device, policy=policy, tol=gtol, kind_layer=i)
