@@ -137,3 +137,27 @@ def test_what_every_policy_emits_passes_every_stage(cap):
             assert "Planning" in type(exc).__name__ or "Validation" in type(exc).__name__, (name, exc)
             continue
         assert chain_problems(planned) == [], name
+
+
+def test_the_command_line_validates_plans_simulates_and_compares(tmp_path, capsys):
+    from dataflow_b200.sim.__main__ import main
+    bare = tmp_path / "chain.json"
+    planned = tmp_path / "planned.json"
+    train_chain(L=4, rounds=2).save(bare)
+    assert main(["validate", str(bare), "--planning-input"]) == 0
+    assert main(["plan", str(bare), "--policy", "max_reduce", "--capacity-gib", str(3000 / 2 ** 30), "-o", str(planned)]) == 0
+    assert "x compute-only" in capsys.readouterr().out and planned.exists()
+    assert main(["validate", str(planned)]) == 0 and main(["validate", str(planned), "--planning-input"]) == 1      # it carries a plan now
+    assert "already-planned" in capsys.readouterr().out
+    assert main(["simulate", str(planned), "--stalls"]) == 0
+    out = capsys.readouterr().out
+    assert '"makespan_us"' in out and "from_slow: busy" in out
+    assert main(["compare", str(bare), "--capacity-gib", str(3000 / 2 ** 30), "--policies", "max_reduce,lookahead,all_resident"]) == 0
+    table = capsys.readouterr().out.strip().splitlines()
+    assert len(table) == 3 and table[-1].startswith("all_resident") and "no plan" in table[-1]        # best first, failures last
+    assert main(["plan", str(bare), "--policy", "nope"]) == 1 and main(["plan", str(bare), "--capacity-gib", "0.0000001"]) == 1
+    bad = base()
+    bad = replace(bad, tasks=[replace(bad.tasks[0], inputs=["x", "ghost"])] + bad.tasks[1:])
+    bad.save(tmp_path / "bad.json")
+    assert main(["validate", str(tmp_path / "bad.json")]) == 1
+    assert "unknown-input" in capsys.readouterr().out
