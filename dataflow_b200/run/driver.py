@@ -275,7 +275,6 @@ class Trainer:
         that did not fit (at least 1 GiB), the pool keeping its size; the new plan is taken when it overflows less and its
         predicted step time is not worse by more than 1 %.  Any failure leaves the first plan and the first sizing in place."""
         from ..runtime.pool_demand import dry_run_pools
-        from ..sim.policies.pressurefit import PlanningError
         try:
             d = dry_run_pools(self.program, store_sizes, fast_capacity, keep_resident=keep_resident, dispatch_ahead=dispatch_ahead)
         except Exception as e:          # noqa: BLE001  (a dry run that cannot finish says nothing about the real run)
@@ -286,6 +285,8 @@ class Trainer:
         if replan and budget is not None and d.fast_overflows:
             cut = max(int(min_cut), int(d.fast_overflow_bytes * 0.5))
             for _ in range(2):
+                if cut > int(budget) // 4:                   # a quarter of the budget is no longer "a little less memory"
+                    break
                 try:
                     p2 = plan_at_budget(self.fam, cfg, int(budget) - cut, self.hw, recompute=recompute, measured=measured,
                                         leeway_bytes=leeway_bytes, lower_kwargs=lower_kwargs)
@@ -293,7 +294,7 @@ class Trainer:
                     if not same_store or p2.makespan_us > self.planned.makespan_us * 1.01:
                         break
                     d2 = dry_run_pools(p2.program, store_sizes, fast_capacity, keep_resident=keep_resident, dispatch_ahead=dispatch_ahead)
-                except (PlanningError, ValueError, RuntimeError):
+                except Exception:       # noqa: BLE001  (an optimisation: whatever goes wrong, the first plan stands)
                     break
                 if d2.fast_overflows < d.fast_overflows:
                     if self.verbose:

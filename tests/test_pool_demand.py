@@ -101,3 +101,33 @@ def test_pool_sizing_runs_on_a_trainer_and_training_goes_on(monkeypatch):
             tr._size_pools(cfg, sizes, None, 0, True, None, None, False, "paged", tr.keep_resident)
     finally:
         tr.close()
+
+
+def test_the_headline_configuration_ends_with_no_overflow_in_either_pool():
+    """Llama-3-8B, 131 072 tokens per step in 8 rounds, 60 GiB: the first plan fills the device pool to 98 % and two 1.2 GiB
+    requests per step find no hole; the pinned pool sized from the plan's ledger is less than half of what the transient
+    copies need.  After fitting: a plan for about 1.2 GiB less in the same pool, no overflow anywhere, and a predicted step
+    that is not slower."""
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["llama3_8b"](), seq_len=4096, batch=4, grad_accum_rounds=8, dtype_policy="bf16_split_master")
+    hw = resolve_hardware("b200")
+    budget = 60 << 30
+    kw = {"resident_params": True}
+    planned = plan_at_budget(fam, cfg, budget, hw, lower_kwargs=kw)
+    sizes = {}
+    for o in planned.program.initial_objects:
+        sizes.setdefault(o.id, o.size_bytes)
+    for t in planned.program.tasks:
+        for out in t.outputs:
+            if out.location == "backing" and out.id.startswith("loss_"):
+                sizes[out.id] = out.size_bytes
+    from dataflow_b200.lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
+    pool = planned.object_capacity + min(DEFAULT_PROGRAM_LEEWAY_BYTES * 3 // 4, 1 << 30)
+    ledger = max(planned.peak_backing_bytes - sum(sizes.values()), 0) + (64 << 20)
+    first = dry_run_pools(planned.program, sizes, pool, backing_capacity=ledger, keep_resident=True, dispatch_ahead=2)
+    assert first.backing_overflows > 20                      # the pinned pool was the one that overflowed
+    stub = SimpleNamespace(program=planned.program, planned=planned, fam=fam, hw=hw, verbose=False, pool_demand=None)
+    backing = Trainer._fit_pools(stub, cfg, sizes, pool, ledger, True, budget, True, None, None, kw, replan=True)
+    assert backing > 1.5 * ledger and stub.planned.makespan_us <= planned.makespan_us * 1.01
+    final = dry_run_pools(stub.program, sizes, pool, backing_capacity=backing, keep_resident=True, dispatch_ahead=2, steps=3)
+    assert final.fits and final.fast_peak <= pool
