@@ -47,6 +47,9 @@ def parse_args(argv=None):
                     help="fp8: e4m3 forward projections (an extra data point; the headline metric is the bf16 run)")
     ap.add_argument("--no-profile", action="store_true", help="plan from roofline seeds instead of measured task costs")
     ap.add_argument("--parallel", default=None, help="fsdp | zero3 | zero1 (default: fsdp when --gpus > 1)")
+    ap.add_argument("--plan-only", action="store_true",
+                    help="no device: plan the configuration from roofline costs, dry-run the plan against its pools on the "
+                         "virtual-time backend and print what is predicted (not a measurement, not the bench line)")
     return ap.parse_args(argv)
 
 
@@ -235,8 +238,66 @@ def _pool_line(tr) -> dict:
     return out
 
 
+def plan_only(a) -> dict:
+    """The planning half of the bench on the CPU: the configuration ``bench_ours`` would run, planned from the hardware row's
+    roofline costs (a device run plans from measured task costs), then the pool fitting a device run does before its first
+    step.  Says what the plan predicts and what the pools would be asked for; measures nothing."""
+    import dataclasses
+    from types import SimpleNamespace
+    from dataflow_b200.lowering import resolve_hardware
+    from dataflow_b200.lowering.planning import DEFAULT_PROGRAM_LEEWAY_BYTES
+    from dataflow_b200.models.families import resolve_family
+    from dataflow_b200.run.driver import Trainer, plan_at_budget
+    from dataflow_b200.runtime.pool_demand import dry_run_pools
+    fam = resolve_family(a.family)
+    cfg = fam.presets[a.preset]()
+    rounds = max(a.tokens_per_gpu // (a.seq_len * a.batch), 1)
+    cfg = dataclasses.replace(cfg, seq_len=a.seq_len, batch=a.batch, grad_accum_rounds=rounds, dtype_policy=a.dtype_policy)
+    if a.layers:
+        cfg = dataclasses.replace(cfg, n_layers=a.layers)
+    budget_gib = a.budget_gib if a.budget_gib is not None else PRESET_BUDGET_GIB.get(a.preset, 60.0)
+    budget = int(budget_gib * (1 << 30))
+    world = max(a.gpus, 1)
+    parallel = a.parallel or ("fsdp" if world > 1 else "solo")
+    lower_kwargs = {"resident_params": True}
+    if world > 1:
+        from dataflow_b200.parallel.zero import zero_lower_kwargs
+        lower_kwargs = zero_lower_kwargs(parallel, 0, world)
+    hw = resolve_hardware("b200").shared(world)
+    planned = plan_at_budget(fam, cfg, budget, hw, lower_kwargs=lower_kwargs)
+    sizes = {}
+    for o in planned.program.initial_objects:
+        sizes.setdefault(o.id, o.size_bytes)
+    for t in planned.program.tasks:
+        for out in t.outputs:
+            if out.location == "backing" and out.id.startswith("loss_"):
+                sizes[out.id] = out.size_bytes
+    pool = planned.object_capacity + min(DEFAULT_PROGRAM_LEEWAY_BYTES * 3 // 4, 1 << 30)
+    keep = any(loc == "fast" for loc in planned.program.final_locations.values())
+    ledger = max(planned.peak_backing_bytes - sum(sizes.values()), 0) + (64 << 20)
+    first = dry_run_pools(planned.program, sizes, pool, backing_capacity=ledger, keep_resident=keep, dispatch_ahead=2)
+    stub = SimpleNamespace(program=planned.program, planned=planned, fam=fam, hw=hw, verbose=False, pool_demand=None)
+    backing = Trainer._fit_pools(stub, cfg, sizes, pool, ledger, keep, budget, True, None, None, lower_kwargs, replan=world == 1)
+    final = dry_run_pools(stub.program, sizes, pool, backing_capacity=backing, keep_resident=keep, dispatch_ahead=2, steps=3)
+    tokens = a.tokens_per_gpu // (a.seq_len * a.batch) * a.seq_len * a.batch
+    gib = 2 ** 30
+    return {"plan_only": True, "note": "predicted from roofline costs on the CPU; not a measurement",
+            "config": {"model": a.preset, "seq_len": a.seq_len, "tokens_per_gpu": tokens, "rounds": rounds, "budget_gib": budget_gib,
+                       "parallelism": parallel if world > 1 else "solo", "n_gpus": world},
+            "first_plan": {"policy": planned.policy, "predicted_ms_per_step": planned.makespan_us / 1e3, "peak_fast_gib": planned.peak_fast_bytes / gib,
+                           "pools_from_the_plans_ledger": {"fast_gib": pool / gib, "backing_gib": ledger / gib,
+                                                           "fast_overflows_per_step": first.fast_overflows, "backing_overflows_per_step": first.backing_overflows}},
+            "fitted": {"policy": stub.planned.policy, "replanned": stub.planned is not planned, "predicted_ms_per_step": stub.planned.makespan_us / 1e3,
+                       "predicted_tokens_per_s_per_gpu": tokens / stub.planned.makespan_us * 1e6, "peak_fast_gib": stub.planned.peak_fast_bytes / gib,
+                       "pools": {"fast_gib": pool / gib, "backing_gib": backing / gib, "fast_overflows_per_step": final.fast_overflows,
+                                 "backing_overflows_per_step": final.backing_overflows}}}
+
+
 def main(argv=None) -> int:
     a = parse_args(argv)
+    if a.plan_only:
+        print(json.dumps(plan_only(a)), flush=True)
+        return 0
     if a.impl == "reference":
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
         from baseline.reference_arm import run_reference_arm

@@ -131,3 +131,20 @@ def test_the_headline_configuration_ends_with_no_overflow_in_either_pool():
     assert backing > 1.5 * ledger and stub.planned.makespan_us <= planned.makespan_us * 1.01
     final = dry_run_pools(stub.program, sizes, pool, backing_capacity=backing, keep_resident=True, dispatch_ahead=2, steps=3)
     assert final.fits and final.fast_peak <= pool
+
+
+def test_bench_plan_only_runs_without_a_device(capsys):
+    """``bench.py --plan-only``: the bench configuration planned and its pools fitted on the CPU; says so in its output and
+    never prints a bench line."""
+    import importlib.util
+    import json
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_script", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.main(["--plan-only", "--layers", "4", "--tokens-per-gpu", "32768", "--budget-gib", "12"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["plan_only"] and "not a measurement" in out["note"] and "metric" not in out and "value" not in out
+    assert out["config"]["rounds"] == 2 and out["fitted"]["pools"]["backing_overflows_per_step"] == 0
+    assert out["fitted"]["predicted_ms_per_step"] <= out["first_plan"]["predicted_ms_per_step"] * 1.01
