@@ -161,3 +161,34 @@ def test_the_command_line_validates_plans_simulates_and_compares(tmp_path, capsy
     bad.save(tmp_path / "bad.json")
     assert main(["validate", str(tmp_path / "bad.json")]) == 1
     assert "unknown-input" in capsys.readouterr().out
+
+
+FIXTURES = __import__("os").path.join(__import__("os").path.dirname(__import__("os").path.abspath(__file__)), "fixtures", "invalid_chains")
+
+
+def test_the_invalid_chains_on_disk_are_the_cases_above_and_the_tools_refuse_them(tmp_path, capsys):
+    """One JSON file per rule under ``tests/fixtures/invalid_chains`` (for the command line, the HTTP route and anything else
+    that reads chains from files).  ``DATAFLOW_WRITE_FIXTURES=1`` rewrites them from the cases of this module."""
+    import json
+    import os
+    from dataflow_b200.sim.__main__ import main
+    if os.environ.get("DATAFLOW_WRITE_FIXTURES") == "1":
+        os.makedirs(FIXTURES, exist_ok=True)
+        for rule, make in CASES.items():
+            with open(os.path.join(FIXTURES, rule + ".json"), "w") as f:
+                json.dump({"rule": rule, "meaning": RULES[rule], "chain": make(base()).to_dict()}, f, indent=1)
+        with open(os.path.join(FIXTURES, "valid.json"), "w") as f:
+            json.dump({"rule": None, "meaning": "the chain every case is one edit away from", "chain": base().to_dict()}, f, indent=1)
+    names = sorted(n[:-5] for n in os.listdir(FIXTURES) if n.endswith(".json"))
+    assert names == sorted(list(CASES) + ["valid"])
+    for rule in CASES:
+        with open(os.path.join(FIXTURES, rule + ".json")) as f:
+            doc = json.load(f)
+        chain = TaskChain.from_dict(doc["chain"])
+        assert chain == CASES[rule](base()), rule                       # the file is what the case builds
+        assert rule in {p.rule for p in chain_problems(chain)}, rule
+        path = tmp_path / (rule + ".json")
+        chain.save(path)
+        assert main(["validate", str(path)]) == 1 and rule in capsys.readouterr().out
+    with open(os.path.join(FIXTURES, "valid.json")) as f:
+        assert chain_problems(TaskChain.from_dict(json.load(f)["chain"])) == []
