@@ -1,4 +1,4 @@
-"""min_grow: start from the least residency that can run and grow it, with the simulator as the judge.
+"""min_grow: start from the least residency that can run and grow it, with the simulator deciding what counts.
 
 The seed is ``SpanPlan.fill_min(0)``: every object is in fast memory only during the tasks that touch it, so every idle gap
 is a round trip through backing memory and every fetch is fired at the last moment.  If even that does not fit, nothing does, and that is the only infeasibility this

@@ -11,7 +11,7 @@ current backing copy exists or nothing needs the bytes any more, an offload othe
 
 ``level[i]`` is the fast memory charged during task ``i``: the spans that cover ``i`` plus the task's workspace.  Planners
 edit spans (``cut``, ``join``, ``move_start``) and the level follows; ``emit`` turns the plan into an annotated chain, and
-``verify`` lets the simulator judge it, shrinking the capacity the planner works against when bytes in flight (an offload
+``verify`` runs it through the simulator, shrinking the capacity the planner works against when bytes in flight (an offload
 holds its fast copy until it completes) push the real run over the cap.
 
 The planners built on this: ``max_reduce`` (accounting only), ``min_grow`` (simulator as the oracle), ``roundtrip`` (explicit

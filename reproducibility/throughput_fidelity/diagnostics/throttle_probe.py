@@ -5,7 +5,7 @@
 power cap is noted, an SM clock stuck far below its maximum with no reason given points at a clock lock left by someone else.
 
     python reproducibility/throughput_fidelity/diagnostics/throttle_probe.py --device 0 -- python bench.py --steps 3
-    python reproducibility/throughput_fidelity/diagnostics/throttle_probe.py --csv gpurun_out/clocks.csv
+    python reproducibility/throughput_fidelity/diagnostics/throttle_probe.py --csv clocks.csv
 """
 from __future__ import annotations
 

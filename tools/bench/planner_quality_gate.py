@@ -2,7 +2,7 @@
 
 A scenario = one model of the workload library x one hardware preset x one step shape (sequence length, tokens per round,
 rounds) x one fast-memory budget, given as a fraction of the all-resident peak.  Every scenario is traced, priced and
-realised into a task chain; every registered policy plans it; the simulator is the judge: a plan counts only if it
+realised into a task chain; every registered policy plans it; the simulator decides: a plan counts only if it
 finishes under the cap.  Per policy the gate reports how many scenarios it solves, the geometric mean of
 makespan / compute-only lower bound over the scenarios EVERY compared policy solves, how often it is the best, and its
 planning time.  ``auto`` is what the training entry uses: the better of Lookahead and PressureFit per scenario.
