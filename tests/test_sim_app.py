@@ -204,3 +204,12 @@ def test_the_structure_check_sees_a_broken_script():
     assert _js_structure_errors("const f = x => { return `a${x}; };") != []
     assert _js_structure_errors("f(a, [b, c);") != []
     assert _js_structure_errors("s.replace(/[&<>]/g, c => c)") == []
+
+
+def test_hardware_overrides_change_the_prediction(client):
+    base = client.post("/api/simulate", json={**BODY, "policy": "max_reduce", "timeline": False}).json()["summary"]
+    slow = client.post("/api/simulate", json={**BODY, "policy": "max_reduce", "timeline": False, "hardware_overrides": {"from_slow_gbs": 10, "to_slow_gbs": 10}})
+    assert slow.status_code == 200 and slow.json()["summary"]["makespan_us"] > base["makespan_us"] * 1.5      # a fifth of the host link
+    eff = client.post("/api/simulate", json={**BODY, "policy": "max_reduce", "timeline": False, "hardware_overrides": {"matmul_efficiency": 0.4}}).json()["summary"]
+    assert eff["compute_us_by_kind"]["matmul"] > base["compute_us_by_kind"]["matmul"] * 1.5
+    assert client.post("/api/simulate", json={**BODY, "hardware_overrides": {"warp_drive": 9}}).status_code == 422
