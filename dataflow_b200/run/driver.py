@@ -243,9 +243,12 @@ class Trainer:
         # sized from its measured peak (the plan's backing peak minus the store's size under-counts it: the store holds
         # every persistent object for the whole run, whatever the plan's ledger says about their backing copies), and a
         # fast pool that overflows gets a plan made with a little less memory, in the pool it already has
+        # ranks of a sharded run must hold the same plan.  Planning is deterministic (the same inputs give the same plan in every
+        # process), so every rank would arrive at the same second plan by itself; that has not run on several GPUs, hence the switch
+        sharded_ranks = int(zero_md.get("world", 1)) if zero_md else 1
         if os.environ.get("DATAFLOW_POOL_FIT", "1") != "0":
             transient_backing = self._fit_pools(cfg, sizes, int(fast) + spare, transient_backing, keep_resident, budget, recompute, measured,
-                                                leeway_bytes, lower_kwargs, replan=may_replan and not (zero_md and int(zero_md.get("world", 1)) > 1))
+                                                leeway_bytes, lower_kwargs, replan=may_replan and (sharded_ranks == 1 or os.environ.get("DATAFLOW_POOL_FIT_RANKS") == "1"))
         # pool mode: "slab" (default) is one allocation under an offset allocator; "vmm" backs the pool page by page behind
         # twice its size of virtual addresses, so fragmentation costs address room instead of failing — at the price of
         # driver calls whenever pages move.  At the 8B headline configuration (plan fills 98 % of the pool) that price was
