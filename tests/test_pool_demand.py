@@ -148,3 +148,35 @@ def test_bench_plan_only_runs_without_a_device(capsys):
     assert out["plan_only"] and "not a measurement" in out["note"] and "metric" not in out and "value" not in out
     assert out["config"]["rounds"] == 2 and out["fitted"]["pools"]["backing_overflows_per_step"] == 0
     assert out["fitted"]["predicted_ms_per_step"] <= out["first_plan"]["predicted_ms_per_step"] * 1.01
+
+
+def test_every_process_arrives_at_the_same_plan():
+    """Ranks of a sharded run plan by themselves and must hold the same plan: the same inputs give the same plan in every
+    process, whatever its string-hash seed (planners iterate over sets and dicts of object names)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import dataclasses, hashlib, json\n"
+        "from dataflow_b200.core import to_sim_chain\n"
+        "from dataflow_b200.lowering import resolve_hardware\n"
+        "from dataflow_b200.models.families import resolve_family\n"
+        "from dataflow_b200.parallel.zero import zero_lower_kwargs\n"
+        "from dataflow_b200.run.driver import plan_at_budget\n"
+        "fam = resolve_family('llama3')\n"
+        "cfg = dataclasses.replace(fam.presets['tiny'](), n_layers=6, grad_accum_rounds=4)\n"
+        "out = []\n"
+        "for kw, gib in (({'resident_params': True}, 0.02), (zero_lower_kwargs('fsdp', 1, 2), 0.02), ({'resident_params': True}, 0.014)):\n"
+        "    p = plan_at_budget(fam, cfg, int(gib * (1 << 30)), resolve_hardware('b200'), leeway_bytes=0, lower_kwargs=kw)\n"
+        "    ch = to_sim_chain(p.program)\n"
+        "    rows = [[t.id, list(t.releases_after), [x.obj_id for x in t.offload_after], [x.obj_id for x in t.prefetch_after]] for t in ch.tasks]\n"
+        "    out.append([hashlib.sha256(json.dumps(rows).encode()).hexdigest()[:16], p.policy, round(p.makespan_us, 3)])\n"
+        "print(json.dumps(out))\n")
+    seen = set()
+    for seed in ("1", "2", "777"):
+        env = dict(os.environ, PYTHONHASHSEED=seed, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env, cwd=root)
+        assert r.returncode == 0, r.stderr[-2000:]
+        seen.add(r.stdout.strip().splitlines()[-1])
+    assert len(seen) == 1, seen
