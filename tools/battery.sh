@@ -16,6 +16,8 @@ fi
 python tools/verify/sweep_ladder3.py
 python tools/verify/pressure_correctness.py --budgets 0.03,0.02
 python tools/bench/pressurefit_exact_oracle.py --chains 5 --tasks 6
+python tools/bench/planner_quality_gate.py --quick --check
+python bench.py --plan-only
 '
 if [ "${1:-}" = "local" ]; then
   cd "$(dirname "$0")/.." && bash -c "$run_battery"
