@@ -198,7 +198,7 @@ def bench_ours(a) -> dict:
         # the communication stream (max over ranks, per step); 0 on one GPU, where nothing is communicated
         "exposed_comm_ms_per_step": exposed_ms / a.steps,
         "loss": float(lsum[0]) if losses else None,
-        "plan": {"predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
+        "plan": {"planner": str(tr.planned.policy), "predicted_ms_per_step": tr.planned.makespan_us / 1e3, "peak_fast_gib": tr.planned.peak_fast_bytes / 2**30,
                  "recompute_layers": len(tr.planned.recompute_levels), "engine_h2d_gb_per_step": res.stats["h2d_bytes"] / 1e9,
                  "engine_d2h_gb_per_step": res.stats["d2h_bytes"] / 1e9, "slab_overflows": res.slab_overflows, "pool": _pool_line(tr),
                  "static_placement": tr.placement is not None,
