@@ -581,6 +581,19 @@ def pressurefit(chain: TaskChain, fast_memory_capacity: int | None = None, *,
         if exited:
             break
     if best is None:
+        # last resort: the least residency that can run (every object on the device only while a task touches it, every fetch
+        # fired right before its use).  Slow, but when the capacity is a hair above what single tasks need it is the plan that fits
+        from .spans import SpanPlan
+        t0 = time.perf_counter()
+        try:
+            planned = SpanPlan(base).fill_min(0.0).emit(cap)
+            log = Simulator(planned).run()
+            c = Candidate("least_residency", "at_use", log.makespan, log.peak_fast_memory_bytes, None, 0, time.perf_counter() - t0)
+            cands.append(c)
+            best = (planned, log, c)
+        except (SimulationCapacityError, SimulationError) as e:
+            cands.append(Candidate("least_residency", "at_use", None, None, str(e)[:300], 0, time.perf_counter() - t0))
+    if best is None:
         detail = "; ".join(f"{c.spec}/{c.rule}: {c.error}" for c in cands[:3])
         raise PlanningError(f"no PressureFit candidate fits {cap} bytes of fast memory ({detail})")
     planned, log, c = best
