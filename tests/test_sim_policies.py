@@ -299,3 +299,41 @@ def test_the_engine_reproduces_the_simulated_log_of_every_planner(name, cap):
     res = Engine(FakeBackend()).execute(from_sim_chain(planned)).raise_if_failed()
     assert compare_to_sim_eventlog(res.trace, log) == []
     assert res.makespan_us == log.makespan and res.peak_fast_bytes <= cap
+
+
+def test_random_chains_every_planner_emits_valid_plans_the_engine_reproduces():
+    """A small sample of the fuzz that was run over thousands of plans while the planners were written: random forward /
+    backward chains and training chains, capacities from a hair above the largest task's own need to unbounded; every plan
+    passes the static validator, stays under its capacity, and runs on the virtual-time engine to the simulator's log."""
+    import importlib.util
+    import os
+    import random
+    from dataflow_b200.core import from_sim_chain
+    from dataflow_b200.runtime import Engine, FakeBackend, compare_to_sim_eventlog
+    from dataflow_b200.sim.validate import ValidationError
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("oracle_tool", os.path.join(root, "tools", "bench", "pressurefit_exact_oracle.py"))
+    tool = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tool)
+    rng = random.Random(11)
+    pols = {k: v for k, v in get_all_policies().items() if k != "all_resident"}
+    checked = 0
+    for c in range(10):
+        chain = (replace(tool.random_chain(rng, rng.choice([4, 6, 8, 10])).bare(), fast_memory_capacity=None) if c % 2
+                 else train_chain(L=rng.choice([2, 3, 5]), rounds=rng.choice([1, 2, 3])).bare())
+        need = float(static_minimum(chain).max())
+        for frac in (1.02, 1.5, None):
+            cap = None if frac is None else int(need * frac)
+            for name, fn in pols.items():
+                try:
+                    planned = fn(chain, cap)
+                except (PlanningError, ValidationError):
+                    assert name == "sliding_window", (name, c, frac)        # only the capacity-blind pattern may give up
+                    continue
+                assert chain_problems(planned) == [], (name, c, frac)
+                log = run(planned)
+                assert cap is None or log.peak_fast_memory_bytes <= cap, (name, c, frac)
+                res = Engine(FakeBackend()).execute(from_sim_chain(planned)).raise_if_failed()
+                assert compare_to_sim_eventlog(res.trace, log) == [] and res.makespan_us == log.makespan, (name, c, frac)
+                checked += 1
+    assert checked > 200
