@@ -414,7 +414,13 @@ def run(chain: TaskChain, validate: bool = True, snapshots: bool = False,
     if validate:
         from .validate import validate_chain
         validate_chain(chain)
-    return Simulator(chain, events=snapshots, memory_trace=memory_trace).run()
+    try:
+        return Simulator(chain, events=snapshots, memory_trace=memory_trace).run()
+    except (KeyError, AssertionError) as e:
+        # only a chain that the static validator would refuse gets here (validate=False): a directive for a copy that an
+        # earlier directive already took away, found when the transfer completes
+        raise SimulationError(f"the chain drove the simulation into an inconsistent state ({type(e).__name__}: {e}); "
+                              f"validate_chain says what is wrong with it") from e
 
 
 def compute_lower_bound(chain: TaskChain) -> float:

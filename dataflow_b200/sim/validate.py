@@ -50,8 +50,10 @@ RULES = {
     "duplicate-transfer": "one task moves one object twice in one direction",
     "release-and-offload": "one task both releases and offloads one object",
     "release-not-resident": "a release of an object that has no fast copy",
+    "duplicate-release": "one task releases one object twice",
     # lifetimes
     "input-not-resident": "a task reads an object whose fast copy is gone and was not brought back",
+    "prefetch-never-used": "a prefetch of an object that nothing reads afterwards and that need not end in fast memory",
     "release-loses-data": "a release drops the only current copy of bytes that are read, fetched or required later",
     "final-not-on-backing": "final_locations wants a backing copy that does not exist",
     "final-backing-stale": "final_locations wants a backing copy, and the one there is older than the fast copy",
@@ -211,15 +213,18 @@ def check_transfers(chain: TaskChain) -> list[Problem]:
         for o in dict.fromkeys(off):
             if o not in st.fast and o not in produced_fast:
                 out.append(Problem("offload-not-resident", f"offloads {o!r}, which has no fast copy", t.id, o))
+        for o in sorted({x for x in t.releases_after if t.releases_after.count(x) > 1}):
+            out.append(Problem("duplicate-release", f"releases {o!r} {t.releases_after.count(o)} times", t.id, o))
         for o in dict.fromkeys(t.releases_after):
             if o not in st.fast and o not in produced_fast:
                 out.append(Problem("release-not-resident", f"releases {o!r}, which has no fast copy", t.id, o))
         for o in dict.fromkeys(pre):
             if o in set(off):
-                continue
+                continue                                   # the fetch waits for this task's offload, which makes the backing copy
             if (o in st.fast or o in produced_fast) and o not in t.releases_after:
                 out.append(Problem("prefetch-already-resident", f"prefetches {o!r}, which is in fast memory", t.id, o))
             elif o not in st.backing and o not in produced_backing:
+                # (also when this task drops the fast copy first: dropping it does not make a backing copy)
                 out.append(Problem("prefetch-without-backing-copy", f"prefetches {o!r}, which has no backing copy", t.id, o))
         st.commit(t)
     return out
@@ -236,11 +241,21 @@ def check_lifetimes(chain: TaskChain) -> list[Problem]:
     n = len(chain.tasks)
     for o in chain.final_locations:
         later_use.setdefault(o, []).append(n)
+    reads: dict[str, list[int]] = {}
+    for i, t in enumerate(chain.tasks):
+        for o in t.inputs:
+            reads.setdefault(o, []).append(i)
     for i, t in enumerate(chain.tasks):
         for o in t.inputs:
             if o not in st.fast:
                 how = "only a backing copy exists" if o in st.backing else "no copy exists"
                 out.append(Problem("input-not-resident", f"reads {o!r}, but {how} and nothing brought it back", t.id, o))
+        for tr in t.prefetch_after:
+            o = tr.obj_id
+            if not any(j > i for j in reads.get(o, ())) and chain.final_locations.get(o) != "fast":
+                # (the simulator frees every copy of an object at a release past its last reference, so such a fetch can
+                # also find its source gone)
+                out.append(Problem("prefetch-never-used", f"prefetches {o!r}, which no later task reads", t.id, o))
         dirty_after = (st.dirty | set(t.mutates_inputs) | {o.id for o in t.outputs if o.location == "fast"})
         for r in t.releases_after:
             if r in {x.obj_id for x in t.offload_after}:

@@ -61,9 +61,12 @@ CASES = {
     "duplicate-transfer": edit(0, prefetch_after=[T("w"), T("w")]),
     "release-and-offload": edit(2, releases_after=["y", "u", "k", "z"]),
     "release-not-resident": edit(0, releases_after=["w"], prefetch_after=[]),
+    "duplicate-release": edit(3, releases_after=["x", "x"]),
     # lifetimes
     # y was offloaded by a and never comes back for c
     "input-not-resident": both(edit(1, prefetch_after=[]), edit(2, releases_after=["u", "k"])),
+    # w comes back after its only reader has run
+    "prefetch-never-used": edit(2, prefetch_after=[T("w")]),
     # u is read by c and was never offloaded
     "release-loses-data": both(edit(1, releases_after=["w", "u"]), edit(2, releases_after=["y", "k"])),
     "final-not-on-backing": edit(2, offload_after=[]),
@@ -192,3 +195,70 @@ def test_the_invalid_chains_on_disk_are_the_cases_above_and_the_tools_refuse_the
         assert main(["validate", str(path)]) == 1 and rule in capsys.readouterr().out
     with open(os.path.join(FIXTURES, "valid.json")) as f:
         assert chain_problems(TaskChain.from_dict(json.load(f)["chain"])) == []
+
+
+def test_what_the_simulator_refuses_for_its_structure_the_validator_refuses_first():
+    """Random single edits of valid plans (a directive dropped, added, doubled, moved later, a release turned into an offload).
+    Whenever the simulator rejects the edited chain for a reason other than capacity at run time, the static validator
+    has already rejected it; the other way round is allowed (the validator also refuses what the simulator tolerates, like
+    a transfer listed twice)."""
+    import random
+    from dataflow_b200.sim.errors import SimulationCapacityError, SimulationError
+    from dataflow_b200.sim.policies import get_all_policies
+    rng = random.Random(5)
+    pols = get_all_policies()
+
+    def mutate(ch):
+        tasks = list(ch.tasks)
+        i = rng.randrange(len(tasks))
+        t = tasks[i]
+        objs = list(ch.sizes())
+        kind = rng.choice(["drop_prefetch", "drop_offload", "add_release", "add_prefetch", "add_offload", "dup_prefetch", "dup_release", "move_prefetch_late", "swap"])
+        if kind == "drop_prefetch" and t.prefetch_after:
+            t = replace(t, prefetch_after=t.prefetch_after[1:])
+        elif kind == "drop_offload" and t.offload_after:
+            t = replace(t, offload_after=t.offload_after[1:])
+        elif kind == "add_release":
+            t = replace(t, releases_after=t.releases_after + [rng.choice(objs)])
+        elif kind == "add_prefetch":
+            t = replace(t, prefetch_after=t.prefetch_after + [T(rng.choice(objs))])
+        elif kind == "add_offload":
+            t = replace(t, offload_after=t.offload_after + [T(rng.choice(objs))])
+        elif kind == "dup_prefetch" and t.prefetch_after:
+            t = replace(t, prefetch_after=t.prefetch_after + [t.prefetch_after[0]])
+        elif kind == "dup_release" and t.releases_after:
+            t = replace(t, releases_after=t.releases_after + [t.releases_after[0]])
+        elif kind == "move_prefetch_late" and t.prefetch_after and i + 2 < len(tasks):
+            tr = t.prefetch_after[0]
+            t = replace(t, prefetch_after=t.prefetch_after[1:])
+            j = rng.randrange(i + 1, len(tasks))
+            tasks[j] = replace(tasks[j], prefetch_after=tasks[j].prefetch_after + [tr])
+        elif kind == "swap" and t.releases_after:
+            t = replace(t, releases_after=t.releases_after[1:], offload_after=t.offload_after + [T(t.releases_after[0])])
+        else:
+            return None
+        tasks[i] = t
+        return replace(ch, tasks=tasks)
+
+    refused_by_both = tolerated = 0
+    for L, R, cap, pol in ((4, 2, 3000, "lookahead"), (5, 2, 2600, "max_reduce"), (3, 3, 2400, "min_grow")):
+        good = pols[pol](train_chain(L=L, rounds=R), cap)
+        assert chain_problems(good) == []
+        for _ in range(250):
+            bad = mutate(good)
+            if bad is None:
+                continue
+            static = chain_problems(bad)
+            try:
+                run(bad, validate=False)
+                structural = None
+            except SimulationCapacityError as e:
+                structural = None if e.kind in ("fast-deadlock", "stuck-transfers") else e       # memory ran out at run time: not a static matter
+            except SimulationError as e:
+                structural = e
+            if structural is not None:
+                assert static, f"{pol}: the simulator refused ({structural}) what the validator passed"
+                refused_by_both += 1
+            elif static:
+                tolerated += 1
+    assert refused_by_both > 150 and tolerated > 10
