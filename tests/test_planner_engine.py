@@ -255,3 +255,56 @@ def test_annotators_see_every_task_and_transfer_under_renamed_labels():
     assert all(not i.name.startswith("[") for i in res.trace.intervals)
     plain = Engine(FakeBackend()).execute(prog).raise_if_failed()
     assert plain.makespan_us == res.makespan_us
+
+
+def test_malformed_plans_end_in_typed_errors_never_in_a_crash():
+    """Random single edits of valid plans (directives dropped, added, doubled, moved) on the virtual-time backend: the
+    engine either runs the program (its valves absorb what is only a capacity problem) or refuses it with one of its typed
+    errors; whatever the simulator accepts, the engine accepts."""
+    import random
+    from dataclasses import replace
+    from dataflow_b200.sim import TransferTrigger as T
+    from dataflow_b200.sim.errors import SimulationError
+    from dataflow_b200.sim.policies import get_all_policies
+    rng = random.Random(21)
+    known = {"ExecutionError", "DeadlockError", "FinalLocationError", "ValidationError", "CapacityError"}
+    seen = set()
+    for pol, cap in (("lookahead", 3000), ("max_reduce", 2600)):
+        good = get_all_policies()[pol](train_chain(L=4, rounds=2), cap)
+        objs = list(good.sizes())
+        for _ in range(120):
+            tasks = list(good.tasks)
+            i = rng.randrange(len(tasks))
+            t = tasks[i]
+            kind = rng.choice(["drop_prefetch", "drop_release", "add_release", "add_prefetch", "add_offload", "dup_release"])
+            if kind == "drop_prefetch" and t.prefetch_after:
+                t = replace(t, prefetch_after=t.prefetch_after[1:])
+            elif kind == "drop_release" and t.releases_after:
+                t = replace(t, releases_after=t.releases_after[1:])
+            elif kind == "add_release":
+                t = replace(t, releases_after=t.releases_after + [rng.choice(objs)])
+            elif kind == "add_prefetch":
+                t = replace(t, prefetch_after=t.prefetch_after + [T(rng.choice(objs))])
+            elif kind == "add_offload":
+                t = replace(t, offload_after=t.offload_after + [T(rng.choice(objs))])
+            elif kind == "dup_release" and t.releases_after:
+                t = replace(t, releases_after=t.releases_after + [t.releases_after[0]])
+            else:
+                continue
+            tasks[i] = t
+            bad = replace(good, tasks=tasks)
+            try:
+                run(bad, validate=False)
+                sim_ok = True
+            except SimulationError:
+                sim_ok = False
+            try:
+                res = Engine(FakeBackend()).execute(from_sim_chain(bad))
+                outcome = "ok" if res.outcome.ok else res.outcome.error_kind
+            except Exception as e:       # noqa: BLE001  (validation refuses before the engine starts)
+                outcome = type(e).__name__
+            seen.add(outcome)
+            assert outcome == "ok" or outcome in known, (kind, outcome)
+            if sim_ok:
+                assert outcome == "ok", (kind, outcome)
+    assert "ok" in seen and len(seen) >= 3
