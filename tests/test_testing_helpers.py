@@ -115,3 +115,34 @@ def test_block_backward_reports_only_the_blocks_fields_with_cosines():
     assert rep, rep.summary()
     assert rep.grad_rel_l2 and all(k.startswith("layers.1.") for k in rep.grad_rel_l2)
     assert set(rep.grad_cos) == set(rep.grad_rel_l2) and min(rep.grad_cos.values()) > 0.999
+
+
+def test_a_daemon_survives_malformed_traffic():
+    """Garbage, truncated and lying frames on fresh connections: the daemon closes or answers with an error and keeps serving
+    its other clients; what it stored is untouched."""
+    import socket
+    with out_of_process_server(0.05, fake=True) as c:
+        path = c.server_process.socket_path
+        c.put_object("keep", b"x" * 64)
+        frames = [os.urandom(300) + b"\n", b"hello world\n", b"[1,2,3]\n", b"42\n", b"\n", b"\x00" * 100 + b"\n",
+                  b'{"schema":"other/v9","op":"health"}\n',
+                  b'{"schema":"dataflow-service/s1","op":"put_object","id":"a","payload_bytes":-5}\n',
+                  b'{"schema":"dataflow-service/s1","op":"put_object","id":"a","payload_bytes":"many"}\n',
+                  b'{"schema":"dataflow-service/s1","op":"put_object","id":"a","payload_bytes":99999999999}\nabc',
+                  b'{"schema":"dataflow-service/s1","op":"hea',
+                  b'{"schema":"dataflow-service/s1","op":"health","x":' + b"[" * 3000 + b"]" * 3000 + b"}\n",
+                  b'{"schema":"dataflow-service/s1","op":"create_object","id":17,"size":"big"}\n']
+        for data in frames:
+            s = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            s.settimeout(2.0)
+            s.connect(path)
+            try:
+                s.sendall(data)
+                try:
+                    s.recv(4096)
+                except (socket.timeout, ConnectionError):
+                    pass
+            finally:
+                s.close()
+            assert c.server_process.alive, data[:40]
+        assert c.health()["ok"] and c.get_object("keep") == b"x" * 64 and "a" not in [o["id"] if isinstance(o, dict) else o for o in c.list_objects()]
