@@ -107,11 +107,24 @@ def read_record(step_dir: str, field_schemas: Mapping[str, Mapping[str, Any]] | 
     path = os.path.join(step_dir, RECORD_FILE)
     if not os.path.exists(path):
         raise RecordError(f"{step_dir}: no {RECORD_FILE} — not a complete checkpoint")
-    with open(path) as f:
-        rec = json.load(f)
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+    except (ValueError, OSError) as e:
+        raise RecordError(f"{path} is damaged ({type(e).__name__}: {e}) — not a complete checkpoint") from None
     validate_record(rec, field_schemas)
     return rec
 
 
 def has_record(step_dir: str) -> bool:
-    return os.path.exists(os.path.join(step_dir, RECORD_FILE))
+    """True when the directory holds a record that parses.  The record is written last, so its presence means every slice
+    was written; a record that does not parse (a damaged disk, a copy cut short) makes the directory no checkpoint at all,
+    and resuming from "latest" then goes to the step before."""
+    path = os.path.join(step_dir, RECORD_FILE)
+    if not os.path.exists(path):
+        return False
+    try:
+        with open(path) as f:
+            return isinstance(json.load(f), dict)
+    except (ValueError, OSError):
+        return False

@@ -70,8 +70,11 @@ def read_snapshot_slice(path, entry: dict) -> bytes:
     """Bytes of one manifest entry, hash-verified."""
     buf = bytearray()
     for name in entry["files"]:
-        with open(Path(path) / name, "rb") as f:
-            buf += f.read()
+        try:
+            with open(Path(path) / name, "rb") as f:
+                buf += f.read()
+        except OSError as e:
+            raise ServiceError("VERIFY_FAILED", f"slice of {entry['as']!r} in {path}: file {name!r} cannot be read ({type(e).__name__})") from None
     buf = bytes(buf[:entry["size"]])
     if slice_hash(memoryview(buf)) != entry["hash"]:
         raise ServiceError("VERIFY_FAILED", f"slice of {entry['as']!r} in {path} does not match its recorded hash")
@@ -99,8 +102,12 @@ def read_manifest(path) -> dict:
     p = Path(path) / MANIFEST
     if not p.exists():
         raise ServiceError("UNKNOWN_SNAPSHOT", f"no complete snapshot at {path}")
-    m = json.loads(p.read_text())
-    if m.get("schema") != SNAPSHOT_SCHEMA:
+    try:
+        m = json.loads(p.read_text())
+    except (ValueError, OSError) as e:
+        raise ServiceError("VERIFY_FAILED", f"the manifest of the snapshot at {path} is damaged ({type(e).__name__}: {e})") from None
+    if not isinstance(m, dict) or m.get("schema") != SNAPSHOT_SCHEMA:
+        m = m if isinstance(m, dict) else {}
         raise ServiceError("VERSION_SKEW", f"snapshot schema {m.get('schema')!r}, expected {SNAPSHOT_SCHEMA!r}")
     return m
 
@@ -148,7 +155,10 @@ def restore_job(server, job: dict) -> None:
             e = w["entry"]
             buf = bytearray()
             for name in e["files"]:
-                buf += (src / name).read_bytes()
+                try:
+                    buf += (src / name).read_bytes()
+                except OSError as err:
+                    raise ServiceError("VERIFY_FAILED", f"slice of {e['as']!r}: file {name!r} cannot be read ({type(err).__name__})") from None
             if id(e) not in verified:
                 if slice_hash(memoryview(buf)) != e["hash"]:
                     raise ServiceError("VERIFY_FAILED", f"slice of {e['as']!r} does not match its recorded hash")

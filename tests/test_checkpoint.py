@@ -93,3 +93,46 @@ def test_solo_resume_is_bitwise(tmp_path, lower_kwargs):
     resumed = [tr2.step(data[s]) for s in range(3, 6)]
     tr2.close()
     assert resumed == straight[3:]
+
+
+def test_damaged_checkpoints_are_refused_by_name_and_latest_skips_them(tmp_path):
+    """A slice cut short, a flipped byte, a missing slice file, a damaged manifest, a damaged record: each is refused with an
+    error that says what is wrong; a directory whose record does not parse is no checkpoint, so "latest" is the step before."""
+    import glob
+    from dataflow_b200.service.wire import ServiceError
+    fam = resolve_family("llama3")
+    cfg = dataclasses.replace(fam.presets["tiny"](), dtype_policy="fp32")
+    tr = Trainer("llama3", cfg, budget_gib=None, device=None, hyper={"lr": 2e-3}, seed=3, leeway_bytes=0)
+    try:
+        tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, 64, 11, 0))
+        first = save_checkpoint(tr, str(tmp_path), 1, seed=3)
+        tr.step(synthetic_rounds(cfg, tr.rounds, tr.T, 64, 11, 1))
+        second = save_checkpoint(tr, str(tmp_path), 2, seed=3)
+        assert resolve_resume("latest", str(tmp_path)) == second
+        big = max(glob.glob(os.path.join(second, "rank0", "*.bin")), key=os.path.getsize)
+        whole = open(big, "rb").read()
+        for damage, needle in ((whole[:len(whole) // 2], "does not match its recorded hash"),
+                               (whole[:100] + bytes([whole[100] ^ 0xFF]) + whole[101:], "does not match its recorded hash"), (None, "cannot be read")):
+            if damage is None:
+                os.remove(big)
+            else:
+                open(big, "wb").write(damage)
+            with pytest.raises(ServiceError, match=needle):
+                load_checkpoint(tr, second)
+        open(big, "wb").write(whole)
+        load_checkpoint(tr, second)                                   # intact again: loads
+        manifest = os.path.join(second, "rank0", "snapshot_manifest.json")
+        text = open(manifest).read()
+        open(manifest, "w").write(text[:len(text) // 2])
+        with pytest.raises(ServiceError, match="manifest .* is damaged"):
+            load_checkpoint(tr, second)
+        open(manifest, "w").write(text)
+        record = os.path.join(second, "checkpoint_record.json")
+        text = open(record).read()
+        open(record, "w").write(text[:len(text) // 2])
+        with pytest.raises(RecordError, match="is damaged"):
+            read_record(second)
+        assert [s for s, _ in list_checkpoints(str(tmp_path))] == [1] and resolve_resume("latest", str(tmp_path)) == first
+        assert load_checkpoint(tr, first)["step"] == 1 and tr.step_index == 1
+    finally:
+        tr.close()
