@@ -36,10 +36,17 @@ class TextSource(DataSource):
     def _records(self, path: str):
         if self.scheme == "jsonl":
             with open(path, "r", encoding="utf-8") as f:
-                for line in f:
+                for lineno, line in enumerate(f, 1):
                     line = line.strip()
-                    if line:
-                        yield json.loads(line)
+                    if not line:
+                        continue
+                    try:
+                        rec = json.loads(line)
+                    except ValueError as e:
+                        raise ValueError(f"{path}:{lineno}: not a JSON document ({e})") from None
+                    if not isinstance(rec, dict):
+                        raise ValueError(f"{path}:{lineno}: a record must be a JSON object, this line is a {type(rec).__name__}")
+                    yield rec
         else:
             with open(path, "r", encoding="utf-8") as f:
                 for part in f.read().split(self.delimiter):
@@ -66,16 +73,23 @@ class TextSource(DataSource):
 
     def raw(self, cursor):
         epoch, fi, ri = int(cursor.get("epoch", 0)), int(cursor.get("file", 0)), int(cursor.get("record", 0))
+        produced = 0                    # documents of the current pass over the files
+        started = (fi, ri)
         while True:
             for k, rec in enumerate(self._records(self.files[fi])):
                 if k < ri:
                     continue
                 seq = self._encode(rec)
                 if seq is not None:
+                    produced += 1
                     yield seq, {"epoch": epoch, "file": fi, "record": k + 1}
             fi, ri = fi + 1, 0
             if fi >= len(self.files):
-                fi, epoch = 0, epoch + 1
+                if produced == 0 and started == (0, 0):
+                    # epochs wrap: without this a corpus with nothing usable in it would be read for ever
+                    what = f"field {self.field!r}" if self.scheme == "jsonl" else "text"
+                    raise ValueError(f"no usable document in {len(self.files)} file(s) matching the source ({what} of at least two tokens)")
+                fi, epoch, produced, started = 0, epoch + 1, 0, (0, 0)
 
     def describe(self) -> dict:
         return {**super().describe(), "files": len(self.files), "tokenizer": self.tok.describe(), "eot_id": self.tok.eot_id,

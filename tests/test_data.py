@@ -140,3 +140,26 @@ def test_capture_replays_exactly(tmp_path):
     st.close()
     assert sorted(np.concatenate(got).tolist()) == sorted(toks.tolist())
     assert sum(len(g) for g in got) == len(toks)
+
+
+def test_text_sources_name_the_bad_line_and_do_not_read_an_empty_corpus_for_ever(tmp_path):
+    good = json.dumps({"text": "a perfectly fine document"})
+    cases = {"broken.jsonl": (good + "\n{\"text\": \"cut sho\n", r"broken\.jsonl:2: not a JSON document"),
+             "list.jsonl": (good + "\n[1, 2, 3]\n", r"list\.jsonl:2: a record must be a JSON object, this line is a list")}
+    for name, (body, needle) in cases.items():
+        p = tmp_path / name
+        p.write_text(body)
+        src = resolve_data(f"jsonl:{p},tokenizer=bytes", vocab_size=65536, max_seqlen=64)
+        with pytest.raises(ValueError, match=needle):
+            take(src, 5)
+    # nothing usable: no text field anywhere, or only documents shorter than two tokens.  Epochs wrap, so without a check
+    # the source would spin through the files for ever
+    empty = tmp_path / "empty.jsonl"
+    empty.write_text(json.dumps({"title": "no text field"}) + "\n" + json.dumps({"text": ""}) + "\n\n")
+    with pytest.raises(ValueError, match="no usable document"):
+        take(resolve_data(f"jsonl:{empty},tokenizer=bytes", vocab_size=65536, max_seqlen=64), 1)
+    # a corpus with one usable document wraps as before
+    one = tmp_path / "one.jsonl"
+    one.write_text(json.dumps({"title": "skip me"}) + "\n" + good + "\n")
+    got = take(resolve_data(f"jsonl:{one},tokenizer=bytes", vocab_size=65536, max_seqlen=64), 3)
+    assert len(got) == 3 and [c["epoch"] for _, c in got] == [0, 1, 2]
