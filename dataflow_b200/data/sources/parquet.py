@@ -32,6 +32,7 @@ class ParquetSource(DataSource):
         import pyarrow.parquet as pq
         epoch, fi = int(cursor.get("epoch", 0)), int(cursor.get("file", 0))
         gi, ri = int(cursor.get("group", 0)), int(cursor.get("row", 0))
+        produced, fresh_pass = 0, (fi, gi, ri) == (0, 0, 0)
         while True:
             pf = pq.ParquetFile(self.files[fi])
             for g in range(gi, pf.num_row_groups):
@@ -42,10 +43,13 @@ class ParquetSource(DataSource):
                         continue
                     ids = np.asarray(self.tok.encode(text), dtype=np.int32)
                     if len(ids) >= 2:
+                        produced += 1
                         yield Sequence.from_document(ids, self.tok.eot_id), {"epoch": epoch, "file": fi, "group": g, "row": k + 1}
             fi, gi, ri = fi + 1, 0, 0
             if fi >= len(self.files):
-                fi, epoch = 0, epoch + 1
+                if produced == 0 and fresh_pass:       # epochs wrap: a corpus with nothing usable would be read for ever
+                    raise ValueError(f"no usable document in {len(self.files)} parquet file(s): column {self.column!r} holds no text of at least two tokens")
+                fi, epoch, produced, fresh_pass = 0, epoch + 1, 0, True
 
     def describe(self) -> dict:
         return {**super().describe(), "files": len(self.files), "column": self.column, "tokenizer": self.tok.describe(),

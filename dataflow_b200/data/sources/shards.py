@@ -59,6 +59,7 @@ class ShardSource(DataSource):
 
     def raw(self, cursor):
         epoch, si, pos = int(cursor.get("epoch", 0)), int(cursor.get("shard", 0)), int(cursor.get("pos", 0))
+        produced, fresh_pass = 0, (si, pos) == (0, 0)
         while True:
             ids = read_shard(self.files[si])
             n = len(ids)
@@ -67,6 +68,7 @@ class ShardSource(DataSource):
                 while pos + w + 1 <= n:
                     chunk = np.asarray(ids[pos:pos + w + 1], dtype=np.int32)
                     pos += w
+                    produced += 1
                     yield Sequence(chunk[:-1], chunk[1:].copy()), {"epoch": epoch, "shard": si, "pos": pos}
             else:
                 delim = np.flatnonzero(np.asarray(ids[pos:]) == self.delimiter) + pos
@@ -74,11 +76,15 @@ class ShardSource(DataSource):
                     if d > pos:
                         doc = np.asarray(ids[pos:d], dtype=np.int32)
                         nxt = int(d) + 1
+                        produced += 1
                         yield Sequence.from_document(doc, self.delimiter), {"epoch": epoch, "shard": si, "pos": nxt}
                     pos = int(d) + 1
             si, pos = si + 1, 0
             if si >= len(self.files):
-                si, epoch = 0, epoch + 1
+                if produced == 0 and fresh_pass:       # epochs wrap: shards with nothing usable would be read for ever
+                    what = f"no window of {self.window} + 1 tokens fits any shard" if self.window else f"no document ends with the delimiter id {self.delimiter}"
+                    raise ValueError(f"no usable sequence in {len(self.files)} shard(s) under {self.root!r}: {what}")
+                si, epoch, produced, fresh_pass = 0, epoch + 1, 0, True
 
     def _cursor_before(self, after, before):
         return dict(before)

@@ -163,3 +163,12 @@ def test_text_sources_name_the_bad_line_and_do_not_read_an_empty_corpus_for_ever
     one.write_text(json.dumps({"title": "skip me"}) + "\n" + good + "\n")
     got = take(resolve_data(f"jsonl:{one},tokenizer=bytes", vocab_size=65536, max_seqlen=64), 3)
     assert len(got) == 3 and [c["epoch"] for _, c in got] == [0, 1, 2]
+
+
+def test_shards_with_nothing_usable_end_with_an_error(tmp_path):
+    write_shard(str(tmp_path / "tiny_train_000.bin"), np.arange(40) % 7)            # 40 tokens, no delimiter id among them
+    with pytest.raises(ValueError, match="no window of 64 \\+ 1 tokens fits any shard"):
+        take(resolve_data(f"shards:{tmp_path},window=64", vocab_size=65536, max_seqlen=128), 1)
+    with pytest.raises(ValueError, match="no document ends with the delimiter"):
+        take(resolve_data(f"shards:{tmp_path}", vocab_size=65536, max_seqlen=128), 1)
+    assert len(take(resolve_data(f"shards:{tmp_path},window=16", vocab_size=65536, max_seqlen=128), 5)) == 5     # wraps as before
