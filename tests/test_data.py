@@ -172,3 +172,19 @@ def test_shards_with_nothing_usable_end_with_an_error(tmp_path):
     with pytest.raises(ValueError, match="no document ends with the delimiter"):
         take(resolve_data(f"shards:{tmp_path}", vocab_size=65536, max_seqlen=128), 1)
     assert len(take(resolve_data(f"shards:{tmp_path},window=16", vocab_size=65536, max_seqlen=128), 5)) == 5     # wraps as before
+
+
+def test_parquet_source_reads_resumes_and_refuses_an_empty_column(tmp_path):
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    docs = [f"parquet document {i} " + "word " * (i % 5 + 1) for i in range(12)]
+    pq.write_table(pa.table({"text": docs[:6] + [""]}), tmp_path / "a.parquet", row_group_size=3)
+    pq.write_table(pa.table({"text": docs[6:]}), tmp_path / "b.parquet", row_group_size=4)
+    spec = f"parquet:{tmp_path}/*.parquet,tokenizer=bytes"
+    got = take(resolve_data(spec, vocab_size=65536, max_seqlen=256), 14)
+    assert [c["epoch"] for _, c in got] == [0] * 12 + [1, 1] and len({bytes(s.tokens) for s, _ in got[:12]}) == 12
+    again = take(resolve_data(spec, vocab_size=65536, max_seqlen=256), 4, got[7][1])          # resume after the eighth document
+    assert all(np.array_equal(a.tokens, b.tokens) for (a, _), (b, _) in zip(again, got[8:12]))
+    pq.write_table(pa.table({"text": ["", "", "x"]}), tmp_path / "none.pq")
+    with pytest.raises(ValueError, match="no usable document"):
+        take(resolve_data(f"parquet:{tmp_path}/none.pq,tokenizer=bytes", vocab_size=65536, max_seqlen=64), 1)
