@@ -33,9 +33,23 @@ def all_resident(chain: TaskChain, fast_memory_capacity: int | None = None) -> T
             initial.append(Object(f.id, f.size, "fast", f.type))
     tasks = [replace(t, releases_after=[], offload_after=[], prefetch_after=[]) for t in base.tasks]
     dirty = {f.id: (f.birth != -1 or not f.in_backing) for f in facts.values()}
+    if tasks:
+        for f in facts.values():
+            # an initial fast object nothing reads: it leaves after the first task (written back when it must end in backing
+            # memory and has no copy there)
+            if f.birth == -1 and f.in_fast and not f.uses and f.final != "fast":
+                if f.final == "backing" and not f.in_backing:
+                    tasks[0].offload_after.append(TransferTrigger(f.id))
+                else:
+                    tasks[0].releases_after.append(f.id)
     for i, t in enumerate(base.tasks):
         for m in t.mutates_inputs:
             dirty[m] = True
+        for x in t.outputs:
+            # an output produced in backing memory that something reads later is fetched at once and stays
+            if x.location == "backing" and len(facts[x.id].uses) > 1:
+                tasks[i].prefetch_after.append(TransferTrigger(x.id))
+                dirty[x.id] = False
         for o in dict.fromkeys(list(t.inputs) + [x.id for x in t.outputs if x.location == "fast"]):
             f = facts[o]
             if not f.uses or f.uses[-1] != i:

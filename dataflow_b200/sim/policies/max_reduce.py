@@ -36,7 +36,7 @@ def reduce_to_fit(plan: SpanPlan, cap: float, slack: float = 1.0) -> int:
             cover[k, a:b + 1] = True
     touched = [set(plan.touch[o]) for o in names]
     rounds = 0
-    while True:
+    while n:
         over = plan.level - cap
         i = int(np.argmax(over))
         if over[i] <= 0:
@@ -78,6 +78,7 @@ def reduce_to_fit(plan: SpanPlan, cap: float, slack: float = 1.0) -> int:
             cuts += 1
             if plan.level[i] <= cap:
                 break
+    return cuts
 
 
 def max_reduce(chain: TaskChain, fast_memory_capacity: int | None = None, slack: float = 1.0) -> TaskChain:

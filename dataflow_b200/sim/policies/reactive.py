@@ -80,6 +80,12 @@ def belady_reactive(chain: TaskChain, fast_memory_capacity: int | None = None, h
             if fl is not None:
                 asked.add(fl.obj)
             leaving: set[str] = set()
+            if i == 0:
+                # initial fast objects nothing ever reads leave at the first boundary
+                for o, e in list(sh.resident().items()):
+                    if o not in fut.uses and final.get(o) != "fast" and o not in task.inputs:
+                        (sh.offload if final.get(o) == "backing" and sh.needs_offload(o) else sh.release)(o)
+                        leaving.add(o)
             # deaths
             for o in dict.fromkeys(list(task.inputs) + [x.id for x in task.outputs if x.location == "fast"]):
                 if fut.next_use(o, i) is not None or sh.where(o)[0] != "live":

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from ..errors import SimulationError
 from ..schema import TaskChain
 from .pressurefit import PlanningError
 from .spans import LaneTimeline, SpanPlan, check_input, verify
@@ -153,7 +154,7 @@ def roundtrip_planner(chain: TaskChain, fast_memory_capacity: int | None = None)
     for share in (0.9, 0.7, 0.5):
         try:
             planned, log, _ = verify(lambda c: build_plan(base, None if c is None else float(c), share).emit(cap), cap, "roundtrip")
-        except PlanningError as e:
+        except (PlanningError, SimulationError) as e:
             err = err or e
             continue
         if best is None or log.makespan < best[1].makespan:

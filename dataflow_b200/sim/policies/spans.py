@@ -62,9 +62,13 @@ class SpanPlan:
 
     # ---------------------------------------------------------------------------------------------------- transfer times
     def tau_in(self, o: str) -> float:
+        if not self.chain.bandwidth_from_slow:
+            raise PlanningError("the chain gives no bandwidth_from_slow: nothing can be fetched, only plans that keep everything resident exist")
         return transfer_runtime(self.facts[o].size, self.chain.bandwidth_from_slow, None, "from_slow")
 
     def tau_out(self, o: str) -> float:
+        if not self.chain.bandwidth_to_slow:
+            raise PlanningError("the chain gives no bandwidth_to_slow: nothing can be offloaded")
         return transfer_runtime(self.facts[o].size, self.chain.bandwidth_to_slow, None, "to_slow")
 
     def lead_start(self, o: str, need: int, slack: float = 1.0) -> int:
