@@ -165,6 +165,19 @@ def program_to_dict(p: Program) -> dict[str, Any]:
 
 
 def program_from_dict(d: dict[str, Any]) -> Program:
+    """A ``Program`` from its JSON form.  A document that is not one (a key missing, a list where an object belongs, a string
+    where a number belongs) is refused with a ``ValueError`` that says where, never with the ``KeyError`` / ``TypeError``
+    the decoding happened to trip over."""
+    if not isinstance(d, dict):
+        raise ValueError(f"not a {SCHEMA_VERSION} program: the document is a {type(d).__name__}, not an object")
+    try:
+        return _program_from_dict(d)
+    except (KeyError, TypeError, AttributeError, IndexError) as e:
+        what = f"key {e.args[0]!r} is missing" if isinstance(e, KeyError) and e.args else f"{type(e).__name__}: {e}"
+        raise ValueError(f"not a {SCHEMA_VERSION} program: {what}") from None
+
+
+def _program_from_dict(d: dict[str, Any]) -> Program:
     version = d.get("schema_version", SCHEMA_VERSION)
     if version != SCHEMA_VERSION:
         raise ValueError(f"unsupported schema_version {version!r}; expected {SCHEMA_VERSION!r}")

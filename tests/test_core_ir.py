@@ -70,3 +70,18 @@ def test_sim_conversion_roundtrip():
     assert [t.releases_after for t in back.tasks] == [t.releases_after for t in p.tasks]
     doc = to_webapp_program(p)
     assert doc["schema_version"] == "dataflow/v1" and len(doc["tasks"]) == 2
+
+
+def test_documents_that_are_not_programs_are_refused_by_name():
+    from dataflow_b200.core import program_from_dict
+    from dataflow_b200.core.jsonio import program_to_dict
+    good = program_to_dict(Program("p", (ObjectSpec("x", 8, "fast"),), (TaskSpec("a", inputs=("x",), outputs=(OutputSpec("y", 8),)),)))
+    assert program_from_dict(good).name == "p"
+    for bad, needle in (([1, 2], "not an object"), ({k: v for k, v in good.items() if k != "name"}, "key 'name' is missing"),
+                        ({**good, "tasks": None}, "TypeError"), ({**good, "tasks": ["not a task"]}, "Error"),
+                        ({**good, "initial_objects": 5}, "TypeError")):
+        with pytest.raises(ValueError, match=needle) as e:
+            program_from_dict(bad)
+        assert "not a dataflow-rt/v1 program" in str(e.value) and not isinstance(e.value, KeyError)
+    with pytest.raises(ValueError, match="unsupported schema_version"):
+        program_from_dict({**good, "schema_version": "other/v9"})
