@@ -86,6 +86,9 @@ def _hardware(req: WorkloadRequest) -> HardwareSpec:
         raise HTTPException(status_code=404, detail=str(e)) from e
     if req.hardware_overrides:
         from dataclasses import replace
+        for k, v in req.hardware_overrides.items():
+            if isinstance(v, (int, float)) and not isinstance(v, bool) and v < 0:
+                raise HTTPException(status_code=422, detail=f"bad hardware override: {k} = {v} is negative")
         try:
             hw = replace(hw, **req.hardware_overrides)
         except TypeError as e:

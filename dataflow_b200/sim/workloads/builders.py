@@ -28,6 +28,13 @@ class DTypePolicy:
     master: str | None = "fp32"
     moments: str = "fp32"
 
+    def __post_init__(self):
+        for name in ("param", "grad", "activation", "compute", "moments"):
+            if getattr(self, name) not in DTYPE_BYTES:
+                raise ValueError(f"dtype policy: {name} = {getattr(self, name)!r} is not one of {sorted(DTYPE_BYTES)}")
+        if self.master is not None and self.master not in DTYPE_BYTES:
+            raise ValueError(f"dtype policy: master = {self.master!r} is not one of {sorted(DTYPE_BYTES)} (or None)")
+
     def state_bytes_per_param(self, optimizer: str) -> float:
         n_moments = {"adamw": 2, "muon": 1, "sgdm": 1, "sgd": 0, "frozen": 0}[optimizer]
         return (DTYPE_BYTES[self.master] if self.master else 0) + n_moments * DTYPE_BYTES[self.moments]
@@ -40,6 +47,13 @@ class ParallelismConfig:
     ep_group_size: int = 1
     zero_stage: int = 0
 
+    def __post_init__(self):
+        for name in ("dp", "tp", "ep_group_size"):
+            if int(getattr(self, name)) < 1:
+                raise ValueError(f"parallel layout: {name} = {getattr(self, name)} must be at least 1")
+        if self.zero_stage not in (0, 1, 2, 3):
+            raise ValueError(f"parallel layout: zero_stage = {self.zero_stage} must be 0, 1, 2 or 3")
+
 
 @dataclass(frozen=True)
 class TrainingConfig:
@@ -51,6 +65,17 @@ class TrainingConfig:
     recompute: str = "none"                         # none | selective | full
     dtypes: DTypePolicy = field(default_factory=DTypePolicy)
     parallel: ParallelismConfig = field(default_factory=ParallelismConfig)
+
+    def __post_init__(self):
+        if int(self.seq_len) < 1 or int(self.tokens_per_round) < 1 or int(self.rounds) < 1:
+            raise ValueError(f"training shape: seq_len = {self.seq_len}, tokens_per_round = {self.tokens_per_round}, rounds = {self.rounds} "
+                             f"must all be at least 1")
+        if self.seq_len > self.tokens_per_round:
+            raise ValueError(f"training shape: a round of {self.tokens_per_round} tokens cannot hold a sequence of {self.seq_len}")
+        if self.recompute not in ("none", "selective", "full"):
+            raise ValueError(f"recompute = {self.recompute!r} must be none, selective or full")
+        if self.optimizer_placement not in ("interleaved", "tail"):
+            raise ValueError(f"optimizer_placement = {self.optimizer_placement!r} must be interleaved or tail")
 
 
 @dataclass(frozen=True)
@@ -239,7 +264,24 @@ class TrainingBuilder:
 
 
 def trace_training_model(model: ModelSpec, cfg: TrainingConfig) -> WorkloadProgram:
-    return TrainingBuilder(model, cfg).build()
+    tp, ep = cfg.parallel.tp, cfg.parallel.ep_group_size
+    for i, layer in enumerate(model.layers):
+        a, m = layer.attn, layer.mlp
+        if tp > 1:
+            # a tensor-parallel layout cuts heads and hidden columns into equal parts: say which dimension does not divide
+            # (instead of failing on a shape deep inside the traced block)
+            for what, n in (("attention heads", getattr(a, "n_heads", tp)), ("key/value heads", getattr(a, "n_kv_heads", tp)),
+                            ("MLP hidden size", getattr(m, "d_ff", tp))):
+                if a.kind == "none" and "heads" in what:
+                    continue
+                if n and int(n) % tp and not (what == "key/value heads" and int(n) < tp):
+                    raise ValueError(f"layer {i}: {what} = {n} is not divisible by tp = {tp}")
+        if ep > 1 and m.kind == "moe" and int(getattr(m, "n_experts", ep)) % ep:
+            raise ValueError(f"layer {i}: {m.n_experts} experts are not divisible by an expert-parallel group of {ep}")
+    try:
+        return TrainingBuilder(model, cfg).build()
+    except AssertionError as e:
+        raise ValueError(f"the model's shapes do not fit this layout (tp = {tp}, ep = {ep}): {e}") from None
 
 
 # ------------------------------------------------------------------------------------------- model library

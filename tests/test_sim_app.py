@@ -213,3 +213,23 @@ def test_hardware_overrides_change_the_prediction(client):
     eff = client.post("/api/simulate", json={**BODY, "policy": "max_reduce", "timeline": False, "hardware_overrides": {"matmul_efficiency": 0.4}}).json()["summary"]
     assert eff["compute_us_by_kind"]["matmul"] > base["compute_us_by_kind"]["matmul"] * 1.5
     assert client.post("/api/simulate", json={**BODY, "hardware_overrides": {"warp_drive": 9}}).status_code == 422
+
+
+def test_nonsense_inputs_are_refused_with_a_reason_never_a_server_error():
+    from fastapi.testclient import TestClient
+    from dataflow_b200.sim.app.api import create_app
+    c = TestClient(create_app(), raise_server_exceptions=False)
+    base = {"model": "llama3_8b", "hardware": "B200", "fast_memory_gib": 60, "policy": "max_reduce", "timeline": False}
+    cases = {"rounds": {"training": {"rounds": 0}}, "tokens_per_round": {"training": {"tokens_per_round": 0}},
+             "seq_len": {"training": {"seq_len": -4096}}, "cannot hold a sequence": {"training": {"seq_len": 65536, "tokens_per_round": 4096}},
+             "dp": {"training": {"parallel": {"dp": 0}}}, "not divisible by tp": {"training": {"parallel": {"tp": 3}}},
+             "zero_stage": {"training": {"parallel": {"dp": 8, "zero_stage": 9}}}, "recompute": {"training": {"recompute": "sometimes"}},
+             "dtype policy": {"training": {"dtypes": {"compute": "fp3"}}}, "is negative": {"hardware_overrides": {"matmul_efficiency": -1}},
+             "negative-size": {"fast_memory_gib": -3}, "bandwidth": {"hardware_overrides": {"from_slow_gbs": 0, "to_slow_gbs": 0}}}
+    for needle, over in cases.items():
+        r = c.post("/api/simulate", json={**base, **over})
+        assert r.status_code in (404, 422), (needle, r.status_code, r.text[:200])
+        assert needle in str(r.json()["detail"]), (needle, r.json()["detail"])
+    # what is merely unusual still runs: one sequence per round, a budget larger than the device
+    assert c.post("/api/simulate", json={**base, "training": {"seq_len": 4096, "tokens_per_round": 4096}}).status_code == 200
+    assert c.post("/api/simulate", json={**base, "fast_memory_gib": 1e6}).status_code == 200
