@@ -136,3 +136,27 @@ def test_task_profiles_soak_first_and_cache_under_their_own_key(tmp_path, monkey
             assert c.copies == 0
     finally:
         tr.close()
+
+
+def test_user_mistakes_end_in_one_line_not_a_traceback(capsys):
+    """An unknown preset, optimizer or data scheme, a flag below its minimum, a budget nothing fits: exit code 2 and one line
+    that says what to fix."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("train_tool", os.path.join(root, "tools", "train", "train.py"))
+    tool = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tool)
+    base = ["train", "--steps", "1", "--device", "cpu"]
+    for extra, needle in ((["--preset", "nope"], "unknown preset 'nope'"),
+                          (["--preset", "llama3:tiny", "--data", "nosuch:thing"], "unknown data scheme 'nosuch'"),
+                          (["--preset", "llama3:tiny", "--fast-budget", "0.0001"], "fits the budget"),
+                          (["--preset", "llama3:tiny", "--resume", "/nonexistent/dir"], "no complete checkpoint")):
+        assert tool.main(base + extra) == 2
+        err = capsys.readouterr().err
+        assert needle in err and "Traceback" not in err, err
+    for extra, needle in ((["--preset", "llama3:tiny", "--opt", "lion"], "unknown optimizer"), (["--preset", "llama3:tiny", "--batch", "0"], "must be at least 1"),
+                          (["--preset", "llama3:tiny", "--ga-rounds", "0"], "must be at least 1")):
+        with pytest.raises(SystemExit) as e:
+            tool.main(base + extra)
+        assert e.value.code == 2 and needle in capsys.readouterr().err

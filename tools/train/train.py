@@ -250,8 +250,30 @@ def main(argv=None) -> int:
     p.add_argument("b")
     p.add_argument("--band", default="bf16")
     a = ap.parse_args(argv)
-    return {"train": cmd_train, "reference": cmd_reference, "smoke": cmd_smoke, "parity": cmd_parity,
-            "scaling": cmd_scaling, "peek": cmd_peek, "compare": cmd_compare}[a.cmd](a, argv)
+    if getattr(a, "opt", None):
+        from dataflow_b200.blocks import optim
+        known = tuple(optim.OPTIMIZERS) + tuple(optim._PLUGIN_OPTIMIZERS)
+        if a.opt not in known:
+            ap.error(f"--opt {a.opt}: unknown optimizer (known: {', '.join(known)})")
+    # flags that cannot mean anything are refused before a model is built
+    for flag, low in (("steps", 0), ("ga_rounds", 1), ("batch", 1), ("max_seq_len", 2), ("gpus", 1), ("fast_budget", 0.0), ("backing_budget", 0.0),
+                      ("checkpoint_every", 0), ("warmup_steps", 0)):
+        v = getattr(a, flag, None)
+        if v is not None and not isinstance(v, str) and v < low:
+            ap.error(f"--{flag.replace('_', '-')} {v}: must be at least {low}")
+    run = {"train": cmd_train, "reference": cmd_reference, "smoke": cmd_smoke, "parity": cmd_parity,
+           "scaling": cmd_scaling, "peek": cmd_peek, "compare": cmd_compare}[a.cmd]
+    if os.environ.get("DATAFLOW_TRACEBACK") == "1":
+        return run(a, argv)
+    from dataflow_b200.sim.policies.pressurefit import PlanningError
+    try:
+        return run(a, argv)
+    except (KeyError, FileNotFoundError, PlanningError) as e:
+        # a name that does not exist (preset, optimizer, data scheme, checkpoint) or a budget nothing fits: the user's to fix,
+        # one line instead of a traceback (DATAFLOW_TRACEBACK=1 shows where it was raised)
+        msg = e.args[0] if isinstance(e, KeyError) and e.args else str(e)
+        print(f"train.py {a.cmd}: {msg}", file=sys.stderr)
+        return 2
 
 
 if __name__ == "__main__":
