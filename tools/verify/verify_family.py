@@ -53,7 +53,10 @@ def main(argv=None) -> int:
     ap.add_argument("--rungs", default=None, help="comma list of: structure, step, gradients, block, recompute, accumulation, invariance, client")
     ap.add_argument("--through-daemon", action="store_true", help="add the client rung (a daemon in this process, CPU backend)")
     a = ap.parse_args(argv)
-    want = set(a.rungs.split(",")) if a.rungs else {"structure", "step", "gradients", "block", "recompute", "accumulation", "invariance"}
+    rungs = ("structure", "step", "gradients", "block", "recompute", "accumulation", "invariance", "client")
+    want = {r.strip() for r in a.rungs.split(",") if r.strip()} if a.rungs else set(rungs[:-1])
+    if want - set(rungs):
+        ap.error(f"--rungs {','.join(sorted(want - set(rungs)))}: no such rung (known: {', '.join(rungs)})")
     if a.through_daemon:
         want.add("client")
     import importlib
@@ -66,6 +69,8 @@ def main(argv=None) -> int:
         return 0
     if not a.family:
         ap.error("--family or --list")
+    if a.family not in all_families():
+        ap.error(f"--family {a.family}: unknown model family (known: {', '.join(sorted(all_families()))}; --plugin MODULE registers more)")
     problems = audit(a.family)
     for p in problems:
         print("audit:", p)
